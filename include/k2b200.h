@@ -1,0 +1,241 @@
+/* k2b200.h - C-ABI of libk2b200.so, the B200 (sm_100a) backend for k2's
+ * dense-intersection / total-score path.
+ *
+ * Every entry point takes plain pointers and sizes.  Pointers are DEVICE
+ * pointers unless the name starts with h_ (HOST).  All device memory - inputs,
+ * outputs and workspaces - is owned by the caller; the library never allocates
+ * device memory.  `stream` is a cudaStream_t passed as void*.  Functions
+ * return 0 on success or a non-zero k2b200_status; k2b200_last_error() then
+ * describes the failure (the reference raises a C++ exception, which its Python
+ * layer surfaces as RuntimeError - the Python host layer of this library does
+ * the same with the status).
+ *
+ * Data layouts are k2's:
+ *   Arc      16 bytes {int32 src_state, int32 dest_state, int32 label, float
+ *            score}; states are relative to the first state of their FSA
+ *            (k2/csrc/fsa.h:31-63).
+ *   FsaVec   row_splits1[num_fsas+1] (fsa -> state), row_ids1[num_states],
+ *            row_splits2[num_states+1] (state -> arc), row_ids2[num_arcs],
+ *            arcs[num_arcs] (k2/csrc/ragged.h:330, fsa.h:113-120).
+ *   DenseFsaVec  scores[rows, cols] contiguous float32 with cols = C+1 and
+ *            column = label+1, plus row_splits[num_seqs+1]; each sequence has
+ *            its T frames followed by one final row [0,-inf,...]
+ *            (k2/csrc/fsa.h:138-185, k2/python/k2/dense_fsa_vec.py:43-145).
+ */
+#ifndef K2B200_H_
+#define K2B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum {
+  K2B200_OK = 0,
+  K2B200_INVALID_ARGUMENT = 1,
+  K2B200_CUDA_ERROR = 2,
+  K2B200_WORKSPACE_TOO_SMALL = 3,
+  K2B200_TOO_LARGE = 4
+} k2b200_status;
+
+/* Text of the last error on the calling thread. */
+const char *k2b200_last_error(void);
+/* ABI version of the library (bumped on any signature change). */
+int32_t k2b200_abi_version(void);
+
+/* ---------------------------------------------------------------------------
+ * Ragged helpers.
+ * ------------------------------------------------------------------------- */
+
+/* row_ids[k] = row r with row_splits[r] <= k < row_splits[r+1].
+ * Replaces k2::RowSplitsToRowIds, k2/csrc/utils.cu:75-130. */
+int32_t k2b200_row_splits_to_row_ids(const int32_t *row_splits, int32_t num_rows,
+                                     int32_t *row_ids, int32_t num_elems,
+                                     void *stream);
+
+/* Exclusive sum of n int32: out[0..n], out[n] = total; in and out may alias.
+ * tmp must hold k2b200_exclusive_sum_tmp_bytes(n) bytes.
+ * Replaces k2::ExclusiveSum, k2/csrc/utils_inl.h:40-60 (cub::DeviceScan). */
+size_t k2b200_exclusive_sum_tmp_bytes(int64_t n);
+int32_t k2b200_exclusive_sum(const int32_t *in, int32_t *out, int64_t n, void *tmp,
+                             void *stream);
+
+/* Incoming-arc index of an FsaVec: in_splits[num_states+1], in_arcs[num_arcs];
+ * the arcs entering each state, in increasing arc index.
+ * Replaces k2::GetDestStates + k2::GetIncomingArcs,
+ * k2/csrc/fsa_utils.cu:650-677, :901-928 (called from
+ * k2/csrc/intersect_dense.cu:139-142 and k2/python/k2/fsa.py:529-562). */
+size_t k2b200_fsa_incoming_tmp_bytes(int32_t num_states, int32_t num_arcs);
+int32_t k2b200_fsa_incoming(const int32_t *row_splits1, const int32_t *row_ids1,
+                            const int32_t *row_ids2, const void *arcs,
+                            int32_t num_fsas, int32_t num_states, int32_t num_arcs,
+                            int32_t *in_splits, int32_t *in_arcs, void *tmp,
+                            void *stream);
+
+/* ---------------------------------------------------------------------------
+ * intersect_dense.
+ * Replaces k2::IntersectDense / MultiGraphDenseIntersect,
+ * k2/csrc/intersect_dense.cu:100-1073, as bound by _k2.intersect_dense,
+ * k2/python/csrc/torch/fsa_algo.cu:224-253.
+ *
+ * Protocol (one host synchronisation, to size the outputs):
+ *   1. k2b200_intersect_dense_workspace_bytes(&args, &bytes)
+ *   2. k2b200_intersect_dense_prune(&args, ws, bytes, stream, &ns, &na, &beam)
+ *      runs the Viterbi forward/backward recursion over all frames, applies the
+ *      output beam (shrinking it like the reference when max_states / max_arcs
+ *      would be exceeded), numbers the surviving states and arcs and returns
+ *      their counts;
+ *   3. k2b200_intersect_dense_emit(&args, ws, bytes, stream, &out) with output
+ *      buffers of those sizes writes the lattice and both arc maps.
+ * ------------------------------------------------------------------------- */
+typedef struct {
+  /* a_fsas: the graphs, one per entry of a_to_b_map */
+  int32_t num_fsas, num_states, num_arcs;
+  const int32_t *a_row_splits1;   /* [num_fsas+1] */
+  const int32_t *a_row_splits2;   /* [num_states+1] */
+  const void *a_arcs;             /* [num_arcs] Arc */
+  const int32_t *a_in_splits;     /* [num_states+1] from k2b200_fsa_incoming */
+  const int32_t *a_in_arcs;       /* [num_arcs] */
+  const int32_t *h_a_row_splits1; /* HOST copy of a_row_splits1 */
+  const int32_t *h_a_arc_splits;  /* HOST [num_fsas+1]: a_row_splits2[a_row_splits1[i]] */
+  /* b_fsas: the DenseFsaVec */
+  const float *scores;            /* [rows, cols] contiguous */
+  int32_t rows, cols, num_seqs;
+  const int32_t *h_b_row_splits;  /* HOST [num_seqs+1] */
+  /* HOST [num_fsas], non-decreasing, or NULL for the identity map */
+  const int32_t *h_a_to_b_map;
+  float output_beam;
+  int32_t max_states, max_arcs;
+  /* 0 = choose automatically, 1 = one launch per frame (any graph size),
+   * 2 = persistent frame-synchronous kernel (graphs that fit in shared memory) */
+  int32_t viterbi_mode;
+} k2b200_intersect_args;
+
+typedef struct {
+  int32_t *row_splits1; /* [num_fsas+1] */
+  int32_t *row_ids1;    /* [num_states_out] */
+  int32_t *row_splits2; /* [num_states_out+1] */
+  int32_t *row_ids2;    /* [num_arcs_out] */
+  void *arcs;           /* [num_arcs_out] Arc */
+  int32_t *arc_map_a;   /* [num_arcs_out] arc idx012 in a_fsas, may be NULL */
+  int32_t *arc_map_b;   /* [num_arcs_out] offset into scores, may be NULL */
+  /* Optional (may be NULL): the time layering of the lattice, used by
+   * k2b200_fsa_scores.  level_offsets[num_fsas+1] gives, per FSA, its range in
+   * level_splits; level_splits[total_levels+1] gives the first state (idx01)
+   * of every (fsa, frame) layer, total_levels = sum_i (T_i + 2). */
+  int32_t *level_offsets;
+  int32_t *level_splits;
+} k2b200_lattice_out;
+
+int32_t k2b200_intersect_dense_workspace_bytes(const k2b200_intersect_args *args,
+                                               size_t *bytes,
+                                               int64_t *total_levels);
+int32_t k2b200_intersect_dense_prune(const k2b200_intersect_args *args, void *workspace,
+                                     size_t workspace_bytes, void *stream,
+                                     int32_t *num_states_out, int32_t *num_arcs_out,
+                                     float *beam_used);
+int32_t k2b200_intersect_dense_emit(const k2b200_intersect_args *args, void *workspace,
+                                    size_t workspace_bytes, void *stream,
+                                    const k2b200_lattice_out *out);
+
+/* ---------------------------------------------------------------------------
+ * Forward / backward scores of a layered (top-sorted, acyclic) FsaVec.
+ * Replaces k2::GetForwardScores / GetBackwardScores,
+ * k2/csrc/fsa_utils.cu:1124-1278, :1345-1454 (bound at
+ * k2/python/csrc/torch/fsa.cu:262-341), with the layering taken from
+ * level_offsets/level_splits instead of GetStateBatches (:679-899).
+ *
+ * use_double selects float64 or float32 state scores (`forward` / `backward`
+ * point to num_states elements of that type; either may be NULL to skip that
+ * direction).  log_semiring != 0: log-sum-exp; == 0: max, and entering_arcs
+ * (may be NULL) receives for every state the best entering arc (ties go to the
+ * highest arc index; -1 when no arc enters), as
+ * k2/csrc/ragged_ops_inl.h:627-657.
+ * ------------------------------------------------------------------------- */
+int32_t k2b200_fsa_scores(const int32_t *row_splits1, const int32_t *row_splits2,
+                          const int32_t *row_ids2, const void *arcs,
+                          const int32_t *in_splits, const int32_t *in_arcs,
+                          const int32_t *level_offsets, const int32_t *level_splits,
+                          int32_t num_fsas, int32_t num_states, int32_t num_arcs,
+                          int32_t log_semiring, int32_t use_double, void *forward,
+                          void *backward, int32_t *entering_arcs, void *stream);
+
+/* tot_scores[i] = forward score of the last state of FSA i, -inf if empty.
+ * Replaces k2::GetTotScores, k2/csrc/fsa_utils.cu:1809-1837. */
+int32_t k2b200_fsa_tot_scores(const int32_t *row_splits1, int32_t num_fsas,
+                              int32_t use_double, const void *forward,
+                              void *tot_scores, void *stream);
+
+/* arc_post[a] = score + forward[src] + backward[dest] - 0.5*(forward[final] +
+ * backward[start]).  Replaces k2::GetArcPost, k2/csrc/fsa_utils.cu:1839-1901. */
+int32_t k2b200_fsa_arc_post(const int32_t *row_splits1, const int32_t *row_ids1,
+                            const int32_t *row_ids2, const void *arcs,
+                            int32_t num_fsas, int32_t num_arcs, int32_t use_double,
+                            const void *forward, const void *backward,
+                            void *arc_post, void *stream);
+
+/* grad[a] = exp(arc_post[a]) * tot_scores_grad[fsa(a) * grad_stride]; float32
+ * output.  Replaces GetTotScoresLogBackward,
+ * k2/python/csrc/torch/fsa.cu:544-592 (grad_stride is 0 when autograd expanded
+ * the gradient of a sum, :565-566). */
+int32_t k2b200_tot_scores_log_backward(const int32_t *row_ids1, const int32_t *row_ids2,
+                                       int32_t num_arcs, int32_t use_double,
+                                       const void *arc_post,
+                                       const void *tot_scores_grad,
+                                       int64_t grad_stride, float *arc_grad,
+                                       void *stream);
+
+/* grad (zero-filled here) gets tot_scores_grad[fsa] on the arcs of the best
+ * paths.  Replaces GetTotScoresTropicalBackward,
+ * k2/python/csrc/torch/fsa.cu:493-534. */
+int32_t k2b200_tot_scores_tropical_backward(const int32_t *row_ids1,
+                                            const int32_t *row_ids2, int32_t num_arcs,
+                                            const int32_t *best_arcs,
+                                            int32_t num_best_arcs, int32_t use_double,
+                                            const void *tot_scores_grad,
+                                            int64_t grad_stride, float *arc_grad,
+                                            void *stream);
+
+/* in_out[index[k]] += value[k] for index[k] >= 0 (atomic float adds).
+ * Replaces k2::IndexAdd, k2/csrc/tensor_ops.cu:304-334, as bound by
+ * _k2.index_add, k2/python/csrc/torch/index_add.cu:38-71, and used by
+ * _IntersectDenseFunction.backward, k2/python/k2/autograd.py:649-650. */
+int32_t k2b200_index_add(const int32_t *index, const float *value, int32_t n,
+                         float *in_out, int64_t in_out_size, void *stream);
+
+/* out[k] = index[k] >= 0 ? src[index[k]] : 0 (int32).  Replaces the 1-D
+ * _k2.index_select used to carry arc attributes through arc_map_a,
+ * k2/python/csrc/torch/index_select.cu:56-92 (autograd.py:580-590). */
+int32_t k2b200_index_select_i32(const int32_t *src, int64_t src_size,
+                                const int32_t *index, int32_t n, int32_t *out,
+                                void *stream);
+
+/* Best path per FSA from entering_arcs (see k2b200_fsa_scores): path_splits
+ * [num_fsas+1] and best_arcs (arc idx012 in path order; capacity: the number
+ * of states) are written on the device; the total number of best-path arcs is
+ * path_splits[num_fsas].  An FSA whose trace does not reach its start state
+ * gets an empty path.  tmp: k2b200_shortest_path_tmp_bytes(num_fsas) bytes.
+ * Replaces k2::ShortestPath, k2/csrc/fsa_algo.cu:869-1144. */
+size_t k2b200_shortest_path_tmp_bytes(int32_t num_fsas);
+int32_t k2b200_shortest_path(const int32_t *row_splits1, const void *arcs,
+                             const int32_t *entering_arcs, int32_t num_fsas,
+                             int32_t *path_splits, int32_t *best_arcs, void *tmp,
+                             void *stream);
+
+/* Per-FSA property bits (k2/csrc/fsa.h:75-101) and their AND.
+ * Replaces k2::GetFsaVecBasicProperties, k2/csrc/fsa.cu:54-217.  tmp must hold
+ * k2b200_fsa_properties_tmp_bytes(...) bytes; properties[num_fsas+1] is written
+ * on the device with the AND over FSAs in the last entry. */
+size_t k2b200_fsa_properties_tmp_bytes(int32_t num_fsas, int32_t num_states);
+int32_t k2b200_fsa_properties(const int32_t *row_splits1, const int32_t *row_ids1,
+                              const int32_t *row_splits2, const int32_t *row_ids2,
+                              const void *arcs, int32_t num_fsas, int32_t num_states,
+                              int32_t num_arcs, int32_t *properties, void *tmp,
+                              void *stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* K2B200_H_ */

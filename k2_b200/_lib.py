@@ -1,0 +1,133 @@
+"""ctypes binding of libk2b200.so (the C-ABI declared in include/k2b200.h).
+
+There is no CPU path and no fallback: importing this module fails loudly when the
+CUDA library has not been built.
+"""
+import ctypes
+import os
+
+import torch
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "libk2b200.so")
+
+if not os.path.exists(LIB_PATH):
+    raise ImportError(
+        f"{LIB_PATH} not found: build it with `python -m k2_b200.build` "
+        "(nvcc, sm_100a). k2_b200 has no CPU or PyTorch fallback.")
+
+lib = ctypes.CDLL(LIB_PATH)
+
+c_i32 = ctypes.c_int32
+c_i64 = ctypes.c_int64
+c_vp = ctypes.c_void_p
+c_sz = ctypes.c_size_t
+c_f32 = ctypes.c_float
+
+
+class IntersectArgs(ctypes.Structure):
+    _fields_ = [
+        ("num_fsas", c_i32), ("num_states", c_i32), ("num_arcs", c_i32),
+        ("a_row_splits1", c_vp), ("a_row_splits2", c_vp), ("a_arcs", c_vp),
+        ("a_in_splits", c_vp), ("a_in_arcs", c_vp),
+        ("h_a_row_splits1", c_vp), ("h_a_arc_splits", c_vp),
+        ("scores", c_vp), ("rows", c_i32), ("cols", c_i32), ("num_seqs", c_i32),
+        ("h_b_row_splits", c_vp), ("h_a_to_b_map", c_vp),
+        ("output_beam", c_f32), ("max_states", c_i32), ("max_arcs", c_i32),
+        ("viterbi_mode", c_i32),
+    ]
+
+
+class LatticeOut(ctypes.Structure):
+    _fields_ = [
+        ("row_splits1", c_vp), ("row_ids1", c_vp), ("row_splits2", c_vp), ("row_ids2", c_vp),
+        ("arcs", c_vp), ("arc_map_a", c_vp), ("arc_map_b", c_vp),
+        ("level_offsets", c_vp), ("level_splits", c_vp),
+    ]
+
+
+def _sig(name, restype, argtypes):
+    fn = getattr(lib, name)
+    fn.restype = restype
+    fn.argtypes = argtypes
+    return fn
+
+
+_sig("k2b200_last_error", ctypes.c_char_p, [])
+_sig("k2b200_abi_version", c_i32, [])
+_sig("k2b200_row_splits_to_row_ids", c_i32, [c_vp, c_i32, c_vp, c_i32, c_vp])
+_sig("k2b200_exclusive_sum_tmp_bytes", c_sz, [c_i64])
+_sig("k2b200_exclusive_sum", c_i32, [c_vp, c_vp, c_i64, c_vp, c_vp])
+_sig("k2b200_fsa_incoming_tmp_bytes", c_sz, [c_i32, c_i32])
+_sig("k2b200_fsa_incoming", c_i32,
+     [c_vp, c_vp, c_vp, c_vp, c_i32, c_i32, c_i32, c_vp, c_vp, c_vp, c_vp])
+_sig("k2b200_intersect_dense_workspace_bytes", c_i32,
+     [ctypes.POINTER(IntersectArgs), ctypes.POINTER(c_sz), ctypes.POINTER(c_i64)])
+_sig("k2b200_intersect_dense_prune", c_i32,
+     [ctypes.POINTER(IntersectArgs), c_vp, c_sz, c_vp, ctypes.POINTER(c_i32),
+      ctypes.POINTER(c_i32), ctypes.POINTER(c_f32)])
+_sig("k2b200_intersect_dense_emit", c_i32,
+     [ctypes.POINTER(IntersectArgs), c_vp, c_sz, c_vp, ctypes.POINTER(LatticeOut)])
+_sig("k2b200_fsa_scores", c_i32,
+     [c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_i32, c_i32, c_i32, c_i32, c_i32, c_vp,
+      c_vp, c_vp, c_vp])
+_sig("k2b200_fsa_tot_scores", c_i32, [c_vp, c_i32, c_i32, c_vp, c_vp, c_vp])
+_sig("k2b200_fsa_arc_post", c_i32,
+     [c_vp, c_vp, c_vp, c_vp, c_i32, c_i32, c_i32, c_vp, c_vp, c_vp, c_vp])
+_sig("k2b200_tot_scores_log_backward", c_i32,
+     [c_vp, c_vp, c_i32, c_i32, c_vp, c_vp, c_i64, c_vp, c_vp])
+_sig("k2b200_tot_scores_tropical_backward", c_i32,
+     [c_vp, c_vp, c_i32, c_vp, c_i32, c_i32, c_vp, c_i64, c_vp, c_vp])
+_sig("k2b200_index_add", c_i32, [c_vp, c_vp, c_i32, c_vp, c_i64, c_vp])
+_sig("k2b200_index_select_i32", c_i32, [c_vp, c_i64, c_vp, c_i32, c_vp, c_vp])
+_sig("k2b200_shortest_path_tmp_bytes", c_sz, [c_i32])
+_sig("k2b200_shortest_path", c_i32, [c_vp, c_vp, c_vp, c_i32, c_vp, c_vp, c_vp, c_vp])
+_sig("k2b200_fsa_properties_tmp_bytes", c_sz, [c_i32, c_i32])
+_sig("k2b200_fsa_properties", c_i32,
+     [c_vp, c_vp, c_vp, c_vp, c_vp, c_i32, c_i32, c_i32, c_vp, c_vp, c_vp])
+
+EXPORTED = [
+    "k2b200_last_error", "k2b200_abi_version", "k2b200_row_splits_to_row_ids",
+    "k2b200_exclusive_sum_tmp_bytes", "k2b200_exclusive_sum", "k2b200_fsa_incoming_tmp_bytes",
+    "k2b200_fsa_incoming", "k2b200_intersect_dense_workspace_bytes",
+    "k2b200_intersect_dense_prune", "k2b200_intersect_dense_emit", "k2b200_fsa_scores",
+    "k2b200_fsa_tot_scores", "k2b200_fsa_arc_post", "k2b200_tot_scores_log_backward",
+    "k2b200_tot_scores_tropical_backward", "k2b200_index_add", "k2b200_index_select_i32",
+    "k2b200_shortest_path_tmp_bytes", "k2b200_shortest_path",
+    "k2b200_fsa_properties_tmp_bytes", "k2b200_fsa_properties",
+]
+
+
+def check(status: int) -> None:
+    """The reference raises a C++ exception that Python sees as RuntimeError
+    (k2/csrc/log.h:196-203); a non-zero status is surfaced the same way."""
+    if status != 0:
+        raise RuntimeError(lib.k2b200_last_error().decode(errors="replace"))
+
+
+def ptr(t) -> int:
+    """Device (or host) address of a tensor, None -> NULL."""
+    if t is None:
+        return None
+    return t.data_ptr()
+
+
+def stream_of(device) -> int:
+    return torch.cuda.current_stream(device).cuda_stream
+
+
+def require_cuda(t: torch.Tensor, what: str) -> None:
+    if not t.is_cuda:
+        raise RuntimeError(
+            f"{what} must be a CUDA tensor: k2_b200 runs on sm_100a only and has no CPU path")
+
+
+def launch_count() -> int:
+    return _launches[0]
+
+
+_launches = [0]
+
+
+def note_launches(n: int) -> None:
+    _launches[0] += n

@@ -1,0 +1,236 @@
+"""The two autograd Functions of the path, with the reference's contracts
+(k2/python/k2/autograd.py:30-117 `_GetTotScoresFunction`, :511-664
+`_IntersectDenseFunction`), and `intersect_dense` itself (:751-824)."""
+import ctypes
+from typing import List, Optional, Tuple
+
+import numpy as np
+import torch
+
+from . import _lib
+from .dense_fsa_vec import DenseFsaVec
+from .fsa import Fsa
+from .ragged import RaggedArc
+
+
+def _index_add(index: torch.Tensor, value: torch.Tensor, in_out: torch.Tensor) -> None:
+    """in_out[index[k]] += value[k] (k2/python/csrc/torch/index_add.cu:38-71)."""
+    assert index.dtype == torch.int32 and in_out.dtype == torch.float32
+    value = value.to(torch.float32).contiguous()
+    with torch.cuda.device(in_out.device):
+        _lib.check(_lib.lib.k2b200_index_add(_lib.ptr(index), _lib.ptr(value), index.numel(),
+                                              _lib.ptr(in_out), in_out.numel(),
+                                              _lib.stream_of(in_out.device)))
+    _lib.note_launches(1)
+
+
+def index_select(src: torch.Tensor, index: torch.Tensor) -> torch.Tensor:
+    """ans[i] = src[index[i]], 0 where index[i] == -1 (1-D int32 `src`;
+    k2/python/csrc/torch/index_select.cu:56-92)."""
+    assert index.dtype == torch.int32
+    if src.dtype != torch.int32 or src.ndim != 1:
+        # other dtypes are carried with torch's own gather (attribute plumbing)
+        ans = src.index_select(0, index.clamp(min=0).long())
+        ans[index < 0] = 0
+        return ans
+    src = src.contiguous()
+    out = torch.empty(index.numel(), dtype=torch.int32, device=src.device)
+    with torch.cuda.device(src.device):
+        _lib.check(_lib.lib.k2b200_index_select_i32(_lib.ptr(src), src.numel(), _lib.ptr(index),
+                                                     index.numel(), _lib.ptr(out),
+                                                     _lib.stream_of(src.device)))
+    _lib.note_launches(1)
+    return out
+
+
+def _intersect_dense_arcs(a: RaggedArc, b: DenseFsaVec, a_to_b_map: Optional[torch.Tensor],
+                          output_beam: float, max_states: int, max_arcs: int,
+                          viterbi_mode: int = 0):
+    """The `_k2.intersect_dense` call (k2/python/csrc/torch/fsa_algo.cu:224-253):
+    returns (RaggedArc lattice, arc_map_a, arc_map_b)."""
+    _lib.require_cuda(a.values(), "a_fsas")
+    _lib.require_cuda(b.scores, "b_fsas.scores")
+    dev = a.device
+    if b.scores.device != dev:
+        raise RuntimeError("a_fsas and b_fsas must be on the same device")
+    scores = b.scores.detach()
+    assert scores.is_contiguous() and scores.dtype == torch.float32
+    in_splits, in_arcs = a.incoming()
+    h_rs1 = np.ascontiguousarray(a.h_row_splits1, dtype=np.int32)
+    h_as = np.ascontiguousarray(a.h_arc_splits, dtype=np.int32)
+    h_brs = b.h_row_splits
+    h_map = None
+    if a_to_b_map is not None:
+        assert a_to_b_map.ndim == 1 and a_to_b_map.dtype == torch.int32
+        h_map = np.ascontiguousarray(a_to_b_map.detach().cpu().numpy(), dtype=np.int32)
+        if h_map.shape[0] != a.num_fsas:
+            raise RuntimeError(
+                f"a_fsas.Dim0() ({a.num_fsas}) != a_to_b_map.Dim() ({h_map.shape[0]})")
+    args = _lib.IntersectArgs(
+        num_fsas=a.num_fsas, num_states=a.num_states, num_arcs=a.num_elements(),
+        a_row_splits1=_lib.ptr(a._row_splits1), a_row_splits2=_lib.ptr(a._row_splits2),
+        a_arcs=_lib.ptr(a.values()), a_in_splits=_lib.ptr(in_splits),
+        a_in_arcs=_lib.ptr(in_arcs), h_a_row_splits1=h_rs1.ctypes.data,
+        h_a_arc_splits=h_as.ctypes.data, scores=_lib.ptr(scores), rows=scores.shape[0],
+        cols=scores.shape[1], num_seqs=len(h_brs) - 1, h_b_row_splits=h_brs.ctypes.data,
+        h_a_to_b_map=None if h_map is None else h_map.ctypes.data,
+        output_beam=float(output_beam), max_states=int(min(max_states, 2**31 - 1)),
+        max_arcs=int(min(max_arcs, 2**31 - 1)), viterbi_mode=viterbi_mode)
+    nbytes = ctypes.c_size_t()
+    levels = ctypes.c_int64()
+    _lib.check(_lib.lib.k2b200_intersect_dense_workspace_bytes(ctypes.byref(args),
+                                                                ctypes.byref(nbytes),
+                                                                ctypes.byref(levels)))
+    ws = torch.empty(nbytes.value, dtype=torch.uint8, device=dev)
+    ns, na, beam = ctypes.c_int32(), ctypes.c_int32(), ctypes.c_float()
+    stream = _lib.stream_of(dev)
+    with torch.cuda.device(dev):
+        _lib.check(_lib.lib.k2b200_intersect_dense_prune(ctypes.byref(args), _lib.ptr(ws),
+                                                          nbytes.value, stream, ctypes.byref(ns),
+                                                          ctypes.byref(na), ctypes.byref(beam)))
+        ns, na = ns.value, na.value
+        i32 = dict(dtype=torch.int32, device=dev)
+        row_splits1 = torch.empty(a.num_fsas + 1, **i32)
+        row_ids1 = torch.empty(ns, **i32)
+        row_splits2 = torch.empty(ns + 1, **i32)
+        row_ids2 = torch.empty(na, **i32)
+        values = torch.empty((na, 4), **i32)
+        arc_map_a = torch.empty(na, **i32)
+        arc_map_b = torch.empty(na, **i32)
+        level_offsets = torch.empty(a.num_fsas + 1, **i32)
+        level_splits = torch.empty(levels.value + 1, **i32)
+        out = _lib.LatticeOut(
+            row_splits1=_lib.ptr(row_splits1), row_ids1=_lib.ptr(row_ids1),
+            row_splits2=_lib.ptr(row_splits2), row_ids2=_lib.ptr(row_ids2),
+            arcs=_lib.ptr(values), arc_map_a=_lib.ptr(arc_map_a), arc_map_b=_lib.ptr(arc_map_b),
+            level_offsets=_lib.ptr(level_offsets), level_splits=_lib.ptr(level_splits))
+        _lib.check(_lib.lib.k2b200_intersect_dense_emit(ctypes.byref(args), _lib.ptr(ws),
+                                                         nbytes.value, stream, ctypes.byref(out)))
+    lattice = RaggedArc(values, row_splits1, row_splits2, row_ids1, row_ids2)
+    lattice._levels = (level_offsets, level_splits)
+    lattice.output_beam_used = beam.value
+    return lattice, arc_map_a, arc_map_b
+
+
+class _GetTotScoresFunction(torch.autograd.Function):
+
+    @staticmethod
+    def forward(ctx, fsas: Fsa, log_semiring: bool, use_double_scores: bool,
+                unused_scores: torch.Tensor) -> torch.Tensor:
+        tot_scores = fsas._get_tot_scores(use_double_scores=use_double_scores,
+                                          log_semiring=log_semiring).detach()
+        ctx.fsas = fsas
+        ctx.log_semiring = log_semiring
+        ctx.use_double_scores = use_double_scores
+        ctx.save_for_backward(unused_scores)
+        return tot_scores
+
+    @staticmethod
+    def backward(ctx, tot_scores_grad: torch.Tensor):
+        fsas = ctx.fsas
+        log_semiring = ctx.log_semiring
+        use_double_scores = ctx.use_double_scores
+        arcs = fsas.arcs
+        dev = arcs.device
+        na = arcs.num_elements()
+        scores_grad = torch.empty(na, dtype=torch.float32, device=dev)
+        # the gradient of a reduction arrives expanded: element stride may be 0
+        # (k2/python/csrc/torch/fsa.cu:515-516, :565-566)
+        dtype = torch.float64 if use_double_scores else torch.float32
+        if tot_scores_grad.dtype != dtype:
+            tot_scores_grad = tot_scores_grad.to(dtype)
+        stride = tot_scores_grad.stride(0) if tot_scores_grad.numel() > 0 else 0
+        rid1 = arcs.row_ids(1 - arcs.single)
+        rid2 = arcs.row_ids(2 - arcs.single)
+        with torch.cuda.device(dev):
+            if log_semiring is False:
+                from .fsa_algo import _shortest_path_arcs
+                _, best_arcs = _shortest_path_arcs(fsas, use_double_scores)
+                _lib.check(_lib.lib.k2b200_tot_scores_tropical_backward(
+                    _lib.ptr(rid1), _lib.ptr(rid2), na, _lib.ptr(best_arcs), best_arcs.numel(),
+                    int(use_double_scores), _lib.ptr(tot_scores_grad), stride,
+                    _lib.ptr(scores_grad), _lib.stream_of(dev)))
+            else:
+                arc_post = fsas._get_arc_post(use_double_scores, log_semiring)
+                _lib.check(_lib.lib.k2b200_tot_scores_log_backward(
+                    _lib.ptr(rid1), _lib.ptr(rid2), na, int(use_double_scores),
+                    _lib.ptr(arc_post), _lib.ptr(tot_scores_grad), stride,
+                    _lib.ptr(scores_grad), _lib.stream_of(dev)))
+        _lib.note_launches(1)
+        return None, None, None, scores_grad
+
+
+class _IntersectDenseFunction(torch.autograd.Function):
+
+    @staticmethod
+    def forward(ctx, a_fsas: Fsa, b_fsas: DenseFsaVec, out_fsa: List[Fsa], output_beam: float,
+                max_states: int, max_arcs: int, unused_scores_a: torch.Tensor,
+                unused_scores_b: torch.Tensor, a_to_b_map: Optional[torch.Tensor] = None,
+                seqframe_idx_name: Optional[str] = None,
+                frame_idx_name: Optional[str] = None) -> torch.Tensor:
+        assert len(out_fsa) == 1
+        ragged_arc, arc_map_a, arc_map_b = _intersect_dense_arcs(
+            a_fsas.arcs, b_fsas, a_to_b_map, output_beam, max_states, max_arcs)
+        # the lattice is valid by construction; its property bits are computed on
+        # first use rather than with a host round trip on every call
+        out_fsa[0] = Fsa(ragged_arc, _check=False)
+
+        for name, a_value in a_fsas.named_tensor_attr(include_scores=False):
+            if name == 'labels':
+                continue
+            setattr(out_fsa[0], name, index_select(a_value, arc_map_a))
+        for name, a_value in a_fsas.named_non_tensor_attr():
+            setattr(out_fsa[0], name, a_value)
+
+        ctx.arc_map_a = arc_map_a
+        ctx.arc_map_b = arc_map_b
+        ctx.save_for_backward(unused_scores_a, unused_scores_b)
+
+        seqframe_idx = None
+        if frame_idx_name is not None:
+            num_cols = b_fsas.scores.shape[1]
+            seqframe_idx = torch.div(arc_map_b, num_cols, rounding_mode="floor")
+            row_ids = torch.repeat_interleave(
+                torch.arange(b_fsas.dim0(), dtype=torch.int32, device=arc_map_b.device),
+                torch.from_numpy(np.diff(b_fsas.h_row_splits)).to(arc_map_b.device))
+            fsa_idx0 = row_ids[seqframe_idx.long()]
+            frame_idx = seqframe_idx - b_fsas.row_splits[fsa_idx0.long()]
+            assert not hasattr(out_fsa[0], frame_idx_name)
+            setattr(out_fsa[0], frame_idx_name, frame_idx.to(torch.int32))
+        if seqframe_idx_name is not None:
+            if seqframe_idx is None:
+                num_cols = b_fsas.scores.shape[1]
+                seqframe_idx = torch.div(arc_map_b, num_cols, rounding_mode="floor")
+            assert not hasattr(out_fsa[0], seqframe_idx_name)
+            setattr(out_fsa[0], seqframe_idx_name, seqframe_idx)
+
+        return out_fsa[0].scores
+
+    @staticmethod
+    def backward(ctx, out_fsa_grad: torch.Tensor):
+        a_scores, b_scores = ctx.saved_tensors
+        arc_map_a = ctx.arc_map_a
+        arc_map_b = ctx.arc_map_b
+        grad_a = torch.zeros(a_scores.size(0), dtype=torch.float32, device=a_scores.device,
+                             requires_grad=False)
+        grad_b = torch.zeros(*b_scores.shape, dtype=torch.float32, device=b_scores.device,
+                             requires_grad=False).contiguous()
+        _index_add(arc_map_a, out_fsa_grad, grad_a)
+        _index_add(arc_map_b, out_fsa_grad, grad_b.view(-1))
+        return (None, None, None, None, None, None, grad_a, grad_b, None, None, None)
+
+
+def intersect_dense(a_fsas: Fsa, b_fsas: DenseFsaVec, output_beam: float,
+                    max_states: int = 15000000, max_arcs: int = 1073741824,
+                    a_to_b_map: Optional[torch.Tensor] = None,
+                    seqframe_idx_name: Optional[str] = None,
+                    frame_idx_name: Optional[str] = None) -> Fsa:
+    """Intersect graphs with a DenseFsaVec; exact forward-backward pruning to
+    `output_beam` (k2/python/k2/autograd.py:751-824).  `a_fsas` has one graph
+    per entry of `a_to_b_map` (default: one per sequence of `b_fsas`), whose
+    sequences must be sorted by decreasing length."""
+    out_fsa = [0]
+    _IntersectDenseFunction.apply(a_fsas, b_fsas, out_fsa, output_beam, max_states, max_arcs,
+                                  a_fsas.scores, b_fsas.scores, a_to_b_map, seqframe_idx_name,
+                                  frame_idx_name)
+    return out_fsa[0]

@@ -1,0 +1,84 @@
+// Shared declarations of the k2-b200 CUDA library: error reporting, the 16-byte
+// Arc (same layout as k2's, k2/csrc/fsa.h:31-63) and small device helpers.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include <cstdarg>
+#include <cstdio>
+
+namespace k2b {
+
+struct __align__(16) Arc {
+  int32_t src;    // source state, relative to the first state of its FSA
+  int32_t dest;   // destination state, likewise
+  int32_t label;  // -1 = final symbol, 0 = blank/epsilon
+  float score;
+};
+static_assert(sizeof(Arc) == 16, "Arc must be 16 bytes");
+
+// Status codes returned by every entry point of the C-ABI.
+enum Status : int32_t {
+  kOk = 0,
+  kInvalidArgument = 1,
+  kCudaError = 2,
+  kWorkspaceTooSmall = 3,
+  kTooLarge = 4,
+};
+
+void SetError(const char *fmt, ...);
+const char *LastError();
+
+#define K2B_CUDA_OK(expr)                                                      \
+  do {                                                                         \
+    cudaError_t e__ = (expr);                                                  \
+    if (e__ != cudaSuccess) {                                                  \
+      ::k2b::SetError("%s:%d: %s failed: %s", __FILE__, __LINE__, #expr,       \
+                      cudaGetErrorString(e__));                                \
+      return ::k2b::kCudaError;                                                \
+    }                                                                          \
+  } while (0)
+
+#define K2B_REQUIRE(cond, ...)            \
+  do {                                    \
+    if (!(cond)) {                        \
+      ::k2b::SetError(__VA_ARGS__);       \
+      return ::k2b::kInvalidArgument;     \
+    }                                     \
+  } while (0)
+
+#define K2B_FORWARD(expr)                 \
+  do {                                    \
+    int32_t s__ = (expr);                 \
+    if (s__ != ::k2b::kOk) return s__;    \
+  } while (0)
+
+static inline size_t AlignUp(size_t x, size_t a = 256) { return (x + a - 1) / a * a; }
+
+static inline int CeilDiv(int64_t a, int64_t b) { return (int)((a + b - 1) / b); }
+
+// ---- generic ragged primitives (ragged_ops.cu) --------------------------------
+// Exclusive prefix sum of n int32 values into out[0..n] (out[n] = total).  `tmp`
+// must hold ScanTmpInts(n) int32.  in and out may alias.
+size_t ScanTmpInts(int64_t n);
+int32_t ExclusiveSum(const int32_t *in, int32_t *out, int64_t n, int32_t *tmp,
+                     cudaStream_t stream);
+// Same for two interleaved counters (x, y) at once.
+int32_t ExclusiveSum2(const int2 *in, int2 *out, int64_t n, int2 *tmp,
+                      cudaStream_t stream);
+// row_ids[k] = the row r with row_splits[r] <= k < row_splits[r+1].
+int32_t RowSplitsToRowIds(const int32_t *row_splits, int32_t num_rows,
+                          int32_t *row_ids, int32_t num_elems,
+                          cudaStream_t stream);
+
+// Incoming-arc index of an FsaVec: for every state (idx01) the arcs (idx012) that
+// enter it, in increasing arc order.
+//   in_splits [num_states + 1], in_arcs [num_arcs]
+// workspace: IncomingTmpBytes(num_states, num_arcs).
+size_t IncomingTmpBytes(int32_t num_states, int32_t num_arcs);
+int32_t BuildIncoming(const int32_t *row_splits1, const int32_t *row_ids1,
+                      const int32_t *row_ids2, const Arc *arcs, int32_t num_fsas,
+                      int32_t num_states, int32_t num_arcs, int32_t *in_splits,
+                      int32_t *in_arcs, void *tmp, cudaStream_t stream);
+
+}  // namespace k2b

@@ -1,0 +1,40 @@
+// Internal declarations shared by intersect.cu and viterbi_persistent.cu.
+#pragma once
+#include <vector>
+
+#include "../../include/k2b200.h"
+#include "common.cuh"
+
+namespace k2b {
+
+// Per (graph, sequence) pair; built on the host, uploaded once per call.
+struct FsaInfo {
+  int32_t state_off;   // first state (idx01) of the graph in a_fsas
+  int32_t num_states;  // S
+  int32_t arc_off;     // first arc (idx012)
+  int32_t num_arcs;
+  int32_t row0;        // first row of the sequence in `scores`
+  int32_t tk;          // rows of the sequence = frames + 1 (k2's FsaInfo.T)
+  int32_t level_off;   // sum over earlier pairs of (tk + 1)
+  int32_t words;       // ceil(S / 32)
+  int64_t grid_off;    // sum over earlier pairs of (tk + 1) * S
+  int64_t word_off;    // sum over earlier pairs of (tk + 1) * words
+};
+
+struct Layout {
+  std::vector<FsaInfo> infos;
+  int64_t grid_elems = 0, total_words = 0, total_levels = 0;
+  int32_t max_states = 0, max_tk = 0, max_arcs = 0;
+  // byte offsets into the workspace
+  size_t off_infos, off_cutoffs, off_fwd, off_bwd, off_mask, off_counts, off_scan_tmp,
+      off_block_cand, off_totals, total_bytes;
+  int32_t count_blocks;
+};
+
+// viterbi_persistent.cu
+bool PersistentViterbiFits(const Layout &L, const k2b200_intersect_args *a);
+int32_t LaunchPersistentViterbi(const Layout &L, const k2b200_intersect_args *a,
+                                const FsaInfo *d_infos, float *fwd, float *bwd,
+                                cudaStream_t stream);
+
+}  // namespace k2b

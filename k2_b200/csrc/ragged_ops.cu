@@ -1,0 +1,277 @@
+// Generic ragged-array primitives, hand-written for sm_100a: multi-block exclusive
+// sums, row_splits -> row_ids, and the incoming-arc index of an FsaVec.  They take
+// the place of the cub / moderngpu wrappers the reference leans on
+// (k2/csrc/utils_inl.h:40-90 ExclusiveSum, k2/csrc/utils.cu:75-200
+// RowSplitsToRowIds, k2/csrc/fsa_utils.cu:901-928 GetIncomingArcs).
+#include "common.cuh"
+
+namespace k2b {
+
+// ----------------------------------------------------------------------------
+// error text (thread local so concurrent callers do not clobber each other)
+// ----------------------------------------------------------------------------
+static thread_local char g_error[1024] = "";
+
+void SetError(const char *fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_error, sizeof(g_error), fmt, ap);
+  va_end(ap);
+}
+const char *LastError() { return g_error; }
+
+// ----------------------------------------------------------------------------
+// exclusive sum: reduce tiles -> scan the tile sums in one block -> rescan tiles
+// ----------------------------------------------------------------------------
+constexpr int kScanThreads = 256;
+constexpr int kScanItems = 8;
+constexpr int kScanTile = kScanThreads * kScanItems;
+
+__device__ __forceinline__ int32_t Add(int32_t a, int32_t b) { return a + b; }
+__device__ __forceinline__ int2 Add(int2 a, int2 b) { return make_int2(a.x + b.x, a.y + b.y); }
+__device__ __forceinline__ int32_t Sub(int32_t a, int32_t b) { return a - b; }
+__device__ __forceinline__ int2 Sub(int2 a, int2 b) { return make_int2(a.x - b.x, a.y - b.y); }
+__device__ __forceinline__ int32_t Zero(int32_t) { return 0; }
+__device__ __forceinline__ int2 Zero(int2) { return make_int2(0, 0); }
+__device__ __forceinline__ int32_t ShflUp(int32_t v, int d) { return __shfl_up_sync(0xffffffffu, v, d); }
+__device__ __forceinline__ int2 ShflUp(int2 v, int d) {
+  return make_int2(__shfl_up_sync(0xffffffffu, v.x, d), __shfl_up_sync(0xffffffffu, v.y, d));
+}
+
+// Inclusive scan of one value per thread across the block; returns the inclusive
+// prefix, *total receives the block sum.  smem must hold kScanThreads/32 values.
+template <typename T>
+__device__ __forceinline__ T BlockInclusiveScan(T v, T *smem, T *total) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+#pragma unroll
+  for (int d = 1; d < 32; d <<= 1) {
+    T o = ShflUp(v, d);
+    if (lane >= d) v = Add(v, o);
+  }
+  if (lane == 31) smem[warp] = v;
+  __syncthreads();
+  if (warp == 0) {
+    T w = lane < (kScanThreads / 32) ? smem[lane] : Zero(v);
+#pragma unroll
+    for (int d = 1; d < kScanThreads / 32; d <<= 1) {
+      T o = ShflUp(w, d);
+      if (lane >= d) w = Add(w, o);
+    }
+    if (lane < kScanThreads / 32) smem[lane] = w;
+  }
+  __syncthreads();
+  if (warp > 0) v = Add(v, smem[warp - 1]);
+  *total = smem[kScanThreads / 32 - 1];
+  __syncthreads();
+  return v;
+}
+
+template <typename T>
+__global__ void __launch_bounds__(kScanThreads)
+ScanTileSums(const T *__restrict__ in, int64_t n, T *__restrict__ tile_sums) {
+  __shared__ T smem[kScanThreads / 32];
+  int64_t base = (int64_t)blockIdx.x * kScanTile + (int64_t)threadIdx.x * kScanItems;
+  T acc = Zero(T());
+#pragma unroll
+  for (int k = 0; k < kScanItems; ++k)
+    if (base + k < n) acc = Add(acc, in[base + k]);
+  T total;
+  BlockInclusiveScan(acc, smem, &total);
+  if (threadIdx.x == 0) tile_sums[blockIdx.x] = total;
+}
+
+// One block turns tile_sums[0..nb) into exclusive offsets (in place).
+template <typename T>
+__global__ void __launch_bounds__(kScanThreads)
+ScanTileOffsets(T *tile_sums, int32_t nb) {
+  __shared__ T smem[kScanThreads / 32];
+  T running = Zero(T());
+  for (int32_t base = 0; base < nb; base += kScanThreads) {
+    int32_t i = base + threadIdx.x;
+    T v = i < nb ? tile_sums[i] : Zero(T());
+    T total;
+    T inc = BlockInclusiveScan(v, smem, &total);
+    if (i < nb) {
+      T ex = Sub(Add(running, inc), v);  // exclusive = inclusive - own value
+      tile_sums[i] = ex;
+    }
+    running = Add(running, total);
+  }
+}
+
+// out[0..n] (n + 1 entries): exclusive sums, out[n] = grand total.
+template <typename T>
+__global__ void __launch_bounds__(kScanThreads)
+ScanApply(const T *in, T *out, int64_t n, const T *__restrict__ tile_offsets) {
+  __shared__ T smem[kScanThreads / 32];
+  int64_t base = (int64_t)blockIdx.x * kScanTile + (int64_t)threadIdx.x * kScanItems;
+  T vals[kScanItems];
+  T acc = Zero(T());
+#pragma unroll
+  for (int k = 0; k < kScanItems; ++k) {
+    vals[k] = (base + k < n) ? in[base + k] : Zero(T());
+    acc = Add(acc, vals[k]);
+  }
+  T total;
+  T inc = BlockInclusiveScan(acc, smem, &total);
+  // exclusive prefix of this thread = tile offset + inclusive - own sum
+  T run = Sub(Add(tile_offsets[blockIdx.x], inc), acc);
+#pragma unroll
+  for (int k = 0; k < kScanItems; ++k) {
+    if (base + k <= n) out[base + k] = run;
+    run = Add(run, vals[k]);
+  }
+}
+
+size_t ScanTmpInts(int64_t n) { return (size_t)((n + 1 + kScanTile - 1) / kScanTile) + 1; }
+
+template <typename T>
+static int32_t ExclusiveSumImpl(const T *in, T *out, int64_t n, T *tmp, cudaStream_t stream) {
+  if (n < 0) {
+    SetError("ExclusiveSum: negative length");
+    return kInvalidArgument;
+  }
+  int64_t nb64 = (n + 1 + kScanTile - 1) / kScanTile;
+  if (nb64 > 0x7fffffff) {
+    SetError("ExclusiveSum: too many elements");
+    return kTooLarge;
+  }
+  int32_t nb = (int32_t)nb64;
+  ScanTileSums<T><<<nb, kScanThreads, 0, stream>>>(in, n, tmp);
+  ScanTileOffsets<T><<<1, kScanThreads, 0, stream>>>(tmp, nb);
+  ScanApply<T><<<nb, kScanThreads, 0, stream>>>(in, out, n, tmp);
+  K2B_CUDA_OK(cudaGetLastError());
+  return kOk;
+}
+
+int32_t ExclusiveSum(const int32_t *in, int32_t *out, int64_t n, int32_t *tmp,
+                     cudaStream_t stream) {
+  return ExclusiveSumImpl<int32_t>(in, out, n, tmp, stream);
+}
+int32_t ExclusiveSum2(const int2 *in, int2 *out, int64_t n, int2 *tmp, cudaStream_t stream) {
+  return ExclusiveSumImpl<int2>(in, out, n, tmp, stream);
+}
+
+// ----------------------------------------------------------------------------
+// row_splits -> row_ids by binary search per element
+// ----------------------------------------------------------------------------
+__global__ void RowIdsKernel(const int32_t *__restrict__ row_splits, int32_t num_rows,
+                             int32_t *__restrict__ row_ids, int32_t num_elems) {
+  int32_t k = blockIdx.x * blockDim.x + threadIdx.x;
+  if (k >= num_elems) return;
+  int32_t lo = 0, hi = num_rows;  // find largest r with row_splits[r] <= k
+  while (hi - lo > 1) {
+    int32_t mid = (lo + hi) >> 1;
+    if (row_splits[mid] <= k) lo = mid; else hi = mid;
+  }
+  row_ids[k] = lo;
+}
+
+int32_t RowSplitsToRowIds(const int32_t *row_splits, int32_t num_rows, int32_t *row_ids,
+                          int32_t num_elems, cudaStream_t stream) {
+  if (num_elems <= 0) return kOk;
+  RowIdsKernel<<<CeilDiv(num_elems, 256), 256, 0, stream>>>(row_splits, num_rows, row_ids,
+                                                            num_elems);
+  K2B_CUDA_OK(cudaGetLastError());
+  return kOk;
+}
+
+// ----------------------------------------------------------------------------
+// incoming-arc index: count -> exclusive sum -> scatter (atomic cursor) -> sort
+// every bucket by arc index so the result does not depend on scheduling.
+// ----------------------------------------------------------------------------
+__global__ void IncomingCount(const int32_t *__restrict__ row_splits1,
+                              const int32_t *__restrict__ row_ids1,
+                              const int32_t *__restrict__ row_ids2, const Arc *__restrict__ arcs,
+                              int32_t num_arcs, int32_t *__restrict__ counts) {
+  int32_t a = blockIdx.x * blockDim.x + threadIdx.x;
+  if (a >= num_arcs) return;
+  int32_t fsa = row_ids1[row_ids2[a]];
+  atomicAdd(&counts[row_splits1[fsa] + arcs[a].dest], 1);
+}
+
+__global__ void IncomingFill(const int32_t *__restrict__ row_splits1,
+                             const int32_t *__restrict__ row_ids1,
+                             const int32_t *__restrict__ row_ids2, const Arc *__restrict__ arcs,
+                             int32_t num_arcs, const int32_t *__restrict__ in_splits,
+                             int32_t *__restrict__ cursor, int32_t *__restrict__ unsorted) {
+  int32_t a = blockIdx.x * blockDim.x + threadIdx.x;
+  if (a >= num_arcs) return;
+  int32_t fsa = row_ids1[row_ids2[a]];
+  int32_t d = row_splits1[fsa] + arcs[a].dest;
+  int32_t pos = atomicAdd(&cursor[d], 1);
+  unsorted[in_splits[d] + pos] = a;
+}
+
+constexpr int kSmallBucket = 64;
+
+// One thread per state: rank sort of buckets of at most kSmallBucket arcs.
+__global__ void IncomingSortSmall(const int32_t *__restrict__ in_splits, int32_t num_states,
+                                  const int32_t *__restrict__ unsorted,
+                                  int32_t *__restrict__ in_arcs) {
+  int32_t s = blockIdx.x * blockDim.x + threadIdx.x;
+  if (s >= num_states) return;
+  int32_t b = in_splits[s], n = in_splits[s + 1] - b;
+  if (n > kSmallBucket) return;
+  for (int32_t i = 0; i < n; ++i) {
+    int32_t x = unsorted[b + i], rank = 0;
+    for (int32_t j = 0; j < n; ++j) rank += (unsorted[b + j] < x);
+    in_arcs[b + rank] = x;
+  }
+}
+
+// One warp per state for the (rare) large buckets.
+__global__ void IncomingSortLarge(const int32_t *__restrict__ in_splits, int32_t num_states,
+                                  const int32_t *__restrict__ unsorted,
+                                  int32_t *__restrict__ in_arcs) {
+  int32_t s = (int32_t)(((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5);
+  int lane = threadIdx.x & 31;
+  if (s >= num_states) return;
+  int32_t b = in_splits[s], n = in_splits[s + 1] - b;
+  if (n <= kSmallBucket) return;
+  for (int32_t i = lane; i < n; i += 32) {
+    int32_t x = unsorted[b + i], rank = 0;
+    for (int32_t j = 0; j < n; ++j) rank += (unsorted[b + j] < x);
+    in_arcs[b + rank] = x;
+  }
+}
+
+size_t IncomingTmpBytes(int32_t num_states, int32_t num_arcs) {
+  // counts/cursor [S+1], unsorted [A], scan tmp
+  return AlignUp(sizeof(int32_t) * ((size_t)num_states + 1)) +
+         AlignUp(sizeof(int32_t) * ((size_t)num_arcs + 1)) +
+         AlignUp(sizeof(int32_t) * ScanTmpInts(num_states));
+}
+
+int32_t BuildIncoming(const int32_t *row_splits1, const int32_t *row_ids1,
+                      const int32_t *row_ids2, const Arc *arcs, int32_t num_fsas,
+                      int32_t num_states, int32_t num_arcs, int32_t *in_splits,
+                      int32_t *in_arcs, void *tmp, cudaStream_t stream) {
+  (void)num_fsas;
+  char *p = reinterpret_cast<char *>(tmp);
+  int32_t *counts = reinterpret_cast<int32_t *>(p);
+  p += AlignUp(sizeof(int32_t) * ((size_t)num_states + 1));
+  int32_t *unsorted = reinterpret_cast<int32_t *>(p);
+  p += AlignUp(sizeof(int32_t) * ((size_t)num_arcs + 1));
+  int32_t *scan_tmp = reinterpret_cast<int32_t *>(p);
+
+  K2B_CUDA_OK(cudaMemsetAsync(counts, 0, sizeof(int32_t) * ((size_t)num_states + 1), stream));
+  if (num_arcs > 0)
+    IncomingCount<<<CeilDiv(num_arcs, 256), 256, 0, stream>>>(row_splits1, row_ids1, row_ids2,
+                                                              arcs, num_arcs, counts);
+  K2B_FORWARD(ExclusiveSum(counts, in_splits, num_states, scan_tmp, stream));
+  if (num_arcs > 0) {
+    K2B_CUDA_OK(cudaMemsetAsync(counts, 0, sizeof(int32_t) * ((size_t)num_states + 1), stream));
+    IncomingFill<<<CeilDiv(num_arcs, 256), 256, 0, stream>>>(row_splits1, row_ids1, row_ids2,
+                                                             arcs, num_arcs, in_splits, counts,
+                                                             unsorted);
+    IncomingSortSmall<<<CeilDiv(num_states, 256), 256, 0, stream>>>(in_splits, num_states,
+                                                                    unsorted, in_arcs);
+    IncomingSortLarge<<<CeilDiv((int64_t)num_states * 32, 256), 256, 0, stream>>>(
+        in_splits, num_states, unsorted, in_arcs);
+  }
+  K2B_CUDA_OK(cudaGetLastError());
+  return kOk;
+}
+
+}  // namespace k2b

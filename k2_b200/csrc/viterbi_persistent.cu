@@ -1,0 +1,176 @@
+// Persistent frame-synchronous Viterbi kernel for graphs that fit in shared memory.
+//
+// One CTA per (graph/sequence pair, direction) walks all frames in-kernel: the
+// graph's arcs (in incoming order for the forward direction, leaving order for
+// the backward one) and the two ping-pong score vectors live in shared memory,
+// the dense rows are prefetched into a shared-memory ring with cp.async several
+// frames ahead of the recursion, and one __syncthreads per frame is the only
+// synchronisation.  Each frame's state scores are also written to the global
+// (t, state) grids that the pruning pass reads.
+//
+// Same arithmetic as the per-frame launch path (and as the reference's DoStep,
+// k2/csrc/intersect_dense.cu:778-847): (prev + arc.score) + dense, then max.
+#include <algorithm>
+#include <vector>
+
+#include "intersect_internal.cuh"
+
+namespace k2b {
+
+constexpr size_t kSmemBudget = 200 * 1024;  // of the 227 KB a CTA may use
+constexpr int kMaxStages = 8;
+
+struct SmemPlan {
+  int32_t s_pad, a_pad, row_pad, stages;
+  size_t bytes;
+};
+
+static SmemPlan PlanSmem(int32_t max_states, int32_t max_arcs, int32_t cols) {
+  SmemPlan p;
+  p.s_pad = (max_states + 1 + 3) & ~3;
+  p.a_pad = (max_arcs + 3) & ~3;
+  p.row_pad = (cols + 1 + 3) & ~3;  // +1: a -inf slot for out-of-range labels
+  size_t fixed = sizeof(float) * 2 * p.s_pad      // score ping-pong
+                 + sizeof(int32_t) * p.s_pad      // splits
+                 + (size_t)12 * p.a_pad;          // other-end state, column slot, score
+  size_t row = sizeof(float) * p.row_pad;
+  int32_t stages = 0;
+  if (fixed < kSmemBudget) stages = (int32_t)std::min<size_t>(kMaxStages, (kSmemBudget - fixed) / row);
+  p.stages = stages;
+  p.bytes = fixed + row * std::max(stages, 0);
+  return p;
+}
+
+bool PersistentViterbiFits(const Layout &L, const k2b200_intersect_args *a) {
+  SmemPlan p = PlanSmem(L.max_states, L.max_arcs, a->cols);
+  return p.stages >= 2 && a->num_fsas <= 65535;
+}
+
+__device__ __forceinline__ void CpAsync4(float *smem_dst, const float *gmem_src) {
+  unsigned dst = (unsigned)__cvta_generic_to_shared(smem_dst);
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4;\n" ::"r"(dst), "l"(gmem_src));
+}
+__device__ __forceinline__ void CpAsyncCommit() { asm volatile("cp.async.commit_group;\n" ::); }
+template <int N>
+__device__ __forceinline__ void CpAsyncWait() {
+  asm volatile("cp.async.wait_group %0;\n" ::"n"(N));
+}
+__device__ __forceinline__ void CpAsyncWaitDyn(int n) {
+  // wait until at most n groups are pending (n < kMaxStages)
+  switch (n) {
+    case 0: CpAsyncWait<0>(); break;
+    case 1: CpAsyncWait<1>(); break;
+    case 2: CpAsyncWait<2>(); break;
+    case 3: CpAsyncWait<3>(); break;
+    case 4: CpAsyncWait<4>(); break;
+    case 5: CpAsyncWait<5>(); break;
+    default: CpAsyncWait<6>(); break;
+  }
+}
+
+// grid = (2 directions, pairs); dynamic shared memory per PlanSmem.
+__global__ void __launch_bounds__(1024)
+PersistentViterbi(const FsaInfo *__restrict__ infos, const Arc *__restrict__ arcs,
+                  const int32_t *__restrict__ a_row_splits2,
+                  const int32_t *__restrict__ in_splits, const int32_t *__restrict__ in_arcs,
+                  const float *__restrict__ scores, int32_t cols, float *__restrict__ fwd,
+                  float *__restrict__ bwd, int32_t s_pad, int32_t a_pad, int32_t row_pad,
+                  int32_t stages, int32_t lanes_log2) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  const FsaInfo f = infos[blockIdx.y];
+  const int dir = blockIdx.x;  // 0 forward, 1 backward
+  const int32_t S = f.num_states, A = f.num_arcs, Tk = f.tk;
+  if (S == 0) return;
+  float *score_buf = reinterpret_cast<float *>(smem_raw);           // [2][s_pad]
+  int32_t *splits = reinterpret_cast<int32_t *>(score_buf + 2 * s_pad);  // [s_pad]
+  int32_t *arc_state = splits + s_pad;                              // [a_pad]
+  int32_t *arc_col = arc_state + a_pad;                             // [a_pad]
+  float *arc_score = reinterpret_cast<float *>(arc_col + a_pad);   // [a_pad]
+  float *ring = arc_score + a_pad;                                  // [stages][row_pad]
+
+  const int tid = threadIdx.x, nt = blockDim.x;
+  // ---- stage the graph --------------------------------------------------
+  const int32_t *gsplits = (dir == 0 ? in_splits : a_row_splits2) + f.state_off;
+  for (int32_t s = tid; s <= S; s += nt) splits[s] = gsplits[s] - f.arc_off;
+  for (int32_t k = tid; k < A; k += nt) {
+    Arc arc = arcs[dir == 0 ? in_arcs[f.arc_off + k] : f.arc_off + k];
+    arc_state[k] = dir == 0 ? arc.src : arc.dest;
+    int32_t c = arc.label + 1;
+    arc_col[k] = (c >= 0 && c < cols) ? c : cols;  // slot `cols` holds -inf
+    arc_score[k] = arc.score;
+  }
+  for (int32_t st = tid; st < stages; st += nt) ring[(size_t)st * row_pad + cols] = -INFINITY;
+  // ---- initial scores -----------------------------------------------------
+  float *grid = (dir == 0 ? fwd : bwd) + f.grid_off;
+  for (int32_t s = tid; s < S; s += nt) {
+    float v = (dir == 0 ? (s == 0) : (s == S - 1)) ? 0.0f : -INFINITY;
+    score_buf[s] = v;
+    grid[(int64_t)(dir == 0 ? 0 : Tk) * S + s] = v;
+  }
+  // ---- prefetch the first stages-1 rows -----------------------------------
+  // step t (1..Tk) consumes dense row t-1 (forward) or Tk-t (backward)
+  auto issue_row = [&](int32_t step) {
+    if (step <= Tk) {
+      const int64_t row = (int64_t)f.row0 + (dir == 0 ? step - 1 : Tk - step);
+      const float *src = scores + row * cols;
+      float *dst = ring + (size_t)((step - 1) % stages) * row_pad;
+      for (int32_t c = tid; c < cols; c += nt) CpAsync4(dst + c, src + c);
+    }
+    CpAsyncCommit();  // always commit so the group count stays uniform
+  };
+  for (int32_t step = 1; step < stages; ++step) issue_row(step);
+
+  const int32_t G = 1 << lanes_log2, g = tid & (G - 1);
+  const int32_t states_per_pass = nt >> lanes_log2;
+  for (int32_t t = 1; t <= Tk; ++t) {
+    CpAsyncWaitDyn(stages - 2);  // this thread's copies of row for step t have landed
+    __syncthreads();             // ... everyone's have; previous frame's scores are complete
+    issue_row(t + stages - 1);   // refills the slot consumed by step t-1
+    const float *cur = score_buf + ((t - 1) & 1) * s_pad;
+    float *nxt = score_buf + (t & 1) * s_pad;
+    const float *row = ring + (size_t)((t - 1) % stages) * row_pad;
+    float *gout = grid + (int64_t)(dir == 0 ? t : Tk - t) * S;
+    for (int32_t s0 = 0; s0 < S; s0 += states_per_pass) {
+      const int32_t s = s0 + (tid >> lanes_log2);
+      float best = -INFINITY;
+      if (s < S) {
+        for (int32_t k = splits[s] + g; k < splits[s + 1]; k += G) {
+          float v = __fadd_rn(__fadd_rn(cur[arc_state[k]], arc_score[k]), row[arc_col[k]]);
+          best = v > best ? v : best;
+        }
+      }
+      for (int32_t d = G >> 1; d > 0; d >>= 1) {
+        float o = __shfl_xor_sync(0xffffffffu, best, d);
+        best = o > best ? o : best;
+      }
+      if (s < S && g == 0) {
+        nxt[s] = best;
+        gout[s] = best;
+      }
+    }
+  }
+  CpAsyncWait<0>();
+}
+
+int32_t LaunchPersistentViterbi(const Layout &L, const k2b200_intersect_args *a,
+                                const FsaInfo *d_infos, float *fwd, float *bwd,
+                                cudaStream_t stream) {
+  SmemPlan p = PlanSmem(L.max_states, L.max_arcs, a->cols);
+  K2B_CUDA_OK(cudaFuncSetAttribute(PersistentViterbi, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                   (int)p.bytes));
+  // lanes per state: about half the mean degree, so every lane loops ~2 arcs
+  int32_t mean_deg = a->num_states > 0 ? (a->num_arcs + a->num_states - 1) / a->num_states : 1;
+  int32_t lanes_log2 = 0;
+  while ((2 << lanes_log2) <= mean_deg / 2 && lanes_log2 < 5) ++lanes_log2;
+  int64_t lanes = (int64_t)L.max_states << lanes_log2;
+  int32_t threads = (int32_t)std::min<int64_t>(1024, std::max<int64_t>(128, (lanes + 31) / 32 * 32));
+  dim3 grid(2, a->num_fsas);
+  PersistentViterbi<<<grid, threads, p.bytes, stream>>>(
+      d_infos, reinterpret_cast<const Arc *>(a->a_arcs), a->a_row_splits2, a->a_in_splits,
+      a->a_in_arcs, a->scores, a->cols, fwd, bwd, p.s_pad, p.a_pad, p.row_pad, p.stages,
+      lanes_log2);
+  K2B_CUDA_OK(cudaGetLastError());
+  return kOk;
+}
+
+}  // namespace k2b

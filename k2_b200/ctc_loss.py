@@ -1,0 +1,69 @@
+"""`CtcLoss` / `ctc_loss`: mirror of k2/python/k2/ctc_loss.py:28-208."""
+from typing import Optional
+
+import torch
+import torch.nn as nn
+
+from .autograd import intersect_dense
+from .dense_fsa_vec import DenseFsaVec
+from .fsa import Fsa
+
+
+class CtcLoss(nn.Module):
+    """CTC loss as the negated log-semiring total score of the graph intersected
+    with the network output.  Blank is label 0."""
+
+    def __init__(self, output_beam: float, reduction: str = "sum",
+                 use_double_scores: bool = True):
+        super().__init__()
+        assert reduction in ("none", "mean", "sum")
+        self.output_beam = output_beam
+        self.reduction = reduction
+        self.use_double_scores = use_double_scores
+
+    def forward(self, decoding_graph: Fsa, dense_fsa_vec: DenseFsaVec,
+                delay_penalty: float = 0.0,
+                target_lengths: Optional[torch.Tensor] = None) -> torch.Tensor:
+        lattice = intersect_dense(
+            a_fsas=decoding_graph, b_fsas=dense_fsa_vec, output_beam=self.output_beam,
+            frame_idx_name="frame_idx" if delay_penalty > 0.0 else None)
+
+        if delay_penalty > 0.0:
+            # ctc_loss.py:99-136: penalise late non-blank symbols relative to the
+            # middle frame of their sequence
+            arcs = lattice.arcs
+            fsa_of_arc = arcs.row_ids(1)[arcs.row_ids(2).long()].long()
+            duration = dense_fsa_vec.duration.to(lattice.device)
+            offset = lattice.frame_idx - (duration >> 1)[fsa_of_arc].to(torch.int32)
+            penalty = -delay_penalty * offset.to(torch.float32)
+            if hasattr(lattice, "_is_repeat_token_"):
+                mask = ((lattice.labels == 0) | (lattice.labels == -1)
+                        | lattice._is_repeat_token_)
+            else:
+                assert hasattr(lattice, "aux_labels")
+                mask = (lattice.aux_labels == 0) | (lattice.aux_labels == -1)
+            penalty.masked_fill_(mask, 0.0)
+            lattice.scores = lattice.scores + penalty
+
+        tot_scores = lattice.get_tot_scores(log_semiring=True,
+                                            use_double_scores=self.use_double_scores)
+        loss = -1 * tot_scores
+        loss = loss.to(torch.float32)
+        if self.reduction == "none":
+            return loss
+        elif self.reduction == "sum":
+            return loss.sum()
+        else:
+            assert self.reduction == "mean"
+            loss /= target_lengths
+            return loss.mean()
+
+
+def ctc_loss(decoding_graph: Fsa, dense_fsa_vec: DenseFsaVec, output_beam: float = 10,
+             delay_penalty: float = 0.0, reduction: str = "sum",
+             use_double_scores: bool = True,
+             target_lengths: Optional[torch.Tensor] = None) -> torch.Tensor:
+    m = CtcLoss(output_beam=output_beam, reduction=reduction,
+                use_double_scores=use_double_scores)
+    return m(decoding_graph=decoding_graph, dense_fsa_vec=dense_fsa_vec,
+             delay_penalty=delay_penalty, target_lengths=target_lengths)

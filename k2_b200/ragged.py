@@ -1,0 +1,214 @@
+"""CUDA-resident counterpart of `_k2.RaggedArc` (k2/python/csrc/torch/ragged.cu:40-160).
+
+A RaggedArc is k2's `Ragged<Arc>` with 3 axes [fsa][state][arc]:
+  values       int32 [num_arcs, 4]: src_state, dest_state, label, score bits
+  row_splits1  int32 [num_fsas + 1]   fsa   -> first state (idx01)
+  row_splits2  int32 [num_states + 1] state -> first arc (idx012)
+  row_ids1/2   the inverse maps, built on demand by a CUDA kernel
+A 2-axis Fsa (single FSA) is stored as a 3-axis one with one entry and
+`single=True`, which is how the reference lifts it before every FsaVec
+algorithm (k2/python/csrc/torch/fsa_algo.cu:236-238).
+"""
+from typing import Optional
+
+import numpy as np
+import torch
+
+from . import _lib
+
+
+class RaggedArc:
+
+    def __init__(self, values: torch.Tensor, row_splits1: torch.Tensor,
+                 row_splits2: torch.Tensor, row_ids1: Optional[torch.Tensor] = None,
+                 row_ids2: Optional[torch.Tensor] = None, single: bool = False,
+                 h_row_splits1: Optional[np.ndarray] = None,
+                 h_arc_splits: Optional[np.ndarray] = None):
+        assert values.dtype == torch.int32 and values.ndim == 2 and values.shape[1] == 4
+        assert values.is_contiguous()
+        assert row_splits1.dtype == torch.int32 and row_splits2.dtype == torch.int32
+        self._values = values
+        self._row_splits1 = row_splits1.contiguous()
+        self._row_splits2 = row_splits2.contiguous()
+        self._row_ids1 = row_ids1
+        self._row_ids2 = row_ids2
+        self.single = single
+        self._h_row_splits1 = h_row_splits1
+        self._h_arc_splits = h_arc_splits
+        # lazily built device-side helpers
+        self._incoming = None  # (in_splits, in_arcs)
+        self._levels = None    # (level_offsets, level_splits) of a layered FsaVec
+
+    # ---- _k2.RaggedArc interface ----------------------------------------
+    def values(self) -> torch.Tensor:
+        return self._values
+
+    def num_axes(self) -> int:
+        return 2 if self.single else 3
+
+    def dim0(self) -> int:
+        if self.single:
+            return self.num_states
+        return self._row_splits1.shape[0] - 1
+
+    @property
+    def num_fsas(self) -> int:
+        return self._row_splits1.shape[0] - 1
+
+    @property
+    def num_states(self) -> int:
+        return self._row_splits2.shape[0] - 1
+
+    def num_elements(self) -> int:
+        return self._values.shape[0]
+
+    def tot_size(self, axis: int) -> int:
+        if self.single:
+            axis += 1
+        return [self.num_fsas, self.num_states, self.num_elements()][axis]
+
+    @property
+    def device(self) -> torch.device:
+        return self._values.device
+
+    def row_splits(self, axis: int) -> torch.Tensor:
+        if self.single:
+            axis += 1
+        assert axis in (1, 2)
+        return self._row_splits1 if axis == 1 else self._row_splits2
+
+    def row_ids(self, axis: int) -> torch.Tensor:
+        if self.single:
+            axis += 1
+        assert axis in (1, 2)
+        if axis == 1:
+            if self._row_ids1 is None:
+                self._row_ids1 = _row_ids(self._row_splits1, self.num_states)
+            return self._row_ids1
+        if self._row_ids2 is None:
+            self._row_ids2 = _row_ids(self._row_splits2, self.num_elements())
+        return self._row_ids2
+
+    def to(self, device) -> "RaggedArc":
+        device = torch.device(device)
+        if device == self.device:
+            return self
+        mv = lambda t: None if t is None else t.to(device)  # noqa: E731
+        out = RaggedArc(self._values.to(device), self._row_splits1.to(device),
+                        self._row_splits2.to(device), mv(self._row_ids1), mv(self._row_ids2),
+                        self.single, self.h_row_splits1, self.h_arc_splits)
+        return out
+
+    def clone(self) -> "RaggedArc":
+        out = RaggedArc(self._values.clone(), self._row_splits1, self._row_splits2,
+                        self._row_ids1, self._row_ids2, self.single, self._h_row_splits1,
+                        self._h_arc_splits)
+        out._incoming = self._incoming
+        out._levels = self._levels
+        return out
+
+    # ---- host copies of the small per-FSA splits ---------------------------
+    @property
+    def h_row_splits1(self) -> np.ndarray:
+        if self._h_row_splits1 is None:
+            self._h_row_splits1 = self._row_splits1.cpu().numpy().astype(np.int32)
+        return self._h_row_splits1
+
+    @property
+    def h_arc_splits(self) -> np.ndarray:
+        """row_splits2[row_splits1[i]]: first arc of every FSA, on the host."""
+        if self._h_arc_splits is None:
+            idx = self._row_splits1.long()
+            self._h_arc_splits = self._row_splits2[idx].cpu().numpy().astype(np.int32)
+        return self._h_arc_splits
+
+    # ---- device-side helpers -------------------------------------------------
+    def incoming(self):
+        """(in_splits, in_arcs): arcs entering every state, by arc index.  Cached;
+        the reference recomputes it on every intersect_dense call
+        (k2/csrc/intersect_dense.cu:139-142)."""
+        if self._incoming is None:
+            _lib.require_cuda(self._values, "arcs")
+            ns, na = self.num_states, self.num_elements()
+            dev = self.device
+            in_splits = torch.empty(ns + 1, dtype=torch.int32, device=dev)
+            in_arcs = torch.empty(max(na, 1), dtype=torch.int32, device=dev)
+            tmp = torch.empty(_lib.lib.k2b200_fsa_incoming_tmp_bytes(ns, na), dtype=torch.uint8,
+                              device=dev)
+            with torch.cuda.device(dev):
+                _lib.check(_lib.lib.k2b200_fsa_incoming(
+                    _lib.ptr(self._row_splits1), _lib.ptr(self.row_ids(1 - self.single)),
+                    _lib.ptr(self.row_ids(2 - self.single)), _lib.ptr(self._values),
+                    self.num_fsas, ns, na, _lib.ptr(in_splits), _lib.ptr(in_arcs),
+                    _lib.ptr(tmp), _lib.stream_of(dev)))
+            self._incoming = (in_splits, in_arcs[:na])
+        return self._incoming
+
+    def levels(self):
+        """(level_offsets, level_splits): a layering of the states such that every
+        arc goes from a lower to a higher layer.  Lattices made by intersect_dense
+        carry their frame layering; for any other top-sorted acyclic FsaVec the
+        layering (longest distance from the start state) is derived on the host
+        once and cached - the scores themselves are always computed on the GPU."""
+        if self._levels is None:
+            self._levels = _host_levels(self)
+        return self._levels
+
+    def __repr__(self):
+        return (f"RaggedArc(num_fsas={self.num_fsas}, num_states={self.num_states}, "
+                f"num_arcs={self.num_elements()}, device={self.device})")
+
+
+def _row_ids(row_splits: torch.Tensor, num_elems: int) -> torch.Tensor:
+    out = torch.empty(num_elems, dtype=torch.int32, device=row_splits.device)
+    if num_elems == 0:
+        return out
+    if row_splits.is_cuda:
+        with torch.cuda.device(row_splits.device):
+            _lib.check(_lib.lib.k2b200_row_splits_to_row_ids(
+                _lib.ptr(row_splits), row_splits.shape[0] - 1, _lib.ptr(out), num_elems,
+                _lib.stream_of(row_splits.device)))
+        return out
+    # host-resident graphs (e.g. straight out of ctc_graph before .to(device))
+    rs = row_splits.numpy()
+    return torch.from_numpy(
+        np.repeat(np.arange(len(rs) - 1, dtype=np.int32), np.diff(rs)).astype(np.int32))
+
+
+def _host_levels(arcs: RaggedArc):
+    """Longest-distance layering, computed with numpy from a host copy."""
+    rs1 = arcs.h_row_splits1
+    rs2 = arcs._row_splits2.cpu().numpy()
+    vals = arcs._values.cpu().numpy()
+    ns = arcs.num_states
+    level = np.zeros(ns, dtype=np.int64)
+    order_ok = True
+    for i in range(len(rs1) - 1):
+        b, e = int(rs1[i]), int(rs1[i + 1])
+        for s in range(b, e):
+            a0, a1 = int(rs2[s]), int(rs2[s + 1])
+            if a1 > a0:
+                d = vals[a0:a1, 1].astype(np.int64) + b
+                if np.any(d <= s):
+                    order_ok = False
+                np.maximum.at(level, d, level[s] + 1)
+    if not order_ok:
+        raise RuntimeError("forward/backward scores need a top-sorted, acyclic FsaVec")
+    # states must be grouped by level within each FSA for contiguous layers; when
+    # they are not, fall back to one state per layer (always valid when top-sorted)
+    offsets = [0]
+    splits = []
+    for i in range(len(rs1) - 1):
+        b, e = int(rs1[i]), int(rs1[i + 1])
+        lv = level[b:e]
+        if e > b and np.all(np.diff(lv) >= 0):
+            change = np.nonzero(np.diff(lv))[0] + 1
+            starts = np.concatenate([[0], change]) + b
+        else:
+            starts = np.arange(b, e)
+        splits.extend(starts.tolist())
+        offsets.append(len(splits))
+    splits.append(int(rs1[-1]))
+    dev = arcs.device
+    return (torch.tensor(offsets, dtype=torch.int32, device=dev),
+            torch.tensor(splits, dtype=torch.int32, device=dev))
