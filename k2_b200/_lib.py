@@ -105,10 +105,20 @@ def check(status: int) -> None:
         raise RuntimeError(lib.k2b200_last_error().decode(errors="replace"))
 
 
+_dummy = {}
+
+
 def ptr(t) -> int:
-    """Device (or host) address of a tensor, None -> NULL."""
+    """Device address of a tensor; None -> NULL.  Empty tensors have no storage
+    address in torch, so they get the address of a small per-device scratch
+    buffer (never dereferenced: their size is 0)."""
     if t is None:
         return None
+    if t.numel() == 0:
+        key = str(t.device)
+        if key not in _dummy:
+            _dummy[key] = torch.zeros(64, dtype=torch.int32, device=t.device)
+        return _dummy[key].data_ptr()
     return t.data_ptr()
 
 

@@ -12,6 +12,9 @@ from .dense_fsa_vec import DenseFsaVec
 from .fsa import Fsa
 from .ragged import RaggedArc
 
+# 0 = automatic, 1 = one launch per frame, 2 = persistent kernel (see include/k2b200.h)
+VITERBI_MODE = 0
+
 
 def _index_add(index: torch.Tensor, value: torch.Tensor, in_out: torch.Tensor) -> None:
     """in_out[index[k]] += value[k] (k2/python/csrc/torch/index_add.cu:38-71)."""
@@ -90,13 +93,14 @@ def _intersect_dense_arcs(a: RaggedArc, b: DenseFsaVec, a_to_b_map: Optional[tor
                                                           ctypes.byref(na), ctypes.byref(beam)))
         ns, na = ns.value, na.value
         i32 = dict(dtype=torch.int32, device=dev)
+        # zero-sized tensors have a NULL data pointer: allocate one spare element
         row_splits1 = torch.empty(a.num_fsas + 1, **i32)
-        row_ids1 = torch.empty(ns, **i32)
+        row_ids1 = torch.empty(ns + 1, **i32)
         row_splits2 = torch.empty(ns + 1, **i32)
-        row_ids2 = torch.empty(na, **i32)
-        values = torch.empty((na, 4), **i32)
-        arc_map_a = torch.empty(na, **i32)
-        arc_map_b = torch.empty(na, **i32)
+        row_ids2 = torch.empty(na + 1, **i32)
+        values = torch.empty((na + 1, 4), **i32)
+        arc_map_a = torch.empty(na + 1, **i32)
+        arc_map_b = torch.empty(na + 1, **i32)
         level_offsets = torch.empty(a.num_fsas + 1, **i32)
         level_splits = torch.empty(levels.value + 1, **i32)
         out = _lib.LatticeOut(
@@ -106,7 +110,8 @@ def _intersect_dense_arcs(a: RaggedArc, b: DenseFsaVec, a_to_b_map: Optional[tor
             level_offsets=_lib.ptr(level_offsets), level_splits=_lib.ptr(level_splits))
         _lib.check(_lib.lib.k2b200_intersect_dense_emit(ctypes.byref(args), _lib.ptr(ws),
                                                          nbytes.value, stream, ctypes.byref(out)))
-    lattice = RaggedArc(values, row_splits1, row_splits2, row_ids1, row_ids2)
+    lattice = RaggedArc(values[:na], row_splits1, row_splits2, row_ids1[:ns], row_ids2[:na])
+    arc_map_a, arc_map_b = arc_map_a[:na], arc_map_b[:na]
     lattice._levels = (level_offsets, level_splits)
     lattice.output_beam_used = beam.value
     return lattice, arc_map_a, arc_map_b
@@ -170,7 +175,7 @@ class _IntersectDenseFunction(torch.autograd.Function):
                 frame_idx_name: Optional[str] = None) -> torch.Tensor:
         assert len(out_fsa) == 1
         ragged_arc, arc_map_a, arc_map_b = _intersect_dense_arcs(
-            a_fsas.arcs, b_fsas, a_to_b_map, output_beam, max_states, max_arcs)
+            a_fsas.arcs, b_fsas, a_to_b_map, output_beam, max_states, max_arcs, VITERBI_MODE)
         # the lattice is valid by construction; its property bits are computed on
         # first use rather than with a host round trip on every call
         out_fsa[0] = Fsa(ragged_arc, _check=False)

@@ -1,0 +1,302 @@
+"""GPU parity: the CUDA path (through the C-ABI) against the CPU oracle on the
+same seeded inputs.  Lattices, arc maps, best paths and property bits must be
+bit-exact; float64 scores agree to 1e-9, float32 scores to 1e-4 relative, and
+gradients w.r.t. the dense scores to 1e-4 absolute (the tolerances of this path)."""
+import numpy as np
+import pytest
+import torch
+
+from oracle import oracle
+from util import close, random_dense, random_fsa_vec, same_fsa
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def k2():
+    import k2_b200
+    return k2_b200
+
+
+def _micro():
+    from oracle.common import HostFsaVec, make_arcs
+    arcs1 = make_arcs([0, 0, 1, 1, 2], [1, 1, 1, 2, 3], [1, 2, 1, 2, -1],
+                      [1.0, 0.5, 50.0, 2.0, 3.0])
+    rs2_one = np.array([0, 2, 4, 5, 5])
+    a = HostFsaVec(np.array([0, 4, 8], np.int32),
+                   np.concatenate([rs2_one, rs2_one[1:] + 5]).astype(np.int32),
+                   np.concatenate([arcs1, arcs1]))
+    ninf = -np.inf
+    scores = np.array([[ninf, .1, .2, .3], [ninf, .04, .05, .06], [ninf, 0, 0, 0],
+                       [0, ninf, ninf, ninf], [ninf, .1, .2, .3], [ninf, .4, .5, .6],
+                       [0, ninf, ninf, ninf]], np.float32)
+    return a, scores, np.array([0, 4, 7], np.int32)
+
+
+@pytest.mark.parametrize("mode", [1, 2])
+def test_micro_example_known_answer(k2, mode):
+    # worked example computed with the reference: two copies of a 4-state graph
+    from gpu_util import dense_from_scores, fsa_to_host, host_to_fsa, intersect_raw
+    a, scores, brs = _micro()
+    lat, ma, mb = intersect_raw(host_to_fsa(a), dense_from_scores(scores, brs), 100.0, mode=mode)
+    h = fsa_to_host(lat, ma, mb)
+    assert h.row_splits1.tolist() == [0, 5, 9]
+    assert h.row_splits2.tolist() == [0, 2, 3, 4, 5, 5, 7, 8, 9, 9]
+    assert h.arc_map_a.tolist() == [0, 1, 2, 3, 4, 5, 6, 8, 9]
+    assert h.arc_map_b.tolist() == [2, 3, 6, 11, 12, 18, 19, 23, 24]
+    assert h.arcs[:, :3].tolist() == [[0, 1, 1], [0, 1, 2], [1, 2, 1], [2, 3, 2], [3, 4, -1],
+                                      [0, 1, 1], [0, 1, 2], [1, 2, 2], [2, 3, -1]]
+    np.testing.assert_array_equal(
+        h.scores, np.array([1.2, 0.8, 50.05, 2.0, 3.0, 1.2, 0.8, 2.6, 3.0], np.float32))
+    # strict '>' at the beam: the 0.4-worse arc of the first FSA is dropped
+    lat2, _, _ = intersect_raw(host_to_fsa(a), dense_from_scores(scores, brs), 0.4, mode=mode)
+    assert fsa_to_host(lat2).arcs[:, :3].tolist() == [[0, 1, 1], [1, 2, 1], [2, 3, 2], [3, 4, -1],
+                                                      [0, 1, 1], [0, 1, 2], [1, 2, 2], [2, 3, -1]]
+
+
+@pytest.mark.parametrize("mode", [1, 2])
+def test_random_fsa_vecs_bit_exact(k2, mode):
+    # in the spirit of Intersect.RandomFsaVec (k2/csrc/intersect_test.cu:262-380)
+    from gpu_util import dense_from_scores, fsa_to_host, host_to_fsa, intersect_raw
+    rng = np.random.default_rng(1)
+    for trial in range(60):
+        n = int(rng.integers(1, 7))
+        a = random_fsa_vec(rng, n, acyclic=bool(trial % 2))
+        scores, brs = random_dense(rng, n, 10, 5)
+        beam = float(rng.choice([0.5, 2.0, 10.0, 100.0]))
+        amap = None
+        if trial % 5 == 0:
+            amap = np.sort(rng.integers(0, n, size=n)).astype(np.int32)
+        want = oracle.intersect_dense(a, scores, brs, beam, amap)
+        lat, ma, mb = intersect_raw(host_to_fsa(a), dense_from_scores(scores, brs), beam, amap,
+                                    mode=mode)
+        same_fsa(fsa_to_host(lat, ma, mb), want, f"trial {trial}")
+        assert lat.properties == oracle.properties(want)[1]
+
+
+def _check_scores(k2, lat, want):
+    from gpu_util import fsa_to_host
+    for log_semiring in (True, False):
+        for use_double in (True, False):
+            tol = dict(rtol=1e-9, atol=1e-9) if use_double else dict(rtol=1e-4, atol=1e-4)
+            of = oracle.forward_scores(want, log_semiring, use_double)
+            ob = oracle.backward_scores(want, log_semiring, use_double)
+            ot, op = oracle.tot_scores_and_arc_post(want, of, ob, use_double)
+            f = lat.get_forward_scores(use_double, log_semiring).cpu().numpy()
+            b = lat.get_backward_scores(use_double, log_semiring).cpu().numpy()
+            t = lat.get_tot_scores(use_double, log_semiring).detach().cpu().numpy()
+            p = lat.get_arc_post(use_double, log_semiring).cpu().numpy()
+            assert close(f, of, **tol) and close(b, ob, **tol), (log_semiring, use_double)
+            assert close(t, ot, **tol), (log_semiring, use_double)
+            finite = np.isfinite(op)
+            # float32 posteriors are differences of scores of magnitude max|fwd|:
+            # allow a few ulps of that magnitude (the reference's float path
+            # carries the same cancellation error)
+            mag = float(np.abs(of[np.isfinite(of)]).max()) if np.isfinite(of).any() else 1.0
+            ptol = tol if use_double else dict(rtol=1e-4, atol=max(1e-4, 8 * 1.2e-7 * mag))
+            assert close(p[finite], op[finite], **ptol)
+    _, oea = oracle.forward_scores(want, False, True, want_entering_arcs=True)
+    ea = lat._get_entering_arcs(True).cpu().numpy()
+    np.testing.assert_array_equal(ea, oea)
+    osplits, obest = oracle.shortest_path(want, oea)
+    best = k2.shortest_path(lat, True)
+    np.testing.assert_array_equal(best._best_arc_map.cpu().numpy(), obest)
+    np.testing.assert_array_equal(np.diff(best.arcs.h_row_splits1),
+                                  np.where(np.diff(osplits) > 0, np.diff(osplits) + 1, 0))
+
+
+def test_scores_on_random_lattices(k2):
+    from gpu_util import dense_from_scores, host_to_fsa, intersect_raw
+    rng = np.random.default_rng(2)
+    for trial in range(25):
+        n = int(rng.integers(1, 6))
+        a = random_fsa_vec(rng, n, acyclic=bool(trial % 2))
+        scores, brs = random_dense(rng, n, 12, 5, low_rows=False)
+        want = oracle.intersect_dense(a, scores, brs, 20.0)
+        lat, _, _ = intersect_raw(host_to_fsa(a), dense_from_scores(scores, brs), 20.0)
+        _check_scores(k2, lat, want)
+
+
+def _workload_case(k2, w, mode=0, check_scores=False):
+    """intersect -> log tot_scores -> backward through the public API, against
+    the oracle's loss path."""
+    from gpu_util import DEV, fsa_to_host
+    from k2_b200 import synthetic as syn
+    from k2_b200 import autograd
+    graphs = syn.build_graphs(w, DEV)
+    log_probs = w.log_probs.to(DEV).requires_grad_(True)
+    dense = k2.DenseFsaVec(log_probs, w.supervision_segments)
+    autograd.VITERBI_MODE = mode
+    try:
+        lat = k2.intersect_dense(graphs, dense, w.output_beam)
+    finally:
+        autograd.VITERBI_MODE = 0
+    tot = lat.get_tot_scores(log_semiring=True, use_double_scores=True)
+    (-tot.sum()).backward()
+    a_host = fsa_to_host(graphs)
+    scores_host = dense.scores.detach().cpu().numpy()
+    want = oracle.loss_path(a_host, scores_host, dense.h_row_splits, w.output_beam)
+    same_fsa(fsa_to_host(lat), want["lattice"], w.name)
+    assert close(tot.detach().cpu().numpy(), want["tot_scores"], rtol=1e-4, atol=0)
+    # gradient w.r.t. log_probs = -(grad_b without column 0, un-gathered)
+    C = log_probs.shape[-1]
+    seg = w.supervision_segments.numpy()
+    expect = np.zeros(tuple(log_probs.shape), np.float32)
+    gb = want["grad_b"]
+    r = 0
+    for (n, s, d) in seg.tolist():
+        expect[n, s:s + d] -= gb[r:r + d, 1:]
+        r += d + 1
+    got = log_probs.grad.cpu().numpy()
+    assert np.abs(got - expect).max() <= 1e-4, np.abs(got - expect).max()
+    if check_scores:
+        _check_scores(k2, lat, want["lattice"])
+    return lat, want
+
+
+def test_ctc_small_full_size(k2):
+    from k2_b200 import synthetic as syn
+    lat, want = _workload_case(k2, syn.ctc_small(), check_scores=True)
+    assert want["lattice"].num_arcs > 50000  # beam 10 keeps ~72k arcs on this workload
+
+
+@pytest.mark.parametrize("mode", [1, 2])
+def test_ctc_large_quarter(k2, mode):
+    from k2_b200 import synthetic as syn
+    _workload_case(k2, syn.ctc_large(scale=0.25), mode=mode)
+
+
+def test_ctc_modified_scaled(k2):
+    from k2_b200 import synthetic as syn
+    _workload_case(k2, syn.ctc_modified(scale=0.2))
+
+
+@pytest.mark.parametrize("mode", [1, 2])
+def test_lfmmi_den_scaled(k2, mode):
+    from k2_b200 import synthetic as syn
+    _workload_case(k2, syn.lfmmi_den(scale=0.05), mode=mode)
+
+
+def test_hlg_decode_scaled_viterbi_and_log(k2):
+    # 70k states: beyond what the reference's uint16 state ids can represent
+    from k2_b200 import synthetic as syn
+    w = syn.hlg_decode(scale=0.04, num_states=70001)
+    lat, want = _workload_case(k2, w, check_scores=False)
+    _, oea = oracle.forward_scores(want["lattice"], False, True, want_entering_arcs=True)
+    _, obest = oracle.shortest_path(want["lattice"], oea)
+    best = k2.shortest_path(lat, True)
+    np.testing.assert_array_equal(best._best_arc_map.cpu().numpy(), obest)
+
+
+def test_ctc_loss_matches_torch(k2):
+    # second, independent check as in k2/python/tests/ctc_loss_test.py:311-441
+    from gpu_util import DEV
+    gen = torch.Generator().manual_seed(7)
+    N, T, C = 4, 30, 10
+    logits = torch.randn(N, T, C, generator=gen)
+    lens = torch.tensor([30, 27, 25, 20], dtype=torch.int32)
+    targets = [torch.randint(1, C, (int(k),), generator=gen).tolist() for k in (5, 7, 3, 6)]
+    ours_in = logits.clone().to(DEV).requires_grad_(True)
+    lp = torch.log_softmax(ours_in, -1)
+    seg = torch.stack([torch.arange(N, dtype=torch.int32), torch.zeros(N, dtype=torch.int32),
+                       lens], 1)
+    dense = k2.DenseFsaVec(lp, seg)
+    graph = k2.ctc_graph(targets, device=DEV)
+    loss = k2.ctc_loss(graph, dense, output_beam=1000.0, reduction="sum")
+    loss.backward()
+    t_in = logits.clone().requires_grad_(True)
+    t_lp = torch.log_softmax(t_in, -1).permute(1, 0, 2)
+    t_loss = torch.nn.functional.ctc_loss(
+        t_lp, torch.tensor([x for t in targets for x in t]), lens.long(),
+        torch.tensor([len(t) for t in targets]), reduction="sum")
+    t_loss.backward()
+    assert abs(loss.item() - t_loss.item()) < 1e-3
+    assert (ours_in.grad.cpu() - t_in.grad).abs().max() < 1e-4
+
+
+def test_edge_cases(k2):
+    from gpu_util import DEV, dense_from_scores, fsa_to_host, host_to_fsa, intersect_raw
+    from oracle.common import HostFsaVec, make_arcs
+    a, scores, brs = _micro()
+    # both graphs against sequence 0 (a_to_b_map = [0, 0],
+    # k2/python/tests/intersect_dense_test.py:111-114)
+    want = oracle.intersect_dense(a, scores, brs, 100.0, np.array([0, 0], np.int32))
+    lat, ma, mb = intersect_raw(host_to_fsa(a), dense_from_scores(scores, brs), 100.0, [0, 0])
+    same_fsa(fsa_to_host(lat, ma, mb), want)
+    # no path of the right length: FSA 1 needs >= 3 arcs but its sequence has 2 rows
+    brs2 = np.array([0, 4, 6], np.int32)
+    sc2 = scores[:6].copy()
+    sc2[5] = scores[6]
+    want = oracle.intersect_dense(a, sc2, brs2, 100.0)
+    lat, ma, mb = intersect_raw(host_to_fsa(a), dense_from_scores(sc2, brs2), 100.0)
+    same_fsa(fsa_to_host(lat, ma, mb), want)
+    assert want.row_splits1[2] == want.row_splits1[1]  # empty second FSA
+    tot = lat.get_tot_scores(True, True).detach().cpu().numpy()
+    assert np.isneginf(tot[1]) and np.isfinite(tot[0])
+    # a label beyond the classes scores -inf: nothing survives, no error
+    bad = HostFsaVec(a.row_splits1.copy(), a.row_splits2.copy(), a.arcs.copy())
+    bad.arcs[:, 2] = np.where(bad.arcs[:, 2] > 0, 7, bad.arcs[:, 2])
+    lat, _, _ = intersect_raw(host_to_fsa(bad), dense_from_scores(scores, brs), 100.0)
+    assert lat.num_arcs == 0 and lat.arcs.num_states == 0
+    # unsorted sequence lengths are rejected like the reference's K2_CHECK
+    with pytest.raises(RuntimeError, match="sorted"):
+        intersect_raw(host_to_fsa(a), dense_from_scores(scores[[4, 5, 6, 0, 1, 2, 3]],
+                                                        np.array([0, 3, 7], np.int32)), 10.0)
+    with pytest.raises(RuntimeError, match="monotonic"):
+        intersect_raw(host_to_fsa(a), dense_from_scores(scores, brs), 10.0, [1, 0])
+    with pytest.raises(RuntimeError, match="output_beam"):
+        intersect_raw(host_to_fsa(a), dense_from_scores(scores, brs), 0.0)
+    # an FSA with no states in a_fsas
+    e = HostFsaVec(np.array([0, 4, 4, 8], np.int32), a.row_splits2, a.arcs)
+    sc3 = np.concatenate([scores[:4], scores[:4], scores[4:]])
+    brs3 = np.array([0, 4, 8, 11], np.int32)
+    want = oracle.intersect_dense(e, sc3, brs3, 100.0)
+    lat, ma, mb = intersect_raw(host_to_fsa(e), dense_from_scores(sc3, brs3), 100.0)
+    same_fsa(fsa_to_host(lat, ma, mb), want)
+
+
+def test_beam_shrinks_when_limits_hit(k2):
+    # intersect_dense.cu:240-320: retry with a smaller beam until within limits
+    from gpu_util import DEV, fsa_to_host, intersect_raw
+    from k2_b200 import synthetic as syn
+    w = syn.ctc_small(scale=0.5)
+    graphs = syn.build_graphs(w, DEV)
+    dense = k2.DenseFsaVec(w.log_probs.to(DEV), w.supervision_segments)
+    a_host = fsa_to_host(graphs)
+    sc = dense.scores.cpu().numpy()
+    for kw in (dict(max_states=2000), dict(max_arcs=3000)):
+        want = oracle.intersect_dense(a_host, sc, dense.h_row_splits, 10.0, **kw)
+        lat, ma, mb = intersect_raw(graphs, dense, 10.0, **kw)
+        same_fsa(fsa_to_host(lat, ma, mb), want)
+        assert want.extra["final_beam"] < 10.0
+        assert abs(lat.arcs.output_beam_used - want.extra["final_beam"]) < 1e-6
+
+
+def test_generic_ragged_ops(k2):
+    import ctypes
+    from gpu_util import DEV
+    from k2_b200 import _lib
+    rng = np.random.default_rng(3)
+    for n in (0, 1, 5, 2047, 2048, 2049, 100000, 1 << 20):
+        x = rng.integers(0, 7, size=n).astype(np.int32)
+        t = torch.from_numpy(x).to(DEV)
+        out = torch.empty(n + 1, dtype=torch.int32, device=DEV)
+        tmp = torch.empty(_lib.lib.k2b200_exclusive_sum_tmp_bytes(n) + 16, dtype=torch.uint8,
+                          device=DEV)
+        _lib.check(_lib.lib.k2b200_exclusive_sum(_lib.ptr(t), _lib.ptr(out), n, _lib.ptr(tmp),
+                                                 _lib.stream_of(torch.device(DEV))))
+        want = np.concatenate([[0], np.cumsum(x)]).astype(np.int32)
+        np.testing.assert_array_equal(out.cpu().numpy(), want)
+    # incoming index against a stable host sort
+    a = random_fsa_vec(rng, 9, max_states=30, max_arcs=300)
+    from gpu_util import host_to_fsa
+    f = host_to_fsa(a)
+    in_splits, in_arcs = f.arcs.incoming()
+    state_of = np.repeat(np.arange(a.num_states), np.diff(a.row_splits2))
+    fsa_of = np.repeat(np.arange(a.num_fsas), np.diff(a.row_splits1))[state_of]
+    dest01 = a.row_splits1[fsa_of] + a.arcs[:, 1]
+    order = np.argsort(dest01, kind="stable")
+    np.testing.assert_array_equal(in_arcs.cpu().numpy(), order)
+    cnt = np.bincount(dest01, minlength=a.num_states)
+    np.testing.assert_array_equal(in_splits.cpu().numpy(), np.concatenate([[0], np.cumsum(cnt)]))
+    np.testing.assert_array_equal(f.arcs.row_ids(2).cpu().numpy(), state_of)
