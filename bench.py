@@ -1,0 +1,369 @@
+"""Benchmark of the dense-intersection loss path: CTC loss forward + backward.
+
+  python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+                  [--workload ctc_large] [--scale 1.0]
+
+Workload (default): "ctc_large" - 64 utterances, T=1000, C=500, 600..1000 frames
+each, transcripts of 100..250 tokens, standard CTC graphs, output_beam 10;
+synthetic (seeded Gaussian logits, random transcripts).
+
+One step = DenseFsaVec construction from device-resident log-probs, ctc_loss
+(intersect_dense + log-semiring total scores in float64) and the backward pass to
+the gradient w.r.t. the log-probs.  `value` is supervised frames per second with
+the inputs resident in HBM; `e2e` times the same step from pinned host log-probs
+(host->device copy inside the timed region) to the loss on the host.  With N > 1
+every rank runs its own batch (weak scaling, utterances are independent) and the
+only collective is one all-reduce of [loss, frames].
+
+--impl reference times the reference's own CPU code for the same path
+(oracle/_ref/libk2ref.so when present, else the C restatement in oracle/) on the
+host cores, single-threaded as the reference is by construction.
+"""
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+
+def parse_args():
+    p = argparse.ArgumentParser()
+    p.add_argument("--gpus", type=int, default=1)
+    p.add_argument("--steps", type=int, default=20)
+    p.add_argument("--warmup", type=int, default=5)
+    p.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    p.add_argument("--workload", default="ctc_large")
+    p.add_argument("--scale", type=float, default=1.0)
+    p.add_argument("--no-cpu-baseline", action="store_true")
+    return p.parse_args()
+
+
+# --------------------------------------------------------------------------- clocks
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed
+    region runs."""
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+             "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.gpu_index = gpu_index
+        self.proc = None
+        self.lines = []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
+                 "-lms", "100", "-i", str(self.gpu_index)],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in self.lines:
+            f = [x.strip() for x in line.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1]))
+                mx.append(float(f[2]))
+            except ValueError:
+                continue
+            for name, v in zip(names, f[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None,
+                "sm_max_mhz": max(mx) if mx else None, "samples": len(sm),
+                "reasons": sorted(reasons)}
+
+
+# --------------------------------------------------------------------------- CPU arm
+def cpu_reference_step(w, graphs_host, scores, row_splits, impl_mod):
+    """The reference's path on the host: intersect_dense, log-semiring forward and
+    backward scores in double, total scores, arc posteriors and the gradient
+    scatter.  Returns (seconds, loss)."""
+    import numpy as np
+    t0 = time.perf_counter()
+    lat = impl_mod.intersect_dense(graphs_host, scores, row_splits, w.output_beam)
+    fwd = impl_mod.forward_scores(lat, True, True)
+    bwd = impl_mod.backward_scores(lat, True, True)
+    tot, post = impl_mod.tot_scores_and_arc_post(lat, fwd, bwd, True)
+    grad = np.zeros(scores.size, np.float32)
+    np.add.at(grad, lat.arc_map_b, np.exp(post).astype(np.float32))
+    dt = time.perf_counter() - t0
+    return dt, float(-tot.sum())
+
+
+def host_inputs(w):
+    """Graphs and the DenseFsaVec score matrix of a workload as host arrays."""
+    import numpy as np
+    from k2_b200 import synthetic as syn
+    from oracle.common import HostFsaVec
+    g = syn.build_graphs(w, "cpu")
+    a = g.arcs
+    graphs = HostFsaVec(a.h_row_splits1, a._row_splits2.numpy(), a.values().numpy())
+    seg = w.supervision_segments.numpy()
+    N, T, C = w.log_probs.shape
+    rows = int(seg[:, 2].sum() + len(seg))
+    scores = np.full((rows, C + 1), -np.inf, np.float32)
+    row_splits = np.zeros(len(seg) + 1, np.int32)
+    lp = w.log_probs.numpy()
+    r = 0
+    for i, (n, s, d) in enumerate(seg.tolist()):
+        scores[r:r + d, 1:] = lp[n, s:s + d]
+        scores[r + d, 0] = 0.0
+        r += d + 1
+        row_splits[i + 1] = r
+    return graphs, scores, row_splits
+
+
+def pick_cpu_impl():
+    from oracle import ref
+    if ref.available():
+        return ref, "reference"
+    from oracle import oracle
+    return oracle, "port"
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    from k2_b200 import synthetic as syn
+    w = syn.WORKLOADS[args.workload](seed=0, scale=args.scale)
+    impl_mod, kind = pick_cpu_impl()
+    graphs, scores, row_splits = host_inputs(w)
+    frames = w.num_frames
+    for _ in range(max(args.warmup, 0) and 1):  # one warm-up pass bounds the run time
+        cpu_reference_step(w, graphs, scores, row_splits, impl_mod)
+    times = []
+    for _ in range(args.steps):
+        dt, _loss = cpu_reference_step(w, graphs, scores, row_splits, impl_mod)
+        times.append(dt)
+    total = sum(times)
+    value = frames * args.steps / total
+    line = {
+        "impl": "reference", "metric": "ctc_loss_fwd_bwd_frames_per_sec", "value": value,
+        "unit": "frames/s", "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": 1e3 * total / args.steps, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f32+f64", "data": "synthetic",
+        "config": workload_config(w, args),
+        "cpu_baseline": {"value": value, "unit": "frames/s", "cores": 1, "kind": kind,
+                         "sample": f"{args.steps} full batches of {args.workload} "
+                                   f"({frames} frames each), intersect + log scores + posteriors "
+                                   "+ gradient scatter, host arrays in and out"},
+        "e2e": {"value": value, "unit": "frames/s", "h2d_bytes_per_step": 0,
+                "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line))
+
+
+def workload_config(w, args):
+    return {"workload": w.name, "utterances": int(w.log_probs.shape[0]),
+            "max_frames": int(w.log_probs.shape[1]), "classes": int(w.log_probs.shape[2]),
+            "frames": w.num_frames, "output_beam": w.output_beam, "scale": args.scale,
+            "l2": "working set per step (~650 MB: log-probs, score matrix, both gradients, "
+                  "Viterbi grids) exceeds the 126 MB L2; no explicit flush"}
+
+
+# --------------------------------------------------------------------------- GPU arm
+def run_ours(args):
+    import numpy as np
+    import torch
+
+    import k2_b200 as k2
+    from k2_b200 import _lib
+    from k2_b200 import synthetic as syn
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    assert torch.cuda.is_available(), "bench.py needs a CUDA device (no CPU fallback)"
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=dev)
+
+    # every rank owns a whole batch (weak scaling); seeds differ per rank
+    w = syn.WORKLOADS[args.workload](seed=rank, scale=args.scale)
+    frames = w.num_frames
+    graphs = syn.build_graphs(w, dev)
+    graphs.arcs.incoming()  # graph preprocessing is cached across steps
+    host_lp = w.log_probs.pin_memory()
+    dev_lp = w.log_probs.to(dev)
+    seg = w.supervision_segments
+    red = torch.zeros(2, dtype=torch.float64, device=dev)
+
+    def step(lp_src, from_host):
+        if from_host:
+            lp = lp_src.to(dev, non_blocking=True)
+        else:
+            lp = lp_src
+        lp = lp.detach().requires_grad_(True)
+        dense = k2.DenseFsaVec(lp, seg)
+        loss = k2.ctc_loss(graphs, dense, output_beam=w.output_beam, reduction="sum")
+        loss.backward()
+        if dist is not None:
+            red[0] = loss.detach().double()
+            red[1] = float(frames)
+            dist.all_reduce(red)
+            out = red[0]
+        else:
+            out = loss.detach()
+        if from_host:
+            return float(out.item()), lp.grad
+        return out, lp.grad
+
+    def barrier():
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(nsteps, from_host, profile=False):
+        src = host_lp if from_host else dev_lp
+        barrier()
+        if profile:
+            _lib.profile_enable(True)
+        launches0 = _lib.launch_count()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        t0 = time.perf_counter()
+        e0.record()
+        for _ in range(nsteps):
+            step(src, from_host)
+        e1.record()
+        barrier()
+        wall = time.perf_counter() - t0
+        ms = e0.elapsed_time(e1)
+        launches = _lib.launch_count() - launches0
+        phases = None
+        if profile:
+            phases = _lib.profile_read()
+            _lib.profile_enable(False)
+        if dist is not None:
+            t = torch.tensor([ms], dtype=torch.float64, device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        return ms, wall, launches, phases
+
+    for _ in range(max(args.warmup, 3)):
+        step(dev_lp, False)
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    ms, wall, launches, _ = timed(args.steps, False)
+    # the same steps again with per-phase events, for the roofline of the top kernel
+    _, _, _, phases = timed(args.steps, False, profile=True)
+    for _ in range(2):
+        step(host_lp, True)
+    e2e_ms, e2e_wall, _, _ = timed(args.steps, True)
+    clocks = sampler.stop() if rank == 0 else None
+
+    # lattice size for the algorithmic-byte figure
+    with torch.no_grad():
+        dense = k2.DenseFsaVec(dev_lp, seg)
+        lat = k2.intersect_dense(graphs, dense, w.output_beam)
+    N, T, C = w.log_probs.shape
+    A = graphs.num_arcs
+    A_out, S_out = lat.num_arcs, lat.arcs.num_states
+    arc_frames = int(sum(int(graphs.arcs.h_arc_splits[i + 1] - graphs.arcs.h_arc_splits[i]) *
+                         int(seg[i, 2]) for i in range(seg.shape[0])))
+    # whole path: rows once, dense gradient once, graph once, lattice once
+    b_alg = 4 * frames * C + 4 * N * T * C + 16 * A + 24 * A_out + 8 * S_out
+    # dominant kernel (Viterbi recursion): each supervised row and the graph once
+    b_vit = 4 * frames * C + 16 * A
+    peaks = {}
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            peaks = json.load(f)
+    except OSError:
+        pass
+    hbm_peak = float(peaks.get("hbm_gbs", 6650.0))
+    peak_src = "measured" if "hbm_gbs" in peaks else "fallback"
+    vit_ms, vit_n = phases["viterbi"]
+    vit_avg_ms = vit_ms / max(vit_n, 1)
+    achieved = b_vit / (vit_avg_ms * 1e-3) / 1e9 if vit_avg_ms > 0 else 0.0
+
+    if rank != 0:
+        if dist is not None:
+            dist.destroy_process_group()
+        return
+
+    sec = ms * 1e-3
+    value = world * frames * args.steps / sec
+    e2e_value = world * frames * args.steps / (e2e_ms * 1e-3)
+    line = {
+        "metric": "ctc_loss_fwd_bwd_frames_per_sec", "value": value, "unit": "frames/s",
+        "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
+        "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f32+f64", "data": "synthetic",
+        "config": workload_config(w, args),
+        "arc_frames_per_sec": world * arc_frames * args.steps / sec,
+        "path_gbs": b_alg * args.steps / sec / 1e9,
+        "path_frac_of_hbm": b_alg * args.steps / sec / 1e9 / hbm_peak,
+        "wall_ms_per_step": 1e3 * wall / args.steps,
+        "phases_ms_per_step": {k: v[0] / args.steps for k, v in phases.items()},
+        "lattice": {"arcs": A_out, "states": S_out, "graph_arcs": A, "arc_frames": arc_frames},
+        "roofline": {"kernel": "PersistentViterbi", "bound": "hbm", "achieved": achieved,
+                     "peak": hbm_peak, "unit": "GB/s", "frac": achieved / hbm_peak,
+                     "peak_source": peak_src, "algorithmic_bytes_per_launch": b_vit,
+                     "avg_launch_ms": vit_avg_ms, "traffic": None},
+        "e2e": {"value": e2e_value, "unit": "frames/s",
+                "h2d_bytes_per_step": int(w.log_probs.numel() * 4), "d2h_bytes_per_step": 8,
+                "ms_per_step": e2e_ms / args.steps},
+        "gpu_launches": int(launches),
+        "clocks": clocks,
+    }
+    if world == 1 and not args.no_cpu_baseline:
+        impl_mod, kind = pick_cpu_impl()
+        w0 = w
+        graphs_h, scores_h, rs_h = host_inputs(w0)
+        cpu_reference_step(w0, graphs_h, scores_h, rs_h, impl_mod)
+        ts = [cpu_reference_step(w0, graphs_h, scores_h, rs_h, impl_mod)[0] for _ in range(3)]
+        best = min(ts)
+        line["cpu_baseline"] = {
+            "value": frames / best, "unit": "frames/s", "cores": 1, "kind": kind,
+            "host_cores": os.cpu_count(),
+            "sample": f"best of 3 full batches of {w0.name} ({frames} frames): intersect + "
+                      "log scores + posteriors + gradient scatter; the reference's path is "
+                      "single-threaded by construction"}
+    print(json.dumps(line))
+    if dist is not None:
+        dist.destroy_process_group()
+
+
+def main():
+    args = parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

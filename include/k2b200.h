@@ -45,6 +45,19 @@ const char *k2b200_last_error(void);
 /* ABI version of the library (bumped on any signature change). */
 int32_t k2b200_abi_version(void);
 
+/* Benchmark bookkeeping (no counterpart in the reference's bindings; its
+ * benchmark harness, k2/csrc/benchmark/benchmark.h:49-66, times from outside).
+ * k2b200_kernel_launch_count: kernels launched by this library so far.
+ * k2b200_profile_enable(1) makes the entry points bracket their phases with
+ * cudaEvents on the launching stream; k2b200_profile_read_ms(phase, &n) waits
+ * for them, returns the summed milliseconds of the n recorded intervals and
+ * resets the phase.  Phases: 0 Viterbi recursion, 1 pruning (count + numbering),
+ * 2 lattice emission, 3 forward/backward scores, 4 posteriors + gradient
+ * scatter, 5 incoming-arc index. */
+int64_t k2b200_kernel_launch_count(void);
+void k2b200_profile_enable(int32_t on);
+double k2b200_profile_read_ms(int32_t phase, int64_t *intervals);
+
 /* ---------------------------------------------------------------------------
  * Ragged helpers.
  * ------------------------------------------------------------------------- */

@@ -55,6 +55,9 @@ def _sig(name, restype, argtypes):
 
 _sig("k2b200_last_error", ctypes.c_char_p, [])
 _sig("k2b200_abi_version", c_i32, [])
+_sig("k2b200_kernel_launch_count", c_i64, [])
+_sig("k2b200_profile_enable", None, [c_i32])
+_sig("k2b200_profile_read_ms", ctypes.c_double, [c_i32, ctypes.POINTER(c_i64)])
 _sig("k2b200_row_splits_to_row_ids", c_i32, [c_vp, c_i32, c_vp, c_i32, c_vp])
 _sig("k2b200_exclusive_sum_tmp_bytes", c_sz, [c_i64])
 _sig("k2b200_exclusive_sum", c_i32, [c_vp, c_vp, c_i64, c_vp, c_vp])
@@ -87,7 +90,8 @@ _sig("k2b200_fsa_properties", c_i32,
      [c_vp, c_vp, c_vp, c_vp, c_vp, c_i32, c_i32, c_i32, c_vp, c_vp, c_vp])
 
 EXPORTED = [
-    "k2b200_last_error", "k2b200_abi_version", "k2b200_row_splits_to_row_ids",
+    "k2b200_last_error", "k2b200_abi_version", "k2b200_kernel_launch_count",
+    "k2b200_profile_enable", "k2b200_profile_read_ms", "k2b200_row_splits_to_row_ids",
     "k2b200_exclusive_sum_tmp_bytes", "k2b200_exclusive_sum", "k2b200_fsa_incoming_tmp_bytes",
     "k2b200_fsa_incoming", "k2b200_intersect_dense_workspace_bytes",
     "k2b200_intersect_dense_prune", "k2b200_intersect_dense_emit", "k2b200_fsa_scores",
@@ -133,11 +137,26 @@ def require_cuda(t: torch.Tensor, what: str) -> None:
 
 
 def launch_count() -> int:
-    return _launches[0]
+    """Kernels launched by libk2b200.so so far (counted inside the library)."""
+    return int(lib.k2b200_kernel_launch_count())
 
 
-_launches = [0]
+def note_launches(n: int) -> None:  # kept for callers; the library counts itself
+    pass
 
 
-def note_launches(n: int) -> None:
-    _launches[0] += n
+PHASES = ["viterbi", "prune", "emit", "scores", "post", "incoming"]
+
+
+def profile_enable(on: bool) -> None:
+    lib.k2b200_profile_enable(int(on))
+
+
+def profile_read():
+    """{phase: (milliseconds, intervals)} since the last read."""
+    out = {}
+    for k, name in enumerate(PHASES):
+        n = c_i64()
+        ms = lib.k2b200_profile_read_ms(k, ctypes.byref(n))
+        out[name] = (float(ms), int(n.value))
+    return out

@@ -53,6 +53,22 @@ const char *LastError();
     if (s__ != ::k2b::kOk) return s__;    \
   } while (0)
 
+// Bookkeeping for benchmarks: number of kernels this library has launched, and
+// optional cudaEvent timing of named phases on the launching stream.
+void NoteLaunch(int n = 1);
+enum Phase : int { kPhaseViterbi = 0, kPhasePrune, kPhaseEmit, kPhaseScores, kPhasePost,
+                   kPhaseIncoming, kNumPhases };
+long long LaunchCount();
+void SetProfiling(bool on);
+double ReadPhase(int phase, long long *count);
+struct PhaseTimer {  // records start/stop events when profiling is enabled
+  PhaseTimer(int phase, cudaStream_t stream);
+  ~PhaseTimer();
+  int phase_;
+  cudaStream_t stream_;
+  int slot_;
+};
+
 static inline size_t AlignUp(size_t x, size_t a = 256) { return (x + a - 1) / a * a; }
 
 static inline int CeilDiv(int64_t a, int64_t b) { return (int)((a + b - 1) / b); }

@@ -420,16 +420,16 @@ static int32_t RunViterbi(const Layout &L, const k2b200_intersect_args *a, char 
   }
   const Arc *arcs = reinterpret_cast<const Arc *>(a->a_arcs);
   dim3 init_grid(CeilDiv(L.max_states, 256), a->num_fsas);
-  ViterbiInit<<<init_grid, 256, 0, stream>>>(d_infos, fwd, bwd);
+  { ViterbiInit<<<init_grid, 256, 0, stream>>>(d_infos, fwd, bwd); NoteLaunch(); }
   // lanes per state from the mean degree of the batch
   int32_t mean_deg = a->num_states > 0 ? (a->num_arcs + a->num_states - 1) / a->num_states : 1;
   int32_t lanes_log2 = 0;
   while ((1 << lanes_log2) < mean_deg && lanes_log2 < 5) ++lanes_log2;
   dim3 grid(CeilDiv((int64_t)L.max_states << lanes_log2, 256), a->num_fsas, 2);
   for (int32_t t = 1; t <= L.max_tk; ++t) {
-    ViterbiStep<<<grid, 256, 0, stream>>>(d_infos, t, arcs, a->a_row_splits2, a->a_in_splits,
+    { ViterbiStep<<<grid, 256, 0, stream>>>(d_infos, t, arcs, a->a_row_splits2, a->a_in_splits,
                                           a->a_in_arcs, a->scores, a->cols, fwd, bwd,
-                                          lanes_log2);
+                                          lanes_log2); NoteLaunch(); }
   }
   K2B_CUDA_OK(cudaGetLastError());
   return kOk;
@@ -480,20 +480,24 @@ int32_t k2b200_intersect_dense_prune(const k2b200_intersect_args *args, void *wo
   long long *totals = reinterpret_cast<long long *>(ws + L.off_totals);
   const Arc *arcs = reinterpret_cast<const Arc *>(args->a_arcs);
 
-  K2B_FORWARD(RunViterbi(L, args, ws, stream));
+  {
+    PhaseTimer timer(kPhaseViterbi, stream);
+    K2B_FORWARD(RunViterbi(L, args, ws, stream));
+  }
+  PhaseTimer prune_timer(kPhasePrune, stream);
 
   float beam = args->output_beam;
   long long h_totals[3] = {0, 0, 0};
   for (int iter = 0;; ++iter) {
-    Cutoffs<<<CeilDiv(args->num_fsas, 128), 128, 0, stream>>>(d_infos, args->num_fsas, fwd, bwd,
-                                                              beam, cutoffs);
+    { Cutoffs<<<CeilDiv(args->num_fsas, 128), 128, 0, stream>>>(d_infos, args->num_fsas, fwd, bwd,
+                                                              beam, cutoffs); NoteLaunch(); }
     if (L.total_words > 0)
-      CountKept<<<L.count_blocks, kCountThreads, 0, stream>>>(
+      { CountKept<<<L.count_blocks, kCountThreads, 0, stream>>>(
           d_infos, args->num_fsas, L.total_words, arcs, args->a_row_splits2, args->scores,
-          args->cols, fwd, bwd, cutoffs, mask, counts, block_cand);
+          args->cols, fwd, bwd, cutoffs, mask, counts, block_cand); NoteLaunch(); }
     K2B_FORWARD(ExclusiveSum2(counts, counts, L.total_words, scan_tmp, stream));
-    Totals<<<1, 256, 0, stream>>>(counts, L.total_words, block_cand,
-                                  L.total_words > 0 ? L.count_blocks : 0, totals);
+    { Totals<<<1, 256, 0, stream>>>(counts, L.total_words, block_cand,
+                                  L.total_words > 0 ? L.count_blocks : 0, totals); NoteLaunch(); }
     K2B_CUDA_OK(cudaGetLastError());
     K2B_CUDA_OK(cudaMemcpyAsync(h_totals, totals, sizeof(h_totals), cudaMemcpyDeviceToHost,
                                 stream));
@@ -540,18 +544,19 @@ int32_t k2b200_intersect_dense_emit(const k2b200_intersect_args *args, void *wor
               "NULL lattice output pointer");
   char *ws = reinterpret_cast<char *>(workspace);
   const FsaInfo *d_infos = reinterpret_cast<const FsaInfo *>(ws + L.off_infos);
-  EmitTails<<<CeilDiv(args->num_fsas + 1, 128), 128, 0, stream>>>(
+  PhaseTimer timer(kPhaseEmit, stream);
+  { EmitTails<<<CeilDiv(args->num_fsas + 1, 128), 128, 0, stream>>>(
       d_infos, args->num_fsas, L.total_words, (int32_t)L.total_levels,
-      reinterpret_cast<const int2 *>(ws + L.off_counts), *out);
+      reinterpret_cast<const int2 *>(ws + L.off_counts), *out); NoteLaunch(); }
   if (L.total_words > 0)
-    EmitLattice<<<CeilDiv(L.total_words, 8), 256, 0, stream>>>(
+    { EmitLattice<<<CeilDiv(L.total_words, 8), 256, 0, stream>>>(
         d_infos, args->num_fsas, L.total_words, reinterpret_cast<const Arc *>(args->a_arcs),
         args->a_row_splits2, args->scores, args->cols,
         reinterpret_cast<const float *>(ws + L.off_fwd),
         reinterpret_cast<const float *>(ws + L.off_bwd),
         reinterpret_cast<const float *>(ws + L.off_cutoffs),
         reinterpret_cast<const uint32_t *>(ws + L.off_mask),
-        reinterpret_cast<const int2 *>(ws + L.off_counts), *out);
+        reinterpret_cast<const int2 *>(ws + L.off_counts), *out); NoteLaunch(); }
   K2B_CUDA_OK(cudaGetLastError());
   return kOk;
 }

@@ -3,6 +3,10 @@
 // the place of the cub / moderngpu wrappers the reference leans on
 // (k2/csrc/utils_inl.h:40-90 ExclusiveSum, k2/csrc/utils.cu:75-200
 // RowSplitsToRowIds, k2/csrc/fsa_utils.cu:901-928 GetIncomingArcs).
+#include <atomic>
+#include <mutex>
+#include <vector>
+
 #include "common.cuh"
 
 namespace k2b {
@@ -19,6 +23,64 @@ void SetError(const char *fmt, ...) {
   va_end(ap);
 }
 const char *LastError() { return g_error; }
+
+// ----------------------------------------------------------------------------
+// launch counter and phase timers
+// ----------------------------------------------------------------------------
+static std::atomic<long long> g_launches{0};
+void NoteLaunch(int n) { g_launches.fetch_add(n, std::memory_order_relaxed); }
+long long LaunchCount() { return g_launches.load(std::memory_order_relaxed); }
+
+namespace {
+struct EventPair { cudaEvent_t start, stop; };
+struct PhaseLog {
+  std::vector<EventPair> pool;  // reused across reads
+  size_t used = 0;
+};
+std::mutex g_prof_mutex;
+bool g_profiling = false;
+PhaseLog g_phase[kNumPhases];
+}  // namespace
+
+void SetProfiling(bool on) {
+  std::lock_guard<std::mutex> lock(g_prof_mutex);
+  g_profiling = on;
+  for (auto &p : g_phase) p.used = 0;
+}
+
+PhaseTimer::PhaseTimer(int phase, cudaStream_t stream) : phase_(phase), stream_(stream), slot_(-1) {
+  std::lock_guard<std::mutex> lock(g_prof_mutex);
+  if (!g_profiling) return;
+  PhaseLog &log = g_phase[phase];
+  if (log.used == log.pool.size()) {
+    EventPair e;
+    if (cudaEventCreate(&e.start) != cudaSuccess || cudaEventCreate(&e.stop) != cudaSuccess) return;
+    log.pool.push_back(e);
+  }
+  slot_ = (int)log.used++;
+  cudaEventRecord(log.pool[slot_].start, stream);
+}
+PhaseTimer::~PhaseTimer() {
+  if (slot_ < 0) return;
+  std::lock_guard<std::mutex> lock(g_prof_mutex);
+  cudaEventRecord(g_phase[phase_].pool[slot_].stop, stream_);
+}
+
+// Sum of the recorded durations of `phase` in ms (waits for the events); resets
+// the phase's log.  count receives the number of recorded intervals.
+double ReadPhase(int phase, long long *count) {
+  std::lock_guard<std::mutex> lock(g_prof_mutex);
+  PhaseLog &log = g_phase[phase];
+  double total = 0;
+  for (size_t k = 0; k < log.used; ++k) {
+    float ms = 0;
+    cudaEventSynchronize(log.pool[k].stop);
+    if (cudaEventElapsedTime(&ms, log.pool[k].start, log.pool[k].stop) == cudaSuccess) total += ms;
+  }
+  if (count) *count = (long long)log.used;
+  log.used = 0;
+  return total;
+}
 
 // ----------------------------------------------------------------------------
 // exclusive sum: reduce tiles -> scan the tile sums in one block -> rescan tiles
@@ -137,9 +199,9 @@ static int32_t ExclusiveSumImpl(const T *in, T *out, int64_t n, T *tmp, cudaStre
     return kTooLarge;
   }
   int32_t nb = (int32_t)nb64;
-  ScanTileSums<T><<<nb, kScanThreads, 0, stream>>>(in, n, tmp);
-  ScanTileOffsets<T><<<1, kScanThreads, 0, stream>>>(tmp, nb);
-  ScanApply<T><<<nb, kScanThreads, 0, stream>>>(in, out, n, tmp);
+  { ScanTileSums<T><<<nb, kScanThreads, 0, stream>>>(in, n, tmp); NoteLaunch(); }
+  { ScanTileOffsets<T><<<1, kScanThreads, 0, stream>>>(tmp, nb); NoteLaunch(); }
+  { ScanApply<T><<<nb, kScanThreads, 0, stream>>>(in, out, n, tmp); NoteLaunch(); }
   K2B_CUDA_OK(cudaGetLastError());
   return kOk;
 }
@@ -170,8 +232,8 @@ __global__ void RowIdsKernel(const int32_t *__restrict__ row_splits, int32_t num
 int32_t RowSplitsToRowIds(const int32_t *row_splits, int32_t num_rows, int32_t *row_ids,
                           int32_t num_elems, cudaStream_t stream) {
   if (num_elems <= 0) return kOk;
-  RowIdsKernel<<<CeilDiv(num_elems, 256), 256, 0, stream>>>(row_splits, num_rows, row_ids,
-                                                            num_elems);
+  { RowIdsKernel<<<CeilDiv(num_elems, 256), 256, 0, stream>>>(row_splits, num_rows, row_ids,
+                                                            num_elems); NoteLaunch(); }
   K2B_CUDA_OK(cudaGetLastError());
   return kOk;
 }
@@ -257,18 +319,18 @@ int32_t BuildIncoming(const int32_t *row_splits1, const int32_t *row_ids1,
 
   K2B_CUDA_OK(cudaMemsetAsync(counts, 0, sizeof(int32_t) * ((size_t)num_states + 1), stream));
   if (num_arcs > 0)
-    IncomingCount<<<CeilDiv(num_arcs, 256), 256, 0, stream>>>(row_splits1, row_ids1, row_ids2,
-                                                              arcs, num_arcs, counts);
+    { IncomingCount<<<CeilDiv(num_arcs, 256), 256, 0, stream>>>(row_splits1, row_ids1, row_ids2,
+                                                              arcs, num_arcs, counts); NoteLaunch(); }
   K2B_FORWARD(ExclusiveSum(counts, in_splits, num_states, scan_tmp, stream));
   if (num_arcs > 0) {
     K2B_CUDA_OK(cudaMemsetAsync(counts, 0, sizeof(int32_t) * ((size_t)num_states + 1), stream));
-    IncomingFill<<<CeilDiv(num_arcs, 256), 256, 0, stream>>>(row_splits1, row_ids1, row_ids2,
+    { IncomingFill<<<CeilDiv(num_arcs, 256), 256, 0, stream>>>(row_splits1, row_ids1, row_ids2,
                                                              arcs, num_arcs, in_splits, counts,
-                                                             unsorted);
-    IncomingSortSmall<<<CeilDiv(num_states, 256), 256, 0, stream>>>(in_splits, num_states,
-                                                                    unsorted, in_arcs);
-    IncomingSortLarge<<<CeilDiv((int64_t)num_states * 32, 256), 256, 0, stream>>>(
-        in_splits, num_states, unsorted, in_arcs);
+                                                             unsorted); NoteLaunch(); }
+    { IncomingSortSmall<<<CeilDiv(num_states, 256), 256, 0, stream>>>(in_splits, num_states,
+                                                                    unsorted, in_arcs); NoteLaunch(); }
+    { IncomingSortLarge<<<CeilDiv((int64_t)num_states * 32, 256), 256, 0, stream>>>(
+        in_splits, num_states, unsorted, in_arcs); NoteLaunch(); }
   }
   K2B_CUDA_OK(cudaGetLastError());
   return kOk;

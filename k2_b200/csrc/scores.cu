@@ -293,18 +293,19 @@ static int32_t LaunchScores(const int32_t *rs1, const int32_t *rs2, const int32_
   int32_t ndir = (fwd != nullptr) + (bwd != nullptr);
   if (ndir == 0 || num_fsas == 0) return kOk;
   int32_t dir_base = fwd ? 0 : 1;
+  PhaseTimer timer(kPhaseScores, stream);
   for (int32_t first = 0; first < num_fsas; first += 65535) {
     int32_t n = num_fsas - first < 65535 ? num_fsas - first : 65535;
     dim3 grid(ndir, n);
     if (log_semiring)
-      LayeredScores<Real, true><<<grid, 256, 0, stream>>>(rs1 + first, rs2, rid2, arcs, in_splits,
+      { LayeredScores<Real, true><<<grid, 256, 0, stream>>>(rs1 + first, rs2, rid2, arcs, in_splits,
                                                          in_arcs, lvl_off + first, lvl_splits,
-                                                         fwd, bwd, nullptr, dir_base);
+                                                         fwd, bwd, nullptr, dir_base); NoteLaunch(); }
     else
-      LayeredScores<Real, false><<<grid, 256, 0, stream>>>(rs1 + first, rs2, rid2, arcs,
+      { LayeredScores<Real, false><<<grid, 256, 0, stream>>>(rs1 + first, rs2, rid2, arcs,
                                                           in_splits, in_arcs, lvl_off + first,
                                                           lvl_splits, fwd, bwd, entering,
-                                                          dir_base);
+                                                          dir_base); NoteLaunch(); }
   }
   K2B_CUDA_OK(cudaGetLastError());
   return kOk;
@@ -314,6 +315,14 @@ extern "C" {
 
 const char *k2b200_last_error(void) { return LastError(); }
 int32_t k2b200_abi_version(void) { return 1; }
+int64_t k2b200_kernel_launch_count(void) { return LaunchCount(); }
+void k2b200_profile_enable(int32_t on) { SetProfiling(on != 0); }
+double k2b200_profile_read_ms(int32_t phase, int64_t *intervals) {
+  long long n = 0;
+  double ms = (phase >= 0 && phase < kNumPhases) ? ReadPhase(phase, &n) : 0.0;
+  if (intervals) *intervals = n;
+  return ms;
+}
 
 int32_t k2b200_row_splits_to_row_ids(const int32_t *row_splits, int32_t num_rows,
                                      int32_t *row_ids, int32_t num_elems, void *stream) {
@@ -335,6 +344,7 @@ int32_t k2b200_fsa_incoming(const int32_t *row_splits1, const int32_t *row_ids1,
                             int32_t *in_arcs, void *tmp, void *stream) {
   K2B_REQUIRE(num_fsas >= 0 && num_states >= 0 && num_arcs >= 0, "negative size");
   K2B_REQUIRE(in_splits && tmp, "NULL pointer");
+  PhaseTimer timer(kPhaseIncoming, STREAM(stream));
   return BuildIncoming(row_splits1, row_ids1, row_ids2, reinterpret_cast<const Arc *>(arcs),
                        num_fsas, num_states, num_arcs, in_splits, in_arcs, tmp, STREAM(stream));
 }
@@ -367,13 +377,13 @@ int32_t k2b200_fsa_tot_scores(const int32_t *row_splits1, int32_t num_fsas, int3
                               const void *forward, void *tot_scores, void *stream) {
   if (num_fsas <= 0) return kOk;
   if (use_double)
-    TotScores<double><<<CeilDiv(num_fsas, 128), 128, 0, STREAM(stream)>>>(
+    { TotScores<double><<<CeilDiv(num_fsas, 128), 128, 0, STREAM(stream)>>>(
         row_splits1, num_fsas, reinterpret_cast<const double *>(forward),
-        reinterpret_cast<double *>(tot_scores));
+        reinterpret_cast<double *>(tot_scores)); NoteLaunch(); }
   else
-    TotScores<float><<<CeilDiv(num_fsas, 128), 128, 0, STREAM(stream)>>>(
+    { TotScores<float><<<CeilDiv(num_fsas, 128), 128, 0, STREAM(stream)>>>(
         row_splits1, num_fsas, reinterpret_cast<const float *>(forward),
-        reinterpret_cast<float *>(tot_scores));
+        reinterpret_cast<float *>(tot_scores)); NoteLaunch(); }
   K2B_CUDA_OK(cudaGetLastError());
   return kOk;
 }
@@ -382,17 +392,18 @@ int32_t k2b200_fsa_arc_post(const int32_t *row_splits1, const int32_t *row_ids1,
                             const int32_t *row_ids2, const void *arcs, int32_t num_fsas,
                             int32_t num_arcs, int32_t use_double, const void *forward,
                             const void *backward, void *arc_post, void *stream) {
+  PhaseTimer timer(kPhasePost, STREAM(stream));
   (void)num_fsas;
   if (num_arcs <= 0) return kOk;
   const Arc *a = reinterpret_cast<const Arc *>(arcs);
   if (use_double)
-    ArcPost<double><<<CeilDiv(num_arcs, 256), 256, 0, STREAM(stream)>>>(
+    { ArcPost<double><<<CeilDiv(num_arcs, 256), 256, 0, STREAM(stream)>>>(
         row_splits1, row_ids1, row_ids2, a, num_arcs, reinterpret_cast<const double *>(forward),
-        reinterpret_cast<const double *>(backward), reinterpret_cast<double *>(arc_post));
+        reinterpret_cast<const double *>(backward), reinterpret_cast<double *>(arc_post)); NoteLaunch(); }
   else
-    ArcPost<float><<<CeilDiv(num_arcs, 256), 256, 0, STREAM(stream)>>>(
+    { ArcPost<float><<<CeilDiv(num_arcs, 256), 256, 0, STREAM(stream)>>>(
         row_splits1, row_ids1, row_ids2, a, num_arcs, reinterpret_cast<const float *>(forward),
-        reinterpret_cast<const float *>(backward), reinterpret_cast<float *>(arc_post));
+        reinterpret_cast<const float *>(backward), reinterpret_cast<float *>(arc_post)); NoteLaunch(); }
   K2B_CUDA_OK(cudaGetLastError());
   return kOk;
 }
@@ -401,15 +412,16 @@ int32_t k2b200_tot_scores_log_backward(const int32_t *row_ids1, const int32_t *r
                                        int32_t num_arcs, int32_t use_double,
                                        const void *arc_post, const void *tot_scores_grad,
                                        int64_t grad_stride, float *arc_grad, void *stream) {
+  PhaseTimer timer(kPhasePost, STREAM(stream));
   if (num_arcs <= 0) return kOk;
   if (use_double)
-    LogBackward<double><<<CeilDiv(num_arcs, 256), 256, 0, STREAM(stream)>>>(
+    { LogBackward<double><<<CeilDiv(num_arcs, 256), 256, 0, STREAM(stream)>>>(
         row_ids1, row_ids2, num_arcs, reinterpret_cast<const double *>(arc_post),
-        reinterpret_cast<const double *>(tot_scores_grad), grad_stride, arc_grad);
+        reinterpret_cast<const double *>(tot_scores_grad), grad_stride, arc_grad); NoteLaunch(); }
   else
-    LogBackward<float><<<CeilDiv(num_arcs, 256), 256, 0, STREAM(stream)>>>(
+    { LogBackward<float><<<CeilDiv(num_arcs, 256), 256, 0, STREAM(stream)>>>(
         row_ids1, row_ids2, num_arcs, reinterpret_cast<const float *>(arc_post),
-        reinterpret_cast<const float *>(tot_scores_grad), grad_stride, arc_grad);
+        reinterpret_cast<const float *>(tot_scores_grad), grad_stride, arc_grad); NoteLaunch(); }
   K2B_CUDA_OK(cudaGetLastError());
   return kOk;
 }
@@ -423,21 +435,22 @@ int32_t k2b200_tot_scores_tropical_backward(const int32_t *row_ids1, const int32
   K2B_CUDA_OK(cudaMemsetAsync(arc_grad, 0, sizeof(float) * (size_t)num_arcs, STREAM(stream)));
   if (num_best_arcs <= 0) return kOk;
   if (use_double)
-    TropicalBackward<double><<<CeilDiv(num_best_arcs, 256), 256, 0, STREAM(stream)>>>(
+    { TropicalBackward<double><<<CeilDiv(num_best_arcs, 256), 256, 0, STREAM(stream)>>>(
         row_ids1, row_ids2, best_arcs, num_best_arcs,
-        reinterpret_cast<const double *>(tot_scores_grad), grad_stride, arc_grad);
+        reinterpret_cast<const double *>(tot_scores_grad), grad_stride, arc_grad); NoteLaunch(); }
   else
-    TropicalBackward<float><<<CeilDiv(num_best_arcs, 256), 256, 0, STREAM(stream)>>>(
+    { TropicalBackward<float><<<CeilDiv(num_best_arcs, 256), 256, 0, STREAM(stream)>>>(
         row_ids1, row_ids2, best_arcs, num_best_arcs,
-        reinterpret_cast<const float *>(tot_scores_grad), grad_stride, arc_grad);
+        reinterpret_cast<const float *>(tot_scores_grad), grad_stride, arc_grad); NoteLaunch(); }
   K2B_CUDA_OK(cudaGetLastError());
   return kOk;
 }
 
 int32_t k2b200_index_add(const int32_t *index, const float *value, int32_t n, float *in_out,
                          int64_t in_out_size, void *stream) {
+  PhaseTimer timer(kPhasePost, STREAM(stream));
   if (n <= 0) return kOk;
-  IndexAdd<<<CeilDiv(n, 256), 256, 0, STREAM(stream)>>>(index, value, n, in_out, in_out_size);
+  { IndexAdd<<<CeilDiv(n, 256), 256, 0, STREAM(stream)>>>(index, value, n, in_out, in_out_size); NoteLaunch(); }
   K2B_CUDA_OK(cudaGetLastError());
   return kOk;
 }
@@ -445,7 +458,7 @@ int32_t k2b200_index_add(const int32_t *index, const float *value, int32_t n, fl
 int32_t k2b200_index_select_i32(const int32_t *src, int64_t src_size, const int32_t *index,
                                 int32_t n, int32_t *out, void *stream) {
   if (n <= 0) return kOk;
-  IndexSelectI32<<<CeilDiv(n, 256), 256, 0, STREAM(stream)>>>(src, src_size, index, n, out);
+  { IndexSelectI32<<<CeilDiv(n, 256), 256, 0, STREAM(stream)>>>(src, src_size, index, n, out); NoteLaunch(); }
   K2B_CUDA_OK(cudaGetLastError());
   return kOk;
 }
@@ -465,11 +478,11 @@ int32_t k2b200_shortest_path(const int32_t *row_splits1, const void *arcs,
   int32_t *scan_tmp =
       reinterpret_cast<int32_t *>(p + AlignUp(sizeof(int32_t) * ((size_t)num_fsas + 1)));
   const Arc *a = reinterpret_cast<const Arc *>(arcs);
-  PathLengths<<<CeilDiv(num_fsas, 64), 64, 0, STREAM(stream)>>>(row_splits1, a, entering_arcs,
-                                                               num_fsas, lengths);
+  { PathLengths<<<CeilDiv(num_fsas, 64), 64, 0, STREAM(stream)>>>(row_splits1, a, entering_arcs,
+                                                               num_fsas, lengths); NoteLaunch(); }
   K2B_FORWARD(ExclusiveSum(lengths, path_splits, num_fsas, scan_tmp, STREAM(stream)));
-  PathFill<<<CeilDiv(num_fsas, 64), 64, 0, STREAM(stream)>>>(row_splits1, a, entering_arcs,
-                                                            num_fsas, path_splits, best_arcs);
+  { PathFill<<<CeilDiv(num_fsas, 64), 64, 0, STREAM(stream)>>>(row_splits1, a, entering_arcs,
+                                                            num_fsas, path_splits, best_arcs); NoteLaunch(); }
   K2B_CUDA_OK(cudaGetLastError());
   return kOk;
 }
@@ -487,17 +500,17 @@ int32_t k2b200_fsa_properties(const int32_t *row_splits1, const int32_t *row_ids
   char *reach = reinterpret_cast<char *>(tmp);
   int64_t nreach = 2 * (int64_t)num_states;
   int64_t n0 = nreach > num_fsas + 1 ? nreach : num_fsas + 1;
-  PropsInit<<<CeilDiv(n0, 256), 256, 0, STREAM(stream)>>>(properties, num_fsas + 1, reach, nreach);
+  { PropsInit<<<CeilDiv(n0, 256), 256, 0, STREAM(stream)>>>(properties, num_fsas + 1, reach, nreach); NoteLaunch(); }
   if (num_arcs > 0)
-    PropsArcs<<<CeilDiv(num_arcs, 256), 256, 0, STREAM(stream)>>>(
+    { PropsArcs<<<CeilDiv(num_arcs, 256), 256, 0, STREAM(stream)>>>(
         row_splits1, row_ids1, row_splits2, row_ids2, reinterpret_cast<const Arc *>(arcs),
-        num_states, num_arcs, properties, reach);
+        num_states, num_arcs, properties, reach); NoteLaunch(); }
   if (num_states > 0)
-    PropsStates<<<CeilDiv(num_states, 256), 256, 0, STREAM(stream)>>>(row_ids1, num_states, reach,
-                                                                     properties);
+    { PropsStates<<<CeilDiv(num_states, 256), 256, 0, STREAM(stream)>>>(row_ids1, num_states, reach,
+                                                                     properties); NoteLaunch(); }
   if (num_fsas > 0)
-    PropsFinish<<<CeilDiv(num_fsas, 128), 128, 0, STREAM(stream)>>>(row_splits1, row_splits2,
-                                                                   num_fsas, properties);
+    { PropsFinish<<<CeilDiv(num_fsas, 128), 128, 0, STREAM(stream)>>>(row_splits1, row_splits2,
+                                                                   num_fsas, properties); NoteLaunch(); }
   K2B_CUDA_OK(cudaGetLastError());
   return kOk;
 }

@@ -165,10 +165,10 @@ int32_t LaunchPersistentViterbi(const Layout &L, const k2b200_intersect_args *a,
   int64_t lanes = (int64_t)L.max_states << lanes_log2;
   int32_t threads = (int32_t)std::min<int64_t>(1024, std::max<int64_t>(128, (lanes + 31) / 32 * 32));
   dim3 grid(2, a->num_fsas);
-  PersistentViterbi<<<grid, threads, p.bytes, stream>>>(
+  { PersistentViterbi<<<grid, threads, p.bytes, stream>>>(
       d_infos, reinterpret_cast<const Arc *>(a->a_arcs), a->a_row_splits2, a->a_in_splits,
       a->a_in_arcs, a->scores, a->cols, fwd, bwd, p.s_pad, p.a_pad, p.row_pad, p.stages,
-      lanes_log2);
+      lanes_log2); NoteLaunch(); }
   K2B_CUDA_OK(cudaGetLastError());
   return kOk;
 }
