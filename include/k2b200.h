@@ -75,6 +75,31 @@ size_t k2b200_exclusive_sum_tmp_bytes(int64_t n);
 int32_t k2b200_exclusive_sum(const int32_t *in, int32_t *out, int64_t n, void *tmp,
                              void *stream);
 
+/* The same exclusive sum for callers that cannot provide scratch memory.  It has
+ * no counterpart in the reference, whose ExclusiveSum always allocates its
+ * temporary storage from the tensor library's allocator.  It is meant for hosts
+ * that drive this library without such an allocator (a plain C/C++ service) or
+ * whose device memory is partitioned once at start-up, where allocating in the
+ * request path is not possible or would stall the device.
+ *
+ * The scratch (the per-tile sums) is a 64 KB array that lives inside the library
+ * on every GPU that loads it, for the lifetime of the process, so:
+ *   - n may be at most k2b200_exclusive_sum_static_max_len() (33 554 431);
+ *     a longer input is refused with K2B200_TOO_LARGE and an explanatory message,
+ *     and k2b200_exclusive_sum is the call to use instead;
+ *   - the first call on each device looks up the array's device address (with
+ *     that device current); make that first call during set-up, before any
+ *     stream capture is begun;
+ *   - all calls on a device share the array: two calls that may run at the same
+ *     time on that device (different streams or threads) race and must be
+ *     ordered by the caller.  Nothing has to be cleared between calls - each
+ *     call overwrites every entry it later reads.
+ * No device memory is allocated or freed; in, out and the result layout are
+ * those of k2b200_exclusive_sum (out[0..n], out[n] = total, in == out allowed). */
+int64_t k2b200_exclusive_sum_static_max_len(void);
+int32_t k2b200_exclusive_sum_static(const int32_t *in, int32_t *out, int64_t n,
+                                    void *stream);
+
 /* Incoming-arc index of an FsaVec: in_splits[num_states+1], in_arcs[num_arcs];
  * the arcs entering each state, in increasing arc index.
  * Replaces k2::GetDestStates + k2::GetIncomingArcs,

@@ -61,6 +61,8 @@ _sig("k2b200_profile_read_ms", ctypes.c_double, [c_i32, ctypes.POINTER(c_i64)])
 _sig("k2b200_row_splits_to_row_ids", c_i32, [c_vp, c_i32, c_vp, c_i32, c_vp])
 _sig("k2b200_exclusive_sum_tmp_bytes", c_sz, [c_i64])
 _sig("k2b200_exclusive_sum", c_i32, [c_vp, c_vp, c_i64, c_vp, c_vp])
+_sig("k2b200_exclusive_sum_static_max_len", c_i64, [])
+_sig("k2b200_exclusive_sum_static", c_i32, [c_vp, c_vp, c_i64, c_vp])
 _sig("k2b200_fsa_incoming_tmp_bytes", c_sz, [c_i32, c_i32])
 _sig("k2b200_fsa_incoming", c_i32,
      [c_vp, c_vp, c_vp, c_vp, c_i32, c_i32, c_i32, c_vp, c_vp, c_vp, c_vp])
@@ -92,7 +94,8 @@ _sig("k2b200_fsa_properties", c_i32,
 EXPORTED = [
     "k2b200_last_error", "k2b200_abi_version", "k2b200_kernel_launch_count",
     "k2b200_profile_enable", "k2b200_profile_read_ms", "k2b200_row_splits_to_row_ids",
-    "k2b200_exclusive_sum_tmp_bytes", "k2b200_exclusive_sum", "k2b200_fsa_incoming_tmp_bytes",
+    "k2b200_exclusive_sum_tmp_bytes", "k2b200_exclusive_sum",
+    "k2b200_exclusive_sum_static_max_len", "k2b200_exclusive_sum_static", "k2b200_fsa_incoming_tmp_bytes",
     "k2b200_fsa_incoming", "k2b200_intersect_dense_workspace_bytes",
     "k2b200_intersect_dense_prune", "k2b200_intersect_dense_emit", "k2b200_fsa_scores",
     "k2b200_fsa_tot_scores", "k2b200_fsa_arc_post", "k2b200_tot_scores_log_backward",

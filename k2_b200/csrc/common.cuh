@@ -79,6 +79,9 @@ static inline int CeilDiv(int64_t a, int64_t b) { return (int)((a + b - 1) / b);
 size_t ScanTmpInts(int64_t n);
 int32_t ExclusiveSum(const int32_t *in, int32_t *out, int64_t n, int32_t *tmp,
                      cudaStream_t stream);
+// Variant whose scratch is a fixed array inside the library (no caller memory).
+int64_t ExclusiveSumStaticMaxLen();
+int32_t ExclusiveSumStatic(const int32_t *in, int32_t *out, int64_t n, cudaStream_t stream);
 // Same for two interleaved counters (x, y) at once.
 int32_t ExclusiveSum2(const int2 *in, int2 *out, int64_t n, int2 *tmp,
                       cudaStream_t stream);

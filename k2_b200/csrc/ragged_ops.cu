@@ -215,6 +215,62 @@ int32_t ExclusiveSum2(const int2 *in, int2 *out, int64_t n, int2 *tmp, cudaStrea
 }
 
 // ----------------------------------------------------------------------------
+// Exclusive sum that needs no memory from the caller beyond input and output.
+//
+// Some users of this library cannot hand it a scratch buffer: a C or C++ host
+// that drives the kernels itself (no tensor library with a caching allocator
+// behind it), or a service whose device memory was carved up once at start-up and
+// must not grow - there a cudaMalloc in the request path is either unavailable
+// or an unwanted device-wide synchronisation.  For them the tile sums of the
+// scan live in the fixed array below, which every GPU that loads the library
+// keeps for the lifetime of the process (kStaticScanTiles * 4 bytes = 64 KB).
+//
+// kStaticScanTiles tiles of kScanTile elements bound the input length.
+// ----------------------------------------------------------------------------
+constexpr int kStaticScanTiles = 16384;
+static __device__ __align__(256) int32_t g_static_scan_tiles[kStaticScanTiles + 1];
+
+constexpr int kMaxDevices = 64;
+static std::mutex g_static_scan_mutex;
+static int32_t *g_static_scan_ptr[kMaxDevices] = {nullptr};
+
+int64_t ExclusiveSumStaticMaxLen() { return (int64_t)kStaticScanTiles * kScanTile - 1; }
+
+// Device address of the array on the current device.  `g_static_scan_tiles` named
+// in host code is only a handle for the runtime, not an address a kernel could
+// use, so it is translated once per device with cudaGetSymbolAddress.
+static int32_t StaticScanScratch(int32_t **ptr) {
+  int dev = -1;
+  K2B_CUDA_OK(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= kMaxDevices) {
+    SetError("device ordinal %d out of range", dev);
+    return kInvalidArgument;
+  }
+  std::lock_guard<std::mutex> lock(g_static_scan_mutex);
+  if (g_static_scan_ptr[dev] == nullptr) {
+    void *p = nullptr;
+    K2B_CUDA_OK(cudaGetSymbolAddress(&p, g_static_scan_tiles));
+    g_static_scan_ptr[dev] = reinterpret_cast<int32_t *>(p);
+  }
+  *ptr = g_static_scan_ptr[dev];
+  return kOk;
+}
+
+int32_t ExclusiveSumStatic(const int32_t *in, int32_t *out, int64_t n, cudaStream_t stream) {
+  if (n < 0 || n > ExclusiveSumStaticMaxLen()) {
+    SetError("k2b200_exclusive_sum_static: n = %lld is outside [0, %lld]; use "
+             "k2b200_exclusive_sum with a caller-provided scratch buffer for longer inputs",
+             (long long)n, (long long)ExclusiveSumStaticMaxLen());
+    return kTooLarge;
+  }
+  int32_t *scratch = nullptr;
+  K2B_FORWARD(StaticScanScratch(&scratch));
+  // every tile sum that is read is written first by ScanTileSums of this call,
+  // so nothing left over from an earlier call needs clearing
+  return ExclusiveSumImpl<int32_t>(in, out, n, scratch, stream);
+}
+
+// ----------------------------------------------------------------------------
 // row_splits -> row_ids by binary search per element
 // ----------------------------------------------------------------------------
 __global__ void RowIdsKernel(const int32_t *__restrict__ row_splits, int32_t num_rows,

@@ -335,6 +335,13 @@ int32_t k2b200_exclusive_sum(const int32_t *in, int32_t *out, int64_t n, void *t
   return ExclusiveSum(in, out, n, reinterpret_cast<int32_t *>(tmp), STREAM(stream));
 }
 
+int64_t k2b200_exclusive_sum_static_max_len(void) { return ExclusiveSumStaticMaxLen(); }
+int32_t k2b200_exclusive_sum_static(const int32_t *in, int32_t *out, int64_t n, void *stream) {
+  K2B_REQUIRE(n == 0 || (in != nullptr && out != nullptr), "NULL pointer");
+  K2B_REQUIRE(out != nullptr, "NULL output pointer");
+  return ExclusiveSumStatic(in, out, n, STREAM(stream));
+}
+
 size_t k2b200_fsa_incoming_tmp_bytes(int32_t num_states, int32_t num_arcs) {
   return IncomingTmpBytes(num_states, num_arcs);
 }
