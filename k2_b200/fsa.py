@@ -443,6 +443,9 @@ def create_fsa_vec(fsas: List[Fsa]) -> Fsa:
     arcs = RaggedArc(values, torch.from_numpy(h1).to(dev), torch.from_numpy(r2).to(dev),
                      h_row_splits1=h1, h_arc_splits=r2[h1].astype(np.int32))
     ans = Fsa(arcs)
+    if any(f.scores.requires_grad for f in fsas):
+        # keep the autograd link from the stacked scores to the inputs' scores
+        ans.scores = torch.cat([f.scores for f in fsas], dim=0)
     names = None
     for f in fsas:
         these = {n for n, _ in f.named_tensor_attr(include_scores=False) if n != 'labels'}

@@ -1,0 +1,118 @@
+"""Host-side logic without a GPU: graph construction, DenseFsaVec layout, text
+format, sharding, and the C-ABI library's exported symbols."""
+import ctypes
+import os
+import re
+
+import numpy as np
+import pytest
+import torch
+
+import k2_b200 as k2
+from k2_b200 import parallel
+from k2_b200 import synthetic as syn
+from oracle import oracle
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def test_library_exports_every_declared_symbol():
+    header = open(os.path.join(ROOT, "include", "k2b200.h")).read()
+    declared = sorted(set(re.findall(r"\b(k2b200_[a-z0-9_]+)\s*\(", header)))
+    assert len(declared) >= 25
+    lib = ctypes.CDLL(os.path.join(ROOT, "k2_b200", "libk2b200.so"))
+    for name in declared:
+        assert hasattr(lib, name), f"{name} declared in include/k2b200.h but not exported"
+    from k2_b200 import _lib
+    assert sorted(_lib.EXPORTED) == [d for d in declared if d in _lib.EXPORTED]
+    assert set(declared) == set(_lib.EXPORTED)
+    assert lib.k2b200_abi_version() == 1
+
+
+def test_no_cpu_path():
+    g = k2.ctc_graph([[1, 2]])
+    lp = torch.log_softmax(torch.randn(1, 4, 5), -1)
+    dense = k2.DenseFsaVec(lp, torch.tensor([[0, 0, 4]], dtype=torch.int32))
+    with pytest.raises(RuntimeError, match="CUDA"):
+        k2.intersect_dense(g, dense, 10.0)
+
+
+def test_ctc_graph_matches_oracle():
+    rng = np.random.default_rng(0)
+    for modified in (False, True):
+        for _ in range(30):
+            syms = [[int(x) for x in rng.integers(1, 5, size=int(rng.integers(0, 7)))]
+                    for _ in range(int(rng.integers(1, 6)))]
+            g = k2.ctc_graph(syms, modified=modified)
+            o = oracle.ctc_graphs(syms, modified)
+            assert np.array_equal(g.arcs.values().numpy(), o.arcs)
+            assert np.array_equal(g.arcs.row_splits(1).numpy(), o.row_splits1)
+            assert np.array_equal(g.arcs.row_splits(2).numpy(), o.row_splits2)
+            assert np.array_equal(g.aux_labels.numpy(), o.aux_labels)
+            assert g.properties == oracle.properties(o)[1]
+
+
+def test_dense_fsa_vec_layout():
+    # k2/python/tests/dense_fsa_vec_test.py:41-127
+    lp = torch.arange(2 * 4 * 3, dtype=torch.float32).reshape(2, 4, 3)
+    seg = torch.tensor([[1, 0, 4], [0, 1, 2]], dtype=torch.int32)
+    d = k2.DenseFsaVec(lp, seg)
+    assert d.scores.shape == (4 + 1 + 2 + 1, 4)
+    assert d.h_row_splits.tolist() == [0, 5, 8]
+    assert d.duration.tolist() == [4, 2]
+    assert torch.equal(d.scores[0:4, 1:], lp[1])
+    assert torch.equal(d.scores[5:7, 1:], lp[0, 1:3])
+    inf = float("inf")
+    assert d.scores[4].tolist() == [0, -inf, -inf, -inf]
+    assert d.scores[7].tolist() == [0, -inf, -inf, -inf]
+    assert torch.all(d.scores[[0, 1, 2, 3, 5, 6], 0] == -inf)
+    # allow_truncate
+    d2 = k2.DenseFsaVec(lp, torch.tensor([[0, 2, 4]], dtype=torch.int32), allow_truncate=2)
+    assert d2.duration.tolist() == [2]
+
+
+def test_from_str_and_properties():
+    f = k2.Fsa.from_str("0 1 1 0.5\n0 1 2 1.5\n1 2 -1 0.25\n2")
+    assert f.shape == (3, None) and f.num_arcs == 3
+    assert f.scores.tolist() == [0.5, 1.5, 0.25] and f.labels.tolist() == [1, 2, -1]
+    assert f.properties & k2.fsa.VALID and f.properties & k2.fsa.ARC_SORTED
+    t = k2.Fsa.from_str("0 1 1 10 0.5\n1 2 -1 -1 0.25\n2", num_aux_labels=1)
+    assert t.aux_labels.tolist() == [10, -1]
+    with pytest.raises(ValueError):
+        k2.Fsa.from_str("0 1 -1 0.5\n1 2 -1 0.25\n2")  # -1 on an arc not entering the final state
+    v = k2.create_fsa_vec([f, f])
+    assert v.shape == (2, None, None) and v.arcs.row_splits(1).tolist() == [0, 3, 6]
+    s = k2.arc_sort(k2.Fsa.from_str("0 1 2 0.5\n0 1 1 1.5\n1 2 -1 0.25\n2"))
+    assert s.labels.tolist() == [1, 2, -1]
+
+
+def test_synthetic_workloads_are_deterministic_and_valid():
+    w1, w2 = syn.ctc_small(), syn.ctc_small()
+    assert torch.equal(w1.log_probs, w2.log_probs) and w1.symbols == w2.symbols
+    assert w1.supervision_segments[:, 2].tolist() == sorted(
+        w1.supervision_segments[:, 2].tolist(), reverse=True)
+    g = syn.build_graphs(w1)
+    assert g.num_arcs == 1325 and g.arcs.num_states == 540
+    big = syn.ctc_large(scale=0.1)
+    d = big.supervision_segments[:, 2].tolist()
+    assert d == sorted(d, reverse=True)
+    rs2, arcs = syn.den_graph(0)
+    assert len(rs2) - 1 == 144 and 4500 < len(arcs) < 4700
+    den = syn.build_graphs(syn.lfmmi_den(scale=0.02))
+    assert den.properties & k2.fsa.ARC_SORTED_AND_DETERMINISTIC
+    hlg = syn.build_graphs(syn.hlg_decode(scale=0.02, num_states=500))
+    assert hlg.properties & k2.fsa.VALID and hlg.properties & k2.fsa.ACCESSIBLE
+
+
+def test_shard_utterances_balances_and_keeps_order():
+    durs = [1000, 990, 800, 750, 700, 650, 600, 600]
+    seen = []
+    for rank in range(4):
+        idx = parallel.shard_utterances(durs, 4, rank)
+        d = [durs[i] for i in idx]
+        assert d == sorted(d, reverse=True)
+        seen.extend(idx.tolist())
+    assert sorted(seen) == list(range(8))
+    seg = torch.tensor([[i, 0, d] for i, d in enumerate(durs)], dtype=torch.int32)
+    mine, idx = parallel.shard_segments(seg, 2, 1)
+    assert mine[:, 2].tolist() == [990, 750, 650, 600]

@@ -1,0 +1,84 @@
+"""Pins the C restatement (oracle/k2_oracle.c) against the reference's own CPU code
+(oracle/_ref/libk2ref.so) on seeded random inputs: everything must be identical,
+bit for bit - lattices, arc maps, float and double scores, best paths, graphs."""
+import numpy as np
+import pytest
+
+from oracle import oracle, ref
+from util import random_dense, random_fsa_vec, same_fsa
+
+pytestmark = pytest.mark.skipif(
+    not ref.available(), reason="oracle/_ref/libk2ref.so not built (needs the k2 checkout)")
+
+
+def test_intersect_and_scores_identical():
+    rng = np.random.default_rng(0)
+    for trial in range(120):
+        n = int(rng.integers(1, 6))
+        a = random_fsa_vec(rng, n, acyclic=bool(trial % 2))
+        scores, brs = random_dense(rng, n, 10, 5)
+        beam = float(rng.choice([0.5, 2.0, 10.0, 100.0]))
+        amap = np.sort(rng.integers(0, n, size=n)).astype(np.int32) if trial % 5 == 0 else None
+        r = ref.intersect_dense(a, scores, brs, beam, amap)
+        o = oracle.intersect_dense(a, scores, brs, beam, amap)
+        same_fsa(r, o, f"trial {trial}")
+        for log in (True, False):
+            for dbl in (True, False):
+                rf, of = ref.forward_scores(r, log, dbl), oracle.forward_scores(o, log, dbl)
+                rb, ob = ref.backward_scores(r, log, dbl), oracle.backward_scores(o, log, dbl)
+                assert np.array_equal(rf, of) and np.array_equal(rb, ob), (trial, log, dbl)
+                rt, rp = ref.tot_scores_and_arc_post(r, rf, rb, dbl)
+                ot, op = oracle.tot_scores_and_arc_post(o, of, ob, dbl)
+                assert np.array_equal(rt, ot) and np.array_equal(rp, op, equal_nan=True)
+        _, rea = ref.forward_scores(r, False, True, True)
+        _, oea = oracle.forward_scores(o, False, True, True)
+        assert np.array_equal(rea, oea)
+        rs, rbest = ref.shortest_path(r, rea)
+        os_, obest = oracle.shortest_path(o, oea)
+        assert np.array_equal(rs, os_) and np.array_equal(rbest, obest)
+        rp_, ro = ref.properties(r), oracle.properties(o)
+        assert np.array_equal(rp_[0], ro[0]) and rp_[1] == ro[1]
+
+
+def test_beam_reduction_identical():
+    # limits are set to 70% of what beam 50 keeps, and only where that is far above
+    # the best paths alone: the reference's retry loop (intersect_dense.cu:240-320)
+    # never ends when even a vanishing beam exceeds the limit
+    rng = np.random.default_rng(5)
+    done = 0
+    for trial in range(60):
+        n = int(rng.integers(2, 6))
+        a = random_fsa_vec(rng, n, max_states=20, max_arcs=80, allow_empty=False)
+        scores, brs = random_dense(rng, n, 12, 5, low_rows=False)
+        full = oracle.intersect_dense(a, scores, brs, 50.0)
+        path_states = int(np.diff(brs).sum() + n)
+        if full.num_states < 3 * path_states or full.num_arcs < 6 * path_states:
+            continue
+        kw = dict(max_states=int(0.7 * full.num_states)) if trial % 2 else dict(
+            max_arcs=int(0.7 * full.num_arcs) + 4 * path_states)
+        r = ref.intersect_dense(a, scores, brs, 50.0, None, **kw)
+        o = oracle.intersect_dense(a, scores, brs, 50.0, None, **kw)
+        same_fsa(r, o, f"trial {trial} {kw}")
+        done += 1
+    assert done >= 5
+
+
+def test_ctc_graphs_identical():
+    rng = np.random.default_rng(1)
+    for modified in (False, True):
+        for _ in range(40):
+            syms = [[int(x) for x in rng.integers(1, 5, size=int(rng.integers(0, 7)))]
+                    for _ in range(int(rng.integers(1, 6)))]
+            r, o = ref.ctc_graphs(syms, modified), oracle.ctc_graphs(syms, modified)
+            same_fsa(r, o)
+            assert np.array_equal(r.aux_labels, o.aux_labels)
+
+
+def test_reference_rejects_what_the_oracle_rejects():
+    rng = np.random.default_rng(3)
+    a = random_fsa_vec(rng, 2, allow_empty=False)
+    scores, brs = random_dense(rng, 2, 6, 5)
+    with pytest.raises(RuntimeError):
+        ref.intersect_dense(a, scores, brs, 10.0, np.array([1, 0], np.int32))
+    with pytest.raises(RuntimeError):
+        oracle.intersect_dense(a, scores, brs, 10.0, np.array([1, 0], np.int32))

@@ -74,5 +74,6 @@ def close(a, b, rtol=1e-6, atol=1e-6):
     a = np.asarray(a, np.float64)
     b = np.asarray(b, np.float64)
     both_inf = np.isinf(a) & np.isinf(b) & (np.sign(a) == np.sign(b))
-    ok = both_inf | (np.abs(a - b) <= atol + rtol * np.abs(b))
+    with np.errstate(invalid="ignore"):
+        ok = both_inf | (np.abs(a - b) <= atol + rtol * np.abs(b))
     return bool(np.all(ok))
