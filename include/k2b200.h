@@ -101,7 +101,9 @@ int32_t k2b200_exclusive_sum_static(const int32_t *in, int32_t *out, int64_t n,
                                     void *stream);
 
 /* Incoming-arc index of an FsaVec: in_splits[num_states+1], in_arcs[num_arcs];
- * the arcs entering each state, in increasing arc index.
+ * the arcs entering each state, in increasing arc index.  in_src and in_score
+ * (each [num_arcs], either may be NULL) receive the source state (idx01) and the
+ * score of those arcs in the same order; k2b200_fsa_scores reads them.
  * Replaces k2::GetDestStates + k2::GetIncomingArcs,
  * k2/csrc/fsa_utils.cu:650-677, :901-928 (called from
  * k2/csrc/intersect_dense.cu:139-142 and k2/python/k2/fsa.py:529-562). */
@@ -109,8 +111,8 @@ size_t k2b200_fsa_incoming_tmp_bytes(int32_t num_states, int32_t num_arcs);
 int32_t k2b200_fsa_incoming(const int32_t *row_splits1, const int32_t *row_ids1,
                             const int32_t *row_ids2, const void *arcs,
                             int32_t num_fsas, int32_t num_states, int32_t num_arcs,
-                            int32_t *in_splits, int32_t *in_arcs, void *tmp,
-                            void *stream);
+                            int32_t *in_splits, int32_t *in_arcs, int32_t *in_src,
+                            float *in_score, void *tmp, void *stream);
 
 /* ---------------------------------------------------------------------------
  * intersect_dense.
@@ -147,8 +149,13 @@ typedef struct {
   float output_beam;
   int32_t max_states, max_arcs;
   /* 0 = choose automatically, 1 = one launch per frame (any graph size),
-   * 2 = persistent frame-synchronous kernel (graphs that fit in shared memory) */
+   * 2 = persistent frame-synchronous kernel (graphs that fit in shared memory),
+   * 3 = persistent kernel with the arcs in registers (needs a_max_degree <= 4
+   *     and at most 1024 states per graph) */
   int32_t viterbi_mode;
+  /* largest number of arcs entering or leaving any state of a_fsas; 0 = unknown
+   * (then mode 3 is never chosen) */
+  int32_t a_max_degree;
 } k2b200_intersect_args;
 
 typedef struct {
@@ -191,14 +198,40 @@ int32_t k2b200_intersect_dense_emit(const k2b200_intersect_args *args, void *wor
  * (may be NULL) receives for every state the best entering arc (ties go to the
  * highest arc index; -1 when no arc enters), as
  * k2/csrc/ragged_ops_inl.h:627-657.
+ *
+ * When the view says the layering is strict (every arc goes from one layer to
+ * the next - true for the lattices of k2b200_intersect_dense_emit) and gives
+ * bounds on the layer sizes, a shared-memory staged kernel is used; otherwise a
+ * general one.  Both give the same values.
  * ------------------------------------------------------------------------- */
-int32_t k2b200_fsa_scores(const int32_t *row_splits1, const int32_t *row_splits2,
-                          const int32_t *row_ids2, const void *arcs,
-                          const int32_t *in_splits, const int32_t *in_arcs,
-                          const int32_t *level_offsets, const int32_t *level_splits,
-                          int32_t num_fsas, int32_t num_states, int32_t num_arcs,
-                          int32_t log_semiring, int32_t use_double, void *forward,
-                          void *backward, int32_t *entering_arcs, void *stream);
+typedef struct {
+  int32_t num_fsas, num_states, num_arcs;
+  const int32_t *row_splits1; /* [num_fsas+1] */
+  const int32_t *row_ids1;    /* [num_states], may be NULL where not needed */
+  const int32_t *row_splits2; /* [num_states+1] */
+  const int32_t *row_ids2;    /* [num_arcs] */
+  const void *arcs;           /* [num_arcs] Arc */
+  /* incoming-arc index from k2b200_fsa_incoming (forward direction only) */
+  const int32_t *in_splits, *in_arcs, *in_src;
+  const float *in_score;
+  /* layering: level_offsets[num_fsas+1] into level_splits[total_levels+1] */
+  const int32_t *level_offsets, *level_splits;
+  int32_t strict_layers;    /* 1: every arc goes from layer l to layer l+1 */
+  int32_t max_layers;       /* upper bound on layers per FSA, 0 = unknown */
+  int32_t max_layer_states; /* upper bound on states per layer, 0 = unknown */
+  int32_t max_layer_arcs;   /* upper bound on arcs between two layers */
+} k2b200_fsa_view;
+
+/* scratch (k2b200_fsa_scores_scratch_bytes(fsas) bytes; may be NULL) enables the
+ * fastest log-semiring kernel for strictly layered views: it keeps every score
+ * as mantissa * 2^exponent so that no exp/log sits on the layer-to-layer
+ * dependency chain (the arcs' exp() and the states' log() run in separate fully
+ * parallel kernels).  Without scratch a slower kernel gives the same values. */
+size_t k2b200_fsa_scores_scratch_bytes(const k2b200_fsa_view *fsas);
+int32_t k2b200_fsa_scores(const k2b200_fsa_view *fsas, int32_t log_semiring,
+                          int32_t use_double, void *forward, void *backward,
+                          int32_t *entering_arcs, void *scratch, size_t scratch_bytes,
+                          void *stream);
 
 /* tot_scores[i] = forward score of the last state of FSA i, -inf if empty.
  * Replaces k2::GetTotScores, k2/csrc/fsa_utils.cu:1809-1837. */

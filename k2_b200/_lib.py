@@ -34,7 +34,7 @@ class IntersectArgs(ctypes.Structure):
         ("scores", c_vp), ("rows", c_i32), ("cols", c_i32), ("num_seqs", c_i32),
         ("h_b_row_splits", c_vp), ("h_a_to_b_map", c_vp),
         ("output_beam", c_f32), ("max_states", c_i32), ("max_arcs", c_i32),
-        ("viterbi_mode", c_i32),
+        ("viterbi_mode", c_i32), ("a_max_degree", c_i32),
     ]
 
 
@@ -43,6 +43,18 @@ class LatticeOut(ctypes.Structure):
         ("row_splits1", c_vp), ("row_ids1", c_vp), ("row_splits2", c_vp), ("row_ids2", c_vp),
         ("arcs", c_vp), ("arc_map_a", c_vp), ("arc_map_b", c_vp),
         ("level_offsets", c_vp), ("level_splits", c_vp),
+    ]
+
+
+class FsaView(ctypes.Structure):
+    _fields_ = [
+        ("num_fsas", c_i32), ("num_states", c_i32), ("num_arcs", c_i32),
+        ("row_splits1", c_vp), ("row_ids1", c_vp), ("row_splits2", c_vp), ("row_ids2", c_vp),
+        ("arcs", c_vp),
+        ("in_splits", c_vp), ("in_arcs", c_vp), ("in_src", c_vp), ("in_score", c_vp),
+        ("level_offsets", c_vp), ("level_splits", c_vp),
+        ("strict_layers", c_i32), ("max_layers", c_i32), ("max_layer_states", c_i32),
+        ("max_layer_arcs", c_i32),
     ]
 
 
@@ -65,7 +77,7 @@ _sig("k2b200_exclusive_sum_static_max_len", c_i64, [])
 _sig("k2b200_exclusive_sum_static", c_i32, [c_vp, c_vp, c_i64, c_vp])
 _sig("k2b200_fsa_incoming_tmp_bytes", c_sz, [c_i32, c_i32])
 _sig("k2b200_fsa_incoming", c_i32,
-     [c_vp, c_vp, c_vp, c_vp, c_i32, c_i32, c_i32, c_vp, c_vp, c_vp, c_vp])
+     [c_vp, c_vp, c_vp, c_vp, c_i32, c_i32, c_i32, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp])
 _sig("k2b200_intersect_dense_workspace_bytes", c_i32,
      [ctypes.POINTER(IntersectArgs), ctypes.POINTER(c_sz), ctypes.POINTER(c_i64)])
 _sig("k2b200_intersect_dense_prune", c_i32,
@@ -73,9 +85,9 @@ _sig("k2b200_intersect_dense_prune", c_i32,
       ctypes.POINTER(c_i32), ctypes.POINTER(c_f32)])
 _sig("k2b200_intersect_dense_emit", c_i32,
      [ctypes.POINTER(IntersectArgs), c_vp, c_sz, c_vp, ctypes.POINTER(LatticeOut)])
+_sig("k2b200_fsa_scores_scratch_bytes", c_sz, [ctypes.POINTER(FsaView)])
 _sig("k2b200_fsa_scores", c_i32,
-     [c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_i32, c_i32, c_i32, c_i32, c_i32, c_vp,
-      c_vp, c_vp, c_vp])
+     [ctypes.POINTER(FsaView), c_i32, c_i32, c_vp, c_vp, c_vp, c_vp, c_sz, c_vp])
 _sig("k2b200_fsa_tot_scores", c_i32, [c_vp, c_i32, c_i32, c_vp, c_vp, c_vp])
 _sig("k2b200_fsa_arc_post", c_i32,
      [c_vp, c_vp, c_vp, c_vp, c_i32, c_i32, c_i32, c_vp, c_vp, c_vp, c_vp])
@@ -98,6 +110,7 @@ EXPORTED = [
     "k2b200_exclusive_sum_static_max_len", "k2b200_exclusive_sum_static", "k2b200_fsa_incoming_tmp_bytes",
     "k2b200_fsa_incoming", "k2b200_intersect_dense_workspace_bytes",
     "k2b200_intersect_dense_prune", "k2b200_intersect_dense_emit", "k2b200_fsa_scores",
+    "k2b200_fsa_scores_scratch_bytes",
     "k2b200_fsa_tot_scores", "k2b200_fsa_arc_post", "k2b200_tot_scores_log_backward",
     "k2b200_tot_scores_tropical_backward", "k2b200_index_add", "k2b200_index_select_i32",
     "k2b200_shortest_path_tmp_bytes", "k2b200_shortest_path",

@@ -58,7 +58,7 @@ def _intersect_dense_arcs(a: RaggedArc, b: DenseFsaVec, a_to_b_map: Optional[tor
         raise RuntimeError("a_fsas and b_fsas must be on the same device")
     scores = b.scores.detach()
     assert scores.is_contiguous() and scores.dtype == torch.float32
-    in_splits, in_arcs = a.incoming()
+    in_splits, in_arcs = a.incoming()[:2]
     h_rs1 = np.ascontiguousarray(a.h_row_splits1, dtype=np.int32)
     h_as = np.ascontiguousarray(a.h_arc_splits, dtype=np.int32)
     h_brs = b.h_row_splits
@@ -78,7 +78,8 @@ def _intersect_dense_arcs(a: RaggedArc, b: DenseFsaVec, a_to_b_map: Optional[tor
         cols=scores.shape[1], num_seqs=len(h_brs) - 1, h_b_row_splits=h_brs.ctypes.data,
         h_a_to_b_map=None if h_map is None else h_map.ctypes.data,
         output_beam=float(output_beam), max_states=int(min(max_states, 2**31 - 1)),
-        max_arcs=int(min(max_arcs, 2**31 - 1)), viterbi_mode=viterbi_mode)
+        max_arcs=int(min(max_arcs, 2**31 - 1)), viterbi_mode=viterbi_mode,
+        a_max_degree=a.max_degree())
     nbytes = ctypes.c_size_t()
     levels = ctypes.c_int64()
     _lib.check(_lib.lib.k2b200_intersect_dense_workspace_bytes(ctypes.byref(args),
@@ -113,6 +114,11 @@ def _intersect_dense_arcs(a: RaggedArc, b: DenseFsaVec, a_to_b_map: Optional[tor
     lattice = RaggedArc(values[:na], row_splits1, row_splits2, row_ids1[:ns], row_ids2[:na])
     arc_map_a, arc_map_b = arc_map_a[:na], arc_map_b[:na]
     lattice._levels = (level_offsets, level_splits)
+    # every lattice arc goes from frame t to t+1; a frame holds at most one copy of
+    # each graph state and arc
+    h1, ha = a.h_row_splits1, a.h_arc_splits
+    lattice._layer_bounds = (1, int(np.diff(h_brs).max()) + 1, int(np.diff(h1).max()),
+                             int(np.diff(ha).max()))
     lattice.output_beam_used = beam.value
     return lattice, arc_map_a, arc_map_b
 

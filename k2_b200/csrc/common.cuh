@@ -92,12 +92,14 @@ int32_t RowSplitsToRowIds(const int32_t *row_splits, int32_t num_rows,
 
 // Incoming-arc index of an FsaVec: for every state (idx01) the arcs (idx012) that
 // enter it, in increasing arc order.
-//   in_splits [num_states + 1], in_arcs [num_arcs]
+//   in_splits [num_states + 1], in_arcs [num_arcs]; optional in_src [num_arcs]
+//   (source state idx01) and in_score [num_arcs] in the same order
 // workspace: IncomingTmpBytes(num_states, num_arcs).
 size_t IncomingTmpBytes(int32_t num_states, int32_t num_arcs);
 int32_t BuildIncoming(const int32_t *row_splits1, const int32_t *row_ids1,
                       const int32_t *row_ids2, const Arc *arcs, int32_t num_fsas,
                       int32_t num_states, int32_t num_arcs, int32_t *in_splits,
-                      int32_t *in_arcs, void *tmp, cudaStream_t stream);
+                      int32_t *in_arcs, int32_t *in_src, float *in_score, void *tmp,
+                      cudaStream_t stream);
 
 }  // namespace k2b

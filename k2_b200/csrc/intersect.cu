@@ -412,7 +412,13 @@ static int32_t RunViterbi(const Layout &L, const k2b200_intersect_args *a, char 
         *bwd = reinterpret_cast<float *>(ws + L.off_bwd);
   if (L.max_states == 0) return kOk;
   int32_t mode = a->viterbi_mode;
-  if (mode == 0) mode = PersistentViterbiFits(L, a) ? 2 : 1;
+  if (mode == 0)
+    mode = RegisterViterbiFits(L, a) ? 3 : (PersistentViterbiFits(L, a) ? 2 : 1);
+  if (mode == 3) {
+    K2B_REQUIRE(RegisterViterbiFits(L, a),
+                "viterbi_mode=3 needs a_max_degree <= 4 and at most 1024 states per graph");
+    return LaunchRegisterViterbi(L, a, d_infos, fwd, bwd, stream);
+  }
   if (mode == 2) {
     K2B_REQUIRE(PersistentViterbiFits(L, a),
                 "viterbi_mode=2 requested but a graph does not fit in shared memory");

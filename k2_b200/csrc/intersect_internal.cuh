@@ -37,4 +37,9 @@ int32_t LaunchPersistentViterbi(const Layout &L, const k2b200_intersect_args *a,
                                 const FsaInfo *d_infos, float *fwd, float *bwd,
                                 cudaStream_t stream);
 
+bool RegisterViterbiFits(const Layout &L, const k2b200_intersect_args *a);
+int32_t LaunchRegisterViterbi(const Layout &L, const k2b200_intersect_args *a,
+                              const FsaInfo *d_infos, float *fwd, float *bwd,
+                              cudaStream_t stream);
+
 }  // namespace k2b

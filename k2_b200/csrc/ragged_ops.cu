@@ -323,34 +323,52 @@ __global__ void IncomingFill(const int32_t *__restrict__ row_splits1,
 
 constexpr int kSmallBucket = 64;
 
-// One thread per state: rank sort of buckets of at most kSmallBucket arcs.
+// One thread per state: rank sort of buckets of at most kSmallBucket arcs; larger
+// buckets are queued in `large` (count in large[num_states]) for the warp kernel.
+// in_src / in_score (optional) receive the source state (idx01) and the score of
+// every arc in incoming order, so that forward recursions read them contiguously.
 __global__ void IncomingSortSmall(const int32_t *__restrict__ in_splits, int32_t num_states,
                                   const int32_t *__restrict__ unsorted,
-                                  int32_t *__restrict__ in_arcs) {
+                                  const int32_t *__restrict__ row_ids2,
+                                  const Arc *__restrict__ arcs, int32_t *__restrict__ in_arcs,
+                                  int32_t *__restrict__ in_src, float *__restrict__ in_score,
+                                  int32_t *__restrict__ large) {
   int32_t s = blockIdx.x * blockDim.x + threadIdx.x;
   if (s >= num_states) return;
   int32_t b = in_splits[s], n = in_splits[s + 1] - b;
-  if (n > kSmallBucket) return;
+  if (n > kSmallBucket) {
+    large[atomicAdd(&large[num_states], 1)] = s;
+    return;
+  }
   for (int32_t i = 0; i < n; ++i) {
     int32_t x = unsorted[b + i], rank = 0;
     for (int32_t j = 0; j < n; ++j) rank += (unsorted[b + j] < x);
     in_arcs[b + rank] = x;
+    if (in_src) in_src[b + rank] = row_ids2[x];
+    if (in_score) in_score[b + rank] = arcs[x].score;
   }
 }
 
-// One warp per state for the (rare) large buckets.
+// One warp per queued state for the (rare) large buckets.
 __global__ void IncomingSortLarge(const int32_t *__restrict__ in_splits, int32_t num_states,
                                   const int32_t *__restrict__ unsorted,
-                                  int32_t *__restrict__ in_arcs) {
-  int32_t s = (int32_t)(((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5);
-  int lane = threadIdx.x & 31;
-  if (s >= num_states) return;
-  int32_t b = in_splits[s], n = in_splits[s + 1] - b;
-  if (n <= kSmallBucket) return;
-  for (int32_t i = lane; i < n; i += 32) {
-    int32_t x = unsorted[b + i], rank = 0;
-    for (int32_t j = 0; j < n; ++j) rank += (unsorted[b + j] < x);
-    in_arcs[b + rank] = x;
+                                  const int32_t *__restrict__ row_ids2,
+                                  const Arc *__restrict__ arcs, int32_t *__restrict__ in_arcs,
+                                  int32_t *__restrict__ in_src, float *__restrict__ in_score,
+                                  const int32_t *__restrict__ large) {
+  const int32_t nwarps = (gridDim.x * blockDim.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  const int32_t nlarge = large[num_states];
+  for (int32_t e = (blockIdx.x * blockDim.x + threadIdx.x) >> 5; e < nlarge; e += nwarps) {
+    const int32_t s = large[e];
+    const int32_t b = in_splits[s], n = in_splits[s + 1] - b;
+    for (int32_t i = lane; i < n; i += 32) {
+      int32_t x = unsorted[b + i], rank = 0;
+      for (int32_t j = 0; j < n; ++j) rank += (unsorted[b + j] < x);
+      in_arcs[b + rank] = x;
+      if (in_src) in_src[b + rank] = row_ids2[x];
+      if (in_score) in_score[b + rank] = arcs[x].score;
+    }
   }
 }
 
@@ -364,7 +382,8 @@ size_t IncomingTmpBytes(int32_t num_states, int32_t num_arcs) {
 int32_t BuildIncoming(const int32_t *row_splits1, const int32_t *row_ids1,
                       const int32_t *row_ids2, const Arc *arcs, int32_t num_fsas,
                       int32_t num_states, int32_t num_arcs, int32_t *in_splits,
-                      int32_t *in_arcs, void *tmp, cudaStream_t stream) {
+                      int32_t *in_arcs, int32_t *in_src, float *in_score, void *tmp,
+                      cudaStream_t stream) {
   (void)num_fsas;
   char *p = reinterpret_cast<char *>(tmp);
   int32_t *counts = reinterpret_cast<int32_t *>(p);
@@ -383,10 +402,14 @@ int32_t BuildIncoming(const int32_t *row_splits1, const int32_t *row_ids1,
     { IncomingFill<<<CeilDiv(num_arcs, 256), 256, 0, stream>>>(row_splits1, row_ids1, row_ids2,
                                                              arcs, num_arcs, in_splits, counts,
                                                              unsorted); NoteLaunch(); }
-    { IncomingSortSmall<<<CeilDiv(num_states, 256), 256, 0, stream>>>(in_splits, num_states,
-                                                                    unsorted, in_arcs); NoteLaunch(); }
-    { IncomingSortLarge<<<CeilDiv((int64_t)num_states * 32, 256), 256, 0, stream>>>(
-        in_splits, num_states, unsorted, in_arcs); NoteLaunch(); }
+    // the cursor array is free again: it becomes the queue of large buckets
+    K2B_CUDA_OK(cudaMemsetAsync(counts + num_states, 0, sizeof(int32_t), stream));
+    { IncomingSortSmall<<<CeilDiv(num_states, 256), 256, 0, stream>>>(
+        in_splits, num_states, unsorted, row_ids2, arcs, in_arcs, in_src, in_score, counts);
+      NoteLaunch(); }
+    { IncomingSortLarge<<<148, 256, 0, stream>>>(in_splits, num_states, unsorted, row_ids2, arcs,
+                                                in_arcs, in_src, in_score, counts);
+      NoteLaunch(); }
   }
   K2B_CUDA_OK(cudaGetLastError());
   return kOk;

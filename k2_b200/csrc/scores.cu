@@ -10,106 +10,19 @@
 // persistent kernel per (FSA, direction) instead of launching per state batch.
 #include <cmath>
 
-#include "../../include/k2b200.h"
-#include "common.cuh"
+#include "scores_internal.cuh"
 
 namespace k2b {
 
-template <typename Real> __device__ __forceinline__ Real Exp(Real x);
-template <> __device__ __forceinline__ float Exp<float>(float x) { return expf(x); }
-template <> __device__ __forceinline__ double Exp<double>(double x) { return exp(x); }
-template <typename Real> __device__ __forceinline__ Real Log(Real x);
-template <> __device__ __forceinline__ float Log<float>(float x) { return logf(x); }
-template <> __device__ __forceinline__ double Log<double>(double x) { return log(x); }
-
 // grid = (directions, fsas).  dir = blockIdx.x + dir_base: 0 forward, 1 backward.
-// Scores of one layer are complete before the next layer reads them: one
-// __syncthreads per layer.  forward/backward are read with ordinary (coherent)
-// loads because the same CTA wrote them a layer earlier.
 template <typename Real, bool kLog>
 __global__ void __launch_bounds__(256)
-LayeredScores(const int32_t *__restrict__ row_splits1, const int32_t *__restrict__ row_splits2,
-              const int32_t *__restrict__ row_ids2, const Arc *__restrict__ arcs,
-              const int32_t *__restrict__ in_splits, const int32_t *__restrict__ in_arcs,
-              const int32_t *__restrict__ level_offsets,
-              const int32_t *__restrict__ level_splits, Real *forward, Real *backward,
-              int32_t *__restrict__ entering_arcs, int32_t dir_base) {
-  const int32_t i = blockIdx.y, dir = blockIdx.x + dir_base;
-  const int32_t s_begin = row_splits1[i], s_end = row_splits1[i + 1];
-  if (s_end == s_begin) return;
-  const int32_t lv0 = level_offsets[i], lv1 = level_offsets[i + 1];
-  const Real kNegInf = -INFINITY;
-  if (dir == 0) {
-    for (int32_t lv = lv0; lv < lv1; ++lv) {
-      const int32_t b = level_splits[lv], e = level_splits[lv + 1];
-      for (int32_t s = b + threadIdx.x; s < e; s += blockDim.x) {
-        const int32_t k0 = in_splits[s], k1 = in_splits[s + 1];
-        Real val = kNegInf;
-        int32_t best = -1;
-        if (kLog) {
-          Real m = kNegInf;
-          for (int32_t k = k0; k < k1; ++k) {
-            int32_t a = in_arcs[k];
-            Real x = forward[row_ids2[a]] + (Real)arcs[a].score;
-            m = x > m ? x : m;
-          }
-          if (m != kNegInf) {
-            Real sum = 0;
-            for (int32_t k = k0; k < k1; ++k) {
-              int32_t a = in_arcs[k];
-              Real x = forward[row_ids2[a]] + (Real)arcs[a].score;
-              sum += Exp<Real>(x - m);
-            }
-            val = m + Log<Real>(sum);
-          }
-        } else {
-          for (int32_t k = k0; k < k1; ++k) {
-            int32_t a = in_arcs[k];
-            Real x = forward[row_ids2[a]] + (Real)arcs[a].score;
-            if (x >= val) {  // ties: the later arc wins (ragged_ops_inl.h:649-655)
-              val = x;
-              best = a;
-            }
-          }
-        }
-        if (s == s_begin && val == kNegInf) val = 0;  // start state
-        forward[s] = val;
-        if (entering_arcs) entering_arcs[s] = best;
-      }
-      __syncthreads();
-    }
-  } else {
-    for (int32_t lv = lv1 - 1; lv >= lv0; --lv) {
-      const int32_t b = level_splits[lv], e = level_splits[lv + 1];
-      for (int32_t s = b + threadIdx.x; s < e; s += blockDim.x) {
-        const int32_t k0 = row_splits2[s], k1 = row_splits2[s + 1];
-        Real val = kNegInf;
-        if (kLog) {
-          Real m = kNegInf;
-          for (int32_t k = k0; k < k1; ++k) {
-            Real x = backward[s_begin + arcs[k].dest] + (Real)arcs[k].score;
-            m = x > m ? x : m;
-          }
-          if (m != kNegInf) {
-            Real sum = 0;
-            for (int32_t k = k0; k < k1; ++k) {
-              Real x = backward[s_begin + arcs[k].dest] + (Real)arcs[k].score;
-              sum += Exp<Real>(x - m);
-            }
-            val = m + Log<Real>(sum);
-          }
-        } else {
-          for (int32_t k = k0; k < k1; ++k) {
-            Real x = backward[s_begin + arcs[k].dest] + (Real)arcs[k].score;
-            val = x > val ? x : val;
-          }
-        }
-        if (s == s_end - 1 && val == kNegInf) val = 0;  // final state
-        backward[s] = val;
-      }
-      __syncthreads();
-    }
-  }
+LayeredScores(k2b200_fsa_view v, Real *forward, Real *backward, int32_t *entering_arcs,
+              int32_t dir_base, int32_t fsa_base, const int32_t *run_if) {
+  // run_if (optional): only do the work when the word it points to is non-zero
+  if (run_if != nullptr && *run_if == 0) return;
+  LayeredScoresDevice<Real, kLog>(v, fsa_base + blockIdx.y, blockIdx.x + dir_base, forward,
+                                  backward, entering_arcs);
 }
 
 template <typename Real>
@@ -146,7 +59,7 @@ __global__ void LogBackward(const int32_t *__restrict__ row_ids1,
   int32_t a = blockIdx.x * blockDim.x + threadIdx.x;
   if (a >= num_arcs) return;
   int32_t fsa = row_ids1[row_ids2[a]];
-  grad[a] = (float)(Exp<Real>(post[a]) * tot_grad[fsa * stride]);
+  grad[a] = (float)(ExpReal<Real>(post[a]) * tot_grad[fsa * stride]);
 }
 
 template <typename Real>
@@ -285,30 +198,40 @@ using namespace k2b;
 #define STREAM(s) reinterpret_cast<cudaStream_t>(s)
 
 template <typename Real>
-static int32_t LaunchScores(const int32_t *rs1, const int32_t *rs2, const int32_t *rid2,
-                            const Arc *arcs, const int32_t *in_splits, const int32_t *in_arcs,
-                            const int32_t *lvl_off, const int32_t *lvl_splits, int32_t num_fsas,
-                            int32_t log_semiring, Real *fwd, Real *bwd, int32_t *entering,
-                            cudaStream_t stream) {
-  int32_t ndir = (fwd != nullptr) + (bwd != nullptr);
-  if (ndir == 0 || num_fsas == 0) return kOk;
-  int32_t dir_base = fwd ? 0 : 1;
-  PhaseTimer timer(kPhaseScores, stream);
-  for (int32_t first = 0; first < num_fsas; first += 65535) {
-    int32_t n = num_fsas - first < 65535 ? num_fsas - first : 65535;
+static int32_t LaunchGeneric(const k2b200_fsa_view *v, int32_t log_semiring, Real *fwd, Real *bwd,
+                             int32_t *entering, const int32_t *run_if, cudaStream_t stream) {
+  int32_t ndir = (fwd != nullptr) + (bwd != nullptr), dir_base = fwd ? 0 : 1;
+  for (int32_t first = 0; first < v->num_fsas; first += 65535) {
+    int32_t n = v->num_fsas - first < 65535 ? v->num_fsas - first : 65535;
     dim3 grid(ndir, n);
     if (log_semiring)
-      { LayeredScores<Real, true><<<grid, 256, 0, stream>>>(rs1 + first, rs2, rid2, arcs, in_splits,
-                                                         in_arcs, lvl_off + first, lvl_splits,
-                                                         fwd, bwd, nullptr, dir_base); NoteLaunch(); }
+      { LayeredScores<Real, true><<<grid, 256, 0, stream>>>(*v, fwd, bwd, nullptr, dir_base,
+                                                            first, run_if); NoteLaunch(); }
     else
-      { LayeredScores<Real, false><<<grid, 256, 0, stream>>>(rs1 + first, rs2, rid2, arcs,
-                                                          in_splits, in_arcs, lvl_off + first,
-                                                          lvl_splits, fwd, bwd, entering,
-                                                          dir_base); NoteLaunch(); }
+      { LayeredScores<Real, false><<<grid, 256, 0, stream>>>(*v, fwd, bwd, entering, dir_base,
+                                                             first, run_if); NoteLaunch(); }
   }
   K2B_CUDA_OK(cudaGetLastError());
   return kOk;
+}
+
+template <typename Real>
+static int32_t LaunchScores(const k2b200_fsa_view *v, int32_t log_semiring, Real *fwd, Real *bwd,
+                            int32_t *entering, void *scratch, size_t scratch_bytes,
+                            cudaStream_t stream) {
+  int32_t ndir = (fwd != nullptr) + (bwd != nullptr);
+  if (ndir == 0 || v->num_fsas == 0) return kOk;
+  PhaseTimer timer(kPhaseScores, stream);
+  bool launched = false;
+  if (log_semiring) {
+    K2B_FORWARD(LaunchProbScores<Real>(v, fwd, bwd, scratch, scratch_bytes, stream, &launched));
+    // if a CTA found the layer bounds violated, redo everything the general way
+    if (launched)
+      return LaunchGeneric<Real>(v, 1, fwd, bwd, nullptr, ProbStatusWord(v, scratch), stream);
+  }
+  K2B_FORWARD(LaunchStagedScores<Real>(v, log_semiring, fwd, bwd, entering, stream, &launched));
+  if (launched) return kOk;
+  return LaunchGeneric<Real>(v, log_semiring, fwd, bwd, entering, nullptr, stream);
 }
 
 extern "C" {
@@ -348,36 +271,36 @@ size_t k2b200_fsa_incoming_tmp_bytes(int32_t num_states, int32_t num_arcs) {
 int32_t k2b200_fsa_incoming(const int32_t *row_splits1, const int32_t *row_ids1,
                             const int32_t *row_ids2, const void *arcs, int32_t num_fsas,
                             int32_t num_states, int32_t num_arcs, int32_t *in_splits,
-                            int32_t *in_arcs, void *tmp, void *stream) {
+                            int32_t *in_arcs, int32_t *in_src, float *in_score, void *tmp,
+                            void *stream) {
   K2B_REQUIRE(num_fsas >= 0 && num_states >= 0 && num_arcs >= 0, "negative size");
   K2B_REQUIRE(in_splits && tmp, "NULL pointer");
   PhaseTimer timer(kPhaseIncoming, STREAM(stream));
   return BuildIncoming(row_splits1, row_ids1, row_ids2, reinterpret_cast<const Arc *>(arcs),
-                       num_fsas, num_states, num_arcs, in_splits, in_arcs, tmp, STREAM(stream));
+                       num_fsas, num_states, num_arcs, in_splits, in_arcs, in_src, in_score, tmp,
+                       STREAM(stream));
 }
 
-int32_t k2b200_fsa_scores(const int32_t *row_splits1, const int32_t *row_splits2,
-                          const int32_t *row_ids2, const void *arcs, const int32_t *in_splits,
-                          const int32_t *in_arcs, const int32_t *level_offsets,
-                          const int32_t *level_splits, int32_t num_fsas, int32_t num_states,
-                          int32_t num_arcs, int32_t log_semiring, int32_t use_double,
-                          void *forward, void *backward, int32_t *entering_arcs, void *stream) {
-  (void)num_states;
-  (void)num_arcs;
-  K2B_REQUIRE(row_splits1 && row_splits2 && level_offsets && level_splits, "NULL pointer");
-  K2B_REQUIRE(forward == nullptr || (in_splits && in_arcs) || num_arcs == 0,
-              "forward scores need the incoming-arc index");
-  const Arc *a = reinterpret_cast<const Arc *>(arcs);
+size_t k2b200_fsa_scores_scratch_bytes(const k2b200_fsa_view *v) {
+  return v ? ProbScratchBytes(v) : 0;
+}
+
+int32_t k2b200_fsa_scores(const k2b200_fsa_view *v, int32_t log_semiring, int32_t use_double,
+                          void *forward, void *backward, int32_t *entering_arcs, void *scratch,
+                          size_t scratch_bytes, void *stream) {
+  K2B_REQUIRE(v != nullptr, "NULL view");
+  K2B_REQUIRE(v->row_splits1 && v->row_splits2 && v->level_offsets && v->level_splits,
+              "NULL pointer in the FsaVec view");
+  K2B_REQUIRE(forward == nullptr || v->num_arcs == 0 ||
+                  (v->in_splits && v->in_arcs && v->row_ids2),
+              "forward scores need the incoming-arc index and row_ids2");
   if (use_double)
-    return LaunchScores<double>(row_splits1, row_splits2, row_ids2, a, in_splits, in_arcs,
-                                level_offsets, level_splits, num_fsas, log_semiring,
-                                reinterpret_cast<double *>(forward),
-                                reinterpret_cast<double *>(backward), entering_arcs,
-                                STREAM(stream));
-  return LaunchScores<float>(row_splits1, row_splits2, row_ids2, a, in_splits, in_arcs,
-                             level_offsets, level_splits, num_fsas, log_semiring,
-                             reinterpret_cast<float *>(forward),
-                             reinterpret_cast<float *>(backward), entering_arcs, STREAM(stream));
+    return LaunchScores<double>(v, log_semiring, reinterpret_cast<double *>(forward),
+                                reinterpret_cast<double *>(backward), entering_arcs, scratch,
+                                scratch_bytes, STREAM(stream));
+  return LaunchScores<float>(v, log_semiring, reinterpret_cast<float *>(forward),
+                             reinterpret_cast<float *>(backward), entering_arcs, scratch,
+                             scratch_bytes, STREAM(stream));
 }
 
 int32_t k2b200_fsa_tot_scores(const int32_t *row_splits1, int32_t num_fsas, int32_t use_double,

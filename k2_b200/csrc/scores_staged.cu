@@ -1,0 +1,560 @@
+// Forward/backward scores of a strictly layered FsaVec (every arc goes from one
+// layer to the next, as in the lattices intersect_dense emits), one persistent CTA
+// per (FSA, direction).
+//
+// The recursion is a chain of T dependent layers, so what matters is the latency
+// of one layer.  Nothing on that chain touches global memory:
+//   * the layer boundaries of the FSA and the arc offsets at those boundaries sit
+//     in shared memory from the start;
+//   * per layer, the per-state splits and the arcs' (other-end state, score) are
+//     contiguous in global memory (incoming order for forward - in_src/in_score -
+//     and leaving order for backward) and are copied into a shared-memory ring by
+//     cp.async several layers ahead;
+//   * the scores of the previous layer are kept in a shared ping-pong buffer.
+// Each layer costs one __syncthreads.  Same arithmetic as LayeredScores in
+// scores.cu (reference: k2/csrc/fsa_utils.cu:1124-1278, :1345-1454).
+#include <algorithm>
+
+#include "../../include/k2b200.h"
+#include "common.cuh"
+#include "cp_async.cuh"
+#include "scores_internal.cuh"
+
+namespace k2b {
+
+constexpr size_t kStagedSmemBudget = 200 * 1024;
+
+struct StagedPlan {
+  int32_t maxw, maxa, nl_cap, stages, stage_ints, lanes_log2, threads;
+  size_t bytes;
+  bool ok;
+};
+
+static StagedPlan PlanStaged(const k2b200_fsa_view *v, size_t real_bytes, bool tropical) {
+  StagedPlan p = {};
+  p.ok = false;
+  if (!v->strict_layers || v->max_layer_states <= 0 || v->max_layer_arcs < 0 ||
+      v->max_layers <= 0)
+    return p;
+  p.maxw = (v->max_layer_states + 3) & ~3;
+  p.maxa = (std::max(v->max_layer_arcs, 1) + 3) & ~3;
+  p.nl_cap = v->max_layers;
+  // one ring stage, in 4-byte units: splits, then either (src, score[, arc id]) or
+  // 16-byte arcs; both directions share the stride
+  int32_t splits_ints = (p.maxw + 1 + 3) & ~3;
+  int32_t fwd_ints = p.maxa * (tropical ? 3 : 2);
+  int32_t bwd_ints = p.maxa * 4;
+  p.stage_ints = splits_ints + std::max(fwd_ints, bwd_ints);
+  size_t fixed = sizeof(int32_t) * 2 * (size_t)((p.nl_cap + 1 + 3) & ~3) +
+                 real_bytes * 2 * (size_t)p.maxw;
+  size_t stage_bytes = sizeof(int32_t) * (size_t)p.stage_ints;
+  if (fixed + 2 * stage_bytes > kStagedSmemBudget) return p;
+  p.stages = (int32_t)std::min<size_t>(8, (kStagedSmemBudget - fixed) / stage_bytes);
+  p.bytes = fixed + stage_bytes * p.stages;
+  int32_t mean_deg = v->num_states > 0 ? (v->num_arcs + v->num_states - 1) / v->num_states : 1;
+  p.lanes_log2 = 0;
+  while ((2 << p.lanes_log2) <= mean_deg / 2 && p.lanes_log2 < 5) ++p.lanes_log2;
+  p.threads = ((int64_t)p.maxw << p.lanes_log2) > 64 ? 128 : 64;
+  if (p.lanes_log2 >= 3) p.threads = 256;
+  p.ok = true;
+  return p;
+}
+
+template <typename Real, bool kLog>
+__global__ void __launch_bounds__(256)
+LayeredScoresStaged(k2b200_fsa_view v, Real *forward, Real *backward,
+                    int32_t *__restrict__ entering_arcs, int32_t dir_base, int32_t fsa_base,
+                    StagedPlan p) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  const int32_t i = fsa_base + blockIdx.y, dir = blockIdx.x + dir_base;
+  const int32_t s_begin = v.row_splits1[i], s_end = v.row_splits1[i + 1];
+  if (s_end == s_begin) return;
+  const int32_t lv0 = v.level_offsets[i], nl = v.level_offsets[i + 1] - lv0;
+  const int tid = threadIdx.x, nt = blockDim.x;
+  const Arc *arcs = reinterpret_cast<const Arc *>(v.arcs);
+  Real *out = dir == 0 ? forward : backward;
+  const Real kNegInf = -INFINITY;
+
+  const int32_t lvl_ints = (p.nl_cap + 1 + 3) & ~3;
+  int32_t *lvl = reinterpret_cast<int32_t *>(smem_raw);  // first state of each layer
+  int32_t *alvl = lvl + lvl_ints;                        // first arc of each layer
+  Real *score_buf = reinterpret_cast<Real *>(alvl + lvl_ints);  // [2][maxw]
+  int32_t *ring = reinterpret_cast<int32_t *>(score_buf + 2 * p.maxw);
+  const int32_t splits_ints = (p.maxw + 1 + 3) & ~3;
+  const int32_t *gsplits = dir == 0 ? v.in_splits : v.row_splits2;
+
+  // Layer boundaries; a layer wider than the plan allows (the caller's bounds were
+  // wrong) makes this CTA take the plain global-memory route below.
+  __shared__ int32_t too_wide;
+  if (tid == 0) too_wide = (nl > p.nl_cap);
+  __syncthreads();
+  if (!too_wide) {
+    for (int32_t k = tid; k <= nl; k += nt) {
+      int32_t s = v.level_splits[lv0 + k];
+      lvl[k] = s;
+      alvl[k] = gsplits[s];
+    }
+  }
+  __syncthreads();
+  if (!too_wide) {
+    int32_t bad = 0;
+    for (int32_t k = tid; k < nl; k += nt)
+      bad |= (lvl[k + 1] - lvl[k] > p.maxw) | (alvl[k + 1] - alvl[k] > p.maxa);
+    if (bad) too_wide = 1;
+  }
+  __syncthreads();
+  if (too_wide) {
+    LayeredScoresDevice<Real, kLog>(v, i, dir, forward, backward, entering_arcs);
+    return;
+  }
+
+  const int32_t stages = p.stages;
+  auto layer_of = [&](int32_t step) { return dir == 0 ? step : nl - 1 - step; };
+  auto issue = [&](int32_t step) {
+    if (step < nl) {
+      const int32_t li = layer_of(step);
+      const int32_t b = lvl[li], w = lvl[li + 1] - b, ab = alvl[li], na = alvl[li + 1] - ab;
+      int32_t *st = ring + (size_t)(step % stages) * p.stage_ints;
+      for (int32_t k = tid; k <= w; k += nt) CpAsync4(st + k, gsplits + b + k);
+      int32_t *body = st + splits_ints;
+      if (dir == 0) {
+        for (int32_t k = tid; k < na; k += nt) {
+          CpAsync4(body + k, v.in_src + ab + k);
+          CpAsync4(body + p.maxa + k, v.in_score + ab + k);
+          if (!kLog) CpAsync4(body + 2 * p.maxa + k, v.in_arcs + ab + k);
+        }
+      } else {
+        for (int32_t k = tid; k < na; k += nt) CpAsync16(body + 4 * k, arcs + ab + k);
+      }
+    }
+    CpAsyncCommit();
+  };
+  for (int32_t step = 0; step < stages - 1; ++step) issue(step);
+
+  const int32_t lg = p.lanes_log2, G = 1 << lg, g = tid & (G - 1), per_pass = nt >> lg;
+  for (int32_t step = 0; step < nl; ++step) {
+    CpAsyncWaitDyn(stages - 2);
+    __syncthreads();
+    issue(step + stages - 1);
+    const int32_t li = layer_of(step);
+    const int32_t b = lvl[li], w = lvl[li + 1] - b, ab = alvl[li];
+    // first state of the layer the arcs come from (forward) or lead to (backward)
+    const int32_t other_base = step == 0 ? 0 : lvl[dir == 0 ? li - 1 : li + 1];
+    const int32_t *st = ring + (size_t)(step % stages) * p.stage_ints;
+    const int32_t *body = st + splits_ints;
+    const Real *prev = score_buf + ((step + 1) & 1) * p.maxw;
+    Real *cur = score_buf + (step & 1) * p.maxw;
+    for (int32_t j0 = 0; j0 < w; j0 += per_pass) {
+      const int32_t j = j0 + (tid >> lg);
+      Real val = kNegInf;
+      int32_t best = -1;
+      int32_t k0 = 0, k1 = 0;
+      if (j < w) {
+        k0 = st[j] - ab;
+        k1 = st[j + 1] - ab;
+      }
+      auto term = [&](int32_t k) -> Real {
+        if (dir == 0) {
+          return prev[body[k] - other_base] + (Real)__int_as_float(body[p.maxa + k]);
+        } else {
+          return prev[s_begin + body[4 * k + 1] - other_base] +
+                 (Real)__int_as_float(body[4 * k + 3]);
+        }
+      };
+      if (kLog) {
+        Real m = kNegInf;
+        for (int32_t k = k0 + g; k < k1; k += G) {
+          Real x = term(k);
+          m = x > m ? x : m;
+        }
+        for (int32_t d = G >> 1; d > 0; d >>= 1) {
+          Real o = __shfl_xor_sync(0xffffffffu, m, d);
+          m = o > m ? o : m;
+        }
+        Real sum = 0;
+        if (m != kNegInf)
+          for (int32_t k = k0 + g; k < k1; k += G) sum += ExpReal<Real>(term(k) - m);
+        for (int32_t d = G >> 1; d > 0; d >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, d);
+        if (m != kNegInf) val = m + LogReal<Real>(sum);
+      } else {
+        for (int32_t k = k0 + g; k < k1; k += G) {
+          Real x = term(k);
+          if (dir == 0) {
+            int32_t a = body[2 * p.maxa + k];
+            if (x > val || (x == val && a > best)) {
+              val = x;
+              best = a;
+            }
+          } else {
+            val = x > val ? x : val;
+          }
+        }
+        for (int32_t d = G >> 1; d > 0; d >>= 1) {
+          Real o = __shfl_xor_sync(0xffffffffu, val, d);
+          int32_t ob = __shfl_xor_sync(0xffffffffu, best, d);
+          if (o > val || (o == val && ob > best)) {
+            val = o;
+            best = ob;
+          }
+        }
+      }
+      if (j < w && g == 0) {
+        const int32_t s = b + j;
+        if (val == kNegInf && s == (dir == 0 ? s_begin : s_end - 1)) val = 0;
+        cur[j] = val;
+        out[s] = val;
+        if (!kLog && dir == 0 && entering_arcs) entering_arcs[s] = best;
+      }
+    }
+  }
+  CpAsyncWait<0>();
+}
+
+template <typename Real>
+int32_t LaunchStagedScores(const k2b200_fsa_view *v, int32_t log_semiring, Real *fwd, Real *bwd,
+                           int32_t *entering, cudaStream_t stream, bool *launched) {
+  *launched = false;
+  if (fwd != nullptr && (v->in_src == nullptr || v->in_score == nullptr)) return kOk;
+  StagedPlan p = PlanStaged(v, sizeof(Real), !log_semiring);
+  if (!p.ok) return kOk;
+  int32_t ndir = (fwd != nullptr) + (bwd != nullptr);
+  int32_t dir_base = fwd ? 0 : 1;
+  auto kernel = log_semiring ? LayeredScoresStaged<Real, true> : LayeredScoresStaged<Real, false>;
+  K2B_CUDA_OK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                   (int)p.bytes));
+  for (int32_t first = 0; first < v->num_fsas; first += 65535) {
+    int32_t n = std::min(v->num_fsas - first, 65535);
+    dim3 grid(ndir, n);
+    { kernel<<<grid, p.threads, p.bytes, stream>>>(*v, fwd, bwd, entering, dir_base, first, p);
+      NoteLaunch(); }
+  }
+  K2B_CUDA_OK(cudaGetLastError());
+  *launched = true;
+  return kOk;
+}
+
+// ---------------------------------------------------------------------------
+// Log-semiring scores without transcendental functions on the dependency chain.
+//
+// A log-sum-exp recursion spends most of a layer's latency in one exp per arc and
+// one log per state (hundreds of cycles each in double precision).  Here every
+// score is carried as a number with a separate integer exponent,
+//     value = m * 2^e   (m a double in [1,2), or m == 0),
+// so a layer is: multiply by the arc weight (also stored as f * 2^k with f in
+// [1,2)), bring the terms of a state to their largest exponent with exact powers
+// of two, add, renormalise.  All of that is a handful of multiply/add and integer
+// instructions; the exponent is a 32-bit integer, so nothing under- or overflows
+// however far apart the scores of a layer are.  exp() of the arc scores and log()
+// of the state values are taken off the chain, in fully parallel kernels before
+// and after.  Rounding differs from the reference's sequential LogAdd by ~1e-15
+// relative per operation.
+// ---------------------------------------------------------------------------
+struct __align__(16) ProbArc {
+  double f;       // mantissa of exp(score) in [1,2), 0 when score == -inf
+  int32_t other;  // idx01 of the arc's source (forward) or destination (backward) state
+  int32_t k;      // binary exponent of exp(score)
+};
+static_assert(sizeof(ProbArc) == 16, "ProbArc must be 16 bytes");
+
+constexpr int32_t kZeroExp = -(1 << 30);
+
+__device__ __forceinline__ void ExpToMantExp(float score, double *f, int32_t *k) {
+  if (score == -INFINITY) {
+    *f = 0.0;
+    *k = kZeroExp;
+    return;
+  }
+  // exp(x) = 2^(x / ln 2): split x / ln 2 into integer and fraction in double
+  double y = (double)score * 1.4426950408889634074;  // log2(e)
+  double fl = floor(y);
+  double frac = y - fl;                 // [0,1)
+  *f = exp2(frac);                      // [1,2)
+  double kk = fmax(fmin(fl, 268435456.0), -268435456.0);
+  *k = (int32_t)kk;
+}
+
+// 2^d for d <= 0 (0 when the result would be subnormal).
+__device__ __forceinline__ double Pow2NonPos(int32_t d) {
+  return d < -1000 ? 0.0 : __longlong_as_double((long long)(1023 + d) << 52);
+}
+
+// Normalise s >= 0 (a sum of a few numbers in [1,4) scaled by powers of two <= 1)
+// to m in [1,2) and add its exponent to *e.
+__device__ __forceinline__ double Renorm(double s, int32_t *e) {
+  if (s == 0.0) {
+    *e = kZeroExp;
+    return 0.0;
+  }
+  long long bits = __double_as_longlong(s);
+  int32_t ex = (int32_t)((bits >> 52) & 0x7ff) - 1023;
+  *e += ex;
+  return __longlong_as_double((bits & 0x800fffffffffffffLL) | (1023LL << 52));
+}
+
+// fwd_arcs[k] (incoming order) and bwd_arcs[a] (leaving order) from the arc scores.
+__global__ void PrepareProbArcs(k2b200_fsa_view v, ProbArc *__restrict__ fwd_arcs,
+                                ProbArc *__restrict__ bwd_arcs) {
+  int32_t k = blockIdx.x * blockDim.x + threadIdx.x;
+  if (k >= v.num_arcs) return;
+  const Arc *arcs = reinterpret_cast<const Arc *>(v.arcs);
+  if (bwd_arcs) {
+    Arc arc = arcs[k];
+    ProbArc p;
+    ExpToMantExp(arc.score, &p.f, &p.k);
+    p.other = v.row_splits1[v.row_ids1[v.row_ids2[k]]] + arc.dest;
+    bwd_arcs[k] = p;
+  }
+  if (fwd_arcs) {
+    ProbArc p;
+    ExpToMantExp(v.in_score[k], &p.f, &p.k);
+    p.other = v.in_src[k];
+    fwd_arcs[k] = p;
+  }
+}
+
+// out[s] = log(m[s]) + e[s] * ln 2
+template <typename Real>
+__global__ void FinishLogScores(const double *__restrict__ m, const int32_t *__restrict__ e,
+                                int32_t n, Real *__restrict__ out) {
+  int32_t s = blockIdx.x * blockDim.x + threadIdx.x;
+  if (s >= n) return;
+  double mm = m[s];
+  out[s] = mm == 0.0 ? (Real)-INFINITY
+                     : (Real)(log(mm) + (double)e[s] * 0.69314718055994530942);
+}
+
+struct ProbPlan {
+  int32_t maxw, maxa, nl_cap, stages, stage_bytes, lanes_log2, threads;
+  size_t bytes;
+  bool ok;
+};
+
+static ProbPlan PlanProb(const k2b200_fsa_view *v) {
+  ProbPlan p = {};
+  if (!v->strict_layers || v->max_layer_states <= 0 || v->max_layer_arcs < 0 ||
+      v->max_layers <= 0)
+    return p;
+  p.maxw = (v->max_layer_states + 3) & ~3;
+  p.maxa = std::max(v->max_layer_arcs, 1);
+  p.nl_cap = v->max_layers;
+  int32_t splits_bytes = (((p.maxw + 1) * 4) + 15) & ~15;
+  p.stage_bytes = splits_bytes + p.maxa * 16;
+  size_t fixed = 8 * (size_t)((p.nl_cap + 1 + 3) & ~3)   // layer / arc boundaries
+                 + 2 * (size_t)p.maxw * 12 + 16;          // mantissa + exponent ping-pong
+  if (fixed + 2 * (size_t)p.stage_bytes > kStagedSmemBudget) return p;
+  p.stages = (int32_t)std::min<size_t>(8, (kStagedSmemBudget - fixed) / p.stage_bytes);
+  p.bytes = fixed + (size_t)p.stage_bytes * p.stages;
+  int32_t mean_deg = v->num_states > 0 ? (v->num_arcs + v->num_states - 1) / v->num_states : 1;
+  p.lanes_log2 = 0;
+  while ((2 << p.lanes_log2) <= mean_deg / 2 && p.lanes_log2 < 5) ++p.lanes_log2;
+  p.threads = p.lanes_log2 >= 3 ? 256 : 128;
+  p.ok = true;
+  return p;
+}
+
+// grid = (directions, fsas).  m_out / e_out: [2][num_states] (forward then backward).
+__global__ void __launch_bounds__(256)
+ProbScoresStaged(k2b200_fsa_view v, const ProbArc *__restrict__ fwd_arcs,
+                 const ProbArc *__restrict__ bwd_arcs, double *__restrict__ m_out,
+                 int32_t *__restrict__ e_out, int32_t dir_base, int32_t fsa_base, ProbPlan p,
+                 int32_t *__restrict__ status) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  const int32_t i = fsa_base + blockIdx.y, dir = blockIdx.x + dir_base;
+  const int32_t s_begin = v.row_splits1[i], s_end = v.row_splits1[i + 1];
+  if (s_end == s_begin) return;
+  const int32_t lv0 = v.level_offsets[i], nl = v.level_offsets[i + 1] - lv0;
+  const int tid = threadIdx.x, nt = blockDim.x;
+  double *mo = m_out + (size_t)dir * v.num_states;
+  int32_t *eo = e_out + (size_t)dir * v.num_states;
+
+  const int32_t lvl_ints = (p.nl_cap + 1 + 3) & ~3;
+  int32_t *lvl = reinterpret_cast<int32_t *>(smem_raw);
+  int32_t *alvl = lvl + lvl_ints;
+  double *mant = reinterpret_cast<double *>(alvl + lvl_ints);      // [2][maxw]
+  int32_t *expo = reinterpret_cast<int32_t *>(mant + 2 * p.maxw);  // [2][maxw]
+  unsigned char *ring = reinterpret_cast<unsigned char *>(
+      (reinterpret_cast<uintptr_t>(expo + 2 * p.maxw) + 15) & ~(uintptr_t)15);
+  const int32_t splits_bytes = (((p.maxw + 1) * 4) + 15) & ~15;
+  const int32_t *gsplits = dir == 0 ? v.in_splits : v.row_splits2;
+  const ProbArc *garcs = dir == 0 ? fwd_arcs : bwd_arcs;
+
+  __shared__ int32_t bad_shared;
+  if (tid == 0) bad_shared = (nl > p.nl_cap);
+  __syncthreads();
+  if (!bad_shared)
+    for (int32_t k = tid; k <= nl; k += nt) {
+      int32_t s = v.level_splits[lv0 + k];
+      lvl[k] = s;
+      alvl[k] = gsplits[s];
+    }
+  __syncthreads();
+  if (!bad_shared) {
+    int32_t bad = 0;
+    for (int32_t k = tid; k < nl; k += nt)
+      bad |= (lvl[k + 1] - lvl[k] > p.maxw) | (alvl[k + 1] - alvl[k] > p.maxa);
+    if (bad) bad_shared = 1;
+  }
+  __syncthreads();
+  if (bad_shared) {  // the caller's bounds do not hold: report, the host falls back
+    if (tid == 0) atomicExch(status, 1);
+    return;
+  }
+
+  const int32_t stages = p.stages;
+  auto layer_of = [&](int32_t step) { return dir == 0 ? step : nl - 1 - step; };
+  auto issue = [&](int32_t step, int32_t slot) {
+    if (step < nl) {
+      const int32_t li = layer_of(step);
+      const int32_t b = lvl[li], w = lvl[li + 1] - b, ab = alvl[li], na = alvl[li + 1] - ab;
+      unsigned char *st = ring + (size_t)slot * p.stage_bytes;
+      int32_t *sp = reinterpret_cast<int32_t *>(st);
+      for (int32_t k = tid; k <= w; k += nt) CpAsync4(sp + k, gsplits + b + k);
+      ProbArc *body = reinterpret_cast<ProbArc *>(st + splits_bytes);
+      for (int32_t k = tid; k < na; k += nt) CpAsync16(body + k, garcs + ab + k);
+    }
+    CpAsyncCommit();
+  };
+  int32_t issue_slot = 0;
+  for (int32_t step = 0; step < stages - 1; ++step) {
+    issue(step, issue_slot);
+    issue_slot = issue_slot + 1 == stages ? 0 : issue_slot + 1;
+  }
+
+  const int32_t lg = p.lanes_log2, G = 1 << lg, g = tid & (G - 1), per_pass = nt >> lg;
+  int32_t slot = 0;
+  for (int32_t step = 0; step < nl; ++step) {
+    CpAsyncWaitDyn(stages - 2);
+    __syncthreads();
+    issue(step + stages - 1, issue_slot);
+    issue_slot = issue_slot + 1 == stages ? 0 : issue_slot + 1;
+    const int32_t li = layer_of(step);
+    const int32_t b = lvl[li], w = lvl[li + 1] - b, ab = alvl[li];
+    const int32_t other_base = step == 0 ? 0 : lvl[dir == 0 ? li - 1 : li + 1];
+    const unsigned char *st = ring + (size_t)slot * p.stage_bytes;
+    slot = slot + 1 == stages ? 0 : slot + 1;
+    const int32_t *sp = reinterpret_cast<const int32_t *>(st);
+    const ProbArc *body = reinterpret_cast<const ProbArc *>(st + splits_bytes);
+    const double *pm = mant + ((step + 1) & 1) * p.maxw;
+    const int32_t *pe = expo + ((step + 1) & 1) * p.maxw;
+    double *cm = mant + (step & 1) * p.maxw;
+    int32_t *ce = expo + (step & 1) * p.maxw;
+    for (int32_t j0 = 0; j0 < w; j0 += per_pass) {
+      const int32_t j = j0 + (tid >> lg);
+      int32_t k0 = 0, k1 = 0;
+      if (j < w) {
+        k0 = sp[j] - ab;
+        k1 = sp[j + 1] - ab;
+      }
+      // terms t_k = m_prev * f_k with exponent e_prev + k_k; E = largest exponent
+      int32_t E = kZeroExp;
+      for (int32_t k = k0 + g; k < k1; k += G) {
+        const ProbArc a = body[k];
+        const int32_t o = a.other - other_base;
+        const int32_t te = (pm[o] == 0.0 || a.f == 0.0) ? kZeroExp : pe[o] + a.k;
+        E = te > E ? te : E;
+      }
+      for (int32_t d = G >> 1; d > 0; d >>= 1) {
+        int32_t o = __shfl_xor_sync(0xffffffffu, E, d);
+        E = o > E ? o : E;
+      }
+      double sum = 0.0;
+      if (E != kZeroExp)
+        for (int32_t k = k0 + g; k < k1; k += G) {
+          const ProbArc a = body[k];
+          const int32_t o = a.other - other_base;
+          const double t = pm[o] * a.f;
+          if (t != 0.0) sum += t * Pow2NonPos(pe[o] + a.k - E);
+        }
+      for (int32_t d = G >> 1; d > 0; d >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, d);
+      if (j < w && g == 0) {
+        const int32_t s = b + j;
+        int32_t e = E;
+        double m = Renorm(sum, &e);
+        if (m == 0.0 && s == (dir == 0 ? s_begin : s_end - 1)) {  // start / final state: 1
+          m = 1.0;
+          e = 0;
+        }
+        cm[j] = m;
+        ce[j] = e;
+        mo[s] = m;
+        eo[s] = e;
+      }
+    }
+  }
+  CpAsyncWait<0>();
+}
+
+size_t ProbScratchBytes(const k2b200_fsa_view *v) {
+  // ProbArc arrays for both directions, (mantissa, exponent) per state and
+  // direction, one status word
+  return AlignUp(2 * sizeof(ProbArc) * (size_t)std::max(v->num_arcs, 1)) +
+         AlignUp(2 * sizeof(double) * (size_t)std::max(v->num_states, 1)) +
+         AlignUp(2 * sizeof(int32_t) * (size_t)std::max(v->num_states, 1)) + 256;
+}
+
+int32_t *ProbStatusWord(const k2b200_fsa_view *v, void *scratch) {
+  char *q = reinterpret_cast<char *>(scratch);
+  q += AlignUp(2 * sizeof(ProbArc) * (size_t)std::max(v->num_arcs, 1));
+  q += AlignUp(2 * sizeof(double) * (size_t)std::max(v->num_states, 1));
+  q += AlignUp(2 * sizeof(int32_t) * (size_t)std::max(v->num_states, 1));
+  return reinterpret_cast<int32_t *>(q);
+}
+
+// Log-semiring scores through the mantissa/exponent recursion.  *launched stays
+// false when the view does not qualify (the caller then uses another kernel).
+// Kernels that find the view's bounds violated raise *status_word (device); the
+// host reads it only via CheckProbStatus.
+template <typename Real>
+int32_t LaunchProbScores(const k2b200_fsa_view *v, Real *fwd, Real *bwd, void *scratch,
+                         size_t scratch_bytes, cudaStream_t stream, bool *launched) {
+  *launched = false;
+  if (scratch == nullptr || scratch_bytes < ProbScratchBytes(v)) return kOk;
+  if (fwd != nullptr && (v->in_src == nullptr || v->in_score == nullptr)) return kOk;
+  if (v->row_ids1 == nullptr || v->row_ids2 == nullptr) return kOk;
+  ProbPlan p = PlanProb(v);
+  if (!p.ok || v->num_arcs == 0) return kOk;
+  char *q = reinterpret_cast<char *>(scratch);
+  ProbArc *fwd_arcs = reinterpret_cast<ProbArc *>(q);
+  ProbArc *bwd_arcs = fwd_arcs + std::max(v->num_arcs, 1);
+  q += AlignUp(2 * sizeof(ProbArc) * (size_t)std::max(v->num_arcs, 1));
+  double *m_out = reinterpret_cast<double *>(q);
+  q += AlignUp(2 * sizeof(double) * (size_t)std::max(v->num_states, 1));
+  int32_t *e_out = reinterpret_cast<int32_t *>(q);
+  q += AlignUp(2 * sizeof(int32_t) * (size_t)std::max(v->num_states, 1));
+  int32_t *status = reinterpret_cast<int32_t *>(q);
+  K2B_CUDA_OK(cudaMemsetAsync(status, 0, sizeof(int32_t), stream));
+  { PrepareProbArcs<<<CeilDiv(v->num_arcs, 256), 256, 0, stream>>>(*v, fwd ? fwd_arcs : nullptr,
+                                                                   bwd ? bwd_arcs : nullptr);
+    NoteLaunch(); }
+  int32_t ndir = (fwd != nullptr) + (bwd != nullptr), dir_base = fwd ? 0 : 1;
+  K2B_CUDA_OK(cudaFuncSetAttribute(ProbScoresStaged, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                   (int)p.bytes));
+  for (int32_t first = 0; first < v->num_fsas; first += 65535) {
+    int32_t n = std::min(v->num_fsas - first, 65535);
+    dim3 grid(ndir, n);
+    { ProbScoresStaged<<<grid, p.threads, p.bytes, stream>>>(*v, fwd_arcs, bwd_arcs, m_out, e_out,
+                                                            dir_base, first, p, status);
+      NoteLaunch(); }
+  }
+  int32_t ns = v->num_states;
+  if (fwd) { FinishLogScores<Real><<<CeilDiv(ns, 256), 256, 0, stream>>>(m_out, e_out, ns, fwd);
+             NoteLaunch(); }
+  if (bwd) { FinishLogScores<Real><<<CeilDiv(ns, 256), 256, 0, stream>>>(m_out + ns, e_out + ns,
+                                                                        ns, bwd);
+             NoteLaunch(); }
+  K2B_CUDA_OK(cudaGetLastError());
+  *launched = true;
+  return kOk;
+}
+
+template int32_t LaunchProbScores<float>(const k2b200_fsa_view *, float *, float *, void *,
+                                         size_t, cudaStream_t, bool *);
+template int32_t LaunchProbScores<double>(const k2b200_fsa_view *, double *, double *, void *,
+                                          size_t, cudaStream_t, bool *);
+
+template int32_t LaunchStagedScores<float>(const k2b200_fsa_view *, int32_t, float *, float *,
+                                           int32_t *, cudaStream_t, bool *);
+template int32_t LaunchStagedScores<double>(const k2b200_fsa_view *, int32_t, double *, double *,
+                                            int32_t *, cudaStream_t, bool *);
+
+}  // namespace k2b

@@ -13,6 +13,7 @@
 #include <algorithm>
 #include <vector>
 
+#include "cp_async.cuh"
 #include "intersect_internal.cuh"
 
 namespace k2b {
@@ -44,28 +45,6 @@ static SmemPlan PlanSmem(int32_t max_states, int32_t max_arcs, int32_t cols) {
 bool PersistentViterbiFits(const Layout &L, const k2b200_intersect_args *a) {
   SmemPlan p = PlanSmem(L.max_states, L.max_arcs, a->cols);
   return p.stages >= 2 && a->num_fsas <= 65535;
-}
-
-__device__ __forceinline__ void CpAsync4(float *smem_dst, const float *gmem_src) {
-  unsigned dst = (unsigned)__cvta_generic_to_shared(smem_dst);
-  asm volatile("cp.async.ca.shared.global [%0], [%1], 4;\n" ::"r"(dst), "l"(gmem_src));
-}
-__device__ __forceinline__ void CpAsyncCommit() { asm volatile("cp.async.commit_group;\n" ::); }
-template <int N>
-__device__ __forceinline__ void CpAsyncWait() {
-  asm volatile("cp.async.wait_group %0;\n" ::"n"(N));
-}
-__device__ __forceinline__ void CpAsyncWaitDyn(int n) {
-  // wait until at most n groups are pending (n < kMaxStages)
-  switch (n) {
-    case 0: CpAsyncWait<0>(); break;
-    case 1: CpAsyncWait<1>(); break;
-    case 2: CpAsyncWait<2>(); break;
-    case 3: CpAsyncWait<3>(); break;
-    case 4: CpAsyncWait<4>(); break;
-    case 5: CpAsyncWait<5>(); break;
-    default: CpAsyncWait<6>(); break;
-  }
 }
 
 // grid = (2 directions, pairs); dynamic shared memory per PlanSmem.
@@ -150,6 +129,119 @@ PersistentViterbi(const FsaInfo *__restrict__ infos, const Arc *__restrict__ arc
     }
   }
   CpAsyncWait<0>();
+}
+
+// ---------------------------------------------------------------------------
+// Register variant for graphs whose states have at most kMaxDeg arcs in each
+// direction (CTC graphs have 3) and at most 1024 states: one thread per state keeps
+// its arcs in registers and fetches the dense scores of its own arcs straight from
+// global memory kPrefetch frames ahead, so a frame costs one __syncthreads, kMaxDeg
+// shared-memory reads of the previous frame's scores and a few adds.  Unused arc
+// slots carry a score of -inf and never win the max.
+// ---------------------------------------------------------------------------
+constexpr int kRegMaxDeg = 4;
+constexpr int kRegPrefetch = 8;
+
+bool RegisterViterbiFits(const Layout &L, const k2b200_intersect_args *a) {
+  return a->a_max_degree > 0 && a->a_max_degree <= kRegMaxDeg && L.max_states <= 1024 &&
+         a->num_fsas <= 65535;
+}
+
+template <int kMaxThreads>
+__global__ void __launch_bounds__(kMaxThreads)
+RegisterViterbi(const FsaInfo *__restrict__ infos, const Arc *__restrict__ arcs,
+                const int32_t *__restrict__ a_row_splits2, const int32_t *__restrict__ in_splits,
+                const int32_t *__restrict__ in_arcs, const float *__restrict__ scores,
+                int32_t cols, float *__restrict__ fwd, float *__restrict__ bwd) {
+  __shared__ float buf[2][1024];
+  const FsaInfo f = infos[blockIdx.y];
+  const int dir = blockIdx.x;
+  const int32_t S = f.num_states, Tk = f.tk;
+  if (S == 0) return;
+  const int32_t s = threadIdx.x;
+  const bool active = s < S;
+
+  int32_t other[kRegMaxDeg], col[kRegMaxDeg];
+  float w[kRegMaxDeg];
+#pragma unroll
+  for (int j = 0; j < kRegMaxDeg; ++j) {
+    other[j] = 0;
+    col[j] = 0;
+    w[j] = -INFINITY;
+  }
+  if (active) {
+    const int32_t *splits = dir == 0 ? in_splits : a_row_splits2;
+    const int32_t a0 = splits[f.state_off + s], n = splits[f.state_off + s + 1] - a0;
+#pragma unroll
+    for (int j = 0; j < kRegMaxDeg; ++j) {
+      if (j < n) {
+        const Arc arc = arcs[dir == 0 ? in_arcs[a0 + j] : a0 + j];
+        other[j] = dir == 0 ? arc.src : arc.dest;
+        const int32_t c = arc.label + 1;
+        if (c >= 0 && c < cols) {
+          col[j] = c;
+          w[j] = arc.score;
+        }
+      }
+    }
+  }
+  // step t (1..Tk) consumes dense row t-1 (forward) or Tk-t (backward)
+  const float *base = scores + (int64_t)f.row0 * cols;
+  auto row_of = [&](int32_t step) {
+    step = step > Tk ? Tk : step;
+    return dir == 0 ? step - 1 : Tk - step;
+  };
+  float x[kRegMaxDeg][kRegPrefetch];
+#pragma unroll
+  for (int d = 0; d < kRegPrefetch; ++d) {
+    const int32_t r = row_of(1 + d) * cols;
+#pragma unroll
+    for (int j = 0; j < kRegMaxDeg; ++j) x[j][d] = __ldg(base + r + col[j]);
+  }
+  float *grid = (dir == 0 ? fwd : bwd) + f.grid_off;
+  {
+    const float v = (dir == 0 ? (s == 0) : (s == S - 1)) ? 0.0f : -INFINITY;
+    buf[0][s] = v;
+    if (active) grid[(int64_t)(dir == 0 ? 0 : Tk) * S + s] = v;
+  }
+  for (int32_t t0 = 1; t0 <= Tk; t0 += kRegPrefetch) {
+#pragma unroll
+    for (int u = 0; u < kRegPrefetch; ++u) {
+      const int32_t t = t0 + u;
+      if (t > Tk) break;
+      __syncthreads();
+      const float *cur = buf[(t - 1) & 1];
+      float best = -INFINITY;
+#pragma unroll
+      for (int j = 0; j < kRegMaxDeg; ++j) {
+        const float v = __fadd_rn(__fadd_rn(cur[other[j]], w[j]), x[j][u]);
+        best = v > best ? v : best;
+      }
+      const int32_t r = row_of(t + kRegPrefetch) * cols;
+#pragma unroll
+      for (int j = 0; j < kRegMaxDeg; ++j) x[j][u] = __ldg(base + r + col[j]);
+      buf[t & 1][s] = best;
+      if (active) grid[(int64_t)(dir == 0 ? t : Tk - t) * S + s] = best;
+    }
+  }
+}
+
+int32_t LaunchRegisterViterbi(const Layout &L, const k2b200_intersect_args *a,
+                              const FsaInfo *d_infos, float *fwd, float *bwd,
+                              cudaStream_t stream) {
+  int32_t threads = std::max(32, (L.max_states + 31) / 32 * 32);
+  dim3 grid(2, a->num_fsas);
+  const Arc *arcs = reinterpret_cast<const Arc *>(a->a_arcs);
+  if (threads <= 512)
+    { RegisterViterbi<512><<<grid, threads, 0, stream>>>(d_infos, arcs, a->a_row_splits2,
+                                                        a->a_in_splits, a->a_in_arcs, a->scores,
+                                                        a->cols, fwd, bwd); NoteLaunch(); }
+  else
+    { RegisterViterbi<1024><<<grid, threads, 0, stream>>>(d_infos, arcs, a->a_row_splits2,
+                                                         a->a_in_splits, a->a_in_arcs, a->scores,
+                                                         a->cols, fwd, bwd); NoteLaunch(); }
+  K2B_CUDA_OK(cudaGetLastError());
+  return kOk;
 }
 
 int32_t LaunchPersistentViterbi(const Layout &L, const k2b200_intersect_args *a,

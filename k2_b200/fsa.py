@@ -9,6 +9,7 @@ score cache and its invalidation when `scores` is re-assigned (fsa.py:242-273,
 `requires_grad_`, `shape`, `num_arcs`.  Not mirrored (outside this path):
 ragged attributes, symbol tables, drawing, (de)serialisation, indexing helpers.
 """
+import ctypes
 import re
 from typing import Any, Dict, Iterator, List, Optional, Tuple, Union
 
@@ -92,6 +93,7 @@ class Fsa(object):
                 assert value.dtype == torch.float32
                 # the float bit patterns are stored in the int32 arc tensor
                 self.arcs.values()[:, 3] = value.detach().view(torch.int32)
+                self.arcs._incoming = None  # it carries a copy of the scores
                 self._invalidate_cache_()
         else:
             self._non_tensor_attr[name] = value
@@ -223,16 +225,17 @@ class Fsa(object):
         entering = None
         if want_forward and not log_semiring:
             entering = torch.empty(ns, dtype=torch.int32, device=dev)
-        in_splits, in_arcs = arcs.incoming() if want_forward else (None, None)
-        lvl_off, lvl_splits = arcs.levels()
+        view, keep = arcs.view(want_incoming=want_forward)
+        scratch, nscratch = None, 0
+        if log_semiring and arcs._layer_bounds[0]:
+            nscratch = _lib.lib.k2b200_fsa_scores_scratch_bytes(ctypes.byref(view))
+            scratch = torch.empty(nscratch, dtype=torch.uint8, device=dev)
         with torch.cuda.device(dev):
             _lib.check(_lib.lib.k2b200_fsa_scores(
-                _lib.ptr(arcs._row_splits1), _lib.ptr(arcs._row_splits2),
-                _lib.ptr(arcs.row_ids(2 - arcs.single)), _lib.ptr(arcs.values()),
-                _lib.ptr(in_splits), _lib.ptr(in_arcs), _lib.ptr(lvl_off), _lib.ptr(lvl_splits),
-                nf, ns, na, int(log_semiring), int(use_double_scores), _lib.ptr(fwd),
-                _lib.ptr(bwd), _lib.ptr(entering), _lib.stream_of(dev)))
-        _lib.note_launches(1)
+                ctypes.byref(view), int(log_semiring), int(use_double_scores), _lib.ptr(fwd),
+                _lib.ptr(bwd), _lib.ptr(entering), _lib.ptr(scratch), nscratch,
+                _lib.stream_of(dev)))
+        del keep, scratch
         if want_forward:
             self._cache[fkey] = fwd
             if entering is not None:

@@ -36,8 +36,11 @@ class RaggedArc:
         self._h_row_splits1 = h_row_splits1
         self._h_arc_splits = h_arc_splits
         # lazily built device-side helpers
-        self._incoming = None  # (in_splits, in_arcs)
+        self._incoming = None  # (in_splits, in_arcs, in_src, in_score)
         self._levels = None    # (level_offsets, level_splits) of a layered FsaVec
+        # (strict, max_layers, max_layer_states, max_layer_arcs): set for lattices
+        # whose arcs all go from one layer to the next, with bounds on layer sizes
+        self._layer_bounds = (0, 0, 0, 0)
 
     # ---- _k2.RaggedArc interface ----------------------------------------
     def values(self) -> torch.Tensor:
@@ -103,8 +106,8 @@ class RaggedArc:
         out = RaggedArc(self._values.clone(), self._row_splits1, self._row_splits2,
                         self._row_ids1, self._row_ids2, self.single, self._h_row_splits1,
                         self._h_arc_splits)
-        out._incoming = self._incoming
         out._levels = self._levels
+        out._layer_bounds = self._layer_bounds
         return out
 
     # ---- host copies of the small per-FSA splits ---------------------------
@@ -124,25 +127,57 @@ class RaggedArc:
 
     # ---- device-side helpers -------------------------------------------------
     def incoming(self):
-        """(in_splits, in_arcs): arcs entering every state, by arc index.  Cached;
-        the reference recomputes it on every intersect_dense call
-        (k2/csrc/intersect_dense.cu:139-142)."""
+        """(in_splits, in_arcs, in_src, in_score): the arcs entering every state by
+        arc index, with their source state (idx01) and score in the same order.
+        Cached; the reference recomputes the index on every intersect_dense call
+        (k2/csrc/intersect_dense.cu:139-142).  The cache is dropped when the
+        scores or labels of the owning Fsa are re-assigned."""
         if self._incoming is None:
             _lib.require_cuda(self._values, "arcs")
             ns, na = self.num_states, self.num_elements()
             dev = self.device
             in_splits = torch.empty(ns + 1, dtype=torch.int32, device=dev)
-            in_arcs = torch.empty(max(na, 1), dtype=torch.int32, device=dev)
+            buf = torch.empty((3, max(na, 1)), dtype=torch.int32, device=dev)
             tmp = torch.empty(_lib.lib.k2b200_fsa_incoming_tmp_bytes(ns, na), dtype=torch.uint8,
                               device=dev)
             with torch.cuda.device(dev):
                 _lib.check(_lib.lib.k2b200_fsa_incoming(
                     _lib.ptr(self._row_splits1), _lib.ptr(self.row_ids(1 - self.single)),
                     _lib.ptr(self.row_ids(2 - self.single)), _lib.ptr(self._values),
-                    self.num_fsas, ns, na, _lib.ptr(in_splits), _lib.ptr(in_arcs),
-                    _lib.ptr(tmp), _lib.stream_of(dev)))
-            self._incoming = (in_splits, in_arcs[:na])
+                    self.num_fsas, ns, na, _lib.ptr(in_splits), buf[0].data_ptr(),
+                    buf[1].data_ptr(), buf[2].data_ptr(), _lib.ptr(tmp), _lib.stream_of(dev)))
+            self._incoming = (in_splits, buf[0, :na], buf[1, :na],
+                              buf[2, :na].view(torch.float32))
         return self._incoming
+
+    def max_degree(self) -> int:
+        """Largest in- or out-degree of any state (one host read, cached)."""
+        if getattr(self, "_max_degree", None) is None:
+            if self.num_elements() == 0:
+                self._max_degree = 0
+            else:
+                in_splits = self.incoming()[0]
+                m = torch.maximum(torch.diff(in_splits).max(), torch.diff(self._row_splits2).max())
+                self._max_degree = int(m.item())
+        return self._max_degree
+
+    def view(self, want_incoming: bool):
+        """The k2b200_fsa_view of this FsaVec (keeps the tensors it points to alive
+        through the returned tuple)."""
+        lvl_off, lvl_splits = self.levels()
+        inc = self.incoming() if want_incoming else (None, None, None, None)
+        strict, max_layers, max_w, max_a = self._layer_bounds
+        rid1, rid2 = self.row_ids(1 - self.single), self.row_ids(2 - self.single)
+        v = _lib.FsaView(
+            num_fsas=self.num_fsas, num_states=self.num_states, num_arcs=self.num_elements(),
+            row_splits1=_lib.ptr(self._row_splits1), row_ids1=_lib.ptr(rid1),
+            row_splits2=_lib.ptr(self._row_splits2), row_ids2=_lib.ptr(rid2),
+            arcs=_lib.ptr(self._values), in_splits=_lib.ptr(inc[0]), in_arcs=_lib.ptr(inc[1]),
+            in_src=_lib.ptr(inc[2]), in_score=_lib.ptr(inc[3]),
+            level_offsets=_lib.ptr(lvl_off), level_splits=_lib.ptr(lvl_splits),
+            strict_layers=strict, max_layers=max_layers, max_layer_states=max_w,
+            max_layer_arcs=max_a)
+        return v, (inc, lvl_off, lvl_splits, rid1, rid2)
 
     def levels(self):
         """(level_offsets, level_splits): a layering of the states such that every

@@ -33,7 +33,7 @@ def _micro():
     return a, scores, np.array([0, 4, 7], np.int32)
 
 
-@pytest.mark.parametrize("mode", [1, 2])
+@pytest.mark.parametrize("mode", [1, 2, 3])
 def test_micro_example_known_answer(k2, mode):
     # worked example computed with the reference: two copies of a 4-state graph
     from gpu_util import dense_from_scores, fsa_to_host, host_to_fsa, intersect_raw
@@ -160,7 +160,7 @@ def test_ctc_small_full_size(k2):
     assert want["lattice"].num_arcs > 50000  # beam 10 keeps ~72k arcs on this workload
 
 
-@pytest.mark.parametrize("mode", [1, 2])
+@pytest.mark.parametrize("mode", [1, 2, 3])
 def test_ctc_large_quarter(k2, mode):
     from k2_b200 import synthetic as syn
     _workload_case(k2, syn.ctc_large(scale=0.25), mode=mode)
@@ -291,7 +291,7 @@ def test_generic_ragged_ops(k2):
     a = random_fsa_vec(rng, 9, max_states=30, max_arcs=300)
     from gpu_util import host_to_fsa
     f = host_to_fsa(a)
-    in_splits, in_arcs = f.arcs.incoming()
+    in_splits, in_arcs, in_src, in_score = f.arcs.incoming()
     state_of = np.repeat(np.arange(a.num_states), np.diff(a.row_splits2))
     fsa_of = np.repeat(np.arange(a.num_fsas), np.diff(a.row_splits1))[state_of]
     dest01 = a.row_splits1[fsa_of] + a.arcs[:, 1]
@@ -300,3 +300,5 @@ def test_generic_ragged_ops(k2):
     cnt = np.bincount(dest01, minlength=a.num_states)
     np.testing.assert_array_equal(in_splits.cpu().numpy(), np.concatenate([[0], np.cumsum(cnt)]))
     np.testing.assert_array_equal(f.arcs.row_ids(2).cpu().numpy(), state_of)
+    np.testing.assert_array_equal(in_src.cpu().numpy(), state_of[order])
+    np.testing.assert_array_equal(in_score.cpu().numpy(), a.scores[order])
