@@ -324,7 +324,7 @@ __global__ void FinishLogScores(const double *__restrict__ m, const int32_t *__r
 }
 
 struct ProbPlan {
-  int32_t maxw, maxa, nl_cap, stages, stage_bytes, lanes_log2, threads;
+  int32_t maxw, maxa, nl_cap, stages, stage_bytes, splits_bytes, lanes_log2, threads;
   size_t bytes;
   bool ok;
 };
@@ -337,9 +337,12 @@ static ProbPlan PlanProb(const k2b200_fsa_view *v) {
   p.maxw = (v->max_layer_states + 3) & ~3;
   p.maxa = std::max(v->max_layer_arcs, 1);
   p.nl_cap = v->max_layers;
-  int32_t splits_bytes = (((p.maxw + 1) * 4) + 15) & ~15;
-  p.stage_bytes = splits_bytes + p.maxa * 16;
-  size_t fixed = 8 * (size_t)((p.nl_cap + 1 + 3) & ~3)   // layer / arc boundaries
+  // splits chunk: up to 3 leading and 3 trailing ints (the copy starts and ends on
+  // 16-byte boundaries) + w + 1
+  p.splits_bytes = (((p.maxw + 8) * 4) + 15) & ~15;
+  p.stage_bytes = p.splits_bytes + p.maxa * 16;
+  size_t fixed = 128                                      // mbarriers
+                 + 8 * (size_t)((p.nl_cap + 1 + 3) & ~3)  // layer / arc boundaries
                  + 2 * (size_t)p.maxw * 12 + 16;          // mantissa + exponent ping-pong
   if (fixed + 2 * (size_t)p.stage_bytes > kStagedSmemBudget) return p;
   p.stages = (int32_t)std::min<size_t>(8, (kStagedSmemBudget - fixed) / p.stage_bytes);
@@ -347,18 +350,23 @@ static ProbPlan PlanProb(const k2b200_fsa_view *v) {
   int32_t mean_deg = v->num_states > 0 ? (v->num_arcs + v->num_states - 1) / v->num_states : 1;
   p.lanes_log2 = 0;
   while ((2 << p.lanes_log2) <= mean_deg / 2 && p.lanes_log2 < 5) ++p.lanes_log2;
-  p.threads = p.lanes_log2 >= 3 ? 256 : 128;
+  // compute threads plus one producer warp
+  p.threads = (p.lanes_log2 >= 3 ? 224 : (p.lanes_log2 >= 1 ? 128 : 64)) + 32;
   p.ok = true;
   return p;
 }
 
 // grid = (directions, fsas).  m_out / e_out: [2][num_states] (forward then backward).
+// Per layer one thread starts two bulk (TMA) copies into the ring - the per-state
+// splits (from the 16-byte boundary below the first one) and the layer's ProbArcs -
+// and every thread waits on the stage's mbarrier; the waits are bounded and raise
+// *status when they give up.
 __global__ void __launch_bounds__(256)
 ProbScoresStaged(k2b200_fsa_view v, const ProbArc *__restrict__ fwd_arcs,
                  const ProbArc *__restrict__ bwd_arcs, double *__restrict__ m_out,
                  int32_t *__restrict__ e_out, int32_t dir_base, int32_t fsa_base, ProbPlan p,
                  int32_t *__restrict__ status) {
-  extern __shared__ __align__(16) unsigned char smem_raw[];
+  extern __shared__ __align__(128) unsigned char smem_raw[];
   const int32_t i = fsa_base + blockIdx.y, dir = blockIdx.x + dir_base;
   const int32_t s_begin = v.row_splits1[i], s_end = v.row_splits1[i + 1];
   if (s_end == s_begin) return;
@@ -367,19 +375,25 @@ ProbScoresStaged(k2b200_fsa_view v, const ProbArc *__restrict__ fwd_arcs,
   double *mo = m_out + (size_t)dir * v.num_states;
   int32_t *eo = e_out + (size_t)dir * v.num_states;
 
+  uint64_t *bars = reinterpret_cast<uint64_t *>(smem_raw);  // [stages], 128 bytes reserved
   const int32_t lvl_ints = (p.nl_cap + 1 + 3) & ~3;
-  int32_t *lvl = reinterpret_cast<int32_t *>(smem_raw);
+  int32_t *lvl = reinterpret_cast<int32_t *>(smem_raw + 128);
   int32_t *alvl = lvl + lvl_ints;
   double *mant = reinterpret_cast<double *>(alvl + lvl_ints);      // [2][maxw]
   int32_t *expo = reinterpret_cast<int32_t *>(mant + 2 * p.maxw);  // [2][maxw]
   unsigned char *ring = reinterpret_cast<unsigned char *>(
       (reinterpret_cast<uintptr_t>(expo + 2 * p.maxw) + 15) & ~(uintptr_t)15);
-  const int32_t splits_bytes = (((p.maxw + 1) * 4) + 15) & ~15;
   const int32_t *gsplits = dir == 0 ? v.in_splits : v.row_splits2;
   const ProbArc *garcs = dir == 0 ? fwd_arcs : bwd_arcs;
+  // last 4-int boundary inside the splits array (num_states + 1 entries)
+  const int32_t splits_aligned_end = (v.num_states + 1) & ~3;
 
   __shared__ int32_t bad_shared;
-  if (tid == 0) bad_shared = (nl > p.nl_cap);
+  if (tid == 0) {
+    bad_shared = (nl > p.nl_cap);
+    for (int32_t s = 0; s < p.stages; ++s) MbarInit(&bars[s], 1);
+    MbarInitFence();
+  }
   __syncthreads();
   if (!bad_shared)
     for (int32_t k = tid; k <= nl; k += nt) {
@@ -401,39 +415,59 @@ ProbScoresStaged(k2b200_fsa_view v, const ProbArc *__restrict__ fwd_arcs,
   }
 
   const int32_t stages = p.stages;
+  // The last warp only feeds the ring; the others own the states.
+  const int32_t nc = nt - 32;
+  const bool producer = tid >= nc;
   auto layer_of = [&](int32_t step) { return dir == 0 ? step : nl - 1 - step; };
-  auto issue = [&](int32_t step, int32_t slot) {
-    if (step < nl) {
-      const int32_t li = layer_of(step);
-      const int32_t b = lvl[li], w = lvl[li + 1] - b, ab = alvl[li], na = alvl[li + 1] - ab;
-      unsigned char *st = ring + (size_t)slot * p.stage_bytes;
-      int32_t *sp = reinterpret_cast<int32_t *>(st);
-      for (int32_t k = tid; k <= w; k += nt) CpAsync4(sp + k, gsplits + b + k);
-      ProbArc *body = reinterpret_cast<ProbArc *>(st + splits_bytes);
-      for (int32_t k = tid; k < na; k += nt) CpAsync16(body + k, garcs + ab + k);
-    }
-    CpAsyncCommit();
+  auto issue = [&](int32_t step, int32_t slot) {  // one thread
+    if (step >= nl) return;
+    const int32_t li = layer_of(step);
+    const int32_t b = lvl[li], e = lvl[li + 1], ab = alvl[li], na = alvl[li + 1] - ab;
+    unsigned char *st = ring + (size_t)slot * p.stage_bytes;
+    int32_t *sp = reinterpret_cast<int32_t *>(st);
+    const int32_t lo = b & ~3;
+    int32_t hi = (e + 1 + 3) & ~3;
+    hi = hi < splits_aligned_end ? hi : splits_aligned_end;
+    hi = hi > lo ? hi : lo;
+    const unsigned bytes_splits = (unsigned)(hi - lo) * 4u, bytes_arcs = (unsigned)na * 16u;
+    MbarArriveExpectTx(&bars[slot], bytes_splits + bytes_arcs);
+    if (bytes_splits) BulkCopyG2S(sp, gsplits + lo, bytes_splits, &bars[slot]);
+    if (bytes_arcs) BulkCopyG2S(st + p.splits_bytes, garcs + ab, bytes_arcs, &bars[slot]);
+    for (int32_t k = hi; k <= e; ++k) sp[k - lo] = gsplits[k];  // at most 3 trailing ints
   };
   int32_t issue_slot = 0;
-  for (int32_t step = 0; step < stages - 1; ++step) {
-    issue(step, issue_slot);
-    issue_slot = issue_slot + 1 == stages ? 0 : issue_slot + 1;
-  }
+  if (tid == nc)
+    for (int32_t step = 0; step < stages - 1; ++step) {
+      issue(step, issue_slot);
+      issue_slot = issue_slot + 1 == stages ? 0 : issue_slot + 1;
+    }
 
-  const int32_t lg = p.lanes_log2, G = 1 << lg, g = tid & (G - 1), per_pass = nt >> lg;
+  const int32_t lg = p.lanes_log2, G = 1 << lg, g = tid & (G - 1), per_pass = nc >> lg;
   int32_t slot = 0;
+  unsigned parity = 0;
   for (int32_t step = 0; step < nl; ++step) {
-    CpAsyncWaitDyn(stages - 2);
-    __syncthreads();
-    issue(step + stages - 1, issue_slot);
-    issue_slot = issue_slot + 1 == stages ? 0 : issue_slot + 1;
+    if (!producer && !MbarTryWait(&bars[slot], parity) && !MbarWaitBounded(&bars[slot], parity)) {
+      // give the copies in flight one more bounded chance to land; the host-side
+      // fallback recomputes everything when it sees the status
+      atomicExch(status, 2);
+      MbarWaitBounded(&bars[slot], parity);
+      *reinterpret_cast<volatile int32_t *>(&bad_shared) = 2;
+    }
+    __syncthreads();  // previous layer's scores are complete; the oldest slot is free
+    if (*reinterpret_cast<volatile int32_t *>(&bad_shared)) break;  // uniform: a wait gave up
+    if (producer) {
+      if (tid == nc) issue(step + stages - 1, issue_slot);
+      issue_slot = issue_slot + 1 == stages ? 0 : issue_slot + 1;
+      continue;
+    }
     const int32_t li = layer_of(step);
     const int32_t b = lvl[li], w = lvl[li + 1] - b, ab = alvl[li];
     const int32_t other_base = step == 0 ? 0 : lvl[dir == 0 ? li - 1 : li + 1];
     const unsigned char *st = ring + (size_t)slot * p.stage_bytes;
+    const int32_t *sp = reinterpret_cast<const int32_t *>(st) + (b & 3);
+    const ProbArc *body = reinterpret_cast<const ProbArc *>(st + p.splits_bytes);
     slot = slot + 1 == stages ? 0 : slot + 1;
-    const int32_t *sp = reinterpret_cast<const int32_t *>(st);
-    const ProbArc *body = reinterpret_cast<const ProbArc *>(st + splits_bytes);
+    parity ^= (slot == 0);
     const double *pm = mant + ((step + 1) & 1) * p.maxw;
     const int32_t *pe = expo + ((step + 1) & 1) * p.maxw;
     double *cm = mant + (step & 1) * p.maxw;
@@ -445,27 +479,38 @@ ProbScoresStaged(k2b200_fsa_view v, const ProbArc *__restrict__ fwd_arcs,
         k0 = sp[j] - ab;
         k1 = sp[j + 1] - ab;
       }
-      // terms t_k = m_prev * f_k with exponent e_prev + k_k; E = largest exponent
+      // Running sum of the terms m_prev * f * 2^(e_prev + k), kept as sum * 2^E with E
+      // the largest exponent met so far; four arcs per trip so that their loads and
+      // multiplies overlap.
+      double sum = 0.0;
       int32_t E = kZeroExp;
-      for (int32_t k = k0 + g; k < k1; k += G) {
-        const ProbArc a = body[k];
-        const int32_t o = a.other - other_base;
-        const int32_t te = (pm[o] == 0.0 || a.f == 0.0) ? kZeroExp : pe[o] + a.k;
-        E = te > E ? te : E;
+      for (int32_t k = k0 + 4 * g; k < k1; k += 4 * G) {
+        double t[4];
+        int32_t te[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const int32_t kk = k + u < k1 ? k + u : k1 - 1;
+          const ProbArc a = body[kk];
+          const int32_t o = a.other - other_base;
+          const double tv = k + u < k1 ? pm[o] * a.f : 0.0;
+          t[u] = tv;
+          te[u] = tv != 0.0 ? pe[o] + a.k : kZeroExp;
+        }
+        int32_t En = E;
+#pragma unroll
+        for (int u = 0; u < 4; ++u) En = te[u] > En ? te[u] : En;
+        sum *= Pow2NonPos(E - En);
+#pragma unroll
+        for (int u = 0; u < 4; ++u) sum += t[u] * Pow2NonPos(te[u] - En);
+        E = En;
       }
       for (int32_t d = G >> 1; d > 0; d >>= 1) {
-        int32_t o = __shfl_xor_sync(0xffffffffu, E, d);
-        E = o > E ? o : E;
+        const int32_t Eo = __shfl_xor_sync(0xffffffffu, E, d);
+        const double so = __shfl_xor_sync(0xffffffffu, sum, d);
+        const int32_t En = Eo > E ? Eo : E;
+        sum = sum * Pow2NonPos(E - En) + so * Pow2NonPos(Eo - En);
+        E = En;
       }
-      double sum = 0.0;
-      if (E != kZeroExp)
-        for (int32_t k = k0 + g; k < k1; k += G) {
-          const ProbArc a = body[k];
-          const int32_t o = a.other - other_base;
-          const double t = pm[o] * a.f;
-          if (t != 0.0) sum += t * Pow2NonPos(pe[o] + a.k - E);
-        }
-      for (int32_t d = G >> 1; d > 0; d >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, d);
       if (j < w && g == 0) {
         const int32_t s = b + j;
         int32_t e = E;
@@ -481,7 +526,6 @@ ProbScoresStaged(k2b200_fsa_view v, const ProbArc *__restrict__ fwd_arcs,
       }
     }
   }
-  CpAsyncWait<0>();
 }
 
 size_t ProbScratchBytes(const k2b200_fsa_view *v) {
@@ -513,6 +557,10 @@ int32_t LaunchProbScores(const k2b200_fsa_view *v, Real *fwd, Real *bwd, void *s
   if (v->row_ids1 == nullptr || v->row_ids2 == nullptr) return kOk;
   ProbPlan p = PlanProb(v);
   if (!p.ok || v->num_arcs == 0) return kOk;
+  // bulk copies need 16-byte aligned sources
+  auto aligned16 = [](const void *ptr) { return (reinterpret_cast<uintptr_t>(ptr) & 15) == 0; };
+  if (!aligned16(scratch) || !aligned16(v->row_splits2) || (fwd && !aligned16(v->in_splits)))
+    return kOk;
   char *q = reinterpret_cast<char *>(scratch);
   ProbArc *fwd_arcs = reinterpret_cast<ProbArc *>(q);
   ProbArc *bwd_arcs = fwd_arcs + std::max(v->num_arcs, 1);
