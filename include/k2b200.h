@@ -53,7 +53,7 @@ int32_t k2b200_abi_version(void);
  * for them, returns the summed milliseconds of the n recorded intervals and
  * resets the phase.  Phases: 0 Viterbi recursion, 1 pruning (count + numbering),
  * 2 lattice emission, 3 forward/backward scores, 4 posteriors + gradient
- * scatter, 5 incoming-arc index. */
+ * scatter, 5 incoming-arc index, 6 DenseFsaVec construction and its backward. */
 int64_t k2b200_kernel_launch_count(void);
 void k2b200_profile_enable(int32_t on);
 double k2b200_profile_read_ms(int32_t phase, int64_t *intervals);
@@ -113,6 +113,31 @@ int32_t k2b200_fsa_incoming(const int32_t *row_splits1, const int32_t *row_ids1,
                             int32_t num_fsas, int32_t num_states, int32_t num_arcs,
                             int32_t *in_splits, int32_t *in_arcs, int32_t *in_src,
                             float *in_score, void *tmp, void *stream);
+
+/* ---------------------------------------------------------------------------
+ * DenseFsaVec.
+ * k2b200_dense_fsa_vec_fill writes the whole score matrix of a DenseFsaVec
+ * (scores[rows, C+1], rows = sum_i (dur_i + 1)) from log_probs[N, T, C]: column
+ * 0 is -inf, columns 1..C hold the frames of each supervision segment, and the
+ * extra last row of each segment is [0, -inf, ...].  segments is the DEVICE copy
+ * of the [num_segs, 3] int32 (sequence, start_frame, duration) rows, durations
+ * already truncated to the frames that exist; row_splits[num_segs+1] (device)
+ * gives the first score row of each segment.  Replaces the gather and fills of
+ * k2.DenseFsaVec.__init__, k2/python/k2/dense_fsa_vec.py:101-133.
+ * k2b200_dense_fsa_vec_backward is its adjoint: grad_log_probs[N, T, C] is
+ * zero-filled and receives grad_scores[:, 1:] of the frame rows; pass
+ * overlapping != 0 when two segments may cover the same frame (atomic adds).
+ * ------------------------------------------------------------------------- */
+int32_t k2b200_dense_fsa_vec_fill(const float *log_probs, int64_t num_seqs,
+                                  int64_t num_frames, int32_t num_classes,
+                                  const int32_t *segments, const int32_t *row_splits,
+                                  int32_t num_segs, float *scores, int32_t rows,
+                                  void *stream);
+int32_t k2b200_dense_fsa_vec_backward(const float *grad_scores, int64_t num_seqs,
+                                      int64_t num_frames, int32_t num_classes,
+                                      const int32_t *segments, const int32_t *row_splits,
+                                      int32_t num_segs, int32_t rows, int32_t overlapping,
+                                      float *grad_log_probs, void *stream);
 
 /* ---------------------------------------------------------------------------
  * intersect_dense.

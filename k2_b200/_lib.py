@@ -97,6 +97,10 @@ _sig("k2b200_tot_scores_tropical_backward", c_i32,
      [c_vp, c_vp, c_i32, c_vp, c_i32, c_i32, c_vp, c_i64, c_vp, c_vp])
 _sig("k2b200_index_add", c_i32, [c_vp, c_vp, c_i32, c_vp, c_i64, c_vp])
 _sig("k2b200_index_select_i32", c_i32, [c_vp, c_i64, c_vp, c_i32, c_vp, c_vp])
+_sig("k2b200_dense_fsa_vec_fill", c_i32,
+     [c_vp, c_i64, c_i64, c_i32, c_vp, c_vp, c_i32, c_vp, c_i32, c_vp])
+_sig("k2b200_dense_fsa_vec_backward", c_i32,
+     [c_vp, c_i64, c_i64, c_i32, c_vp, c_vp, c_i32, c_i32, c_i32, c_vp, c_vp])
 _sig("k2b200_shortest_path_tmp_bytes", c_sz, [c_i32])
 _sig("k2b200_shortest_path", c_i32, [c_vp, c_vp, c_vp, c_i32, c_vp, c_vp, c_vp, c_vp])
 _sig("k2b200_fsa_properties_tmp_bytes", c_sz, [c_i32, c_i32])
@@ -114,6 +118,7 @@ EXPORTED = [
     "k2b200_fsa_tot_scores", "k2b200_fsa_arc_post", "k2b200_tot_scores_log_backward",
     "k2b200_tot_scores_tropical_backward", "k2b200_index_add", "k2b200_index_select_i32",
     "k2b200_shortest_path_tmp_bytes", "k2b200_shortest_path",
+    "k2b200_dense_fsa_vec_fill", "k2b200_dense_fsa_vec_backward",
     "k2b200_fsa_properties_tmp_bytes", "k2b200_fsa_properties",
 ]
 
@@ -161,7 +166,7 @@ def note_launches(n: int) -> None:  # kept for callers; the library counts itsel
     pass
 
 
-PHASES = ["viterbi", "prune", "emit", "scores", "post", "incoming"]
+PHASES = ["viterbi", "prune", "emit", "scores", "post", "incoming", "dense"]
 
 
 def profile_enable(on: bool) -> None:

@@ -1,0 +1,114 @@
+// DenseFsaVec construction and its backward as single kernels.
+//
+// The reference builds the [sum(T_i + 1), C + 1] score matrix with a Python loop, a
+// torch index_select over whole rows and three fill operations
+// (k2/python/k2/dense_fsa_vec.py:101-133); autograd later replays that backwards
+// with an index_add over the full matrix.  Here one kernel writes every element of
+// the matrix exactly once (column 0, the gathered log-probs, and the extra final
+// row of each sequence), and one kernel scatters the gradient back.
+#include "../../include/k2b200.h"
+#include "common.cuh"
+
+namespace k2b {
+
+// Segment owning score row r (row_splits has num_segs + 1 entries).
+__device__ __forceinline__ int32_t SegmentOfRow(const int32_t *__restrict__ row_splits,
+                                                int32_t num_segs, int32_t r) {
+  int32_t lo = 0, hi = num_segs;
+  while (hi - lo > 1) {
+    int32_t mid = (lo + hi) >> 1;
+    if (row_splits[mid] <= r) lo = mid; else hi = mid;
+  }
+  return lo;
+}
+
+// One CTA per score row.  segments: [num_segs, 3] = (sequence, start_frame, duration
+// after truncation).
+__global__ void __launch_bounds__(128)
+DenseFill(const float *__restrict__ log_probs, int64_t T, int32_t C,
+          const int32_t *__restrict__ segments, const int32_t *__restrict__ row_splits,
+          int32_t num_segs, float *__restrict__ scores) {
+  const int32_t r = blockIdx.x;
+  __shared__ int64_t src_row;  // row of log_probs viewed as [N*T, C], -1 for a final row
+  if (threadIdx.x == 0) {
+    const int32_t k = SegmentOfRow(row_splits, num_segs, r);
+    const int32_t t = r - row_splits[k], dur = row_splits[k + 1] - row_splits[k] - 1;
+    src_row = t < dur ? (int64_t)segments[3 * k] * T + segments[3 * k + 1] + t : -1;
+  }
+  __syncthreads();
+  float *out = scores + (int64_t)r * (C + 1);
+  const int64_t src = src_row;
+  if (src >= 0) {
+    const float *in = log_probs + src * C;
+    if (threadIdx.x == 0) out[0] = -INFINITY;
+    for (int32_t c = threadIdx.x; c < C; c += blockDim.x) out[1 + c] = __ldg(in + c);
+  } else {
+    if (threadIdx.x == 0) out[0] = 0.0f;
+    for (int32_t c = threadIdx.x; c < C; c += blockDim.x) out[1 + c] = -INFINITY;
+  }
+}
+
+// grad_log_probs[seq, start + t, c] (+)= grad_scores[row, 1 + c].
+__global__ void __launch_bounds__(128)
+DenseBackward(const float *__restrict__ grad_scores, int64_t T, int32_t C,
+              const int32_t *__restrict__ segments, const int32_t *__restrict__ row_splits,
+              int32_t num_segs, int32_t use_atomics, float *__restrict__ grad_log_probs) {
+  const int32_t r = blockIdx.x;
+  __shared__ int64_t dst_row;
+  if (threadIdx.x == 0) {
+    const int32_t k = SegmentOfRow(row_splits, num_segs, r);
+    const int32_t t = r - row_splits[k], dur = row_splits[k + 1] - row_splits[k] - 1;
+    dst_row = t < dur ? (int64_t)segments[3 * k] * T + segments[3 * k + 1] + t : -1;
+  }
+  __syncthreads();
+  const int64_t dst = dst_row;
+  if (dst < 0) return;
+  const float *in = grad_scores + (int64_t)r * (C + 1) + 1;
+  float *out = grad_log_probs + dst * C;
+  if (use_atomics) {
+    for (int32_t c = threadIdx.x; c < C; c += blockDim.x) atomicAdd(out + c, in[c]);
+  } else {
+    for (int32_t c = threadIdx.x; c < C; c += blockDim.x) out[c] = in[c];
+  }
+}
+
+}  // namespace k2b
+
+using namespace k2b;
+
+extern "C" {
+
+int32_t k2b200_dense_fsa_vec_fill(const float *log_probs, int64_t num_seqs, int64_t num_frames,
+                                  int32_t num_classes, const int32_t *segments,
+                                  const int32_t *row_splits, int32_t num_segs, float *scores,
+                                  int32_t rows, void *stream) {
+  (void)num_seqs;
+  K2B_REQUIRE(log_probs && segments && row_splits && scores, "NULL pointer");
+  K2B_REQUIRE(num_segs > 0 && num_classes > 0 && rows > 0, "empty DenseFsaVec");
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  PhaseTimer timer(kPhaseDense, s);
+  { DenseFill<<<rows, 128, 0, s>>>(log_probs, num_frames, num_classes, segments, row_splits,
+                                   num_segs, scores); NoteLaunch(); }
+  K2B_CUDA_OK(cudaGetLastError());
+  return kOk;
+}
+
+int32_t k2b200_dense_fsa_vec_backward(const float *grad_scores, int64_t num_seqs,
+                                      int64_t num_frames, int32_t num_classes,
+                                      const int32_t *segments, const int32_t *row_splits,
+                                      int32_t num_segs, int32_t rows, int32_t overlapping,
+                                      float *grad_log_probs, void *stream) {
+  K2B_REQUIRE(grad_scores && segments && row_splits && grad_log_probs, "NULL pointer");
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  PhaseTimer timer(kPhaseDense, s);
+  K2B_CUDA_OK(cudaMemsetAsync(grad_log_probs, 0,
+                              sizeof(float) * (size_t)num_seqs * num_frames * num_classes, s));
+  if (rows > 0)
+    { DenseBackward<<<rows, 128, 0, s>>>(grad_scores, num_frames, num_classes, segments,
+                                         row_splits, num_segs, overlapping, grad_log_probs);
+      NoteLaunch(); }
+  K2B_CUDA_OK(cudaGetLastError());
+  return kOk;
+}
+
+}  // extern "C"

@@ -79,7 +79,13 @@ static int32_t MakeLayout(const k2b200_intersect_args *a, Layout *L) {
   L->grid_elems = grid;
   L->total_words = words;
   L->total_levels = levels;
-  L->count_blocks = CeilDiv(words, kCountThreads / 32);
+  // CountKept / EmitLattice run on a (word tiles of the largest pair, pairs) grid
+  int64_t max_pair_words = 0;
+  for (const FsaInfo &f : L->infos)
+    max_pair_words = std::max<int64_t>(max_pair_words, (int64_t)(f.tk + 1) * f.words);
+  L->tiles_per_pair = CeilDiv(max_pair_words, kCountThreads / 32);
+  L->count_blocks = (int32_t)std::min<int64_t>((int64_t)L->tiles_per_pair * a->num_fsas,
+                                               0x7fffffff);
   size_t off = 0;
   auto take = [&](size_t bytes) {
     size_t o = off;
@@ -106,19 +112,6 @@ __device__ __forceinline__ float DenseScore(const float *__restrict__ scores, in
                                             int32_t cols, int32_t label) {
   int32_t c = label + 1;
   return (c >= 0 && c < cols) ? __ldg(scores + row * cols + c) : -INFINITY;
-}
-
-// The pair owning flat word index w (infos sorted by word_off).
-__device__ __forceinline__ int32_t FindFsaByWord(const FsaInfo *__restrict__ infos, int32_t n,
-                                                 int64_t w) {
-  int32_t lo = 0, hi = n;
-  while (hi - lo > 1) {
-    int32_t mid = (lo + hi) >> 1;
-    if (infos[mid].word_off <= w) lo = mid; else hi = mid;
-  }
-  // skip pairs with zero words (empty graphs) that share the same offset
-  while (lo + 1 < n && infos[lo + 1].word_off <= w) ++lo;
-  return lo;
 }
 
 // ---------------------------------------------------------------------------
@@ -222,16 +215,17 @@ CountKept(const FsaInfo *__restrict__ infos, int32_t n, int64_t total_words,
           const float *__restrict__ scores, int32_t cols, const float *__restrict__ fwd,
           const float *__restrict__ bwd, const float *__restrict__ cutoffs,
           uint32_t *__restrict__ mask, int2 *__restrict__ counts,
-          unsigned long long *__restrict__ block_cand) {
+          unsigned long long *__restrict__ block_cand, int32_t fsa_base) {
   __shared__ unsigned long long cand_smem[kCountThreads / 32];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const int64_t w = (int64_t)blockIdx.x * (kCountThreads / 32) + warp;
+  const int32_t i = blockIdx.y + fsa_base;
+  const FsaInfo f = infos[i];
+  const int64_t rel = (int64_t)blockIdx.x * (kCountThreads / 32) + warp;
+  const int64_t w = f.word_off + rel;
+  const bool valid = rel < (int64_t)(f.tk + 1) * f.words;
   int32_t narcs = 0, cand = 0;
   uint32_t m = 0;
-  if (w < total_words) {
-    const int32_t i = FindFsaByWord(infos, n, w);
-    const FsaInfo f = infos[i];
-    const int64_t rel = w - f.word_off;
+  if (valid) {
     const int32_t t = (int32_t)(rel / f.words), s = (int32_t)(rel % f.words) * 32 + lane;
     const int32_t S = f.num_states;
     const float cutoff = cutoffs[i];
@@ -263,7 +257,7 @@ CountKept(const FsaInfo *__restrict__ infos, int32_t n, int64_t total_words,
     cand += __shfl_xor_sync(0xffffffffu, cand, d);
   }
   if (lane == 0) {
-    if (w < total_words) {
+    if (valid) {
       mask[w] = m;
       counts[w] = make_int2(__popc(m), narcs);
     }
@@ -273,7 +267,7 @@ CountKept(const FsaInfo *__restrict__ infos, int32_t n, int64_t total_words,
   if (threadIdx.x == 0) {
     unsigned long long c = 0;
     for (int k = 0; k < kCountThreads / 32; ++k) c += cand_smem[k];
-    block_cand[blockIdx.x] = c;
+    block_cand[(size_t)(blockIdx.y + fsa_base) * gridDim.x + blockIdx.x] = c;
   }
 }
 
@@ -282,12 +276,19 @@ CountKept(const FsaInfo *__restrict__ infos, int32_t n, int64_t total_words,
 __global__ void Totals(const int2 *__restrict__ bases, int64_t total_words,
                        const unsigned long long *__restrict__ block_cand, int32_t nblocks,
                        long long *__restrict__ totals) {
-  __shared__ unsigned long long red[256];
-  unsigned long long c = 0;
-  for (int32_t k = threadIdx.x; k < nblocks; k += blockDim.x) c += block_cand[k];
-  red[threadIdx.x] = c;
+  __shared__ unsigned long long red[1024];
+  unsigned long long c0 = 0, c1 = 0, c2 = 0, c3 = 0;
+  int32_t k = threadIdx.x;
+  for (; k + 3 * (int32_t)blockDim.x < nblocks; k += 4 * blockDim.x) {
+    c0 += block_cand[k];
+    c1 += block_cand[k + blockDim.x];
+    c2 += block_cand[k + 2 * blockDim.x];
+    c3 += block_cand[k + 3 * blockDim.x];
+  }
+  for (; k < nblocks; k += blockDim.x) c0 += block_cand[k];
+  red[threadIdx.x] = c0 + c1 + c2 + c3;
   __syncthreads();
-  for (int d = 128; d > 0; d >>= 1) {
+  for (int d = blockDim.x >> 1; d > 0; d >>= 1) {
     if (threadIdx.x < d) red[threadIdx.x] += red[threadIdx.x + d];
     __syncthreads();
   }
@@ -306,13 +307,13 @@ EmitLattice(const FsaInfo *__restrict__ infos, int32_t n, int64_t total_words,
             const float *__restrict__ scores, int32_t cols, const float *__restrict__ fwd,
             const float *__restrict__ bwd, const float *__restrict__ cutoffs,
             const uint32_t *__restrict__ mask, const int2 *__restrict__ bases,
-            k2b200_lattice_out out) {
+            k2b200_lattice_out out, int32_t fsa_base) {
   const int lane = threadIdx.x & 31;
-  const int64_t w = (int64_t)blockIdx.x * (blockDim.x / 32) + (threadIdx.x >> 5);
-  if (w >= total_words) return;
-  const int32_t i = FindFsaByWord(infos, n, w);
+  const int32_t i = blockIdx.y + fsa_base;
   const FsaInfo f = infos[i];
-  const int64_t rel = w - f.word_off;
+  const int64_t rel = (int64_t)blockIdx.x * (blockDim.x / 32) + (threadIdx.x >> 5);
+  if (rel >= (int64_t)(f.tk + 1) * f.words) return;
+  const int64_t w = f.word_off + rel;
   const int32_t t = (int32_t)(rel / f.words), wi = (int32_t)(rel % f.words), s = wi * 32 + lane;
   const int32_t S = f.num_states;
   const uint32_t m = mask[w];
@@ -498,11 +499,14 @@ int32_t k2b200_intersect_dense_prune(const k2b200_intersect_args *args, void *wo
     { Cutoffs<<<CeilDiv(args->num_fsas, 128), 128, 0, stream>>>(d_infos, args->num_fsas, fwd, bwd,
                                                               beam, cutoffs); NoteLaunch(); }
     if (L.total_words > 0)
-      { CountKept<<<L.count_blocks, kCountThreads, 0, stream>>>(
-          d_infos, args->num_fsas, L.total_words, arcs, args->a_row_splits2, args->scores,
-          args->cols, fwd, bwd, cutoffs, mask, counts, block_cand); NoteLaunch(); }
+      for (int32_t first = 0; first < args->num_fsas; first += 65535) {
+        dim3 grid(L.tiles_per_pair, std::min(args->num_fsas - first, 65535));
+        { CountKept<<<grid, kCountThreads, 0, stream>>>(
+            d_infos, args->num_fsas, L.total_words, arcs, args->a_row_splits2, args->scores,
+            args->cols, fwd, bwd, cutoffs, mask, counts, block_cand, first); NoteLaunch(); }
+      }
     K2B_FORWARD(ExclusiveSum2(counts, counts, L.total_words, scan_tmp, stream));
-    { Totals<<<1, 256, 0, stream>>>(counts, L.total_words, block_cand,
+    { Totals<<<1, 1024, 0, stream>>>(counts, L.total_words, block_cand,
                                   L.total_words > 0 ? L.count_blocks : 0, totals); NoteLaunch(); }
     K2B_CUDA_OK(cudaGetLastError());
     K2B_CUDA_OK(cudaMemcpyAsync(h_totals, totals, sizeof(h_totals), cudaMemcpyDeviceToHost,
@@ -555,14 +559,17 @@ int32_t k2b200_intersect_dense_emit(const k2b200_intersect_args *args, void *wor
       d_infos, args->num_fsas, L.total_words, (int32_t)L.total_levels,
       reinterpret_cast<const int2 *>(ws + L.off_counts), *out); NoteLaunch(); }
   if (L.total_words > 0)
-    { EmitLattice<<<CeilDiv(L.total_words, 8), 256, 0, stream>>>(
-        d_infos, args->num_fsas, L.total_words, reinterpret_cast<const Arc *>(args->a_arcs),
-        args->a_row_splits2, args->scores, args->cols,
-        reinterpret_cast<const float *>(ws + L.off_fwd),
-        reinterpret_cast<const float *>(ws + L.off_bwd),
-        reinterpret_cast<const float *>(ws + L.off_cutoffs),
-        reinterpret_cast<const uint32_t *>(ws + L.off_mask),
-        reinterpret_cast<const int2 *>(ws + L.off_counts), *out); NoteLaunch(); }
+    for (int32_t first = 0; first < args->num_fsas; first += 65535) {
+      dim3 grid(L.tiles_per_pair, std::min(args->num_fsas - first, 65535));
+      { EmitLattice<<<grid, 256, 0, stream>>>(
+          d_infos, args->num_fsas, L.total_words, reinterpret_cast<const Arc *>(args->a_arcs),
+          args->a_row_splits2, args->scores, args->cols,
+          reinterpret_cast<const float *>(ws + L.off_fwd),
+          reinterpret_cast<const float *>(ws + L.off_bwd),
+          reinterpret_cast<const float *>(ws + L.off_cutoffs),
+          reinterpret_cast<const uint32_t *>(ws + L.off_mask),
+          reinterpret_cast<const int2 *>(ws + L.off_counts), *out, first); NoteLaunch(); }
+    }
   K2B_CUDA_OK(cudaGetLastError());
   return kOk;
 }

@@ -391,7 +391,10 @@ ProbScoresStaged(k2b200_fsa_view v, const ProbArc *__restrict__ fwd_arcs,
   __shared__ int32_t bad_shared;
   if (tid == 0) {
     bad_shared = (nl > p.nl_cap);
-    for (int32_t s = 0; s < p.stages; ++s) MbarInit(&bars[s], 1);
+    for (int32_t s = 0; s < p.stages; ++s) {
+      MbarInit(&bars[s], 1);      // full: the producer's arrive + the copies' bytes
+      MbarInit(&bars[8 + s], 1);  // empty: one elected compute thread
+    }
     MbarInitFence();
   }
   __syncthreads();
@@ -415,51 +418,58 @@ ProbScoresStaged(k2b200_fsa_view v, const ProbArc *__restrict__ fwd_arcs,
   }
 
   const int32_t stages = p.stages;
-  // The last warp only feeds the ring; the others own the states.
+  // The last warp only feeds the ring (one thread of it); the others own the
+  // states.  full[slot] completes when a layer's copies have landed, empty[slot]
+  // when the compute warps are done reading it, so the producer runs up to
+  // `stages` layers ahead and is never on the layer-to-layer critical path.
   const int32_t nc = nt - 32;
-  const bool producer = tid >= nc;
+  uint64_t *full = bars, *empty = bars + 8;
   auto layer_of = [&](int32_t step) { return dir == 0 ? step : nl - 1 - step; };
-  auto issue = [&](int32_t step, int32_t slot) {  // one thread
-    if (step >= nl) return;
-    const int32_t li = layer_of(step);
-    const int32_t b = lvl[li], e = lvl[li + 1], ab = alvl[li], na = alvl[li + 1] - ab;
-    unsigned char *st = ring + (size_t)slot * p.stage_bytes;
-    int32_t *sp = reinterpret_cast<int32_t *>(st);
-    const int32_t lo = b & ~3;
-    int32_t hi = (e + 1 + 3) & ~3;
-    hi = hi < splits_aligned_end ? hi : splits_aligned_end;
-    hi = hi > lo ? hi : lo;
-    const unsigned bytes_splits = (unsigned)(hi - lo) * 4u, bytes_arcs = (unsigned)na * 16u;
-    MbarArriveExpectTx(&bars[slot], bytes_splits + bytes_arcs);
-    if (bytes_splits) BulkCopyG2S(sp, gsplits + lo, bytes_splits, &bars[slot]);
-    if (bytes_arcs) BulkCopyG2S(st + p.splits_bytes, garcs + ab, bytes_arcs, &bars[slot]);
-    for (int32_t k = hi; k <= e; ++k) sp[k - lo] = gsplits[k];  // at most 3 trailing ints
-  };
-  int32_t issue_slot = 0;
-  if (tid == nc)
-    for (int32_t step = 0; step < stages - 1; ++step) {
-      issue(step, issue_slot);
-      issue_slot = issue_slot + 1 == stages ? 0 : issue_slot + 1;
+  if (tid >= nc) {
+    if (tid != nc) return;
+    int32_t slot = 0;
+    unsigned empty_parity = 1;  // a fresh barrier counts as "previous phase complete"
+    for (int32_t step = 0; step < nl; ++step) {
+      if (!MbarTryWait(&empty[slot], empty_parity) &&
+          !MbarWaitBounded(&empty[slot], empty_parity)) {
+        atomicExch(status, 3);
+        return;
+      }
+      const int32_t li = layer_of(step);
+      const int32_t b = lvl[li], e = lvl[li + 1], ab = alvl[li], na = alvl[li + 1] - ab;
+      unsigned char *st = ring + (size_t)slot * p.stage_bytes;
+      int32_t *sp = reinterpret_cast<int32_t *>(st);
+      const int32_t lo = b & ~3;
+      int32_t hi = (e + 1 + 3) & ~3;
+      hi = hi < splits_aligned_end ? hi : splits_aligned_end;
+      hi = hi > lo ? hi : lo;
+      const unsigned bytes_splits = (unsigned)(hi - lo) * 4u, bytes_arcs = (unsigned)na * 16u;
+      for (int32_t k = hi; k <= e; ++k) sp[k - lo] = gsplits[k];  // at most 3 trailing ints
+      MbarArriveExpectTx(&full[slot], bytes_splits + bytes_arcs);
+      if (bytes_splits) BulkCopyG2S(sp, gsplits + lo, bytes_splits, &full[slot]);
+      if (bytes_arcs) BulkCopyG2S(st + p.splits_bytes, garcs + ab, bytes_arcs, &full[slot]);
+      slot = slot + 1 == stages ? 0 : slot + 1;
+      empty_parity ^= (slot == 0);
     }
+    return;
+  }
 
   const int32_t lg = p.lanes_log2, G = 1 << lg, g = tid & (G - 1), per_pass = nc >> lg;
-  int32_t slot = 0;
+  int32_t slot = 0, prev_slot = -1;
   unsigned parity = 0;
   for (int32_t step = 0; step < nl; ++step) {
-    if (!producer && !MbarTryWait(&bars[slot], parity) && !MbarWaitBounded(&bars[slot], parity)) {
-      // give the copies in flight one more bounded chance to land; the host-side
-      // fallback recomputes everything when it sees the status
+    if (!MbarTryWait(&full[slot], parity) && !MbarWaitBounded(&full[slot], parity)) {
       atomicExch(status, 2);
-      MbarWaitBounded(&bars[slot], parity);
       *reinterpret_cast<volatile int32_t *>(&bad_shared) = 2;
     }
-    __syncthreads();  // previous layer's scores are complete; the oldest slot is free
+    // compute warps only: the previous layer's scores are complete and nobody reads
+    // the previous slot any more
+    asm volatile("bar.sync 1, %0;" ::"r"(nc) : "memory");
     if (*reinterpret_cast<volatile int32_t *>(&bad_shared)) break;  // uniform: a wait gave up
-    if (producer) {
-      if (tid == nc) issue(step + stages - 1, issue_slot);
-      issue_slot = issue_slot + 1 == stages ? 0 : issue_slot + 1;
-      continue;
-    }
+    if (tid == 0 && prev_slot >= 0)
+      asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(SmemAddr(&empty[prev_slot]))
+                   : "memory");
+    prev_slot = slot;
     const int32_t li = layer_of(step);
     const int32_t b = lvl[li], w = lvl[li + 1] - b, ab = alvl[li];
     const int32_t other_base = step == 0 ? 0 : lvl[dir == 0 ? li - 1 : li + 1];

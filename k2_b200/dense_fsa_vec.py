@@ -8,6 +8,44 @@ torch index_select, so gradients w.r.t. `scores` flow back to `log_probs`.
 import numpy as np
 import torch
 
+from . import _lib
+
+
+class _DenseFsaVecFunction(torch.autograd.Function):
+    """scores = layout(log_probs) on the GPU: one kernel forward, one backward
+    (the CPU branch below keeps the reference's torch formulation)."""
+
+    @staticmethod
+    def forward(ctx, log_probs: torch.Tensor, segments: torch.Tensor,
+                row_splits: torch.Tensor, rows: int, overlapping: bool) -> torch.Tensor:
+        log_probs = log_probs.contiguous()
+        N, T, C = log_probs.shape
+        dev = log_probs.device
+        scores = torch.empty(rows, C + 1, dtype=torch.float32, device=dev)
+        with torch.cuda.device(dev):
+            _lib.check(_lib.lib.k2b200_dense_fsa_vec_fill(
+                _lib.ptr(log_probs), N, T, C, _lib.ptr(segments), _lib.ptr(row_splits),
+                segments.shape[0], _lib.ptr(scores), rows, _lib.stream_of(dev)))
+        ctx.save_for_backward(segments, row_splits)
+        ctx.shape = (N, T, C)
+        ctx.rows = rows
+        ctx.overlapping = overlapping
+        return scores
+
+    @staticmethod
+    def backward(ctx, grad_scores: torch.Tensor):
+        segments, row_splits = ctx.saved_tensors
+        N, T, C = ctx.shape
+        grad_scores = grad_scores.contiguous()
+        dev = grad_scores.device
+        grad = torch.empty(N, T, C, dtype=torch.float32, device=dev)
+        with torch.cuda.device(dev):
+            _lib.check(_lib.lib.k2b200_dense_fsa_vec_backward(
+                _lib.ptr(grad_scores), N, T, C, _lib.ptr(segments), _lib.ptr(row_splits),
+                segments.shape[0], ctx.rows, int(ctx.overlapping), _lib.ptr(grad),
+                _lib.stream_of(dev)))
+        return grad, None, None, None, None
+
 
 class DenseFsaVec(object):
 
@@ -22,33 +60,43 @@ class DenseFsaVec(object):
 
         N, T, C = log_probs.shape
         seg = supervision_segments.numpy().astype(np.int64)
-        indexes = []
-        last_frame_indexes = []
-        cur = 0
-        for segment_index, start_frame, duration in seg.tolist():
-            assert 0 <= segment_index < N
-            assert 0 <= start_frame < T
-            assert duration >= 0
-            assert start_frame + duration <= T + allow_truncate
-            end_frame = min(start_frame + duration, T)
-            duration = end_frame - start_frame
-            indexes.append(np.arange(start_frame, end_frame, dtype=np.int64) + segment_index * T)
-            indexes.append(np.zeros(1, dtype=np.int64))  # placeholder for the extra row
-            cur += duration
-            last_frame_indexes.append(cur)
-            cur += 1
-
-        device = log_probs.device
-        index = torch.from_numpy(np.concatenate(indexes)).to(device, non_blocking=True)
-        scores = torch.empty(cur, C + 1, dtype=log_probs.dtype, device=device)
-        scores[:, 1:] = log_probs.reshape(-1, C).index_select(0, index)
-        scores[:, 0] = float('-inf')
-        last = torch.tensor(last_frame_indexes, dtype=torch.int64).to(device, non_blocking=True)
-        scores[last] = torch.tensor([0] + [float('-inf')] * C, dtype=log_probs.dtype,
-                                    device=device)
-
+        assert np.all((seg[:, 0] >= 0) & (seg[:, 0] < N))
+        assert np.all((seg[:, 1] >= 0) & (seg[:, 1] < T))
+        assert np.all(seg[:, 2] >= 0)
+        assert np.all(seg[:, 1] + seg[:, 2] <= T + allow_truncate)
+        # durations after truncation; every segment gets one extra (final) row
+        dur = np.minimum(seg[:, 1] + seg[:, 2], T) - seg[:, 1]
         row_splits = np.zeros(seg.shape[0] + 1, dtype=np.int32)
-        row_splits[1:] = np.asarray(last_frame_indexes, dtype=np.int32) + 1
+        np.cumsum(dur + 1, out=row_splits[1:])
+        rows = int(row_splits[-1])
+        device = log_probs.device
+
+        if log_probs.is_cuda:
+            # one kernel writes the whole matrix; two segments that touch the same
+            # frame make the backward use atomic adds
+            first = seg[:, 0] * T + seg[:, 1]
+            order = np.argsort(first, kind="stable")
+            overlapping = bool(np.any((first + dur)[order][:-1] > first[order][1:]))
+            eff = np.stack([seg[:, 0], seg[:, 1], dur], axis=1).astype(np.int32)
+            meta = torch.from_numpy(np.concatenate([eff.reshape(-1), row_splits])).to(
+                device, non_blocking=True)
+            k3 = 3 * seg.shape[0]
+            scores = _DenseFsaVecFunction.apply(log_probs, meta[:k3].view(-1, 3), meta[k3:],
+                                                rows, overlapping)
+        else:
+            # host tensors (layout checks, graph preparation): the reference's own
+            # formulation with torch ops
+            last_frame_indexes = (row_splits[1:] - 1).astype(np.int64)
+            index = np.zeros(rows, dtype=np.int64)
+            for k in range(seg.shape[0]):
+                r0 = int(row_splits[k])
+                index[r0:r0 + int(dur[k])] = np.arange(seg[k, 1], seg[k, 1] + dur[k]) + \
+                    seg[k, 0] * T
+            scores = torch.empty(rows, C + 1, dtype=log_probs.dtype, device=device)
+            scores[:, 1:] = log_probs.reshape(-1, C).index_select(0, torch.from_numpy(index))
+            scores[:, 0] = float('-inf')
+            scores[torch.from_numpy(last_frame_indexes)] = torch.tensor(
+                [0] + [float('-inf')] * C, dtype=log_probs.dtype)
         self._init(scores, row_splits)
 
     def _init(self, scores: torch.Tensor, h_row_splits: np.ndarray) -> None:
