@@ -251,7 +251,8 @@ int32_t LaunchStagedScores(const k2b200_fsa_view *v, int32_t log_semiring, Real 
 // ---------------------------------------------------------------------------
 struct __align__(16) ProbArc {
   double f;       // mantissa of exp(score) in [1,2), 0 when score == -inf
-  int32_t other;  // idx01 of the arc's source (forward) or destination (backward) state
+  int32_t other;  // source (forward) / destination (backward) state, relative to the first
+                  // state of its layer
   int32_t k;      // binary exponent of exp(score)
 };
 static_assert(sizeof(ProbArc) == 16, "ProbArc must be 16 bytes");
@@ -278,6 +279,19 @@ __device__ __forceinline__ double Pow2NonPos(int32_t d) {
   return d < -1000 ? 0.0 : __longlong_as_double((long long)(1023 + d) << 52);
 }
 
+// x * 2^d for d <= 0 and x == 0 or 1 <= x < 2^20: an integer add on the exponent field.
+__device__ __forceinline__ double ScaleDown(double x, int32_t d) {
+  const int32_t hi = __double2hiint(x) + (d << 20);
+  return (d < -1000 || x == 0.0) ? 0.0 : __hiloint2double(hi, __double2loint(x));
+}
+
+// One state's score in shared memory: mantissa and exponent side by side.
+struct __align__(16) ProbState {
+  double m;
+  int32_t e;
+  int32_t pad;
+};
+
 // Normalise s >= 0 (a sum of a few numbers in [1,4) scaled by powers of two <= 1)
 // to m in [1,2) and add its exponent to *e.
 __device__ __forceinline__ double Renorm(double s, int32_t *e) {
@@ -285,10 +299,10 @@ __device__ __forceinline__ double Renorm(double s, int32_t *e) {
     *e = kZeroExp;
     return 0.0;
   }
-  long long bits = __double_as_longlong(s);
-  int32_t ex = (int32_t)((bits >> 52) & 0x7ff) - 1023;
+  const int32_t hi = __double2hiint(s);
+  const int32_t ex = (hi >> 20) - 1023;  // s > 0 and normal
   *e += ex;
-  return __longlong_as_double((bits & 0x800fffffffffffffLL) | (1023LL << 52));
+  return __hiloint2double(hi - (ex << 20), __double2loint(s));
 }
 
 // fwd_arcs[k] (incoming order) and bwd_arcs[a] (leaving order) from the arc scores.
@@ -297,17 +311,28 @@ __global__ void PrepareProbArcs(k2b200_fsa_view v, ProbArc *__restrict__ fwd_arc
   int32_t k = blockIdx.x * blockDim.x + threadIdx.x;
   if (k >= v.num_arcs) return;
   const Arc *arcs = reinterpret_cast<const Arc *>(v.arcs);
+  // index of state s (idx01, in FSA i) within its layer
+  auto local_index = [&](int32_t i, int32_t s) {
+    int32_t lo = v.level_offsets[i], hi = v.level_offsets[i + 1];
+    while (hi - lo > 1) {
+      const int32_t mid = (lo + hi) >> 1;
+      if (v.level_splits[mid] <= s) lo = mid; else hi = mid;
+    }
+    return s - v.level_splits[lo];
+  };
   if (bwd_arcs) {
     Arc arc = arcs[k];
     ProbArc p;
     ExpToMantExp(arc.score, &p.f, &p.k);
-    p.other = v.row_splits1[v.row_ids1[v.row_ids2[k]]] + arc.dest;
+    const int32_t i = v.row_ids1[v.row_ids2[k]];
+    p.other = local_index(i, v.row_splits1[i] + arc.dest);
     bwd_arcs[k] = p;
   }
   if (fwd_arcs) {
     ProbArc p;
     ExpToMantExp(v.in_score[k], &p.f, &p.k);
-    p.other = v.in_src[k];
+    const int32_t src = v.in_src[k];
+    p.other = local_index(v.row_ids1[src], src);
     fwd_arcs[k] = p;
   }
 }
@@ -343,7 +368,7 @@ static ProbPlan PlanProb(const k2b200_fsa_view *v) {
   p.stage_bytes = p.splits_bytes + p.maxa * 16;
   size_t fixed = 128                                      // mbarriers
                  + 8 * (size_t)((p.nl_cap + 1 + 3) & ~3)  // layer / arc boundaries
-                 + 2 * (size_t)p.maxw * 12 + 16;          // mantissa + exponent ping-pong
+                 + 2 * (size_t)p.maxw * 16 + 16;          // (mantissa, exponent) ping-pong
   if (fixed + 2 * (size_t)p.stage_bytes > kStagedSmemBudget) return p;
   p.stages = (int32_t)std::min<size_t>(8, (kStagedSmemBudget - fixed) / p.stage_bytes);
   p.bytes = fixed + (size_t)p.stage_bytes * p.stages;
@@ -379,10 +404,8 @@ ProbScoresStaged(k2b200_fsa_view v, const ProbArc *__restrict__ fwd_arcs,
   const int32_t lvl_ints = (p.nl_cap + 1 + 3) & ~3;
   int32_t *lvl = reinterpret_cast<int32_t *>(smem_raw + 128);
   int32_t *alvl = lvl + lvl_ints;
-  double *mant = reinterpret_cast<double *>(alvl + lvl_ints);      // [2][maxw]
-  int32_t *expo = reinterpret_cast<int32_t *>(mant + 2 * p.maxw);  // [2][maxw]
-  unsigned char *ring = reinterpret_cast<unsigned char *>(
-      (reinterpret_cast<uintptr_t>(expo + 2 * p.maxw) + 15) & ~(uintptr_t)15);
+  ProbState *pstate = reinterpret_cast<ProbState *>(alvl + lvl_ints);  // [2][maxw]
+  unsigned char *ring = reinterpret_cast<unsigned char *>(pstate + 2 * p.maxw);
   const int32_t *gsplits = dir == 0 ? v.in_splits : v.row_splits2;
   const ProbArc *garcs = dir == 0 ? fwd_arcs : bwd_arcs;
   // last 4-int boundary inside the splits array (num_states + 1 entries)
@@ -457,6 +480,9 @@ ProbScoresStaged(k2b200_fsa_view v, const ProbArc *__restrict__ fwd_arcs,
   const int32_t lg = p.lanes_log2, G = 1 << lg, g = tid & (G - 1), per_pass = nc >> lg;
   int32_t slot = 0, prev_slot = -1;
   unsigned parity = 0;
+  // first state of the layer handled in the previous step (the layer the arcs of
+  // this step come from / lead to) and, walking forward, of the current layer
+  int32_t edge = dir == 0 ? lvl[0] : lvl[nl];
   for (int32_t step = 0; step < nl; ++step) {
     if (!MbarTryWait(&full[slot], parity) && !MbarWaitBounded(&full[slot], parity)) {
       atomicExch(status, 2);
@@ -470,18 +496,26 @@ ProbScoresStaged(k2b200_fsa_view v, const ProbArc *__restrict__ fwd_arcs,
       asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(SmemAddr(&empty[prev_slot]))
                    : "memory");
     prev_slot = slot;
-    const int32_t li = layer_of(step);
-    const int32_t b = lvl[li], w = lvl[li + 1] - b, ab = alvl[li];
-    const int32_t other_base = step == 0 ? 0 : lvl[dir == 0 ? li - 1 : li + 1];
+    int32_t b, w, ab;
+    if (dir == 0) {
+      b = edge;
+      edge = lvl[step + 1];
+      w = edge - b;
+      ab = alvl[step];
+    } else {
+      const int32_t li = nl - 1 - step;
+      b = lvl[li];
+      w = edge - b;
+      edge = b;
+      ab = alvl[li];
+    }
     const unsigned char *st = ring + (size_t)slot * p.stage_bytes;
     const int32_t *sp = reinterpret_cast<const int32_t *>(st) + (b & 3);
     const ProbArc *body = reinterpret_cast<const ProbArc *>(st + p.splits_bytes);
     slot = slot + 1 == stages ? 0 : slot + 1;
     parity ^= (slot == 0);
-    const double *pm = mant + ((step + 1) & 1) * p.maxw;
-    const int32_t *pe = expo + ((step + 1) & 1) * p.maxw;
-    double *cm = mant + (step & 1) * p.maxw;
-    int32_t *ce = expo + (step & 1) * p.maxw;
+    const ProbState *prev = pstate + ((step + 1) & 1) * p.maxw;
+    ProbState *cur = pstate + (step & 1) * p.maxw;
     for (int32_t j0 = 0; j0 < w; j0 += per_pass) {
       const int32_t j = j0 + (tid >> lg);
       int32_t k0 = 0, k1 = 0;
@@ -490,49 +524,42 @@ ProbScoresStaged(k2b200_fsa_view v, const ProbArc *__restrict__ fwd_arcs,
         k1 = sp[j + 1] - ab;
       }
       // Running sum of the terms m_prev * f * 2^(e_prev + k), kept as sum * 2^E with E
-      // the largest exponent met so far; four arcs per trip so that their loads and
+      // the largest exponent met so far; two arcs per trip so that their loads and
       // multiplies overlap.
       double sum = 0.0;
       int32_t E = kZeroExp;
-      for (int32_t k = k0 + 4 * g; k < k1; k += 4 * G) {
-        double t[4];
-        int32_t te[4];
-#pragma unroll
-        for (int u = 0; u < 4; ++u) {
-          const int32_t kk = k + u < k1 ? k + u : k1 - 1;
-          const ProbArc a = body[kk];
-          const int32_t o = a.other - other_base;
-          const double tv = k + u < k1 ? pm[o] * a.f : 0.0;
-          t[u] = tv;
-          te[u] = tv != 0.0 ? pe[o] + a.k : kZeroExp;
-        }
-        int32_t En = E;
-#pragma unroll
-        for (int u = 0; u < 4; ++u) En = te[u] > En ? te[u] : En;
-        sum *= Pow2NonPos(E - En);
-#pragma unroll
-        for (int u = 0; u < 4; ++u) sum += t[u] * Pow2NonPos(te[u] - En);
+      for (int32_t k = k0 + 2 * g; k < k1; k += 2 * G) {
+        const bool two = k + 1 < k1;
+        const ProbArc a0 = body[k], a1 = body[two ? k + 1 : k];
+        const ProbState s0 = prev[a0.other], s1 = prev[a1.other];
+        const double t0 = s0.m * a0.f, t1 = two ? s1.m * a1.f : 0.0;
+        const int32_t e0 = t0 != 0.0 ? s0.e + a0.k : kZeroExp;
+        const int32_t e1 = t1 != 0.0 ? s1.e + a1.k : kZeroExp;
+        int32_t En = e0 > e1 ? e0 : e1;
+        En = E > En ? E : En;
+        sum = ScaleDown(sum, E - En) + ScaleDown(t0, e0 - En) + ScaleDown(t1, e1 - En);
         E = En;
       }
       for (int32_t d = G >> 1; d > 0; d >>= 1) {
         const int32_t Eo = __shfl_xor_sync(0xffffffffu, E, d);
         const double so = __shfl_xor_sync(0xffffffffu, sum, d);
         const int32_t En = Eo > E ? Eo : E;
-        sum = sum * Pow2NonPos(E - En) + so * Pow2NonPos(Eo - En);
+        sum = ScaleDown(sum, E - En) + ScaleDown(so, Eo - En);
         E = En;
       }
       if (j < w && g == 0) {
         const int32_t s = b + j;
-        int32_t e = E;
-        double m = Renorm(sum, &e);
-        if (m == 0.0 && s == (dir == 0 ? s_begin : s_end - 1)) {  // start / final state: 1
-          m = 1.0;
-          e = 0;
+        ProbState r;
+        r.e = E;
+        r.m = Renorm(sum, &r.e);
+        r.pad = 0;
+        if (r.m == 0.0 && s == (dir == 0 ? s_begin : s_end - 1)) {  // start / final state: 1
+          r.m = 1.0;
+          r.e = 0;
         }
-        cm[j] = m;
-        ce[j] = e;
-        mo[s] = m;
-        eo[s] = e;
+        cur[j] = r;
+        mo[s] = r.m;
+        eo[s] = r.e;
       }
     }
   }
