@@ -20,7 +20,8 @@
 
 namespace k2b {
 
-constexpr int kCountThreads = 256;  // 8 words per block
+constexpr int kCountThreads = 256;
+constexpr int kWordsPerCtaHost = 4 * (kCountThreads / 32);  // == kWordsPerCta below
 
 static int32_t MakeLayout(const k2b200_intersect_args *a, Layout *L) {
   K2B_REQUIRE(a != nullptr, "args is NULL");
@@ -83,7 +84,8 @@ static int32_t MakeLayout(const k2b200_intersect_args *a, Layout *L) {
   int64_t max_pair_words = 0;
   for (const FsaInfo &f : L->infos)
     max_pair_words = std::max<int64_t>(max_pair_words, (int64_t)(f.tk + 1) * f.words);
-  L->tiles_per_pair = CeilDiv(max_pair_words, kCountThreads / 32);
+  L->tiles_per_pair = CeilDiv(max_pair_words, kWordsPerCtaHost);
+  L->emit_tiles_per_pair = CeilDiv(max_pair_words, 8);
   L->count_blocks = (int32_t)std::min<int64_t>((int64_t)L->tiles_per_pair * a->num_fsas,
                                                0x7fffffff);
   size_t off = 0;
@@ -208,7 +210,12 @@ __device__ __forceinline__ bool KeepArc(const Arc &arc, float fs, const float *f
   return __fadd_rn(__fadd_rn(fs, sc), bd) > cutoff;
 }
 
-// One warp per 32-state word of the (pair, t, state) grid.
+// Each warp handles kWordsPerWarp consecutive 32-state words of the (pair, t, state)
+// grid; the loads of all its words are issued before any is used.  Most words hold
+// no surviving state and cost two loads, a ballot and one 12-byte store.
+constexpr int kWordsPerWarp = 4;
+constexpr int kWordsPerCta = kWordsPerWarp * (kCountThreads / 32);
+
 __global__ void __launch_bounds__(kCountThreads)
 CountKept(const FsaInfo *__restrict__ infos, int32_t n, int64_t total_words,
           const Arc *__restrict__ arcs, const int32_t *__restrict__ a_row_splits2,
@@ -216,59 +223,76 @@ CountKept(const FsaInfo *__restrict__ infos, int32_t n, int64_t total_words,
           const float *__restrict__ bwd, const float *__restrict__ cutoffs,
           uint32_t *__restrict__ mask, int2 *__restrict__ counts,
           unsigned long long *__restrict__ block_cand, int32_t fsa_base) {
-  __shared__ unsigned long long cand_smem[kCountThreads / 32];
+  __shared__ unsigned long long cand_smem;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int32_t i = blockIdx.y + fsa_base;
   const FsaInfo f = infos[i];
-  const int64_t rel = (int64_t)blockIdx.x * (kCountThreads / 32) + warp;
-  const int64_t w = f.word_off + rel;
-  const bool valid = rel < (int64_t)(f.tk + 1) * f.words;
-  int32_t narcs = 0, cand = 0;
-  uint32_t m = 0;
-  if (valid) {
-    const int32_t t = (int32_t)(rel / f.words), s = (int32_t)(rel % f.words) * 32 + lane;
-    const int32_t S = f.num_states;
-    const float cutoff = cutoffs[i];
-    const float *fwd0 = fwd + f.grid_off + (int64_t)t * S, *bwd0 = bwd + f.grid_off + (int64_t)t * S;
-    bool keep = false;
-    float fs = 0;
-    if (s < S) {
-      fs = fwd0[s];
-      keep = __fadd_rn(fs, bwd0[s]) > cutoff;
+  const int64_t pair_words = (int64_t)(f.tk + 1) * f.words;
+  const int64_t rel0 = (int64_t)blockIdx.x * kWordsPerCta + (int64_t)warp * kWordsPerWarp;
+  if (threadIdx.x == 0) cand_smem = 0;
+  __syncthreads();
+  const int32_t S = f.num_states;
+  const float cutoff = cutoffs[i];
+  const float *fgrid = fwd + f.grid_off, *bgrid = bwd + f.grid_off;
+  float fs[kWordsPerWarp], bs[kWordsPerWarp];
+  int32_t ts[kWordsPerWarp], ss[kWordsPerWarp];
+#pragma unroll
+  for (int u = 0; u < kWordsPerWarp; ++u) {
+    const int64_t rel = rel0 + u;
+    const int32_t t = (int32_t)(rel / f.words), s = (int32_t)(rel - (int64_t)t * f.words) * 32 + lane;
+    ts[u] = t;
+    ss[u] = s;
+    const bool in = rel < pair_words && s < S;
+    fs[u] = in ? fgrid[(int64_t)t * S + s] : -INFINITY;
+    bs[u] = in ? bgrid[(int64_t)t * S + s] : -INFINITY;
+  }
+  int32_t cand = 0;
+  bool any = false;
+#pragma unroll
+  for (int u = 0; u < kWordsPerWarp; ++u) {
+    const int64_t rel = rel0 + u;
+    if (rel >= pair_words) break;  // warp-uniform
+    const bool keep = __fadd_rn(fs[u], bs[u]) > cutoff;
+    const uint32_t m = __ballot_sync(0xffffffffu, keep);
+    const int64_t w = f.word_off + rel;
+    if (m == 0) {
+      if (lane == 0) {
+        mask[w] = 0;
+        counts[w] = make_int2(0, 0);
+      }
+      continue;
     }
-    m = __ballot_sync(0xffffffffu, keep);
+    any = true;
+    int32_t narcs = 0;
     if (keep) {
-      const int32_t idx01 = f.state_off + s, a0 = a_row_splits2[idx01],
+      const int32_t t = ts[u];
+      const int32_t idx01 = f.state_off + ss[u], a0 = a_row_splits2[idx01],
                     a1 = a_row_splits2[idx01 + 1];
-      cand = a1 - a0;
+      cand += a1 - a0;
       if (t < f.tk) {
-        const float *fwd1 = fwd0 + S, *bwd1 = bwd0 + S;
+        const float *fwd1 = fgrid + (int64_t)(t + 1) * S, *bwd1 = bgrid + (int64_t)(t + 1) * S;
         const int64_t row = (int64_t)f.row0 + t;
         for (int32_t a = a0; a < a1; ++a) {
           float sc;
-          narcs += KeepArc(arcs[a], fs, fwd1, bwd1, scores, row, cols, cutoff, &sc);
+          narcs += KeepArc(arcs[a], fs[u], fwd1, bwd1, scores, row, cols, cutoff, &sc);
         }
       }
     }
-  }
 #pragma unroll
-  for (int d = 16; d > 0; d >>= 1) {
-    narcs += __shfl_xor_sync(0xffffffffu, narcs, d);
-    cand += __shfl_xor_sync(0xffffffffu, cand, d);
-  }
-  if (lane == 0) {
-    if (valid) {
+    for (int d = 16; d > 0; d >>= 1) narcs += __shfl_xor_sync(0xffffffffu, narcs, d);
+    if (lane == 0) {
       mask[w] = m;
       counts[w] = make_int2(__popc(m), narcs);
     }
-    cand_smem[warp] = (unsigned long long)cand;
+  }
+  if (any) {  // warp-uniform
+#pragma unroll
+    for (int d = 16; d > 0; d >>= 1) cand += __shfl_xor_sync(0xffffffffu, cand, d);
+    if (lane == 0 && cand) atomicAdd(&cand_smem, (unsigned long long)cand);
   }
   __syncthreads();
-  if (threadIdx.x == 0) {
-    unsigned long long c = 0;
-    for (int k = 0; k < kCountThreads / 32; ++k) c += cand_smem[k];
-    block_cand[(size_t)(blockIdx.y + fsa_base) * gridDim.x + blockIdx.x] = c;
-  }
+  if (threadIdx.x == 0)
+    block_cand[(size_t)(blockIdx.y + fsa_base) * gridDim.x + blockIdx.x] = cand_smem;
 }
 
 // totals[0] = kept states, [1] = kept arcs, [2] = sum over kept states of their
@@ -315,8 +339,9 @@ EmitLattice(const FsaInfo *__restrict__ infos, int32_t n, int64_t total_words,
   if (rel >= (int64_t)(f.tk + 1) * f.words) return;
   const int64_t w = f.word_off + rel;
   const int32_t t = (int32_t)(rel / f.words), wi = (int32_t)(rel % f.words), s = wi * 32 + lane;
-  const int32_t S = f.num_states;
   const uint32_t m = mask[w];
+  if (m == 0 && wi != 0) return;  // nothing kept in this word and no layer boundary to record
+  const int32_t S = f.num_states;
   const int2 base = bases[w];
   const int32_t fsa_first_state = bases[f.word_off].x;
 
@@ -560,7 +585,7 @@ int32_t k2b200_intersect_dense_emit(const k2b200_intersect_args *args, void *wor
       reinterpret_cast<const int2 *>(ws + L.off_counts), *out); NoteLaunch(); }
   if (L.total_words > 0)
     for (int32_t first = 0; first < args->num_fsas; first += 65535) {
-      dim3 grid(L.tiles_per_pair, std::min(args->num_fsas - first, 65535));
+      dim3 grid(L.emit_tiles_per_pair, std::min(args->num_fsas - first, 65535));
       { EmitLattice<<<grid, 256, 0, stream>>>(
           d_infos, args->num_fsas, L.total_words, reinterpret_cast<const Arc *>(args->a_arcs),
           args->a_row_splits2, args->scores, args->cols,

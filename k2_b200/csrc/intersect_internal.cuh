@@ -28,7 +28,7 @@ struct Layout {
   // byte offsets into the workspace
   size_t off_infos, off_cutoffs, off_fwd, off_bwd, off_mask, off_counts, off_scan_tmp,
       off_block_cand, off_totals, total_bytes;
-  int32_t count_blocks, tiles_per_pair;
+  int32_t count_blocks, tiles_per_pair, emit_tiles_per_pair;
 };
 
 // viterbi_persistent.cu
