@@ -21,7 +21,7 @@
 namespace k2b {
 
 constexpr int kCountThreads = 256;
-constexpr int kWordsPerCtaHost = 4 * (kCountThreads / 32);  // == kWordsPerCta below
+constexpr int kWordsPerCtaHost = 4 * 4 * (kCountThreads / 32);  // == kWordsPerCta below
 
 static int32_t MakeLayout(const k2b200_intersect_args *a, Layout *L) {
   K2B_REQUIRE(a != nullptr, "args is NULL");
@@ -85,7 +85,7 @@ static int32_t MakeLayout(const k2b200_intersect_args *a, Layout *L) {
   for (const FsaInfo &f : L->infos)
     max_pair_words = std::max<int64_t>(max_pair_words, (int64_t)(f.tk + 1) * f.words);
   L->tiles_per_pair = CeilDiv(max_pair_words, kWordsPerCtaHost);
-  L->emit_tiles_per_pair = CeilDiv(max_pair_words, 8);
+  L->emit_tiles_per_pair = CeilDiv(max_pair_words, 16 * 8);  // kEmitWordsPerCta
   L->count_blocks = (int32_t)std::min<int64_t>((int64_t)L->tiles_per_pair * a->num_fsas,
                                                0x7fffffff);
   size_t off = 0;
@@ -214,7 +214,8 @@ __device__ __forceinline__ bool KeepArc(const Arc &arc, float fs, const float *f
 // grid; the loads of all its words are issued before any is used.  Most words hold
 // no surviving state and cost two loads, a ballot and one 12-byte store.
 constexpr int kWordsPerWarp = 4;
-constexpr int kWordsPerCta = kWordsPerWarp * (kCountThreads / 32);
+constexpr int kCountRounds = 4;
+constexpr int kWordsPerCta = kCountRounds * kWordsPerWarp * (kCountThreads / 32);
 
 __global__ void __launch_bounds__(kCountThreads)
 CountKept(const FsaInfo *__restrict__ infos, int32_t n, int64_t total_words,
@@ -228,12 +229,17 @@ CountKept(const FsaInfo *__restrict__ infos, int32_t n, int64_t total_words,
   const int32_t i = blockIdx.y + fsa_base;
   const FsaInfo f = infos[i];
   const int64_t pair_words = (int64_t)(f.tk + 1) * f.words;
-  const int64_t rel0 = (int64_t)blockIdx.x * kWordsPerCta + (int64_t)warp * kWordsPerWarp;
   if (threadIdx.x == 0) cand_smem = 0;
   __syncthreads();
   const int32_t S = f.num_states;
   const float cutoff = cutoffs[i];
   const float *fgrid = fwd + f.grid_off, *bgrid = bwd + f.grid_off;
+  int32_t cand = 0;
+  bool any = false;
+  for (int round = 0; round < kCountRounds; ++round) {
+  const int64_t rel0 = (int64_t)blockIdx.x * kWordsPerCta +
+                       ((int64_t)round * (kCountThreads / 32) + warp) * kWordsPerWarp;
+  if (rel0 >= pair_words) break;  // warp-uniform
   float fs[kWordsPerWarp], bs[kWordsPerWarp];
   int32_t ts[kWordsPerWarp], ss[kWordsPerWarp];
 #pragma unroll
@@ -246,8 +252,6 @@ CountKept(const FsaInfo *__restrict__ infos, int32_t n, int64_t total_words,
     fs[u] = in ? fgrid[(int64_t)t * S + s] : -INFINITY;
     bs[u] = in ? bgrid[(int64_t)t * S + s] : -INFINITY;
   }
-  int32_t cand = 0;
-  bool any = false;
 #pragma unroll
   for (int u = 0; u < kWordsPerWarp; ++u) {
     const int64_t rel = rel0 + u;
@@ -285,6 +289,7 @@ CountKept(const FsaInfo *__restrict__ infos, int32_t n, int64_t total_words,
       counts[w] = make_int2(__popc(m), narcs);
     }
   }
+  }  // rounds
   if (any) {  // warp-uniform
 #pragma unroll
     for (int d = 16; d > 0; d >>= 1) cand += __shfl_xor_sync(0xffffffffu, cand, d);
@@ -324,19 +329,13 @@ __global__ void Totals(const int2 *__restrict__ bases, int64_t total_words,
   }
 }
 
-// One warp per word: writes the states of the word and the arcs leaving them.
-__global__ void __launch_bounds__(256)
-EmitLattice(const FsaInfo *__restrict__ infos, int32_t n, int64_t total_words,
-            const Arc *__restrict__ arcs, const int32_t *__restrict__ a_row_splits2,
-            const float *__restrict__ scores, int32_t cols, const float *__restrict__ fwd,
-            const float *__restrict__ bwd, const float *__restrict__ cutoffs,
-            const uint32_t *__restrict__ mask, const int2 *__restrict__ bases,
-            k2b200_lattice_out out, int32_t fsa_base) {
-  const int lane = threadIdx.x & 31;
-  const int32_t i = blockIdx.y + fsa_base;
-  const FsaInfo f = infos[i];
-  const int64_t rel = (int64_t)blockIdx.x * (blockDim.x / 32) + (threadIdx.x >> 5);
-  if (rel >= (int64_t)(f.tk + 1) * f.words) return;
+// One warp writes the states of word `rel` of pair i and the arcs leaving them.
+__device__ __forceinline__ void
+EmitWord(const FsaInfo &f, int32_t i, int32_t n, int64_t rel, float cutoff, int lane,
+         const Arc *__restrict__ arcs, const int32_t *__restrict__ a_row_splits2,
+         const float *__restrict__ scores, int32_t cols, const float *__restrict__ fwd,
+         const float *__restrict__ bwd, const uint32_t *__restrict__ mask,
+         const int2 *__restrict__ bases, const k2b200_lattice_out &out) {
   const int64_t w = f.word_off + rel;
   const int32_t t = (int32_t)(rel / f.words), wi = (int32_t)(rel % f.words), s = wi * 32 + lane;
   const uint32_t m = mask[w];
@@ -355,7 +354,6 @@ EmitLattice(const FsaInfo *__restrict__ infos, int32_t n, int64_t total_words,
     }
   }
   const bool keep = (m >> lane) & 1u;
-  const float cutoff = cutoffs[i];
   const float *fwd0 = fwd + f.grid_off + (int64_t)t * S, *bwd0 = bwd + f.grid_off + (int64_t)t * S;
   const float *fwd1 = fwd0 + S, *bwd1 = bwd0 + S;
   const int64_t row = (int64_t)f.row0 + t;
@@ -404,6 +402,34 @@ EmitLattice(const FsaInfo *__restrict__ infos, int32_t n, int64_t total_words,
     if (out.arc_map_a) out.arc_map_a[pos] = a;
     if (out.arc_map_b) out.arc_map_b[pos] = (int32_t)(row * cols + (arc.label + 1));
     ++pos;
+  }
+}
+
+
+constexpr int kEmitWordsPerWarp = 16;
+constexpr int kEmitWordsPerCta = kEmitWordsPerWarp * 8;
+
+// Each warp walks kEmitWordsPerWarp consecutive words (few, fat CTAs: most words
+// hold nothing and are skipped after one load).
+__global__ void __launch_bounds__(256)
+EmitLattice(const FsaInfo *__restrict__ infos, int32_t n, int64_t total_words,
+            const Arc *__restrict__ arcs, const int32_t *__restrict__ a_row_splits2,
+            const float *__restrict__ scores, int32_t cols, const float *__restrict__ fwd,
+            const float *__restrict__ bwd, const float *__restrict__ cutoffs,
+            const uint32_t *__restrict__ mask, const int2 *__restrict__ bases,
+            k2b200_lattice_out out, int32_t fsa_base) {
+  const int lane = threadIdx.x & 31;
+  const int32_t i = blockIdx.y + fsa_base;
+  const FsaInfo f = infos[i];
+  const float cutoff = cutoffs[i];
+  const int64_t pair_words = (int64_t)(f.tk + 1) * f.words;
+  const int64_t rel0 =
+      ((int64_t)blockIdx.x * (blockDim.x / 32) + (threadIdx.x >> 5)) * kEmitWordsPerWarp;
+  for (int u = 0; u < kEmitWordsPerWarp; ++u) {
+    const int64_t rel = rel0 + u;
+    if (rel >= pair_words) return;
+    EmitWord(f, i, n, rel, cutoff, lane, arcs, a_row_splits2, scores, cols, fwd, bwd, mask, bases,
+             out);
   }
 }
 
