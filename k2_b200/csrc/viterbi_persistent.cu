@@ -139,15 +139,14 @@ PersistentViterbi(const FsaInfo *__restrict__ infos, const Arc *__restrict__ arc
 // shared-memory reads of the previous frame's scores and a few adds.  Unused arc
 // slots carry a score of -inf and never win the max.
 // ---------------------------------------------------------------------------
-constexpr int kRegMaxDeg = 4;
-constexpr int kRegPrefetch = 8;
+constexpr int kRegMaxDeg = 4;  // largest degree any instantiation handles
 
 bool RegisterViterbiFits(const Layout &L, const k2b200_intersect_args *a) {
   return a->a_max_degree > 0 && a->a_max_degree <= kRegMaxDeg && L.max_states <= 1024 &&
          a->num_fsas <= 65535;
 }
 
-template <int kMaxThreads>
+template <int kMaxThreads, int kDeg, int kRegPrefetch>
 __global__ void __launch_bounds__(kMaxThreads)
 RegisterViterbi(const FsaInfo *__restrict__ infos, const Arc *__restrict__ arcs,
                 const int32_t *__restrict__ a_row_splits2, const int32_t *__restrict__ in_splits,
@@ -161,10 +160,10 @@ RegisterViterbi(const FsaInfo *__restrict__ infos, const Arc *__restrict__ arcs,
   const int32_t s = threadIdx.x;
   const bool active = s < S;
 
-  int32_t other[kRegMaxDeg], col[kRegMaxDeg];
-  float w[kRegMaxDeg];
+  int32_t other[kDeg], col[kDeg];
+  float w[kDeg];
 #pragma unroll
-  for (int j = 0; j < kRegMaxDeg; ++j) {
+  for (int j = 0; j < kDeg; ++j) {
     other[j] = 0;
     col[j] = 0;
     w[j] = -INFINITY;
@@ -173,7 +172,7 @@ RegisterViterbi(const FsaInfo *__restrict__ infos, const Arc *__restrict__ arcs,
     const int32_t *splits = dir == 0 ? in_splits : a_row_splits2;
     const int32_t a0 = splits[f.state_off + s], n = splits[f.state_off + s + 1] - a0;
 #pragma unroll
-    for (int j = 0; j < kRegMaxDeg; ++j) {
+    for (int j = 0; j < kDeg; ++j) {
       if (j < n) {
         const Arc arc = arcs[dir == 0 ? in_arcs[a0 + j] : a0 + j];
         other[j] = dir == 0 ? arc.src : arc.dest;
@@ -191,12 +190,12 @@ RegisterViterbi(const FsaInfo *__restrict__ infos, const Arc *__restrict__ arcs,
     step = step > Tk ? Tk : step;
     return dir == 0 ? step - 1 : Tk - step;
   };
-  float x[kRegMaxDeg][kRegPrefetch];
+  float x[kDeg][kRegPrefetch];
 #pragma unroll
   for (int d = 0; d < kRegPrefetch; ++d) {
     const int32_t r = row_of(1 + d) * cols;
 #pragma unroll
-    for (int j = 0; j < kRegMaxDeg; ++j) x[j][d] = __ldg(base + r + col[j]);
+    for (int j = 0; j < kDeg; ++j) x[j][d] = __ldg(base + r + col[j]);
   }
   float *grid = (dir == 0 ? fwd : bwd) + f.grid_off;
   {
@@ -213,13 +212,13 @@ RegisterViterbi(const FsaInfo *__restrict__ infos, const Arc *__restrict__ arcs,
       const float *cur = buf[(t - 1) & 1];
       float best = -INFINITY;
 #pragma unroll
-      for (int j = 0; j < kRegMaxDeg; ++j) {
+      for (int j = 0; j < kDeg; ++j) {
         const float v = __fadd_rn(__fadd_rn(cur[other[j]], w[j]), x[j][u]);
         best = v > best ? v : best;
       }
       const int32_t r = row_of(t + kRegPrefetch) * cols;
 #pragma unroll
-      for (int j = 0; j < kRegMaxDeg; ++j) x[j][u] = __ldg(base + r + col[j]);
+      for (int j = 0; j < kDeg; ++j) x[j][u] = __ldg(base + r + col[j]);
       buf[t & 1][s] = best;
       if (active) grid[(int64_t)(dir == 0 ? t : Tk - t) * S + s] = best;
     }
@@ -232,14 +231,16 @@ int32_t LaunchRegisterViterbi(const Layout &L, const k2b200_intersect_args *a,
   int32_t threads = std::max(32, (L.max_states + 31) / 32 * 32);
   dim3 grid(2, a->num_fsas);
   const Arc *arcs = reinterpret_cast<const Arc *>(a->a_arcs);
-  if (threads <= 512)
-    { RegisterViterbi<512><<<grid, threads, 0, stream>>>(d_infos, arcs, a->a_row_splits2,
-                                                        a->a_in_splits, a->a_in_arcs, a->scores,
-                                                        a->cols, fwd, bwd); NoteLaunch(); }
-  else
-    { RegisterViterbi<1024><<<grid, threads, 0, stream>>>(d_infos, arcs, a->a_row_splits2,
-                                                         a->a_in_splits, a->a_in_arcs, a->scores,
-                                                         a->cols, fwd, bwd); NoteLaunch(); }
+#define K2B_LAUNCH_REG(MAXT, DEG, PF)                                                      \
+  { RegisterViterbi<MAXT, DEG, PF><<<grid, threads, 0, stream>>>(                         \
+        d_infos, arcs, a->a_row_splits2, a->a_in_splits, a->a_in_arcs, a->scores, a->cols, \
+        fwd, bwd); NoteLaunch(); }
+  if (threads <= 512) {
+    if (a->a_max_degree <= 3) K2B_LAUNCH_REG(512, 3, 12) else K2B_LAUNCH_REG(512, 4, 8)
+  } else {
+    if (a->a_max_degree <= 3) K2B_LAUNCH_REG(1024, 3, 8) else K2B_LAUNCH_REG(1024, 4, 6)
+  }
+#undef K2B_LAUNCH_REG
   K2B_CUDA_OK(cudaGetLastError());
   return kOk;
 }
