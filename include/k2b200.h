@@ -115,6 +115,23 @@ int32_t k2b200_fsa_incoming(const int32_t *row_splits1, const int32_t *row_ids1,
                             float *in_score, void *tmp, void *stream);
 
 /* ---------------------------------------------------------------------------
+ * CTC graphs.
+ * Builds the CTC graphs of num_seqs transcripts (sym_row_splits[num_seqs+1] into
+ * symbols[num_symbols], both on the device; symbols != -1) with all scores 0:
+ * row_splits1[num_seqs+1], row_splits2[num_states+1] with num_states =
+ * 2*num_symbols + 2*num_seqs, arcs and aux_labels[num_arcs].  num_arcs =
+ * 4*num_symbols + 2*num_seqs + (number of symbol positions with a third arc:
+ * every position when modified != 0, otherwise those whose next symbol differs
+ * or that are last) - the caller counts it to size the outputs.
+ * Replaces k2::CtcGraphs, k2/csrc/fsa_algo.cu:577-730 (bound as _k2.ctc_graph).
+ * ------------------------------------------------------------------------- */
+size_t k2b200_ctc_graph_tmp_bytes(int32_t num_symbols);
+int32_t k2b200_ctc_graph(const int32_t *sym_row_splits, const int32_t *symbols,
+                         int32_t num_seqs, int32_t num_symbols, int32_t modified,
+                         int32_t *row_splits1, int32_t *row_splits2, void *arcs,
+                         int32_t *aux_labels, void *tmp, void *stream);
+
+/* ---------------------------------------------------------------------------
  * DenseFsaVec.
  * k2b200_dense_fsa_vec_fill writes the whole score matrix of a DenseFsaVec
  * (scores[rows, C+1], rows = sum_i (dur_i + 1)) from log_probs[N, T, C]: column

@@ -97,6 +97,9 @@ _sig("k2b200_tot_scores_tropical_backward", c_i32,
      [c_vp, c_vp, c_i32, c_vp, c_i32, c_i32, c_vp, c_i64, c_vp, c_vp])
 _sig("k2b200_index_add", c_i32, [c_vp, c_vp, c_i32, c_vp, c_i64, c_vp])
 _sig("k2b200_index_select_i32", c_i32, [c_vp, c_i64, c_vp, c_i32, c_vp, c_vp])
+_sig("k2b200_ctc_graph_tmp_bytes", c_sz, [c_i32])
+_sig("k2b200_ctc_graph", c_i32,
+     [c_vp, c_vp, c_i32, c_i32, c_i32, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp])
 _sig("k2b200_dense_fsa_vec_fill", c_i32,
      [c_vp, c_i64, c_i64, c_i32, c_vp, c_vp, c_i32, c_vp, c_i32, c_vp])
 _sig("k2b200_dense_fsa_vec_backward", c_i32,
@@ -119,6 +122,7 @@ EXPORTED = [
     "k2b200_tot_scores_tropical_backward", "k2b200_index_add", "k2b200_index_select_i32",
     "k2b200_shortest_path_tmp_bytes", "k2b200_shortest_path",
     "k2b200_dense_fsa_vec_fill", "k2b200_dense_fsa_vec_backward",
+    "k2b200_ctc_graph_tmp_bytes", "k2b200_ctc_graph",
     "k2b200_fsa_properties_tmp_bytes", "k2b200_fsa_properties",
 ]
 

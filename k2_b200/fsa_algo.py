@@ -43,6 +43,8 @@ def ctc_graph(symbols: List[List[int]], modified: bool = False,
     tot = int(lens.sum())
     sym = np.asarray([x for s in symbols for x in s], dtype=np.int64).reshape(-1)
     assert not np.any(sym == -1), "symbols must not contain -1"
+    if torch.device(device).type == "cuda":
+        return _ctc_graph_cuda(lens, sym, modified, torch.device(device))
     sym_off = np.zeros(n + 1, dtype=np.int64)
     np.cumsum(lens, out=sym_off[1:])
     fsa_of_sym = np.repeat(np.arange(n), lens)
@@ -99,6 +101,42 @@ def ctc_graph(symbols: List[List[int]], modified: bool = False,
     rs2[state_off[:-1] + L2 + 1] = tail + 2
     rs2[num_states] = num_arcs
     return _fsa_vec_from_numpy(state_off, rs2, values, device, aux)
+
+
+def _ctc_graph_cuda(lens: np.ndarray, sym: np.ndarray, modified: bool, device) -> Fsa:
+    """The graphs are written by CUDA kernels; the host only counts the arcs (to
+    size the outputs) and derives the per-FSA splits it needs later anyway."""
+    n, tot = len(lens), int(lens.sum())
+    sym_off = np.zeros(n + 1, dtype=np.int64)
+    np.cumsum(lens, out=sym_off[1:])
+    fsa_of_sym = np.repeat(np.arange(n), lens)
+    is_last = (np.arange(tot) + 1) == sym_off[1:][fsa_of_sym]
+    nxt = np.where(is_last, -1, np.append(sym[1:], -1)) if tot else sym
+    has3 = np.ones(tot, dtype=np.int64) if modified else (sym != nxt).astype(np.int64)
+    per_fsa = np.zeros(n, dtype=np.int64)
+    np.add.at(per_fsa, fsa_of_sym, 4 + has3)
+    per_fsa += 2
+    h_arc_splits = np.zeros(n + 1, dtype=np.int64)
+    np.cumsum(per_fsa, out=h_arc_splits[1:])
+    h_rs1 = 2 * sym_off + 2 * np.arange(n + 1)
+    num_arcs, num_states = int(h_arc_splits[-1]), int(h_rs1[-1])
+    meta = torch.from_numpy(np.concatenate([sym_off, sym]).astype(np.int32)).to(device)
+    i32 = dict(dtype=torch.int32, device=device)
+    rs1 = torch.empty(n + 1, **i32)
+    rs2 = torch.empty(num_states + 1, **i32)
+    values = torch.empty((num_arcs, 4), **i32)
+    aux = torch.empty(num_arcs, **i32)
+    tmp = torch.empty(_lib.lib.k2b200_ctc_graph_tmp_bytes(tot), dtype=torch.uint8, device=device)
+    with torch.cuda.device(device):
+        _lib.check(_lib.lib.k2b200_ctc_graph(
+            _lib.ptr(meta[:n + 1]), _lib.ptr(meta[n + 1:]), n, tot, int(modified), _lib.ptr(rs1),
+            _lib.ptr(rs2), _lib.ptr(values), _lib.ptr(aux), _lib.ptr(tmp),
+            _lib.stream_of(device)))
+    arcs = RaggedArc(values, rs1, rs2, h_row_splits1=h_rs1.astype(np.int32),
+                     h_arc_splits=h_arc_splits.astype(np.int32))
+    # valid, non-empty, not top-sorted (self-loops), epsilon arcs present (blank = 0),
+    # accessible and co-accessible by construction: the bits the host path computes
+    return Fsa(arcs, aux_labels=aux, _check=False)
 
 
 def linear_fsa(labels: Union[List[int], List[List[int]]],

@@ -302,3 +302,24 @@ def test_generic_ragged_ops(k2):
     np.testing.assert_array_equal(f.arcs.row_ids(2).cpu().numpy(), state_of)
     np.testing.assert_array_equal(in_src.cpu().numpy(), state_of[order])
     np.testing.assert_array_equal(in_score.cpu().numpy(), a.scores[order])
+
+
+def test_ctc_graph_on_gpu_matches_oracle(k2):
+    from gpu_util import DEV
+    rng = np.random.default_rng(4)
+    for modified in (False, True):
+        for trial in range(25):
+            n = int(rng.integers(1, 7))
+            syms = [[int(x) for x in rng.integers(1, 5, size=int(rng.integers(0, 9)))]
+                    for _ in range(n)]
+            if trial == 0:
+                syms = [[] for _ in range(n)]  # only empty transcripts
+            g = k2.ctc_graph(syms, modified=modified, device=DEV)
+            o = oracle.ctc_graphs(syms, modified)
+            np.testing.assert_array_equal(g.arcs.values().cpu().numpy(), o.arcs)
+            np.testing.assert_array_equal(g.arcs.row_splits(1).cpu().numpy(), o.row_splits1)
+            np.testing.assert_array_equal(g.arcs.row_splits(2).cpu().numpy(), o.row_splits2)
+            np.testing.assert_array_equal(g.aux_labels.cpu().numpy(), o.aux_labels)
+            np.testing.assert_array_equal(g.arcs.h_row_splits1, o.row_splits1)
+            np.testing.assert_array_equal(g.arcs.h_arc_splits, o.row_splits2[o.row_splits1])
+            assert g.properties == oracle.properties(o)[1]
