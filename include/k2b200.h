@@ -168,7 +168,9 @@ int32_t k2b200_dense_fsa_vec_backward(const float *grad_scores, int64_t num_seqs
  *      runs the Viterbi forward/backward recursion over all frames, applies the
  *      output beam (shrinking it like the reference when max_states / max_arcs
  *      would be exceeded), numbers the surviving states and arcs and returns
- *      their counts;
+ *      their counts, plus (optional, may be NULL) the largest number of states in
+ *      one (fsa, frame) layer and of arcs between two layers - the bounds a
+ *      k2b200_fsa_view of the lattice wants;
  *   3. k2b200_intersect_dense_emit(&args, ws, bytes, stream, &out) with output
  *      buffers of those sizes writes the lattice and both arc maps.
  * ------------------------------------------------------------------------- */
@@ -222,7 +224,8 @@ int32_t k2b200_intersect_dense_workspace_bytes(const k2b200_intersect_args *args
 int32_t k2b200_intersect_dense_prune(const k2b200_intersect_args *args, void *workspace,
                                      size_t workspace_bytes, void *stream,
                                      int32_t *num_states_out, int32_t *num_arcs_out,
-                                     float *beam_used);
+                                     float *beam_used, int32_t *max_layer_states,
+                                     int32_t *max_layer_arcs);
 int32_t k2b200_intersect_dense_emit(const k2b200_intersect_args *args, void *workspace,
                                     size_t workspace_bytes, void *stream,
                                     const k2b200_lattice_out *out);

@@ -82,7 +82,8 @@ _sig("k2b200_intersect_dense_workspace_bytes", c_i32,
      [ctypes.POINTER(IntersectArgs), ctypes.POINTER(c_sz), ctypes.POINTER(c_i64)])
 _sig("k2b200_intersect_dense_prune", c_i32,
      [ctypes.POINTER(IntersectArgs), c_vp, c_sz, c_vp, ctypes.POINTER(c_i32),
-      ctypes.POINTER(c_i32), ctypes.POINTER(c_f32)])
+      ctypes.POINTER(c_i32), ctypes.POINTER(c_f32), ctypes.POINTER(c_i32),
+      ctypes.POINTER(c_i32)])
 _sig("k2b200_intersect_dense_emit", c_i32,
      [ctypes.POINTER(IntersectArgs), c_vp, c_sz, c_vp, ctypes.POINTER(LatticeOut)])
 _sig("k2b200_fsa_scores_scratch_bytes", c_sz, [ctypes.POINTER(FsaView)])

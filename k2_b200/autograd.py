@@ -87,11 +87,14 @@ def _intersect_dense_arcs(a: RaggedArc, b: DenseFsaVec, a_to_b_map: Optional[tor
                                                                 ctypes.byref(levels)))
     ws = torch.empty(nbytes.value, dtype=torch.uint8, device=dev)
     ns, na, beam = ctypes.c_int32(), ctypes.c_int32(), ctypes.c_float()
+    max_w, max_a = ctypes.c_int32(), ctypes.c_int32()
     stream = _lib.stream_of(dev)
     with torch.cuda.device(dev):
         _lib.check(_lib.lib.k2b200_intersect_dense_prune(ctypes.byref(args), _lib.ptr(ws),
                                                           nbytes.value, stream, ctypes.byref(ns),
-                                                          ctypes.byref(na), ctypes.byref(beam)))
+                                                          ctypes.byref(na), ctypes.byref(beam),
+                                                          ctypes.byref(max_w),
+                                                          ctypes.byref(max_a)))
         ns, na = ns.value, na.value
         i32 = dict(dtype=torch.int32, device=dev)
         # zero-sized tensors have a NULL data pointer: allocate one spare element
@@ -114,11 +117,10 @@ def _intersect_dense_arcs(a: RaggedArc, b: DenseFsaVec, a_to_b_map: Optional[tor
     lattice = RaggedArc(values[:na], row_splits1, row_splits2, row_ids1[:ns], row_ids2[:na])
     arc_map_a, arc_map_b = arc_map_a[:na], arc_map_b[:na]
     lattice._levels = (level_offsets, level_splits)
-    # every lattice arc goes from frame t to t+1; a frame holds at most one copy of
-    # each graph state and arc
-    h1, ha = a.h_row_splits1, a.h_arc_splits
-    lattice._layer_bounds = (1, int(np.diff(h_brs).max()) + 1, int(np.diff(h1).max()),
-                             int(np.diff(ha).max()))
+    # every lattice arc goes from frame t to t+1; the pruning pass measured the
+    # largest layer
+    lattice._layer_bounds = (1, int(np.diff(h_brs).max()) + 1, max(max_w.value, 1),
+                             max(max_a.value, 1))
     lattice.output_beam_used = beam.value
     return lattice, arc_map_a, arc_map_b
 

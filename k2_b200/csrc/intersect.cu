@@ -326,6 +326,39 @@ __global__ void Totals(const int2 *__restrict__ bases, int64_t total_words,
     totals[0] = tot.x;
     totals[1] = tot.y;
     totals[2] = (long long)red[0];
+    totals[3] = 0;
+    totals[4] = 0;
+  }
+}
+
+// Largest number of kept states in any (pair, t) layer and of kept arcs between two
+// layers: totals[3], totals[4].  One thread per layer.
+__global__ void LayerMaxima(const FsaInfo *__restrict__ infos, int32_t n, int32_t total_levels,
+                            const int2 *__restrict__ bases, long long *__restrict__ totals) {
+  const int32_t lv = blockIdx.x * blockDim.x + threadIdx.x;
+  int32_t ns = 0, na = 0;
+  if (lv < total_levels) {
+    int32_t lo = 0, hi = n;
+    while (hi - lo > 1) {
+      const int32_t mid = (lo + hi) >> 1;
+      if (infos[mid].level_off <= lv) lo = mid; else hi = mid;
+    }
+    const FsaInfo f = infos[lo];
+    if (f.words > 0) {
+      const int64_t w0 = f.word_off + (int64_t)(lv - f.level_off) * f.words;
+      const int2 a = bases[w0], b = bases[w0 + f.words];
+      ns = b.x - a.x;
+      na = b.y - a.y;
+    }
+  }
+#pragma unroll
+  for (int d = 16; d > 0; d >>= 1) {
+    ns = max(ns, __shfl_xor_sync(0xffffffffu, ns, d));
+    na = max(na, __shfl_xor_sync(0xffffffffu, na, d));
+  }
+  if ((threadIdx.x & 31) == 0) {
+    atomicMax(reinterpret_cast<long long *>(totals + 3), (long long)ns);
+    atomicMax(reinterpret_cast<long long *>(totals + 4), (long long)na);
   }
 }
 
@@ -511,7 +544,8 @@ int32_t k2b200_intersect_dense_workspace_bytes(const k2b200_intersect_args *args
 int32_t k2b200_intersect_dense_prune(const k2b200_intersect_args *args, void *workspace,
                                      size_t workspace_bytes, void *stream_v,
                                      int32_t *num_states_out, int32_t *num_arcs_out,
-                                     float *beam_used) {
+                                     float *beam_used, int32_t *max_layer_states,
+                                     int32_t *max_layer_arcs) {
   cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_v);
   Layout L;
   K2B_FORWARD(MakeLayout(args, &L));
@@ -545,7 +579,7 @@ int32_t k2b200_intersect_dense_prune(const k2b200_intersect_args *args, void *wo
   PhaseTimer prune_timer(kPhasePrune, stream);
 
   float beam = args->output_beam;
-  long long h_totals[3] = {0, 0, 0};
+  long long h_totals[5] = {0, 0, 0, 0, 0};
   for (int iter = 0;; ++iter) {
     { Cutoffs<<<CeilDiv(args->num_fsas, 128), 128, 0, stream>>>(d_infos, args->num_fsas, fwd, bwd,
                                                               beam, cutoffs); NoteLaunch(); }
@@ -559,6 +593,9 @@ int32_t k2b200_intersect_dense_prune(const k2b200_intersect_args *args, void *wo
     K2B_FORWARD(ExclusiveSum2(counts, counts, L.total_words, scan_tmp, stream));
     { Totals<<<1, 1024, 0, stream>>>(counts, L.total_words, block_cand,
                                   L.total_words > 0 ? L.count_blocks : 0, totals); NoteLaunch(); }
+    if (L.total_words > 0)
+      { LayerMaxima<<<CeilDiv(L.total_levels, 256), 256, 0, stream>>>(
+          d_infos, args->num_fsas, (int32_t)L.total_levels, counts, totals); NoteLaunch(); }
     K2B_CUDA_OK(cudaGetLastError());
     K2B_CUDA_OK(cudaMemcpyAsync(h_totals, totals, sizeof(h_totals), cudaMemcpyDeviceToHost,
                                 stream));
@@ -586,6 +623,8 @@ int32_t k2b200_intersect_dense_prune(const k2b200_intersect_args *args, void *wo
   *num_states_out = (int32_t)h_totals[0];
   *num_arcs_out = (int32_t)h_totals[1];
   if (beam_used) *beam_used = beam;
+  if (max_layer_states) *max_layer_states = (int32_t)h_totals[3];
+  if (max_layer_arcs) *max_layer_arcs = (int32_t)h_totals[4];
   return kOk;
 }
 

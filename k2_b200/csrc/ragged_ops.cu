@@ -321,7 +321,8 @@ __global__ void IncomingFill(const int32_t *__restrict__ row_splits1,
   unsorted[in_splits[d] + pos] = a;
 }
 
-constexpr int kSmallBucket = 64;
+constexpr int kSmallBucket = 8;    // sorted by one thread
+constexpr int kMediumBucket = 64;  // sorted by one warp with shuffles, two keys per lane
 
 // One thread per state: rank sort of buckets of at most kSmallBucket arcs; larger
 // buckets are queued in `large` (count in large[num_states]) for the warp kernel.
@@ -334,12 +335,22 @@ __global__ void IncomingSortSmall(const int32_t *__restrict__ in_splits, int32_t
                                   int32_t *__restrict__ in_src, float *__restrict__ in_score,
                                   int32_t *__restrict__ large) {
   int32_t s = blockIdx.x * blockDim.x + threadIdx.x;
-  if (s >= num_states) return;
-  int32_t b = in_splits[s], n = in_splits[s + 1] - b;
-  if (n > kSmallBucket) {
-    large[atomicAdd(&large[num_states], 1)] = s;
-    return;
+  int32_t b = 0, n = 0;
+  if (s < num_states) {
+    b = in_splits[s];
+    n = in_splits[s + 1] - b;
   }
+  // queue the larger buckets, one atomic per warp
+  const bool queue = n > kSmallBucket;
+  const unsigned qmask = __ballot_sync(0xffffffffu, queue);
+  if (qmask) {
+    const int lane = threadIdx.x & 31, leader = __ffs(qmask) - 1;
+    int32_t base = 0;
+    if (lane == leader) base = atomicAdd(&large[num_states], __popc(qmask));
+    base = __shfl_sync(0xffffffffu, base, leader);
+    if (queue) large[base + __popc(qmask & ((1u << lane) - 1u))] = s;
+  }
+  if (queue || s >= num_states) return;
   for (int32_t i = 0; i < n; ++i) {
     int32_t x = unsorted[b + i], rank = 0;
     for (int32_t j = 0; j < n; ++j) rank += (unsorted[b + j] < x);
@@ -349,7 +360,9 @@ __global__ void IncomingSortSmall(const int32_t *__restrict__ in_splits, int32_t
   }
 }
 
-// One warp per queued state for the (rare) large buckets.
+// One warp per queued state.  Buckets of up to kMediumBucket arcs are ranked with
+// shuffles (each lane holds two keys and compares them with every other key);
+// larger ones by reading the bucket from memory once per key.
 __global__ void IncomingSortLarge(const int32_t *__restrict__ in_splits, int32_t num_states,
                                   const int32_t *__restrict__ unsorted,
                                   const int32_t *__restrict__ row_ids2,
@@ -362,6 +375,29 @@ __global__ void IncomingSortLarge(const int32_t *__restrict__ in_splits, int32_t
   for (int32_t e = (blockIdx.x * blockDim.x + threadIdx.x) >> 5; e < nlarge; e += nwarps) {
     const int32_t s = large[e];
     const int32_t b = in_splits[s], n = in_splits[s + 1] - b;
+    if (n <= kMediumBucket) {
+      const int32_t big = 0x7fffffff;
+      const int32_t x0 = lane < n ? unsorted[b + lane] : big;
+      const int32_t x1 = lane + 32 < n ? unsorted[b + lane + 32] : big;
+      int32_t r0 = 0, r1 = 0;
+#pragma unroll 8
+      for (int j = 0; j < 32; ++j) {
+        const int32_t y0 = __shfl_sync(0xffffffffu, x0, j), y1 = __shfl_sync(0xffffffffu, x1, j);
+        r0 += (y0 < x0) + (y1 < x0);
+        r1 += (y0 < x1) + (y1 < x1);
+      }
+      if (lane < n) {
+        in_arcs[b + r0] = x0;
+        if (in_src) in_src[b + r0] = row_ids2[x0];
+        if (in_score) in_score[b + r0] = arcs[x0].score;
+      }
+      if (lane + 32 < n) {
+        in_arcs[b + r1] = x1;
+        if (in_src) in_src[b + r1] = row_ids2[x1];
+        if (in_score) in_score[b + r1] = arcs[x1].score;
+      }
+      continue;
+    }
     for (int32_t i = lane; i < n; i += 32) {
       int32_t x = unsorted[b + i], rank = 0;
       for (int32_t j = 0; j < n; ++j) rank += (unsorted[b + j] < x);
@@ -407,7 +443,7 @@ int32_t BuildIncoming(const int32_t *row_splits1, const int32_t *row_ids1,
     { IncomingSortSmall<<<CeilDiv(num_states, 256), 256, 0, stream>>>(
         in_splits, num_states, unsorted, row_ids2, arcs, in_arcs, in_src, in_score, counts);
       NoteLaunch(); }
-    { IncomingSortLarge<<<148, 256, 0, stream>>>(in_splits, num_states, unsorted, row_ids2, arcs,
+    { IncomingSortLarge<<<148 * 8, 256, 0, stream>>>(in_splits, num_states, unsorted, row_ids2, arcs,
                                                 in_arcs, in_src, in_score, counts);
       NoteLaunch(); }
   }

@@ -348,6 +348,8 @@ __global__ void FinishLogScores(const double *__restrict__ m, const int32_t *__r
                      : (Real)(log(mm) + (double)e[s] * 0.69314718055994530942);
 }
 
+constexpr int kMaxSlots = 64;
+
 struct ProbPlan {
   int32_t maxw, maxa, nl_cap, stages, stage_bytes, splits_bytes, lanes_log2, threads;
   size_t bytes;
@@ -366,11 +368,14 @@ static ProbPlan PlanProb(const k2b200_fsa_view *v) {
   // 16-byte boundaries) + w + 1
   p.splits_bytes = (((p.maxw + 8) * 4) + 15) & ~15;
   p.stage_bytes = p.splits_bytes + p.maxa * 16;
-  size_t fixed = 128                                      // mbarriers
+  size_t fixed = 1024                                     // 64 full + 64 empty mbarriers
                  + 8 * (size_t)((p.nl_cap + 1 + 3) & ~3)  // layer / arc boundaries
                  + 2 * (size_t)p.maxw * 16 + 16;          // (mantissa, exponent) ping-pong
-  if (fixed + 2 * (size_t)p.stage_bytes > kStagedSmemBudget) return p;
-  p.stages = (int32_t)std::min<size_t>(8, (kStagedSmemBudget - fixed) / p.stage_bytes);
+  // with more CTAs (2 per FSA) than SMs, leave room for two CTAs per SM
+  size_t budget = 2 * (size_t)v->num_fsas > 148 ? kStagedSmemBudget / 2 : kStagedSmemBudget;
+  if (fixed + 2 * (size_t)p.stage_bytes > budget) budget = kStagedSmemBudget;
+  if (fixed + 2 * (size_t)p.stage_bytes > budget) return p;
+  p.stages = (int32_t)std::min<size_t>(8, (budget - fixed) / p.stage_bytes);
   p.bytes = fixed + (size_t)p.stage_bytes * p.stages;
   int32_t mean_deg = v->num_states > 0 ? (v->num_arcs + v->num_states - 1) / v->num_states : 1;
   p.lanes_log2 = 0;
@@ -402,7 +407,7 @@ ProbScoresStaged(k2b200_fsa_view v, const ProbArc *__restrict__ fwd_arcs,
 
   uint64_t *bars = reinterpret_cast<uint64_t *>(smem_raw);  // [stages], 128 bytes reserved
   const int32_t lvl_ints = (p.nl_cap + 1 + 3) & ~3;
-  int32_t *lvl = reinterpret_cast<int32_t *>(smem_raw + 128);
+  int32_t *lvl = reinterpret_cast<int32_t *>(smem_raw + 1024);
   int32_t *alvl = lvl + lvl_ints;
   ProbState *pstate = reinterpret_cast<ProbState *>(alvl + lvl_ints);  // [2][maxw]
   unsigned char *ring = reinterpret_cast<unsigned char *>(pstate + 2 * p.maxw);
@@ -414,9 +419,9 @@ ProbScoresStaged(k2b200_fsa_view v, const ProbArc *__restrict__ fwd_arcs,
   __shared__ int32_t bad_shared;
   if (tid == 0) {
     bad_shared = (nl > p.nl_cap);
-    for (int32_t s = 0; s < p.stages; ++s) {
-      MbarInit(&bars[s], 1);      // full: the producer's arrive + the copies' bytes
-      MbarInit(&bars[8 + s], 1);  // empty: one elected compute thread
+    for (int32_t s = 0; s < kMaxSlots; ++s) {
+      MbarInit(&bars[s], 1);              // full: the producer's arrive + the copies' bytes
+      MbarInit(&bars[kMaxSlots + s], 1);  // empty: one elected compute thread
     }
     MbarInitFence();
   }
@@ -440,13 +445,37 @@ ProbScoresStaged(k2b200_fsa_view v, const ProbArc *__restrict__ fwd_arcs,
     return;
   }
 
-  const int32_t stages = p.stages;
+  // The plan's stage size comes from loose bounds (a layer could hold every state
+  // and arc of the graph); the layers of this lattice are usually smaller.  The ring
+  // is re-cut into slots of the largest layer actually present so that more layers
+  // are in flight.
+  __shared__ int32_t max_splits_ints, max_arcs_shared;
+  if (tid == 0) {
+    max_splits_ints = 0;
+    max_arcs_shared = 0;
+  }
+  __syncthreads();
+  {
+    int32_t ms = 0, ma = 0;
+    for (int32_t k = tid; k < nl; k += nt) {
+      ms = max(ms, lvl[k + 1] - lvl[k] + 8);
+      ma = max(ma, alvl[k + 1] - alvl[k]);
+    }
+    atomicMax(&max_splits_ints, ms);
+    atomicMax(&max_arcs_shared, ma);
+  }
+  __syncthreads();
+  const int32_t splits_bytes = ((max_splits_ints * 4) + 15) & ~15;
+  const int32_t slot_bytes = splits_bytes + (max_arcs_shared > 0 ? max_arcs_shared : 1) * 16;
+  const int32_t ring_bytes = p.stage_bytes * p.stages;
+  int32_t stages = ring_bytes / slot_bytes;
+  stages = stages > kMaxSlots ? kMaxSlots : stages;
   // The last warp only feeds the ring (one thread of it); the others own the
   // states.  full[slot] completes when a layer's copies have landed, empty[slot]
   // when the compute warps are done reading it, so the producer runs up to
   // `stages` layers ahead and is never on the layer-to-layer critical path.
   const int32_t nc = nt - 32;
-  uint64_t *full = bars, *empty = bars + 8;
+  uint64_t *full = bars, *empty = bars + kMaxSlots;
   auto layer_of = [&](int32_t step) { return dir == 0 ? step : nl - 1 - step; };
   if (tid >= nc) {
     if (tid != nc) return;
@@ -460,7 +489,7 @@ ProbScoresStaged(k2b200_fsa_view v, const ProbArc *__restrict__ fwd_arcs,
       }
       const int32_t li = layer_of(step);
       const int32_t b = lvl[li], e = lvl[li + 1], ab = alvl[li], na = alvl[li + 1] - ab;
-      unsigned char *st = ring + (size_t)slot * p.stage_bytes;
+      unsigned char *st = ring + (size_t)slot * slot_bytes;
       int32_t *sp = reinterpret_cast<int32_t *>(st);
       const int32_t lo = b & ~3;
       int32_t hi = (e + 1 + 3) & ~3;
@@ -470,7 +499,7 @@ ProbScoresStaged(k2b200_fsa_view v, const ProbArc *__restrict__ fwd_arcs,
       for (int32_t k = hi; k <= e; ++k) sp[k - lo] = gsplits[k];  // at most 3 trailing ints
       MbarArriveExpectTx(&full[slot], bytes_splits + bytes_arcs);
       if (bytes_splits) BulkCopyG2S(sp, gsplits + lo, bytes_splits, &full[slot]);
-      if (bytes_arcs) BulkCopyG2S(st + p.splits_bytes, garcs + ab, bytes_arcs, &full[slot]);
+      if (bytes_arcs) BulkCopyG2S(st + splits_bytes, garcs + ab, bytes_arcs, &full[slot]);
       slot = slot + 1 == stages ? 0 : slot + 1;
       empty_parity ^= (slot == 0);
     }
@@ -509,9 +538,9 @@ ProbScoresStaged(k2b200_fsa_view v, const ProbArc *__restrict__ fwd_arcs,
       edge = b;
       ab = alvl[li];
     }
-    const unsigned char *st = ring + (size_t)slot * p.stage_bytes;
+    const unsigned char *st = ring + (size_t)slot * slot_bytes;
     const int32_t *sp = reinterpret_cast<const int32_t *>(st) + (b & 3);
-    const ProbArc *body = reinterpret_cast<const ProbArc *>(st + p.splits_bytes);
+    const ProbArc *body = reinterpret_cast<const ProbArc *>(st + splits_bytes);
     slot = slot + 1 == stages ? 0 : slot + 1;
     parity ^= (slot == 0);
     const ProbState *prev = pstate + ((step + 1) & 1) * p.maxw;
