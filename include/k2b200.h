@@ -53,7 +53,8 @@ int32_t k2b200_abi_version(void);
  * for them, returns the summed milliseconds of the n recorded intervals and
  * resets the phase.  Phases: 0 Viterbi recursion, 1 pruning (count + numbering),
  * 2 lattice emission, 3 forward/backward scores, 4 posteriors + gradient
- * scatter, 5 incoming-arc index, 6 DenseFsaVec construction and its backward. */
+ * scatter, 5 incoming-arc index, 6 DenseFsaVec construction and its backward,
+ * 7 lattice-free alpha/beta recursion, 8 lattice-free gradients. */
 int64_t k2b200_kernel_launch_count(void);
 void k2b200_profile_enable(int32_t on);
 double k2b200_profile_read_ms(int32_t phase, int64_t *intervals);
@@ -229,6 +230,39 @@ int32_t k2b200_intersect_dense_prune(const k2b200_intersect_args *args, void *wo
 int32_t k2b200_intersect_dense_emit(const k2b200_intersect_args *args, void *workspace,
                                     size_t workspace_bytes, void *stream,
                                     const k2b200_lattice_out *out);
+
+/* ---------------------------------------------------------------------------
+ * Lattice-free total scores: the log-semiring total score of
+ * intersect_dense(a_fsas, b_fsas, output_beam) for every graph, and its
+ * gradients, without materialising the lattice.
+ * Replaces, for callers that only want the loss, the chain
+ *   k2::IntersectDense (k2/csrc/intersect_dense.cu:100-1073) ->
+ *   k2::GetForwardScores / GetTotScores (k2/csrc/fsa_utils.cu:1124-1278, :1456-1490) ->
+ *   k2::GetArcPost (:1492-1560) -> index_add through both arc maps
+ *   (k2/python/k2/autograd.py:30-117, :560-664),
+ * as k2.ctc_loss drives it (k2/python/k2/ctc_loss.py:86-150).  The same states and
+ * arcs survive pruning as in the lattice (same fp32 tests, same beam reduction
+ * against max_states / max_arcs); sums run in float64.
+ *
+ *   k2b200_dense_loss_supported: *supported = 1 when every graph fits the
+ *     shared-memory recursion; otherwise use the lattice entry points.
+ *   k2b200_dense_loss_forward: tot_scores[num_fsas] (device, float64; -inf for a
+ *     graph with no surviving path).  The workspace keeps what the backward needs.
+ *   k2b200_dense_loss_backward: with tot_grad[i * tot_grad_stride] = dL/dtot[i]
+ *     (device, float64), ADDS dL/d(arc score) to grad_a[num_arcs] and
+ *     dL/d(scores) to grad_b[rows * cols]; both must be zero-filled (or hold
+ *     gradients to accumulate onto) and the workspace must be the one the forward
+ *     call filled, with the same args.
+ * ------------------------------------------------------------------------- */
+int32_t k2b200_dense_loss_supported(const k2b200_intersect_args *args, int32_t *supported);
+int32_t k2b200_dense_loss_workspace_bytes(const k2b200_intersect_args *args, size_t *bytes);
+int32_t k2b200_dense_loss_forward(const k2b200_intersect_args *args, void *workspace,
+                                  size_t workspace_bytes, void *stream, double *tot_scores,
+                                  float *beam_used);
+int32_t k2b200_dense_loss_backward(const k2b200_intersect_args *args, void *workspace,
+                                   size_t workspace_bytes, const double *tot_grad,
+                                   int32_t tot_grad_stride, float *grad_a, float *grad_b,
+                                   void *stream);
 
 /* ---------------------------------------------------------------------------
  * Forward / backward scores of a layered (top-sorted, acyclic) FsaVec.

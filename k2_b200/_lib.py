@@ -86,6 +86,14 @@ _sig("k2b200_intersect_dense_prune", c_i32,
       ctypes.POINTER(c_i32)])
 _sig("k2b200_intersect_dense_emit", c_i32,
      [ctypes.POINTER(IntersectArgs), c_vp, c_sz, c_vp, ctypes.POINTER(LatticeOut)])
+_sig("k2b200_dense_loss_supported", c_i32,
+     [ctypes.POINTER(IntersectArgs), ctypes.POINTER(c_i32)])
+_sig("k2b200_dense_loss_workspace_bytes", c_i32,
+     [ctypes.POINTER(IntersectArgs), ctypes.POINTER(c_sz)])
+_sig("k2b200_dense_loss_forward", c_i32,
+     [ctypes.POINTER(IntersectArgs), c_vp, c_sz, c_vp, c_vp, ctypes.POINTER(c_f32)])
+_sig("k2b200_dense_loss_backward", c_i32,
+     [ctypes.POINTER(IntersectArgs), c_vp, c_sz, c_vp, c_i32, c_vp, c_vp, c_vp])
 _sig("k2b200_fsa_scores_scratch_bytes", c_sz, [ctypes.POINTER(FsaView)])
 _sig("k2b200_fsa_scores", c_i32,
      [ctypes.POINTER(FsaView), c_i32, c_i32, c_vp, c_vp, c_vp, c_vp, c_sz, c_vp])
@@ -125,6 +133,8 @@ EXPORTED = [
     "k2b200_dense_fsa_vec_fill", "k2b200_dense_fsa_vec_backward",
     "k2b200_ctc_graph_tmp_bytes", "k2b200_ctc_graph",
     "k2b200_fsa_properties_tmp_bytes", "k2b200_fsa_properties",
+    "k2b200_dense_loss_supported", "k2b200_dense_loss_workspace_bytes",
+    "k2b200_dense_loss_forward", "k2b200_dense_loss_backward",
 ]
 
 
@@ -171,7 +181,7 @@ def note_launches(n: int) -> None:  # kept for callers; the library counts itsel
     pass
 
 
-PHASES = ["viterbi", "prune", "emit", "scores", "post", "incoming", "dense"]
+PHASES = ["viterbi", "prune", "emit", "scores", "post", "incoming", "dense", "chain", "grad"]
 
 
 def profile_enable(on: bool) -> None:

@@ -46,11 +46,11 @@ def index_select(src: torch.Tensor, index: torch.Tensor) -> torch.Tensor:
     return out
 
 
-def _intersect_dense_arcs(a: RaggedArc, b: DenseFsaVec, a_to_b_map: Optional[torch.Tensor],
-                          output_beam: float, max_states: int, max_arcs: int,
-                          viterbi_mode: int = 0):
-    """The `_k2.intersect_dense` call (k2/python/csrc/torch/fsa_algo.cu:224-253):
-    returns (RaggedArc lattice, arc_map_a, arc_map_b)."""
+def _make_intersect_args(a: RaggedArc, b: DenseFsaVec, a_to_b_map: Optional[torch.Tensor],
+                         output_beam: float, max_states: int, max_arcs: int,
+                         viterbi_mode: int = 0):
+    """The argument block shared by the lattice and the lattice-free entry points.
+    Returns (args, objects that must outlive the call, device, host row splits of b)."""
     _lib.require_cuda(a.values(), "a_fsas")
     _lib.require_cuda(b.scores, "b_fsas.scores")
     dev = a.device
@@ -80,6 +80,16 @@ def _intersect_dense_arcs(a: RaggedArc, b: DenseFsaVec, a_to_b_map: Optional[tor
         output_beam=float(output_beam), max_states=int(min(max_states, 2**31 - 1)),
         max_arcs=int(min(max_arcs, 2**31 - 1)), viterbi_mode=viterbi_mode,
         a_max_degree=a.max_degree())
+    return args, (h_rs1, h_as, h_map, in_splits, in_arcs, scores), dev, h_brs
+
+
+def _intersect_dense_arcs(a: RaggedArc, b: DenseFsaVec, a_to_b_map: Optional[torch.Tensor],
+                          output_beam: float, max_states: int, max_arcs: int,
+                          viterbi_mode: int = 0):
+    """The `_k2.intersect_dense` call (k2/python/csrc/torch/fsa_algo.cu:224-253):
+    returns (RaggedArc lattice, arc_map_a, arc_map_b)."""
+    args, _keep, dev, h_brs = _make_intersect_args(a, b, a_to_b_map, output_beam, max_states,
+                                                   max_arcs, viterbi_mode)
     nbytes = ctypes.c_size_t()
     levels = ctypes.c_int64()
     _lib.check(_lib.lib.k2b200_intersect_dense_workspace_bytes(ctypes.byref(args),
@@ -247,3 +257,72 @@ def intersect_dense(a_fsas: Fsa, b_fsas: DenseFsaVec, output_beam: float,
                                   a_fsas.scores, b_fsas.scores, a_to_b_map, seqframe_idx_name,
                                   frame_idx_name)
     return out_fsa[0]
+
+
+class _DenseTotScoresFunction(torch.autograd.Function):
+    """tot_scores = log-semiring total score of intersect_dense(a_fsas, b_fsas) per
+    graph, with gradients to the graph scores and the dense scores, computed on the
+    (frame, state) grid without building the lattice.  Same pruning as
+    `intersect_dense` followed by `get_tot_scores(log_semiring=True)`."""
+
+    @staticmethod
+    def forward(ctx, a_fsas: Fsa, b_fsas: DenseFsaVec, output_beam: float, max_states: int,
+                max_arcs: int, use_double_scores: bool, a_to_b_map: Optional[torch.Tensor],
+                unused_scores_a: torch.Tensor, unused_scores_b: torch.Tensor) -> torch.Tensor:
+        args, keep, dev, _ = _make_intersect_args(a_fsas.arcs, b_fsas, a_to_b_map, output_beam,
+                                                  max_states, max_arcs, VITERBI_MODE)
+        nbytes = ctypes.c_size_t()
+        _lib.check(_lib.lib.k2b200_dense_loss_workspace_bytes(ctypes.byref(args),
+                                                               ctypes.byref(nbytes)))
+        ws = torch.empty(nbytes.value, dtype=torch.uint8, device=dev)
+        tot = torch.empty(a_fsas.arcs.num_fsas, dtype=torch.float64, device=dev)
+        beam = ctypes.c_float()
+        with torch.cuda.device(dev):
+            _lib.check(_lib.lib.k2b200_dense_loss_forward(
+                ctypes.byref(args), _lib.ptr(ws), nbytes.value, _lib.stream_of(dev),
+                _lib.ptr(tot), ctypes.byref(beam)))
+        ctx.args, ctx.keep, ctx.ws, ctx.ws_bytes = args, (keep, a_fsas.arcs), ws, nbytes.value
+        ctx.dev = dev
+        ctx.shape_a = unused_scores_a.shape
+        ctx.shape_b = unused_scores_b.shape
+        ctx.output_beam_used = beam.value
+        return tot if use_double_scores else tot.to(torch.float32)
+
+    @staticmethod
+    def backward(ctx, tot_grad: torch.Tensor):
+        dev = ctx.dev
+        if tot_grad.dtype != torch.float64:
+            tot_grad = tot_grad.to(torch.float64)
+        stride = tot_grad.stride(0) if tot_grad.numel() > 0 else 0
+        grad_a = torch.zeros(ctx.shape_a, dtype=torch.float32, device=dev)
+        grad_b = torch.zeros(ctx.shape_b, dtype=torch.float32, device=dev)
+        with torch.cuda.device(dev):
+            _lib.check(_lib.lib.k2b200_dense_loss_backward(
+                ctypes.byref(ctx.args), _lib.ptr(ctx.ws), ctx.ws_bytes, _lib.ptr(tot_grad),
+                stride, _lib.ptr(grad_a), _lib.ptr(grad_b), _lib.stream_of(dev)))
+        return None, None, None, None, None, None, None, grad_a, grad_b
+
+
+def dense_loss_supported(a_fsas: Fsa, b_fsas: DenseFsaVec,
+                         a_to_b_map: Optional[torch.Tensor] = None) -> bool:
+    """Can `intersect_dense_tot_scores` handle these inputs (CUDA tensors, graphs
+    small enough for the shared-memory recursion)?"""
+    if not (a_fsas.arcs.values().is_cuda and b_fsas.scores.is_cuda):
+        return False
+    args, _keep, _, _ = _make_intersect_args(a_fsas.arcs, b_fsas, a_to_b_map, 1.0, 1, 1)
+    ok = ctypes.c_int32()
+    _lib.check(_lib.lib.k2b200_dense_loss_supported(ctypes.byref(args), ctypes.byref(ok)))
+    return bool(ok.value)
+
+
+def intersect_dense_tot_scores(a_fsas: Fsa, b_fsas: DenseFsaVec, output_beam: float,
+                               max_states: int = 15000000, max_arcs: int = 1073741824,
+                               a_to_b_map: Optional[torch.Tensor] = None,
+                               use_double_scores: bool = True) -> torch.Tensor:
+    """`intersect_dense(a_fsas, b_fsas, output_beam, ...).get_tot_scores(
+    log_semiring=True, use_double_scores=...)` in one step (the composition
+    k2/python/k2/ctc_loss.py:86-140 makes), differentiable w.r.t. `a_fsas.scores`
+    and `b_fsas.scores`.  The lattice is not built."""
+    return _DenseTotScoresFunction.apply(a_fsas, b_fsas, output_beam, max_states, max_arcs,
+                                         use_double_scores, a_to_b_map, a_fsas.scores,
+                                         b_fsas.scores)

@@ -57,7 +57,7 @@ const char *LastError();
 // optional cudaEvent timing of named phases on the launching stream.
 void NoteLaunch(int n = 1);
 enum Phase : int { kPhaseViterbi = 0, kPhasePrune, kPhaseEmit, kPhaseScores, kPhasePost,
-                   kPhaseIncoming, kPhaseDense, kNumPhases };
+                   kPhaseIncoming, kPhaseDense, kPhaseChain, kPhaseGrad, kNumPhases };
 long long LaunchCount();
 void SetProfiling(bool on);
 double ReadPhase(int phase, long long *count);

@@ -1,0 +1,1062 @@
+// Total scores of intersect_dense(a_fsas, b_fsas) in the log semiring, and their
+// gradients, without ever writing the lattice.
+//
+// The reference computes a CTC / LF-MMI loss as
+//   lattice = intersect_dense(graphs, dense, beam)      (k2/csrc/intersect_dense.cu)
+//   tot     = lattice.get_tot_scores(log_semiring=True) (k2/csrc/fsa_utils.cu:708-1271)
+// and back-propagates through the arc posteriors and the two arc maps
+// (k2/python/k2/autograd.py:30-117, :511-664).  Every lattice state is a (frame,
+// graph state) pair and every lattice arc a (frame, graph arc) pair, so the same
+// numbers can be had from recursions over the dense (frame, state) grid that the
+// pruning pass already uses:
+//
+//   1. the Viterbi grids and the cutoffs decide, exactly as for the lattice, which
+//      (frame, state) and (frame, arc) pairs survive pruning;
+//   2. alpha[t][s] and beta[t][s] are the log-semiring forward / backward scores
+//      of the surviving pairs, carried as mantissa * 2^exponent so that the
+//      frame-to-frame chain has no exp or log on it;
+//   3. the posterior of (t, arc) is alpha[t][src] * w(arc) * p(t, label) *
+//      beta[t+1][dest] / Z; summed over t it is the gradient of the graph arc,
+//      summed over the arcs with one label it is the gradient of one element of
+//      the dense matrix.  No arc map, no scatter through lattice-sized arrays.
+//
+// exp() of the dense scores is taken once per element in a parallel pass
+// (ExpDense) shared by both recursions and the gradient pass.
+#include <algorithm>
+
+#include "cp_async.cuh"
+#include "intersect_internal.cuh"
+#include "prob_math.cuh"
+
+namespace k2b {
+
+// The dense scores are repacked once per call, one 16-byte aligned record per row:
+//   float  lp[cols4]   the scores themselves (for the pruning tests), then
+//   double p[cols2]    exp(lp) (0 where that would be subnormal);
+// element `cols` of both parts is the "no such column" entry (-inf / 0).  A whole
+// record moves to shared memory with one bulk copy.
+struct DensePack {
+  int32_t cols, cols4, cols2, pitch;  // pitch in bytes, a multiple of 16
+};
+static DensePack MakeDensePack(int32_t cols) {
+  DensePack d;
+  d.cols = cols;
+  d.cols4 = (cols + 1 + 3) & ~3;
+  d.cols2 = (cols + 1 + 1) & ~1;
+  d.pitch = 4 * d.cols4 + 8 * d.cols2;
+  return d;
+}
+__device__ __forceinline__ const float *PackLp(const unsigned char *rec) {
+  return reinterpret_cast<const float *>(rec);
+}
+__device__ __forceinline__ const double *PackP(const unsigned char *rec, const DensePack &d) {
+  return reinterpret_cast<const double *>(rec + 4 * d.cols4);
+}
+
+// exp(arc.score) = f * 2^k of a graph arc.
+struct __align__(16) ArcFactor {
+  double f;
+  int32_t k;
+  int32_t pad;
+};
+
+__global__ void ExpDense(const float *__restrict__ scores, int64_t rows, DensePack d,
+                         unsigned char *__restrict__ out) {
+  const int64_t n = rows * d.cols4;
+  for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < n;
+       idx += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t r = idx / d.cols4;
+    const int32_t c = (int32_t)(idx - r * d.cols4);
+    unsigned char *rec = out + r * d.pitch;
+    const float lp = c < d.cols ? scores[r * d.cols + c] : -INFINITY;
+    reinterpret_cast<float *>(rec)[c] = lp;
+    if (c < d.cols2) {
+      double p = exp((double)lp);
+      if (p < 1e-300) p = 0.0;
+      reinterpret_cast<double *>(rec + 4 * d.cols4)[c] = p;
+    }
+  }
+}
+
+// t = m * 2^e with m in [1,2) from a positive normal double; (0, kZeroExp) for 0.
+__device__ __forceinline__ double SplitExp(double t, int32_t *e) {
+  if (t == 0.0) {
+    *e = kZeroExp;
+    return 0.0;
+  }
+  const int32_t hi = __double2hiint(t);
+  const int32_t ex = (hi >> 20) - 1023;
+  *e = ex;
+  return __hiloint2double(hi - (ex << 20), __double2loint(t));
+}
+
+__global__ void ExpArcs(const Arc *__restrict__ arcs, int32_t n, ArcFactor *__restrict__ out) {
+  int32_t i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  ArcFactor a;
+  ExpToMantExp(arcs[i].score, &a.f, &a.k);
+  a.pad = 0;
+  out[i] = a;
+}
+
+// ---------------------------------------------------------------------------
+// Lane plans.  The recursion kernel keeps the arcs of state s in the registers of
+// G(s) = ceil(degree(s) / kDeg) lanes of one warp, so that a frame costs every lane
+// the same few arcs whatever the degree distribution of the graph is.  PlanLanes
+// lays the lane groups of one graph and direction out over a CTA of kLaneThreads
+// threads: groups sorted by size, largest first (states in increasing order within
+// a size), packed next-fit into warps - a group never straddles two warps.
+//   plan[(dir * n + i) * kLaneThreads + thread] = state | lane << 16 | G << 24, or -1
+// unfit[i] is set when graph i needs more lanes than a CTA has (or has more than
+// 32 * kDeg arcs on a state); the shared-memory kernels below take those graphs.
+// Graphs whose largest degree is at most kDeg need no plan: thread s owns state s.
+// ---------------------------------------------------------------------------
+constexpr int kLaneThreads = 768;
+
+__global__ void __launch_bounds__(256)
+PlanLanes(const FsaInfo *__restrict__ infos, int32_t n,
+          const int32_t *__restrict__ a_row_splits2, const int32_t *__restrict__ in_splits,
+          int32_t k_deg, int32_t *__restrict__ plan, int32_t *__restrict__ unfit) {
+  // per group size G = 1..32: number of states, lanes left in the warp where the
+  // size class starts, first lane of that start, first lane of the following warps
+  __shared__ int32_t count[33], head_room[33], head_pos[33], body_pos[33];
+  __shared__ int32_t bad;
+  const int32_t i = blockIdx.y, dir = blockIdx.x;
+  const FsaInfo f = infos[i];
+  const int32_t S = f.num_states;
+  const int tid = threadIdx.x, nt = blockDim.x;
+  int32_t *out = plan + ((int64_t)dir * n + i) * kLaneThreads;
+  for (int32_t t = tid; t < kLaneThreads; t += nt) out[t] = -1;
+  if (tid < 33) count[tid] = 0;
+  if (tid == 0) bad = S > kLaneThreads;
+  __syncthreads();
+  const int32_t *splits = (dir == 0 ? in_splits : a_row_splits2) + f.state_off;
+  auto lanes_of = [&](int32_t s) {
+    const int32_t deg = splits[s + 1] - splits[s];
+    return deg <= k_deg ? 1 : (deg + k_deg - 1) / k_deg;
+  };
+  if (S <= kLaneThreads)
+    for (int32_t s = tid; s < S; s += nt) {
+      const int32_t G = lanes_of(s);
+      if (G > 32) bad = 1; else atomicAdd(&count[G], 1);
+    }
+  __syncthreads();
+  if (tid == 0 && !bad) {
+    int32_t pos = 0;
+    for (int G = 32; G >= 1; --G) {
+      const int32_t c = count[G];
+      if (c == 0) continue;
+      const int32_t room = (32 - (pos & 31)) / G;  // groups that still fit in this warp
+      const int32_t per_warp = 32 / G;
+      head_room[G] = room;
+      head_pos[G] = pos;
+      if (c <= room) {
+        pos += c * G;
+      } else {
+        const int32_t rest = c - room;
+        const int32_t body = (pos + room * G + 31) & ~31;
+        body_pos[G] = body;
+        pos = body + (rest / per_warp) * 32 + (rest % per_warp) * G;
+      }
+      if (pos > kLaneThreads) bad = 1;
+    }
+  }
+  __syncthreads();
+  if (bad) {
+    if (tid == 0) atomicOr(&unfit[i], 1);
+    return;
+  }
+  // warp w places the size classes w, w + 8, ...: ordered compaction by ballot
+  const int warp = tid >> 5, lane = tid & 31;
+  for (int G = 1 + warp; G <= 32; G += nt >> 5) {
+    if (count[G] == 0) continue;
+    const int32_t per_warp = 32 / G, room = head_room[G];
+    int32_t seen = 0;
+    for (int32_t s0 = 0; s0 < S; s0 += 32) {
+      const int32_t s = s0 + lane;
+      const bool in = s < S && lanes_of(s) == G;
+      const uint32_t m = __ballot_sync(0xffffffffu, in);
+      if (in) {
+        const int32_t j = seen + __popc(m & ((1u << lane) - 1u));
+        int32_t p0;
+        if (j < room) {
+          p0 = head_pos[G] + j * G;
+        } else {
+          const int32_t r = j - room;
+          p0 = body_pos[G] + (r / per_warp) * 32 + (r % per_warp) * G;
+        }
+        for (int32_t g = 0; g < G; ++g) out[p0 + g] = s | (g << 16) | (G << 24);
+      }
+      seen += __popc(m);
+    }
+  }
+}
+
+struct LaneSmem {
+  int32_t s_pad, a_pad, stages;
+  size_t bytes;
+};
+constexpr size_t kChainSmemBudget = 220 * 1024;
+
+static LaneSmem PlanLaneSmem(const Layout &L, const DensePack &d, bool smem_factors) {
+  LaneSmem p;
+  p.s_pad = (L.max_states + 3) & ~3;
+  p.a_pad = smem_factors ? (L.max_arcs + 3) & ~3 : 0;
+  const size_t fixed =
+      (sizeof(ProbState) + sizeof(float)) * 2 * p.s_pad + sizeof(ArcFactor) * p.a_pad;
+  p.stages = 0;
+  if (fixed < kChainSmemBudget)
+    p.stages = (int32_t)std::min<size_t>(8, (kChainSmemBudget - fixed) / d.pitch);
+  p.bytes = fixed + (size_t)d.pitch * std::max(p.stages, 0);
+  return p;
+}
+
+// ---------------------------------------------------------------------------
+// The alpha / beta recursion.  grid = (2 directions, pairs), one CTA walks all
+// frames of its pair.  Per frame: one bulk copy (issued stages - 1 frames ahead by
+// thread 0, completion on an mbarrier) brings the packed dense row into a
+// shared-memory ring; every lane runs the reference's pruning test
+// (intersect_dense.cu:430-470) on its arcs with the same fp32 expressions and sums
+// the survivors in mantissa/exponent form; the lanes of a state merge by shuffles.
+// The Viterbi scores of the lane's own state are fetched kPF frames ahead into
+// registers.  With kSmemFactors the exp() of the arc scores sits in a shared-memory
+// table (arcs in the order of the direction walked), otherwise in registers.
+//
+// `oth` holds, for the states of the previous frame, the Viterbi score the arc
+// test needs (forward score walking forward, backward score walking backward), or
+// -inf when that state was pruned - which fails the arc test by itself.
+// A wait that gives up marks the graph in `unfit`; the shared-memory kernel that
+// runs next then recomputes it.
+// ---------------------------------------------------------------------------
+template <int kDeg, bool kSmemFactors, int kPF, int kMaxThreads>
+__global__ void __launch_bounds__(kMaxThreads)
+GridChainLanes(const FsaInfo *__restrict__ infos, int32_t n, const Arc *__restrict__ arcs,
+               const int32_t *__restrict__ a_row_splits2, const int32_t *__restrict__ in_splits,
+               const int32_t *__restrict__ in_arcs, const unsigned char *__restrict__ dense,
+               DensePack dp, const float *__restrict__ vfwd, const float *__restrict__ vbwd,
+               const float *__restrict__ cutoffs, ProbState *__restrict__ alpha,
+               ProbState *__restrict__ beta, double *__restrict__ tot,
+               const int32_t *__restrict__ plan, int32_t *__restrict__ unfit, LaneSmem sm) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  __shared__ __align__(8) uint64_t full[8];
+  __shared__ int32_t gave_up;
+  const int32_t i = blockIdx.y;
+  const int dir = blockIdx.x;
+  if (plan != nullptr && unfit[i]) return;
+  const FsaInfo f = infos[i];
+  const int32_t S = f.num_states, Tk = f.tk, cols = dp.cols;
+  const int tid = threadIdx.x, nt = blockDim.x;
+  if (S == 0) {
+    if (dir == 0 && tid == 0) tot[i] = -INFINITY;
+    return;
+  }
+  const int32_t stages = sm.stages, s_pad = sm.s_pad;
+  unsigned char *ring = smem_raw;                                              // [stages][pitch]
+  ProbState *ps = reinterpret_cast<ProbState *>(ring + (size_t)stages * dp.pitch);  // [2][s_pad]
+  ArcFactor *table = reinterpret_cast<ArcFactor *>(ps + 2 * s_pad);            // [a_pad]
+  float *oth = reinterpret_cast<float *>(table + sm.a_pad);                    // [2][s_pad]
+
+  int32_t s = -1, g = 0, G = 1;
+  if (plan != nullptr) {
+    const int32_t code = plan[((int64_t)dir * n + i) * kLaneThreads + tid];
+    if (code >= 0) {
+      s = code & 0xffff;
+      g = (code >> 16) & 0xff;
+      G = code >> 24;
+    }
+  } else if (tid < S) {
+    s = tid;
+  }
+  // ---- this lane's arcs: dir 0 arcs entering s (other end = source), dir 1 leaving
+  int32_t other_col[kDeg];  // other-end state | column << 16
+  float w[kDeg];            // arc score, -inf for an unused slot
+  double ewf[kSmemFactors ? 1 : kDeg];
+  int32_t ewk[kSmemFactors ? 1 : kDeg];
+  int32_t tbl0 = 0;  // table index of slot 0; slot j is tbl0 + j * G
+#pragma unroll
+  for (int j = 0; j < kDeg; ++j) {
+    other_col[j] = cols << 16;
+    w[j] = -INFINITY;
+    if (!kSmemFactors) {
+      ewf[j] = 0.0;
+      ewk[j] = kZeroExp;
+    }
+  }
+  const int32_t *gsplits = dir == 0 ? in_splits : a_row_splits2;
+  if (s >= 0) {
+    const int32_t a0 = gsplits[f.state_off + s], a1 = gsplits[f.state_off + s + 1];
+    tbl0 = a0 - f.arc_off + g;
+#pragma unroll
+    for (int j = 0; j < kDeg; ++j) {
+      const int32_t k = a0 + g + j * G;
+      if (k < a1) {
+        const Arc arc = arcs[dir == 0 ? in_arcs[k] : k];
+        const int32_t c = arc.label + 1;
+        if (c >= 0 && c < cols) {
+          other_col[j] = (dir == 0 ? arc.src : arc.dest) | (c << 16);
+          w[j] = arc.score;
+          if (!kSmemFactors) ExpToMantExp(arc.score, &ewf[j], &ewk[j]);
+        }
+      }
+    }
+  }
+  if (kSmemFactors)
+    for (int32_t k = tid; k < f.num_arcs; k += nt) {
+      const Arc arc = arcs[dir == 0 ? in_arcs[f.arc_off + k] : f.arc_off + k];
+      ArcFactor af;
+      ExpToMantExp(arc.score, &af.f, &af.k);
+      af.pad = 0;
+      table[k] = af;
+    }
+  if (tid == 0) {
+    for (int st = 0; st < stages; ++st) MbarInit(&full[st], 1);
+    gave_up = 0;
+    MbarInitFence();
+  }
+  const float cutoff = cutoffs[i];
+  const float *fgrid = vfwd + f.grid_off, *bgrid = vbwd + f.grid_off;
+  ProbState *out = (dir == 0 ? alpha : beta) + f.grid_off;
+  // ---- first level ------------------------------------------------------------
+  {
+    const int64_t lv = dir == 0 ? 0 : Tk;
+    for (int32_t q = tid; q < S; q += nt) {
+      const float fu = fgrid[lv * S + q], bu = bgrid[lv * S + q];
+      const bool keep = __fadd_rn(fu, bu) > cutoff;
+      ProbState v;
+      v.pad = 0;
+      if (keep && q == (dir == 0 ? 0 : S - 1)) {
+        v.m = 1.0;
+        v.e = 0;
+      } else {
+        v.m = 0.0;
+        v.e = kZeroExp;
+      }
+      ps[q] = v;
+      oth[q] = keep ? (dir == 0 ? fu : bu) : -INFINITY;
+      out[lv * S + q] = v;
+    }
+  }
+  __syncthreads();  // barriers initialised, first level and table in place
+  // step t (1..Tk) handles level t (forward) / Tk - t (backward) and reads dense
+  // row t - 1 / Tk - t
+  const unsigned char *dense0 = dense + (int64_t)f.row0 * dp.pitch;
+  auto issue_row = [&](int32_t step) {  // thread 0 only
+    if (step > Tk) return;
+    const int32_t slot = (step - 1) % stages;
+    const int64_t row = dir == 0 ? step - 1 : Tk - step;
+    MbarArriveExpectTx(&full[slot], (unsigned)dp.pitch);
+    BulkCopyG2S(ring + (size_t)slot * dp.pitch, dense0 + row * dp.pitch, (unsigned)dp.pitch,
+                &full[slot]);
+  };
+  if (tid == 0)
+    for (int32_t step = 1; step < stages; ++step) issue_row(step);
+
+  // Viterbi scores of this lane's state for steps t .. t + kPF - 1
+  auto level_of = [&](int32_t step) {
+    step = step > Tk ? Tk : step;
+    return (int64_t)(dir == 0 ? step : Tk - step);
+  };
+  const int32_t s_ld = s >= 0 ? s : 0;
+  float fq[kPF], bq[kPF];
+#pragma unroll
+  for (int d = 0; d < kPF; ++d) {
+    const int64_t lv = level_of(1 + d);
+    fq[d] = fgrid[lv * S + s_ld];
+    bq[d] = bgrid[lv * S + s_ld];
+  }
+  ProbState last;
+  last.m = 0.0;
+  last.e = kZeroExp;
+  int32_t slot = 0;
+  unsigned parity = 0;
+  bool stop = false;
+  for (int32_t t0 = 1; t0 <= Tk && !stop; t0 += kPF) {
+#pragma unroll
+    for (int u = 0; u < kPF; ++u) {
+      const int32_t t = t0 + u;
+      if (t > Tk) break;
+      if (!MbarTryWait(&full[slot], parity) && !MbarWaitBounded(&full[slot], parity))
+        *reinterpret_cast<volatile int32_t *>(&gave_up) = 1;
+      __syncthreads();  // the previous frame is complete; nobody reads its slot any more
+      if (*reinterpret_cast<volatile int32_t *>(&gave_up)) {  // uniform
+        stop = true;
+        break;
+      }
+      if (tid == 0) issue_row(t + stages - 1);
+      const ProbState *prev = ps + ((t - 1) & 1) * s_pad;
+      ProbState *cur = ps + (t & 1) * s_pad;
+      const float *po = oth + ((t - 1) & 1) * s_pad;
+      float *co = oth + (t & 1) * s_pad;
+      const unsigned char *rec = ring + (size_t)slot * dp.pitch;
+      const float *lprow = PackLp(rec);
+      const double *prow = PackP(rec, dp);
+      slot = slot + 1 == stages ? 0 : slot + 1;
+      parity ^= (slot == 0);
+      const int64_t lv = dir == 0 ? t : Tk - t;
+      const float fu = fq[u], bu = bq[u];
+      {
+        const int64_t nlv = level_of(t + kPF);
+        fq[u] = fgrid[nlv * S + s_ld];
+        bq[u] = bgrid[nlv * S + s_ld];
+      }
+      const bool keep = s >= 0 && __fadd_rn(fu, bu) > cutoff;
+      // arcs in groups of up to four: the loads and multiplies of a group are
+      // independent, then the group joins the running (sum, E)
+      constexpr int kGroup = kDeg < 4 ? kDeg : 4;
+      double sum = 0.0;
+      int32_t E = kZeroExp;
+#pragma unroll
+      for (int j0 = 0; j0 < kDeg; j0 += kGroup) {
+        double tt[kGroup];
+        int32_t ee[kGroup];
+        int32_t Eg = kZeroExp;
+#pragma unroll
+        for (int jj = 0; jj < kGroup; ++jj) {
+          const int j = j0 + jj;
+          const int32_t o_idx = other_col[j] & 0xffff, c = other_col[j] >> 16;
+          const float sc = __fadd_rn(w[j], lprow[c]);
+          const float o = po[o_idx];
+          const float through = dir == 0 ? __fadd_rn(__fadd_rn(o, sc), bu)
+                                         : __fadd_rn(__fadd_rn(fu, sc), o);
+          tt[jj] = 0.0;
+          ee[jj] = kZeroExp;
+          if (keep && through > cutoff) {
+            const ProbState q = prev[o_idx];
+            double af_f;
+            int32_t af_k;
+            if (kSmemFactors) {
+              const ArcFactor af = table[tbl0 + j * G];
+              af_f = af.f;
+              af_k = af.k;
+            } else {
+              af_f = ewf[j];
+              af_k = ewk[j];
+            }
+            int32_t ex;
+            tt[jj] = SplitExp(q.m * af_f * prow[c], &ex);
+            if (tt[jj] != 0.0) ee[jj] = q.e + af_k + ex;
+          }
+          Eg = ee[jj] > Eg ? ee[jj] : Eg;
+        }
+        const int32_t En = Eg > E ? Eg : E;
+        sum = ScaleDown(sum, E - En);
+#pragma unroll
+        for (int jj = 0; jj < kGroup; ++jj) sum += ScaleDown(tt[jj], ee[jj] - En);
+        E = En;
+      }
+      if (plan != nullptr) {  // uniform: lanes of a state merge into lane g == 0
+#pragma unroll
+        for (int32_t d = 16; d > 0; d >>= 1) {
+          const int32_t Eo = __shfl_down_sync(0xffffffffu, E, d);
+          const double so = __shfl_down_sync(0xffffffffu, sum, d);
+          if (g + d < G) {
+            const int32_t En = Eo > E ? Eo : E;
+            sum = ScaleDown(sum, E - En) + ScaleDown(so, Eo - En);
+            E = En;
+          }
+        }
+      }
+      if (s >= 0 && g == 0) {
+        ProbState r;
+        r.e = E;
+        r.m = Renorm(sum, &r.e);
+        r.pad = 0;
+        cur[s] = r;
+        co[s] = keep ? (dir == 0 ? fu : bu) : -INFINITY;
+        out[lv * S + s] = r;
+        last = r;
+      }
+    }
+  }
+  if (*reinterpret_cast<volatile int32_t *>(&gave_up)) {
+    if (tid == 0) {
+      atomicOr(&unfit[i], 1);
+      // copies may still be in flight towards this CTA's shared memory: give them
+      // a bounded while before the CTA retires
+      for (int k = 0; k < 1000; ++k) __nanosleep(1000);
+    }
+    __syncthreads();
+    return;
+  }
+  if (dir == 0 && s == S - 1 && g == 0)
+    tot[i] = last.m == 0.0 ? -INFINITY
+                           : log(last.m) + (double)last.e * 0.69314718055994530942;
+}
+
+// ---------------------------------------------------------------------------
+// Gradients.  grid = (frame chunks, pairs): frames do not depend on one another,
+// so the GPU is filled with (pair, chunk) CTAs and every warp of a CTA takes whole
+// frames.  For its frame u the warp scans the states 32 at a time, keeps the
+// surviving ones as a bit mask, and hands them to groups of 2^lanes_log2 lanes;
+// the lanes of a group walk the arcs leaving the state, run the pruning test and
+// add posterior = alpha[u][src] * w * p(u, label) * beta[u+1][dest] / Z to
+//   * gb[u - u0][label + 1] in shared memory, written to grad_b once per CTA;
+//   * ga[arc] in shared memory (global memory for very large graphs), added to
+//     grad_a once per CTA.
+// With kStage the warp first copies what the arcs of the frame can touch - beta
+// and the backward Viterbi score of level u + 1 - into its own shared-memory
+// scratch, so that the arc loop has no dependent global loads (small, dense
+// graphs); without it those are gathered from global memory (large sparse ones).
+// ---------------------------------------------------------------------------
+struct __align__(16) NextState {
+  double m;
+  int32_t e;
+  float bo;  // backward Viterbi score, -inf when the state was pruned
+};
+
+constexpr int kGradWarps = 8;
+
+template <bool kStage>
+__global__ void __launch_bounds__(kGradWarps * 32)
+GridGradWarp(const FsaInfo *__restrict__ infos, const Arc *__restrict__ arcs,
+             const ArcFactor *__restrict__ arc_factors,
+             const int32_t *__restrict__ a_row_splits2, const unsigned char *__restrict__ dense,
+             DensePack dp, const float *__restrict__ vfwd, const float *__restrict__ vbwd,
+             const float *__restrict__ cutoffs, const ProbState *__restrict__ alpha,
+             const ProbState *__restrict__ beta, const double *__restrict__ tot_grad,
+             int32_t tot_grad_stride, float *__restrict__ grad_a, float *__restrict__ grad_b,
+             int32_t frames_per_cta, int32_t lanes_log2, int32_t s_pad, int32_t ga_in_smem,
+             int32_t exclusive_rows) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  const int32_t i = blockIdx.y;
+  const FsaInfo f = infos[i];
+  const int32_t S = f.num_states, A = f.num_arcs, Tk = f.tk, cols = dp.cols;
+  const int32_t u0 = blockIdx.x * frames_per_cta;
+  if (S == 0 || u0 >= Tk) return;
+  const int32_t u1 = min(u0 + frames_per_cta, Tk);
+  const int tid = threadIdx.x, nt = blockDim.x, lane = tid & 31, warp = tid >> 5;
+  NextState *nb_all = reinterpret_cast<NextState *>(smem_raw);  // [warps][s_pad] if kStage
+  float *gb = reinterpret_cast<float *>(nb_all + (kStage ? kGradWarps * s_pad : 0));
+  float *ga = gb + (((size_t)frames_per_cta * cols + 3) & ~(size_t)3);  // [A] when ga_in_smem
+  const ProbState *al = alpha + f.grid_off, *be = beta + f.grid_off;
+  const ProbState z = al[(int64_t)Tk * S + (S - 1)];
+  if (z.m == 0.0) return;  // no path survives: all gradients are zero
+  const double zinv = tot_grad[(int64_t)i * tot_grad_stride] / z.m;
+  const int32_t zk = -z.e;
+  const int32_t gb_elems = (u1 - u0) * cols;
+  for (int32_t k = tid; k < gb_elems; k += nt) gb[k] = 0.0f;
+  if (ga_in_smem)
+    for (int32_t k = tid; k < A; k += nt) ga[k] = 0.0f;
+  __syncthreads();
+  const float cutoff = cutoffs[i];
+  const float *fgrid = vfwd + f.grid_off, *bgrid = vbwd + f.grid_off;
+  const Arc *my_arcs = arcs + f.arc_off;
+  const ArcFactor *my_factors = arc_factors + f.arc_off;
+  const int32_t *splits = a_row_splits2 + f.state_off;
+  const int32_t lg = lanes_log2, G = 1 << lg, sub = lane & (G - 1), grp = lane >> lg,
+                groups = 32 >> lg;
+  NextState *nb = nb_all + warp * s_pad;
+  for (int32_t u = u0 + warp; u < u1; u += kGradWarps) {
+    const int64_t cur = (int64_t)u * S, nxt = (int64_t)(u + 1) * S;
+    if (kStage) {
+      __syncwarp();  // the previous frame's readers are done with nb
+      for (int32_t q = lane; q < S; q += 32) {
+        const float fn = fgrid[nxt + q], bn = bgrid[nxt + q];
+        const ProbState b = be[nxt + q];
+        NextState nx;
+        nx.m = b.m;
+        nx.e = b.e;
+        nx.bo = __fadd_rn(fn, bn) > cutoff ? bn : -INFINITY;
+        nb[q] = nx;
+      }
+      __syncwarp();
+    }
+    const unsigned char *rec = dense + ((int64_t)f.row0 + u) * dp.pitch;
+    const float *lprow = PackLp(rec);
+    const double *prow = PackP(rec, dp);
+    float *gbrow = gb + (size_t)(u - u0) * cols;
+    for (int32_t c0 = 0; c0 < S; c0 += 32) {
+      const int32_t q = c0 + lane;
+      float fu = -INFINITY, bu = -INFINITY;
+      if (q < S) {
+        fu = fgrid[cur + q];
+        bu = bgrid[cur + q];
+      }
+      ProbState a;
+      a.m = 0.0;
+      a.e = kZeroExp;
+      if (__fadd_rn(fu, bu) > cutoff) a = al[cur + q];
+      const uint32_t m = __ballot_sync(0xffffffffu, a.m != 0.0);
+      const int32_t kept = __popc(m);
+      for (int32_t r0 = 0; r0 < kept; r0 += groups) {  // warp-uniform
+        const int32_t nth = r0 + grp;
+        const int32_t owner = nth < kept ? (int32_t)__fns(m, 0, nth + 1) : 0;
+        const float fs = __shfl_sync(0xffffffffu, fu, owner);
+        const double am = __shfl_sync(0xffffffffu, a.m, owner);
+        const int32_t ae = __shfl_sync(0xffffffffu, a.e, owner);
+        if (nth >= kept) continue;
+        const int32_t sq = c0 + owner;
+        const int32_t k1 = splits[sq + 1] - f.arc_off;
+        for (int32_t k = splits[sq] - f.arc_off + sub; k < k1; k += G) {
+          const Arc arc = my_arcs[k];
+          const int32_t c = arc.label + 1;
+          if (c < 0 || c >= cols) continue;
+          const float sc = __fadd_rn(arc.score, lprow[c]);
+          double bm;
+          int32_t bexp;
+          if (kStage) {
+            const NextState nx = nb[arc.dest];
+            if (!(__fadd_rn(__fadd_rn(fs, sc), nx.bo) > cutoff)) continue;
+            bm = nx.m;
+            bexp = nx.e;
+          } else {
+            const float fn = fgrid[nxt + arc.dest], bn = bgrid[nxt + arc.dest];
+            if (!(__fadd_rn(fn, bn) > cutoff)) continue;
+            if (!(__fadd_rn(__fadd_rn(fs, sc), bn) > cutoff)) continue;
+            const ProbState b = be[nxt + arc.dest];
+            bm = b.m;
+            bexp = b.e;
+          }
+          const ArcFactor af = my_factors[k];
+          const double prod = am * af.f * prow[c] * bm * zinv;
+          if (prod == 0.0) continue;
+          const float post = (float)scalbn(prod, ae + af.k + bexp + zk);
+          atomicAdd(&gbrow[c], post);
+          atomicAdd(ga_in_smem ? &ga[k] : &grad_a[f.arc_off + k], post);
+        }
+      }
+    }
+  }
+  __syncthreads();
+  float *grow = grad_b + ((int64_t)f.row0 + u0) * cols;
+  for (int32_t k = tid; k < gb_elems; k += nt) {
+    const float v = gb[k];
+    if (v != 0.0f) {
+      if (exclusive_rows) grow[k] = v; else atomicAdd(&grow[k], v);
+    }
+  }
+  if (ga_in_smem)
+    for (int32_t k = tid; k < A; k += nt) {
+      const float v = ga[k];
+      if (v != 0.0f) atomicAdd(&grad_a[f.arc_off + k], v);
+    }
+}
+
+// ---------------------------------------------------------------------------
+// Shared-memory variants for the graphs PlanLanes could not place (very high or
+// very uneven degrees): the arcs sit in shared memory (incoming order walking
+// forward, leaving order walking backward) and G = 2^lanes_log2 lanes per state
+// loop over them; dense rows are staged with 16-byte cp.async.  Slower, any degree.
+// With only_unfit set they skip every graph the lane kernels handled.
+// ---------------------------------------------------------------------------
+struct ChainPlan {
+  int32_t s_pad, a_pad, stages, lanes_log2, threads;
+  size_t bytes;
+};
+
+static ChainPlan PlanChain(const Layout &L, const k2b200_intersect_args *a, const DensePack &d) {
+  ChainPlan p;
+  p.s_pad = (L.max_states + 1 + 3) & ~3;
+  p.a_pad = (L.max_arcs + 3) & ~3;
+  size_t fixed = sizeof(ProbState) * 2 * p.s_pad + (size_t)24 * p.a_pad +
+                 sizeof(float) * 2 * p.s_pad + sizeof(int32_t) * p.s_pad;
+  p.stages = 0;
+  if (fixed < kChainSmemBudget)
+    p.stages = (int32_t)std::min<size_t>(8, (kChainSmemBudget - fixed) / d.pitch);
+  p.bytes = fixed + (size_t)d.pitch * std::max(p.stages, 0);
+  int32_t mean_deg = a->num_states > 0 ? (a->num_arcs + a->num_states - 1) / a->num_states : 1;
+  int32_t lg = 0;
+  while ((2 << lg) <= mean_deg / 2 && lg < 5) ++lg;
+  while (lg > 0 && ((int64_t)L.max_states << lg) > 1024) --lg;
+  p.lanes_log2 = lg;
+  int64_t lanes = (int64_t)L.max_states << lg;
+  p.threads = (int32_t)std::min<int64_t>(1024, std::max<int64_t>(128, (lanes + 31) / 32 * 32));
+  return p;
+}
+
+__global__ void __launch_bounds__(1024)
+GridChain(const FsaInfo *__restrict__ infos, const Arc *__restrict__ arcs,
+          const int32_t *__restrict__ a_row_splits2, const int32_t *__restrict__ in_splits,
+          const int32_t *__restrict__ in_arcs, const unsigned char *__restrict__ dense,
+          DensePack dp, const float *__restrict__ vfwd, const float *__restrict__ vbwd,
+          const float *__restrict__ cutoffs, ProbState *__restrict__ alpha,
+          ProbState *__restrict__ beta, double *__restrict__ tot,
+          const int32_t *__restrict__ only_unfit, ChainPlan p) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  const int32_t i = blockIdx.y;
+  if (only_unfit != nullptr && !only_unfit[i]) return;
+  const FsaInfo f = infos[i];
+  const int dir = blockIdx.x;  // 0 forward, 1 backward
+  const int32_t S = f.num_states, A = f.num_arcs, Tk = f.tk, cols = dp.cols;
+  const int tid = threadIdx.x, nt = blockDim.x;
+  if (S == 0) {
+    if (dir == 0 && tid == 0) tot[i] = -INFINITY;
+    return;
+  }
+  const int32_t s_pad = p.s_pad, stages = p.stages;
+  unsigned char *ring = smem_raw;                                              // [stages][pitch]
+  ProbState *ps = reinterpret_cast<ProbState *>(ring + (size_t)stages * dp.pitch);  // [2][s_pad]
+  int4 *meta = reinterpret_cast<int4 *>(ps + 2 * s_pad);                       // [a_pad]
+  double *ewf = reinterpret_cast<double *>(meta + p.a_pad);                    // [a_pad]
+  float *oth = reinterpret_cast<float *>(ewf + p.a_pad);                       // [2][s_pad]
+  int32_t *splits = reinterpret_cast<int32_t *>(oth + 2 * s_pad);              // [s_pad]
+
+  // ---- stage the graph ------------------------------------------------------
+  const int32_t *gsplits = (dir == 0 ? in_splits : a_row_splits2) + f.state_off;
+  for (int32_t s = tid; s <= S; s += nt) splits[s] = gsplits[s] - f.arc_off;
+  for (int32_t k = tid; k < A; k += nt) {
+    const Arc arc = arcs[dir == 0 ? in_arcs[f.arc_off + k] : f.arc_off + k];
+    double ef;
+    int32_t ek;
+    ExpToMantExp(arc.score, &ef, &ek);
+    const int32_t c = arc.label + 1;
+    meta[k] = make_int4(dir == 0 ? arc.src : arc.dest, (c >= 0 && c < cols) ? c : cols,
+                        __float_as_int(arc.score), ek);
+    ewf[k] = ef;
+  }
+  const float cutoff = cutoffs[i];
+  const float *fgrid = vfwd + f.grid_off, *bgrid = vbwd + f.grid_off;
+  ProbState *out = (dir == 0 ? alpha : beta) + f.grid_off;
+  {
+    const int64_t lv = dir == 0 ? 0 : Tk;
+    for (int32_t s = tid; s < S; s += nt) {
+      const float fu = fgrid[lv * S + s], bu = bgrid[lv * S + s];
+      const bool keep = __fadd_rn(fu, bu) > cutoff;
+      ProbState v;
+      v.pad = 0;
+      if (keep && s == (dir == 0 ? 0 : S - 1)) {
+        v.m = 1.0;
+        v.e = 0;
+      } else {
+        v.m = 0.0;
+        v.e = kZeroExp;
+      }
+      ps[s] = v;
+      oth[s] = keep ? (dir == 0 ? fu : bu) : -INFINITY;
+      out[lv * S + s] = v;
+    }
+  }
+  const unsigned char *dense0 = dense + (int64_t)f.row0 * dp.pitch;
+  const int32_t chunks = dp.pitch / 16;
+  auto issue_row = [&](int32_t step) {
+    if (step <= Tk) {
+      const int64_t row = dir == 0 ? step - 1 : Tk - step;
+      const unsigned char *src = dense0 + row * dp.pitch;
+      unsigned char *dst = ring + (size_t)((step - 1) % stages) * dp.pitch;
+      for (int32_t c = tid; c < chunks; c += nt) CpAsync16(dst + 16 * c, src + 16 * c);
+    }
+    CpAsyncCommit();
+  };
+  for (int32_t step = 1; step < stages; ++step) issue_row(step);
+
+  const int32_t lg = p.lanes_log2, G = 1 << lg, g = tid & (G - 1);
+  const int32_t per_pass = nt >> lg;
+  const int32_t s_own = tid >> lg;
+  ProbState last;
+  last.m = 0.0;
+  last.e = kZeroExp;
+  for (int32_t t = 1; t <= Tk; ++t) {
+    CpAsyncWaitDyn(stages - 2);
+    __syncthreads();
+    issue_row(t + stages - 1);
+    const ProbState *prev = ps + ((t - 1) & 1) * s_pad;
+    ProbState *cur = ps + (t & 1) * s_pad;
+    const float *po = oth + ((t - 1) & 1) * s_pad;
+    float *co = oth + (t & 1) * s_pad;
+    const unsigned char *rec = ring + (size_t)((t - 1) % stages) * dp.pitch;
+    const float *lprow = PackLp(rec);
+    const double *prow = PackP(rec, dp);
+    const int64_t lv = dir == 0 ? t : Tk - t;
+    for (int32_t s0 = 0; s0 < S; s0 += per_pass) {
+      const int32_t s = s0 + s_own;
+      float fu = -INFINITY, bu = -INFINITY;
+      if (s < S) {
+        fu = fgrid[lv * S + s];
+        bu = bgrid[lv * S + s];
+      }
+      const bool keep = s < S && __fadd_rn(fu, bu) > cutoff;
+      double sum = 0.0;
+      int32_t E = kZeroExp;
+      if (keep) {
+        const int32_t k1 = splits[s + 1];
+        for (int32_t k = splits[s] + g; k < k1; k += G) {
+          const int4 m = meta[k];
+          const float sc = __fadd_rn(__int_as_float(m.z), lprow[m.y]);
+          const float o = po[m.x];
+          const float through = dir == 0 ? __fadd_rn(__fadd_rn(o, sc), bu)
+                                         : __fadd_rn(__fadd_rn(fu, sc), o);
+          if (through > cutoff) {
+            const ProbState q = prev[m.x];
+            int32_t ex;
+            const double t0 = SplitExp(q.m * ewf[k] * prow[m.y], &ex);
+            const int32_t e0 = t0 != 0.0 ? q.e + m.w + ex : kZeroExp;
+            const int32_t En = E > e0 ? E : e0;
+            sum = ScaleDown(sum, E - En) + ScaleDown(t0, e0 - En);
+            E = En;
+          }
+        }
+      }
+      for (int32_t d = G >> 1; d > 0; d >>= 1) {
+        const int32_t Eo = __shfl_xor_sync(0xffffffffu, E, d);
+        const double so = __shfl_xor_sync(0xffffffffu, sum, d);
+        const int32_t En = Eo > E ? Eo : E;
+        sum = ScaleDown(sum, E - En) + ScaleDown(so, Eo - En);
+        E = En;
+      }
+      if (s < S && g == 0) {
+        ProbState r;
+        r.e = E;
+        r.m = Renorm(sum, &r.e);
+        r.pad = 0;
+        cur[s] = r;
+        co[s] = keep ? (dir == 0 ? fu : bu) : -INFINITY;
+        out[lv * S + s] = r;
+        if (s == S - 1) last = r;
+      }
+    }
+  }
+  CpAsyncWait<0>();
+  // the thread that owns the final state holds alpha[Tk][final]
+  if (dir == 0 && g == 0 && ((S - 1) % per_pass) == s_own)
+    tot[i] = last.m == 0.0 ? -INFINITY
+                           : log(last.m) + (double)last.e * 0.69314718055994530942;
+}
+
+// ---------------------------------------------------------------------------
+// host side
+// ---------------------------------------------------------------------------
+struct LossLayout {
+  Layout base;
+  DensePack pack;
+  size_t off_dense, off_arc_factors, off_alpha, off_beta, off_plan, off_unfit, total_bytes;
+  bool exclusive_rows;
+  int32_t k_deg;      // arcs per lane of the lane kernel
+  bool identity;      // every degree <= k_deg: thread s owns state s, no plan
+  int32_t threads;    // CTA size of the lane kernel
+};
+
+static int32_t MakeLossLayout(const k2b200_intersect_args *a, LossLayout *LL) {
+  K2B_FORWARD(MakeLayout(a, &LL->base));
+  LL->pack = MakeDensePack(a->cols);
+  LL->identity = a->a_max_degree > 0 && a->a_max_degree <= 4 && LL->base.max_states <= 1024;
+  LL->k_deg = LL->identity ? (a->a_max_degree <= 3 ? 3 : 4) : 8;
+  LL->threads = LL->identity ? std::max(32, (LL->base.max_states + 31) / 32 * 32) : kLaneThreads;
+  size_t off = AlignUp(LL->base.total_bytes);
+  auto take = [&](size_t bytes) {
+    size_t o = off;
+    off += AlignUp(bytes ? bytes : 1);
+    return o;
+  };
+  LL->off_dense = take((size_t)LL->pack.pitch * (size_t)a->rows);
+  LL->off_arc_factors = take(sizeof(ArcFactor) * (size_t)std::max(a->num_arcs, 1));
+  LL->off_alpha = take(sizeof(ProbState) * (size_t)LL->base.grid_elems);
+  LL->off_beta = take(sizeof(ProbState) * (size_t)LL->base.grid_elems);
+  LL->off_plan = take(LL->identity ? 0 : sizeof(int32_t) * 2 * (size_t)a->num_fsas * kLaneThreads);
+  LL->off_unfit = take(sizeof(int32_t) * (size_t)a->num_fsas);
+  LL->total_bytes = off;
+  // two graphs on one sequence write the same rows of the dense gradient
+  LL->exclusive_rows = true;
+  if (a->h_a_to_b_map)
+    for (int32_t i = 1; i < a->num_fsas; ++i)
+      if (a->h_a_to_b_map[i] == a->h_a_to_b_map[i - 1]) LL->exclusive_rows = false;
+  return kOk;
+}
+
+static bool LossFits(const LossLayout &LL, const k2b200_intersect_args *a, ChainPlan *p,
+                     LaneSmem *ls) {
+  *p = PlanChain(LL.base, a, LL.pack);
+  *ls = PlanLaneSmem(LL.base, LL.pack, !LL.identity);
+  return p->stages >= 2 && ls->stages >= 2 && a->num_fsas <= 65535 && a->cols < 32768 &&
+         LL.base.max_states < 65536;
+}
+
+template <int kDeg, bool kSmemFactors, int kPF, int kMaxThreads>
+static int32_t LaunchChainLanes(const LossLayout &LL, const k2b200_intersect_args *args, char *ws,
+                                const LaneSmem &ls, double *tot, cudaStream_t stream) {
+  const Layout &L = LL.base;
+  K2B_CUDA_OK(cudaFuncSetAttribute(GridChainLanes<kDeg, kSmemFactors, kPF, kMaxThreads>,
+                                   cudaFuncAttributeMaxDynamicSharedMemorySize, (int)ls.bytes));
+  dim3 grid(2, args->num_fsas);
+  { GridChainLanes<kDeg, kSmemFactors, kPF, kMaxThreads><<<grid, LL.threads, ls.bytes, stream>>>(
+      reinterpret_cast<const FsaInfo *>(ws + L.off_infos), args->num_fsas,
+      reinterpret_cast<const Arc *>(args->a_arcs), args->a_row_splits2, args->a_in_splits,
+      args->a_in_arcs, reinterpret_cast<const unsigned char *>(ws + LL.off_dense), LL.pack,
+      reinterpret_cast<const float *>(ws + L.off_fwd),
+      reinterpret_cast<const float *>(ws + L.off_bwd),
+      reinterpret_cast<const float *>(ws + L.off_cutoffs),
+      reinterpret_cast<ProbState *>(ws + LL.off_alpha),
+      reinterpret_cast<ProbState *>(ws + LL.off_beta), tot,
+      LL.identity ? nullptr : reinterpret_cast<const int32_t *>(ws + LL.off_plan),
+      reinterpret_cast<int32_t *>(ws + LL.off_unfit), ls); NoteLaunch(); }
+  K2B_CUDA_OK(cudaGetLastError());
+  return kOk;
+}
+
+template <bool kStage>
+static int32_t LaunchGrad(const LossLayout &LL, const k2b200_intersect_args *args, char *ws,
+                          const double *tot_grad, int32_t stride, float *grad_a, float *grad_b,
+                          cudaStream_t stream) {
+  const Layout &L = LL.base;
+  const int32_t s_pad = (L.max_states + 3) & ~3;
+  const size_t nb_bytes = kStage ? sizeof(NextState) * kGradWarps * (size_t)s_pad : 0;
+  // frames per CTA: the chunk's rows of the dense gradient live in shared memory
+  int32_t frames = 32;
+  while (frames > kGradWarps && sizeof(float) * (size_t)frames * args->cols > 48 * 1024)
+    frames >>= 1;
+  const size_t gb_bytes = sizeof(float) * (((size_t)frames * args->cols + 3) & ~(size_t)3);
+  const size_t ga_bytes = sizeof(float) * (size_t)L.max_arcs;
+  size_t smem = nb_bytes + gb_bytes;
+  const int32_t ga_in_smem = smem + ga_bytes <= 100 * 1024;
+  if (ga_in_smem) smem += ga_bytes;
+  K2B_REQUIRE(smem <= kChainSmemBudget, "too many columns for the fused loss path");
+  K2B_CUDA_OK(cudaFuncSetAttribute(GridGradWarp<kStage>,
+                                   cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  // lanes per surviving state: about the mean out-degree
+  int32_t mean_deg =
+      args->num_states > 0 ? (args->num_arcs + args->num_states - 1) / args->num_states : 1;
+  int32_t lg = 0;
+  while ((1 << lg) < mean_deg && lg < 5) ++lg;
+  dim3 grid(CeilDiv(L.max_tk, frames), args->num_fsas);
+  { GridGradWarp<kStage><<<grid, kGradWarps * 32, smem, stream>>>(
+      reinterpret_cast<const FsaInfo *>(ws + L.off_infos),
+      reinterpret_cast<const Arc *>(args->a_arcs),
+      reinterpret_cast<const ArcFactor *>(ws + LL.off_arc_factors), args->a_row_splits2,
+      reinterpret_cast<const unsigned char *>(ws + LL.off_dense), LL.pack,
+      reinterpret_cast<const float *>(ws + L.off_fwd),
+      reinterpret_cast<const float *>(ws + L.off_bwd),
+      reinterpret_cast<const float *>(ws + L.off_cutoffs),
+      reinterpret_cast<const ProbState *>(ws + LL.off_alpha),
+      reinterpret_cast<const ProbState *>(ws + LL.off_beta), tot_grad, stride, grad_a, grad_b,
+      frames, lg, s_pad, ga_in_smem, LL.exclusive_rows ? 1 : 0); NoteLaunch(); }
+  K2B_CUDA_OK(cudaGetLastError());
+  return kOk;
+}
+
+}  // namespace k2b
+
+using namespace k2b;
+
+extern "C" {
+
+int32_t k2b200_dense_loss_supported(const k2b200_intersect_args *args, int32_t *supported) {
+  K2B_REQUIRE(supported != nullptr, "NULL output pointer");
+  LossLayout LL;
+  K2B_FORWARD(MakeLossLayout(args, &LL));
+  ChainPlan p;
+  LaneSmem ls;
+  *supported = LossFits(LL, args, &p, &ls) ? 1 : 0;
+  return kOk;
+}
+
+int32_t k2b200_dense_loss_workspace_bytes(const k2b200_intersect_args *args, size_t *bytes) {
+  K2B_REQUIRE(bytes != nullptr, "NULL output pointer");
+  LossLayout LL;
+  K2B_FORWARD(MakeLossLayout(args, &LL));
+  *bytes = LL.total_bytes;
+  return kOk;
+}
+
+int32_t k2b200_dense_loss_forward(const k2b200_intersect_args *args, void *workspace,
+                                  size_t workspace_bytes, void *stream_v, double *tot_scores,
+                                  float *beam_used) {
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_v);
+  LossLayout LL;
+  K2B_FORWARD(MakeLossLayout(args, &LL));
+  const Layout &L = LL.base;
+  if (workspace == nullptr || workspace_bytes < LL.total_bytes) {
+    SetError("workspace of %zu bytes is smaller than the %zu required", workspace_bytes,
+             LL.total_bytes);
+    return kWorkspaceTooSmall;
+  }
+  K2B_REQUIRE(args->a_row_splits1 && args->a_row_splits2 && args->a_arcs && args->a_in_splits &&
+                  args->a_in_arcs && args->scores && tot_scores,
+              "NULL device pointer");
+  ChainPlan p;
+  LaneSmem ls;
+  K2B_REQUIRE(LossFits(LL, args, &p, &ls),
+              "graphs too large for the fused loss path (%d states, %d arcs, %d columns): "
+              "use intersect_dense + get_tot_scores",
+              L.max_states, L.max_arcs, args->cols);
+  char *ws = reinterpret_cast<char *>(workspace);
+  K2B_CUDA_OK(cudaMemcpyAsync(ws + L.off_infos, L.infos.data(), sizeof(FsaInfo) * args->num_fsas,
+                              cudaMemcpyHostToDevice, stream));
+  const FsaInfo *d_infos = reinterpret_cast<const FsaInfo *>(ws + L.off_infos);
+  unsigned char *dense = reinterpret_cast<unsigned char *>(ws + LL.off_dense);
+  int32_t *unfit = reinterpret_cast<int32_t *>(ws + LL.off_unfit);
+  int32_t *plan = reinterpret_cast<int32_t *>(ws + LL.off_plan);
+  {
+    PhaseTimer timer(kPhaseChain, stream);
+    const int64_t n_dense = (int64_t)args->rows * LL.pack.cols4;
+    { ExpDense<<<(int)std::min<int64_t>(CeilDiv(n_dense, 256), 148 * 32), 256, 0, stream>>>(
+        args->scores, args->rows, LL.pack, dense); NoteLaunch(); }
+    K2B_CUDA_OK(cudaMemsetAsync(unfit, 0, sizeof(int32_t) * args->num_fsas, stream));
+    if (!LL.identity)
+      { PlanLanes<<<dim3(2, args->num_fsas), 256, 0, stream>>>(
+          d_infos, args->num_fsas, args->a_row_splits2, args->a_in_splits, LL.k_deg, plan,
+          unfit); NoteLaunch(); }
+  }
+  {
+    PhaseTimer timer(kPhaseViterbi, stream);
+    K2B_FORWARD(RunViterbi(L, args, ws, stream));
+  }
+  // The lattice is never built, but its size still decides the beam
+  // (intersect_dense.cu:300-320).  The grid itself bounds it: count only when the
+  // bound does not already satisfy the limits.
+  float beam = args->output_beam;
+  long long arc_frames = 0;
+  for (const FsaInfo &f : L.infos) arc_frames += (long long)f.tk * f.num_arcs;
+  if (L.grid_elems > args->max_states || arc_frames > args->max_arcs) {
+    long long h_totals[5];
+    K2B_FORWARD(PruneLoop(L, args, ws, stream, &beam, h_totals));
+  } else {
+    K2B_FORWARD(LaunchCutoffs(L, args, ws, beam, stream));
+  }
+  if (beam_used) *beam_used = beam;
+  {
+    PhaseTimer timer(kPhaseChain, stream);
+    if (LL.k_deg == 3 && LL.threads <= 512)
+      K2B_FORWARD((LaunchChainLanes<3, false, 6, 512>(LL, args, ws, ls, tot_scores, stream)));
+    else if (LL.k_deg == 3)
+      K2B_FORWARD((LaunchChainLanes<3, false, 6, 1024>(LL, args, ws, ls, tot_scores, stream)));
+    else if (LL.k_deg == 4 && LL.threads <= 512)
+      K2B_FORWARD((LaunchChainLanes<4, false, 6, 512>(LL, args, ws, ls, tot_scores, stream)));
+    else if (LL.k_deg == 4)
+      K2B_FORWARD((LaunchChainLanes<4, false, 4, 1024>(LL, args, ws, ls, tot_scores, stream)));
+    else
+      K2B_FORWARD((LaunchChainLanes<8, true, 4, kLaneThreads>(LL, args, ws, ls, tot_scores,
+                                                              stream)));
+    // graphs the lane kernel skipped or gave up on
+    K2B_CUDA_OK(cudaFuncSetAttribute(GridChain, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     (int)p.bytes));
+    dim3 grid(2, args->num_fsas);
+    { GridChain<<<grid, p.threads, p.bytes, stream>>>(
+        d_infos, reinterpret_cast<const Arc *>(args->a_arcs), args->a_row_splits2,
+        args->a_in_splits, args->a_in_arcs, dense, LL.pack,
+        reinterpret_cast<const float *>(ws + L.off_fwd),
+        reinterpret_cast<const float *>(ws + L.off_bwd),
+        reinterpret_cast<const float *>(ws + L.off_cutoffs),
+        reinterpret_cast<ProbState *>(ws + LL.off_alpha),
+        reinterpret_cast<ProbState *>(ws + LL.off_beta), tot_scores, unfit, p); NoteLaunch(); }
+  }
+  K2B_CUDA_OK(cudaGetLastError());
+  return kOk;
+}
+
+int32_t k2b200_dense_loss_backward(const k2b200_intersect_args *args, void *workspace,
+                                   size_t workspace_bytes, const double *tot_grad,
+                                   int32_t tot_grad_stride, float *grad_a, float *grad_b,
+                                   void *stream_v) {
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_v);
+  LossLayout LL;
+  K2B_FORWARD(MakeLossLayout(args, &LL));
+  const Layout &L = LL.base;
+  if (workspace == nullptr || workspace_bytes < LL.total_bytes) {
+    SetError("workspace of %zu bytes is smaller than the %zu required", workspace_bytes,
+             LL.total_bytes);
+    return kWorkspaceTooSmall;
+  }
+  K2B_REQUIRE(tot_grad && grad_a && grad_b, "NULL device pointer");
+  if (L.max_states == 0 || L.max_tk == 0) return kOk;
+  char *ws = reinterpret_cast<char *>(workspace);
+  PhaseTimer timer(kPhaseGrad, stream);
+  if (args->num_arcs > 0)
+    { ExpArcs<<<CeilDiv(args->num_arcs, 256), 256, 0, stream>>>(
+        reinterpret_cast<const Arc *>(args->a_arcs), args->num_arcs,
+        reinterpret_cast<ArcFactor *>(ws + LL.off_arc_factors)); NoteLaunch(); }
+  // small graphs: stage level u + 1 per warp; large ones: gather
+  if (L.max_states <= 256)
+    return LaunchGrad<true>(LL, args, ws, tot_grad, tot_grad_stride, grad_a, grad_b, stream);
+  return LaunchGrad<false>(LL, args, ws, tot_grad, tot_grad_stride, grad_a, grad_b, stream);
+}
+
+}  // extern "C"

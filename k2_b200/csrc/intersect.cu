@@ -23,7 +23,7 @@ namespace k2b {
 constexpr int kCountThreads = 256;
 constexpr int kWordsPerCtaHost = 4 * 4 * (kCountThreads / 32);  // == kWordsPerCta below
 
-static int32_t MakeLayout(const k2b200_intersect_args *a, Layout *L) {
+int32_t MakeLayout(const k2b200_intersect_args *a, Layout *L) {
   K2B_REQUIRE(a != nullptr, "args is NULL");
   K2B_REQUIRE(a->num_fsas > 0, "a_fsas must contain at least one FSA (got %d)", a->num_fsas);
   K2B_REQUIRE(a->output_beam > 0, "output_beam must be > 0 (got %f)", a->output_beam);
@@ -490,7 +490,7 @@ __global__ void EmitTails(const FsaInfo *__restrict__ infos, int32_t n, int64_t 
     for (int32_t t = 0; t <= f.tk; ++t) out.level_splits[f.level_off + t] = first;
 }
 
-static int32_t RunViterbi(const Layout &L, const k2b200_intersect_args *a, char *ws,
+int32_t RunViterbi(const Layout &L, const k2b200_intersect_args *a, char *ws,
                           cudaStream_t stream) {
   const FsaInfo *d_infos = reinterpret_cast<const FsaInfo *>(ws + L.off_infos);
   float *fwd = reinterpret_cast<float *>(ws + L.off_fwd),
@@ -523,6 +523,81 @@ static int32_t RunViterbi(const Layout &L, const k2b200_intersect_args *a, char 
                                           lanes_log2); NoteLaunch(); }
   }
   K2B_CUDA_OK(cudaGetLastError());
+  return kOk;
+}
+
+
+int32_t LaunchCutoffs(const Layout &L, const k2b200_intersect_args *a, char *ws, float beam,
+                      cudaStream_t stream) {
+  { Cutoffs<<<CeilDiv(a->num_fsas, 128), 128, 0, stream>>>(
+      reinterpret_cast<const FsaInfo *>(ws + L.off_infos), a->num_fsas,
+      reinterpret_cast<const float *>(ws + L.off_fwd),
+      reinterpret_cast<const float *>(ws + L.off_bwd), beam,
+      reinterpret_cast<float *>(ws + L.off_cutoffs)); NoteLaunch(); }
+  K2B_CUDA_OK(cudaGetLastError());
+  return kOk;
+}
+
+// Keep masks, counts and numbering for the current beam, shrinking the beam as the
+// reference does (intersect_dense.cu:300-320 and :854-862) until the lattice fits
+// max_states / max_arcs.  One host synchronisation per iteration.  h_totals:
+// states, arcs, candidate arcs, largest layer in states and in arcs.
+int32_t PruneLoop(const Layout &L, const k2b200_intersect_args *args, char *ws,
+                  cudaStream_t stream, float *beam_io, long long *h_totals) {
+  const FsaInfo *d_infos = reinterpret_cast<const FsaInfo *>(ws + L.off_infos);
+  float *cutoffs = reinterpret_cast<float *>(ws + L.off_cutoffs);
+  float *fwd = reinterpret_cast<float *>(ws + L.off_fwd),
+        *bwd = reinterpret_cast<float *>(ws + L.off_bwd);
+  uint32_t *mask = reinterpret_cast<uint32_t *>(ws + L.off_mask);
+  int2 *counts = reinterpret_cast<int2 *>(ws + L.off_counts);
+  int2 *scan_tmp = reinterpret_cast<int2 *>(ws + L.off_scan_tmp);
+  unsigned long long *block_cand = reinterpret_cast<unsigned long long *>(ws + L.off_block_cand);
+  long long *totals = reinterpret_cast<long long *>(ws + L.off_totals);
+  const Arc *arcs = reinterpret_cast<const Arc *>(args->a_arcs);
+  float beam = *beam_io;
+  PhaseTimer prune_timer(kPhasePrune, stream);
+
+  for (int iter = 0;; ++iter) {
+    { Cutoffs<<<CeilDiv(args->num_fsas, 128), 128, 0, stream>>>(d_infos, args->num_fsas, fwd, bwd,
+                                                              beam, cutoffs); NoteLaunch(); }
+    if (L.total_words > 0)
+      for (int32_t first = 0; first < args->num_fsas; first += 65535) {
+        dim3 grid(L.tiles_per_pair, std::min(args->num_fsas - first, 65535));
+        { CountKept<<<grid, kCountThreads, 0, stream>>>(
+            d_infos, args->num_fsas, L.total_words, arcs, args->a_row_splits2, args->scores,
+            args->cols, fwd, bwd, cutoffs, mask, counts, block_cand, first); NoteLaunch(); }
+      }
+    K2B_FORWARD(ExclusiveSum2(counts, counts, L.total_words, scan_tmp, stream));
+    { Totals<<<1, 1024, 0, stream>>>(counts, L.total_words, block_cand,
+                                  L.total_words > 0 ? L.count_blocks : 0, totals); NoteLaunch(); }
+    if (L.total_words > 0)
+      { LayerMaxima<<<CeilDiv(L.total_levels, 256), 256, 0, stream>>>(
+          d_infos, args->num_fsas, (int32_t)L.total_levels, counts, totals); NoteLaunch(); }
+    K2B_CUDA_OK(cudaGetLastError());
+    K2B_CUDA_OK(cudaMemcpyAsync(h_totals, totals, 5 * sizeof(long long), cudaMemcpyDeviceToHost,
+                                stream));
+    K2B_CUDA_OK(cudaStreamSynchronize(stream));
+    // the reference's retry loop, intersect_dense.cu:300-320 and :854-862
+    long long limit = 0, total = 0;
+    if (h_totals[0] > args->max_states) {
+      limit = args->max_states;
+      total = h_totals[0];
+    } else if (h_totals[2] > args->max_arcs) {
+      limit = args->max_arcs;
+      total = h_totals[2];
+    } else {
+      break;
+    }
+    float cur = beam, next = cur * sqrt(limit * 1.0 / total);
+    if (next < cur * 0.25) next = cur * 0.25;
+    if (next > cur * 0.75) next = cur * 0.75;
+    beam = next;
+    if (iter > 200) {
+      SetError("output beam reduction did not converge");
+      return kInvalidArgument;
+    }
+  }
+  *beam_io = beam;
   return kOk;
 }
 
@@ -561,65 +636,13 @@ int32_t k2b200_intersect_dense_prune(const k2b200_intersect_args *args, void *wo
   char *ws = reinterpret_cast<char *>(workspace);
   K2B_CUDA_OK(cudaMemcpyAsync(ws + L.off_infos, L.infos.data(), sizeof(FsaInfo) * args->num_fsas,
                               cudaMemcpyHostToDevice, stream));
-  const FsaInfo *d_infos = reinterpret_cast<const FsaInfo *>(ws + L.off_infos);
-  float *cutoffs = reinterpret_cast<float *>(ws + L.off_cutoffs);
-  float *fwd = reinterpret_cast<float *>(ws + L.off_fwd),
-        *bwd = reinterpret_cast<float *>(ws + L.off_bwd);
-  uint32_t *mask = reinterpret_cast<uint32_t *>(ws + L.off_mask);
-  int2 *counts = reinterpret_cast<int2 *>(ws + L.off_counts);
-  int2 *scan_tmp = reinterpret_cast<int2 *>(ws + L.off_scan_tmp);
-  unsigned long long *block_cand = reinterpret_cast<unsigned long long *>(ws + L.off_block_cand);
-  long long *totals = reinterpret_cast<long long *>(ws + L.off_totals);
-  const Arc *arcs = reinterpret_cast<const Arc *>(args->a_arcs);
-
   {
     PhaseTimer timer(kPhaseViterbi, stream);
     K2B_FORWARD(RunViterbi(L, args, ws, stream));
   }
-  PhaseTimer prune_timer(kPhasePrune, stream);
-
   float beam = args->output_beam;
   long long h_totals[5] = {0, 0, 0, 0, 0};
-  for (int iter = 0;; ++iter) {
-    { Cutoffs<<<CeilDiv(args->num_fsas, 128), 128, 0, stream>>>(d_infos, args->num_fsas, fwd, bwd,
-                                                              beam, cutoffs); NoteLaunch(); }
-    if (L.total_words > 0)
-      for (int32_t first = 0; first < args->num_fsas; first += 65535) {
-        dim3 grid(L.tiles_per_pair, std::min(args->num_fsas - first, 65535));
-        { CountKept<<<grid, kCountThreads, 0, stream>>>(
-            d_infos, args->num_fsas, L.total_words, arcs, args->a_row_splits2, args->scores,
-            args->cols, fwd, bwd, cutoffs, mask, counts, block_cand, first); NoteLaunch(); }
-      }
-    K2B_FORWARD(ExclusiveSum2(counts, counts, L.total_words, scan_tmp, stream));
-    { Totals<<<1, 1024, 0, stream>>>(counts, L.total_words, block_cand,
-                                  L.total_words > 0 ? L.count_blocks : 0, totals); NoteLaunch(); }
-    if (L.total_words > 0)
-      { LayerMaxima<<<CeilDiv(L.total_levels, 256), 256, 0, stream>>>(
-          d_infos, args->num_fsas, (int32_t)L.total_levels, counts, totals); NoteLaunch(); }
-    K2B_CUDA_OK(cudaGetLastError());
-    K2B_CUDA_OK(cudaMemcpyAsync(h_totals, totals, sizeof(h_totals), cudaMemcpyDeviceToHost,
-                                stream));
-    K2B_CUDA_OK(cudaStreamSynchronize(stream));
-    // the reference's retry loop, intersect_dense.cu:300-320 and :854-862
-    long long limit = 0, total = 0;
-    if (h_totals[0] > args->max_states) {
-      limit = args->max_states;
-      total = h_totals[0];
-    } else if (h_totals[2] > args->max_arcs) {
-      limit = args->max_arcs;
-      total = h_totals[2];
-    } else {
-      break;
-    }
-    float cur = beam, next = cur * sqrt(limit * 1.0 / total);
-    if (next < cur * 0.25) next = cur * 0.25;
-    if (next > cur * 0.75) next = cur * 0.75;
-    beam = next;
-    if (iter > 200) {
-      SetError("output beam reduction did not converge");
-      return kInvalidArgument;
-    }
-  }
+  K2B_FORWARD(PruneLoop(L, args, ws, stream, &beam, h_totals));
   *num_states_out = (int32_t)h_totals[0];
   *num_arcs_out = (int32_t)h_totals[1];
   if (beam_used) *beam_used = beam;

@@ -31,6 +31,16 @@ struct Layout {
   int32_t count_blocks, tiles_per_pair, emit_tiles_per_pair;
 };
 
+// intersect.cu
+int32_t MakeLayout(const k2b200_intersect_args *a, Layout *L);
+int32_t RunViterbi(const Layout &L, const k2b200_intersect_args *a, char *ws,
+                   cudaStream_t stream);
+int32_t PruneLoop(const Layout &L, const k2b200_intersect_args *args, char *ws,
+                  cudaStream_t stream, float *beam_io, long long *h_totals);
+// cutoffs[i] = min(best forward, best backward total) - beam, from the Viterbi grids
+int32_t LaunchCutoffs(const Layout &L, const k2b200_intersect_args *a, char *ws, float beam,
+                      cudaStream_t stream);
+
 // viterbi_persistent.cu
 bool PersistentViterbiFits(const Layout &L, const k2b200_intersect_args *a);
 int32_t LaunchPersistentViterbi(const Layout &L, const k2b200_intersect_args *a,

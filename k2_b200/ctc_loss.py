@@ -4,9 +4,15 @@ from typing import Optional
 import torch
 import torch.nn as nn
 
-from .autograd import intersect_dense
+from .autograd import dense_loss_supported, intersect_dense, intersect_dense_tot_scores
 from .dense_fsa_vec import DenseFsaVec
 from .fsa import Fsa
+
+
+# With no delay penalty nothing but the total scores of the lattice is used, so they
+# are computed without building it when the graphs allow; set to False to force
+# the reference's intersect_dense + get_tot_scores sequence.
+FUSED_LOSS = True
 
 
 class CtcLoss(nn.Module):
@@ -24,6 +30,13 @@ class CtcLoss(nn.Module):
     def forward(self, decoding_graph: Fsa, dense_fsa_vec: DenseFsaVec,
                 delay_penalty: float = 0.0,
                 target_lengths: Optional[torch.Tensor] = None) -> torch.Tensor:
+        if (FUSED_LOSS and delay_penalty <= 0.0
+                and dense_loss_supported(decoding_graph, dense_fsa_vec)):
+            tot_scores = intersect_dense_tot_scores(
+                decoding_graph, dense_fsa_vec, self.output_beam,
+                use_double_scores=self.use_double_scores)
+            return self._reduce(tot_scores, target_lengths)
+
         lattice = intersect_dense(
             a_fsas=decoding_graph, b_fsas=dense_fsa_vec, output_beam=self.output_beam,
             frame_idx_name="frame_idx" if delay_penalty > 0.0 else None)
@@ -47,6 +60,10 @@ class CtcLoss(nn.Module):
 
         tot_scores = lattice.get_tot_scores(log_semiring=True,
                                             use_double_scores=self.use_double_scores)
+        return self._reduce(tot_scores, target_lengths)
+
+    def _reduce(self, tot_scores: torch.Tensor,
+                target_lengths: Optional[torch.Tensor]) -> torch.Tensor:
         loss = -1 * tot_scores
         loss = loss.to(torch.float32)
         if self.reduction == "none":
