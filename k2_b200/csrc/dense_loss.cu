@@ -90,6 +90,13 @@ __device__ __forceinline__ double SplitExp(double t, int32_t *e) {
   return __hiloint2double(hi - (ex << 20), __double2loint(t));
 }
 
+// 2^e, 0 below 2^-1000 and 2^1000 above that.
+__device__ __forceinline__ double Pow2Clamped(int32_t e) {
+  if (e < -1000) return 0.0;
+  e = e > 1000 ? 1000 : e;
+  return __longlong_as_double((long long)(1023 + e) << 52);
+}
+
 __global__ void ExpArcs(const Arc *__restrict__ arcs, int32_t n, ArcFactor *__restrict__ out) {
   int32_t i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= n) return;
@@ -99,136 +106,58 @@ __global__ void ExpArcs(const Arc *__restrict__ arcs, int32_t n, ArcFactor *__re
   out[i] = a;
 }
 
-// ---------------------------------------------------------------------------
-// Lane plans.  The recursion kernel keeps the arcs of state s in the registers of
-// G(s) = ceil(degree(s) / kDeg) lanes of one warp, so that a frame costs every lane
-// the same few arcs whatever the degree distribution of the graph is.  PlanLanes
-// lays the lane groups of one graph and direction out over a CTA of kLaneThreads
-// threads: groups sorted by size, largest first (states in increasing order within
-// a size), packed next-fit into warps - a group never straddles two warps.
-//   plan[(dir * n + i) * kLaneThreads + thread] = state | lane << 16 | G << 24, or -1
-// unfit[i] is set when graph i needs more lanes than a CTA has (or has more than
-// 32 * kDeg arcs on a state); the shared-memory kernels below take those graphs.
-// Graphs whose largest degree is at most kDeg need no plan: thread s owns state s.
-// ---------------------------------------------------------------------------
-constexpr int kLaneThreads = 768;
-
-__global__ void __launch_bounds__(256)
-PlanLanes(const FsaInfo *__restrict__ infos, int32_t n,
-          const int32_t *__restrict__ a_row_splits2, const int32_t *__restrict__ in_splits,
-          int32_t k_deg, int32_t *__restrict__ plan, int32_t *__restrict__ unfit) {
-  // per group size G = 1..32: number of states, lanes left in the warp where the
-  // size class starts, first lane of that start, first lane of the following warps
-  __shared__ int32_t count[33], head_room[33], head_pos[33], body_pos[33];
-  __shared__ int32_t bad;
-  const int32_t i = blockIdx.y, dir = blockIdx.x;
-  const FsaInfo f = infos[i];
-  const int32_t S = f.num_states;
-  const int tid = threadIdx.x, nt = blockDim.x;
-  int32_t *out = plan + ((int64_t)dir * n + i) * kLaneThreads;
-  for (int32_t t = tid; t < kLaneThreads; t += nt) out[t] = -1;
-  if (tid < 33) count[tid] = 0;
-  if (tid == 0) bad = S > kLaneThreads;
-  __syncthreads();
-  const int32_t *splits = (dir == 0 ? in_splits : a_row_splits2) + f.state_off;
-  auto lanes_of = [&](int32_t s) {
-    const int32_t deg = splits[s + 1] - splits[s];
-    return deg <= k_deg ? 1 : (deg + k_deg - 1) / k_deg;
-  };
-  if (S <= kLaneThreads)
-    for (int32_t s = tid; s < S; s += nt) {
-      const int32_t G = lanes_of(s);
-      if (G > 32) bad = 1; else atomicAdd(&count[G], 1);
-    }
-  __syncthreads();
-  if (tid == 0 && !bad) {
-    int32_t pos = 0;
-    for (int G = 32; G >= 1; --G) {
-      const int32_t c = count[G];
-      if (c == 0) continue;
-      const int32_t room = (32 - (pos & 31)) / G;  // groups that still fit in this warp
-      const int32_t per_warp = 32 / G;
-      head_room[G] = room;
-      head_pos[G] = pos;
-      if (c <= room) {
-        pos += c * G;
-      } else {
-        const int32_t rest = c - room;
-        const int32_t body = (pos + room * G + 31) & ~31;
-        body_pos[G] = body;
-        pos = body + (rest / per_warp) * 32 + (rest % per_warp) * G;
-      }
-      if (pos > kLaneThreads) bad = 1;
-    }
-  }
-  __syncthreads();
-  if (bad) {
-    if (tid == 0) atomicOr(&unfit[i], 1);
-    return;
-  }
-  // warp w places the size classes w, w + 8, ...: ordered compaction by ballot
-  const int warp = tid >> 5, lane = tid & 31;
-  for (int G = 1 + warp; G <= 32; G += nt >> 5) {
-    if (count[G] == 0) continue;
-    const int32_t per_warp = 32 / G, room = head_room[G];
-    int32_t seen = 0;
-    for (int32_t s0 = 0; s0 < S; s0 += 32) {
-      const int32_t s = s0 + lane;
-      const bool in = s < S && lanes_of(s) == G;
-      const uint32_t m = __ballot_sync(0xffffffffu, in);
-      if (in) {
-        const int32_t j = seen + __popc(m & ((1u << lane) - 1u));
-        int32_t p0;
-        if (j < room) {
-          p0 = head_pos[G] + j * G;
-        } else {
-          const int32_t r = j - room;
-          p0 = body_pos[G] + (r / per_warp) * 32 + (r % per_warp) * G;
-        }
-        for (int32_t g = 0; g < G; ++g) out[p0 + g] = s | (g << 16) | (G << 24);
-      }
-      seen += __popc(m);
-    }
-  }
-}
-
 struct LaneSmem {
-  int32_t s_pad, a_pad, stages;
+  int32_t s_pad, stages;
   size_t bytes;
 };
 constexpr size_t kChainSmemBudget = 220 * 1024;
 
-static LaneSmem PlanLaneSmem(const Layout &L, const DensePack &d, bool smem_factors) {
+// frames per unrolled group = ring slots = prefetch depth of the lane kernel (even)
+constexpr int kChainGroup = 6, kChainGroupSmall = 2;
+
+static LaneSmem PlanLaneSmem(const Layout &L, const DensePack &d, int group) {
   LaneSmem p;
   p.s_pad = (L.max_states + 3) & ~3;
-  p.a_pad = smem_factors ? (L.max_arcs + 3) & ~3 : 0;
-  const size_t fixed =
-      (sizeof(ProbState) + sizeof(float)) * 2 * p.s_pad + sizeof(ArcFactor) * p.a_pad;
-  p.stages = 0;
-  if (fixed < kChainSmemBudget)
-    p.stages = (int32_t)std::min<size_t>(8, (kChainSmemBudget - fixed) / d.pitch);
-  p.bytes = fixed + (size_t)d.pitch * std::max(p.stages, 0);
+  const size_t fixed = (sizeof(double) + sizeof(float)) * 2 * p.s_pad;
+  p.bytes = fixed + (size_t)d.pitch * group;
+  p.stages = p.bytes <= kChainSmemBudget ? group : 0;
   return p;
 }
+
+// Limits of the shared-exponent arithmetic below; outside them a graph is handed
+// to the per-state-exponent kernel.
+constexpr float kMaxAbsArcScore = 80.0f;   // |arc score| of every arc with a finite score
+constexpr float kMinDenseScore = -200.0f;  // dense score of every surviving arc
+constexpr int32_t kMinExponent = -480;     // binary exponent of every non-zero stored value
 
 // ---------------------------------------------------------------------------
 // The alpha / beta recursion.  grid = (2 directions, pairs), one CTA walks all
 // frames of its pair.  Per frame: one bulk copy (issued stages - 1 frames ahead by
 // thread 0, completion on an mbarrier) brings the packed dense row into a
-// shared-memory ring; every lane runs the reference's pruning test
-// (intersect_dense.cu:430-470) on its arcs with the same fp32 expressions and sums
-// the survivors in mantissa/exponent form; the lanes of a state merge by shuffles.
-// The Viterbi scores of the lane's own state are fetched kPF frames ahead into
-// registers.  With kSmemFactors the exp() of the arc scores sits in a shared-memory
-// table (arcs in the order of the direction walked), otherwise in registers.
+// shared-memory ring of kChainGroup slots; every lane runs the reference's pruning test
+// (intersect_dense.cu:430-470) on its arcs with the same fp32 expressions and adds
+// the survivors' alpha[src] * exp(w) * exp(lp); the lanes of a state merge by
+// shuffles.  The Viterbi scores of the lane's own state are fetched kChainGroup
+// frames ahead into registers; the frame loop is unrolled by that number, so ring
+// slots, buffers and register slots are compile-time constants.
+//
+// Arithmetic: all states of a level share one binary exponent K, so a value is a
+// plain double v with alpha = v * 2^K and an arc costs two multiplies and an add.
+// K follows the data in steps: every kChainGroup levels the values are scaled by
+// 2^-e, e the exponent of the largest value of the level before (a shared-memory
+// max), and every stored value's exponent is checked against the limits.  The
+// grid receives (v, K) per state, the same (mantissa, exponent) format the
+// per-state-exponent kernel writes.  A double spans 2^+-1022, far more than the
+// survivors of one level normally differ by; when a surviving value does get
+// within reach of the limits above, the graph is marked in `unfit` and the
+// per-state-exponent kernel, which runs next, recomputes it.  The same happens
+// when a wait on a copy gives up.
 //
 // `oth` holds, for the states of the previous frame, the Viterbi score the arc
 // test needs (forward score walking forward, backward score walking backward), or
 // -inf when that state was pruned - which fails the arc test by itself.
-// A wait that gives up marks the graph in `unfit`; the shared-memory kernel that
-// runs next then recomputes it.
 // ---------------------------------------------------------------------------
-template <int kDeg, bool kSmemFactors, int kPF, int kMaxThreads>
+template <int kDeg, int kMaxThreads, int kU>
 __global__ void __launch_bounds__(kMaxThreads)
 GridChainLanes(const FsaInfo *__restrict__ infos, int32_t n, const Arc *__restrict__ arcs,
                const int32_t *__restrict__ a_row_splits2, const int32_t *__restrict__ in_splits,
@@ -238,8 +167,9 @@ GridChainLanes(const FsaInfo *__restrict__ infos, int32_t n, const Arc *__restri
                ProbState *__restrict__ beta, double *__restrict__ tot,
                const int32_t *__restrict__ plan, int32_t *__restrict__ unfit, LaneSmem sm) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
-  __shared__ __align__(8) uint64_t full[8];
-  __shared__ int32_t gave_up;
+  __shared__ __align__(8) uint64_t full[kU];
+  __shared__ int32_t emax;  // largest exponent among the values of a group's last level
+  constexpr int32_t kNone = INT32_MIN;
   const int32_t i = blockIdx.y;
   const int dir = blockIdx.x;
   if (plan != nullptr && unfit[i]) return;
@@ -250,12 +180,12 @@ GridChainLanes(const FsaInfo *__restrict__ infos, int32_t n, const Arc *__restri
     if (dir == 0 && tid == 0) tot[i] = -INFINITY;
     return;
   }
-  const int32_t stages = sm.stages, s_pad = sm.s_pad;
-  unsigned char *ring = smem_raw;                                              // [stages][pitch]
-  ProbState *ps = reinterpret_cast<ProbState *>(ring + (size_t)stages * dp.pitch);  // [2][s_pad]
-  ArcFactor *table = reinterpret_cast<ArcFactor *>(ps + 2 * s_pad);            // [a_pad]
-  float *oth = reinterpret_cast<float *>(table + sm.a_pad);                    // [2][s_pad]
+  const int32_t s_pad = sm.s_pad;
+  unsigned char *ring = smem_raw;                                     // [kU][pitch]
+  double *pv = reinterpret_cast<double *>(ring + (size_t)kU * dp.pitch);  // [2][s_pad]
+  float *oth = reinterpret_cast<float *>(pv + 2 * s_pad);             // [2][s_pad]
 
+  const bool producer = tid == 0;  // issues the bulk copies
   int32_t s = -1, g = 0, G = 1;
   if (plan != nullptr) {
     const int32_t code = plan[((int64_t)dir * n + i) * kLaneThreads + tid];
@@ -270,205 +200,190 @@ GridChainLanes(const FsaInfo *__restrict__ infos, int32_t n, const Arc *__restri
   // ---- this lane's arcs: dir 0 arcs entering s (other end = source), dir 1 leaving
   int32_t other_col[kDeg];  // other-end state | column << 16
   float w[kDeg];            // arc score, -inf for an unused slot
-  double ewf[kSmemFactors ? 1 : kDeg];
-  int32_t ewk[kSmemFactors ? 1 : kDeg];
-  int32_t tbl0 = 0;  // table index of slot 0; slot j is tbl0 + j * G
+  double ew[kDeg];          // exp(w)
+  bool risky = false;       // something is outside the limits of this arithmetic
 #pragma unroll
   for (int j = 0; j < kDeg; ++j) {
     other_col[j] = cols << 16;
     w[j] = -INFINITY;
-    if (!kSmemFactors) {
-      ewf[j] = 0.0;
-      ewk[j] = kZeroExp;
-    }
+    ew[j] = 0.0;
   }
-  const int32_t *gsplits = dir == 0 ? in_splits : a_row_splits2;
   if (s >= 0) {
+    const int32_t *gsplits = dir == 0 ? in_splits : a_row_splits2;
     const int32_t a0 = gsplits[f.state_off + s], a1 = gsplits[f.state_off + s + 1];
-    tbl0 = a0 - f.arc_off + g;
 #pragma unroll
     for (int j = 0; j < kDeg; ++j) {
       const int32_t k = a0 + g + j * G;
       if (k < a1) {
         const Arc arc = arcs[dir == 0 ? in_arcs[k] : k];
         const int32_t c = arc.label + 1;
-        if (c >= 0 && c < cols) {
+        if (c >= 0 && c < cols && arc.score != -INFINITY) {
           other_col[j] = (dir == 0 ? arc.src : arc.dest) | (c << 16);
           w[j] = arc.score;
-          if (!kSmemFactors) ExpToMantExp(arc.score, &ewf[j], &ewk[j]);
+          ew[j] = exp((double)arc.score);
+          if (!(fabsf(arc.score) <= kMaxAbsArcScore)) risky = true;
         }
       }
     }
   }
-  if (kSmemFactors)
-    for (int32_t k = tid; k < f.num_arcs; k += nt) {
-      const Arc arc = arcs[dir == 0 ? in_arcs[f.arc_off + k] : f.arc_off + k];
-      ArcFactor af;
-      ExpToMantExp(arc.score, &af.f, &af.k);
-      af.pad = 0;
-      table[k] = af;
-    }
   if (tid == 0) {
-    for (int st = 0; st < stages; ++st) MbarInit(&full[st], 1);
-    gave_up = 0;
+    for (int st = 0; st < kU; ++st) MbarInit(&full[st], 1);
+    emax = kNone;
     MbarInitFence();
+  }
+  if (__syncthreads_or(risky)) {  // also orders the initialisation above
+    if (tid == 0) atomicOr(&unfit[i], 1);
+    return;
   }
   const float cutoff = cutoffs[i];
   const float *fgrid = vfwd + f.grid_off, *bgrid = vbwd + f.grid_off;
   ProbState *out = (dir == 0 ? alpha : beta) + f.grid_off;
-  // ---- first level ------------------------------------------------------------
+  // ---- first level: the start (final) state holds 1 = 1.0 * 2^0 -------------------
   {
     const int64_t lv = dir == 0 ? 0 : Tk;
     for (int32_t q = tid; q < S; q += nt) {
       const float fu = fgrid[lv * S + q], bu = bgrid[lv * S + q];
       const bool keep = __fadd_rn(fu, bu) > cutoff;
+      const bool one = keep && q == (dir == 0 ? 0 : S - 1);
       ProbState v;
+      v.m = one ? 1.0 : 0.0;
+      v.e = 0;
       v.pad = 0;
-      if (keep && q == (dir == 0 ? 0 : S - 1)) {
-        v.m = 1.0;
-        v.e = 0;
-      } else {
-        v.m = 0.0;
-        v.e = kZeroExp;
-      }
-      ps[q] = v;
+      pv[q] = v.m;
       oth[q] = keep ? (dir == 0 ? fu : bu) : -INFINITY;
       out[lv * S + q] = v;
+      if (one) emax = 0;
     }
   }
-  __syncthreads();  // barriers initialised, first level and table in place
-  // step t (1..Tk) handles level t (forward) / Tk - t (backward) and reads dense
-  // row t - 1 / Tk - t
+  __syncthreads();
+  // Step t (1..Tk) handles level t (forward) / Tk - t (backward) and reads dense
+  // row t - 1 / Tk - t.  Steps come in groups of kU: step t0 + u (t0 = 1, 1 + kU, ...)
+  // always finds its row in ring slot u and its operands in buffer u & 1.
+  const int64_t step_stride = dir == 0 ? (int64_t)S : -(int64_t)S;
   const unsigned char *dense0 = dense + (int64_t)f.row0 * dp.pitch;
-  auto issue_row = [&](int32_t step) {  // thread 0 only
+  auto issue_row = [&](int32_t step, int32_t slot) {  // producer only
     if (step > Tk) return;
-    const int32_t slot = (step - 1) % stages;
     const int64_t row = dir == 0 ? step - 1 : Tk - step;
     MbarArriveExpectTx(&full[slot], (unsigned)dp.pitch);
     BulkCopyG2S(ring + (size_t)slot * dp.pitch, dense0 + row * dp.pitch, (unsigned)dp.pitch,
                 &full[slot]);
   };
-  if (tid == 0)
-    for (int32_t step = 1; step < stages; ++step) issue_row(step);
+  if (producer)
+    for (int32_t step = 1; step < kU; ++step) issue_row(step, step - 1);
 
-  // Viterbi scores of this lane's state for steps t .. t + kPF - 1
-  auto level_of = [&](int32_t step) {
-    step = step > Tk ? Tk : step;
-    return (int64_t)(dir == 0 ? step : Tk - step);
-  };
+  // Viterbi scores of this lane's state for the next kU steps
   const int32_t s_ld = s >= 0 ? s : 0;
-  float fq[kPF], bq[kPF];
+  const int64_t first = dir == 0 ? 1 : Tk - 1;  // level of step 1
+  float fq[kU], bq[kU];
 #pragma unroll
-  for (int d = 0; d < kPF; ++d) {
-    const int64_t lv = level_of(1 + d);
-    fq[d] = fgrid[lv * S + s_ld];
-    bq[d] = bgrid[lv * S + s_ld];
+  for (int d = 0; d < kU; ++d) {
+    const bool in = 1 + d <= Tk;
+    fq[d] = in ? fgrid[(first * S + s_ld) + d * step_stride] : -INFINITY;
+    bq[d] = in ? bgrid[(first * S + s_ld) + d * step_stride] : -INFINITY;
   }
-  ProbState last;
-  last.m = 0.0;
-  last.e = kZeroExp;
-  int32_t slot = 0;
+  int64_t pos = first * S + s_ld;  // grid index of this lane's state at step t
+  double last = 0.0;
+  int32_t K = 0;  // exponent shared by the stored values
   unsigned parity = 0;
-  bool stop = false;
-  for (int32_t t0 = 1; t0 <= Tk && !stop; t0 += kPF) {
+  uint32_t rec_off = (uint32_t)(kU - 1) * dp.pitch;  // ring offset of the previous frame's slot
+  // row of step kU (the producer walks it one row per frame)
+  const unsigned char *src_next = dense0 + (int64_t)(dir == 0 ? kU - 1 : Tk - kU) * dp.pitch;
+  bool gave_up = false;
+  for (int32_t t0 = 1; t0 <= Tk && !gave_up; t0 += kU) {
 #pragma unroll
-    for (int u = 0; u < kPF; ++u) {
+    for (int u = 0; u < kU; ++u) {
       const int32_t t = t0 + u;
       if (t > Tk) break;
-      if (!MbarTryWait(&full[slot], parity) && !MbarWaitBounded(&full[slot], parity))
-        *reinterpret_cast<volatile int32_t *>(&gave_up) = 1;
-      __syncthreads();  // the previous frame is complete; nobody reads its slot any more
-      if (*reinterpret_cast<volatile int32_t *>(&gave_up)) {  // uniform
-        stop = true;
+      const bool late = !MbarTryWait(&full[u], parity) && !MbarWaitBounded(&full[u], parity);
+      // the previous frame is complete; nobody reads its ring slot any more
+      if (__syncthreads_or(late)) {  // uniform
+        gave_up = true;
         break;
       }
-      if (tid == 0) issue_row(t + stages - 1);
-      const ProbState *prev = ps + ((t - 1) & 1) * s_pad;
-      ProbState *cur = ps + (t & 1) * s_pad;
-      const float *po = oth + ((t - 1) & 1) * s_pad;
-      float *co = oth + (t & 1) * s_pad;
-      const unsigned char *rec = ring + (size_t)slot * dp.pitch;
+      if (producer) {
+        // the slot the previous frame used (offset rec_off) takes the row of step
+        // t + kU - 1
+        if (t + kU - 1 <= Tk) {
+          uint64_t *bar = &full[(u + kU - 1) % kU];
+          MbarArriveExpectTx(bar, (unsigned)dp.pitch);
+          BulkCopyG2S(ring + rec_off, src_next, (unsigned)dp.pitch, bar);
+        }
+        src_next += dir == 0 ? (int64_t)dp.pitch : -(int64_t)dp.pitch;
+        if (u == 1) emax = kNone;  // read by everyone during the frame before
+      }
+      double scale = 1.0;
+      if (u == 0) {  // once per group: renormalise by the exponent of the largest value
+        const int32_t e_prev = emax;
+        const int32_t shift = e_prev == kNone ? 0 : e_prev;
+        K += shift;
+        scale = __longlong_as_double((long long)(1023 - shift) << 52);
+      }
+      const double *prev = pv + (u & 1) * s_pad;
+      double *cur = pv + ((u + 1) & 1) * s_pad;
+      const float *po = oth + (u & 1) * s_pad;
+      float *co = oth + ((u + 1) & 1) * s_pad;
+      // ring slot u, as a running offset (kept opaque so that the unrolled frames
+      // do not each pin their own pointers in registers)
+      rec_off = u == 0 ? 0u : rec_off + (uint32_t)dp.pitch;
+      asm volatile("" : "+r"(rec_off));
+      const unsigned char *rec = ring + rec_off;
       const float *lprow = PackLp(rec);
       const double *prow = PackP(rec, dp);
-      slot = slot + 1 == stages ? 0 : slot + 1;
-      parity ^= (slot == 0);
-      const int64_t lv = dir == 0 ? t : Tk - t;
       const float fu = fq[u], bu = bq[u];
-      {
-        const int64_t nlv = level_of(t + kPF);
-        fq[u] = fgrid[nlv * S + s_ld];
-        bq[u] = bgrid[nlv * S + s_ld];
+      if (t + kU <= Tk) {
+        fq[u] = fgrid[pos + kU * step_stride];
+        bq[u] = bgrid[pos + kU * step_stride];
       }
       const bool keep = s >= 0 && __fadd_rn(fu, bu) > cutoff;
-      // arcs in groups of up to four: the loads and multiplies of a group are
-      // independent, then the group joins the running (sum, E)
-      constexpr int kGroup = kDeg < 4 ? kDeg : 4;
       double sum = 0.0;
-      int32_t E = kZeroExp;
+      if (__any_sync(0xffffffffu, keep)) {  // most warps of a sparse lattice skip this
 #pragma unroll
-      for (int j0 = 0; j0 < kDeg; j0 += kGroup) {
-        double tt[kGroup];
-        int32_t ee[kGroup];
-        int32_t Eg = kZeroExp;
-#pragma unroll
-        for (int jj = 0; jj < kGroup; ++jj) {
-          const int j = j0 + jj;
+        for (int j = 0; j < kDeg; ++j) {
           const int32_t o_idx = other_col[j] & 0xffff, c = other_col[j] >> 16;
-          const float sc = __fadd_rn(w[j], lprow[c]);
+          const float lp = lprow[c];
+          const float sc = __fadd_rn(w[j], lp);
           const float o = po[o_idx];
           const float through = dir == 0 ? __fadd_rn(__fadd_rn(o, sc), bu)
                                          : __fadd_rn(__fadd_rn(fu, sc), o);
-          tt[jj] = 0.0;
-          ee[jj] = kZeroExp;
           if (keep && through > cutoff) {
-            const ProbState q = prev[o_idx];
-            double af_f;
-            int32_t af_k;
-            if (kSmemFactors) {
-              const ArcFactor af = table[tbl0 + j * G];
-              af_f = af.f;
-              af_k = af.k;
-            } else {
-              af_f = ewf[j];
-              af_k = ewk[j];
-            }
-            int32_t ex;
-            tt[jj] = SplitExp(q.m * af_f * prow[c], &ex);
-            if (tt[jj] != 0.0) ee[jj] = q.e + af_k + ex;
+            sum += prev[o_idx] * ew[j] * prow[c];
+            risky |= lp < kMinDenseScore;
           }
-          Eg = ee[jj] > Eg ? ee[jj] : Eg;
         }
-        const int32_t En = Eg > E ? Eg : E;
-        sum = ScaleDown(sum, E - En);
+        if (plan != nullptr) {  // uniform: the lanes of a state add up in lane g == 0
 #pragma unroll
-        for (int jj = 0; jj < kGroup; ++jj) sum += ScaleDown(tt[jj], ee[jj] - En);
-        E = En;
-      }
-      if (plan != nullptr) {  // uniform: lanes of a state merge into lane g == 0
-#pragma unroll
-        for (int32_t d = 16; d > 0; d >>= 1) {
-          const int32_t Eo = __shfl_down_sync(0xffffffffu, E, d);
-          const double so = __shfl_down_sync(0xffffffffu, sum, d);
-          if (g + d < G) {
-            const int32_t En = Eo > E ? Eo : E;
-            sum = ScaleDown(sum, E - En) + ScaleDown(so, Eo - En);
-            E = En;
+          for (int32_t d = 16; d > 0; d >>= 1) {
+            const double so = __shfl_down_sync(0xffffffffu, sum, d);
+            if (g + d < G) sum += so;
           }
         }
       }
+      const double v = u == 0 ? sum * scale : sum;
+      const int32_t vhi = __double2hiint(v);  // v >= 0: the exponent is vhi >> 20
       if (s >= 0 && g == 0) {
-        ProbState r;
-        r.e = E;
-        r.m = Renorm(sum, &r.e);
-        r.pad = 0;
-        cur[s] = r;
+        cur[s] = v;
         co[s] = keep ? (dir == 0 ? fu : bu) : -INFINITY;
-        out[lv * S + s] = r;
-        last = r;
+        if (keep || t == Tk) {  // pruned states of the grid are read on the last level only
+          ProbState r;
+          r.m = v;
+          r.e = K;
+          r.pad = 0;
+          out[pos] = r;
+          last = v;
+          risky |= v != 0.0 && vhi < ((1023 + kMinExponent) << 20);
+        }
+      }
+      pos += step_stride;
+      if (u == kU - 1) {  // the next group renormalises by this level's largest value
+        int32_t ex = (s >= 0 && g == 0 && v != 0.0) ? (vhi >> 20) - 1023 : kNone;
+        ex = __reduce_max_sync(0xffffffffu, ex);
+        if ((tid & 31) == 0 && ex != kNone) atomicMax(&emax, ex);
       }
     }
+    parity ^= 1u;
   }
-  if (*reinterpret_cast<volatile int32_t *>(&gave_up)) {
+  const int32_t any_risky = __syncthreads_or(risky);
+  if (gave_up) {
     if (tid == 0) {
       atomicOr(&unfit[i], 1);
       // copies may still be in flight towards this CTA's shared memory: give them
@@ -478,9 +393,12 @@ GridChainLanes(const FsaInfo *__restrict__ infos, int32_t n, const Arc *__restri
     __syncthreads();
     return;
   }
+  if (any_risky) {
+    if (tid == 0) atomicOr(&unfit[i], 1);
+    return;
+  }
   if (dir == 0 && s == S - 1 && g == 0)
-    tot[i] = last.m == 0.0 ? -INFINITY
-                           : log(last.m) + (double)last.e * 0.69314718055994530942;
+    tot[i] = last == 0.0 ? -INFINITY : log(last) + (double)K * 0.69314718055994530942;
 }
 
 // ---------------------------------------------------------------------------
@@ -608,9 +526,12 @@ GridGradWarp(const FsaInfo *__restrict__ infos, const Arc *__restrict__ arcs,
             bexp = b.e;
           }
           const ArcFactor af = my_factors[k];
-          const double prod = am * af.f * prow[c] * bm * zinv;
+          // two steps, so that no intermediate product leaves the range of a double
+          int32_t e1;
+          const double m1 = SplitExp(am * af.f * prow[c], &e1);
+          const double prod = m1 * bm * zinv;
           if (prod == 0.0) continue;
-          const float post = (float)scalbn(prod, ae + af.k + bexp + zk);
+          const float post = (float)(prod * Pow2Clamped(e1 + ae + af.k + bexp + zk));
           atomicAdd(&gbrow[c], post);
           atomicAdd(ga_in_smem ? &ga[k] : &grad_a[f.arc_off + k], post);
         }
@@ -818,7 +739,7 @@ GridChain(const FsaInfo *__restrict__ infos, const Arc *__restrict__ arcs,
 struct LossLayout {
   Layout base;
   DensePack pack;
-  size_t off_dense, off_arc_factors, off_alpha, off_beta, off_plan, off_unfit, total_bytes;
+  size_t off_dense, off_arc_factors, off_alpha, off_beta, total_bytes;
   bool exclusive_rows;
   int32_t k_deg;      // arcs per lane of the lane kernel
   bool identity;      // every degree <= k_deg: thread s owns state s, no plan
@@ -828,8 +749,8 @@ struct LossLayout {
 static int32_t MakeLossLayout(const k2b200_intersect_args *a, LossLayout *LL) {
   K2B_FORWARD(MakeLayout(a, &LL->base));
   LL->pack = MakeDensePack(a->cols);
-  LL->identity = a->a_max_degree > 0 && a->a_max_degree <= 4 && LL->base.max_states <= 1024;
-  LL->k_deg = LL->identity ? (a->a_max_degree <= 3 ? 3 : 4) : 8;
+  LL->identity = !LL->base.lane_plan;
+  LL->k_deg = LL->identity ? (a->a_max_degree <= 3 ? 3 : 4) : kLaneDeg;
   LL->threads = LL->identity ? std::max(32, (LL->base.max_states + 31) / 32 * 32) : kLaneThreads;
   size_t off = AlignUp(LL->base.total_bytes);
   auto take = [&](size_t bytes) {
@@ -841,8 +762,6 @@ static int32_t MakeLossLayout(const k2b200_intersect_args *a, LossLayout *LL) {
   LL->off_arc_factors = take(sizeof(ArcFactor) * (size_t)std::max(a->num_arcs, 1));
   LL->off_alpha = take(sizeof(ProbState) * (size_t)LL->base.grid_elems);
   LL->off_beta = take(sizeof(ProbState) * (size_t)LL->base.grid_elems);
-  LL->off_plan = take(LL->identity ? 0 : sizeof(int32_t) * 2 * (size_t)a->num_fsas * kLaneThreads);
-  LL->off_unfit = take(sizeof(int32_t) * (size_t)a->num_fsas);
   LL->total_bytes = off;
   // two graphs on one sequence write the same rows of the dense gradient
   LL->exclusive_rows = true;
@@ -855,19 +774,23 @@ static int32_t MakeLossLayout(const k2b200_intersect_args *a, LossLayout *LL) {
 static bool LossFits(const LossLayout &LL, const k2b200_intersect_args *a, ChainPlan *p,
                      LaneSmem *ls) {
   *p = PlanChain(LL.base, a, LL.pack);
-  *ls = PlanLaneSmem(LL.base, LL.pack, !LL.identity);
-  return p->stages >= 2 && ls->stages >= 2 && a->num_fsas <= 65535 && a->cols < 32768 &&
-         LL.base.max_states < 65536;
+  // the deep ring when it fits (identity lanes only), else two slots
+  *ls = PlanLaneSmem(LL.base, LL.pack, kChainGroup);
+  if (!LL.identity || ls->stages == 0) *ls = PlanLaneSmem(LL.base, LL.pack, kChainGroupSmall);
+  const bool lanes_ok = LL.base.lane_plan ||
+                        (a->a_max_degree > 0 && a->a_max_degree <= 4 && LL.base.max_states <= 1024);
+  return lanes_ok && p->stages >= 2 && ls->stages >= 2 && a->num_fsas <= 65535 &&
+         a->cols < 32768 && LL.base.max_states < 65536;
 }
 
-template <int kDeg, bool kSmemFactors, int kPF, int kMaxThreads>
+template <int kDeg, int kMaxThreads, int kU>
 static int32_t LaunchChainLanes(const LossLayout &LL, const k2b200_intersect_args *args, char *ws,
                                 const LaneSmem &ls, double *tot, cudaStream_t stream) {
   const Layout &L = LL.base;
-  K2B_CUDA_OK(cudaFuncSetAttribute(GridChainLanes<kDeg, kSmemFactors, kPF, kMaxThreads>,
+  K2B_CUDA_OK(cudaFuncSetAttribute(GridChainLanes<kDeg, kMaxThreads, kU>,
                                    cudaFuncAttributeMaxDynamicSharedMemorySize, (int)ls.bytes));
   dim3 grid(2, args->num_fsas);
-  { GridChainLanes<kDeg, kSmemFactors, kPF, kMaxThreads><<<grid, LL.threads, ls.bytes, stream>>>(
+  { GridChainLanes<kDeg, kMaxThreads, kU><<<grid, LL.threads, ls.bytes, stream>>>(
       reinterpret_cast<const FsaInfo *>(ws + L.off_infos), args->num_fsas,
       reinterpret_cast<const Arc *>(args->a_arcs), args->a_row_splits2, args->a_in_splits,
       args->a_in_arcs, reinterpret_cast<const unsigned char *>(ws + LL.off_dense), LL.pack,
@@ -876,8 +799,8 @@ static int32_t LaunchChainLanes(const LossLayout &LL, const k2b200_intersect_arg
       reinterpret_cast<const float *>(ws + L.off_cutoffs),
       reinterpret_cast<ProbState *>(ws + LL.off_alpha),
       reinterpret_cast<ProbState *>(ws + LL.off_beta), tot,
-      LL.identity ? nullptr : reinterpret_cast<const int32_t *>(ws + LL.off_plan),
-      reinterpret_cast<int32_t *>(ws + LL.off_unfit), ls); NoteLaunch(); }
+      LL.identity ? nullptr : reinterpret_cast<const int32_t *>(ws + L.off_plan),
+      reinterpret_cast<int32_t *>(ws + L.off_unfit), ls); NoteLaunch(); }
   K2B_CUDA_OK(cudaGetLastError());
   return kOk;
 }
@@ -972,22 +895,17 @@ int32_t k2b200_dense_loss_forward(const k2b200_intersect_args *args, void *works
                               cudaMemcpyHostToDevice, stream));
   const FsaInfo *d_infos = reinterpret_cast<const FsaInfo *>(ws + L.off_infos);
   unsigned char *dense = reinterpret_cast<unsigned char *>(ws + LL.off_dense);
-  int32_t *unfit = reinterpret_cast<int32_t *>(ws + LL.off_unfit);
-  int32_t *plan = reinterpret_cast<int32_t *>(ws + LL.off_plan);
+  int32_t *unfit = reinterpret_cast<int32_t *>(ws + L.off_unfit);
   {
     PhaseTimer timer(kPhaseChain, stream);
     const int64_t n_dense = (int64_t)args->rows * LL.pack.cols4;
     { ExpDense<<<(int)std::min<int64_t>(CeilDiv(n_dense, 256), 148 * 32), 256, 0, stream>>>(
         args->scores, args->rows, LL.pack, dense); NoteLaunch(); }
-    K2B_CUDA_OK(cudaMemsetAsync(unfit, 0, sizeof(int32_t) * args->num_fsas, stream));
-    if (!LL.identity)
-      { PlanLanes<<<dim3(2, args->num_fsas), 256, 0, stream>>>(
-          d_infos, args->num_fsas, args->a_row_splits2, args->a_in_splits, LL.k_deg, plan,
-          unfit); NoteLaunch(); }
+    K2B_FORWARD(LaunchPlanLanes(L, args, ws, stream));
   }
   {
     PhaseTimer timer(kPhaseViterbi, stream);
-    K2B_FORWARD(RunViterbi(L, args, ws, stream));
+    K2B_FORWARD(RunViterbi(L, args, ws, stream, /*plan_ready=*/true));
   }
   // The lattice is never built, but its size still decides the beam
   // (intersect_dense.cu:300-320).  The grid itself bounds it: count only when the
@@ -1004,17 +922,18 @@ int32_t k2b200_dense_loss_forward(const k2b200_intersect_args *args, void *works
   if (beam_used) *beam_used = beam;
   {
     PhaseTimer timer(kPhaseChain, stream);
-    if (LL.k_deg == 3 && LL.threads <= 512)
-      K2B_FORWARD((LaunchChainLanes<3, false, 6, 512>(LL, args, ws, ls, tot_scores, stream)));
-    else if (LL.k_deg == 3)
-      K2B_FORWARD((LaunchChainLanes<3, false, 6, 1024>(LL, args, ws, ls, tot_scores, stream)));
-    else if (LL.k_deg == 4 && LL.threads <= 512)
-      K2B_FORWARD((LaunchChainLanes<4, false, 6, 512>(LL, args, ws, ls, tot_scores, stream)));
-    else if (LL.k_deg == 4)
-      K2B_FORWARD((LaunchChainLanes<4, false, 4, 1024>(LL, args, ws, ls, tot_scores, stream)));
+#define K2B_CHAIN(DEG, MAXT)                                                              \
+  (ls.stages == kChainGroup                                                               \
+       ? LaunchChainLanes<DEG, MAXT, kChainGroup>(LL, args, ws, ls, tot_scores, stream)   \
+       : LaunchChainLanes<DEG, MAXT, kChainGroupSmall>(LL, args, ws, ls, tot_scores, stream))
+    if (LL.k_deg == 3 && LL.threads <= 512) K2B_FORWARD(K2B_CHAIN(3, 512));
+    else if (LL.k_deg == 3) K2B_FORWARD(K2B_CHAIN(3, 1024));
+    else if (LL.k_deg == 4 && LL.threads <= 512) K2B_FORWARD(K2B_CHAIN(4, 512));
+    else if (LL.k_deg == 4) K2B_FORWARD(K2B_CHAIN(4, 1024));
     else
-      K2B_FORWARD((LaunchChainLanes<8, true, 4, kLaneThreads>(LL, args, ws, ls, tot_scores,
-                                                              stream)));
+      K2B_FORWARD((LaunchChainLanes<8, kLaneThreads, kChainGroupSmall>(LL, args, ws, ls,
+                                                                       tot_scores, stream)));
+#undef K2B_CHAIN
     // graphs the lane kernel skipped or gave up on
     K2B_CUDA_OK(cudaFuncSetAttribute(GridChain, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                      (int)p.bytes));

@@ -103,6 +103,9 @@ int32_t MakeLayout(const k2b200_intersect_args *a, Layout *L) {
   L->off_scan_tmp = take(sizeof(int2) * ScanTmpInts(words));
   L->off_block_cand = take(sizeof(unsigned long long) * (size_t)L->count_blocks);
   L->off_totals = take(64);
+  L->lane_plan = LanePlanApplies(*L, a);
+  L->off_plan = take(L->lane_plan ? sizeof(int32_t) * 2 * (size_t)a->num_fsas * kLaneThreads : 0);
+  L->off_unfit = take(sizeof(int32_t) * (size_t)a->num_fsas);
   L->total_bytes = off;
   return kOk;
 }
@@ -490,19 +493,29 @@ __global__ void EmitTails(const FsaInfo *__restrict__ infos, int32_t n, int64_t 
     for (int32_t t = 0; t <= f.tk; ++t) out.level_splits[f.level_off + t] = first;
 }
 
-int32_t RunViterbi(const Layout &L, const k2b200_intersect_args *a, char *ws,
-                          cudaStream_t stream) {
+int32_t RunViterbi(const Layout &L, const k2b200_intersect_args *a, char *ws, cudaStream_t stream,
+                   bool plan_ready) {
   const FsaInfo *d_infos = reinterpret_cast<const FsaInfo *>(ws + L.off_infos);
   float *fwd = reinterpret_cast<float *>(ws + L.off_fwd),
         *bwd = reinterpret_cast<float *>(ws + L.off_bwd);
   if (L.max_states == 0) return kOk;
   int32_t mode = a->viterbi_mode;
   if (mode == 0)
-    mode = RegisterViterbiFits(L, a) ? 3 : (PersistentViterbiFits(L, a) ? 2 : 1);
+    mode = RegisterViterbiFits(L, a) ? 3 : L.lane_plan ? 4 : (PersistentViterbiFits(L, a) ? 2 : 1);
   if (mode == 3) {
     K2B_REQUIRE(RegisterViterbiFits(L, a),
                 "viterbi_mode=3 needs a_max_degree <= 4 and at most 1024 states per graph");
     return LaunchRegisterViterbi(L, a, d_infos, fwd, bwd, stream);
+  }
+  if (mode == 4) {
+    K2B_REQUIRE(L.lane_plan, "viterbi_mode=4 needs graphs of at most %d states that fit in "
+                "shared memory, with some state of more than four arcs", kLaneThreads);
+    if (!plan_ready) K2B_FORWARD(LaunchPlanLanes(L, a, ws, stream));
+    const int32_t *unfit = reinterpret_cast<const int32_t *>(ws + L.off_unfit);
+    K2B_FORWARD(LaunchLanesViterbi(L, a, d_infos, fwd, bwd,
+                                   reinterpret_cast<const int32_t *>(ws + L.off_plan), unfit,
+                                   stream));
+    return LaunchPersistentViterbi(L, a, d_infos, fwd, bwd, stream, unfit);
   }
   if (mode == 2) {
     K2B_REQUIRE(PersistentViterbiFits(L, a),

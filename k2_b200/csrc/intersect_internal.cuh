@@ -27,14 +27,17 @@ struct Layout {
   int32_t max_states = 0, max_tk = 0, max_arcs = 0;
   // byte offsets into the workspace
   size_t off_infos, off_cutoffs, off_fwd, off_bwd, off_mask, off_counts, off_scan_tmp,
-      off_block_cand, off_totals, total_bytes;
+      off_block_cand, off_totals, off_plan, off_unfit, total_bytes;
+  // graphs with states of more than four arcs, small enough for one CTA: lanes are
+  // assigned to states by a plan (viterbi_persistent.cu)
+  bool lane_plan = false;
   int32_t count_blocks, tiles_per_pair, emit_tiles_per_pair;
 };
 
 // intersect.cu
 int32_t MakeLayout(const k2b200_intersect_args *a, Layout *L);
 int32_t RunViterbi(const Layout &L, const k2b200_intersect_args *a, char *ws,
-                   cudaStream_t stream);
+                   cudaStream_t stream, bool plan_ready = false);
 int32_t PruneLoop(const Layout &L, const k2b200_intersect_args *args, char *ws,
                   cudaStream_t stream, float *beam_io, long long *h_totals);
 // cutoffs[i] = min(best forward, best backward total) - beam, from the Viterbi grids
@@ -45,7 +48,18 @@ int32_t LaunchCutoffs(const Layout &L, const k2b200_intersect_args *a, char *ws,
 bool PersistentViterbiFits(const Layout &L, const k2b200_intersect_args *a);
 int32_t LaunchPersistentViterbi(const Layout &L, const k2b200_intersect_args *a,
                                 const FsaInfo *d_infos, float *fwd, float *bwd,
-                                cudaStream_t stream);
+                                cudaStream_t stream, const int32_t *only_unfit = nullptr);
+
+// Lane plans: CTA size and arcs per lane of the kernels that use them.
+constexpr int kLaneThreads = 768;
+constexpr int kLaneDeg = 8;
+bool LanePlanApplies(const Layout &L, const k2b200_intersect_args *a);
+// Clears unfit[] and, when L.lane_plan, writes the plans of both directions.
+int32_t LaunchPlanLanes(const Layout &L, const k2b200_intersect_args *a, char *ws,
+                        cudaStream_t stream);
+int32_t LaunchLanesViterbi(const Layout &L, const k2b200_intersect_args *a,
+                           const FsaInfo *d_infos, float *fwd, float *bwd, const int32_t *plan,
+                           const int32_t *unfit, cudaStream_t stream);
 
 bool RegisterViterbiFits(const Layout &L, const k2b200_intersect_args *a);
 int32_t LaunchRegisterViterbi(const Layout &L, const k2b200_intersect_args *a,

@@ -54,8 +54,9 @@ PersistentViterbi(const FsaInfo *__restrict__ infos, const Arc *__restrict__ arc
                   const int32_t *__restrict__ in_splits, const int32_t *__restrict__ in_arcs,
                   const float *__restrict__ scores, int32_t cols, float *__restrict__ fwd,
                   float *__restrict__ bwd, int32_t s_pad, int32_t a_pad, int32_t row_pad,
-                  int32_t stages, int32_t lanes_log2) {
+                  int32_t stages, int32_t lanes_log2, const int32_t *__restrict__ only_unfit) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
+  if (only_unfit != nullptr && !only_unfit[blockIdx.y]) return;
   const FsaInfo f = infos[blockIdx.y];
   const int dir = blockIdx.x;  // 0 forward, 1 backward
   const int32_t S = f.num_states, A = f.num_arcs, Tk = f.tk;
@@ -225,6 +226,231 @@ RegisterViterbi(const FsaInfo *__restrict__ infos, const Arc *__restrict__ arcs,
   }
 }
 
+// ---------------------------------------------------------------------------
+// Lane plans.  The recursion kernel keeps the arcs of state s in the registers of
+// G(s) = ceil(degree(s) / kDeg) lanes of one warp, so that a frame costs every lane
+// the same few arcs whatever the degree distribution of the graph is.  PlanLanes
+// lays the lane groups of one graph and direction out over a CTA of kLaneThreads
+// threads: groups sorted by size, largest first (states in increasing order within
+// a size), packed next-fit into warps - a group never straddles two warps.
+//   plan[(dir * n + i) * kLaneThreads + thread] = state | lane << 16 | G << 24, or -1
+// unfit[i] is set when graph i needs more lanes than a CTA has (or has more than
+// 32 * kDeg arcs on a state); the shared-memory kernels below take those graphs.
+// Graphs whose largest degree is at most kDeg need no plan: thread s owns state s.
+// ---------------------------------------------------------------------------
+__global__ void __launch_bounds__(256)
+PlanLanes(const FsaInfo *__restrict__ infos, int32_t n,
+          const int32_t *__restrict__ a_row_splits2, const int32_t *__restrict__ in_splits,
+          int32_t k_deg, int32_t *__restrict__ plan, int32_t *__restrict__ unfit) {
+  // per group size G = 1..32: number of states, lanes left in the warp where the
+  // size class starts, first lane of that start, first lane of the following warps
+  __shared__ int32_t count[33], head_room[33], head_pos[33], body_pos[33];
+  __shared__ int32_t bad;
+  const int32_t i = blockIdx.y, dir = blockIdx.x;
+  const FsaInfo f = infos[i];
+  const int32_t S = f.num_states;
+  const int tid = threadIdx.x, nt = blockDim.x;
+  int32_t *out = plan + ((int64_t)dir * n + i) * kLaneThreads;
+  for (int32_t t = tid; t < kLaneThreads; t += nt) out[t] = -1;
+  if (tid < 33) count[tid] = 0;
+  if (tid == 0) bad = S > kLaneThreads;
+  __syncthreads();
+  const int32_t *splits = (dir == 0 ? in_splits : a_row_splits2) + f.state_off;
+  auto lanes_of = [&](int32_t s) {
+    const int32_t deg = splits[s + 1] - splits[s];
+    return deg <= k_deg ? 1 : (deg + k_deg - 1) / k_deg;
+  };
+  if (S <= kLaneThreads)
+    for (int32_t s = tid; s < S; s += nt) {
+      const int32_t G = lanes_of(s);
+      if (G > 32) bad = 1; else atomicAdd(&count[G], 1);
+    }
+  __syncthreads();
+  if (tid == 0 && !bad) {
+    int32_t pos = 0;
+    for (int G = 32; G >= 1; --G) {
+      const int32_t c = count[G];
+      if (c == 0) continue;
+      const int32_t room = (32 - (pos & 31)) / G;  // groups that still fit in this warp
+      const int32_t per_warp = 32 / G;
+      head_room[G] = room;
+      head_pos[G] = pos;
+      if (c <= room) {
+        pos += c * G;
+      } else {
+        const int32_t rest = c - room;
+        const int32_t body = (pos + room * G + 31) & ~31;
+        body_pos[G] = body;
+        pos = body + (rest / per_warp) * 32 + (rest % per_warp) * G;
+      }
+      if (pos > kLaneThreads) bad = 1;
+    }
+  }
+  __syncthreads();
+  if (bad) {
+    if (tid == 0) atomicOr(&unfit[i], 1);
+    return;
+  }
+  // warp w places the size classes w, w + 8, ...: ordered compaction by ballot
+  const int warp = tid >> 5, lane = tid & 31;
+  for (int G = 1 + warp; G <= 32; G += nt >> 5) {
+    if (count[G] == 0) continue;
+    const int32_t per_warp = 32 / G, room = head_room[G];
+    int32_t seen = 0;
+    for (int32_t s0 = 0; s0 < S; s0 += 32) {
+      const int32_t s = s0 + lane;
+      const bool in = s < S && lanes_of(s) == G;
+      const uint32_t m = __ballot_sync(0xffffffffu, in);
+      if (in) {
+        const int32_t j = seen + __popc(m & ((1u << lane) - 1u));
+        int32_t p0;
+        if (j < room) {
+          p0 = head_pos[G] + j * G;
+        } else {
+          const int32_t r = j - room;
+          p0 = body_pos[G] + (r / per_warp) * 32 + (r % per_warp) * G;
+        }
+        for (int32_t g = 0; g < G; ++g) out[p0 + g] = s | (g << 16) | (G << 24);
+      }
+      seen += __popc(m);
+    }
+  }
+}
+
+
+bool LanePlanApplies(const Layout &L, const k2b200_intersect_args *a) {
+  const bool register_fit = a->a_max_degree > 0 && a->a_max_degree <= 4 && L.max_states <= 1024;
+  return !register_fit && L.max_states <= kLaneThreads && a->num_fsas <= 65535 &&
+         PersistentViterbiFits(L, a);
+}
+
+int32_t LaunchPlanLanes(const Layout &L, const k2b200_intersect_args *a, char *ws,
+                        cudaStream_t stream) {
+  int32_t *unfit = reinterpret_cast<int32_t *>(ws + L.off_unfit);
+  K2B_CUDA_OK(cudaMemsetAsync(unfit, 0, sizeof(int32_t) * a->num_fsas, stream));
+  if (!L.lane_plan) return kOk;
+  { PlanLanes<<<dim3(2, a->num_fsas), 256, 0, stream>>>(
+      reinterpret_cast<const FsaInfo *>(ws + L.off_infos), a->num_fsas, a->a_row_splits2,
+      a->a_in_splits, kLaneDeg, reinterpret_cast<int32_t *>(ws + L.off_plan), unfit);
+    NoteLaunch(); }
+  K2B_CUDA_OK(cudaGetLastError());
+  return kOk;
+}
+
+// ---------------------------------------------------------------------------
+// Viterbi recursion with planned lanes: as RegisterViterbi, but the arcs of a state
+// are spread over the G(s) lanes its plan gives it, which take the max by shuffles.
+// Graphs marked unfit are skipped (PersistentViterbi handles them).
+// ---------------------------------------------------------------------------
+template <int kDeg, int kRegPrefetch>
+__global__ void __launch_bounds__(kLaneThreads)
+LanesViterbi(const FsaInfo *__restrict__ infos, int32_t n, const Arc *__restrict__ arcs,
+             const int32_t *__restrict__ a_row_splits2, const int32_t *__restrict__ in_splits,
+             const int32_t *__restrict__ in_arcs, const float *__restrict__ scores,
+             int32_t cols, float *__restrict__ fwd, float *__restrict__ bwd,
+             const int32_t *__restrict__ plan, const int32_t *__restrict__ unfit) {
+  __shared__ float buf[2][kLaneThreads];
+  const int32_t i = blockIdx.y;
+  if (unfit[i]) return;
+  const FsaInfo f = infos[i];
+  const int dir = blockIdx.x;
+  const int32_t S = f.num_states, Tk = f.tk;
+  if (S == 0) return;
+  const int tid = threadIdx.x;
+  int32_t s = -1, g = 0, G = 1;
+  {
+    const int32_t code = plan[((int64_t)dir * n + i) * kLaneThreads + tid];
+    if (code >= 0) {
+      s = code & 0xffff;
+      g = (code >> 16) & 0xff;
+      G = code >> 24;
+    }
+  }
+  int32_t other[kDeg], col[kDeg];
+  float w[kDeg];
+#pragma unroll
+  for (int j = 0; j < kDeg; ++j) {
+    other[j] = 0;
+    col[j] = 0;
+    w[j] = -INFINITY;
+  }
+  if (s >= 0) {
+    const int32_t *splits = dir == 0 ? in_splits : a_row_splits2;
+    const int32_t a0 = splits[f.state_off + s], a1 = splits[f.state_off + s + 1];
+#pragma unroll
+    for (int j = 0; j < kDeg; ++j) {
+      const int32_t k = a0 + g + j * G;
+      if (k < a1) {
+        const Arc arc = arcs[dir == 0 ? in_arcs[k] : k];
+        other[j] = dir == 0 ? arc.src : arc.dest;
+        const int32_t c = arc.label + 1;
+        if (c >= 0 && c < cols) {
+          col[j] = c;
+          w[j] = arc.score;
+        }
+      }
+    }
+  }
+  // step t (1..Tk) consumes dense row t-1 (forward) or Tk-t (backward)
+  const float *base = scores + (int64_t)f.row0 * cols;
+  auto row_of = [&](int32_t step) {
+    step = step > Tk ? Tk : step;
+    return dir == 0 ? step - 1 : Tk - step;
+  };
+  float x[kDeg][kRegPrefetch];
+#pragma unroll
+  for (int d = 0; d < kRegPrefetch; ++d) {
+    const int32_t r = row_of(1 + d) * cols;
+#pragma unroll
+    for (int j = 0; j < kDeg; ++j) x[j][d] = __ldg(base + r + col[j]);
+  }
+  float *grid = (dir == 0 ? fwd : bwd) + f.grid_off;
+  for (int32_t q = tid; q < S; q += blockDim.x) {
+    const float v = (dir == 0 ? (q == 0) : (q == S - 1)) ? 0.0f : -INFINITY;
+    buf[0][q] = v;
+    grid[(int64_t)(dir == 0 ? 0 : Tk) * S + q] = v;
+  }
+  for (int32_t t0 = 1; t0 <= Tk; t0 += kRegPrefetch) {
+#pragma unroll
+    for (int u = 0; u < kRegPrefetch; ++u) {
+      const int32_t t = t0 + u;
+      if (t > Tk) break;
+      __syncthreads();
+      const float *cur = buf[(t - 1) & 1];
+      float best = -INFINITY;
+#pragma unroll
+      for (int j = 0; j < kDeg; ++j) {
+        const float v = __fadd_rn(__fadd_rn(cur[other[j]], w[j]), x[j][u]);
+        best = v > best ? v : best;
+      }
+      const int32_t r = row_of(t + kRegPrefetch) * cols;
+#pragma unroll
+      for (int j = 0; j < kDeg; ++j) x[j][u] = __ldg(base + r + col[j]);
+#pragma unroll
+      for (int32_t d = 16; d > 0; d >>= 1) {
+        const float o = __shfl_down_sync(0xffffffffu, best, d);
+        if (g + d < G) best = o > best ? o : best;
+      }
+      if (s >= 0 && g == 0) {
+        buf[t & 1][s] = best;
+        grid[(int64_t)(dir == 0 ? t : Tk - t) * S + s] = best;
+      }
+    }
+  }
+}
+
+int32_t LaunchLanesViterbi(const Layout &L, const k2b200_intersect_args *a,
+                           const FsaInfo *d_infos, float *fwd, float *bwd, const int32_t *plan,
+                           const int32_t *unfit, cudaStream_t stream) {
+  (void)L;
+  dim3 grid(2, a->num_fsas);
+  { LanesViterbi<kLaneDeg, 4><<<grid, kLaneThreads, 0, stream>>>(
+      d_infos, a->num_fsas, reinterpret_cast<const Arc *>(a->a_arcs), a->a_row_splits2,
+      a->a_in_splits, a->a_in_arcs, a->scores, a->cols, fwd, bwd, plan, unfit); NoteLaunch(); }
+  K2B_CUDA_OK(cudaGetLastError());
+  return kOk;
+}
+
 int32_t LaunchRegisterViterbi(const Layout &L, const k2b200_intersect_args *a,
                               const FsaInfo *d_infos, float *fwd, float *bwd,
                               cudaStream_t stream) {
@@ -247,7 +473,7 @@ int32_t LaunchRegisterViterbi(const Layout &L, const k2b200_intersect_args *a,
 
 int32_t LaunchPersistentViterbi(const Layout &L, const k2b200_intersect_args *a,
                                 const FsaInfo *d_infos, float *fwd, float *bwd,
-                                cudaStream_t stream) {
+                                cudaStream_t stream, const int32_t *only_unfit) {
   SmemPlan p = PlanSmem(L.max_states, L.max_arcs, a->cols);
   K2B_CUDA_OK(cudaFuncSetAttribute(PersistentViterbi, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                    (int)p.bytes));
@@ -261,7 +487,7 @@ int32_t LaunchPersistentViterbi(const Layout &L, const k2b200_intersect_args *a,
   { PersistentViterbi<<<grid, threads, p.bytes, stream>>>(
       d_infos, reinterpret_cast<const Arc *>(a->a_arcs), a->a_row_splits2, a->a_in_splits,
       a->a_in_arcs, a->scores, a->cols, fwd, bwd, p.s_pad, p.a_pad, p.row_pad, p.stages,
-      lanes_log2); NoteLaunch(); }
+      lanes_log2, only_unfit); NoteLaunch(); }
   K2B_CUDA_OK(cudaGetLastError());
   return kOk;
 }

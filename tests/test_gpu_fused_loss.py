@@ -61,6 +61,25 @@ def test_random_fsa_vecs():
         _compare(a, scores, brs, beam, amap, tot_grad, f"trial {trial}")
 
 
+def test_extreme_scores_take_the_per_state_exponent_kernels():
+    # arc scores of +-100 and dense rows near -300 are outside what the
+    # shared-exponent recursion accepts: those graphs are recomputed by the
+    # mantissa/exponent kernels; the results must not show the seam
+    rng = np.random.default_rng(23)
+    for trial in range(12):
+        n = int(rng.integers(1, 5))
+        a = random_fsa_vec(rng, n, acyclic=bool(trial % 2))
+        scores, brs = random_dense(rng, n, 10, 5, low_rows=False)
+        if trial % 3 == 0:
+            a.arcs[:, 3] = (a.scores * 40.0).astype(np.float32).view(np.int32)
+        elif trial % 3 == 1:
+            finite = np.isfinite(scores)
+            scores = np.where(finite, scores * 150.0, scores).astype(np.float32)
+        else:
+            a.arcs[::3, 3] = np.float32(-np.inf).view(np.int32)
+        _compare(a, scores, brs, 1.0e4 if trial % 3 else 50.0, tag=f"extreme {trial}")
+
+
 def test_micro_example():
     from test_gpu_parity import _micro
     a, scores, brs = _micro()
