@@ -172,7 +172,7 @@ GridChainLanes(const FsaInfo *__restrict__ infos, int32_t n, const Arc *__restri
   constexpr int32_t kNone = INT32_MIN;
   const int32_t i = blockIdx.y;
   const int dir = blockIdx.x;
-  if (plan != nullptr && unfit[i]) return;
+  if (plan != nullptr && (unfit[i] & 1)) return;  // no plan for this graph
   const FsaInfo f = infos[i];
   const int32_t S = f.num_states, Tk = f.tk, cols = dp.cols;
   const int tid = threadIdx.x, nt = blockDim.x;
@@ -232,7 +232,7 @@ GridChainLanes(const FsaInfo *__restrict__ infos, int32_t n, const Arc *__restri
     MbarInitFence();
   }
   if (__syncthreads_or(risky)) {  // also orders the initialisation above
-    if (tid == 0) atomicOr(&unfit[i], 1);
+    if (tid == 0) atomicOr(&unfit[i], 2);
     return;
   }
   const float cutoff = cutoffs[i];
@@ -385,7 +385,7 @@ GridChainLanes(const FsaInfo *__restrict__ infos, int32_t n, const Arc *__restri
   const int32_t any_risky = __syncthreads_or(risky);
   if (gave_up) {
     if (tid == 0) {
-      atomicOr(&unfit[i], 1);
+      atomicOr(&unfit[i], 2);
       // copies may still be in flight towards this CTA's shared memory: give them
       // a bounded while before the CTA retires
       for (int k = 0; k < 1000; ++k) __nanosleep(1000);
@@ -394,7 +394,7 @@ GridChainLanes(const FsaInfo *__restrict__ infos, int32_t n, const Arc *__restri
     return;
   }
   if (any_risky) {
-    if (tid == 0) atomicOr(&unfit[i], 1);
+    if (tid == 0) atomicOr(&unfit[i], 2);
     return;
   }
   if (dir == 0 && s == S - 1 && g == 0)
@@ -434,9 +434,10 @@ GridGradWarp(const FsaInfo *__restrict__ infos, const Arc *__restrict__ arcs,
              const ProbState *__restrict__ beta, const double *__restrict__ tot_grad,
              int32_t tot_grad_stride, float *__restrict__ grad_a, float *__restrict__ grad_b,
              int32_t frames_per_cta, int32_t lanes_log2, int32_t s_pad, int32_t ga_in_smem,
-             int32_t exclusive_rows) {
+             int32_t exclusive_rows, const int32_t *__restrict__ only_noplan) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   const int32_t i = blockIdx.y;
+  if (only_noplan != nullptr && !(only_noplan[i] & 1)) return;  // the lane kernel took it
   const FsaInfo f = infos[i];
   const int32_t S = f.num_states, A = f.num_arcs, Tk = f.tk, cols = dp.cols;
   const int32_t u0 = blockIdx.x * frames_per_cta;
@@ -444,17 +445,22 @@ GridGradWarp(const FsaInfo *__restrict__ infos, const Arc *__restrict__ arcs,
   const int32_t u1 = min(u0 + frames_per_cta, Tk);
   const int tid = threadIdx.x, nt = blockDim.x, lane = tid & 31, warp = tid >> 5;
   NextState *nb_all = reinterpret_cast<NextState *>(smem_raw);  // [warps][s_pad] if kStage
-  float *gb = reinterpret_cast<float *>(nb_all + (kStage ? kGradWarps * s_pad : 0));
-  float *ga = gb + (((size_t)frames_per_cta * cols + 3) & ~(size_t)3);  // [A] when ga_in_smem
+  // sums of posteriors in fixed point (integer atomics are native in shared memory,
+  // float ones are compare-and-swap loops; the sums also become order independent):
+  // gb per (frame, column) in 2^-31 units (a sum of at most 1), ga per arc in 2^-26
+  // units (at most one per frame of the chunk, frames_per_cta <= 32)
+  uint32_t *gb = reinterpret_cast<uint32_t *>(nb_all + (kStage ? kGradWarps * s_pad : 0));
+  uint32_t *ga = gb + (((size_t)frames_per_cta * cols + 3) & ~(size_t)3);  // [A] when ga_in_smem
   const ProbState *al = alpha + f.grid_off, *be = beta + f.grid_off;
   const ProbState z = al[(int64_t)Tk * S + (S - 1)];
   if (z.m == 0.0) return;  // no path survives: all gradients are zero
-  const double zinv = tot_grad[(int64_t)i * tot_grad_stride] / z.m;
+  const double zinv = 1.0 / z.m;
+  const float tg = (float)tot_grad[(int64_t)i * tot_grad_stride];
   const int32_t zk = -z.e;
   const int32_t gb_elems = (u1 - u0) * cols;
-  for (int32_t k = tid; k < gb_elems; k += nt) gb[k] = 0.0f;
+  for (int32_t k = tid; k < gb_elems; k += nt) gb[k] = 0u;
   if (ga_in_smem)
-    for (int32_t k = tid; k < A; k += nt) ga[k] = 0.0f;
+    for (int32_t k = tid; k < A; k += nt) ga[k] = 0u;
   __syncthreads();
   const float cutoff = cutoffs[i];
   const float *fgrid = vfwd + f.grid_off, *bgrid = vbwd + f.grid_off;
@@ -482,7 +488,7 @@ GridGradWarp(const FsaInfo *__restrict__ infos, const Arc *__restrict__ arcs,
     const unsigned char *rec = dense + ((int64_t)f.row0 + u) * dp.pitch;
     const float *lprow = PackLp(rec);
     const double *prow = PackP(rec, dp);
-    float *gbrow = gb + (size_t)(u - u0) * cols;
+    uint32_t *gbrow = gb + (size_t)(u - u0) * cols;
     for (int32_t c0 = 0; c0 < S; c0 += 32) {
       const int32_t q = c0 + lane;
       float fu = -INFINITY, bu = -INFINITY;
@@ -532,8 +538,9 @@ GridGradWarp(const FsaInfo *__restrict__ infos, const Arc *__restrict__ arcs,
           const double prod = m1 * bm * zinv;
           if (prod == 0.0) continue;
           const float post = (float)(prod * Pow2Clamped(e1 + ae + af.k + bexp + zk));
-          atomicAdd(&gbrow[c], post);
-          atomicAdd(ga_in_smem ? &ga[k] : &grad_a[f.arc_off + k], post);
+          atomicAdd(&gbrow[c], __float2uint_rn(post * 2147483648.0f));
+          if (ga_in_smem) atomicAdd(&ga[k], __float2uint_rn(post * 67108864.0f));
+          else atomicAdd(&grad_a[f.arc_off + k], tg * post);
         }
       }
     }
@@ -541,16 +548,203 @@ GridGradWarp(const FsaInfo *__restrict__ infos, const Arc *__restrict__ arcs,
   __syncthreads();
   float *grow = grad_b + ((int64_t)f.row0 + u0) * cols;
   for (int32_t k = tid; k < gb_elems; k += nt) {
-    const float v = gb[k];
-    if (v != 0.0f) {
+    const uint32_t fixed = gb[k];
+    if (fixed != 0u) {
+      const float v = tg * ((float)fixed * (1.0f / 2147483648.0f));
       if (exclusive_rows) grow[k] = v; else atomicAdd(&grow[k], v);
     }
   }
   if (ga_in_smem)
     for (int32_t k = tid; k < A; k += nt) {
-      const float v = ga[k];
-      if (v != 0.0f) atomicAdd(&grad_a[f.arc_off + k], v);
+      const uint32_t fixed = ga[k];
+      if (fixed != 0u) atomicAdd(&grad_a[f.arc_off + k], tg * ((float)fixed * (1.0f / 67108864.0f)));
     }
+}
+
+// ---------------------------------------------------------------------------
+// Gradients with planned lanes, for the graphs PlanLanes placed (dense lattices:
+// most states and a good part of the arcs survive on every frame).  grid = (frame
+// chunks, pairs).  The CTA first copies everything its frames can touch into shared
+// memory - per (level, state) the surviving alpha and beta, normalised, and the
+// Viterbi scores the arc test needs; per frame the packed dense row - then every
+// lane walks the chunk's frames over the arcs it holds in registers (leaving
+// order, the plan of the backward recursion) with no further barrier.
+// ---------------------------------------------------------------------------
+template <int kDeg>
+__global__ void __launch_bounds__(kLaneThreads)
+GridGradLanes(const FsaInfo *__restrict__ infos, int32_t n, const Arc *__restrict__ arcs,
+              const int32_t *__restrict__ a_row_splits2, const unsigned char *__restrict__ dense,
+              DensePack dp, const float *__restrict__ vfwd, const float *__restrict__ vbwd,
+              const float *__restrict__ cutoffs, const ProbState *__restrict__ alpha,
+              const ProbState *__restrict__ beta, const double *__restrict__ tot_grad,
+              int32_t tot_grad_stride, float *__restrict__ grad_a, float *__restrict__ grad_b,
+              const int32_t *__restrict__ plan, const int32_t *__restrict__ unfit,
+              int32_t frames_per_cta, int32_t sub_frames, int32_t s_pad,
+              int32_t exclusive_rows) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  const int32_t i = blockIdx.y;
+  if (unfit[i] & 1) return;  // no plan: the warp-per-frame kernel takes this graph
+  const FsaInfo f = infos[i];
+  const int32_t S = f.num_states, Tk = f.tk, cols = dp.cols;
+  const int32_t cta_u0 = blockIdx.x * frames_per_cta;
+  if (S == 0 || cta_u0 >= Tk) return;
+  const int32_t cta_u1 = min(cta_u0 + frames_per_cta, Tk);
+  const int tid = threadIdx.x, nt = blockDim.x;
+  // per (level, state), as separate arrays so that gathers by state spread over the
+  // banks: alpha / Z and beta mantissas (0 when pruned or unreachable), their
+  // exponents, and the Viterbi scores (-inf when pruned)
+  const int32_t lv_elems = (sub_frames + 1) * s_pad;
+  double *st_am = reinterpret_cast<double *>(smem_raw);
+  double *st_bm = st_am + lv_elems;
+  int32_t *st_ae = reinterpret_cast<int32_t *>(st_bm + lv_elems);
+  int32_t *st_be = st_ae + lv_elems;
+  float *st_fo = reinterpret_cast<float *>(st_be + lv_elems);
+  float *st_bo = st_fo + lv_elems;
+  unsigned char *rows = reinterpret_cast<unsigned char *>(st_bo + lv_elems);
+  // posteriors per (frame, column) in fixed point, 2^-31 units: integer atomics are
+  // native in shared memory (float ones are compare-and-swap loops) and make the sum
+  // independent of the order of the additions
+  uint32_t *gb = reinterpret_cast<uint32_t *>(rows + (size_t)sub_frames * dp.pitch);
+  const ProbState *al = alpha + f.grid_off, *be = beta + f.grid_off;
+  const ProbState z = al[(int64_t)Tk * S + (S - 1)];
+  if (z.m == 0.0) return;  // no path survives: all gradients are zero
+  int32_t zex;
+  const double zm = SplitExp(z.m, &zex);
+  const double zinv = 1.0 / zm;
+  const float tg = (float)tot_grad[(int64_t)i * tot_grad_stride];
+  const int32_t zk = -(z.e + zex);
+  const float cutoff = cutoffs[i];
+  const float *fgrid = vfwd + f.grid_off, *bgrid = vbwd + f.grid_off;
+  // ---- this lane's arcs --------------------------------------------------------
+  int32_t s = -1, g = 0, G = 1;
+  {
+    const int32_t code = plan[((int64_t)n + i) * kLaneThreads + tid];  // direction 1
+    if (code >= 0) {
+      s = code & 0xffff;
+      g = (code >> 16) & 0xff;
+      G = code >> 24;
+    }
+  }
+  int32_t dest_col[kDeg];
+  float w[kDeg];
+  double ewf[kDeg];
+  int32_t ewk[kDeg];
+  float ga[kDeg];
+  int32_t first_arc = 0;
+#pragma unroll
+  for (int j = 0; j < kDeg; ++j) {
+    dest_col[j] = cols << 16;
+    w[j] = -INFINITY;
+    ewf[j] = 0.0;
+    ewk[j] = 0;
+    ga[j] = 0.0f;
+  }
+  if (s >= 0) {
+    const int32_t a0 = a_row_splits2[f.state_off + s], a1 = a_row_splits2[f.state_off + s + 1];
+    first_arc = a0 + g;
+#pragma unroll
+    for (int j = 0; j < kDeg; ++j) {
+      const int32_t k = a0 + g + j * G;
+      if (k < a1) {
+        const Arc arc = arcs[k];
+        const int32_t c = arc.label + 1;
+        if (c >= 0 && c < cols && arc.score != -INFINITY) {
+          dest_col[j] = arc.dest | (c << 16);
+          w[j] = arc.score;
+          ExpToMantExp(arc.score, &ewf[j], &ewk[j]);
+        }
+      }
+    }
+  }
+  // the CTA's frames in sub-chunks that fit in shared memory; arcs and their
+  // gradients stay in registers throughout
+  for (int32_t u0 = cta_u0; u0 < cta_u1; u0 += sub_frames) {
+    const int32_t u1 = min(u0 + sub_frames, cta_u1), nf = u1 - u0;
+    __syncthreads();  // the previous sub-chunk is flushed
+    // ---- stage levels u0 .. u1 ---------------------------------------------------
+    for (int32_t idx = tid; idx < (nf + 1) * S; idx += nt) {
+      const int32_t l = idx / S, q = idx - l * S;
+      const int64_t gi = (int64_t)(u0 + l) * S + q;
+      const float fu = fgrid[gi], bu = bgrid[gi];
+      double am = 0.0, bm = 0.0;
+      int32_t ae = 0, bexp = 0;
+      const bool keep = __fadd_rn(fu, bu) > cutoff;
+      if (keep) {
+        const ProbState a = al[gi], b = be[gi];
+        int32_t ex;
+        am = SplitExp(a.m, &ex) * zinv;
+        ae = a.m == 0.0 ? 0 : a.e + ex + zk;
+        bm = SplitExp(b.m, &ex);
+        bexp = b.m == 0.0 ? 0 : b.e + ex;
+      }
+      const int32_t k = l * s_pad + q;
+      st_am[k] = am;
+      st_bm[k] = bm;
+      st_ae[k] = ae;
+      st_be[k] = bexp;
+      st_fo[k] = keep ? fu : -INFINITY;
+      st_bo[k] = keep ? bu : -INFINITY;
+    }
+    {
+      const int32_t chunks = dp.pitch / 16;
+      const uint4 *src = reinterpret_cast<const uint4 *>(dense + ((int64_t)f.row0 + u0) * dp.pitch);
+      uint4 *dst = reinterpret_cast<uint4 *>(rows);
+      for (int32_t k = tid; k < nf * chunks; k += nt) dst[k] = src[k];
+    }
+    for (int32_t k = tid; k < nf * cols; k += nt) gb[k] = 0u;
+    __syncthreads();
+    if (s >= 0) {
+      for (int32_t l = 0; l < nf; ++l) {
+        const double own_am = st_am[l * s_pad + s];
+        if (own_am == 0.0) continue;  // pruned or unreachable
+        const int32_t own_ae = st_ae[l * s_pad + s];
+        const float own_fo = st_fo[l * s_pad + s];
+        const int32_t nx = (l + 1) * s_pad;
+        const unsigned char *rec = rows + (size_t)l * dp.pitch;
+        const float *lprow = PackLp(rec);
+        const double *prow = PackP(rec, dp);
+        uint32_t *gbrow = gb + l * cols;
+        // all posteriors first, then the additions: a shared-memory atomic between
+        // two arcs would order the loads of the second behind it
+        float post[kDeg];
+#pragma unroll
+        for (int j = 0; j < kDeg; ++j) {
+          const int32_t d = dest_col[j] & 0xffff, c = dest_col[j] >> 16;
+          const float sc = __fadd_rn(w[j], lprow[c]);
+          const float bo = st_bo[nx + d];
+          post[j] = 0.0f;
+          if (__fadd_rn(__fadd_rn(own_fo, sc), bo) > cutoff) {
+            const double bm = st_bm[nx + d];
+            const int32_t e = own_ae + ewk[j] + st_be[nx + d];
+            // alpha/Z, exp(w) and beta have mantissas in [0.5, 2); exp(lp) >= 1e-300
+            const double prod = own_am * ewf[j] * prow[c] * bm;
+            post[j] = (float)(prod * Pow2Clamped(e));
+          }
+        }
+#pragma unroll
+        for (int j = 0; j < kDeg; ++j) {
+          if (post[j] != 0.0f) {
+            ga[j] += post[j];
+            atomicAdd(&gbrow[dest_col[j] >> 16], __float2uint_rn(post[j] * 2147483648.0f));
+          }
+        }
+      }
+    }
+    __syncthreads();
+    float *grow = grad_b + ((int64_t)f.row0 + u0) * cols;
+    for (int32_t k = tid; k < nf * cols; k += nt) {
+      const uint32_t fixed = gb[k];
+      if (fixed != 0u) {
+        const float v = tg * ((float)fixed * (1.0f / 2147483648.0f));
+        if (exclusive_rows) grow[k] = v; else atomicAdd(&grow[k], v);
+      }
+    }
+  }
+  if (s >= 0) {
+#pragma unroll
+    for (int j = 0; j < kDeg; ++j)
+      if (ga[j] != 0.0f) atomicAdd(&grad_a[first_arc + j * G], tg * ga[j]);
+  }
 }
 
 // ---------------------------------------------------------------------------
@@ -808,7 +1002,7 @@ static int32_t LaunchChainLanes(const LossLayout &LL, const k2b200_intersect_arg
 template <bool kStage>
 static int32_t LaunchGrad(const LossLayout &LL, const k2b200_intersect_args *args, char *ws,
                           const double *tot_grad, int32_t stride, float *grad_a, float *grad_b,
-                          cudaStream_t stream) {
+                          const int32_t *only_noplan, cudaStream_t stream) {
   const Layout &L = LL.base;
   const int32_t s_pad = (L.max_states + 3) & ~3;
   const size_t nb_bytes = kStage ? sizeof(NextState) * kGradWarps * (size_t)s_pad : 0;
@@ -840,7 +1034,40 @@ static int32_t LaunchGrad(const LossLayout &LL, const k2b200_intersect_args *arg
       reinterpret_cast<const float *>(ws + L.off_cutoffs),
       reinterpret_cast<const ProbState *>(ws + LL.off_alpha),
       reinterpret_cast<const ProbState *>(ws + LL.off_beta), tot_grad, stride, grad_a, grad_b,
-      frames, lg, s_pad, ga_in_smem, LL.exclusive_rows ? 1 : 0); NoteLaunch(); }
+      frames, lg, s_pad, ga_in_smem, LL.exclusive_rows ? 1 : 0, only_noplan); NoteLaunch(); }
+  K2B_CUDA_OK(cudaGetLastError());
+  return kOk;
+}
+
+static int32_t LaunchGradLanes(const LossLayout &LL, const k2b200_intersect_args *args, char *ws,
+                               const double *tot_grad, int32_t stride, float *grad_a,
+                               float *grad_b, cudaStream_t stream) {
+  const Layout &L = LL.base;
+  const int32_t s_pad = (L.max_states + 3) & ~3;
+  auto bytes_for = [&](int32_t frames) {
+    return (size_t)32 * (frames + 1) * s_pad + (size_t)frames * LL.pack.pitch +
+           sizeof(float) * (size_t)frames * args->cols;
+  };
+  int32_t sub = 16;
+  while (sub > 1 && bytes_for(sub) > 100 * 1024) sub >>= 1;
+  const size_t smem = bytes_for(sub);
+  const int32_t frames = 4 * sub;  // per CTA: amortises loading the arcs and adding grad_a
+  K2B_REQUIRE(smem <= kChainSmemBudget, "graphs too large for the fused loss path");
+  K2B_CUDA_OK(cudaFuncSetAttribute(GridGradLanes<kLaneDeg>,
+                                   cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  dim3 grid(CeilDiv(L.max_tk, frames), args->num_fsas);
+  { GridGradLanes<kLaneDeg><<<grid, kLaneThreads, smem, stream>>>(
+      reinterpret_cast<const FsaInfo *>(ws + L.off_infos), args->num_fsas,
+      reinterpret_cast<const Arc *>(args->a_arcs), args->a_row_splits2,
+      reinterpret_cast<const unsigned char *>(ws + LL.off_dense), LL.pack,
+      reinterpret_cast<const float *>(ws + L.off_fwd),
+      reinterpret_cast<const float *>(ws + L.off_bwd),
+      reinterpret_cast<const float *>(ws + L.off_cutoffs),
+      reinterpret_cast<const ProbState *>(ws + LL.off_alpha),
+      reinterpret_cast<const ProbState *>(ws + LL.off_beta), tot_grad, stride, grad_a, grad_b,
+      reinterpret_cast<const int32_t *>(ws + L.off_plan),
+      reinterpret_cast<const int32_t *>(ws + L.off_unfit), frames, sub, s_pad,
+      LL.exclusive_rows ? 1 : 0); NoteLaunch(); }
   K2B_CUDA_OK(cudaGetLastError());
   return kOk;
 }
@@ -972,10 +1199,17 @@ int32_t k2b200_dense_loss_backward(const k2b200_intersect_args *args, void *work
     { ExpArcs<<<CeilDiv(args->num_arcs, 256), 256, 0, stream>>>(
         reinterpret_cast<const Arc *>(args->a_arcs), args->num_arcs,
         reinterpret_cast<ArcFactor *>(ws + LL.off_arc_factors)); NoteLaunch(); }
+  const int32_t *only_noplan = nullptr;
+  if (!LL.identity) {
+    K2B_FORWARD(LaunchGradLanes(LL, args, ws, tot_grad, tot_grad_stride, grad_a, grad_b, stream));
+    only_noplan = reinterpret_cast<const int32_t *>(ws + L.off_unfit);
+  }
   // small graphs: stage level u + 1 per warp; large ones: gather
   if (L.max_states <= 256)
-    return LaunchGrad<true>(LL, args, ws, tot_grad, tot_grad_stride, grad_a, grad_b, stream);
-  return LaunchGrad<false>(LL, args, ws, tot_grad, tot_grad_stride, grad_a, grad_b, stream);
+    return LaunchGrad<true>(LL, args, ws, tot_grad, tot_grad_stride, grad_a, grad_b, only_noplan,
+                            stream);
+  return LaunchGrad<false>(LL, args, ws, tot_grad, tot_grad_stride, grad_a, grad_b, only_noplan,
+                           stream);
 }
 
 }  // extern "C"

@@ -234,7 +234,7 @@ RegisterViterbi(const FsaInfo *__restrict__ infos, const Arc *__restrict__ arcs,
 // threads: groups sorted by size, largest first (states in increasing order within
 // a size), packed next-fit into warps - a group never straddles two warps.
 //   plan[(dir * n + i) * kLaneThreads + thread] = state | lane << 16 | G << 24, or -1
-// unfit[i] is set when graph i needs more lanes than a CTA has (or has more than
+// bit 0 of unfit[i] is set when graph i needs more lanes than a CTA has (or has more than
 // 32 * kDeg arcs on a state); the shared-memory kernels below take those graphs.
 // Graphs whose largest degree is at most kDeg need no plan: thread s owns state s.
 // ---------------------------------------------------------------------------
@@ -351,7 +351,7 @@ LanesViterbi(const FsaInfo *__restrict__ infos, int32_t n, const Arc *__restrict
              const int32_t *__restrict__ plan, const int32_t *__restrict__ unfit) {
   __shared__ float buf[2][kLaneThreads];
   const int32_t i = blockIdx.y;
-  if (unfit[i]) return;
+  if (unfit[i] & 1) return;
   const FsaInfo f = infos[i];
   const int dir = blockIdx.x;
   const int32_t S = f.num_states, Tk = f.tk;
