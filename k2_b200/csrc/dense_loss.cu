@@ -108,6 +108,7 @@ __global__ void ExpArcs(const Arc *__restrict__ arcs, int32_t n, ArcFactor *__re
 
 struct LaneSmem {
   int32_t s_pad, stages;
+  int32_t vrow;  // bytes reserved per Viterbi row in a ring slot (a multiple of 16)
   size_t bytes;
 };
 constexpr size_t kChainSmemBudget = 220 * 1024;
@@ -119,7 +120,9 @@ static LaneSmem PlanLaneSmem(const Layout &L, const DensePack &d, int group) {
   LaneSmem p;
   p.s_pad = (L.max_states + 3) & ~3;
   const size_t fixed = (sizeof(double) + sizeof(float)) * 2 * p.s_pad;
-  p.bytes = fixed + (size_t)d.pitch * group;
+  // a row of S floats starting anywhere, widened to 16-byte boundaries on both sides
+  p.vrow = ((L.max_states * 4 + 15) & ~15) + 16;
+  p.bytes = fixed + ((size_t)d.pitch + 2 * p.vrow) * group;
   p.stages = p.bytes <= kChainSmemBudget ? group : 0;
   return p;
 }
@@ -181,8 +184,10 @@ GridChainLanes(const FsaInfo *__restrict__ infos, int32_t n, const Arc *__restri
     return;
   }
   const int32_t s_pad = sm.s_pad;
-  unsigned char *ring = smem_raw;                                     // [kU][pitch]
-  double *pv = reinterpret_cast<double *>(ring + (size_t)kU * dp.pitch);  // [2][s_pad]
+  // ring slot: the packed dense row, then the forward and the backward Viterbi row
+  const uint32_t slot_bytes = (uint32_t)dp.pitch + 2u * (uint32_t)sm.vrow;
+  unsigned char *ring = smem_raw;                                     // [kU][slot_bytes]
+  double *pv = reinterpret_cast<double *>(ring + (size_t)kU * slot_bytes);  // [2][s_pad]
   float *oth = reinterpret_cast<float *>(pv + 2 * s_pad);             // [2][s_pad]
 
   const bool producer = tid == 0;  // issues the bulk copies
@@ -261,33 +266,35 @@ GridChainLanes(const FsaInfo *__restrict__ infos, int32_t n, const Arc *__restri
   // always finds its row in ring slot u and its operands in buffer u & 1.
   const int64_t step_stride = dir == 0 ? (int64_t)S : -(int64_t)S;
   const unsigned char *dense0 = dense + (int64_t)f.row0 * dp.pitch;
+  // A row of a Viterbi grid starts at any multiple of 4 bytes; the bulk copy takes
+  // the 16-byte aligned range around it (the grids sit inside the workspace with
+  // other arrays before and after them), and the reader skips the leading floats.
+  const unsigned vbytes = (((unsigned)S * 4u + 15u) & ~15u) + 16u;
   auto issue_row = [&](int32_t step, int32_t slot) {  // producer only
     if (step > Tk) return;
     const int64_t row = dir == 0 ? step - 1 : Tk - step;
-    MbarArriveExpectTx(&full[slot], (unsigned)dp.pitch);
-    BulkCopyG2S(ring + (size_t)slot * dp.pitch, dense0 + row * dp.pitch, (unsigned)dp.pitch,
+    const int64_t lv = dir == 0 ? step : Tk - step;
+    unsigned char *dst = ring + (size_t)slot * slot_bytes;
+    const uintptr_t fa = reinterpret_cast<uintptr_t>(fgrid + lv * S) & ~(uintptr_t)15;
+    const uintptr_t ba = reinterpret_cast<uintptr_t>(bgrid + lv * S) & ~(uintptr_t)15;
+    MbarArriveExpectTx(&full[slot], (unsigned)dp.pitch + 2u * vbytes);
+    BulkCopyG2S(dst, dense0 + row * dp.pitch, (unsigned)dp.pitch, &full[slot]);
+    BulkCopyG2S(dst + dp.pitch, reinterpret_cast<const void *>(fa), vbytes, &full[slot]);
+    BulkCopyG2S(dst + dp.pitch + sm.vrow, reinterpret_cast<const void *>(ba), vbytes,
                 &full[slot]);
   };
   if (producer)
     for (int32_t step = 1; step < kU; ++step) issue_row(step, step - 1);
 
-  // Viterbi scores of this lane's state for the next kU steps
   const int32_t s_ld = s >= 0 ? s : 0;
   const int64_t first = dir == 0 ? 1 : Tk - 1;  // level of step 1
-  float fq[kU], bq[kU];
-#pragma unroll
-  for (int d = 0; d < kU; ++d) {
-    const bool in = 1 + d <= Tk;
-    fq[d] = in ? fgrid[(first * S + s_ld) + d * step_stride] : -INFINITY;
-    bq[d] = in ? bgrid[(first * S + s_ld) + d * step_stride] : -INFINITY;
-  }
   int64_t pos = first * S + s_ld;  // grid index of this lane's state at step t
   double last = 0.0;
   int32_t K = 0;  // exponent shared by the stored values
   unsigned parity = 0;
-  uint32_t rec_off = (uint32_t)(kU - 1) * dp.pitch;  // ring offset of the previous frame's slot
-  // row of step kU (the producer walks it one row per frame)
-  const unsigned char *src_next = dense0 + (int64_t)(dir == 0 ? kU - 1 : Tk - kU) * dp.pitch;
+  uint32_t rec_off = 0;  // ring offset of the frame's slot
+  // index of the first float of this lane's state in a staged Viterbi row
+  int64_t lv_elem = first * S;  // grid element where the row of step t starts
   bool gave_up = false;
   for (int32_t t0 = 1; t0 <= Tk && !gave_up; t0 += kU) {
 #pragma unroll
@@ -301,14 +308,8 @@ GridChainLanes(const FsaInfo *__restrict__ infos, int32_t n, const Arc *__restri
         break;
       }
       if (producer) {
-        // the slot the previous frame used (offset rec_off) takes the row of step
-        // t + kU - 1
-        if (t + kU - 1 <= Tk) {
-          uint64_t *bar = &full[(u + kU - 1) % kU];
-          MbarArriveExpectTx(bar, (unsigned)dp.pitch);
-          BulkCopyG2S(ring + rec_off, src_next, (unsigned)dp.pitch, bar);
-        }
-        src_next += dir == 0 ? (int64_t)dp.pitch : -(int64_t)dp.pitch;
+        // the slot the previous frame used takes the rows of step t + kU - 1
+        issue_row(t + kU - 1, (u + kU - 1) % kU);
         if (u == 1) emax = kNone;  // read by everyone during the frame before
       }
       double scale = 1.0;
@@ -324,16 +325,18 @@ GridChainLanes(const FsaInfo *__restrict__ infos, int32_t n, const Arc *__restri
       float *co = oth + ((u + 1) & 1) * s_pad;
       // ring slot u, as a running offset (kept opaque so that the unrolled frames
       // do not each pin their own pointers in registers)
-      rec_off = u == 0 ? 0u : rec_off + (uint32_t)dp.pitch;
+      rec_off = u == 0 ? 0u : rec_off + slot_bytes;
       asm volatile("" : "+r"(rec_off));
       const unsigned char *rec = ring + rec_off;
       const float *lprow = PackLp(rec);
       const double *prow = PackP(rec, dp);
-      const float fu = fq[u], bu = bq[u];
-      if (t + kU <= Tk) {
-        fq[u] = fgrid[pos + kU * step_stride];
-        bq[u] = bgrid[pos + kU * step_stride];
-      }
+      // this lane's Viterbi scores: the rows start (address mod 16) / 4 floats into
+      // their staged ranges
+      const int32_t f_skip = (int32_t)((reinterpret_cast<uintptr_t>(fgrid + lv_elem) & 15) >> 2);
+      const int32_t b_skip = (int32_t)((reinterpret_cast<uintptr_t>(bgrid + lv_elem) & 15) >> 2);
+      const float fu = reinterpret_cast<const float *>(rec + dp.pitch)[f_skip + s_ld];
+      const float bu = reinterpret_cast<const float *>(rec + dp.pitch + sm.vrow)[b_skip + s_ld];
+      lv_elem += step_stride;
       const bool keep = s >= 0 && __fadd_rn(fu, bu) > cutoff;
       double sum = 0.0;
       if (__any_sync(0xffffffffu, keep)) {  // most warps of a sparse lattice skip this

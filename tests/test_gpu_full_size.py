@@ -11,7 +11,9 @@ the path are checked instead:
     dense gradient sums to -1 for loss = -sum(tot_scores));
   * the tropical total equals the score of the best path, which has one arc per
     frame plus the final arc; every kept arc lies within the beam of it;
-  * running the path twice gives identical bytes.
+  * running the path twice gives identical bytes;
+  * the lattice-free loss path (`intersect_dense_tot_scores`) gives the same total
+    scores and the same gradient as the lattice path.
 """
 import numpy as np
 import pytest
@@ -111,6 +113,15 @@ def _oracle_parity(k2, w, graphs, log_probs, dense, lat):
         r += d + 1
     err = np.abs(log_probs.grad.cpu().numpy() - expect).max()
     assert err <= 1e-4, err
+    # the lattice-free loss path on the same inputs
+    lp2 = w.log_probs.to(DEV).requires_grad_(True)
+    dense2 = k2.DenseFsaVec(lp2, w.supervision_segments)
+    assert k2.dense_loss_supported(graphs, dense2)
+    tot2 = k2.intersect_dense_tot_scores(graphs, dense2, w.output_beam)
+    assert close(tot2.detach().cpu().numpy(), want["tot_scores"], rtol=1e-6, atol=0)
+    (-tot2.sum()).backward()
+    err2 = np.abs(lp2.grad.cpu().numpy() - expect).max()
+    assert err2 <= 1e-4, err2
     return want
 
 
@@ -150,6 +161,22 @@ def test_full_size_properties(name):
     _, _, _, _, lat2 = _run(w)
     assert torch.equal(lat.arcs.values(), lat2.arcs.values())
     assert torch.equal(lat.arcs.row_splits(2), lat2.arcs.row_splits(2))
+    # lattice-free loss path against the lattice path (log_probs.grad holds the
+    # gradient of -sum(tot) from _check_properties)
+    lp2 = w.log_probs.to(DEV).requires_grad_(True)
+    dense2 = k2.DenseFsaVec(lp2, w.supervision_segments)
+    tot2 = k2.intersect_dense_tot_scores(graphs, dense2, w.output_beam)
+    tot = lat.get_tot_scores(log_semiring=True, use_double_scores=True).detach()
+    assert torch.allclose(tot2.detach(), tot, rtol=1e-6, atol=0)
+    finite = torch.isfinite(tot2)
+    (-tot2[finite].sum()).backward()
+    assert (lp2.grad - log_probs.grad).abs().max().item() <= 1e-4
+    # the dense gradient is summed in fixed point: bit-identical from run to run
+    lp3 = w.log_probs.to(DEV).requires_grad_(True)
+    tot3 = k2.intersect_dense_tot_scores(
+        graphs, k2.DenseFsaVec(lp3, w.supervision_segments), w.output_beam)
+    (-tot3[finite].sum()).backward()
+    assert torch.equal(tot3.detach(), tot2.detach()) and torch.equal(lp3.grad, lp2.grad)
 
 
 def test_hlg_decode_full_size_properties():
