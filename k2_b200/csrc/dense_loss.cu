@@ -1145,7 +1145,7 @@ int32_t k2b200_dense_loss_forward(const k2b200_intersect_args *args, void *works
   for (const FsaInfo &f : L.infos) arc_frames += (long long)f.tk * f.num_arcs;
   if (L.grid_elems > args->max_states || arc_frames > args->max_arcs) {
     long long h_totals[5];
-    K2B_FORWARD(PruneLoop(L, args, ws, stream, &beam, h_totals));
+    K2B_FORWARD(PruneLoop(L, args, ws, stream, &beam, h_totals, /*sizes_only=*/true));
   } else {
     K2B_FORWARD(LaunchCutoffs(L, args, ws, beam, stream));
   }

@@ -540,6 +540,40 @@ int32_t RunViterbi(const Layout &L, const k2b200_intersect_args *a, char *ws, cu
 }
 
 
+// Sizes only, for callers that never build the lattice: the number of surviving
+// (frame, state) pairs and of arcs leaving them (the two totals the beam reduction
+// looks at), added into totals[0] and totals[2].  grid = (tiles, pairs).
+__global__ void __launch_bounds__(256)
+CountStates(const FsaInfo *__restrict__ infos, const int32_t *__restrict__ a_row_splits2,
+            const float *__restrict__ fwd, const float *__restrict__ bwd,
+            const float *__restrict__ cutoffs, unsigned long long *__restrict__ totals,
+            int32_t fsa_base) {
+  const int32_t i = blockIdx.y + fsa_base;
+  const FsaInfo f = infos[i];
+  const int64_t elems = (int64_t)(f.tk + 1) * f.num_states;
+  const float cutoff = cutoffs[i];
+  const float *fg = fwd + f.grid_off, *bg = bwd + f.grid_off;
+  const int32_t *splits = a_row_splits2 + f.state_off;
+  uint32_t states = 0, cand = 0;
+  for (int64_t k = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; k < elems;
+       k += (int64_t)gridDim.x * blockDim.x) {
+    if (__fadd_rn(fg[k], bg[k]) > cutoff) {
+      const int32_t s = (int32_t)(k % f.num_states);
+      ++states;
+      cand += splits[s + 1] - splits[s];
+    }
+  }
+#pragma unroll
+  for (int d = 16; d > 0; d >>= 1) {
+    states += __shfl_xor_sync(0xffffffffu, states, d);
+    cand += __shfl_xor_sync(0xffffffffu, cand, d);
+  }
+  if ((threadIdx.x & 31) == 0 && (states | cand)) {
+    atomicAdd(&totals[0], (unsigned long long)states);
+    atomicAdd(&totals[2], (unsigned long long)cand);
+  }
+}
+
 int32_t LaunchCutoffs(const Layout &L, const k2b200_intersect_args *a, char *ws, float beam,
                       cudaStream_t stream) {
   { Cutoffs<<<CeilDiv(a->num_fsas, 128), 128, 0, stream>>>(
@@ -556,7 +590,7 @@ int32_t LaunchCutoffs(const Layout &L, const k2b200_intersect_args *a, char *ws,
 // max_states / max_arcs.  One host synchronisation per iteration.  h_totals:
 // states, arcs, candidate arcs, largest layer in states and in arcs.
 int32_t PruneLoop(const Layout &L, const k2b200_intersect_args *args, char *ws,
-                  cudaStream_t stream, float *beam_io, long long *h_totals) {
+                  cudaStream_t stream, float *beam_io, long long *h_totals, bool sizes_only) {
   const FsaInfo *d_infos = reinterpret_cast<const FsaInfo *>(ws + L.off_infos);
   float *cutoffs = reinterpret_cast<float *>(ws + L.off_cutoffs);
   float *fwd = reinterpret_cast<float *>(ws + L.off_fwd),
@@ -573,19 +607,32 @@ int32_t PruneLoop(const Layout &L, const k2b200_intersect_args *args, char *ws,
   for (int iter = 0;; ++iter) {
     { Cutoffs<<<CeilDiv(args->num_fsas, 128), 128, 0, stream>>>(d_infos, args->num_fsas, fwd, bwd,
                                                               beam, cutoffs); NoteLaunch(); }
-    if (L.total_words > 0)
-      for (int32_t first = 0; first < args->num_fsas; first += 65535) {
-        dim3 grid(L.tiles_per_pair, std::min(args->num_fsas - first, 65535));
-        { CountKept<<<grid, kCountThreads, 0, stream>>>(
-            d_infos, args->num_fsas, L.total_words, arcs, args->a_row_splits2, args->scores,
-            args->cols, fwd, bwd, cutoffs, mask, counts, block_cand, first); NoteLaunch(); }
-      }
-    K2B_FORWARD(ExclusiveSum2(counts, counts, L.total_words, scan_tmp, stream));
-    { Totals<<<1, 1024, 0, stream>>>(counts, L.total_words, block_cand,
-                                  L.total_words > 0 ? L.count_blocks : 0, totals); NoteLaunch(); }
-    if (L.total_words > 0)
-      { LayerMaxima<<<CeilDiv(L.total_levels, 256), 256, 0, stream>>>(
-          d_infos, args->num_fsas, (int32_t)L.total_levels, counts, totals); NoteLaunch(); }
+    if (sizes_only) {
+      K2B_CUDA_OK(cudaMemsetAsync(totals, 0, 5 * sizeof(long long), stream));
+      if (L.grid_elems > 0)
+        for (int32_t first = 0; first < args->num_fsas; first += 65535) {
+          int64_t max_elems = (int64_t)(L.max_tk + 1) * L.max_states;
+          dim3 grid((unsigned)std::min<int64_t>(CeilDiv(max_elems, 256 * 8), 1024),
+                    std::min(args->num_fsas - first, 65535));
+          { CountStates<<<grid, 256, 0, stream>>>(
+              d_infos, args->a_row_splits2, fwd, bwd, cutoffs,
+              reinterpret_cast<unsigned long long *>(totals), first); NoteLaunch(); }
+        }
+    } else {
+      if (L.total_words > 0)
+        for (int32_t first = 0; first < args->num_fsas; first += 65535) {
+          dim3 grid(L.tiles_per_pair, std::min(args->num_fsas - first, 65535));
+          { CountKept<<<grid, kCountThreads, 0, stream>>>(
+              d_infos, args->num_fsas, L.total_words, arcs, args->a_row_splits2, args->scores,
+              args->cols, fwd, bwd, cutoffs, mask, counts, block_cand, first); NoteLaunch(); }
+        }
+      K2B_FORWARD(ExclusiveSum2(counts, counts, L.total_words, scan_tmp, stream));
+      { Totals<<<1, 1024, 0, stream>>>(counts, L.total_words, block_cand,
+                                    L.total_words > 0 ? L.count_blocks : 0, totals); NoteLaunch(); }
+      if (L.total_words > 0)
+        { LayerMaxima<<<CeilDiv(L.total_levels, 256), 256, 0, stream>>>(
+            d_infos, args->num_fsas, (int32_t)L.total_levels, counts, totals); NoteLaunch(); }
+    }
     K2B_CUDA_OK(cudaGetLastError());
     K2B_CUDA_OK(cudaMemcpyAsync(h_totals, totals, 5 * sizeof(long long), cudaMemcpyDeviceToHost,
                                 stream));

@@ -38,8 +38,11 @@ struct Layout {
 int32_t MakeLayout(const k2b200_intersect_args *a, Layout *L);
 int32_t RunViterbi(const Layout &L, const k2b200_intersect_args *a, char *ws,
                    cudaStream_t stream, bool plan_ready = false);
+// sizes_only: just the totals the beam reduction needs (states and candidate arcs),
+// no keep masks or numbering.
 int32_t PruneLoop(const Layout &L, const k2b200_intersect_args *args, char *ws,
-                  cudaStream_t stream, float *beam_io, long long *h_totals);
+                  cudaStream_t stream, float *beam_io, long long *h_totals,
+                  bool sizes_only = false);
 // cutoffs[i] = min(best forward, best backward total) - beam, from the Viterbi grids
 int32_t LaunchCutoffs(const Layout &L, const k2b200_intersect_args *a, char *ws, float beam,
                       cudaStream_t stream);

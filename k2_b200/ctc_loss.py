@@ -13,6 +13,10 @@ from .fsa import Fsa
 # are computed without building it when the graphs allow; set to False to force
 # the reference's intersect_dense + get_tot_scores sequence.
 FUSED_LOSS = True
+# The lattice-free path exponentiates every element of the dense matrix and streams
+# whole rows through shared memory; with very many classes, of which a graph uses
+# few, building the (small) lattice is cheaper.
+FUSED_MAX_CLASSES = 2048
 
 
 class CtcLoss(nn.Module):
@@ -31,6 +35,7 @@ class CtcLoss(nn.Module):
                 delay_penalty: float = 0.0,
                 target_lengths: Optional[torch.Tensor] = None) -> torch.Tensor:
         if (FUSED_LOSS and delay_penalty <= 0.0
+                and dense_fsa_vec.scores.shape[1] <= FUSED_MAX_CLASSES
                 and dense_loss_supported(decoding_graph, dense_fsa_vec)):
             tot_scores = intersect_dense_tot_scores(
                 decoding_graph, dense_fsa_vec, self.output_beam,
