@@ -377,21 +377,21 @@ def run_ours(args):
         "scores": 16 * A_out + 16 * S_out,
         "prune": grid_bytes,
         "emit": grid_bytes + 24 * A_out + 8 * S_out,
-        "dense": 8 * frames * C + 4 * N * T * C,
+        # DenseFill + DenseBackward, and the repacking with exp() for the lattice-free loss
+        "dense": 8 * frames * C + 4 * N * T * C + 16 * frames * C,
         "post": 40 * A_out,
         "incoming": 24 * A_out,
-        # lattice-free loss: exp of the rows (read 4, write 12 bytes per element), both
-        # recursions read the packed rows and the two Viterbi grids and write one
-        # 16-byte value per surviving state
-        "chain": 16 * frames * C + 2 * 12 * frames * C + 2 * grid_bytes + 32 * S_out,
+        # lattice-free loss: both recursions read the packed rows (12 bytes per element)
+        # and the two Viterbi grids and write one 16-byte value per surviving state
+        "chain": 2 * 12 * frames * C + 2 * grid_bytes + 32 * S_out,
         # gradients: grids, surviving alpha/beta, packed rows, one write per dense element
         # that a surviving arc touches
         "grad": grid_bytes + 32 * S_out + 12 * frames * C + 4 * A_out,
     }
     phase_kernel = {"viterbi": "RegisterViterbi", "scores": "ProbScoresStaged",
-                    "prune": "CountKept", "emit": "EmitLattice", "dense": "DenseFill+DenseBackward",
+                    "prune": "CountStates|CountKept", "emit": "EmitLattice", "dense": "DenseFill+DenseBackward+ExpDense",
                     "post": "ArcPost+LogBackward+IndexAdd", "incoming": "BuildIncoming",
-                    "chain": "ExpDense+GridChainLanes", "grad": "GridGradWarp"}
+                    "chain": "GridChainLanes", "grad": "GridGradWarp/GridGradLanes"}
     peaks = {}
     try:
         with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:

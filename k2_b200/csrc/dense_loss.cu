@@ -492,13 +492,22 @@ GridGradWarp(const FsaInfo *__restrict__ infos, const Arc *__restrict__ arcs,
     const float *lprow = PackLp(rec);
     const double *prow = PackP(rec, dp);
     uint32_t *gbrow = gb + (size_t)(u - u0) * cols;
-    for (int32_t c0 = 0; c0 < S; c0 += 32) {
-      const int32_t q = c0 + lane;
-      float fu = -INFINITY, bu = -INFINITY;
-      if (q < S) {
-        fu = fgrid[cur + q];
-        bu = bgrid[cur + q];
+    // four words of 32 states at a time, so that their loads overlap (most words
+    // of a sparse lattice hold no survivor)
+    for (int32_t cc = 0; cc < S; cc += 128) {
+      float fu4[4], bu4[4];
+#pragma unroll
+      for (int w4 = 0; w4 < 4; ++w4) {
+        const int32_t q = cc + 32 * w4 + lane;
+        fu4[w4] = q < S ? fgrid[cur + q] : -INFINITY;
+        bu4[w4] = q < S ? bgrid[cur + q] : -INFINITY;
       }
+#pragma unroll
+    for (int w4 = 0; w4 < 4; ++w4) {
+      const int32_t c0 = cc + 32 * w4;
+      if (c0 >= S) break;
+      const int32_t q = c0 + lane;
+      const float fu = fu4[w4], bu = bu4[w4];
       ProbState a;
       a.m = 0.0;
       a.e = kZeroExp;
@@ -546,6 +555,7 @@ GridGradWarp(const FsaInfo *__restrict__ infos, const Arc *__restrict__ arcs,
           else atomicAdd(&grad_a[f.arc_off + k], tg * post);
         }
       }
+    }
     }
   }
   __syncthreads();
@@ -1127,7 +1137,7 @@ int32_t k2b200_dense_loss_forward(const k2b200_intersect_args *args, void *works
   unsigned char *dense = reinterpret_cast<unsigned char *>(ws + LL.off_dense);
   int32_t *unfit = reinterpret_cast<int32_t *>(ws + L.off_unfit);
   {
-    PhaseTimer timer(kPhaseChain, stream);
+    PhaseTimer timer(kPhaseDense, stream);  // repacking belongs with the dense matrix
     const int64_t n_dense = (int64_t)args->rows * LL.pack.cols4;
     { ExpDense<<<(int)std::min<int64_t>(CeilDiv(n_dense, 256), 148 * 32), 256, 0, stream>>>(
         args->scores, args->rows, LL.pack, dense); NoteLaunch(); }

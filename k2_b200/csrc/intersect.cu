@@ -555,22 +555,37 @@ CountStates(const FsaInfo *__restrict__ infos, const int32_t *__restrict__ a_row
   const float *fg = fwd + f.grid_off, *bg = bwd + f.grid_off;
   const int32_t *splits = a_row_splits2 + f.state_off;
   uint32_t states = 0, cand = 0;
-  for (int64_t k = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; k < elems;
-       k += (int64_t)gridDim.x * blockDim.x) {
+  // state of element k, kept up to date without a division per element
+  const int32_t S = f.num_states;
+  const int64_t k0 = (int64_t)blockIdx.x * blockDim.x + threadIdx.x,
+                stride = (int64_t)gridDim.x * blockDim.x;
+  int32_t s = S > 0 ? (int32_t)(k0 % S) : 0;
+  const int32_t s_step = S > 0 ? (int32_t)(stride % S) : 0;
+  for (int64_t k = k0; k < elems; k += stride) {
     if (__fadd_rn(fg[k], bg[k]) > cutoff) {
-      const int32_t s = (int32_t)(k % f.num_states);
       ++states;
       cand += splits[s + 1] - splits[s];
     }
+    s += s_step;
+    if (s >= S) s -= S;
   }
 #pragma unroll
   for (int d = 16; d > 0; d >>= 1) {
     states += __shfl_xor_sync(0xffffffffu, states, d);
     cand += __shfl_xor_sync(0xffffffffu, cand, d);
   }
+  // one pair of atomics per CTA: all of them hit the same two words
+  __shared__ uint32_t cta_states, cta_cand;
+  if (threadIdx.x == 0) cta_states = cta_cand = 0;
+  __syncthreads();
   if ((threadIdx.x & 31) == 0 && (states | cand)) {
-    atomicAdd(&totals[0], (unsigned long long)states);
-    atomicAdd(&totals[2], (unsigned long long)cand);
+    atomicAdd(&cta_states, states);
+    atomicAdd(&cta_cand, cand);
+  }
+  __syncthreads();
+  if (threadIdx.x == 0 && (cta_states | cta_cand)) {
+    atomicAdd(&totals[0], (unsigned long long)cta_states);
+    atomicAdd(&totals[2], (unsigned long long)cta_cand);
   }
 }
 
@@ -612,7 +627,7 @@ int32_t PruneLoop(const Layout &L, const k2b200_intersect_args *args, char *ws,
       if (L.grid_elems > 0)
         for (int32_t first = 0; first < args->num_fsas; first += 65535) {
           int64_t max_elems = (int64_t)(L.max_tk + 1) * L.max_states;
-          dim3 grid((unsigned)std::min<int64_t>(CeilDiv(max_elems, 256 * 8), 1024),
+          dim3 grid((unsigned)std::min<int64_t>(CeilDiv(max_elems, 256 * 16), 64),
                     std::min(args->num_fsas - first, 65535));
           { CountStates<<<grid, 256, 0, stream>>>(
               d_infos, args->a_row_splits2, fwd, bwd, cutoffs,
