@@ -405,6 +405,316 @@ GridChainLanes(const FsaInfo *__restrict__ infos, int32_t n, const Arc *__restri
 }
 
 // ---------------------------------------------------------------------------
+// Arc survival masks for planned graphs.  The pruning test of a (frame, arc) pair
+// is needed three times - by the forward recursion (arcs grouped by destination),
+// by the backward recursion and by the gradients (arcs grouped by source).  The
+// recursions are chains of dependent frames, where every instruction counts; the
+// tests have no such dependency.  So they run here, for all frames at once:
+//   masks[(dir * total_levels + level_off(i) + r) * kLaneThreads + lane], bit j =
+//   slot j of that lane survives at row r
+// with r the step t = 1..T of the forward recursion (dir 0) or the level u = 0..T-1
+// the arc leaves from (dir 1).  grid = (row chunks, pairs, 2 directions); the CTA
+// stages the Viterbi scores of its levels (-inf for pruned states) and the dense
+// scores of its rows in shared memory.  Also enforces kMinDenseScore.
+// ---------------------------------------------------------------------------
+constexpr int kMaskRows = 32;  // rows per CTA
+
+template <int kDeg>
+__global__ void __launch_bounds__(kLaneThreads)
+ArcMasks(const FsaInfo *__restrict__ infos, int32_t n, int64_t total_levels,
+         const Arc *__restrict__ arcs, const int32_t *__restrict__ a_row_splits2,
+         const int32_t *__restrict__ in_splits, const int32_t *__restrict__ in_arcs,
+         const unsigned char *__restrict__ dense, DensePack dp,
+         const float *__restrict__ vfwd, const float *__restrict__ vbwd,
+         const float *__restrict__ cutoffs, const int32_t *__restrict__ plan,
+         int32_t *__restrict__ unfit, unsigned char *__restrict__ masks, int32_t s_pad) {
+  static_assert(kDeg <= 8, "one byte per lane");
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  const int32_t i = blockIdx.y, dir = blockIdx.z;
+  if (unfit[i] & 1) return;
+  const FsaInfo f = infos[i];
+  const int32_t S = f.num_states, Tk = f.tk, cols = dp.cols;
+  const int32_t r0 = blockIdx.x * kMaskRows + (dir == 0 ? 1 : 0);
+  const int32_t r_end = dir == 0 ? Tk + 1 : Tk;
+  if (S == 0 || r0 >= r_end) return;
+  const int32_t nf = min(kMaskRows, r_end - r0);
+  const int32_t lb = dir == 0 ? r0 - 1 : r0;  // first staged level and first dense row
+  const int tid = threadIdx.x, nt = blockDim.x;
+  float *fo = reinterpret_cast<float *>(smem_raw);  // [kMaskRows + 1][s_pad]
+  float *bo = fo + (kMaskRows + 1) * s_pad;         // [kMaskRows + 1][s_pad]
+  float *lp = bo + (kMaskRows + 1) * s_pad;         // [kMaskRows][cols4]
+  const float cutoff = cutoffs[i];
+  const float *fgrid = vfwd + f.grid_off, *bgrid = vbwd + f.grid_off;
+  for (int32_t idx = tid; idx < (nf + 1) * S; idx += nt) {
+    const int32_t l = idx / S, q = idx - l * S;
+    const int64_t gi = (int64_t)(lb + l) * S + q;
+    const float fu = fgrid[gi], bu = bgrid[gi];
+    const bool keep = __fadd_rn(fu, bu) > cutoff;
+    fo[l * s_pad + q] = keep ? fu : -INFINITY;
+    bo[l * s_pad + q] = keep ? bu : -INFINITY;
+  }
+  for (int32_t idx = tid; idx < nf * dp.cols4; idx += nt) {
+    const int32_t l = idx / dp.cols4, c = idx - l * dp.cols4;
+    lp[idx] = PackLp(dense + ((int64_t)f.row0 + lb + l) * dp.pitch)[c];
+  }
+  int32_t s = -1, g = 0, G = 1;
+  {
+    const int32_t code = plan[((int64_t)dir * n + i) * kLaneThreads + tid];
+    if (code >= 0) {
+      s = code & 0xffff;
+      g = (code >> 16) & 0xff;
+      G = code >> 24;
+    }
+  }
+  int32_t other_col[kDeg];
+  float w[kDeg];
+#pragma unroll
+  for (int j = 0; j < kDeg; ++j) {
+    other_col[j] = cols << 16;
+    w[j] = -INFINITY;
+  }
+  if (s >= 0) {
+    const int32_t *gsplits = dir == 0 ? in_splits : a_row_splits2;
+    const int32_t a0 = gsplits[f.state_off + s], a1 = gsplits[f.state_off + s + 1];
+#pragma unroll
+    for (int j = 0; j < kDeg; ++j) {
+      const int32_t k = a0 + g + j * G;
+      if (k < a1) {
+        const Arc arc = arcs[dir == 0 ? in_arcs[k] : k];
+        const int32_t c = arc.label + 1;
+        if (c >= 0 && c < cols && arc.score != -INFINITY) {
+          other_col[j] = (dir == 0 ? arc.src : arc.dest) | (c << 16);
+          w[j] = arc.score;
+        }
+      }
+    }
+  }
+  __syncthreads();
+  bool risky = false;
+  unsigned char *out = masks + ((int64_t)dir * total_levels + f.level_off + r0) * kLaneThreads;
+  for (int32_t k = 0; k < nf; ++k) {
+    uint32_t bits = 0;
+    if (s >= 0) {
+      // dir 0: arcs from level k into level k + 1 (own); dir 1: from level k (own) to k + 1
+      const float own = dir == 0 ? bo[(k + 1) * s_pad + s] : fo[k * s_pad + s];
+      if (own != -INFINITY) {
+        const float *oth = dir == 0 ? fo + k * s_pad : bo + (k + 1) * s_pad;
+        const float *lprow = lp + k * dp.cols4;
+#pragma unroll
+        for (int j = 0; j < kDeg; ++j) {
+          const int32_t o_idx = other_col[j] & 0xffff, c = other_col[j] >> 16;
+          const float l = lprow[c];
+          const float sc = __fadd_rn(w[j], l);
+          const float o = oth[o_idx];
+          const float through = dir == 0 ? __fadd_rn(__fadd_rn(o, sc), own)
+                                         : __fadd_rn(__fadd_rn(own, sc), o);
+          if (through > cutoff) {
+            bits |= 1u << j;
+            risky |= l < kMinDenseScore;
+          }
+        }
+      }
+    }
+    out[(int64_t)k * kLaneThreads + tid] = (unsigned char)bits;
+  }
+  if (__syncthreads_or(risky) && tid == 0) atomicOr(&unfit[i], 2);
+}
+
+// ---------------------------------------------------------------------------
+// The alpha / beta recursion for planned graphs, driven by the masks of ArcMasks:
+// same arithmetic and ring as GridChainLanes, but a frame needs no Viterbi score and
+// no test - one mask byte per lane says which of its arcs to add.  A ring slot holds
+// the exp() part of the packed dense row and the frame's row of mask bytes.  Every
+// state is written to the grid (0 for pruned ones).
+// ---------------------------------------------------------------------------
+template <int kDeg, int kU>
+__global__ void __launch_bounds__(kLaneThreads)
+GridChainMasked(const FsaInfo *__restrict__ infos, int32_t n, int64_t total_levels,
+                const Arc *__restrict__ arcs, const int32_t *__restrict__ a_row_splits2,
+                const int32_t *__restrict__ in_splits, const int32_t *__restrict__ in_arcs,
+                const unsigned char *__restrict__ dense, DensePack dp,
+                const unsigned char *__restrict__ masks, const float *__restrict__ vfwd,
+                const float *__restrict__ vbwd, const float *__restrict__ cutoffs,
+                ProbState *__restrict__ alpha, ProbState *__restrict__ beta,
+                double *__restrict__ tot, const int32_t *__restrict__ plan,
+                int32_t *__restrict__ unfit, int32_t s_pad) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  __shared__ __align__(8) uint64_t full[kU];
+  __shared__ int32_t emax;
+  constexpr int32_t kNone = INT32_MIN;
+  const int32_t i = blockIdx.y;
+  const int dir = blockIdx.x;
+  if (unfit[i]) return;  // no plan, or outside the limits: the fallback kernel takes it
+  const FsaInfo f = infos[i];
+  const int32_t S = f.num_states, Tk = f.tk, cols = dp.cols;
+  const int tid = threadIdx.x, nt = blockDim.x;
+  if (S == 0) {
+    if (dir == 0 && tid == 0) tot[i] = -INFINITY;
+    return;
+  }
+  const uint32_t p_bytes = 8u * (uint32_t)dp.cols2;
+  const uint32_t slot_bytes = p_bytes + (uint32_t)kLaneThreads;
+  unsigned char *ring = smem_raw;                                            // [kU][slot_bytes]
+  double *pv = reinterpret_cast<double *>(ring + (size_t)kU * slot_bytes);   // [2][s_pad]
+  int32_t s = -1, g = 0, G = 1;
+  {
+    const int32_t code = plan[((int64_t)dir * n + i) * kLaneThreads + tid];
+    if (code >= 0) {
+      s = code & 0xffff;
+      g = (code >> 16) & 0xff;
+      G = code >> 24;
+    }
+  }
+  int32_t other_col[kDeg];
+  double ew[kDeg];
+  bool risky = false;
+#pragma unroll
+  for (int j = 0; j < kDeg; ++j) {
+    other_col[j] = cols << 16;
+    ew[j] = 0.0;
+  }
+  if (s >= 0) {
+    const int32_t *gsplits = dir == 0 ? in_splits : a_row_splits2;
+    const int32_t a0 = gsplits[f.state_off + s], a1 = gsplits[f.state_off + s + 1];
+#pragma unroll
+    for (int j = 0; j < kDeg; ++j) {
+      const int32_t k = a0 + g + j * G;
+      if (k < a1) {
+        const Arc arc = arcs[dir == 0 ? in_arcs[k] : k];
+        const int32_t c = arc.label + 1;
+        if (c >= 0 && c < cols && arc.score != -INFINITY) {
+          other_col[j] = (dir == 0 ? arc.src : arc.dest) | (c << 16);
+          ew[j] = exp((double)arc.score);
+          if (!(fabsf(arc.score) <= kMaxAbsArcScore)) risky = true;
+        }
+      }
+    }
+  }
+  if (tid == 0) {
+    for (int st = 0; st < kU; ++st) MbarInit(&full[st], 1);
+    emax = kNone;
+    MbarInitFence();
+  }
+  if (__syncthreads_or(risky)) {
+    if (tid == 0) atomicOr(&unfit[i], 2);
+    return;
+  }
+  ProbState *out = (dir == 0 ? alpha : beta) + f.grid_off;
+  {  // first level: 1 for the start (final) state if it survives, 0 elsewhere
+    const int64_t lv = dir == 0 ? 0 : Tk;
+    const int32_t q1 = dir == 0 ? 0 : S - 1;
+    const bool one_ok = __fadd_rn(vfwd[f.grid_off + lv * S + q1], vbwd[f.grid_off + lv * S + q1]) >
+                        cutoffs[i];
+    for (int32_t q = tid; q < S; q += nt) {
+      ProbState v;
+      v.m = (q == q1 && one_ok) ? 1.0 : 0.0;
+      v.e = 0;
+      v.pad = 0;
+      pv[q] = v.m;
+      out[lv * S + q] = v;
+    }
+    if (tid == 0 && one_ok) emax = 0;
+  }
+  __syncthreads();
+  const int64_t step_stride = dir == 0 ? (int64_t)S : -(int64_t)S;
+  const unsigned char *dense_p = dense + (int64_t)f.row0 * dp.pitch + 4 * dp.cols4;
+  const unsigned char *mask0 = masks + ((int64_t)dir * total_levels + f.level_off) * kLaneThreads;
+  auto issue_row = [&](int32_t step, int32_t slot) {  // thread 0 only
+    if (step > Tk) return;
+    const int64_t row = dir == 0 ? step - 1 : Tk - step;  // dense row
+    const int64_t r = dir == 0 ? step : Tk - step;        // mask row
+    unsigned char *dst = ring + (size_t)slot * slot_bytes;
+    MbarArriveExpectTx(&full[slot], p_bytes + (unsigned)kLaneThreads);
+    BulkCopyG2S(dst, dense_p + row * dp.pitch, p_bytes, &full[slot]);
+    BulkCopyG2S(dst + p_bytes, mask0 + r * kLaneThreads, (unsigned)kLaneThreads, &full[slot]);
+  };
+  if (tid == 0)
+    for (int32_t step = 1; step < kU; ++step) issue_row(step, step - 1);
+  const int32_t s_ld = s >= 0 ? s : 0;
+  int64_t pos = (dir == 0 ? 1 : Tk - 1) * (int64_t)S + s_ld;
+  double last = 0.0;
+  int32_t K = 0;
+  unsigned parity = 0;
+  uint32_t rec_off = 0;
+  bool gave_up = false;
+  for (int32_t t0 = 1; t0 <= Tk && !gave_up; t0 += kU) {
+#pragma unroll
+    for (int u = 0; u < kU; ++u) {
+      const int32_t t = t0 + u;
+      if (t > Tk) break;
+      const bool late = !MbarTryWait(&full[u], parity) && !MbarWaitBounded(&full[u], parity);
+      if (__syncthreads_or(late)) {  // uniform
+        gave_up = true;
+        break;
+      }
+      if (tid == 0) {
+        issue_row(t + kU - 1, (u + kU - 1) % kU);
+        if (u == 1) emax = kNone;
+      }
+      double scale = 1.0;
+      if (u == 0) {
+        const int32_t e_prev = emax;
+        const int32_t shift = e_prev == kNone ? 0 : e_prev;
+        K += shift;
+        scale = __longlong_as_double((long long)(1023 - shift) << 52);
+      }
+      const double *prev = pv + (u & 1) * s_pad;
+      double *cur = pv + ((u + 1) & 1) * s_pad;
+      rec_off = u == 0 ? 0u : rec_off + slot_bytes;
+      asm volatile("" : "+r"(rec_off));
+      const double *prow = reinterpret_cast<const double *>(ring + rec_off);
+      const uint32_t m = (ring + rec_off + p_bytes)[tid];
+      double sum = 0.0;
+      if (__any_sync(0xffffffffu, m != 0)) {
+#pragma unroll
+        for (int j = 0; j < kDeg; ++j)
+          if (m & (1u << j))
+            sum += prev[other_col[j] & 0xffff] * ew[j] * prow[other_col[j] >> 16];
+#pragma unroll
+        for (int32_t d = 16; d > 0; d >>= 1) {
+          const double so = __shfl_down_sync(0xffffffffu, sum, d);
+          if (g + d < G) sum += so;
+        }
+      }
+      const double v = u == 0 ? sum * scale : sum;
+      const int32_t vhi = __double2hiint(v);
+      if (s >= 0 && g == 0) {
+        cur[s] = v;
+        ProbState r;
+        r.m = v;
+        r.e = K;
+        r.pad = 0;
+        out[pos] = r;
+        last = v;
+        risky |= v != 0.0 && vhi < ((1023 + kMinExponent) << 20);
+      }
+      pos += step_stride;
+      if (u == kU - 1) {
+        int32_t ex = (s >= 0 && g == 0 && v != 0.0) ? (vhi >> 20) - 1023 : kNone;
+        ex = __reduce_max_sync(0xffffffffu, ex);
+        if ((tid & 31) == 0 && ex != kNone) atomicMax(&emax, ex);
+      }
+    }
+    parity ^= 1u;
+  }
+  const int32_t any_risky = __syncthreads_or(risky);
+  if (gave_up) {
+    if (tid == 0) {
+      atomicOr(&unfit[i], 2);
+      for (int k = 0; k < 1000; ++k) __nanosleep(1000);  // copies still in flight
+    }
+    __syncthreads();
+    return;
+  }
+  if (any_risky) {
+    if (tid == 0) atomicOr(&unfit[i], 2);
+    return;
+  }
+  if (dir == 0 && s == S - 1 && g == 0)
+    tot[i] = last == 0.0 ? -INFINITY : log(last) + (double)K * 0.69314718055994530942;
+}
+
+// ---------------------------------------------------------------------------
 // Gradients.  grid = (frame chunks, pairs): frames do not depend on one another,
 // so the GPU is filled with (pair, chunk) CTAs and every warp of a CTA takes whole
 // frames.  For its frame u the warp scans the states 32 at a time, keeps the
@@ -587,8 +897,8 @@ template <int kDeg>
 __global__ void __launch_bounds__(kLaneThreads)
 GridGradLanes(const FsaInfo *__restrict__ infos, int32_t n, const Arc *__restrict__ arcs,
               const int32_t *__restrict__ a_row_splits2, const unsigned char *__restrict__ dense,
-              DensePack dp, const float *__restrict__ vfwd, const float *__restrict__ vbwd,
-              const float *__restrict__ cutoffs, const ProbState *__restrict__ alpha,
+              DensePack dp, const unsigned char *__restrict__ masks, int64_t total_levels,
+              const ProbState *__restrict__ alpha,
               const ProbState *__restrict__ beta, const double *__restrict__ tot_grad,
               int32_t tot_grad_stride, float *__restrict__ grad_a, float *__restrict__ grad_b,
               const int32_t *__restrict__ plan, const int32_t *__restrict__ unfit,
@@ -611,13 +921,12 @@ GridGradLanes(const FsaInfo *__restrict__ infos, int32_t n, const Arc *__restric
   double *st_bm = st_am + lv_elems;
   int32_t *st_ae = reinterpret_cast<int32_t *>(st_bm + lv_elems);
   int32_t *st_be = st_ae + lv_elems;
-  float *st_fo = reinterpret_cast<float *>(st_be + lv_elems);
-  float *st_bo = st_fo + lv_elems;
-  unsigned char *rows = reinterpret_cast<unsigned char *>(st_bo + lv_elems);
+  unsigned char *rows = reinterpret_cast<unsigned char *>(st_be + lv_elems);
   // posteriors per (frame, column) in fixed point, 2^-31 units: integer atomics are
   // native in shared memory (float ones are compare-and-swap loops) and make the sum
   // independent of the order of the additions
-  uint32_t *gb = reinterpret_cast<uint32_t *>(rows + (size_t)sub_frames * dp.pitch);
+  unsigned char *mk = rows + (size_t)sub_frames * dp.pitch;  // [sub_frames][kLaneThreads]
+  uint32_t *gb = reinterpret_cast<uint32_t *>(mk + (size_t)sub_frames * kLaneThreads);
   const ProbState *al = alpha + f.grid_off, *be = beta + f.grid_off;
   const ProbState z = al[(int64_t)Tk * S + (S - 1)];
   if (z.m == 0.0) return;  // no path survives: all gradients are zero
@@ -626,8 +935,8 @@ GridGradLanes(const FsaInfo *__restrict__ infos, int32_t n, const Arc *__restric
   const double zinv = 1.0 / zm;
   const float tg = (float)tot_grad[(int64_t)i * tot_grad_stride];
   const int32_t zk = -(z.e + zex);
-  const float cutoff = cutoffs[i];
-  const float *fgrid = vfwd + f.grid_off, *bgrid = vbwd + f.grid_off;
+  // survival bits of the lanes' arcs, one row of bytes per level (ArcMasks, direction 1)
+  const unsigned char *mask0 = masks + (total_levels + f.level_off) * (int64_t)kLaneThreads;
   // ---- this lane's arcs --------------------------------------------------------
   int32_t s = -1, g = 0, G = 1;
   {
@@ -678,25 +987,18 @@ GridGradLanes(const FsaInfo *__restrict__ infos, int32_t n, const Arc *__restric
     for (int32_t idx = tid; idx < (nf + 1) * S; idx += nt) {
       const int32_t l = idx / S, q = idx - l * S;
       const int64_t gi = (int64_t)(u0 + l) * S + q;
-      const float fu = fgrid[gi], bu = bgrid[gi];
-      double am = 0.0, bm = 0.0;
-      int32_t ae = 0, bexp = 0;
-      const bool keep = __fadd_rn(fu, bu) > cutoff;
-      if (keep) {
-        const ProbState a = al[gi], b = be[gi];
-        int32_t ex;
-        am = SplitExp(a.m, &ex) * zinv;
-        ae = a.m == 0.0 ? 0 : a.e + ex + zk;
-        bm = SplitExp(b.m, &ex);
-        bexp = b.m == 0.0 ? 0 : b.e + ex;
-      }
+      // the recursions wrote every state (0 for pruned or unreachable ones)
+      const ProbState a = al[gi], b = be[gi];
+      int32_t ex;
+      const double am = SplitExp(a.m, &ex) * zinv;
+      const int32_t ae = a.m == 0.0 ? 0 : a.e + ex + zk;
+      const double bm = SplitExp(b.m, &ex);
+      const int32_t bexp = b.m == 0.0 ? 0 : b.e + ex;
       const int32_t k = l * s_pad + q;
       st_am[k] = am;
       st_bm[k] = bm;
       st_ae[k] = ae;
       st_be[k] = bexp;
-      st_fo[k] = keep ? fu : -INFINITY;
-      st_bo[k] = keep ? bu : -INFINITY;
     }
     {
       const int32_t chunks = dp.pitch / 16;
@@ -705,16 +1007,21 @@ GridGradLanes(const FsaInfo *__restrict__ infos, int32_t n, const Arc *__restric
       for (int32_t k = tid; k < nf * chunks; k += nt) dst[k] = src[k];
     }
     for (int32_t k = tid; k < nf * cols; k += nt) gb[k] = 0u;
+    {
+      const uint4 *src = reinterpret_cast<const uint4 *>(mask0 + (int64_t)u0 * kLaneThreads);
+      uint4 *dst = reinterpret_cast<uint4 *>(mk);
+      for (int32_t k = tid; k < nf * (kLaneThreads / 16); k += nt) dst[k] = src[k];
+    }
     __syncthreads();
     if (s >= 0) {
       for (int32_t l = 0; l < nf; ++l) {
         const double own_am = st_am[l * s_pad + s];
         if (own_am == 0.0) continue;  // pruned or unreachable
+        const uint32_t m = mk[l * kLaneThreads + tid];
+        if (m == 0) continue;
         const int32_t own_ae = st_ae[l * s_pad + s];
-        const float own_fo = st_fo[l * s_pad + s];
         const int32_t nx = (l + 1) * s_pad;
         const unsigned char *rec = rows + (size_t)l * dp.pitch;
-        const float *lprow = PackLp(rec);
         const double *prow = PackP(rec, dp);
         uint32_t *gbrow = gb + l * cols;
         // all posteriors first, then the additions: a shared-memory atomic between
@@ -723,10 +1030,8 @@ GridGradLanes(const FsaInfo *__restrict__ infos, int32_t n, const Arc *__restric
 #pragma unroll
         for (int j = 0; j < kDeg; ++j) {
           const int32_t d = dest_col[j] & 0xffff, c = dest_col[j] >> 16;
-          const float sc = __fadd_rn(w[j], lprow[c]);
-          const float bo = st_bo[nx + d];
           post[j] = 0.0f;
-          if (__fadd_rn(__fadd_rn(own_fo, sc), bo) > cutoff) {
+          if (m & (1u << j)) {
             const double bm = st_bm[nx + d];
             const int32_t e = own_ae + ewk[j] + st_be[nx + d];
             // alpha/Z, exp(w) and beta have mantissas in [0.5, 2); exp(lp) >= 1e-300
@@ -946,7 +1251,7 @@ GridChain(const FsaInfo *__restrict__ infos, const Arc *__restrict__ arcs,
 struct LossLayout {
   Layout base;
   DensePack pack;
-  size_t off_dense, off_arc_factors, off_alpha, off_beta, total_bytes;
+  size_t off_dense, off_arc_factors, off_alpha, off_beta, off_masks, total_bytes;
   bool exclusive_rows;
   int32_t k_deg;      // arcs per lane of the lane kernel
   bool identity;      // every degree <= k_deg: thread s owns state s, no plan
@@ -969,6 +1274,8 @@ static int32_t MakeLossLayout(const k2b200_intersect_args *a, LossLayout *LL) {
   LL->off_arc_factors = take(sizeof(ArcFactor) * (size_t)std::max(a->num_arcs, 1));
   LL->off_alpha = take(sizeof(ProbState) * (size_t)LL->base.grid_elems);
   LL->off_beta = take(sizeof(ProbState) * (size_t)LL->base.grid_elems);
+  // arc survival bytes, planned graphs only: [2 directions][levels][lanes]
+  LL->off_masks = take(LL->identity ? 0 : (size_t)2 * LL->base.total_levels * kLaneThreads + 16);
   LL->total_bytes = off;
   // two graphs on one sequence write the same rows of the dense gradient
   LL->exclusive_rows = true;
@@ -1008,6 +1315,51 @@ static int32_t LaunchChainLanes(const LossLayout &LL, const k2b200_intersect_arg
       reinterpret_cast<ProbState *>(ws + LL.off_beta), tot,
       LL.identity ? nullptr : reinterpret_cast<const int32_t *>(ws + L.off_plan),
       reinterpret_cast<int32_t *>(ws + L.off_unfit), ls); NoteLaunch(); }
+  K2B_CUDA_OK(cudaGetLastError());
+  return kOk;
+}
+
+// Planned graphs: survival masks for all frames, then the mask-driven recursion.
+static int32_t LaunchChainMasked(const LossLayout &LL, const k2b200_intersect_args *args,
+                                 char *ws, double *tot, cudaStream_t stream) {
+  const Layout &L = LL.base;
+  const int32_t s_pad = (L.max_states + 3) & ~3;
+  const FsaInfo *d_infos = reinterpret_cast<const FsaInfo *>(ws + L.off_infos);
+  const Arc *arcs = reinterpret_cast<const Arc *>(args->a_arcs);
+  const unsigned char *dense = reinterpret_cast<const unsigned char *>(ws + LL.off_dense);
+  const float *fwd = reinterpret_cast<const float *>(ws + L.off_fwd),
+              *bwd = reinterpret_cast<const float *>(ws + L.off_bwd),
+              *cutoffs = reinterpret_cast<const float *>(ws + L.off_cutoffs);
+  const int32_t *plan = reinterpret_cast<const int32_t *>(ws + L.off_plan);
+  int32_t *unfit = reinterpret_cast<int32_t *>(ws + L.off_unfit);
+  unsigned char *masks = reinterpret_cast<unsigned char *>(ws + LL.off_masks);
+  {
+    const size_t smem = sizeof(float) * ((size_t)2 * (kMaskRows + 1) * s_pad +
+                                         (size_t)kMaskRows * LL.pack.cols4);
+    K2B_REQUIRE(smem <= kChainSmemBudget, "too many columns for the fused loss path");
+    K2B_CUDA_OK(cudaFuncSetAttribute(ArcMasks<kLaneDeg>,
+                                     cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    dim3 grid(CeilDiv(L.max_tk + 1, kMaskRows), args->num_fsas, 2);
+    { ArcMasks<kLaneDeg><<<grid, kLaneThreads, smem, stream>>>(
+        d_infos, args->num_fsas, L.total_levels, arcs, args->a_row_splits2, args->a_in_splits,
+        args->a_in_arcs, dense, LL.pack, fwd, bwd, cutoffs, plan, unfit, masks, s_pad);
+      NoteLaunch(); }
+  }
+  {
+    constexpr int kU = kChainGroup;
+    const size_t smem = (size_t)kU * (8 * (size_t)LL.pack.cols2 + kLaneThreads) +
+                        sizeof(double) * 2 * s_pad;
+    K2B_REQUIRE(smem <= kChainSmemBudget, "too many columns for the fused loss path");
+    K2B_CUDA_OK(cudaFuncSetAttribute(GridChainMasked<kLaneDeg, kU>,
+                                     cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    dim3 grid(2, args->num_fsas);
+    { GridChainMasked<kLaneDeg, kU><<<grid, kLaneThreads, smem, stream>>>(
+        d_infos, args->num_fsas, L.total_levels, arcs, args->a_row_splits2, args->a_in_splits,
+        args->a_in_arcs, dense, LL.pack, masks, fwd, bwd, cutoffs,
+        reinterpret_cast<ProbState *>(ws + LL.off_alpha),
+        reinterpret_cast<ProbState *>(ws + LL.off_beta), tot, plan, unfit, s_pad);
+      NoteLaunch(); }
+  }
   K2B_CUDA_OK(cudaGetLastError());
   return kOk;
 }
@@ -1058,8 +1410,8 @@ static int32_t LaunchGradLanes(const LossLayout &LL, const k2b200_intersect_args
   const Layout &L = LL.base;
   const int32_t s_pad = (L.max_states + 3) & ~3;
   auto bytes_for = [&](int32_t frames) {
-    return (size_t)32 * (frames + 1) * s_pad + (size_t)frames * LL.pack.pitch +
-           sizeof(float) * (size_t)frames * args->cols;
+    return (size_t)24 * (frames + 1) * s_pad + (size_t)frames * LL.pack.pitch +
+           (size_t)frames * kLaneThreads + sizeof(float) * (size_t)frames * args->cols;
   };
   int32_t sub = 16;
   while (sub > 1 && bytes_for(sub) > 100 * 1024) sub >>= 1;
@@ -1073,9 +1425,7 @@ static int32_t LaunchGradLanes(const LossLayout &LL, const k2b200_intersect_args
       reinterpret_cast<const FsaInfo *>(ws + L.off_infos), args->num_fsas,
       reinterpret_cast<const Arc *>(args->a_arcs), args->a_row_splits2,
       reinterpret_cast<const unsigned char *>(ws + LL.off_dense), LL.pack,
-      reinterpret_cast<const float *>(ws + L.off_fwd),
-      reinterpret_cast<const float *>(ws + L.off_bwd),
-      reinterpret_cast<const float *>(ws + L.off_cutoffs),
+      reinterpret_cast<const unsigned char *>(ws + LL.off_masks), L.total_levels,
       reinterpret_cast<const ProbState *>(ws + LL.off_alpha),
       reinterpret_cast<const ProbState *>(ws + LL.off_beta), tot_grad, stride, grad_a, grad_b,
       reinterpret_cast<const int32_t *>(ws + L.off_plan),
@@ -1171,8 +1521,7 @@ int32_t k2b200_dense_loss_forward(const k2b200_intersect_args *args, void *works
     else if (LL.k_deg == 4 && LL.threads <= 512) K2B_FORWARD(K2B_CHAIN(4, 512));
     else if (LL.k_deg == 4) K2B_FORWARD(K2B_CHAIN(4, 1024));
     else
-      K2B_FORWARD((LaunchChainLanes<8, kLaneThreads, kChainGroupSmall>(LL, args, ws, ls,
-                                                                       tot_scores, stream)));
+      K2B_FORWARD(LaunchChainMasked(LL, args, ws, tot_scores, stream));
 #undef K2B_CHAIN
     // graphs the lane kernel skipped or gave up on
     K2B_CUDA_OK(cudaFuncSetAttribute(GridChain, cudaFuncAttributeMaxDynamicSharedMemorySize,
