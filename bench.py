@@ -388,10 +388,13 @@ def run_ours(args):
         # that a surviving arc touches
         "grad": grid_bytes + 32 * S_out + 12 * frames * C + 4 * A_out,
     }
-    phase_kernel = {"viterbi": "RegisterViterbi", "scores": "ProbScoresStaged",
-                    "prune": "CountStates|CountKept", "emit": "EmitLattice", "dense": "DenseFill+DenseBackward+ExpDense",
+    planned = graphs.arcs.max_degree() > 4  # lanes assigned to states by a plan
+    phase_kernel = {"viterbi": "LanesViterbi" if planned else "RegisterViterbi",
+                    "scores": "ProbScoresStaged", "prune": "CountStates|CountKept",
+                    "emit": "EmitLattice", "dense": "DenseFill+DenseBackward+ExpDense",
                     "post": "ArcPost+LogBackward+IndexAdd", "incoming": "BuildIncoming",
-                    "chain": "GridChainLanes", "grad": "GridGradWarp/GridGradLanes"}
+                    "chain": "ArcMasks+GridChainMasked" if planned else "GridChainLanes",
+                    "grad": "GridGradLanes" if planned else "GridGradWarp"}
     peaks = {}
     try:
         with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
@@ -403,9 +406,14 @@ def run_ours(args):
     # the dominant phase of the timed region carries the roofline figure
     top = max(phases, key=lambda k: phases[k][0])
     top_ms, top_n = phases[top]
-    top_avg_ms = top_ms / max(top_n, 1)
+    top_avg_ms = top_ms / args.steps  # the phase's kernels of one step
     achieved = phase_bytes[top] / (top_avg_ms * 1e-3) / 1e9 if top_avg_ms > 0 else 0.0
-    traffic = {"RegisterViterbi": 282.4e6, "ProbScoresStaged": 96.4e6}.get(phase_kernel[top])
+    # dram read + write of one launch from the ncu capture of this workload (profiles/);
+    # known for ctc_large only
+    traffic = None
+    if w.name == "ctc_large" and args.scale == 1.0:
+        traffic = {"GridChainLanes": 928.2e6, "RegisterViterbi": 282.4e6,
+                   "ProbScoresStaged": 96.4e6}.get(phase_kernel[top])
 
     if rank != 0:
         if dist is not None:
@@ -434,7 +442,8 @@ def run_ours(args):
                      "note": "latency-bound: a chain of T dependent frames per utterance; "
                              "traffic is the ncu dram read+write of one launch on this "
                              "workload (profiles/)"},
-        "phase_gbs": {k: (phase_bytes[k] / (v[0] / max(v[1], 1) * 1e-3) / 1e9 if v[0] > 0 else 0.0)
+        # algorithmic bytes of a phase over its time per step
+        "phase_gbs": {k: (phase_bytes[k] / (v[0] / args.steps * 1e-3) / 1e9 if v[0] > 0 else 0.0)
                       for k, v in phases.items()},
         "e2e": {"value": e2e_value, "unit": "frames/s",
                 "h2d_bytes_per_step": int(w.log_probs.numel() * 4), "d2h_bytes_per_step": 8,
