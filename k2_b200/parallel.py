@@ -35,3 +35,50 @@ def all_reduce_loss(loss_sum: torch.Tensor, num_frames: int, group=None) -> Tupl
                                     device=loss_sum.device)])
     dist.all_reduce(buf, group=group)
     return buf[0], int(round(buf[1].item()))
+
+
+class HostPrefetcher:
+    """Double-buffered host -> device input pipeline for a training loop: the copy
+    of batch k+1 (from pinned host memory, on its own stream) runs while batch k is
+    being processed.  Usage::
+
+        pf = HostPrefetcher("cuda:0")
+        pf.submit(first_batch)
+        for k in range(steps):
+            x = pf.get()                    # batch k on the device
+            if k + 1 < steps:
+                pf.submit(next_batch)       # overlaps the work on batch k
+            ...                             # forward / backward on x
+
+    A buffer is reused `depth` batches later; `submit` first makes the copy stream
+    wait for everything already enqueued on the current stream, so work that still
+    reads the buffer is never overtaken."""
+
+    def __init__(self, device, depth: int = 2):
+        self.device = torch.device(device)
+        self.depth = depth
+        self.stream = torch.cuda.Stream(self.device)
+        self.bufs: List[torch.Tensor] = [None] * depth
+        self.ready = [torch.cuda.Event() for _ in range(depth)]
+        self.submitted = 0
+        self.taken = 0
+
+    def submit(self, host_tensor: torch.Tensor) -> None:
+        assert self.submitted - self.taken < self.depth, "all buffers are in flight"
+        slot = self.submitted % self.depth
+        buf = self.bufs[slot]
+        if buf is None or buf.shape != host_tensor.shape or buf.dtype != host_tensor.dtype:
+            buf = torch.empty(host_tensor.shape, dtype=host_tensor.dtype, device=self.device)
+            self.bufs[slot] = buf
+        self.stream.wait_stream(torch.cuda.current_stream(self.device))
+        with torch.cuda.stream(self.stream):
+            buf.copy_(host_tensor, non_blocking=True)
+            self.ready[slot].record(self.stream)
+        self.submitted += 1
+
+    def get(self) -> torch.Tensor:
+        assert self.taken < self.submitted, "nothing submitted"
+        slot = self.taken % self.depth
+        torch.cuda.current_stream(self.device).wait_event(self.ready[slot])
+        self.taken += 1
+        return self.bufs[slot]
