@@ -415,7 +415,8 @@ GridChainLanes(const FsaInfo *__restrict__ infos, int32_t n, const Arc *__restri
 // with r the step t = 1..T of the forward recursion (dir 0) or the level u = 0..T-1
 // the arc leaves from (dir 1).  grid = (row chunks, pairs, 2 directions); the CTA
 // stages the Viterbi scores of its levels (-inf for pruned states) and the dense
-// scores of its rows in shared memory.  Also enforces kMinDenseScore.
+// scores of its rows in shared memory.  Also enforces kMinDenseScore (on every finite
+// element of the rows, a little stricter than on surviving arcs only).
 // ---------------------------------------------------------------------------
 constexpr int kMaskRows = 32;  // rows per CTA
 
@@ -453,9 +454,14 @@ ArcMasks(const FsaInfo *__restrict__ infos, int32_t n, int64_t total_levels,
     fo[l * s_pad + q] = keep ? fu : -INFINITY;
     bo[l * s_pad + q] = keep ? bu : -INFINITY;
   }
+  bool risky = false;
   for (int32_t idx = tid; idx < nf * dp.cols4; idx += nt) {
     const int32_t l = idx / dp.cols4, c = idx - l * dp.cols4;
-    lp[idx] = PackLp(dense + ((int64_t)f.row0 + lb + l) * dp.pitch)[c];
+    const float v = PackLp(dense + ((int64_t)f.row0 + lb + l) * dp.pitch)[c];
+    lp[idx] = v;
+    // checked per row element rather than per surviving arc: stricter, and off the
+    // inner loop
+    risky |= v < kMinDenseScore && v != -INFINITY;
   }
   int32_t s = -1, g = 0, G = 1;
   {
@@ -490,7 +496,12 @@ ArcMasks(const FsaInfo *__restrict__ infos, int32_t n, int64_t total_levels,
     }
   }
   __syncthreads();
-  bool risky = false;
+  // slots that no lane of this warp uses are skipped (lanes of a warp hold states of
+  // similar degree)
+  uint32_t used = 0;
+#pragma unroll
+  for (int j = 0; j < kDeg; ++j)
+    if (__any_sync(0xffffffffu, w[j] != -INFINITY)) used |= 1u << j;
   unsigned char *out = masks + ((int64_t)dir * total_levels + f.level_off + r0) * kLaneThreads;
   for (int32_t k = 0; k < nf; ++k) {
     uint32_t bits = 0;
@@ -502,16 +513,13 @@ ArcMasks(const FsaInfo *__restrict__ infos, int32_t n, int64_t total_levels,
         const float *lprow = lp + k * dp.cols4;
 #pragma unroll
         for (int j = 0; j < kDeg; ++j) {
+          if (!(used & (1u << j))) continue;  // warp-uniform
           const int32_t o_idx = other_col[j] & 0xffff, c = other_col[j] >> 16;
-          const float l = lprow[c];
-          const float sc = __fadd_rn(w[j], l);
+          const float sc = __fadd_rn(w[j], lprow[c]);
           const float o = oth[o_idx];
           const float through = dir == 0 ? __fadd_rn(__fadd_rn(o, sc), own)
                                          : __fadd_rn(__fadd_rn(own, sc), o);
-          if (through > cutoff) {
-            bits |= 1u << j;
-            risky |= l < kMinDenseScore;
-          }
+          if (through > cutoff) bits |= 1u << j;
         }
       }
     }
@@ -630,6 +638,7 @@ GridChainMasked(const FsaInfo *__restrict__ infos, int32_t n, int64_t total_leve
   };
   if (tid == 0)
     for (int32_t step = 1; step < kU; ++step) issue_row(step, step - 1);
+  const int32_t g_max = __reduce_max_sync(0xffffffffu, G);  // widest lane group of this warp
   const int32_t s_ld = s >= 0 ? s : 0;
   int64_t pos = (dir == 0 ? 1 : Tk - 1) * (int64_t)S + s_ld;
   double last = 0.0;
@@ -666,14 +675,21 @@ GridChainMasked(const FsaInfo *__restrict__ infos, int32_t n, int64_t total_leve
       const uint32_t m = (ring + rec_off + p_bytes)[tid];
       double sum = 0.0;
       if (__any_sync(0xffffffffu, m != 0)) {
+        double sum1 = 0.0;  // two partial sums: half the chain of dependent additions
 #pragma unroll
-        for (int j = 0; j < kDeg; ++j)
+        for (int j = 0; j < kDeg; j += 2) {
           if (m & (1u << j))
             sum += prev[other_col[j] & 0xffff] * ew[j] * prow[other_col[j] >> 16];
+          if (j + 1 < kDeg && (m & (2u << j)))
+            sum1 += prev[other_col[j + 1] & 0xffff] * ew[j + 1] * prow[other_col[j + 1] >> 16];
+        }
+        sum += sum1;
 #pragma unroll
         for (int32_t d = 16; d > 0; d >>= 1) {
-          const double so = __shfl_down_sync(0xffffffffu, sum, d);
-          if (g + d < G) sum += so;
+          if (d < g_max) {  // warp-uniform: no group of this warp is that wide
+            const double so = __shfl_down_sync(0xffffffffu, sum, d);
+            if (g + d < G) sum += so;
+          }
         }
       }
       const double v = u == 0 ? sum * scale : sum;
