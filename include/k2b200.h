@@ -201,6 +201,12 @@ typedef struct {
   /* largest number of arcs entering or leaving any state of a_fsas; 0 = unknown
    * (then mode 3 is never chosen) */
   int32_t a_max_degree;
+  /* non-zero: every graph of a_fsas is a copy of graph 0 (same states, arcs and
+   * scores), as k2 users build them for decoding (one HLG per sequence) because
+   * k2::IntersectDense cannot share a graph (k2/csrc/intersect_dense.cu:75-93).
+   * Only graph 0 is then read, so that it stays cache-resident; results are the
+   * same as with 0.  The caller vouches for the equality. */
+  int32_t a_shared;
 } k2b200_intersect_args;
 
 typedef struct {

@@ -34,7 +34,7 @@ class IntersectArgs(ctypes.Structure):
         ("scores", c_vp), ("rows", c_i32), ("cols", c_i32), ("num_seqs", c_i32),
         ("h_b_row_splits", c_vp), ("h_a_to_b_map", c_vp),
         ("output_beam", c_f32), ("max_states", c_i32), ("max_arcs", c_i32),
-        ("viterbi_mode", c_i32), ("a_max_degree", c_i32),
+        ("viterbi_mode", c_i32), ("a_max_degree", c_i32), ("a_shared", c_i32),
     ]
 
 

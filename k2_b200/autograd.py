@@ -14,6 +14,9 @@ from .ragged import RaggedArc
 
 # 0 = automatic, 1 = one launch per frame, 2 = persistent kernel (see include/k2b200.h)
 VITERBI_MODE = 0
+# a_fsas made of identical copies of one graph are read through copy 0 only when
+# they are at least this large (smaller ones stay cache-resident anyway)
+SHARED_GRAPH_MIN_BYTES = 32 << 20
 
 
 def _index_add(index: torch.Tensor, value: torch.Tensor, in_out: torch.Tensor) -> None:
@@ -79,7 +82,9 @@ def _make_intersect_args(a: RaggedArc, b: DenseFsaVec, a_to_b_map: Optional[torc
         h_a_to_b_map=None if h_map is None else h_map.ctypes.data,
         output_beam=float(output_beam), max_states=int(min(max_states, 2**31 - 1)),
         max_arcs=int(min(max_arcs, 2**31 - 1)), viterbi_mode=viterbi_mode,
-        a_max_degree=a.max_degree())
+        a_max_degree=a.max_degree(),
+        # one large graph copied once per sequence: read copy 0 only
+        a_shared=int(h_map is None and a.replicated(SHARED_GRAPH_MIN_BYTES)))
     return args, (h_rs1, h_as, h_map, in_splits, in_arcs, scores), dev, h_brs
 
 

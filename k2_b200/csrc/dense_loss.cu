@@ -878,7 +878,7 @@ GridGradWarp(const FsaInfo *__restrict__ infos, const Arc *__restrict__ arcs,
           const float post = (float)(prod * Pow2Clamped(e1 + ae + af.k + bexp + zk));
           atomicAdd(&gbrow[c], __float2uint_rn(post * 2147483648.0f));
           if (ga_in_smem) atomicAdd(&ga[k], __float2uint_rn(post * 67108864.0f));
-          else atomicAdd(&grad_a[f.arc_off + k], tg * post);
+          else atomicAdd(&grad_a[f.arc_off + f.arc_out_off + k], tg * post);
         }
       }
     }
@@ -896,7 +896,9 @@ GridGradWarp(const FsaInfo *__restrict__ infos, const Arc *__restrict__ arcs,
   if (ga_in_smem)
     for (int32_t k = tid; k < A; k += nt) {
       const uint32_t fixed = ga[k];
-      if (fixed != 0u) atomicAdd(&grad_a[f.arc_off + k], tg * ((float)fixed * (1.0f / 67108864.0f)));
+      if (fixed != 0u)
+        atomicAdd(&grad_a[f.arc_off + f.arc_out_off + k],
+                  tg * ((float)fixed * (1.0f / 67108864.0f)));
     }
 }
 
@@ -1077,7 +1079,7 @@ GridGradLanes(const FsaInfo *__restrict__ infos, int32_t n, const Arc *__restric
   if (s >= 0) {
 #pragma unroll
     for (int j = 0; j < kDeg; ++j)
-      if (ga[j] != 0.0f) atomicAdd(&grad_a[first_arc + j * G], tg * ga[j]);
+      if (ga[j] != 0.0f) atomicAdd(&grad_a[first_arc + f.arc_out_off + j * G], tg * ga[j]);
   }
 }
 

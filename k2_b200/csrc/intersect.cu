@@ -58,6 +58,15 @@ int32_t MakeLayout(const k2b200_intersect_args *a, Layout *L) {
     f.num_states = a->h_a_row_splits1[i + 1] - f.state_off;
     f.arc_off = a->h_a_arc_splits[i];
     f.num_arcs = a->h_a_arc_splits[i + 1] - f.arc_off;
+    f.arc_out_off = 0;
+    if (a->a_shared) {  // read graph 0 in place of its copy i
+      K2B_REQUIRE(f.num_states == a->h_a_row_splits1[1] - a->h_a_row_splits1[0] &&
+                      f.num_arcs == a->h_a_arc_splits[1] - a->h_a_arc_splits[0],
+                  "a_shared is set but graph %d differs in size from graph 0", i);
+      f.arc_out_off = f.arc_off - a->h_a_arc_splits[0];
+      f.state_off = a->h_a_row_splits1[0];
+      f.arc_off = a->h_a_arc_splits[0];
+    }
     f.row0 = a->h_b_row_splits[j];
     f.tk = a->h_b_row_splits[j + 1] - f.row0;
     K2B_REQUIRE(f.tk >= 1, "sequence %d has no rows", j);
@@ -435,7 +444,7 @@ EmitWord(const FsaInfo &f, int32_t i, int32_t n, int64_t rel, float cutoff, int 
     o.score = sc;
     out_arcs[pos] = o;
     out.row_ids2[pos] = state_id;
-    if (out.arc_map_a) out.arc_map_a[pos] = a;
+    if (out.arc_map_a) out.arc_map_a[pos] = a + f.arc_out_off;
     if (out.arc_map_b) out.arc_map_b[pos] = (int32_t)(row * cols + (arc.label + 1));
     ++pos;
   }

@@ -17,6 +17,8 @@ struct FsaInfo {
   int32_t tk;          // rows of the sequence = frames + 1 (k2's FsaInfo.T)
   int32_t level_off;   // sum over earlier pairs of (tk + 1)
   int32_t words;       // ceil(S / 32)
+  int32_t arc_out_off; // added to a graph arc index when it names the arc to the caller
+                       // (arc_map_a, grad_a): non-zero only when graphs share storage
   int64_t grid_off;    // sum over earlier pairs of (tk + 1) * S
   int64_t word_off;    // sum over earlier pairs of (tk + 1) * words
 };

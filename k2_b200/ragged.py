@@ -150,6 +150,31 @@ class RaggedArc:
                               buf[2, :na].view(torch.float32))
         return self._incoming
 
+    def replicated(self, min_bytes: int = 32 << 20) -> bool:
+        """Is every FSA of this FsaVec an exact copy of FSA 0 (states, arcs and
+        scores), and is the whole large enough (`min_bytes`) for that to matter?
+        Decoding graphs are stacked like this, one copy per sequence.  One device
+        comparison and host read per version of the arc tensor, then cached."""
+        n = self.num_fsas
+        vals = self._values
+        if n < 2 or vals.numel() * 4 < min_bytes or not vals.is_cuda:
+            return False
+        key = (vals.data_ptr(), vals._version, self._row_splits2.data_ptr())
+        cached = getattr(self, "_replicated", None)
+        if cached is not None and cached[0] == key:
+            return cached[1]
+        h1 = np.asarray(self.h_row_splits1, dtype=np.int64)
+        ha = np.asarray(self.h_arc_splits, dtype=np.int64)
+        S, A = int(h1[1] - h1[0]), int(ha[1] - ha[0])
+        same = bool(np.all(np.diff(h1) == S) and np.all(np.diff(ha) == A)) and S > 0 and A > 0
+        if same:
+            v = vals.view(n, A, 4)
+            rs2 = self._row_splits2[:-1].view(n, S)
+            same = bool(((v == v[0]).all() & ((rs2 - rs2[:, :1]) == (rs2[0] - rs2[0, 0])).all())
+                        .item())
+        self._replicated = (key, same)
+        return same
+
     def max_degree(self) -> int:
         """Largest in- or out-degree of any state (one host read, cached)."""
         if getattr(self, "_max_degree", None) is None:

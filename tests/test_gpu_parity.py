@@ -323,3 +323,41 @@ def test_ctc_graph_on_gpu_matches_oracle(k2):
             np.testing.assert_array_equal(g.arcs.h_row_splits1, o.row_splits1)
             np.testing.assert_array_equal(g.arcs.h_arc_splits, o.row_splits2[o.row_splits1])
             assert g.properties == oracle.properties(o)[1]
+
+
+def test_replicated_graph_is_read_through_its_first_copy(k2):
+    # one graph copied once per sequence (how decoding graphs are stacked): with the
+    # sharing threshold lowered the kernels read copy 0 only; lattice, arc maps and
+    # gradients must not change
+    from gpu_util import dense_from_scores, fsa_to_host, host_to_fsa
+    from k2_b200 import autograd
+    from oracle.common import HostFsaVec
+    rng = np.random.default_rng(31)
+    one = random_fsa_vec(rng, 1, max_states=40, max_arcs=200, acyclic=False, allow_empty=False)
+    n, S, A = 5, one.num_states, one.num_arcs
+    rs1 = (np.arange(n + 1) * S).astype(np.int32)
+    rs2 = np.concatenate([one.row_splits2[:-1] + i * A for i in range(n)] + [[n * A]]).astype(np.int32)
+    a = HostFsaVec(rs1, rs2, np.tile(one.arcs, (n, 1)))
+    scores, brs = random_dense(rng, n, 12, 5, low_rows=False)
+    out = {}
+    for shared in (False, True):
+        autograd.SHARED_GRAPH_MIN_BYTES = 0 if shared else 1 << 40
+        try:
+            fsa = host_to_fsa(a)
+            assert fsa.arcs.replicated(autograd.SHARED_GRAPH_MIN_BYTES) == shared
+            fsa.scores.requires_grad_(True)
+            dense = dense_from_scores(scores, brs, requires_grad=True)
+            lat, ma, mb = autograd._intersect_dense_arcs(fsa.arcs, dense, None, 8.0, 15000000, 1 << 30)
+            tot = k2.intersect_dense_tot_scores(fsa, dense, 8.0)
+            tot[torch.isfinite(tot)].sum().backward()
+            out[shared] = (fsa_to_host(k2.Fsa(lat, _check=False), ma, mb),
+                           tot.detach().cpu().numpy(), fsa.scores.grad.cpu().numpy(),
+                           dense.scores.grad.cpu().numpy())
+        finally:
+            autograd.SHARED_GRAPH_MIN_BYTES = 32 << 20
+    same_fsa(out[True][0], out[False][0], "shared")
+    np.testing.assert_array_equal(out[True][1], out[False][1])
+    np.testing.assert_allclose(out[True][2], out[False][2], atol=1e-6)
+    np.testing.assert_array_equal(out[True][3], out[False][3])
+    want = oracle.intersect_dense(a, scores, brs, 8.0)
+    same_fsa(out[True][0], want, "shared vs oracle")
