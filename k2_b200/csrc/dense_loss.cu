@@ -135,14 +135,15 @@ constexpr int32_t kMinExponent = -480;     // binary exponent of every non-zero 
 
 // ---------------------------------------------------------------------------
 // The alpha / beta recursion.  grid = (2 directions, pairs), one CTA walks all
-// frames of its pair.  Per frame: one bulk copy (issued stages - 1 frames ahead by
-// thread 0, completion on an mbarrier) brings the packed dense row into a
-// shared-memory ring of kChainGroup slots; every lane runs the reference's pruning test
-// (intersect_dense.cu:430-470) on its arcs with the same fp32 expressions and adds
-// the survivors' alpha[src] * exp(w) * exp(lp); the lanes of a state merge by
-// shuffles.  The Viterbi scores of the lane's own state are fetched kChainGroup
-// frames ahead into registers; the frame loop is unrolled by that number, so ring
-// slots, buffers and register slots are compile-time constants.
+// frames of its pair.  Per frame three bulk copies (issued kU - 1 frames ahead by
+// thread 0, completion on one mbarrier) bring the packed dense row and the two
+// Viterbi rows of the level into a shared-memory ring of kU slots; every lane runs
+// the reference's pruning test (intersect_dense.cu:430-470) on its arcs with the
+// same fp32 expressions and adds the survivors' alpha[src] * exp(w) * exp(lp); the
+// lanes of a state merge by shuffles.  The frame loop is unrolled by kU, so ring
+// slots and buffers are compile-time constants.  Nothing is prefetched through
+// registers: global loads kept in flight across frames made every frame wait a
+// full memory latency (the scoreboards a load waits on are shared counters).
 //
 // Arithmetic: all states of a level share one binary exponent K, so a value is a
 // plain double v with alpha = v * 2^K and an arc costs two multiplies and an add.
