@@ -380,6 +380,20 @@ int32_t k2b200_shortest_path(const int32_t *row_splits1, const void *arcs,
                              int32_t *path_splits, int32_t *best_arcs, void *tmp,
                              void *stream);
 
+/* Layering of a top-sorted, acyclic FsaVec for k2b200_fsa_scores (what the
+ * reference calls state batches, k2::GetStateBatches, k2/csrc/fsa_utils.cu:679-899):
+ * level_offsets[num_fsas+1] and level_splits[<= num_states+1] (allocate
+ * num_states + 1 entries; level_offsets[num_fsas] is the number of layers).  Every
+ * arc leads from a lower to a higher layer.  *status (device) receives 0, or 1 when
+ * some arc does not lead to a higher-numbered state (not top-sorted, cyclic or a
+ * self-loop): the outputs are then meaningless.  row_ids2[num_arcs]: state (idx01)
+ * of every arc.  tmp: k2b200_fsa_levels_tmp_bytes(num_states) bytes. */
+size_t k2b200_fsa_levels_tmp_bytes(int32_t num_states);
+int32_t k2b200_fsa_levels(const int32_t *row_splits1, const int32_t *row_splits2,
+                          const int32_t *row_ids2, const void *arcs, int32_t num_fsas,
+                          int32_t num_states, int32_t num_arcs, int32_t *level_offsets,
+                          int32_t *level_splits, int32_t *status, void *tmp, void *stream);
+
 /* Per-FSA property bits (k2/csrc/fsa.h:75-101) and their AND.
  * Replaces k2::GetFsaVecBasicProperties, k2/csrc/fsa.cu:54-217.  tmp must hold
  * k2b200_fsa_properties_tmp_bytes(...) bytes; properties[num_fsas+1] is written

@@ -94,6 +94,9 @@ _sig("k2b200_dense_loss_forward", c_i32,
      [ctypes.POINTER(IntersectArgs), c_vp, c_sz, c_vp, c_vp, ctypes.POINTER(c_f32)])
 _sig("k2b200_dense_loss_backward", c_i32,
      [ctypes.POINTER(IntersectArgs), c_vp, c_sz, c_vp, c_i32, c_vp, c_vp, c_vp])
+_sig("k2b200_fsa_levels_tmp_bytes", c_sz, [c_i32])
+_sig("k2b200_fsa_levels", c_i32,
+     [c_vp, c_vp, c_vp, c_vp, c_i32, c_i32, c_i32, c_vp, c_vp, c_vp, c_vp, c_vp])
 _sig("k2b200_fsa_scores_scratch_bytes", c_sz, [ctypes.POINTER(FsaView)])
 _sig("k2b200_fsa_scores", c_i32,
      [ctypes.POINTER(FsaView), c_i32, c_i32, c_vp, c_vp, c_vp, c_vp, c_sz, c_vp])
@@ -133,6 +136,7 @@ EXPORTED = [
     "k2b200_dense_fsa_vec_fill", "k2b200_dense_fsa_vec_backward",
     "k2b200_ctc_graph_tmp_bytes", "k2b200_ctc_graph",
     "k2b200_fsa_properties_tmp_bytes", "k2b200_fsa_properties",
+    "k2b200_fsa_levels_tmp_bytes", "k2b200_fsa_levels",
     "k2b200_dense_loss_supported", "k2b200_dense_loss_workspace_bytes",
     "k2b200_dense_loss_forward", "k2b200_dense_loss_backward",
 ]

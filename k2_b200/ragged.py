@@ -208,10 +208,11 @@ class RaggedArc:
         """(level_offsets, level_splits): a layering of the states such that every
         arc goes from a lower to a higher layer.  Lattices made by intersect_dense
         carry their frame layering; for any other top-sorted acyclic FsaVec the
-        layering (longest distance from the start state) is derived on the host
-        once and cached - the scores themselves are always computed on the GPU."""
+        layering (longest distance from a state without entering arcs) is computed
+        on the GPU once and cached (k2b200_fsa_levels; one host read of its status
+        and of the number of layers)."""
         if self._levels is None:
-            self._levels = _host_levels(self)
+            self._levels = _gpu_levels(self)
         return self._levels
 
     def __repr__(self):
@@ -235,40 +236,23 @@ def _row_ids(row_splits: torch.Tensor, num_elems: int) -> torch.Tensor:
         np.repeat(np.arange(len(rs) - 1, dtype=np.int32), np.diff(rs)).astype(np.int32))
 
 
-def _host_levels(arcs: RaggedArc):
-    """Longest-distance layering, computed with numpy from a host copy."""
-    rs1 = arcs.h_row_splits1
-    rs2 = arcs._row_splits2.cpu().numpy()
-    vals = arcs._values.cpu().numpy()
-    ns = arcs.num_states
-    level = np.zeros(ns, dtype=np.int64)
-    order_ok = True
-    for i in range(len(rs1) - 1):
-        b, e = int(rs1[i]), int(rs1[i + 1])
-        for s in range(b, e):
-            a0, a1 = int(rs2[s]), int(rs2[s + 1])
-            if a1 > a0:
-                d = vals[a0:a1, 1].astype(np.int64) + b
-                if np.any(d <= s):
-                    order_ok = False
-                np.maximum.at(level, d, level[s] + 1)
-    if not order_ok:
-        raise RuntimeError("forward/backward scores need a top-sorted, acyclic FsaVec")
-    # states must be grouped by level within each FSA for contiguous layers; when
-    # they are not, fall back to one state per layer (always valid when top-sorted)
-    offsets = [0]
-    splits = []
-    for i in range(len(rs1) - 1):
-        b, e = int(rs1[i]), int(rs1[i + 1])
-        lv = level[b:e]
-        if e > b and np.all(np.diff(lv) >= 0):
-            change = np.nonzero(np.diff(lv))[0] + 1
-            starts = np.concatenate([[0], change]) + b
-        else:
-            starts = np.arange(b, e)
-        splits.extend(starts.tolist())
-        offsets.append(len(splits))
-    splits.append(int(rs1[-1]))
+def _gpu_levels(arcs: RaggedArc):
+    _lib.require_cuda(arcs._values, "fsas")
     dev = arcs.device
-    return (torch.tensor(offsets, dtype=torch.int32, device=dev),
-            torch.tensor(splits, dtype=torch.int32, device=dev))
+    ns, na, nf = arcs.num_states, arcs.num_elements(), arcs.num_fsas
+    i32 = dict(dtype=torch.int32, device=dev)
+    offsets = torch.empty(nf + 2, **i32)   # [nf + 1] offsets, then the status word
+    splits = torch.empty(ns + 2, **i32)
+    tmp = torch.empty(_lib.lib.k2b200_fsa_levels_tmp_bytes(ns), dtype=torch.uint8, device=dev)
+    rid2 = arcs.row_ids(2 - arcs.single)
+    status = offsets[nf + 1:]
+    with torch.cuda.device(dev):
+        _lib.check(_lib.lib.k2b200_fsa_levels(
+            _lib.ptr(arcs._row_splits1), _lib.ptr(arcs._row_splits2), _lib.ptr(rid2),
+            _lib.ptr(arcs._values), nf, ns, na, _lib.ptr(offsets), _lib.ptr(splits),
+            _lib.ptr(status), _lib.ptr(tmp), _lib.stream_of(dev)))
+    _lib.note_launches(4)
+    total, bad = (int(v) for v in offsets[nf:].tolist())
+    if bad:
+        raise RuntimeError("forward/backward scores need a top-sorted, acyclic FsaVec")
+    return offsets[:nf + 1], splits[:total + 1]

@@ -138,6 +138,6 @@ def test_ctc_loss_uses_the_same_numbers_either_way():
         finally:
             ctc_mod.FUSED_LOSS = True
         loss.backward()
-        out[fused] = (float(loss), lp.grad.cpu().numpy())
+        out[fused] = (float(loss.detach()), lp.grad.cpu().numpy())
     assert abs(out[True][0] - out[False][0]) <= 1e-6 * abs(out[False][0])
     assert np.abs(out[True][1] - out[False][1]).max() <= 1e-4

@@ -361,3 +361,29 @@ def test_replicated_graph_is_read_through_its_first_copy(k2):
     np.testing.assert_array_equal(out[True][3], out[False][3])
     want = oracle.intersect_dense(a, scores, brs, 8.0)
     same_fsa(out[True][0], want, "shared vs oracle")
+
+
+def test_layering_of_arbitrary_fsa_vecs(k2):
+    # k2b200_fsa_levels against the numpy longest-distance layering
+    from gpu_util import host_to_fsa
+    from util import host_levels
+    rng = np.random.default_rng(41)
+    for trial in range(30):
+        a = random_fsa_vec(rng, int(rng.integers(1, 7)), max_states=30, max_arcs=80, acyclic=True)
+        arcs = host_to_fsa(a).arcs
+        arcs._levels = None
+        off, spl = arcs.levels()
+        want_off, want_spl = host_levels(arcs)
+        np.testing.assert_array_equal(off.cpu().numpy(), want_off, f"trial {trial}")
+        np.testing.assert_array_equal(spl.cpu().numpy(), want_spl, f"trial {trial}")
+    # a linear chain (one state per layer) and a graph with a cycle
+    lin = k2.linear_fsa([3, 1, 4, 1, 5], device="cuda:0").arcs
+    lin._levels = None
+    off, spl = lin.levels()
+    assert off.tolist() == [0, 7] and spl.tolist() == list(range(8))
+    cyc = random_fsa_vec(rng, 2, max_states=8, max_arcs=30, acyclic=False, allow_empty=False)
+    cyc_arcs = host_to_fsa(cyc).arcs
+    cyc_arcs._levels = None
+    if np.any(cyc.arcs[:, 1] <= cyc.arcs[:, 0]):
+        with pytest.raises(RuntimeError):
+            cyc_arcs.levels()

@@ -77,3 +77,41 @@ def close(a, b, rtol=1e-6, atol=1e-6):
     with np.errstate(invalid="ignore"):
         ok = both_inf | (np.abs(a - b) <= atol + rtol * np.abs(b))
     return bool(np.all(ok))
+
+
+def host_levels(arcs):
+    """Longest-distance layering of a RaggedArc computed with numpy from a host copy:
+    the checker of k2b200_fsa_levels.  Returns (offsets, splits) as numpy arrays."""
+    rs1 = arcs.h_row_splits1
+    rs2 = arcs._row_splits2.cpu().numpy()
+    vals = arcs._values.cpu().numpy()
+    ns = arcs.num_states
+    level = np.zeros(ns, dtype=np.int64)
+    order_ok = True
+    for i in range(len(rs1) - 1):
+        b, e = int(rs1[i]), int(rs1[i + 1])
+        for s in range(b, e):
+            a0, a1 = int(rs2[s]), int(rs2[s + 1])
+            if a1 > a0:
+                d = vals[a0:a1, 1].astype(np.int64) + b
+                if np.any(d <= s):
+                    order_ok = False
+                np.maximum.at(level, d, level[s] + 1)
+    if not order_ok:
+        raise RuntimeError("forward/backward scores need a top-sorted, acyclic FsaVec")
+    # states must be grouped by level within each FSA for contiguous layers; when
+    # they are not, fall back to one state per layer (always valid when top-sorted)
+    offsets = [0]
+    splits = []
+    for i in range(len(rs1) - 1):
+        b, e = int(rs1[i]), int(rs1[i + 1])
+        lv = level[b:e]
+        if e > b and np.all(np.diff(lv) >= 0):
+            change = np.nonzero(np.diff(lv))[0] + 1
+            starts = np.concatenate([[0], change]) + b
+        else:
+            starts = np.arange(b, e)
+        splits.extend(starts.tolist())
+        offsets.append(len(splits))
+    splits.append(int(rs1[-1]))
+    return np.asarray(offsets, np.int32), np.asarray(splits, np.int32)
