@@ -157,6 +157,23 @@ int32_t k2b200_dense_fsa_vec_backward(const float *grad_scores, int64_t num_seqs
                                       int32_t num_segs, int32_t rows, int32_t overlapping,
                                       float *grad_log_probs, void *stream);
 
+/* The same with log_softmax(logits, dim=-1) fused in: scores =
+ * layout(log_softmax(logits)), and the adjoint w.r.t. the logits (needs the scores
+ * the forward call wrote).  Replaces torch.log_softmax followed by the
+ * DenseFsaVec constructor, k2/python/k2/dense_fsa_vec.py:101-133, in one pass each
+ * way. */
+int32_t k2b200_dense_fsa_vec_from_logits(const float *logits, int64_t num_seqs,
+                                         int64_t num_frames, int32_t num_classes,
+                                         const int32_t *segments, const int32_t *row_splits,
+                                         int32_t num_segs, float *scores, int32_t rows,
+                                         void *stream);
+int32_t k2b200_dense_fsa_vec_from_logits_backward(const float *grad_scores, const float *scores,
+                                                  int64_t num_seqs, int64_t num_frames,
+                                                  int32_t num_classes, const int32_t *segments,
+                                                  const int32_t *row_splits, int32_t num_segs,
+                                                  int32_t rows, int32_t overlapping,
+                                                  float *grad_logits, void *stream);
+
 /* ---------------------------------------------------------------------------
  * intersect_dense.
  * Replaces k2::IntersectDense / MultiGraphDenseIntersect,

@@ -116,6 +116,10 @@ _sig("k2b200_dense_fsa_vec_fill", c_i32,
      [c_vp, c_i64, c_i64, c_i32, c_vp, c_vp, c_i32, c_vp, c_i32, c_vp])
 _sig("k2b200_dense_fsa_vec_backward", c_i32,
      [c_vp, c_i64, c_i64, c_i32, c_vp, c_vp, c_i32, c_i32, c_i32, c_vp, c_vp])
+_sig("k2b200_dense_fsa_vec_from_logits", c_i32,
+     [c_vp, c_i64, c_i64, c_i32, c_vp, c_vp, c_i32, c_vp, c_i32, c_vp])
+_sig("k2b200_dense_fsa_vec_from_logits_backward", c_i32,
+     [c_vp, c_vp, c_i64, c_i64, c_i32, c_vp, c_vp, c_i32, c_i32, c_i32, c_vp, c_vp])
 _sig("k2b200_shortest_path_tmp_bytes", c_sz, [c_i32])
 _sig("k2b200_shortest_path", c_i32, [c_vp, c_vp, c_vp, c_i32, c_vp, c_vp, c_vp, c_vp])
 _sig("k2b200_fsa_properties_tmp_bytes", c_sz, [c_i32, c_i32])
@@ -134,6 +138,7 @@ EXPORTED = [
     "k2b200_tot_scores_tropical_backward", "k2b200_index_add", "k2b200_index_select_i32",
     "k2b200_shortest_path_tmp_bytes", "k2b200_shortest_path",
     "k2b200_dense_fsa_vec_fill", "k2b200_dense_fsa_vec_backward",
+    "k2b200_dense_fsa_vec_from_logits", "k2b200_dense_fsa_vec_from_logits_backward",
     "k2b200_ctc_graph_tmp_bytes", "k2b200_ctc_graph",
     "k2b200_fsa_properties_tmp_bytes", "k2b200_fsa_properties",
     "k2b200_fsa_levels_tmp_bytes", "k2b200_fsa_levels",

@@ -47,10 +47,46 @@ class _DenseFsaVecFunction(torch.autograd.Function):
         return grad, None, None, None, None
 
 
+class _LogSoftmaxDenseFunction(torch.autograd.Function):
+    """scores = layout(log_softmax(logits, dim=-1)): normalisation and layout in one
+    kernel, and one kernel for the gradient w.r.t. the logits."""
+
+    @staticmethod
+    def forward(ctx, logits: torch.Tensor, segments: torch.Tensor,
+                row_splits: torch.Tensor, rows: int, overlapping: bool) -> torch.Tensor:
+        logits = logits.contiguous()
+        N, T, C = logits.shape
+        dev = logits.device
+        scores = torch.empty(rows, C + 1, dtype=torch.float32, device=dev)
+        with torch.cuda.device(dev):
+            _lib.check(_lib.lib.k2b200_dense_fsa_vec_from_logits(
+                _lib.ptr(logits), N, T, C, _lib.ptr(segments), _lib.ptr(row_splits),
+                segments.shape[0], _lib.ptr(scores), rows, _lib.stream_of(dev)))
+        ctx.save_for_backward(segments, row_splits, scores)
+        ctx.shape = (N, T, C)
+        ctx.rows = rows
+        ctx.overlapping = overlapping
+        return scores
+
+    @staticmethod
+    def backward(ctx, grad_scores: torch.Tensor):
+        segments, row_splits, scores = ctx.saved_tensors
+        N, T, C = ctx.shape
+        grad_scores = grad_scores.contiguous()
+        dev = grad_scores.device
+        grad = torch.empty(N, T, C, dtype=torch.float32, device=dev)
+        with torch.cuda.device(dev):
+            _lib.check(_lib.lib.k2b200_dense_fsa_vec_from_logits_backward(
+                _lib.ptr(grad_scores), _lib.ptr(scores), N, T, C, _lib.ptr(segments),
+                _lib.ptr(row_splits), segments.shape[0], ctx.rows, int(ctx.overlapping),
+                _lib.ptr(grad), _lib.stream_of(dev)))
+        return grad, None, None, None, None
+
+
 class DenseFsaVec(object):
 
     def __init__(self, log_probs: torch.Tensor, supervision_segments: torch.Tensor,
-                 allow_truncate: int = 0) -> None:
+                 allow_truncate: int = 0, _logits: bool = False) -> None:
         assert log_probs.ndim == 3
         assert log_probs.dtype == torch.float32
         assert supervision_segments.ndim == 2
@@ -81,9 +117,11 @@ class DenseFsaVec(object):
             meta = torch.from_numpy(np.concatenate([eff.reshape(-1), row_splits])).to(
                 device, non_blocking=True)
             k3 = 3 * seg.shape[0]
-            scores = _DenseFsaVecFunction.apply(log_probs, meta[:k3].view(-1, 3), meta[k3:],
-                                                rows, overlapping)
+            fn = _LogSoftmaxDenseFunction if _logits else _DenseFsaVecFunction
+            scores = fn.apply(log_probs, meta[:k3].view(-1, 3), meta[k3:], rows, overlapping)
         else:
+            if _logits:
+                log_probs = torch.log_softmax(log_probs, dim=-1)
             # host tensors (layout checks, graph preparation): the reference's own
             # formulation with torch ops
             last_frame_indexes = (row_splits[1:] - 1).astype(np.int64)
@@ -98,6 +136,15 @@ class DenseFsaVec(object):
             scores[torch.from_numpy(last_frame_indexes)] = torch.tensor(
                 [0] + [float('-inf')] * C, dtype=log_probs.dtype)
         self._init(scores, row_splits)
+
+    @classmethod
+    def from_logits(cls, logits: torch.Tensor, supervision_segments: torch.Tensor,
+                    allow_truncate: int = 0) -> 'DenseFsaVec':
+        """`DenseFsaVec(torch.log_softmax(logits, dim=-1), supervision_segments,
+        allow_truncate)` without materialising the log-probs: on CUDA the
+        normalisation runs inside the layout kernel (and its adjoint inside the
+        scatter of the gradient)."""
+        return cls(logits, supervision_segments, allow_truncate, _logits=True)
 
     def _init(self, scores: torch.Tensor, h_row_splits: np.ndarray) -> None:
         assert scores.is_contiguous()

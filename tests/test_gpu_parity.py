@@ -387,3 +387,24 @@ def test_layering_of_arbitrary_fsa_vecs(k2):
     if np.any(cyc.arcs[:, 1] <= cyc.arcs[:, 0]):
         with pytest.raises(RuntimeError):
             cyc_arcs.levels()
+
+
+def test_dense_fsa_vec_from_logits_matches_log_softmax(k2):
+    torch.manual_seed(3)
+    dev = "cuda:0"
+    logits = (torch.randn(5, 37, 91, device=dev) * 3.0)
+    segs = torch.tensor([[0, 0, 37], [3, 2, 30], [1, 5, 25], [4, 0, 12], [2, 10, 7]], dtype=torch.int32)
+    a = logits.clone().requires_grad_(True)
+    b = logits.clone().requires_grad_(True)
+    d1 = k2.DenseFsaVec(torch.log_softmax(a, dim=-1), segs)
+    d2 = k2.DenseFsaVec.from_logits(b, segs)
+    assert torch.equal(torch.isinf(d1.scores), torch.isinf(d2.scores))
+    fin = torch.isfinite(d1.scores)
+    assert (d1.scores[fin] - d2.scores[fin]).abs().max().item() <= 2e-6
+    g = torch.randn_like(d1.scores)
+    g[~fin] = 0.0
+    (d1.scores.masked_fill(~fin, 0.0) * g).sum().backward()
+    (d2.scores.masked_fill(~fin, 0.0) * g).sum().backward()
+    assert (a.grad - b.grad).abs().max().item() <= 2e-5
+    # frames outside every segment get no gradient
+    assert float(b.grad[2, :10].abs().max()) == 0.0
