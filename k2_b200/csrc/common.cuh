@@ -69,6 +69,14 @@ struct PhaseTimer {  // records start/stop events when profiling is enabled
   int slot_;
 };
 
+// A second stream per device for kernels that do not depend on what the caller's
+// stream is running (they fill the SMs that a latency-bound recursion leaves mostly
+// idle).  SideFork makes the side stream wait for everything enqueued on `main` so
+// far and returns it; SideJoin makes `main` wait for the side stream.  Both are
+// plain event record/wait pairs, so they are also legal under stream capture.
+int32_t SideFork(cudaStream_t main, cudaStream_t *side);
+int32_t SideJoin(cudaStream_t main);
+
 static inline size_t AlignUp(size_t x, size_t a = 256) { return (x + a - 1) / a * a; }
 
 static inline int CeilDiv(int64_t a, int64_t b) { return (int)((a + b - 1) / b); }

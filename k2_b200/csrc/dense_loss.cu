@@ -1505,16 +1505,28 @@ int32_t k2b200_dense_loss_forward(const k2b200_intersect_args *args, void *works
   const FsaInfo *d_infos = reinterpret_cast<const FsaInfo *>(ws + L.off_infos);
   unsigned char *dense = reinterpret_cast<unsigned char *>(ws + LL.off_dense);
   int32_t *unfit = reinterpret_cast<int32_t *>(ws + L.off_unfit);
-  {
-    PhaseTimer timer(kPhaseDense, stream);  // repacking belongs with the dense matrix
-    const int64_t n_dense = (int64_t)args->rows * LL.pack.cols4;
-    { ExpDense<<<(int)std::min<int64_t>(CeilDiv(n_dense, 256), 148 * 32), 256, 0, stream>>>(
-        args->scores, args->rows, LL.pack, dense); NoteLaunch(); }
-    K2B_FORWARD(LaunchPlanLanes(L, args, ws, stream));
-  }
+  // The repacking does not depend on the Viterbi pass.  It is enqueued on the side
+  // stream AFTER the Viterbi kernels have been launched, so that their CTAs own the
+  // SMs first and the repacking fills in beside them; joined before the recursions
+  // read the packed rows.
+  struct JoinOnExit {  // also on error returns: the caller may free the workspace
+    cudaStream_t main;
+    bool armed;
+    ~JoinOnExit() { if (armed) SideJoin(main); }
+  } join_guard{stream, false};
+  cudaStream_t side;
+  K2B_FORWARD(SideFork(stream, &side));
+  join_guard.armed = true;
+  K2B_FORWARD(LaunchPlanLanes(L, args, ws, stream));
   {
     PhaseTimer timer(kPhaseViterbi, stream);
     K2B_FORWARD(RunViterbi(L, args, ws, stream, /*plan_ready=*/true));
+  }
+  {
+    PhaseTimer timer(kPhaseDense, side);  // repacking belongs with the dense matrix
+    const int64_t n_dense = (int64_t)args->rows * LL.pack.cols4;
+    { ExpDense<<<(int)std::min<int64_t>(CeilDiv(n_dense, 256), 148 * 8), 256, 0, side>>>(
+        args->scores, args->rows, LL.pack, dense); NoteLaunch(); }
   }
   // The lattice is never built, but its size still decides the beam
   // (intersect_dense.cu:300-320).  The grid itself bounds it: count only when the
@@ -1529,6 +1541,8 @@ int32_t k2b200_dense_loss_forward(const k2b200_intersect_args *args, void *works
     K2B_FORWARD(LaunchCutoffs(L, args, ws, beam, stream));
   }
   if (beam_used) *beam_used = beam;
+  join_guard.armed = false;
+  K2B_FORWARD(SideJoin(stream));
   {
     PhaseTimer timer(kPhaseChain, stream);
 #define K2B_CHAIN(DEG, MAXT)                                                              \

@@ -83,6 +83,51 @@ double ReadPhase(int phase, long long *count) {
 }
 
 // ----------------------------------------------------------------------------
+// side stream (one per device, created on first use)
+// ----------------------------------------------------------------------------
+namespace {
+struct SideState {
+  cudaStream_t stream = nullptr;
+  cudaEvent_t fork_ev = nullptr, join_ev = nullptr;
+};
+std::mutex g_side_mutex;
+std::vector<SideState> g_side;
+
+int32_t SideOfCurrentDevice(SideState **out) {
+  int dev = 0;
+  K2B_CUDA_OK(cudaGetDevice(&dev));
+  if ((size_t)dev >= g_side.size()) g_side.resize(dev + 1);
+  SideState &st = g_side[dev];
+  if (st.stream == nullptr) {
+    K2B_CUDA_OK(cudaStreamCreateWithFlags(&st.stream, cudaStreamNonBlocking));
+    K2B_CUDA_OK(cudaEventCreateWithFlags(&st.fork_ev, cudaEventDisableTiming));
+    K2B_CUDA_OK(cudaEventCreateWithFlags(&st.join_ev, cudaEventDisableTiming));
+  }
+  *out = &st;
+  return kOk;
+}
+}  // namespace
+
+int32_t SideFork(cudaStream_t main, cudaStream_t *side) {
+  std::lock_guard<std::mutex> lock(g_side_mutex);
+  SideState *st;
+  K2B_FORWARD(SideOfCurrentDevice(&st));
+  K2B_CUDA_OK(cudaEventRecord(st->fork_ev, main));
+  K2B_CUDA_OK(cudaStreamWaitEvent(st->stream, st->fork_ev, 0));
+  *side = st->stream;
+  return kOk;
+}
+
+int32_t SideJoin(cudaStream_t main) {
+  std::lock_guard<std::mutex> lock(g_side_mutex);
+  SideState *st;
+  K2B_FORWARD(SideOfCurrentDevice(&st));
+  K2B_CUDA_OK(cudaEventRecord(st->join_ev, st->stream));
+  K2B_CUDA_OK(cudaStreamWaitEvent(main, st->join_ev, 0));
+  return kOk;
+}
+
+// ----------------------------------------------------------------------------
 // exclusive sum: reduce tiles -> scan the tile sums in one block -> rescan tiles
 // ----------------------------------------------------------------------------
 constexpr int kScanThreads = 256;
