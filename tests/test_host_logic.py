@@ -116,3 +116,59 @@ def test_shard_utterances_balances_and_keeps_order():
     seg = torch.tensor([[i, 0, d] for i, d in enumerate(durs)], dtype=torch.int32)
     mine, idx = parallel.shard_segments(seg, 2, 1)
     assert mine[:, 2].tolist() == [990, 750, 650, 600]
+
+
+def _host_args(num_states_per, num_arcs_per, n, rows_per, cols, max_degree, sorted_ok=True,
+               shared=0):
+    """A k2b200_intersect_args block whose device pointers are never dereferenced:
+    the sizing / validation entry points only read the host arrays."""
+    import ctypes
+    from k2_b200 import _lib
+    rs1 = (np.arange(n + 1) * num_states_per).astype(np.int32)
+    asp = (np.arange(n + 1) * num_arcs_per).astype(np.int32)
+    lens = np.full(n, rows_per, np.int32)
+    if not sorted_ok:
+        lens[-1] += 3
+    brs = np.concatenate([[0], np.cumsum(lens)]).astype(np.int32)
+    fake = 256  # any non-NULL address
+    args = _lib.IntersectArgs(
+        num_fsas=n, num_states=int(rs1[-1]), num_arcs=int(asp[-1]), a_row_splits1=fake,
+        a_row_splits2=fake, a_arcs=fake, a_in_splits=fake, a_in_arcs=fake,
+        h_a_row_splits1=rs1.ctypes.data, h_a_arc_splits=asp.ctypes.data, scores=fake,
+        rows=int(brs[-1]), cols=cols, num_seqs=n, h_b_row_splits=brs.ctypes.data,
+        h_a_to_b_map=None, output_beam=10.0, max_states=15000000, max_arcs=1 << 30,
+        viterbi_mode=0, a_max_degree=max_degree, a_shared=shared)
+    return args, (rs1, asp, brs)
+
+
+def test_workspace_sizing_and_validation_need_no_gpu():
+    import ctypes
+    from k2_b200 import _lib
+    lib = _lib.lib
+    # a CTC-sized problem: the loss workspace holds the intersect workspace plus the
+    # packed matrix and the alpha / beta grids
+    args, keep = _host_args(101, 250, 8, 201, 501, 3)
+    b1, b2, lv = ctypes.c_size_t(), ctypes.c_size_t(), ctypes.c_int64()
+    assert lib.k2b200_intersect_dense_workspace_bytes(ctypes.byref(args), ctypes.byref(b1),
+                                                      ctypes.byref(lv)) == 0
+    assert lv.value == 8 * 202
+    assert lib.k2b200_dense_loss_workspace_bytes(ctypes.byref(args), ctypes.byref(b2)) == 0
+    grid = 8 * 202 * 101
+    pack = 8 * 201 * (4 * 504 + 8 * 502)
+    assert b2.value >= b1.value + pack + 2 * 16 * grid
+    ok = ctypes.c_int32()
+    assert lib.k2b200_dense_loss_supported(ctypes.byref(args), ctypes.byref(ok)) == 0 and ok.value == 1
+    # a 200 000-state graph is not for the lattice-free path
+    big, keep2 = _host_args(200000, 600000, 2, 101, 501, 12)
+    assert lib.k2b200_dense_loss_supported(ctypes.byref(big), ctypes.byref(ok)) == 0 and ok.value == 0
+    # sequences must be sorted by decreasing length (intersect_dense.cu:168-177)
+    bad, keep3 = _host_args(101, 250, 4, 201, 501, 3, sorted_ok=False)
+    assert lib.k2b200_dense_loss_workspace_bytes(ctypes.byref(bad), ctypes.byref(b2)) != 0
+    assert b"sorted order" in lib.k2b200_last_error()
+    # a_shared with graphs of different sizes is refused
+    sh, keep4 = _host_args(50, 120, 3, 51, 73, 9, shared=1)
+    keep4[0][3] += 1  # last graph has one more state
+    sh.num_states += 1
+    assert lib.k2b200_intersect_dense_workspace_bytes(ctypes.byref(sh), ctypes.byref(b1),
+                                                      ctypes.byref(lv)) != 0
+    assert b"a_shared" in lib.k2b200_last_error()
