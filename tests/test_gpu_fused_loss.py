@@ -141,3 +141,67 @@ def test_ctc_loss_uses_the_same_numbers_either_way():
         out[fused] = (float(loss.detach()), lp.grad.cpu().numpy())
     assert abs(out[True][0] - out[False][0]) <= 1e-6 * abs(out[False][0])
     assert np.abs(out[True][1] - out[False][1]).max() <= 1e-4
+
+
+def _star_graph(rng, fan, tail_states, num_labels):
+    """A graph whose start state has `fan` leaving arcs (more than a lane plan can
+    place when fan > 256), followed by a few random states, all reaching the final
+    state."""
+    rows = []
+    mid = list(range(1, 1 + tail_states))
+    final = 1 + tail_states
+    for k in range(fan):
+        rows.append((0, mid[k % tail_states], int(rng.integers(0, num_labels)), float(rng.normal())))
+    for s in mid:
+        for _ in range(3):
+            d = int(rng.integers(1, final))
+            rows.append((s, d, int(rng.integers(0, num_labels)), float(rng.normal())))
+        rows.append((s, final, -1, float(rng.normal())))
+    rows.sort(key=lambda r: r[0])
+    return rows, final + 1
+
+
+def test_graphs_a_plan_cannot_place_take_the_fallback_kernels():
+    # one graph with a 300-arc state (no lane plan possible: > 32 lanes of 8 arcs)
+    # next to ordinary ones: plan-less graphs go through PersistentViterbi, GridChain
+    # and GridGradWarp while the others keep the planned kernels, in the same call
+    from oracle.common import HostFsaVec, make_arcs
+    rng = np.random.default_rng(17)
+    rs1, rs2, arcs = [0], [0], []
+    for fan in (300, 12, 40):
+        rows, ns = _star_graph(rng, fan, 6, 5)
+        base = len(arcs)
+        src = np.array([r[0] for r in rows])
+        for s in range(ns):
+            rs2.append(base + int(np.sum(src <= s)))
+        arcs.extend(rows)
+        rs1.append(rs1[-1] + ns)
+    r = np.array(arcs, dtype=np.float64)
+    a = HostFsaVec(np.asarray(rs1, np.int32), np.asarray(rs2, np.int32),
+                   make_arcs(r[:, 0].astype(np.int32), r[:, 1].astype(np.int32),
+                             r[:, 2].astype(np.int32), r[:, 3].astype(np.float32)))
+    scores, brs = random_dense(rng, 3, 14, 5, low_rows=False)
+    for beam in (4.0, 30.0):
+        _compare(a, scores, brs, beam, tag=f"star beam {beam}")
+    # the lattice path on the same batch: planned Viterbi for two graphs, the
+    # shared-memory kernel for the third, bit-exact lattice
+    from gpu_util import dense_from_scores, fsa_to_host, host_to_fsa, intersect_raw
+    from util import same_fsa
+    lat, ma, mb = intersect_raw(host_to_fsa(a), dense_from_scores(scores, brs), 30.0, mode=0)
+    same_fsa(fsa_to_host(lat, ma, mb), oracle.intersect_dense(a, scores, brs, 30.0), "star lattice")
+
+
+def test_ctc_graphs_with_more_than_512_states():
+    # the 1024-thread instantiations of the register kernels
+    import k2_b200 as k2
+    from gpu_util import fsa_to_host
+    rng = np.random.default_rng(19)
+    syms = [[int(x) for x in rng.integers(1, 20, size=n)] for n in (300, 280)]
+    graphs = k2.ctc_graph(syms, device=DEV)
+    assert graphs.arcs.num_states > 1024 and max(np.diff(graphs.arcs.h_row_splits1)) > 512
+    T = 330
+    lp = torch.log_softmax(torch.randn(2, T, 20, generator=torch.Generator().manual_seed(1)) * 2, -1)
+    segs = torch.tensor([[0, 0, T], [1, 0, T - 10]], dtype=torch.int32)
+    dense = k2.DenseFsaVec(lp.to(DEV), segs)
+    _compare(fsa_to_host(graphs), dense.scores.cpu().numpy(), dense.h_row_splits, 12.0,
+             tag="long ctc")
