@@ -904,6 +904,166 @@ GridGradWarp(const FsaInfo *__restrict__ infos, const Arc *__restrict__ arcs,
 }
 
 // ---------------------------------------------------------------------------
+// Gradients of sparse lattices (CTC: a few tens of surviving states per frame out
+// of hundreds).  grid = (frame chunks, pairs).  The CTA first compacts the surviving
+// (frame, state) pairs of its frames into a list in shared memory - a coalesced scan
+// of the Viterbi grids by warps, positions from ballots and one shared counter (the
+// order of the list does not matter: the sums are integers) - and then spreads (survivor, arc) items over all its threads, so that the dependent
+// gathers of an arc (destination scores, beta, factors) of many arcs are in flight
+// at once instead of one warp walking one frame.  Same fixed-point sums as
+// GridGradWarp.
+// ---------------------------------------------------------------------------
+constexpr int kItemThreads = 256;
+constexpr int kItemCap = 1024;  // list entries; at least the states of one frame
+
+__global__ void __launch_bounds__(kItemThreads)
+GridGradItems(const FsaInfo *__restrict__ infos, const Arc *__restrict__ arcs,
+              const ArcFactor *__restrict__ arc_factors,
+              const int32_t *__restrict__ a_row_splits2, const unsigned char *__restrict__ dense,
+              DensePack dp, const float *__restrict__ vfwd, const float *__restrict__ vbwd,
+              const float *__restrict__ cutoffs, const ProbState *__restrict__ alpha,
+              const ProbState *__restrict__ beta, const double *__restrict__ tot_grad,
+              int32_t tot_grad_stride, float *__restrict__ grad_a, float *__restrict__ grad_b,
+              int32_t frames_per_cta, int32_t lanes_log2, int32_t ga_in_smem,
+              int32_t exclusive_rows) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  __shared__ int32_t list_count;
+  const int32_t i = blockIdx.y;
+  const FsaInfo f = infos[i];
+  const int32_t S = f.num_states, A = f.num_arcs, Tk = f.tk, cols = dp.cols;
+  const int32_t u0 = blockIdx.x * frames_per_cta;
+  if (S == 0 || u0 >= Tk) return;
+  const int32_t nf = min(u0 + frames_per_cta, Tk) - u0;
+  const int tid = threadIdx.x, nt = blockDim.x, lane = tid & 31, warp = tid >> 5,
+            nw = nt >> 5;
+  double *it_am = reinterpret_cast<double *>(smem_raw);              // [kItemCap]
+  float *it_fu = reinterpret_cast<float *>(it_am + kItemCap);        // [kItemCap]
+  int32_t *it_ae = reinterpret_cast<int32_t *>(it_fu + kItemCap);    // [kItemCap]
+  int32_t *it_su = it_ae + kItemCap;                                 // state | frame << 16
+  uint32_t *gb = reinterpret_cast<uint32_t *>(it_su + kItemCap);     // [frames_per_cta][cols]
+  uint32_t *ga = gb + (((size_t)frames_per_cta * cols + 3) & ~(size_t)3);  // [A] if ga_in_smem
+  const ProbState *al = alpha + f.grid_off, *be = beta + f.grid_off;
+  const ProbState z = al[(int64_t)Tk * S + (S - 1)];
+  if (z.m == 0.0) return;  // no path survives: all gradients are zero
+  const double zinv = 1.0 / z.m;
+  const int32_t zk = -z.e;
+  const float tg = (float)tot_grad[(int64_t)i * tot_grad_stride];
+  for (int32_t k = tid; k < nf * cols; k += nt) gb[k] = 0u;
+  if (ga_in_smem)
+    for (int32_t k = tid; k < A; k += nt) ga[k] = 0u;
+  const float cutoff = cutoffs[i];
+  const float *fgrid = vfwd + f.grid_off, *bgrid = vbwd + f.grid_off;
+  const Arc *my_arcs = arcs + f.arc_off;
+  const ArcFactor *my_factors = arc_factors + f.arc_off;
+  const int32_t *splits = a_row_splits2 + f.state_off;
+  const int32_t lg = lanes_log2, G = 1 << lg;
+  // frames per round: all of them if their survivors fit the list (the usual case),
+  // else as many as fit whatever survives
+  const int32_t words = (S + 31) >> 5, safe_step = max(1, kItemCap / S);
+  int32_t step = nf;
+  for (int32_t f0 = 0; f0 < nf;) {
+    const int32_t f1 = min(nf, f0 + step);
+    if (tid == 0) list_count = 0;
+    __syncthreads();
+    // ---- compact the survivors of frames f0 .. f1 - 1: one 32-state word per warp and
+    // trip, four trips' loads issued together ---------------------------------------
+    const int32_t nwords = (f1 - f0) * words;
+    for (int32_t w0 = warp; w0 < nwords; w0 += 4 * nw) {
+      float fu4[4], bu4[4];
+      int32_t fr4[4], q4[4];
+#pragma unroll
+      for (int r = 0; r < 4; ++r) {
+        const int32_t w = w0 + r * nw;
+        const int32_t fr = f0 + w / words, q = (w % words) * 32 + lane;
+        fr4[r] = fr;
+        q4[r] = q;
+        const bool in = w < nwords && q < S;
+        const int64_t gi = (int64_t)(u0 + fr) * S + q;
+        fu4[r] = in ? fgrid[gi] : -INFINITY;
+        bu4[r] = in ? bgrid[gi] : -INFINITY;
+      }
+#pragma unroll
+      for (int r = 0; r < 4; ++r) {
+        const bool keep = __fadd_rn(fu4[r], bu4[r]) > cutoff;
+        const uint32_t m = __ballot_sync(0xffffffffu, keep);
+        if (m == 0) continue;  // warp-uniform
+        int32_t base = 0;
+        if (lane == 0) base = atomicAdd(&list_count, __popc(m));
+        base = __shfl_sync(0xffffffffu, base, 0);
+        if (keep) {
+          const int32_t p = base + __popc(m & ((1u << lane) - 1u));
+          if (p < kItemCap) {
+            const ProbState a = al[(int64_t)(u0 + fr4[r]) * S + q4[r]];
+            it_am[p] = a.m * zinv;
+            it_ae[p] = a.e + zk;
+            it_fu[p] = fu4[r];
+            it_su[p] = q4[r] | (fr4[r] << 16);
+          }
+        }
+      }
+    }
+    __syncthreads();
+    const int32_t survivors = list_count;
+    if (survivors > kItemCap) {  // uniform: does not fit, take fewer frames (always fits)
+      step = safe_step;
+      __syncthreads();  // everyone has read list_count before it is reset
+      continue;
+    }
+    // ---- (survivor, lane) items over all threads -------------------------------------
+    const int32_t items = survivors << lg;
+    for (int32_t idx = tid; idx < items; idx += nt) {
+      const int32_t it = idx >> lg, sub = idx & (G - 1);
+      const double am = it_am[it];
+      if (am == 0.0) continue;
+      const int32_t sq = it_su[it] & 0xffff, fr = it_su[it] >> 16, ae = it_ae[it];
+      const float fs = it_fu[it];
+      const int64_t nxt = (int64_t)(u0 + fr + 1) * S;
+      const unsigned char *rec = dense + ((int64_t)f.row0 + u0 + fr) * dp.pitch;
+      const float *lprow = PackLp(rec);
+      const double *prow = PackP(rec, dp);
+      uint32_t *gbrow = gb + (size_t)fr * cols;
+      const int32_t k1 = splits[sq + 1] - f.arc_off;
+      for (int32_t k = splits[sq] - f.arc_off + sub; k < k1; k += G) {
+        const Arc arc = my_arcs[k];
+        const int32_t c = arc.label + 1;
+        if (c < 0 || c >= cols) continue;
+        const float fn = fgrid[nxt + arc.dest], bn = bgrid[nxt + arc.dest];
+        if (!(__fadd_rn(fn, bn) > cutoff)) continue;
+        const float sc = __fadd_rn(arc.score, lprow[c]);
+        if (!(__fadd_rn(__fadd_rn(fs, sc), bn) > cutoff)) continue;
+        const ProbState b = be[nxt + arc.dest];
+        const ArcFactor af = my_factors[k];
+        int32_t e1;
+        const double m1 = SplitExp(am * af.f * prow[c], &e1);
+        const double prod = m1 * b.m;
+        if (prod == 0.0) continue;
+        const float post = (float)(prod * Pow2Clamped(e1 + ae + af.k + b.e));
+        atomicAdd(&gbrow[c], __float2uint_rn(post * 2147483648.0f));
+        if (ga_in_smem) atomicAdd(&ga[k], __float2uint_rn(post * 67108864.0f));
+        else atomicAdd(&grad_a[f.arc_off + f.arc_out_off + k], tg * post);
+      }
+    }
+    __syncthreads();
+    f0 = f1;
+  }
+  float *grow = grad_b + ((int64_t)f.row0 + u0) * cols;
+  for (int32_t k = tid; k < nf * cols; k += nt) {
+    const uint32_t fixed = gb[k];
+    if (fixed != 0u) {
+      const float v = tg * ((float)fixed * (1.0f / 2147483648.0f));
+      if (exclusive_rows) grow[k] = v; else atomicAdd(&grow[k], v);
+    }
+  }
+  if (ga_in_smem)
+    for (int32_t k = tid; k < A; k += nt) {
+      const uint32_t fixed = ga[k];
+      if (fixed != 0u)
+        atomicAdd(&grad_a[f.arc_off + f.arc_out_off + k],
+                  tg * ((float)fixed * (1.0f / 67108864.0f)));
+    }
+}
+
+// ---------------------------------------------------------------------------
 // Gradients with planned lanes, for the graphs PlanLanes placed (dense lattices:
 // most states and a good part of the arcs survive on every frame).  grid = (frame
 // chunks, pairs).  The CTA first copies everything its frames can touch into shared
@@ -1423,6 +1583,43 @@ static int32_t LaunchGrad(const LossLayout &LL, const k2b200_intersect_args *arg
   return kOk;
 }
 
+static int32_t LaunchGradItems(const LossLayout &LL, const k2b200_intersect_args *args, char *ws,
+                               const double *tot_grad, int32_t stride, float *grad_a,
+                               float *grad_b, cudaStream_t stream) {
+  const Layout &L = LL.base;
+  // few frames per CTA: the shared memory of a CTA decides how many CTAs an SM holds,
+  // and the gathers want many warps in flight
+  int32_t frames = 16;
+  while (frames > 4 && sizeof(float) * (size_t)frames * args->cols > 16 * 1024) frames >>= 1;
+  const size_t list_bytes = (size_t)kItemCap * (8 + 4 + 4 + 4);
+  const size_t gb_bytes = sizeof(float) * (((size_t)frames * args->cols + 3) & ~(size_t)3);
+  const size_t ga_bytes = sizeof(float) * (size_t)L.max_arcs;
+  size_t smem = list_bytes + gb_bytes;
+  const int32_t ga_in_smem = smem + ga_bytes <= 100 * 1024;
+  if (ga_in_smem) smem += ga_bytes;
+  K2B_REQUIRE(smem <= kChainSmemBudget, "too many columns for the fused loss path");
+  K2B_CUDA_OK(cudaFuncSetAttribute(GridGradItems, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                   (int)smem));
+  int32_t mean_deg =
+      args->num_states > 0 ? (args->num_arcs + args->num_states - 1) / args->num_states : 1;
+  int32_t lg = 0;
+  while ((1 << lg) < mean_deg && lg < 5) ++lg;
+  dim3 grid(CeilDiv(L.max_tk, frames), args->num_fsas);
+  { GridGradItems<<<grid, kItemThreads, smem, stream>>>(
+      reinterpret_cast<const FsaInfo *>(ws + L.off_infos),
+      reinterpret_cast<const Arc *>(args->a_arcs),
+      reinterpret_cast<const ArcFactor *>(ws + LL.off_arc_factors), args->a_row_splits2,
+      reinterpret_cast<const unsigned char *>(ws + LL.off_dense), LL.pack,
+      reinterpret_cast<const float *>(ws + L.off_fwd),
+      reinterpret_cast<const float *>(ws + L.off_bwd),
+      reinterpret_cast<const float *>(ws + L.off_cutoffs),
+      reinterpret_cast<const ProbState *>(ws + LL.off_alpha),
+      reinterpret_cast<const ProbState *>(ws + LL.off_beta), tot_grad, stride, grad_a, grad_b,
+      frames, lg, ga_in_smem, LL.exclusive_rows ? 1 : 0); NoteLaunch(); }
+  K2B_CUDA_OK(cudaGetLastError());
+  return kOk;
+}
+
 static int32_t LaunchGradLanes(const LossLayout &LL, const k2b200_intersect_args *args, char *ws,
                                const double *tot_grad, int32_t stride, float *grad_a,
                                float *grad_b, cudaStream_t stream) {
@@ -1599,6 +1796,9 @@ int32_t k2b200_dense_loss_backward(const k2b200_intersect_args *args, void *work
     K2B_FORWARD(LaunchGradLanes(LL, args, ws, tot_grad, tot_grad_stride, grad_a, grad_b, stream));
     only_noplan = reinterpret_cast<const int32_t *>(ws + L.off_unfit);
   }
+  // register-lane graphs of some size (CTC): compacted survivor list
+  if (LL.identity && L.max_states > 256 && L.max_states <= 1024)
+    return LaunchGradItems(LL, args, ws, tot_grad, tot_grad_stride, grad_a, grad_b, stream);
   // small graphs: stage level u + 1 per warp; large ones: gather
   if (L.max_states <= 256)
     return LaunchGrad<true>(LL, args, ws, tot_grad, tot_grad_stride, grad_a, grad_b, only_noplan,
