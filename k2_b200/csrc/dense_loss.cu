@@ -60,15 +60,20 @@ struct __align__(16) ArcFactor {
   int32_t pad;
 };
 
+// *low_flag is set when some finite score is below `low` (the shared-exponent
+// recursion then leaves the whole batch to the per-state-exponent kernel).
 __global__ void ExpDense(const float *__restrict__ scores, int64_t rows, DensePack d,
-                         unsigned char *__restrict__ out) {
+                         unsigned char *__restrict__ out, float low,
+                         int32_t *__restrict__ low_flag) {
   const int64_t n = rows * d.cols4;
+  bool found = false;
   for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < n;
        idx += (int64_t)gridDim.x * blockDim.x) {
     const int64_t r = idx / d.cols4;
     const int32_t c = (int32_t)(idx - r * d.cols4);
     unsigned char *rec = out + r * d.pitch;
     const float lp = c < d.cols ? scores[r * d.cols + c] : -INFINITY;
+    found |= lp < low && lp != -INFINITY;
     reinterpret_cast<float *>(rec)[c] = lp;
     if (c < d.cols2) {
       double p = exp((double)lp);
@@ -76,6 +81,7 @@ __global__ void ExpDense(const float *__restrict__ scores, int64_t rows, DensePa
       reinterpret_cast<double *>(rec + 4 * d.cols4)[c] = p;
     }
   }
+  if (__any_sync(0xffffffffu, found) && (threadIdx.x & 31) == 0) atomicOr(low_flag, 1);
 }
 
 // t = m * 2^e with m in [1,2) from a positive normal double; (0, kZeroExp) for 0.
@@ -130,17 +136,18 @@ static LaneSmem PlanLaneSmem(const Layout &L, const DensePack &d, int group) {
 // Limits of the shared-exponent arithmetic below; outside them a graph is handed
 // to the per-state-exponent kernel.
 constexpr float kMaxAbsArcScore = 80.0f;   // |arc score| of every arc with a finite score
-constexpr float kMinDenseScore = -200.0f;  // dense score of every surviving arc
+constexpr float kMinDenseScore = -200.0f;  // every finite dense score
 constexpr int32_t kMinExponent = -480;     // binary exponent of every non-zero stored value
 
 // ---------------------------------------------------------------------------
-// The alpha / beta recursion.  grid = (2 directions, pairs), one CTA walks all
-// frames of its pair.  Per frame three bulk copies (issued kU - 1 frames ahead by
+// The alpha / beta recursion for graphs whose states have at most four arcs each
+// way (CTC): one thread per state, its arcs in registers.  grid = (2 directions,
+// pairs), one CTA walks all frames of its pair.  Per frame three bulk copies (issued kU - 1 frames ahead by
 // thread 0, completion on one mbarrier) bring the packed dense row and the two
 // Viterbi rows of the level into a shared-memory ring of kU slots; every lane runs
 // the reference's pruning test (intersect_dense.cu:430-470) on its arcs with the
-// same fp32 expressions and adds the survivors' alpha[src] * exp(w) * exp(lp); the
-// lanes of a state merge by shuffles.  The frame loop is unrolled by kU, so ring
+// same fp32 expressions and adds the survivors' alpha[src] * exp(w) * exp(lp).
+// The frame loop is unrolled by kU, so ring
 // slots and buffers are compile-time constants.  Nothing is prefetched through
 // registers: global loads kept in flight across frames made every frame wait a
 // full memory latency (the scoreboards a load waits on are shared counters).
@@ -169,14 +176,14 @@ GridChainLanes(const FsaInfo *__restrict__ infos, int32_t n, const Arc *__restri
                DensePack dp, const float *__restrict__ vfwd, const float *__restrict__ vbwd,
                const float *__restrict__ cutoffs, ProbState *__restrict__ alpha,
                ProbState *__restrict__ beta, double *__restrict__ tot,
-               const int32_t *__restrict__ plan, int32_t *__restrict__ unfit, LaneSmem sm) {
+               int32_t *__restrict__ unfit, const int32_t *__restrict__ low_flag,
+               LaneSmem sm) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   __shared__ __align__(8) uint64_t full[kU];
   __shared__ int32_t emax;  // largest exponent among the values of a group's last level
   constexpr int32_t kNone = INT32_MIN;
   const int32_t i = blockIdx.y;
   const int dir = blockIdx.x;
-  if (plan != nullptr && (unfit[i] & 1)) return;  // no plan for this graph
   const FsaInfo f = infos[i];
   const int32_t S = f.num_states, Tk = f.tk, cols = dp.cols;
   const int tid = threadIdx.x, nt = blockDim.x;
@@ -192,22 +199,14 @@ GridChainLanes(const FsaInfo *__restrict__ infos, int32_t n, const Arc *__restri
   float *oth = reinterpret_cast<float *>(pv + 2 * s_pad);             // [2][s_pad]
 
   const bool producer = tid == 0;  // issues the bulk copies
-  int32_t s = -1, g = 0, G = 1;
-  if (plan != nullptr) {
-    const int32_t code = plan[((int64_t)dir * n + i) * kLaneThreads + tid];
-    if (code >= 0) {
-      s = code & 0xffff;
-      g = (code >> 16) & 0xff;
-      G = code >> 24;
-    }
-  } else if (tid < S) {
-    s = tid;
-  }
+  const int32_t s = tid < S ? tid : -1;  // one thread per state
   // ---- this lane's arcs: dir 0 arcs entering s (other end = source), dir 1 leaving
   int32_t other_col[kDeg];  // other-end state | column << 16
   float w[kDeg];            // arc score, -inf for an unused slot
   double ew[kDeg];          // exp(w)
-  bool risky = false;       // something is outside the limits of this arithmetic
+  // something is outside the limits of this arithmetic (kMinDenseScore is checked
+  // on the whole matrix when it is repacked)
+  bool risky = *low_flag != 0;
 #pragma unroll
   for (int j = 0; j < kDeg; ++j) {
     other_col[j] = cols << 16;
@@ -219,7 +218,7 @@ GridChainLanes(const FsaInfo *__restrict__ infos, int32_t n, const Arc *__restri
     const int32_t a0 = gsplits[f.state_off + s], a1 = gsplits[f.state_off + s + 1];
 #pragma unroll
     for (int j = 0; j < kDeg; ++j) {
-      const int32_t k = a0 + g + j * G;
+      const int32_t k = a0 + j;
       if (k < a1) {
         const Arc arc = arcs[dir == 0 ? in_arcs[k] : k];
         const int32_t c = arc.label + 1;
@@ -344,27 +343,16 @@ GridChainLanes(const FsaInfo *__restrict__ infos, int32_t n, const Arc *__restri
 #pragma unroll
         for (int j = 0; j < kDeg; ++j) {
           const int32_t o_idx = other_col[j] & 0xffff, c = other_col[j] >> 16;
-          const float lp = lprow[c];
-          const float sc = __fadd_rn(w[j], lp);
+          const float sc = __fadd_rn(w[j], lprow[c]);
           const float o = po[o_idx];
           const float through = dir == 0 ? __fadd_rn(__fadd_rn(o, sc), bu)
                                          : __fadd_rn(__fadd_rn(fu, sc), o);
-          if (keep && through > cutoff) {
-            sum += prev[o_idx] * ew[j] * prow[c];
-            risky |= lp < kMinDenseScore;
-          }
-        }
-        if (plan != nullptr) {  // uniform: the lanes of a state add up in lane g == 0
-#pragma unroll
-          for (int32_t d = 16; d > 0; d >>= 1) {
-            const double so = __shfl_down_sync(0xffffffffu, sum, d);
-            if (g + d < G) sum += so;
-          }
+          if (keep && through > cutoff) sum += prev[o_idx] * ew[j] * prow[c];
         }
       }
       const double v = u == 0 ? sum * scale : sum;
       const int32_t vhi = __double2hiint(v);  // v >= 0: the exponent is vhi >> 20
-      if (s >= 0 && g == 0) {
+      if (s >= 0) {
         cur[s] = v;
         co[s] = keep ? (dir == 0 ? fu : bu) : -INFINITY;
         if (keep || t == Tk) {  // pruned states of the grid are read on the last level only
@@ -379,7 +367,7 @@ GridChainLanes(const FsaInfo *__restrict__ infos, int32_t n, const Arc *__restri
       }
       pos += step_stride;
       if (u == kU - 1) {  // the next group renormalises by this level's largest value
-        int32_t ex = (s >= 0 && g == 0 && v != 0.0) ? (vhi >> 20) - 1023 : kNone;
+        int32_t ex = (s >= 0 && v != 0.0) ? (vhi >> 20) - 1023 : kNone;
         ex = __reduce_max_sync(0xffffffffu, ex);
         if ((tid & 31) == 0 && ex != kNone) atomicMax(&emax, ex);
       }
@@ -401,7 +389,7 @@ GridChainLanes(const FsaInfo *__restrict__ infos, int32_t n, const Arc *__restri
     if (tid == 0) atomicOr(&unfit[i], 2);
     return;
   }
-  if (dir == 0 && s == S - 1 && g == 0)
+  if (dir == 0 && s == S - 1)
     tot[i] = last == 0.0 ? -INFINITY : log(last) + (double)K * 0.69314718055994530942;
 }
 
@@ -1430,7 +1418,7 @@ GridChain(const FsaInfo *__restrict__ infos, const Arc *__restrict__ arcs,
 struct LossLayout {
   Layout base;
   DensePack pack;
-  size_t off_dense, off_arc_factors, off_alpha, off_beta, off_masks, total_bytes;
+  size_t off_dense, off_arc_factors, off_alpha, off_beta, off_masks, off_flags, total_bytes;
   bool exclusive_rows;
   int32_t k_deg;      // arcs per lane of the lane kernel
   bool identity;      // every degree <= k_deg: thread s owns state s, no plan
@@ -1455,6 +1443,7 @@ static int32_t MakeLossLayout(const k2b200_intersect_args *a, LossLayout *LL) {
   LL->off_beta = take(sizeof(ProbState) * (size_t)LL->base.grid_elems);
   // arc survival bytes, planned graphs only: [2 directions][levels][lanes]
   LL->off_masks = take(LL->identity ? 0 : (size_t)2 * LL->base.total_levels * kLaneThreads + 16);
+  LL->off_flags = take(sizeof(int32_t));
   LL->total_bytes = off;
   // two graphs on one sequence write the same rows of the dense gradient
   LL->exclusive_rows = true;
@@ -1492,8 +1481,8 @@ static int32_t LaunchChainLanes(const LossLayout &LL, const k2b200_intersect_arg
       reinterpret_cast<const float *>(ws + L.off_cutoffs),
       reinterpret_cast<ProbState *>(ws + LL.off_alpha),
       reinterpret_cast<ProbState *>(ws + LL.off_beta), tot,
-      LL.identity ? nullptr : reinterpret_cast<const int32_t *>(ws + L.off_plan),
-      reinterpret_cast<int32_t *>(ws + L.off_unfit), ls); NoteLaunch(); }
+      reinterpret_cast<int32_t *>(ws + L.off_unfit),
+      reinterpret_cast<const int32_t *>(ws + LL.off_flags), ls); NoteLaunch(); }
   K2B_CUDA_OK(cudaGetLastError());
   return kOk;
 }
@@ -1711,6 +1700,7 @@ int32_t k2b200_dense_loss_forward(const k2b200_intersect_args *args, void *works
     bool armed;
     ~JoinOnExit() { if (armed) SideJoin(main); }
   } join_guard{stream, false};
+  K2B_CUDA_OK(cudaMemsetAsync(ws + LL.off_flags, 0, sizeof(int32_t), stream));
   cudaStream_t side;
   K2B_FORWARD(SideFork(stream, &side));
   join_guard.armed = true;
@@ -1723,7 +1713,8 @@ int32_t k2b200_dense_loss_forward(const k2b200_intersect_args *args, void *works
     PhaseTimer timer(kPhaseDense, side);  // repacking belongs with the dense matrix
     const int64_t n_dense = (int64_t)args->rows * LL.pack.cols4;
     { ExpDense<<<(int)std::min<int64_t>(CeilDiv(n_dense, 256), 148 * 8), 256, 0, side>>>(
-        args->scores, args->rows, LL.pack, dense); NoteLaunch(); }
+        args->scores, args->rows, LL.pack, dense, kMinDenseScore,
+        reinterpret_cast<int32_t *>(ws + LL.off_flags)); NoteLaunch(); }
   }
   // The lattice is never built, but its size still decides the beam
   // (intersect_dense.cu:300-320).  The grid itself bounds it: count only when the
