@@ -347,7 +347,10 @@ GridChainLanes(const FsaInfo *__restrict__ infos, int32_t n, const Arc *__restri
           const float o = po[o_idx];
           const float through = dir == 0 ? __fadd_rn(__fadd_rn(o, sc), bu)
                                          : __fadd_rn(__fadd_rn(fu, sc), o);
-          if (keep && through > cutoff) sum += prev[o_idx] * ew[j] * prow[c];
+          // computed for every arc of the warp and selected: cheaper than a divergent
+          // branch per arc
+          const double term = prev[o_idx] * ew[j] * prow[c];
+          sum += (keep && through > cutoff) ? term : 0.0;
         }
       }
       const double v = u == 0 ? sum * scale : sum;
