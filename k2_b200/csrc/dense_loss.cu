@@ -293,8 +293,11 @@ GridChainLanes(const FsaInfo *__restrict__ infos, int32_t n, const Arc *__restri
   int32_t K = 0;  // exponent shared by the stored values
   unsigned parity = 0;
   uint32_t rec_off = 0;  // ring offset of the frame's slot
-  // index of the first float of this lane's state in a staged Viterbi row
-  int64_t lv_elem = first * S;  // grid element where the row of step t starts
+  // A staged Viterbi row starts `skip` floats into its 16-byte aligned range; the
+  // two grids have the same layout, so one value serves both.  It advances by S
+  // (mod 4) per step.
+  int32_t skip = (int32_t)(((reinterpret_cast<uintptr_t>(fgrid) >> 2) + (uintptr_t)(first * S)) & 3);
+  const int32_t skip_step = (int32_t)(step_stride & 3);
   bool gave_up = false;
   for (int32_t t0 = 1; t0 <= Tk && !gave_up; t0 += kU) {
 #pragma unroll
@@ -330,13 +333,9 @@ GridChainLanes(const FsaInfo *__restrict__ infos, int32_t n, const Arc *__restri
       const unsigned char *rec = ring + rec_off;
       const float *lprow = PackLp(rec);
       const double *prow = PackP(rec, dp);
-      // this lane's Viterbi scores: the rows start (address mod 16) / 4 floats into
-      // their staged ranges
-      const int32_t f_skip = (int32_t)((reinterpret_cast<uintptr_t>(fgrid + lv_elem) & 15) >> 2);
-      const int32_t b_skip = (int32_t)((reinterpret_cast<uintptr_t>(bgrid + lv_elem) & 15) >> 2);
-      const float fu = reinterpret_cast<const float *>(rec + dp.pitch)[f_skip + s_ld];
-      const float bu = reinterpret_cast<const float *>(rec + dp.pitch + sm.vrow)[b_skip + s_ld];
-      lv_elem += step_stride;
+      const float fu = reinterpret_cast<const float *>(rec + dp.pitch)[skip + s_ld];
+      const float bu = reinterpret_cast<const float *>(rec + dp.pitch + sm.vrow)[skip + s_ld];
+      skip = (skip + skip_step) & 3;
       const bool keep = s >= 0 && __fadd_rn(fu, bu) > cutoff;
       double sum = 0.0;
       if (__any_sync(0xffffffffu, keep)) {  // most warps of a sparse lattice skip this
