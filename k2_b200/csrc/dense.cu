@@ -22,56 +22,56 @@ __device__ __forceinline__ int32_t SegmentOfRow(const int32_t *__restrict__ row_
   return lo;
 }
 
-// One CTA per score row.  segments: [num_segs, 3] = (sequence, start_frame, duration
-// after truncation).
-__global__ void __launch_bounds__(128)
+// One warp per score row (no block-level synchronisation: the rows are short and
+// there are tens of thousands of them).  segments: [num_segs, 3] = (sequence,
+// start_frame, duration after truncation).
+constexpr int kRowsPerCta = 8;
+
+// Row of log_probs viewed as [N*T, C] that score row r copies, -1 for a final row.
+__device__ __forceinline__ int64_t SourceRow(const int32_t *__restrict__ segments,
+                                             const int32_t *__restrict__ row_splits,
+                                             int32_t num_segs, int64_t T, int32_t r) {
+  const int32_t k = SegmentOfRow(row_splits, num_segs, r);
+  const int32_t t = r - row_splits[k], dur = row_splits[k + 1] - row_splits[k] - 1;
+  return t < dur ? (int64_t)segments[3 * k] * T + segments[3 * k + 1] + t : -1;
+}
+
+__global__ void __launch_bounds__(32 * kRowsPerCta)
 DenseFill(const float *__restrict__ log_probs, int64_t T, int32_t C,
           const int32_t *__restrict__ segments, const int32_t *__restrict__ row_splits,
-          int32_t num_segs, float *__restrict__ scores) {
-  const int32_t r = blockIdx.x;
-  __shared__ int64_t src_row;  // row of log_probs viewed as [N*T, C], -1 for a final row
-  if (threadIdx.x == 0) {
-    const int32_t k = SegmentOfRow(row_splits, num_segs, r);
-    const int32_t t = r - row_splits[k], dur = row_splits[k + 1] - row_splits[k] - 1;
-    src_row = t < dur ? (int64_t)segments[3 * k] * T + segments[3 * k + 1] + t : -1;
-  }
-  __syncthreads();
+          int32_t num_segs, int32_t rows, float *__restrict__ scores) {
+  const int32_t r = blockIdx.x * kRowsPerCta + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  if (r >= rows) return;
+  const int64_t src = SourceRow(segments, row_splits, num_segs, T, r);
   float *out = scores + (int64_t)r * (C + 1);
-  const int64_t src = src_row;
   if (src >= 0) {
     const float *in = log_probs + src * C;
-    if (threadIdx.x == 0) out[0] = -INFINITY;
-    for (int32_t c = threadIdx.x; c < C; c += blockDim.x) out[1 + c] = __ldg(in + c);
+    if (lane == 0) out[0] = -INFINITY;
+    for (int32_t c = lane; c < C; c += 32) out[1 + c] = __ldg(in + c);
   } else {
-    if (threadIdx.x == 0) out[0] = 0.0f;
-    for (int32_t c = threadIdx.x; c < C; c += blockDim.x) out[1 + c] = -INFINITY;
+    if (lane == 0) out[0] = 0.0f;
+    for (int32_t c = lane; c < C; c += 32) out[1 + c] = -INFINITY;
   }
 }
 
 // grad_log_probs[seq, start + t, c] (+)= grad_scores[row, 1 + c].
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(32 * kRowsPerCta)
 DenseBackward(const float *__restrict__ grad_scores, int64_t T, int32_t C,
               const int32_t *__restrict__ segments, const int32_t *__restrict__ row_splits,
-              int32_t num_segs, int32_t use_atomics, float *__restrict__ grad_log_probs) {
-  const int32_t r = blockIdx.x;
-  __shared__ int64_t dst_row;
-  if (threadIdx.x == 0) {
-    const int32_t k = SegmentOfRow(row_splits, num_segs, r);
-    const int32_t t = r - row_splits[k], dur = row_splits[k + 1] - row_splits[k] - 1;
-    dst_row = t < dur ? (int64_t)segments[3 * k] * T + segments[3 * k + 1] + t : -1;
-  }
-  __syncthreads();
-  const int64_t dst = dst_row;
+              int32_t num_segs, int32_t rows, int32_t use_atomics,
+              float *__restrict__ grad_log_probs) {
+  const int32_t r = blockIdx.x * kRowsPerCta + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  if (r >= rows) return;
+  const int64_t dst = SourceRow(segments, row_splits, num_segs, T, r);
   if (dst < 0) return;
   const float *in = grad_scores + (int64_t)r * (C + 1) + 1;
   float *out = grad_log_probs + dst * C;
   if (use_atomics) {
-    for (int32_t c = threadIdx.x; c < C; c += blockDim.x) atomicAdd(out + c, in[c]);
+    for (int32_t c = lane; c < C; c += 32) atomicAdd(out + c, in[c]);
   } else {
-    for (int32_t c = threadIdx.x; c < C; c += blockDim.x) out[c] = in[c];
+    for (int32_t c = lane; c < C; c += 32) out[c] = in[c];
   }
 }
-
 
 // ---------------------------------------------------------------------------
 // log_softmax fused with the layout: scores = layout(log_softmax(logits, dim=-1)).
@@ -172,8 +172,9 @@ int32_t k2b200_dense_fsa_vec_fill(const float *log_probs, int64_t num_seqs, int6
   K2B_REQUIRE(num_segs > 0 && num_classes > 0 && rows > 0, "empty DenseFsaVec");
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
   PhaseTimer timer(kPhaseDense, s);
-  { DenseFill<<<rows, 128, 0, s>>>(log_probs, num_frames, num_classes, segments, row_splits,
-                                   num_segs, scores); NoteLaunch(); }
+  { DenseFill<<<CeilDiv(rows, kRowsPerCta), 32 * kRowsPerCta, 0, s>>>(
+      log_probs, num_frames, num_classes, segments, row_splits, num_segs, rows, scores);
+    NoteLaunch(); }
   K2B_CUDA_OK(cudaGetLastError());
   return kOk;
 }
@@ -189,9 +190,9 @@ int32_t k2b200_dense_fsa_vec_backward(const float *grad_scores, int64_t num_seqs
   K2B_CUDA_OK(cudaMemsetAsync(grad_log_probs, 0,
                               sizeof(float) * (size_t)num_seqs * num_frames * num_classes, s));
   if (rows > 0)
-    { DenseBackward<<<rows, 128, 0, s>>>(grad_scores, num_frames, num_classes, segments,
-                                         row_splits, num_segs, overlapping, grad_log_probs);
-      NoteLaunch(); }
+    { DenseBackward<<<CeilDiv(rows, kRowsPerCta), 32 * kRowsPerCta, 0, s>>>(
+        grad_scores, num_frames, num_classes, segments, row_splits, num_segs, rows, overlapping,
+        grad_log_probs); NoteLaunch(); }
   K2B_CUDA_OK(cudaGetLastError());
   return kOk;
 }
