@@ -77,81 +77,63 @@ DenseBackward(const float *__restrict__ grad_scores, int64_t T, int32_t C,
 // log_softmax fused with the layout: scores = layout(log_softmax(logits, dim=-1)).
 // The reference's callers run torch.log_softmax over [N, T, C] and then build the
 // DenseFsaVec from the result (k2/python/k2/dense_fsa_vec.py:101-133): two full
-// passes over the matrix forward and two more backward.  Here one CTA per score row
+// passes over the matrix forward and two more backward.  Here one warp per score row
 // normalises its row while it lays it out, and the backward applies
 //   dL/dlogit[c] = g[c] - softmax[c] * sum_c' g[c'],   softmax = exp(scores)
 // while it scatters.
 // ---------------------------------------------------------------------------
-__device__ __forceinline__ float BlockReduce(float v, bool take_max, float *red) {
+__device__ __forceinline__ float WarpMax(float v) {
 #pragma unroll
-  for (int d = 16; d > 0; d >>= 1) {
-    const float o = __shfl_xor_sync(0xffffffffu, v, d);
-    v = take_max ? fmaxf(v, o) : v + o;
-  }
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
-  __syncthreads();  // red may still be read from a previous call
-  if (lane == 0) red[warp] = v;
-  __syncthreads();
-  v = red[0];
-  for (int k = 1; k < nw; ++k) v = take_max ? fmaxf(v, red[k]) : v + red[k];
+  for (int d = 16; d > 0; d >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, d));
+  return v;
+}
+__device__ __forceinline__ float WarpSum(float v) {
+#pragma unroll
+  for (int d = 16; d > 0; d >>= 1) v += __shfl_xor_sync(0xffffffffu, v, d);
   return v;
 }
 
-__global__ void __launch_bounds__(128)
+// One warp per score row, as DenseFill.
+__global__ void __launch_bounds__(32 * kRowsPerCta)
 LogSoftmaxFill(const float *__restrict__ logits, int64_t T, int32_t C,
                const int32_t *__restrict__ segments, const int32_t *__restrict__ row_splits,
-               int32_t num_segs, float *__restrict__ scores) {
-  const int32_t r = blockIdx.x;
-  __shared__ int64_t src_row;
-  __shared__ float red[4];
-  if (threadIdx.x == 0) {
-    const int32_t k = SegmentOfRow(row_splits, num_segs, r);
-    const int32_t t = r - row_splits[k], dur = row_splits[k + 1] - row_splits[k] - 1;
-    src_row = t < dur ? (int64_t)segments[3 * k] * T + segments[3 * k + 1] + t : -1;
-  }
-  __syncthreads();
+               int32_t num_segs, int32_t rows, float *__restrict__ scores) {
+  const int32_t r = blockIdx.x * kRowsPerCta + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  if (r >= rows) return;
+  const int64_t src = SourceRow(segments, row_splits, num_segs, T, r);
   float *out = scores + (int64_t)r * (C + 1);
-  const int64_t src = src_row;
   if (src < 0) {
-    if (threadIdx.x == 0) out[0] = 0.0f;
-    for (int32_t c = threadIdx.x; c < C; c += blockDim.x) out[1 + c] = -INFINITY;
+    if (lane == 0) out[0] = 0.0f;
+    for (int32_t c = lane; c < C; c += 32) out[1 + c] = -INFINITY;
     return;
   }
   const float *in = logits + src * C;
   float mx = -INFINITY;
-  for (int32_t c = threadIdx.x; c < C; c += blockDim.x) mx = fmaxf(mx, __ldg(in + c));
-  mx = BlockReduce(mx, true, red);
+  for (int32_t c = lane; c < C; c += 32) mx = fmaxf(mx, __ldg(in + c));
+  mx = WarpMax(mx);
   float sum = 0.0f;
-  for (int32_t c = threadIdx.x; c < C; c += blockDim.x) sum += expf(__ldg(in + c) - mx);
-  sum = BlockReduce(sum, false, red);
-  const float lse = logf(sum);
-  if (threadIdx.x == 0) out[0] = -INFINITY;
-  for (int32_t c = threadIdx.x; c < C; c += blockDim.x) out[1 + c] = (__ldg(in + c) - mx) - lse;
+  for (int32_t c = lane; c < C; c += 32) sum += expf(__ldg(in + c) - mx);
+  const float lse = logf(WarpSum(sum));
+  if (lane == 0) out[0] = -INFINITY;
+  for (int32_t c = lane; c < C; c += 32) out[1 + c] = (__ldg(in + c) - mx) - lse;
 }
 
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(32 * kRowsPerCta)
 LogSoftmaxBackward(const float *__restrict__ grad_scores, const float *__restrict__ scores,
                    int64_t T, int32_t C, const int32_t *__restrict__ segments,
-                   const int32_t *__restrict__ row_splits, int32_t num_segs, int32_t use_atomics,
-                   float *__restrict__ grad_logits) {
-  const int32_t r = blockIdx.x;
-  __shared__ int64_t dst_row;
-  __shared__ float red[4];
-  if (threadIdx.x == 0) {
-    const int32_t k = SegmentOfRow(row_splits, num_segs, r);
-    const int32_t t = r - row_splits[k], dur = row_splits[k + 1] - row_splits[k] - 1;
-    dst_row = t < dur ? (int64_t)segments[3 * k] * T + segments[3 * k + 1] + t : -1;
-  }
-  __syncthreads();
-  const int64_t dst = dst_row;
+                   const int32_t *__restrict__ row_splits, int32_t num_segs, int32_t rows,
+                   int32_t use_atomics, float *__restrict__ grad_logits) {
+  const int32_t r = blockIdx.x * kRowsPerCta + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  if (r >= rows) return;
+  const int64_t dst = SourceRow(segments, row_splits, num_segs, T, r);
   if (dst < 0) return;
   const float *g = grad_scores + (int64_t)r * (C + 1) + 1;
   const float *lp = scores + (int64_t)r * (C + 1) + 1;
   float gsum = 0.0f;
-  for (int32_t c = threadIdx.x; c < C; c += blockDim.x) gsum += g[c];
-  gsum = BlockReduce(gsum, false, red);
+  for (int32_t c = lane; c < C; c += 32) gsum += g[c];
+  gsum = WarpSum(gsum);
   float *out = grad_logits + dst * C;
-  for (int32_t c = threadIdx.x; c < C; c += blockDim.x) {
+  for (int32_t c = lane; c < C; c += 32) {
     const float v = g[c] - expf(lp[c]) * gsum;
     if (use_atomics) atomicAdd(out + c, v); else out[c] = v;
   }
@@ -207,8 +189,9 @@ int32_t k2b200_dense_fsa_vec_from_logits(const float *logits, int64_t num_seqs,
   K2B_REQUIRE(num_segs > 0 && num_classes > 0 && rows > 0, "empty DenseFsaVec");
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
   PhaseTimer timer(kPhaseDense, s);
-  { LogSoftmaxFill<<<rows, 128, 0, s>>>(logits, num_frames, num_classes, segments, row_splits,
-                                        num_segs, scores); NoteLaunch(); }
+  { LogSoftmaxFill<<<CeilDiv(rows, kRowsPerCta), 32 * kRowsPerCta, 0, s>>>(
+      logits, num_frames, num_classes, segments, row_splits, num_segs, rows, scores);
+    NoteLaunch(); }
   K2B_CUDA_OK(cudaGetLastError());
   return kOk;
 }
@@ -225,9 +208,9 @@ int32_t k2b200_dense_fsa_vec_from_logits_backward(const float *grad_scores, cons
   K2B_CUDA_OK(cudaMemsetAsync(grad_logits, 0,
                               sizeof(float) * (size_t)num_seqs * num_frames * num_classes, s));
   if (rows > 0)
-    { LogSoftmaxBackward<<<rows, 128, 0, s>>>(grad_scores, scores, num_frames, num_classes,
-                                              segments, row_splits, num_segs, overlapping,
-                                              grad_logits); NoteLaunch(); }
+    { LogSoftmaxBackward<<<CeilDiv(rows, kRowsPerCta), 32 * kRowsPerCta, 0, s>>>(
+        grad_scores, scores, num_frames, num_classes, segments, row_splits, num_segs, rows,
+        overlapping, grad_logits); NoteLaunch(); }
   K2B_CUDA_OK(cudaGetLastError());
   return kOk;
 }
