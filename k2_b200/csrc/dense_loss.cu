@@ -149,8 +149,8 @@ constexpr int32_t kMinExponent = -480;     // binary exponent of every non-zero 
 // same fp32 expressions and adds the survivors' alpha[src] * exp(w) * exp(lp).
 // The frame loop is unrolled by kU, so ring
 // slots and buffers are compile-time constants.  Nothing is prefetched through
-// registers: global loads kept in flight across frames made every frame wait a
-// full memory latency (the scoreboards a load waits on are shared counters).
+// registers: with the Viterbi scores fetched that way the frames still waited on
+// global loads; the ring removed that wait.
 //
 // Arithmetic: all states of a level share one binary exponent K, so a value is a
 // plain double v with alpha = v * 2^K and an arc costs two multiplies and an add.
