@@ -69,6 +69,14 @@ int32_t k2b200_row_splits_to_row_ids(const int32_t *row_splits, int32_t num_rows
                                      int32_t *row_ids, int32_t num_elems,
                                      void *stream);
 
+/* n int32 values from (pageable or pinned) host memory to device memory, passed as
+ * kernel parameters in launches of up to 960 values: asynchronous on `stream`, the
+ * host array is free for reuse on return, and the copy engine is not involved.  For
+ * the few hundred integers of a batch description (segments, row_splits, symbol
+ * lists), where k2 copies through Array1::To (k2/csrc/array.h:234-250). */
+int32_t k2b200_upload_i32(const int32_t *host_values, int64_t n, int32_t *device_out,
+                          void *stream);
+
 /* Exclusive sum of n int32: out[0..n], out[n] = total; in and out may alias.
  * tmp must hold k2b200_exclusive_sum_tmp_bytes(n) bytes.
  * Replaces k2::ExclusiveSum, k2/csrc/utils_inl.h:40-60 (cub::DeviceScan). */

@@ -13,7 +13,7 @@ LIB_PATH = os.path.join(_HERE, "libk2b200.so")
 
 if not os.path.exists(LIB_PATH):
     raise ImportError(
-        f"{LIB_PATH} not found: build it with `python -m k2_b200.build` "
+        f"{LIB_PATH} not found: build it with `python k2_b200/build.py` "
         "(nvcc, sm_100a). k2_b200 has no CPU or PyTorch fallback.")
 
 lib = ctypes.CDLL(LIB_PATH)
@@ -71,6 +71,7 @@ _sig("k2b200_kernel_launch_count", c_i64, [])
 _sig("k2b200_profile_enable", None, [c_i32])
 _sig("k2b200_profile_read_ms", ctypes.c_double, [c_i32, ctypes.POINTER(c_i64)])
 _sig("k2b200_row_splits_to_row_ids", c_i32, [c_vp, c_i32, c_vp, c_i32, c_vp])
+_sig("k2b200_upload_i32", c_i32, [c_vp, c_i64, c_vp, c_vp])
 _sig("k2b200_exclusive_sum_tmp_bytes", c_sz, [c_i64])
 _sig("k2b200_exclusive_sum", c_i32, [c_vp, c_vp, c_i64, c_vp, c_vp])
 _sig("k2b200_exclusive_sum_static_max_len", c_i64, [])
@@ -129,6 +130,7 @@ _sig("k2b200_fsa_properties", c_i32,
 EXPORTED = [
     "k2b200_last_error", "k2b200_abi_version", "k2b200_kernel_launch_count",
     "k2b200_profile_enable", "k2b200_profile_read_ms", "k2b200_row_splits_to_row_ids",
+    "k2b200_upload_i32",
     "k2b200_exclusive_sum_tmp_bytes", "k2b200_exclusive_sum",
     "k2b200_exclusive_sum_static_max_len", "k2b200_exclusive_sum_static", "k2b200_fsa_incoming_tmp_bytes",
     "k2b200_fsa_incoming", "k2b200_intersect_dense_workspace_bytes",
@@ -173,6 +175,20 @@ def ptr(t) -> int:
 
 def stream_of(device) -> int:
     return torch.cuda.current_stream(device).cuda_stream
+
+
+def upload_i32(arr, device) -> torch.Tensor:
+    """Host int32 array -> new device tensor.  The values travel as kernel parameters
+    (k2b200_upload_i32): no stream synchronisation, unlike a torch copy from pageable
+    memory, and no queueing behind a large host-to-device transfer in flight."""
+    import numpy as np
+    arr = np.ascontiguousarray(arr, dtype=np.int32).reshape(-1)
+    out = torch.empty(arr.shape[0], dtype=torch.int32, device=device)
+    if arr.shape[0]:
+        with torch.cuda.device(out.device):
+            check(lib.k2b200_upload_i32(arr.ctypes.data, arr.shape[0], out.data_ptr(),
+                                        stream_of(out.device)))
+    return out
 
 
 def require_cuda(t: torch.Tensor, what: str) -> None:

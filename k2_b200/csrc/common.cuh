@@ -98,6 +98,9 @@ int32_t RowSplitsToRowIds(const int32_t *row_splits, int32_t num_rows,
                           int32_t *row_ids, int32_t num_elems,
                           cudaStream_t stream);
 
+// n host integers -> device memory as kernel parameters (no copy engine, no sync).
+int32_t UploadInts(const int32_t *host, int64_t n, int32_t *device_out, cudaStream_t stream);
+
 // Incoming-arc index of an FsaVec: for every state (idx01) the arcs (idx012) that
 // enter it, in increasing arc order.
 //   in_splits [num_states + 1], in_arcs [num_arcs]; optional in_src [num_arcs]

@@ -4,6 +4,7 @@
 // (k2/csrc/utils_inl.h:40-90 ExclusiveSum, k2/csrc/utils.cu:75-200
 // RowSplitsToRowIds, k2/csrc/fsa_utils.cu:901-928 GetIncomingArcs).
 #include <atomic>
+#include <cstring>
 #include <mutex>
 #include <vector>
 
@@ -124,6 +125,31 @@ int32_t SideJoin(cudaStream_t main) {
   K2B_FORWARD(SideOfCurrentDevice(&st));
   K2B_CUDA_OK(cudaEventRecord(st->join_ev, st->stream));
   K2B_CUDA_OK(cudaStreamWaitEvent(main, st->join_ev, 0));
+  return kOk;
+}
+
+// ----------------------------------------------------------------------------
+// A few hundred host integers to device memory without the copy engine: the values
+// travel as kernel parameters.  A copy from pageable memory synchronises the stream
+// in torch, and one from pinned memory queues behind whatever large transfer the
+// application has in flight; a launch does neither.
+// ----------------------------------------------------------------------------
+struct IntChunk {
+  int32_t v[960];  // kernel parameters are limited to 4 KB
+};
+__global__ void StoreInts(IntChunk c, int32_t n, int32_t *__restrict__ out) {
+  const int32_t k = blockIdx.x * blockDim.x + threadIdx.x;
+  if (k < n) out[k] = c.v[k];
+}
+
+int32_t UploadInts(const int32_t *host, int64_t n, int32_t *device_out, cudaStream_t stream) {
+  IntChunk c;
+  for (int64_t done = 0; done < n; done += 960) {
+    const int32_t m = (int32_t)std::min<int64_t>(960, n - done);
+    memcpy(c.v, host + done, sizeof(int32_t) * m);
+    { StoreInts<<<CeilDiv(m, 256), 256, 0, stream>>>(c, m, device_out + done); NoteLaunch(); }
+  }
+  K2B_CUDA_OK(cudaGetLastError());
   return kOk;
 }
 

@@ -252,6 +252,13 @@ int32_t k2b200_row_splits_to_row_ids(const int32_t *row_splits, int32_t num_rows
   return RowSplitsToRowIds(row_splits, num_rows, row_ids, num_elems, STREAM(stream));
 }
 
+int32_t k2b200_upload_i32(const int32_t *host_values, int64_t n, int32_t *device_out,
+                          void *stream) {
+  K2B_REQUIRE(n >= 0, "negative length");
+  K2B_REQUIRE(n == 0 || (host_values != nullptr && device_out != nullptr), "NULL pointer");
+  return UploadInts(host_values, n, device_out, STREAM(stream));
+}
+
 size_t k2b200_exclusive_sum_tmp_bytes(int64_t n) { return sizeof(int32_t) * ScanTmpInts(n); }
 int32_t k2b200_exclusive_sum(const int32_t *in, int32_t *out, int64_t n, void *tmp,
                              void *stream) {

@@ -114,11 +114,12 @@ class DenseFsaVec(object):
             order = np.argsort(first, kind="stable")
             overlapping = bool(np.any((first + dur)[order][:-1] > first[order][1:]))
             eff = np.stack([seg[:, 0], seg[:, 1], dur], axis=1).astype(np.int32)
-            meta = torch.from_numpy(np.concatenate([eff.reshape(-1), row_splits])).to(
-                device, non_blocking=True)
+            meta = _lib.upload_i32(np.concatenate([eff.reshape(-1), row_splits]), device)
             k3 = 3 * seg.shape[0]
             fn = _LogSoftmaxDenseFunction if _logits else _DenseFsaVecFunction
             scores = fn.apply(log_probs, meta[:k3].view(-1, 3), meta[k3:], rows, overlapping)
+            self._init(scores, row_splits, meta[k3:])
+            return
         else:
             if _logits:
                 log_probs = torch.log_softmax(log_probs, dim=-1)
@@ -146,11 +147,17 @@ class DenseFsaVec(object):
         scatter of the gradient)."""
         return cls(logits, supervision_segments, allow_truncate, _logits=True)
 
-    def _init(self, scores: torch.Tensor, h_row_splits: np.ndarray) -> None:
+    def _init(self, scores: torch.Tensor, h_row_splits: np.ndarray,
+              d_row_splits: torch.Tensor = None) -> None:
         assert scores.is_contiguous()
         self.scores = scores  # for back propagation
         self.h_row_splits = np.ascontiguousarray(h_row_splits, dtype=np.int32)
-        self.row_splits = torch.from_numpy(self.h_row_splits).to(scores.device)
+        if d_row_splits is not None:
+            self.row_splits = d_row_splits
+        elif scores.is_cuda:
+            self.row_splits = _lib.upload_i32(self.h_row_splits, scores.device)
+        else:
+            self.row_splits = torch.from_numpy(self.h_row_splits)
         self._duration = torch.from_numpy(np.diff(self.h_row_splits) - 1)
 
     @classmethod

@@ -120,7 +120,7 @@ def _ctc_graph_cuda(lens: np.ndarray, sym: np.ndarray, modified: bool, device) -
     np.cumsum(per_fsa, out=h_arc_splits[1:])
     h_rs1 = 2 * sym_off + 2 * np.arange(n + 1)
     num_arcs, num_states = int(h_arc_splits[-1]), int(h_rs1[-1])
-    meta = torch.from_numpy(np.concatenate([sym_off, sym]).astype(np.int32)).to(device)
+    meta = _lib.upload_i32(np.concatenate([sym_off, sym]), device)
     i32 = dict(dtype=torch.int32, device=device)
     rs1 = torch.empty(n + 1, **i32)
     rs2 = torch.empty(num_states + 1, **i32)

@@ -287,6 +287,10 @@ def test_generic_ragged_ops(k2):
                                                  _lib.stream_of(torch.device(DEV))))
         want = np.concatenate([[0], np.cumsum(x)]).astype(np.int32)
         np.testing.assert_array_equal(out.cpu().numpy(), want)
+    # host integers -> device through kernel parameters, across the 960-value launches
+    for n in (0, 1, 959, 960, 961, 5000):
+        x = rng.integers(-2**31, 2**31, size=n).astype(np.int32)
+        np.testing.assert_array_equal(_lib.upload_i32(x, DEV).cpu().numpy(), x)
     # incoming index against a stable host sort
     a = random_fsa_vec(rng, 9, max_states=30, max_arcs=300)
     from gpu_util import host_to_fsa
