@@ -263,6 +263,55 @@ int32_t k2b200_intersect_dense_emit(const k2b200_intersect_args *args, void *wor
                                     const k2b200_lattice_out *out);
 
 /* ---------------------------------------------------------------------------
+ * Pruned intersection (decoding): a beam search over the frames with a dynamic
+ * beam per sequence between min_active_states and max_active_states, and
+ * backward pruning to output_beam in windows of 30 frames every 20.
+ * Replaces k2::IntersectDensePruned (k2/csrc/intersect_dense_pruned.cu:1678-1694;
+ * declaration k2/csrc/fsa_algo.h:150-206), bound as _k2.intersect_dense_pruned
+ * (k2/python/csrc/torch/fsa_algo.cu:200-222).  a_fsas holds one graph per
+ * sequence or a single graph shared by all sequences (num_fsas == 1).  States of
+ * a frame are numbered as the reference's CPU build numbers them (by the first
+ * arc that reaches them above the cutoff), so lattices and arc maps are
+ * identical to it.  Online (chunk by chunk) decoding is not provided.
+ *
+ * Protocol (one host synchronisation):
+ *   1. k2b200_intersect_dense_pruned_workspace_bytes(&args, &bytes, &levels)
+ *   2. k2b200_intersect_dense_pruned_search(&args, ws, bytes, stream, &ns, &na,
+ *      &arena_full): one CTA per sequence walks all frames.  arena_full = 1 means
+ *      max_states_per_seq / max_arcs_per_seq were too small for some sequence:
+ *      call again with larger values (and a workspace sized for them).
+ *   3. k2b200_intersect_dense_pruned_emit(&args, ws, bytes, stream, &out) writes
+ *      the lattice (ns states, na arcs), both arc maps (arc_map_a is -1 on the
+ *      arcs that allow_partial turned into final arcs) and, optionally, the
+ *      layering: levels = num_seqs * (T + 2) with T the longest sequence's rows.
+ * ------------------------------------------------------------------------- */
+typedef struct {
+  int32_t num_fsas, num_states, num_arcs; /* a_fsas; num_fsas is 1 or num_seqs */
+  const int32_t *a_row_splits1;           /* [num_fsas+1] */
+  const int32_t *a_row_splits2;           /* [num_states+1] */
+  const void *a_arcs;                     /* [num_arcs] Arc, arc-sorted */
+  const float *scores;                    /* [rows, cols] contiguous */
+  int32_t rows, cols, num_seqs;
+  const int32_t *b_row_splits;            /* device [num_seqs+1] */
+  const int32_t *h_b_row_splits;          /* HOST copy */
+  float search_beam, output_beam;
+  int32_t min_active_states, max_active_states, allow_partial;
+  /* capacity, per sequence, for the states and arcs alive at any one time: the
+   * pruned frames so far plus the unpruned last 30 */
+  int64_t max_states_per_seq, max_arcs_per_seq;
+} k2b200_pruned_args;
+
+int32_t k2b200_intersect_dense_pruned_workspace_bytes(const k2b200_pruned_args *args,
+                                                      size_t *bytes, int64_t *total_levels);
+int32_t k2b200_intersect_dense_pruned_search(const k2b200_pruned_args *args, void *workspace,
+                                             size_t workspace_bytes, void *stream,
+                                             int32_t *num_states_out, int32_t *num_arcs_out,
+                                             int32_t *arena_full);
+int32_t k2b200_intersect_dense_pruned_emit(const k2b200_pruned_args *args, void *workspace,
+                                           size_t workspace_bytes, void *stream,
+                                           const k2b200_lattice_out *out);
+
+/* ---------------------------------------------------------------------------
  * Lattice-free total scores: the log-semiring total score of
  * intersect_dense(a_fsas, b_fsas, output_beam) for every graph, and its
  * gradients, without materialising the lattice.

@@ -2,7 +2,7 @@
 loss path, behind k2's own Python API names for that path."""
 from . import _lib  # noqa: F401  (fails loudly when the CUDA library is missing)
 from .autograd import (dense_loss_supported, index_select, intersect_dense,  # noqa: F401
-                       intersect_dense_tot_scores)
+                       intersect_dense_pruned, intersect_dense_tot_scores)
 from .ctc_loss import CtcLoss, ctc_loss  # noqa: F401
 from .dense_fsa_vec import DenseFsaVec  # noqa: F401
 from .fsa import Fsa, create_fsa_vec  # noqa: F401

@@ -46,6 +46,18 @@ class LatticeOut(ctypes.Structure):
     ]
 
 
+class PrunedArgs(ctypes.Structure):
+    _fields_ = [
+        ("num_fsas", c_i32), ("num_states", c_i32), ("num_arcs", c_i32),
+        ("a_row_splits1", c_vp), ("a_row_splits2", c_vp), ("a_arcs", c_vp),
+        ("scores", c_vp), ("rows", c_i32), ("cols", c_i32), ("num_seqs", c_i32),
+        ("b_row_splits", c_vp), ("h_b_row_splits", c_vp),
+        ("search_beam", c_f32), ("output_beam", c_f32),
+        ("min_active_states", c_i32), ("max_active_states", c_i32), ("allow_partial", c_i32),
+        ("max_states_per_seq", c_i64), ("max_arcs_per_seq", c_i64),
+    ]
+
+
 class FsaView(ctypes.Structure):
     _fields_ = [
         ("num_fsas", c_i32), ("num_states", c_i32), ("num_arcs", c_i32),
@@ -72,6 +84,13 @@ _sig("k2b200_profile_enable", None, [c_i32])
 _sig("k2b200_profile_read_ms", ctypes.c_double, [c_i32, ctypes.POINTER(c_i64)])
 _sig("k2b200_row_splits_to_row_ids", c_i32, [c_vp, c_i32, c_vp, c_i32, c_vp])
 _sig("k2b200_upload_i32", c_i32, [c_vp, c_i64, c_vp, c_vp])
+_sig("k2b200_intersect_dense_pruned_workspace_bytes", c_i32,
+     [ctypes.POINTER(PrunedArgs), ctypes.POINTER(c_sz), ctypes.POINTER(c_i64)])
+_sig("k2b200_intersect_dense_pruned_search", c_i32,
+     [ctypes.POINTER(PrunedArgs), c_vp, c_sz, c_vp, ctypes.POINTER(c_i32),
+      ctypes.POINTER(c_i32), ctypes.POINTER(c_i32)])
+_sig("k2b200_intersect_dense_pruned_emit", c_i32,
+     [ctypes.POINTER(PrunedArgs), c_vp, c_sz, c_vp, ctypes.POINTER(LatticeOut)])
 _sig("k2b200_exclusive_sum_tmp_bytes", c_sz, [c_i64])
 _sig("k2b200_exclusive_sum", c_i32, [c_vp, c_vp, c_i64, c_vp, c_vp])
 _sig("k2b200_exclusive_sum_static_max_len", c_i64, [])
@@ -146,6 +165,8 @@ EXPORTED = [
     "k2b200_fsa_levels_tmp_bytes", "k2b200_fsa_levels",
     "k2b200_dense_loss_supported", "k2b200_dense_loss_workspace_bytes",
     "k2b200_dense_loss_forward", "k2b200_dense_loss_backward",
+    "k2b200_intersect_dense_pruned_workspace_bytes", "k2b200_intersect_dense_pruned_search",
+    "k2b200_intersect_dense_pruned_emit",
 ]
 
 

@@ -264,6 +264,144 @@ def intersect_dense(a_fsas: Fsa, b_fsas: DenseFsaVec, output_beam: float,
     return out_fsa[0]
 
 
+# Arena capacity that `intersect_dense_pruned` starts from: arcs alive at one time over
+# all sequences, and the most one sequence gets of it (the call is repeated with four
+# times as much per sequence while some sequence overflows its share).
+PRUNED_ARCS_TOTAL = 1 << 26
+PRUNED_ARCS_PER_SEQ = 1 << 21
+PRUNED_ARCS_MIN = 1 << 16
+
+
+def _intersect_dense_pruned_arcs(a: RaggedArc, b: DenseFsaVec, search_beam: float,
+                                 output_beam: float, min_active_states: int,
+                                 max_active_states: int, allow_partial: bool):
+    """The `_k2.intersect_dense_pruned` call (k2/python/csrc/torch/fsa_algo.cu:200-222):
+    returns (RaggedArc lattice, arc_map_a, arc_map_b)."""
+    dev = b.scores.device
+    _lib.require_cuda(a.values(), "a_fsas")
+    _lib.require_cuda(b.scores, "b_fsas.scores")
+    if a.device != dev:
+        raise RuntimeError("a_fsas and b_fsas must be on the same device")
+    scores = b.scores.detach()
+    assert scores.is_contiguous() and scores.dtype == torch.float32
+    h_brs = np.ascontiguousarray(b.h_row_splits, dtype=np.int32)
+    num_seqs = h_brs.shape[0] - 1
+    cap_a = max(PRUNED_ARCS_MIN, min(PRUNED_ARCS_PER_SEQ, PRUNED_ARCS_TOTAL // max(num_seqs, 1)))
+    stream = _lib.stream_of(dev)
+    i32 = dict(dtype=torch.int32, device=dev)
+    while True:
+        args = _lib.PrunedArgs(
+            num_fsas=a.num_fsas, num_states=a.num_states, num_arcs=a.num_elements(),
+            a_row_splits1=_lib.ptr(a._row_splits1), a_row_splits2=_lib.ptr(a._row_splits2),
+            a_arcs=_lib.ptr(a.values()), scores=_lib.ptr(scores), rows=scores.shape[0],
+            cols=scores.shape[1], num_seqs=num_seqs, b_row_splits=_lib.ptr(b.row_splits),
+            h_b_row_splits=h_brs.ctypes.data, search_beam=search_beam, output_beam=output_beam,
+            min_active_states=min_active_states, max_active_states=max_active_states,
+            allow_partial=int(bool(allow_partial)), max_states_per_seq=max(cap_a // 2, 2),
+            max_arcs_per_seq=cap_a)
+        nbytes, levels = ctypes.c_size_t(), ctypes.c_int64()
+        _lib.check(_lib.lib.k2b200_intersect_dense_pruned_workspace_bytes(
+            ctypes.byref(args), ctypes.byref(nbytes), ctypes.byref(levels)))
+        ws = torch.empty(nbytes.value, dtype=torch.uint8, device=dev)
+        ns, na, full = ctypes.c_int32(), ctypes.c_int32(), ctypes.c_int32()
+        with torch.cuda.device(dev):
+            _lib.check(_lib.lib.k2b200_intersect_dense_pruned_search(
+                ctypes.byref(args), _lib.ptr(ws), nbytes.value, stream, ctypes.byref(ns),
+                ctypes.byref(na), ctypes.byref(full)))
+        if not full.value:
+            break
+        del ws
+        cap_a *= 4
+        if cap_a >= 1 << 30:
+            raise RuntimeError("intersect_dense_pruned: more than 2^30 arcs alive in one sequence")
+    ns, na = ns.value, na.value
+    with torch.cuda.device(dev):
+        row_splits1 = torch.empty(num_seqs + 1, **i32)
+        row_ids1 = torch.empty(ns + 1, **i32)
+        row_splits2 = torch.empty(ns + 1, **i32)
+        row_ids2 = torch.empty(na + 1, **i32)
+        values = torch.empty((na + 1, 4), **i32)
+        arc_map_a = torch.empty(na + 1, **i32)
+        arc_map_b = torch.empty(na + 1, **i32)
+        level_offsets = torch.empty(num_seqs + 1, **i32)
+        level_splits = torch.empty(levels.value + 1, **i32)
+        out = _lib.LatticeOut(
+            row_splits1=_lib.ptr(row_splits1), row_ids1=_lib.ptr(row_ids1),
+            row_splits2=_lib.ptr(row_splits2), row_ids2=_lib.ptr(row_ids2),
+            arcs=_lib.ptr(values), arc_map_a=_lib.ptr(arc_map_a), arc_map_b=_lib.ptr(arc_map_b),
+            level_offsets=_lib.ptr(level_offsets), level_splits=_lib.ptr(level_splits))
+        _lib.check(_lib.lib.k2b200_intersect_dense_pruned_emit(
+            ctypes.byref(args), _lib.ptr(ws), nbytes.value, stream, ctypes.byref(out)))
+    lattice = RaggedArc(values[:na], row_splits1, row_splits2, row_ids1[:ns], row_ids2[:na])
+    lattice._levels = (level_offsets, level_splits)
+    return lattice, arc_map_a[:na], arc_map_b[:na]
+
+
+class _IntersectDensePrunedFunction(torch.autograd.Function):
+    """Autograd contract of k2/python/k2/autograd.py:350-510."""
+
+    @staticmethod
+    def forward(ctx, a_fsas: Fsa, b_fsas: DenseFsaVec, out_fsa: List[Fsa], search_beam: float,
+                output_beam: float, min_active_states: int, max_active_states: int,
+                allow_partial: bool, unused_scores_a: torch.Tensor,
+                unused_scores_b: torch.Tensor, seqframe_idx_name: Optional[str] = None,
+                frame_idx_name: Optional[str] = None) -> torch.Tensor:
+        assert len(out_fsa) == 1
+        ragged_arc, arc_map_a, arc_map_b = _intersect_dense_pruned_arcs(
+            a_fsas.arcs, b_fsas, search_beam, output_beam, min_active_states,
+            max_active_states, allow_partial)
+        out_fsa[0] = Fsa(ragged_arc, _check=False)
+        for name, a_value in a_fsas.named_tensor_attr(include_scores=False):
+            if name == 'labels':
+                continue
+            setattr(out_fsa[0], name, index_select(a_value, arc_map_a))
+        for name, a_value in a_fsas.named_non_tensor_attr():
+            setattr(out_fsa[0], name, a_value)
+        ctx.arc_map_a = arc_map_a
+        ctx.arc_map_b = arc_map_b
+        ctx.save_for_backward(unused_scores_a, unused_scores_b)
+        seqframe_idx = None
+        if frame_idx_name is not None or seqframe_idx_name is not None:
+            seqframe_idx = torch.div(arc_map_b, b_fsas.scores.shape[1], rounding_mode="floor")
+        if frame_idx_name is not None:
+            row_ids = torch.repeat_interleave(
+                torch.arange(b_fsas.dim0(), dtype=torch.int32, device=arc_map_b.device),
+                torch.from_numpy(np.diff(b_fsas.h_row_splits)).to(arc_map_b.device))
+            fsa_idx0 = row_ids[seqframe_idx.long()]
+            frame_idx = seqframe_idx - b_fsas.row_splits[fsa_idx0.long()]
+            assert not hasattr(out_fsa[0], frame_idx_name)
+            setattr(out_fsa[0], frame_idx_name, frame_idx.to(torch.int32))
+        if seqframe_idx_name is not None:
+            assert not hasattr(out_fsa[0], seqframe_idx_name)
+            setattr(out_fsa[0], seqframe_idx_name, seqframe_idx)
+        return out_fsa[0].scores
+
+    @staticmethod
+    def backward(ctx, out_fsa_grad: torch.Tensor):
+        a_scores, b_scores = ctx.saved_tensors
+        grad_a = torch.zeros(a_scores.size(0), dtype=torch.float32, device=a_scores.device)
+        grad_b = torch.zeros(*b_scores.shape, dtype=torch.float32,
+                             device=b_scores.device).contiguous()
+        _index_add(ctx.arc_map_a, out_fsa_grad, grad_a)  # -1 (allow_partial arcs) is skipped
+        _index_add(ctx.arc_map_b, out_fsa_grad, grad_b.view(-1))
+        return (None, None, None, None, None, None, None, None, grad_a, grad_b, None, None)
+
+
+def intersect_dense_pruned(a_fsas: Fsa, b_fsas: DenseFsaVec, search_beam: float,
+                           output_beam: float, min_active_states: int, max_active_states: int,
+                           seqframe_idx_name: Optional[str] = None,
+                           frame_idx_name: Optional[str] = None,
+                           allow_partial: bool = False) -> Fsa:
+    """Pruned intersection for decoding (k2/python/k2/autograd.py:667-746): `a_fsas` holds
+    one arc-sorted graph per sequence of `b_fsas`, or a single graph shared by all."""
+    out_fsa = [0]
+    _IntersectDensePrunedFunction.apply(a_fsas, b_fsas, out_fsa, search_beam, output_beam,
+                                        min_active_states, max_active_states, allow_partial,
+                                        a_fsas.scores, b_fsas.scores, seqframe_idx_name,
+                                        frame_idx_name)
+    return out_fsa[0]
+
+
 class _DenseTotScoresFunction(torch.autograd.Function):
     """tot_scores = log-semiring total score of intersect_dense(a_fsas, b_fsas) per
     graph, with gradients to the graph scores and the dense scores, computed on the

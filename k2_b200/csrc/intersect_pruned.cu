@@ -1,0 +1,768 @@
+// Pruned intersection of decoding graphs with a DenseFsaVec: a frame-synchronous
+// beam search with a dynamic beam per sequence, followed window by window by a
+// backward pass that applies the output beam.  Behaviour follows
+// k2/csrc/intersect_dense_pruned.cu:41-1694 (MultiGraphDenseIntersectPruned with
+// online_decoding == false) as its CPU build executes it:
+//   - the states of frame t+1 are numbered in the order of the first arc of frame t
+//     (in [state][arc] order) that reaches them above the cutoff; the reference
+//     inserts into a hash sequentially on CPU, so the first arc wins (:1005-1028);
+//   - the search beam per sequence moves towards `search_beam`, shrinks while more
+//     than max_active states are alive and grows while fewer than min_active are,
+//     in the reference's mixed float/double arithmetic (:687-767);
+//   - every 20 frames the last 30 are pruned backwards (:164-199, :1373-1634); the
+//     backward thread of the reference never changes what the forward pass reads,
+//     so the windows are simply run in order.
+//
+// Sequences are independent, so one CTA owns one sequence from the first frame to
+// the last: no host round trip per frame, no hash (a direct table per sequence,
+// indexed by graph state, plays its role) and no kernel waits on another.  States
+// and arcs of all frames of a sequence live in one arena, frame after frame, so the
+// pruned result is already in lattice order and the output pass is a copy.
+#include <algorithm>
+#include <climits>
+#include <cmath>
+#include <cstring>
+#include <vector>
+
+#include "common.cuh"
+#include "../../include/k2b200.h"
+
+namespace k2b {
+namespace {
+
+constexpr int kSearchThreads = 1024;
+constexpr int kWindow = 30;       // frames pruned per backward phase (:171)
+constexpr int kWindowShift = 20;  // frames between two phases (:172)
+constexpr int32_t kNoWinner = 0x7f7f7f7f;  // what a byte fill with 0x7f leaves
+
+// order-preserving float <-> int (k2/csrc/utils.h:609-624 plays the same role)
+__device__ __forceinline__ int32_t OrderedInt(float f) {
+  int32_t i = __float_as_int(f);
+  return i >= 0 ? i : i ^ 0x7fffffff;
+}
+__device__ __forceinline__ float OrderedFloat(int32_t i) {
+  return __int_as_float(i >= 0 ? i : i ^ 0x7fffffff);
+}
+
+struct SearchArgs {
+  // graphs
+  const int32_t *a_rs1, *a_rs2;
+  const Arc *a_arcs;
+  int32_t a_stride;  // 1: one graph per sequence, 0: one graph shared by all
+  int32_t a_states;  // states of all graphs together
+  // dense scores
+  const float *scores;
+  int32_t rows, cols;
+  const int32_t *b_rs;
+  int32_t num_seqs, T;  // T = rows of the longest sequence
+  float search_beam, output_beam, min_active, max_active;
+  int32_t allow_partial;
+  // arenas, [num_seqs] slices of cap_s (+1) and cap_a elements
+  int64_t cap_s, cap_a;
+  int32_t *st_astate, *st_fwd, *st_arc0, *st_new;
+  float *st_bwd;
+  int32_t *arc_aidx, *arc_dest;
+  float *arc_ll, *arc_end;
+  uint8_t *arc_keep;
+  int32_t *winner;            // [num_seqs * a_states] (shared) or [a_states]
+  int32_t *frame_s0, *frame_a0;  // [num_seqs][T + 2]
+  int32_t *seq_out;           // [num_seqs][4]: states, arcs, extra final state, status
+};
+
+enum : int32_t { kSeqOk = 0, kSeqOverflow = 1, kSeqManyFinal = 2 };
+
+// exclusive scan of one int per thread over the CTA; every thread gets the total
+__device__ __forceinline__ int32_t BlockScan(int32_t v, int32_t *total, int32_t *sh) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  int32_t inc = v;
+#pragma unroll
+  for (int d = 1; d < 32; d <<= 1) {
+    int32_t o = __shfl_up_sync(0xffffffffu, inc, d);
+    if (lane >= d) inc += o;
+  }
+  if (lane == 31) sh[warp] = inc;
+  __syncthreads();
+  if (warp == 0) {
+    int32_t w = sh[lane];
+    int32_t winc = w;
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) {
+      int32_t o = __shfl_up_sync(0xffffffffu, winc, d);
+      if (lane >= d) winc += o;
+    }
+    sh[32 + lane] = winc - w;
+    if (lane == 31) sh[64] = winc;
+  }
+  __syncthreads();
+  const int32_t ex = sh[32 + warp] + inc - v;
+  *total = sh[64];
+  __syncthreads();  // sh is reused by the next call
+  return ex;
+}
+
+__device__ __forceinline__ float BlockMax(float v, float *shf) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+#pragma unroll
+  for (int d = 16; d > 0; d >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, d));
+  if (lane == 0) shf[warp] = v;
+  __syncthreads();
+  if (warp == 0) {
+    float w = shf[lane];
+#pragma unroll
+    for (int d = 16; d > 0; d >>= 1) w = fmaxf(w, __shfl_xor_sync(0xffffffffu, w, d));
+    if (lane == 0) shf[32] = w;
+  }
+  __syncthreads();
+  const float r = shf[32];
+  __syncthreads();
+  return r;
+}
+
+// Views of one sequence's slices of the arenas.
+struct SeqView {
+  int32_t *st_astate, *st_fwd, *st_arc0, *st_new;
+  float *st_bwd;
+  int32_t *arc_aidx, *arc_dest;
+  float *arc_ll, *arc_end;
+  uint8_t *arc_keep;
+  int32_t *winner, *frame_s0, *frame_a0;
+};
+
+__device__ __forceinline__ SeqView ViewOf(const SearchArgs &g, int32_t seq) {
+  SeqView v;
+  const int64_t so = (int64_t)seq * (g.cap_s + 1), ao = (int64_t)seq * g.cap_a;
+  v.st_astate = g.st_astate + so;
+  v.st_fwd = g.st_fwd + so;
+  v.st_arc0 = g.st_arc0 + so;
+  v.st_new = g.st_new + so;
+  v.st_bwd = g.st_bwd + so;
+  v.arc_aidx = g.arc_aidx + ao;
+  v.arc_dest = g.arc_dest + ao;
+  v.arc_ll = g.arc_ll + ao;
+  v.arc_end = g.arc_end + ao;
+  v.arc_keep = g.arc_keep + ao;
+  // the reference's hash key is dest_state_idx01 + seq * stride with the stride 0
+  // for per-sequence graphs (:118-127): the same index works for a direct table
+  v.winner = g.winner + (g.a_stride ? 0 : (int64_t)seq * g.a_states);
+  v.frame_s0 = g.frame_s0 + (int64_t)seq * (g.T + 2);
+  v.frame_a0 = g.frame_a0 + (int64_t)seq * (g.T + 2);
+  return v;
+}
+
+struct Shared {
+  int32_t scan[65];
+  float fmax[33];
+  float cutoff;
+  float beam;
+  int32_t flag;
+};
+
+// The search beam and the cutoff of frame t (:718-766).  `dyn` is the beam carried
+// from the previous frame; products with the literals 0.8, 0.2 and 1.25 are double
+// products in the reference and are rounded to float on assignment.
+__device__ float NextBeam(float dyn, float best, int32_t active, int32_t t, int32_t final_t,
+                          const SearchArgs &g, float *cutoff) {
+  const float default_beam = g.search_beam, max_active = g.max_active,
+              min_active = g.min_active;
+  float cur_min = min_active;
+  if (t + 5 >= final_t) cur_min = fmaxf(min_active, max_active / 2);
+  if ((float)active <= max_active) {
+    if ((float)active >= cur_min || active == 0) {
+      dyn = (float)(0.8 * (double)dyn + 0.2 * (double)default_beam);
+    } else {
+      if (dyn < default_beam) dyn = default_beam;
+      dyn = (float)((double)dyn * 1.25);
+    }
+  } else if (t + 5 < final_t) {
+    if (dyn > default_beam) dyn = default_beam;
+    dyn = (float)((double)dyn * 0.8);
+  }
+  if (t == final_t - 1) dyn = 1.0e+10f;
+  *cutoff = best - dyn;
+  return dyn;
+}
+
+// One step of the search (GetArcs + PropagateForward, :778-1153): expands the arcs
+// leaving the ns states of frame t at [s0, s0 + ns), which start at arena position
+// a0, and creates the states of frame t + 1 behind them.  Returns false when an
+// arena is full.  *na_out / *ns_next: arcs of frame t and states of frame t + 1.
+__device__ bool SearchStep(const SearchArgs &g, const SeqView &v, Shared *sh, int32_t seq,
+                           int32_t t, int32_t final_t, int32_t row0, int32_t s0, int32_t ns,
+                           int32_t a0, int32_t *na_out, int32_t *ns_next) {
+  const int tid = threadIdx.x;
+  const float kNegInf = -INFINITY;
+  // arc ranges of the states (row_splits of [state][arc] on this frame)
+  int32_t na = 0;
+  for (int32_t base = 0; base < ns; base += kSearchThreads) {
+    const int32_t k = base + tid;
+    int32_t deg = 0;
+    if (k < ns) {
+      const int32_t as = v.st_astate[s0 + k];
+      deg = g.a_rs2[as + 1] - g.a_rs2[as];
+    }
+    int32_t tot;
+    const int32_t ex = BlockScan(deg, &tot, sh->scan);
+    if (k < ns) v.st_arc0[s0 + k] = a0 + na + ex;
+    na += tot;
+  }
+  if ((int64_t)a0 + na > g.cap_a) return false;
+  if (tid == 0) v.st_arc0[s0 + ns] = a0 + na;
+
+  // graph of this sequence: its final state, for allow_partial (:861-871)
+  const int32_t gi = seq * g.a_stride;
+  const int32_t g_final = g.a_rs1[gi + 1] - 1;
+  bool redirect = false;
+  if (g.allow_partial && t == final_t - 1) {
+    // is there any arc with label -1 among the arcs expanded on this frame (:839-857)
+    int32_t has = 0;
+    for (int32_t k = tid; k < ns; k += kSearchThreads) {
+      const int32_t as = v.st_astate[s0 + k];
+      for (int32_t a = g.a_rs2[as]; a < g.a_rs2[as + 1]; ++a) has |= (g.a_arcs[a].label == -1);
+    }
+    redirect = !__syncthreads_or(has);
+  }
+
+  // arcs: scores, destination (as a graph state) and the best end score (:858-905)
+  // (a row past the end is only asked for by a malformed graph whose arcs with
+  // label -1 do not end in a state without arcs)
+  const bool row_ok = row0 + t < g.rows;
+  const float *row = g.scores + (int64_t)(row_ok ? row0 + t : 0) * g.cols;
+  float best = kNegInf;
+  for (int32_t k = tid; k < ns; k += kSearchThreads) {
+    const int32_t as = v.st_astate[s0 + k];
+    const float fwd = OrderedFloat(v.st_fwd[s0 + k]);
+    const int32_t ga0 = g.a_rs2[as], ga1 = g.a_rs2[as + 1];
+    int32_t p = v.st_arc0[s0 + k];
+    for (int32_t a = ga0; a < ga1; ++a, ++p) {
+      const Arc arc = g.a_arcs[a];
+      const uint32_t col = (uint32_t)(arc.label + 1);
+      float acoustic = (row_ok && col < (uint32_t)g.cols) ? row[col] : kNegInf;
+      int32_t dest = as + arc.dest - arc.src;
+      if (redirect) {
+        dest = g_final;
+        acoustic = 0.0f;
+      }
+      const float ll = acoustic + arc.score;
+      const float end = fwd + ll;
+      v.arc_aidx[p] = a;
+      v.arc_ll[p] = ll;
+      v.arc_dest[p] = dest;
+      v.arc_end[p] = end;
+      best = fmaxf(best, end);
+    }
+  }
+  best = BlockMax(best, sh->fmax);  // also makes the arc records visible to the CTA
+  if (tid == 0) sh->beam = NextBeam(sh->beam, best, ns, t, final_t, g, &sh->cutoff);
+  __syncthreads();
+  const float cutoff = sh->cutoff;
+
+  // first arc above the cutoff into every destination state (:1005-1028)
+  for (int32_t q = tid; q < na; q += kSearchThreads) {
+    if (v.arc_end[a0 + q] > cutoff) atomicMin(&v.winner[v.arc_dest[a0 + q]], q);
+  }
+  __syncthreads();
+  // number the new states in the order of their winning arcs (:1031-1100)
+  const int32_t s1 = s0 + ns;
+  int32_t nn = 0;
+  for (int32_t base = 0; base < na; base += kSearchThreads) {
+    const int32_t q = base + tid;
+    int32_t won = 0, dest = 0;
+    if (q < na) {
+      dest = v.arc_dest[a0 + q];
+      won = v.arc_end[a0 + q] > cutoff && v.winner[dest] == q;
+    }
+    int32_t tot;
+    const int32_t j = nn + BlockScan(won, &tot, sh->scan);
+    if (won && (int64_t)s1 + j < g.cap_s) {
+      v.st_astate[s1 + j] = dest;
+      v.st_fwd[s1 + j] = OrderedInt(kNegInf);
+      v.winner[dest] = -(j + 1);
+    }
+    nn += tot;
+  }
+  if ((int64_t)s1 + nn > g.cap_s) return false;
+  __syncthreads();
+  // destination index of every arc and the best score into every new state; an
+  // arc below the cutoff still enters a state that another arc created (:1103-1138)
+  for (int32_t q = tid; q < na; q += kSearchThreads) {
+    const int32_t w = v.winner[v.arc_dest[a0 + q]];
+    int32_t idx1 = -1;
+    if (w < 0) {
+      idx1 = -w - 1;
+      atomicMax(&v.st_fwd[s1 + idx1], OrderedInt(v.arc_end[a0 + q]));
+    }
+    v.arc_dest[a0 + q] = idx1;
+  }
+  __syncthreads();
+  for (int32_t j = tid; j < nn; j += kSearchThreads) v.winner[v.st_astate[s1 + j]] = kNoWinner;
+  __syncthreads();
+  *na_out = na;
+  *ns_next = nn;
+  return true;
+}
+
+// Backward pass over frames [begin, end) with the output beam (PruneTimeRange,
+// :1373-1634, with SetBackwardProbsFinal :1170-1193 and PropagateBackward
+// :1239-1346), then compaction of those frames in place.  On entry the frames up to
+// `end` are complete and frame `end` has its states but no arcs yet; on return
+// *s_top / *a_top are the ends of the arenas and the frame tables are updated.
+__device__ void PruneWindow(const SearchArgs &g, const SeqView &v, Shared *sh, int32_t seq,
+                            int32_t begin, int32_t end, int32_t *s_top, int32_t *a_top) {
+  const int tid = threadIdx.x;
+  const float kNegInf = -INFINITY;
+  const int32_t gi = seq * g.a_stride;
+  const int32_t g_final = g.a_rs1[gi + 1] - 1;  // last state of this sequence's graph
+  const float beam = g.output_beam;
+
+  {  // frame `end`: backward score = -forward score, whatever the state
+    const int32_t s0 = v.frame_s0[end], ns = *s_top - s0;
+    for (int32_t k = tid; k < ns; k += kSearchThreads) {
+      const float fwd = OrderedFloat(v.st_fwd[s0 + k]);
+      v.st_bwd[s0 + k] = (fwd - fwd == 0.0f) ? -fwd : kNegInf;
+    }
+  }
+  __syncthreads();
+
+  // backwards: arc and state survival, backward scores, new state numbers
+  for (int32_t t = end - 1; t >= begin; --t) {
+    const int32_t s0 = v.frame_s0[t], ns = v.frame_s0[t + 1] - s0, s_next = v.frame_s0[t + 1];
+    int32_t kept = 0;
+    for (int32_t base = 0; base < ns; base += kSearchThreads) {
+      const int32_t k = base + tid;
+      int32_t keep_state = 0;
+      if (k < ns) {
+        const float fwd = OrderedFloat(v.st_fwd[s0 + k]);
+        const int32_t p0 = v.st_arc0[s0 + k], p1 = v.st_arc0[s0 + k + 1];
+        float best = kNegInf;
+        for (int32_t p = p0; p < p1; ++p) {
+          const int32_t d = v.arc_dest[p];
+          uint8_t keep = 0;
+          if (d >= 0) {
+            const float bl = v.arc_ll[p] + v.st_bwd[s_next + d];
+            if (bl + fwd >= -beam) {
+              keep = 1;
+              best = fmaxf(best, bl);
+            }
+          }
+          v.arc_keep[p] = keep;
+        }
+        const float bwd = (v.st_astate[s0 + k] == g_final) ? -fwd : best;
+        v.st_bwd[s0 + k] = bwd;
+        keep_state = (bwd != kNegInf) || t == begin;
+      }
+      int32_t tot;
+      const int32_t j = kept + BlockScan(keep_state, &tot, sh->scan);
+      if (k < ns) v.st_new[s0 + k] = keep_state ? j : -1;
+      kept += tot;
+    }
+    __syncthreads();
+  }
+
+  // forwards: move the surviving states and arcs down.  Reads of a chunk complete
+  // before its writes (the scans synchronise), and writes never reach past the
+  // chunk being read, so the compaction is done in place.
+  int32_t ws = v.frame_s0[begin], wa = v.frame_a0[begin];
+  int32_t old_s0 = ws, old_a0 = wa;
+  for (int32_t t = begin; t < end; ++t) {
+    const int32_t old_s1 = v.frame_s0[t + 1], old_a1 = v.frame_a0[t + 1];
+    const int32_t ns = old_s1 - old_s0, na = old_a1 - old_a0;
+    __syncthreads();  // every thread has read the old offsets of frame t + 1
+    int32_t s_run = 0, a_run = 0;
+    for (int32_t base = 0; base < ns; base += kSearchThreads) {
+      const int32_t k = base + tid;
+      int32_t keep_state = 0, cnt = 0, as = 0, fwd = 0;
+      float bwd = 0.0f;
+      if (k < ns) {
+        keep_state = v.st_new[old_s0 + k] >= 0;
+        as = v.st_astate[old_s0 + k];
+        fwd = v.st_fwd[old_s0 + k];
+        bwd = v.st_bwd[old_s0 + k];
+        const int32_t p0 = v.st_arc0[old_s0 + k], p1 = v.st_arc0[old_s0 + k + 1];
+        for (int32_t p = p0; p < p1; ++p) cnt += v.arc_keep[p];
+      }
+      int32_t stot, atot;
+      const int32_t sj = s_run + BlockScan(keep_state, &stot, sh->scan);
+      const int32_t aj = a_run + BlockScan(cnt, &atot, sh->scan);
+      if (keep_state) {
+        v.st_astate[ws + sj] = as;
+        v.st_fwd[ws + sj] = fwd;
+        v.st_bwd[ws + sj] = bwd;
+        v.st_arc0[ws + sj] = wa + aj;
+      }
+      s_run += stot;
+      a_run += atot;
+    }
+    __syncthreads();
+    int32_t moved = 0;
+    const bool renumber = t + 1 < end;  // the states of frame `end` keep their numbers
+    for (int32_t base = 0; base < na; base += kSearchThreads) {
+      const int32_t q = base + tid;
+      int32_t keep = 0, aidx = 0, dest = 0;
+      float ll = 0.0f;
+      if (q < na) {
+        keep = v.arc_keep[old_a0 + q];
+        aidx = v.arc_aidx[old_a0 + q];
+        ll = v.arc_ll[old_a0 + q];
+        dest = v.arc_dest[old_a0 + q];
+        if (keep && renumber) dest = v.st_new[old_s1 + dest];
+      }
+      int32_t tot;
+      const int32_t j = moved + BlockScan(keep, &tot, sh->scan);
+      if (keep) {
+        v.arc_aidx[wa + j] = aidx;
+        v.arc_ll[wa + j] = ll;
+        v.arc_dest[wa + j] = dest;
+      }
+      moved += tot;
+    }
+    __syncthreads();
+    if (tid == 0) {
+      v.frame_s0[t] = ws;
+      v.frame_a0[t] = wa;
+    }
+    ws += s_run;
+    wa += a_run;
+    old_s0 = old_s1;
+    old_a0 = old_a1;
+  }
+  // frame `end`: its states follow the compacted frames
+  const int32_t ns_end = *s_top - old_s0;
+  for (int32_t base = 0; base < ns_end; base += kSearchThreads) {
+    const int32_t k = base + tid;
+    int32_t as = 0, fwd = 0;
+    float bwd = 0.0f;
+    if (k < ns_end) {
+      as = v.st_astate[old_s0 + k];
+      fwd = v.st_fwd[old_s0 + k];
+      bwd = v.st_bwd[old_s0 + k];
+    }
+    __syncthreads();
+    if (k < ns_end) {
+      v.st_astate[ws + k] = as;
+      v.st_fwd[ws + k] = fwd;
+      v.st_bwd[ws + k] = bwd;
+    }
+  }
+  if (tid == 0) {
+    v.frame_s0[end] = ws;
+    v.frame_a0[end] = wa;
+    v.st_arc0[ws] = wa;  // closes the arc range of the last state of frame end - 1
+  }
+  __syncthreads();
+  *s_top = ws + ns_end;
+  *a_top = wa;
+}
+
+// One CTA per sequence: all frames of the search with the pruning windows in the
+// reference's schedule (:164-199, :213-229).
+__global__ void __launch_bounds__(kSearchThreads, 1) PrunedSearch(const SearchArgs g) {
+  __shared__ Shared sh;
+  const int32_t seq = blockIdx.x;
+  const int tid = threadIdx.x;
+  const SeqView v = ViewOf(g, seq);
+  const int32_t row0 = g.b_rs[seq], final_t = g.b_rs[seq + 1] - row0;
+  const int32_t T = g.T;
+  const int32_t gi = seq * g.a_stride;
+  const int32_t g_start = g.a_rs1[gi], g_states = g.a_rs1[gi + 1] - g_start;
+
+  // frame 0: the start state, if the graph has states (:435-472)
+  int32_t s0 = 0, ns = g_states > 0 ? 1 : 0, a0 = 0;
+  if (tid == 0) {
+    sh.beam = g.search_beam;
+    v.frame_s0[0] = 0;
+    v.frame_a0[0] = 0;
+    if (ns) {
+      v.st_astate[0] = g_start;
+      v.st_fwd[0] = OrderedInt(0.0f);
+    }
+  }
+  __syncthreads();
+  int32_t s_top = ns, a_top = 0;
+  int32_t status = kSeqOk;
+  int32_t next_end = kWindowShift;  // end of the next pruning window
+  for (int32_t t = 0; t < T; ++t) {
+    int32_t na, nn;
+    if (!SearchStep(g, v, &sh, seq, t, final_t, row0, s0, ns, a0, &na, &nn)) {
+      status = kSeqOverflow;
+      break;
+    }
+    s0 += ns;
+    a0 += na;
+    ns = nn;
+    s_top = s0 + ns;
+    a_top = a0;
+    if (tid == 0) {
+      v.frame_s0[t + 1] = s0;
+      v.frame_a0[t + 1] = a0;
+    }
+    __syncthreads();
+    const int32_t this_end = next_end >= T ? T : next_end;
+    if (t == this_end - 1) {
+      const int32_t begin = max(0, next_end - kWindow);
+      PruneWindow(g, v, &sh, seq, begin, this_end, &s_top, &a_top);
+      s0 = s_top - ns;
+      a0 = a_top;
+      next_end += kWindowShift;
+    }
+  }
+  if (tid == 0) {
+    int32_t extra = 0;
+    if (status == kSeqOk) {
+      v.frame_s0[T + 1] = s_top;  // frame T has no arcs
+      v.frame_a0[T + 1] = a_top;
+      v.st_arc0[s_top] = a_top;
+      // a sequence whose final state did not survive still gets a final state, so
+      // that the result is a valid FSA (:519-547)
+      const int32_t at_final = v.frame_s0[final_t + 1] - v.frame_s0[final_t];
+      if (at_final > 1) status = kSeqManyFinal;
+      extra = (g_states > 0) * (1 - min(at_final, 1));
+    }
+    int32_t *o = g.seq_out + 4 * seq;
+    o[0] = s_top + extra;
+    o[1] = a_top;
+    o[2] = extra;
+    o[3] = status;
+  }
+}
+
+struct FormatArgs {
+  SearchArgs g;
+  const int32_t *out_rs1;   // [num_seqs + 1] first lattice state of every sequence
+  const int32_t *arc_base;  // [num_seqs + 1] first lattice arc of every sequence
+  int32_t *row_ids1, *row_splits2, *row_ids2;
+  Arc *arcs;
+  int32_t *arc_map_a, *arc_map_b;
+  int32_t *level_offsets, *level_splits;
+};
+
+// Lattice of one (sequence, frame) per CTA (FormatOutput, :474-657): the arenas are
+// already in [sequence][frame][state][arc] order.
+__global__ void FormatPruned(const FormatArgs f) {
+  const SearchArgs &g = f.g;
+  const int32_t seq = blockIdx.y, t = blockIdx.x;  // t in [0, T + 1]
+  const SeqView v = ViewOf(g, seq);
+  const int32_t row0 = g.b_rs[seq], final_t = g.b_rs[seq + 1] - row0;
+  const int32_t sb = f.out_rs1[seq], ab = f.arc_base[seq];
+  const int32_t s0 = v.frame_s0[t], s1 = v.frame_s0[t + 1];
+  if (f.level_splits != nullptr && threadIdx.x == 0) {
+    f.level_splits[(int64_t)seq * (g.T + 2) + t] = sb + s0;
+    if (t == 0) f.level_offsets[seq] = seq * (g.T + 2);
+    if (seq == g.num_seqs - 1 && t == g.T + 1) {
+      f.level_offsets[g.num_seqs] = g.num_seqs * (g.T + 2);
+      f.level_splits[(int64_t)g.num_seqs * (g.T + 2)] = f.out_rs1[g.num_seqs];
+    }
+  }
+  if (t == g.T + 1) {
+    // the extra final state, if any, and the end of the row_splits
+    if (threadIdx.x == 0) {
+      const int32_t extra = g.seq_out[4 * seq + 2];
+      if (extra) {
+        f.row_ids1[sb + s0] = seq;
+        f.row_splits2[sb + s0] = ab + g.seq_out[4 * seq + 1];
+      }
+      if (seq == g.num_seqs - 1) f.row_splits2[f.out_rs1[g.num_seqs]] = f.arc_base[g.num_seqs];
+    }
+    return;
+  }
+  const int32_t next_s0 = s1;  // the states of frame t + 1 start where frame t ends
+  for (int32_t k = s0 + threadIdx.x; k < s1; k += blockDim.x) {
+    const int32_t p0 = v.st_arc0[k], p1 = v.st_arc0[k + 1];
+    f.row_ids1[sb + k] = seq;
+    f.row_splits2[sb + k] = ab + p0;
+    for (int32_t p = p0; p < p1; ++p) {
+      int32_t aidx = v.arc_aidx[p];
+      const int32_t graph_label = g.a_arcs[aidx].label;
+      Arc out;
+      out.src = k;
+      out.dest = next_s0 + v.arc_dest[p];
+      out.label = graph_label;
+      out.score = v.arc_ll[p];
+      if (t == final_t - 1 && graph_label != -1) {  // allow_partial (:625-634)
+        out.label = -1;
+        aidx = -1;
+      }
+      f.arcs[ab + p] = out;
+      f.row_ids2[ab + p] = sb + k;
+      f.arc_map_a[ab + p] = aidx;
+      f.arc_map_b[ab + p] = (row0 + t) * g.cols + graph_label + 1;
+    }
+  }
+}
+
+
+// Carves the workspace.  Everything is sized from the arguments alone, so the
+// search and the output call agree on it.
+struct PrunedLayout {
+  SearchArgs g;
+  int32_t *out_rs1, *arc_base;  // [num_seqs + 1] each
+  size_t winner_bytes, bytes;
+};
+
+size_t Take(size_t *off, size_t n) {
+  const size_t at = *off;
+  *off += AlignUp(n);
+  return at;
+}
+
+int32_t MakePrunedLayout(const k2b200_pruned_args *a, char *ws, PrunedLayout *L) {
+  K2B_REQUIRE(a != nullptr, "NULL arguments");
+  K2B_REQUIRE(a->search_beam > 0 && a->output_beam > 0, "search_beam and output_beam must be positive");
+  K2B_REQUIRE(a->min_active_states >= 0 && a->max_active_states > a->min_active_states,
+              "need 0 <= min_active_states < max_active_states");
+  K2B_REQUIRE(a->num_seqs >= 1 && a->num_seqs <= 65535, "num_seqs must be in [1, 65535]");
+  K2B_REQUIRE(a->num_fsas == a->num_seqs || a->num_fsas == 1,
+              "a_fsas must hold one graph per sequence or a single shared graph (got %d graphs "
+              "for %d sequences)", a->num_fsas, a->num_seqs);
+  K2B_REQUIRE(a->h_b_row_splits != nullptr, "NULL h_b_row_splits");
+  K2B_REQUIRE(a->max_states_per_seq >= 2 && a->max_arcs_per_seq >= 1 &&
+                  a->max_states_per_seq < 0x7f000000 && a->max_arcs_per_seq < 0x7f000000,
+              "arena capacities out of range");
+  int32_t T = 0;
+  for (int32_t i = 0; i < a->num_seqs; ++i) {
+    const int32_t rows = a->h_b_row_splits[i + 1] - a->h_b_row_splits[i];
+    K2B_REQUIRE(rows >= 1, "sequence %d has no rows", i);
+    T = std::max(T, rows);
+  }
+  K2B_REQUIRE(a->h_b_row_splits[a->num_seqs] == a->rows, "b row_splits do not cover the scores");
+  SearchArgs &g = L->g;
+  g.a_rs1 = a->a_row_splits1;
+  g.a_rs2 = a->a_row_splits2;
+  g.a_arcs = reinterpret_cast<const Arc *>(a->a_arcs);
+  g.a_stride = a->num_fsas == 1 && a->num_seqs > 1 ? 0 : 1;
+  g.a_states = a->num_states;
+  g.scores = a->scores;
+  g.rows = a->rows;
+  g.cols = a->cols;
+  g.b_rs = a->b_row_splits;
+  g.num_seqs = a->num_seqs;
+  g.T = T;
+  g.search_beam = a->search_beam;
+  g.output_beam = a->output_beam;
+  g.min_active = (float)a->min_active_states;
+  g.max_active = (float)a->max_active_states;
+  g.allow_partial = a->allow_partial;
+  g.cap_s = a->max_states_per_seq;
+  g.cap_a = a->max_arcs_per_seq;
+  const size_t n = (size_t)a->num_seqs, ns = n * ((size_t)g.cap_s + 1), na = n * (size_t)g.cap_a;
+  size_t off = 0;
+  auto i32 = [&](size_t count) { return reinterpret_cast<int32_t *>(ws + Take(&off, 4 * count)); };
+  auto f32 = [&](size_t count) { return reinterpret_cast<float *>(ws + Take(&off, 4 * count)); };
+  g.st_astate = i32(ns);
+  g.st_fwd = i32(ns);
+  g.st_arc0 = i32(ns);
+  g.st_new = i32(ns);
+  g.st_bwd = f32(ns);
+  g.arc_aidx = i32(na);
+  g.arc_dest = i32(na);
+  g.arc_ll = f32(na);
+  g.arc_end = f32(na);
+  g.arc_keep = reinterpret_cast<uint8_t *>(ws + Take(&off, na));
+  L->winner_bytes = 4 * (g.a_stride ? (size_t)std::max(a->num_states, 1)
+                                    : n * (size_t)std::max(a->num_states, 1));
+  g.winner = reinterpret_cast<int32_t *>(ws + Take(&off, L->winner_bytes));
+  g.frame_s0 = i32(n * ((size_t)T + 2));
+  g.frame_a0 = i32(n * ((size_t)T + 2));
+  g.seq_out = i32(4 * n);
+  L->out_rs1 = i32(n + 1);
+  L->arc_base = i32(n + 1);
+  L->bytes = off;
+  return kOk;
+}
+
+}  // namespace
+}  // namespace k2b
+
+using namespace k2b;  // NOLINT
+
+extern "C" {
+
+int32_t k2b200_intersect_dense_pruned_workspace_bytes(const k2b200_pruned_args *args,
+                                                      size_t *bytes, int64_t *total_levels) {
+  PrunedLayout L;
+  K2B_FORWARD(MakePrunedLayout(args, nullptr, &L));
+  K2B_REQUIRE(bytes != nullptr, "NULL bytes");
+  *bytes = L.bytes;
+  if (total_levels) *total_levels = (int64_t)args->num_seqs * (L.g.T + 2);
+  return kOk;
+}
+
+int32_t k2b200_intersect_dense_pruned_search(const k2b200_pruned_args *args, void *workspace,
+                                             size_t workspace_bytes, void *stream_v,
+                                             int32_t *num_states_out, int32_t *num_arcs_out,
+                                             int32_t *arena_full) {
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_v);
+  PrunedLayout L;
+  K2B_FORWARD(MakePrunedLayout(args, reinterpret_cast<char *>(workspace), &L));
+  K2B_REQUIRE(workspace != nullptr && workspace_bytes >= L.bytes, "workspace too small");
+  K2B_REQUIRE(num_states_out && num_arcs_out && arena_full, "NULL output pointer");
+  K2B_REQUIRE(args->a_row_splits1 && args->a_row_splits2 && args->b_row_splits &&
+                  (args->a_arcs || args->num_arcs == 0) && args->scores,
+              "NULL input pointer");
+  const int32_t n = args->num_seqs;
+  K2B_CUDA_OK(cudaMemsetAsync(L.g.winner, 0x7f, L.winner_bytes, stream));
+  { PrunedSearch<<<n, kSearchThreads, 0, stream>>>(L.g); NoteLaunch(); }
+  K2B_CUDA_OK(cudaGetLastError());
+  std::vector<int32_t> h(4 * (size_t)n);
+  K2B_CUDA_OK(cudaMemcpyAsync(h.data(), L.g.seq_out, sizeof(int32_t) * h.size(),
+                              cudaMemcpyDeviceToHost, stream));
+  K2B_CUDA_OK(cudaStreamSynchronize(stream));
+  std::vector<int32_t> bases(2 * ((size_t)n + 1));
+  int32_t *srs = bases.data(), *ars = bases.data() + n + 1;
+  int64_t ts = 0, ta = 0;
+  *arena_full = 0;
+  for (int32_t i = 0; i < n; ++i) {
+    if (h[4 * i + 3] == kSeqOverflow) *arena_full = 1;
+    K2B_REQUIRE(h[4 * i + 3] != kSeqManyFinal,
+                "sequence %d reaches more than one state on its last frame: arcs with label -1 "
+                "must enter the final state of their graph", i);
+    srs[i] = (int32_t)ts;
+    ars[i] = (int32_t)ta;
+    ts += h[4 * i + 0];
+    ta += h[4 * i + 1];
+  }
+  srs[n] = (int32_t)ts;
+  ars[n] = (int32_t)ta;
+  *num_states_out = *num_arcs_out = 0;
+  if (*arena_full) return kOk;
+  K2B_REQUIRE(ts < INT_MAX && ta < INT_MAX, "the lattice has too many states or arcs for int32");
+  // out_rs1 and arc_base are adjacent in the workspace only up to alignment: two uploads
+  K2B_FORWARD(UploadInts(srs, n + 1, L.out_rs1, stream));
+  K2B_FORWARD(UploadInts(ars, n + 1, L.arc_base, stream));
+  *num_states_out = (int32_t)ts;
+  *num_arcs_out = (int32_t)ta;
+  return kOk;
+}
+
+int32_t k2b200_intersect_dense_pruned_emit(const k2b200_pruned_args *args, void *workspace,
+                                           size_t workspace_bytes, void *stream_v,
+                                           const k2b200_lattice_out *out) {
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_v);
+  PrunedLayout L;
+  K2B_FORWARD(MakePrunedLayout(args, reinterpret_cast<char *>(workspace), &L));
+  K2B_REQUIRE(workspace != nullptr && workspace_bytes >= L.bytes, "workspace too small");
+  K2B_REQUIRE(out && out->row_splits1 && out->row_ids1 && out->row_splits2 && out->row_ids2 &&
+                  out->arcs && out->arc_map_a && out->arc_map_b,
+              "NULL output pointer");
+  K2B_REQUIRE((out->level_offsets == nullptr) == (out->level_splits == nullptr),
+              "level_offsets and level_splits go together");
+  FormatArgs f;
+  f.g = L.g;
+  f.out_rs1 = L.out_rs1;
+  f.arc_base = L.arc_base;
+  f.row_ids1 = out->row_ids1;
+  f.row_splits2 = out->row_splits2;
+  f.row_ids2 = out->row_ids2;
+  f.arcs = reinterpret_cast<Arc *>(out->arcs);
+  f.arc_map_a = out->arc_map_a;
+  f.arc_map_b = out->arc_map_b;
+  f.level_offsets = out->level_offsets;
+  f.level_splits = out->level_splits;
+  K2B_CUDA_OK(cudaMemcpyAsync(out->row_splits1, L.out_rs1, sizeof(int32_t) * (args->num_seqs + 1),
+                              cudaMemcpyDeviceToDevice, stream));
+  dim3 grid(L.g.T + 2, args->num_seqs);
+  { FormatPruned<<<grid, 128, 0, stream>>>(f); NoteLaunch(); }
+  K2B_CUDA_OK(cudaGetLastError());
+  return kOk;
+}
+
+}  // extern "C"

@@ -58,6 +58,10 @@ def lib():
         L.kref_intersect_dense.argtypes = [ctypes.c_void_p, _f32p, ctypes.c_int32,
                                            ctypes.c_int32, _i32p, ctypes.c_int32, _i32p,
                                            ctypes.c_float, ctypes.c_int32, ctypes.c_int32]
+        L.kref_intersect_dense_pruned.restype = ctypes.c_void_p
+        L.kref_intersect_dense_pruned.argtypes = [
+            ctypes.c_void_p, _f32p, ctypes.c_int32, ctypes.c_int32, _i32p, ctypes.c_int32,
+            ctypes.c_float, ctypes.c_float, ctypes.c_int32, ctypes.c_int32, ctypes.c_int32]
         L.kref_forward_scores.argtypes = [ctypes.c_void_p, ctypes.c_int32, ctypes.c_int32,
                                           _f64p, _i32p]
         L.kref_backward_scores.argtypes = [ctypes.c_void_p, ctypes.c_int32, ctypes.c_int32,
@@ -146,6 +150,20 @@ def intersect_dense(a: HostFsaVec, scores: np.ndarray, b_row_splits: np.ndarray,
                                              scores.shape[1], _p(brs, _i32p), len(brs) - 1,
                                              _p(m, _i32p), float(output_beam),
                                              int(max_states), int(max_arcs)))
+    return out.to_host(maps=True)
+
+
+def intersect_dense_pruned(a: HostFsaVec, scores, b_row_splits, search_beam, output_beam,
+                           min_active, max_active, allow_partial=False):
+    """The reference's IntersectDensePruned on CPU; `a` holds one graph per sequence or a
+    single shared graph.  Returns a HostFsaVec with arc_map_a / arc_map_b."""
+    ha = to_handle(a)
+    scores = np.ascontiguousarray(scores, np.float32)
+    brs = np.ascontiguousarray(b_row_splits, np.int32)
+    out = _Handle(lib().kref_intersect_dense_pruned(
+        ha.ptr, _p(scores, _f32p), scores.shape[0], scores.shape[1], _p(brs, _i32p),
+        len(brs) - 1, float(search_beam), float(output_beam), int(min_active),
+        int(max_active), int(bool(allow_partial))))
     return out.to_host(maps=True)
 
 

@@ -202,6 +202,35 @@ void *kref_intersect_dense(void *a_handle, const float *scores, int32_t rows,
   KREF_CATCH(nullptr)
 }
 
+// Pruned intersection (k2/csrc/intersect_dense_pruned.cu:1678-1694).  a_handle holds
+// one graph per sequence, or a single graph shared by all of them.
+void *kref_intersect_dense_pruned(void *a_handle, const float *scores, int32_t rows,
+                                  int32_t cols, const int32_t *b_row_splits,
+                                  int32_t num_seqs, float search_beam,
+                                  float output_beam, int32_t min_active,
+                                  int32_t max_active, int32_t allow_partial) {
+  KREF_TRY
+  auto *a = reinterpret_cast<FsaVecHandle *>(a_handle);
+  k2::ContextPtr c = k2::GetCpuContext();
+  k2::Array2<float> sc(c, rows, cols);
+  if (rows * cols > 0)
+    memcpy(sc.Data(), scores, sizeof(float) * (size_t)rows * (size_t)cols);
+  k2::Array1<int32_t> brs = FromHost(b_row_splits, num_seqs + 1);
+  k2::RaggedShape bshape = k2::RaggedShape2(&brs, nullptr, rows);
+  k2::DenseFsaVec b(bshape, sc);
+  auto *out = new FsaVecHandle;
+  try {
+    k2::IntersectDensePruned(a->fsas, b, search_beam, output_beam, min_active,
+                             max_active, allow_partial != 0, &out->fsas,
+                             &out->arc_map_a, &out->arc_map_b);
+  } catch (...) {
+    delete out;
+    throw;
+  }
+  return out;
+  KREF_CATCH(nullptr)
+}
+
 // Forward scores of a top-sorted acyclic FsaVec.  `out` is [num_states] double
 // (float results are widened exactly).  entering_arcs may be NULL; it is only
 // filled when log_semiring == 0.

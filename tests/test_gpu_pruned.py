@@ -1,0 +1,128 @@
+"""Pruned intersection (k2.intersect_dense_pruned) on the GPU against the reference's
+own CPU code: bit-identical lattices and arc maps.  The small cases are checked
+against committed answers (tests/golden/pruned_cases.npz, made by
+tests/golden/make_pruned_golden.py); the larger ones against the reference library
+itself when it has been built (oracle/_ref)."""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import ref
+from oracle.common import HostFsaVec
+from pruned_util import decoding_graph, pruned_cases
+from util import random_dense, same_fsa
+
+pytestmark = pytest.mark.gpu
+
+GOLDEN = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "pruned_cases.npz")
+
+
+@pytest.fixture(scope="module")
+def k2():
+    import k2_b200
+    return k2_b200
+
+
+def run_gpu(k2, c, requires_grad=False):
+    from gpu_util import dense_from_scores, fsa_to_host, host_to_fsa
+    from k2_b200.autograd import _intersect_dense_pruned_arcs
+    a = host_to_fsa(c["a"])
+    dense = dense_from_scores(c["scores"], c["brs"])
+    sb, ob, mn, mx, partial = c["params"]
+    ragged, ma, mb = _intersect_dense_pruned_arcs(a.arcs, dense, sb, ob, mn, mx, partial)
+    lat = k2.Fsa(ragged, _check=False)
+    return lat, fsa_to_host(lat, ma, mb)
+
+
+def test_small_cases_match_the_committed_reference_answers(k2):
+    z = np.load(GOLDEN)
+    cases = {c["name"]: c for c in pruned_cases(small=True)}
+    assert sorted(cases) == sorted(z["names"].tolist())
+    for name, c in cases.items():
+        want = HostFsaVec(z[f"{name}.l_rs1"], z[f"{name}.l_rs2"], z[f"{name}.l_arcs"],
+                          arc_map_a=z[f"{name}.map_a"], arc_map_b=z[f"{name}.map_b"])
+        _, got = run_gpu(k2, c)
+        same_fsa(got, want, name)
+
+
+@pytest.mark.skipif(not ref.available(), reason="oracle/_ref/libk2ref.so not built")
+def test_larger_cases_match_the_reference_library(k2):
+    for c in pruned_cases(small=False):
+        want = ref.intersect_dense_pruned(c["a"], c["scores"], c["brs"], *c["params"])
+        _, got = run_gpu(k2, c)
+        same_fsa(got, want, c["name"])
+
+
+@pytest.mark.skipif(not ref.available(), reason="oracle/_ref/libk2ref.so not built")
+def test_decoding_graph_many_windows(k2):
+    rng = np.random.default_rng(5)
+    g = decoding_graph(rng, 3000, 40, mean_degree=4.0)
+    scores, brs = random_dense(rng, 6, 300, 40, scale=2.0, low_rows=False)
+    for params in ((12.0, 5.0, 30, 400, False), (8.0, 4.0, 10, 60, True)):
+        c = dict(a=g, scores=scores, brs=brs, params=params)
+        want = ref.intersect_dense_pruned(g, scores, brs, *params)
+        lat, got = run_gpu(k2, c)
+        same_fsa(got, want, str(params))
+        assert want.num_arcs > 1000
+
+
+def test_public_api_scores_attributes_and_gradients(k2):
+    from gpu_util import DEV, host_to_fsa
+    c = pruned_cases(small=True)[0]
+    a = host_to_fsa(c["a"])
+    a.aux_labels = torch.arange(a.arcs.num_elements(), dtype=torch.int32, device=DEV)
+    a.scores.requires_grad_(True)
+    scores = torch.from_numpy(c["scores"]).to(DEV).requires_grad_(True)
+    dense = k2.DenseFsaVec._from_dense_fsa_vec(scores, c["brs"])
+    lat = k2.intersect_dense_pruned(a, dense, 20.0, 8.0, 0, 10000, seqframe_idx_name="seqframe",
+                                    frame_idx_name="frame")
+    z = np.load(GOLDEN)
+    map_a, map_b = z["ctc_wide.map_a"], z["ctc_wide.map_b"]
+    np.testing.assert_array_equal(lat.aux_labels.cpu().numpy(), map_a)
+    np.testing.assert_array_equal(lat.seqframe.cpu().numpy(), map_b // c["scores"].shape[1])
+    row_of = np.repeat(np.arange(len(c["brs"]) - 1), np.diff(c["brs"]))
+    np.testing.assert_array_equal(lat.frame.cpu().numpy(),
+                                  map_b // c["scores"].shape[1] - c["brs"][row_of[
+                                      map_b // c["scores"].shape[1]]])
+    w = torch.linspace(0.5, 1.5, lat.scores.numel(), device=DEV)
+    (lat.scores * w).sum().backward()
+    ga = np.zeros(a.arcs.num_elements(), np.float32)
+    np.add.at(ga, map_a, w.cpu().numpy())
+    gb = np.zeros(c["scores"].size, np.float32)
+    np.add.at(gb, map_b, w.cpu().numpy())
+    np.testing.assert_allclose(a.scores.grad.cpu().numpy(), ga, rtol=1e-6)
+    np.testing.assert_allclose(scores.grad.cpu().numpy().reshape(-1), gb, rtol=1e-6)
+    # the lattice is a valid, top-sorted FsaVec whose best path has the tropical total
+    tot = lat.get_tot_scores(use_double_scores=True, log_semiring=False)
+    best = k2.shortest_path(lat, use_double_scores=True)
+    assert torch.allclose(best.get_tot_scores(use_double_scores=True, log_semiring=False), tot)
+
+
+def test_argument_checks(k2):
+    from gpu_util import dense_from_scores, host_to_fsa
+    cs = pruned_cases(small=True)
+    a = host_to_fsa(cs[0]["a"])
+    dense = dense_from_scores(cs[0]["scores"], cs[0]["brs"])
+    with pytest.raises(RuntimeError, match="positive"):
+        k2.intersect_dense_pruned(a, dense, 0.0, 8.0, 0, 100)
+    with pytest.raises(RuntimeError, match="min_active"):
+        k2.intersect_dense_pruned(a, dense, 20.0, 8.0, 10, 10)
+    two = host_to_fsa(HostFsaVec(cs[0]["a"].row_splits1[:3], cs[0]["a"].row_splits2[
+        :cs[0]["a"].row_splits1[2] + 1], cs[0]["a"].arcs[:cs[0]["a"].row_splits2[
+            cs[0]["a"].row_splits1[2]]]))
+    with pytest.raises(RuntimeError, match="one graph per sequence"):
+        k2.intersect_dense_pruned(two, dense, 20.0, 8.0, 0, 100)
+
+
+def test_small_arena_is_grown(k2, monkeypatch):
+    from k2_b200 import autograd
+    monkeypatch.setattr(autograd, "PRUNED_ARCS_TOTAL", 1 << 8)
+    monkeypatch.setattr(autograd, "PRUNED_ARCS_MIN", 1 << 6)
+    c = pruned_cases(small=True)[3]
+    z = np.load(GOLDEN)
+    want = HostFsaVec(z["shared_wide.l_rs1"], z["shared_wide.l_rs2"], z["shared_wide.l_arcs"],
+                      arc_map_a=z["shared_wide.map_a"], arc_map_b=z["shared_wide.map_b"])
+    _, got = run_gpu(k2, c)
+    same_fsa(got, want, "after growing the arena")
