@@ -299,6 +299,9 @@ typedef struct {
   /* capacity, per sequence, for the states and arcs alive at any one time: the
    * pruned frames so far plus the unpruned last 30 */
   int64_t max_states_per_seq, max_arcs_per_seq;
+  /* CTAs (a thread-block cluster) that share one sequence: 0 = as many as keep
+   * the GPU filled, else 1, 2, 4 or 8.  The result does not depend on it. */
+  int32_t team_ctas;
 } k2b200_pruned_args;
 
 int32_t k2b200_intersect_dense_pruned_workspace_bytes(const k2b200_pruned_args *args,

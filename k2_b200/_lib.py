@@ -54,7 +54,7 @@ class PrunedArgs(ctypes.Structure):
         ("b_row_splits", c_vp), ("h_b_row_splits", c_vp),
         ("search_beam", c_f32), ("output_beam", c_f32),
         ("min_active_states", c_i32), ("max_active_states", c_i32), ("allow_partial", c_i32),
-        ("max_states_per_seq", c_i64), ("max_arcs_per_seq", c_i64),
+        ("max_states_per_seq", c_i64), ("max_arcs_per_seq", c_i64), ("team_ctas", c_i32),
     ]
 
 

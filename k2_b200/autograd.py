@@ -274,9 +274,11 @@ PRUNED_ARCS_MIN = 1 << 16
 
 def _intersect_dense_pruned_arcs(a: RaggedArc, b: DenseFsaVec, search_beam: float,
                                  output_beam: float, min_active_states: int,
-                                 max_active_states: int, allow_partial: bool):
+                                 max_active_states: int, allow_partial: bool,
+                                 team_ctas: int = 0):
     """The `_k2.intersect_dense_pruned` call (k2/python/csrc/torch/fsa_algo.cu:200-222):
-    returns (RaggedArc lattice, arc_map_a, arc_map_b)."""
+    returns (RaggedArc lattice, arc_map_a, arc_map_b).  `team_ctas` (0 = automatic) is
+    the number of CTAs that share a sequence; it changes the speed only."""
     dev = b.scores.device
     _lib.require_cuda(a.values(), "a_fsas")
     _lib.require_cuda(b.scores, "b_fsas.scores")
@@ -298,7 +300,7 @@ def _intersect_dense_pruned_arcs(a: RaggedArc, b: DenseFsaVec, search_beam: floa
             h_b_row_splits=h_brs.ctypes.data, search_beam=search_beam, output_beam=output_beam,
             min_active_states=min_active_states, max_active_states=max_active_states,
             allow_partial=int(bool(allow_partial)), max_states_per_seq=max(cap_a // 2, 2),
-            max_arcs_per_seq=cap_a)
+            max_arcs_per_seq=cap_a, team_ctas=team_ctas)
         nbytes, levels = ctypes.c_size_t(), ctypes.c_int64()
         _lib.check(_lib.lib.k2b200_intersect_dense_pruned_workspace_bytes(
             ctypes.byref(args), ctypes.byref(nbytes), ctypes.byref(levels)))

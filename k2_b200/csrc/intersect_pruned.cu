@@ -24,8 +24,12 @@
 #include <cstring>
 #include <vector>
 
+#include <cooperative_groups.h>
+
 #include "common.cuh"
 #include "../../include/k2b200.h"
+
+namespace cg = cooperative_groups;
 
 namespace k2b {
 namespace {
@@ -71,52 +75,122 @@ struct SearchArgs {
 
 enum : int32_t { kSeqOk = 0, kSeqOverflow = 1, kSeqManyFinal = 2 };
 
-// exclusive scan of one int per thread over the CTA; every thread gets the total
-__device__ __forceinline__ int32_t BlockScan(int32_t v, int32_t *total, int32_t *sh) {
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  int32_t inc = v;
-#pragma unroll
-  for (int d = 1; d < 32; d <<= 1) {
-    int32_t o = __shfl_up_sync(0xffffffffu, inc, d);
-    if (lane >= d) inc += o;
+// The CTAs that work on one sequence: a thread-block cluster (of one CTA when there are
+// enough sequences to fill the GPU).  Arena data is exchanged through global memory,
+// ordered by the cluster barrier; scan totals and maxima through distributed shared
+// memory.  Item k of a pass is handled by team thread k mod team size, and the CTAs
+// of a cluster are always co-resident, so the barrier cannot wait for an unscheduled
+// CTA.
+struct Shared {
+  int32_t scan[65];
+  float fmax[33];
+  int32_t team_i[2];  // this CTA's contribution to the team-wide scan / or
+  float team_f[2];    // ... and to the team-wide max; two slots used alternately
+  int32_t phase_i, phase_f;
+  float cutoff;
+  float beam;
+};
+
+struct Team {
+  cg::cluster_group cluster;
+  Shared *sh;
+  int32_t rank, size;     // this CTA within the cluster
+  int32_t tid, threads;   // this thread within the team
+
+  __device__ Team(Shared *shared) : cluster(cg::this_cluster()), sh(shared) {
+    rank = (int32_t)cluster.block_rank();
+    size = (int32_t)cluster.num_blocks();
+    tid = rank * kSearchThreads + (int32_t)threadIdx.x;
+    threads = size * kSearchThreads;
   }
-  if (lane == 31) sh[warp] = inc;
-  __syncthreads();
-  if (warp == 0) {
-    int32_t w = sh[lane];
-    int32_t winc = w;
+  __device__ __forceinline__ void Sync() const {
+    if (size == 1) __syncthreads(); else cluster.sync();
+  }
+
+  // exclusive scan of one int per team thread; every thread gets the total
+  __device__ int32_t Scan(int32_t v, int32_t *total) const {
+    int32_t *s = sh->scan;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    int32_t inc = v;
 #pragma unroll
     for (int d = 1; d < 32; d <<= 1) {
-      int32_t o = __shfl_up_sync(0xffffffffu, winc, d);
-      if (lane >= d) winc += o;
+      int32_t o = __shfl_up_sync(0xffffffffu, inc, d);
+      if (lane >= d) inc += o;
     }
-    sh[32 + lane] = winc - w;
-    if (lane == 31) sh[64] = winc;
+    if (lane == 31) s[warp] = inc;
+    __syncthreads();
+    if (warp == 0) {
+      int32_t w = s[lane];
+      int32_t winc = w;
+#pragma unroll
+      for (int d = 1; d < 32; d <<= 1) {
+        int32_t o = __shfl_up_sync(0xffffffffu, winc, d);
+        if (lane >= d) winc += o;
+      }
+      s[32 + lane] = winc - w;
+      if (lane == 31) s[64] = winc;
+    }
+    __syncthreads();
+    int32_t ex = s[32 + warp] + inc - v;
+    int32_t all = s[64];
+    if (size == 1) {
+      __syncthreads();  // s is reused by the next call
+      *total = all;
+      return ex;
+    }
+    // a slot is rewritten two calls later, after a cluster barrier that every CTA
+    // reaches only when it has read the slot
+    const int32_t slot = sh->phase_i & 1;
+    if (threadIdx.x == 0) sh->team_i[slot] = all;
+    cluster.sync();
+    int32_t before = 0, sum = 0;
+    for (int32_t r = 0; r < size; ++r) {
+      const int32_t x = *cluster.map_shared_rank(&sh->team_i[slot], r);
+      sum += x;
+      if (r < rank) before += x;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) sh->phase_i += 1;
+    __syncthreads();
+    *total = sum;
+    return before + ex;
   }
-  __syncthreads();
-  const int32_t ex = sh[32 + warp] + inc - v;
-  *total = sh[64];
-  __syncthreads();  // sh is reused by the next call
-  return ex;
-}
 
-__device__ __forceinline__ float BlockMax(float v, float *shf) {
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  __device__ float Max(float v) const {
+    float *s = sh->fmax;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
 #pragma unroll
-  for (int d = 16; d > 0; d >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, d));
-  if (lane == 0) shf[warp] = v;
-  __syncthreads();
-  if (warp == 0) {
-    float w = shf[lane];
+    for (int d = 16; d > 0; d >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, d));
+    if (lane == 0) s[warp] = v;
+    __syncthreads();
+    if (warp == 0) {
+      float w = s[lane];
 #pragma unroll
-    for (int d = 16; d > 0; d >>= 1) w = fmaxf(w, __shfl_xor_sync(0xffffffffu, w, d));
-    if (lane == 0) shf[32] = w;
+      for (int d = 16; d > 0; d >>= 1) w = fmaxf(w, __shfl_xor_sync(0xffffffffu, w, d));
+      if (lane == 0) s[32] = w;
+    }
+    __syncthreads();
+    float r = s[32];
+    const int32_t slot = sh->phase_f & 1;
+    if (threadIdx.x == 0) sh->team_f[slot] = r;
+    Sync();  // also orders the global writes made before the call
+    if (size > 1) {
+      for (int32_t k = 0; k < size; ++k)
+        r = fmaxf(r, *cluster.map_shared_rank(&sh->team_f[slot], k));
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) sh->phase_f += 1;
+    __syncthreads();
+    return r;
   }
-  __syncthreads();
-  const float r = shf[32];
-  __syncthreads();
-  return r;
-}
+
+  // true when `v` is non-zero on any thread of the team
+  __device__ bool Any(int32_t v) const {
+    int32_t total;
+    Scan(v != 0, &total);
+    return total != 0;
+  }
+};
 
 // Views of one sequence's slices of the arenas.
 struct SeqView {
@@ -149,14 +223,6 @@ __device__ __forceinline__ SeqView ViewOf(const SearchArgs &g, int32_t seq) {
   return v;
 }
 
-struct Shared {
-  int32_t scan[65];
-  float fmax[33];
-  float cutoff;
-  float beam;
-  int32_t flag;
-};
-
 // The search beam and the cutoff of frame t (:718-766).  `dyn` is the beam carried
 // from the previous frame; products with the literals 0.8, 0.2 and 1.25 are double
 // products in the reference and are rounded to float on assignment.
@@ -182,31 +248,33 @@ __device__ float NextBeam(float dyn, float best, int32_t active, int32_t t, int3
   return dyn;
 }
 
+constexpr int kPer = 4;  // consecutive arcs per thread in the scan-heavy passes
+
 // One step of the search (GetArcs + PropagateForward, :778-1153): expands the arcs
 // leaving the ns states of frame t at [s0, s0 + ns), which start at arena position
 // a0, and creates the states of frame t + 1 behind them.  Returns false when an
 // arena is full.  *na_out / *ns_next: arcs of frame t and states of frame t + 1.
-__device__ bool SearchStep(const SearchArgs &g, const SeqView &v, Shared *sh, int32_t seq,
+__device__ bool SearchStep(const SearchArgs &g, const SeqView &v, const Team &tm, int32_t seq,
                            int32_t t, int32_t final_t, int32_t row0, int32_t s0, int32_t ns,
                            int32_t a0, int32_t *na_out, int32_t *ns_next) {
-  const int tid = threadIdx.x;
+  Shared *sh = tm.sh;
   const float kNegInf = -INFINITY;
   // arc ranges of the states (row_splits of [state][arc] on this frame)
   int32_t na = 0;
-  for (int32_t base = 0; base < ns; base += kSearchThreads) {
-    const int32_t k = base + tid;
+  for (int32_t base = 0; base < ns; base += tm.threads) {
+    const int32_t k = base + tm.tid;
     int32_t deg = 0;
     if (k < ns) {
       const int32_t as = v.st_astate[s0 + k];
       deg = g.a_rs2[as + 1] - g.a_rs2[as];
     }
     int32_t tot;
-    const int32_t ex = BlockScan(deg, &tot, sh->scan);
+    const int32_t ex = tm.Scan(deg, &tot);
     if (k < ns) v.st_arc0[s0 + k] = a0 + na + ex;
     na += tot;
   }
   if ((int64_t)a0 + na > g.cap_a) return false;
-  if (tid == 0) v.st_arc0[s0 + ns] = a0 + na;
+  if (tm.tid == 0) v.st_arc0[s0 + ns] = a0 + na;
 
   // graph of this sequence: its final state, for allow_partial (:861-871)
   const int32_t gi = seq * g.a_stride;
@@ -215,11 +283,11 @@ __device__ bool SearchStep(const SearchArgs &g, const SeqView &v, Shared *sh, in
   if (g.allow_partial && t == final_t - 1) {
     // is there any arc with label -1 among the arcs expanded on this frame (:839-857)
     int32_t has = 0;
-    for (int32_t k = tid; k < ns; k += kSearchThreads) {
+    for (int32_t k = tm.tid; k < ns; k += tm.threads) {
       const int32_t as = v.st_astate[s0 + k];
       for (int32_t a = g.a_rs2[as]; a < g.a_rs2[as + 1]; ++a) has |= (g.a_arcs[a].label == -1);
     }
-    redirect = !__syncthreads_or(has);
+    redirect = !tm.Any(has);
   }
 
   // arcs: scores, destination (as a graph state) and the best end score (:858-905)
@@ -228,7 +296,7 @@ __device__ bool SearchStep(const SearchArgs &g, const SeqView &v, Shared *sh, in
   const bool row_ok = row0 + t < g.rows;
   const float *row = g.scores + (int64_t)(row_ok ? row0 + t : 0) * g.cols;
   float best = kNegInf;
-  for (int32_t k = tid; k < ns; k += kSearchThreads) {
+  for (int32_t k = tm.tid; k < ns; k += tm.threads) {
     const int32_t as = v.st_astate[s0 + k];
     const float fwd = OrderedFloat(v.st_fwd[s0 + k]);
     const int32_t ga0 = g.a_rs2[as], ga1 = g.a_rs2[as + 1];
@@ -251,40 +319,51 @@ __device__ bool SearchStep(const SearchArgs &g, const SeqView &v, Shared *sh, in
       best = fmaxf(best, end);
     }
   }
-  best = BlockMax(best, sh->fmax);  // also makes the arc records visible to the CTA
-  if (tid == 0) sh->beam = NextBeam(sh->beam, best, ns, t, final_t, g, &sh->cutoff);
+  best = tm.Max(best);  // also makes the arc records visible to the team
+  if (threadIdx.x == 0) sh->beam = NextBeam(sh->beam, best, ns, t, final_t, g, &sh->cutoff);
   __syncthreads();
   const float cutoff = sh->cutoff;
 
   // first arc above the cutoff into every destination state (:1005-1028)
-  for (int32_t q = tid; q < na; q += kSearchThreads) {
+  for (int32_t q = tm.tid; q < na; q += tm.threads) {
     if (v.arc_end[a0 + q] > cutoff) atomicMin(&v.winner[v.arc_dest[a0 + q]], q);
   }
-  __syncthreads();
+  tm.Sync();
   // number the new states in the order of their winning arcs (:1031-1100)
   const int32_t s1 = s0 + ns;
   int32_t nn = 0;
-  for (int32_t base = 0; base < na; base += kSearchThreads) {
-    const int32_t q = base + tid;
-    int32_t won = 0, dest = 0;
-    if (q < na) {
-      dest = v.arc_dest[a0 + q];
-      won = v.arc_end[a0 + q] > cutoff && v.winner[dest] == q;
+  for (int32_t base = 0; base < na; base += tm.threads * kPer) {
+    const int32_t q0 = base + tm.tid * kPer;
+    int32_t dest[kPer];
+    int32_t won = 0;  // bit i: arc q0 + i created its destination state
+#pragma unroll
+    for (int i = 0; i < kPer; ++i) {
+      dest[i] = 0;
+      if (q0 + i < na) {
+        dest[i] = v.arc_dest[a0 + q0 + i];
+        if (v.arc_end[a0 + q0 + i] > cutoff && v.winner[dest[i]] == q0 + i) won |= 1 << i;
+      }
     }
     int32_t tot;
-    const int32_t j = nn + BlockScan(won, &tot, sh->scan);
-    if (won && (int64_t)s1 + j < g.cap_s) {
-      v.st_astate[s1 + j] = dest;
-      v.st_fwd[s1 + j] = OrderedInt(kNegInf);
-      v.winner[dest] = -(j + 1);
+    int32_t j = nn + tm.Scan(__popc(won), &tot);
+#pragma unroll
+    for (int i = 0; i < kPer; ++i) {
+      if (won >> i & 1) {
+        if ((int64_t)s1 + j < g.cap_s) {
+          v.st_astate[s1 + j] = dest[i];
+          v.st_fwd[s1 + j] = OrderedInt(kNegInf);
+          v.winner[dest[i]] = -(j + 1);
+        }
+        ++j;
+      }
     }
     nn += tot;
   }
   if ((int64_t)s1 + nn > g.cap_s) return false;
-  __syncthreads();
+  tm.Sync();
   // destination index of every arc and the best score into every new state; an
   // arc below the cutoff still enters a state that another arc created (:1103-1138)
-  for (int32_t q = tid; q < na; q += kSearchThreads) {
+  for (int32_t q = tm.tid; q < na; q += tm.threads) {
     const int32_t w = v.winner[v.arc_dest[a0 + q]];
     int32_t idx1 = -1;
     if (w < 0) {
@@ -293,9 +372,9 @@ __device__ bool SearchStep(const SearchArgs &g, const SeqView &v, Shared *sh, in
     }
     v.arc_dest[a0 + q] = idx1;
   }
-  __syncthreads();
-  for (int32_t j = tid; j < nn; j += kSearchThreads) v.winner[v.st_astate[s1 + j]] = kNoWinner;
-  __syncthreads();
+  tm.Sync();
+  for (int32_t j = tm.tid; j < nn; j += tm.threads) v.winner[v.st_astate[s1 + j]] = kNoWinner;
+  tm.Sync();
   *na_out = na;
   *ns_next = nn;
   return true;
@@ -306,9 +385,8 @@ __device__ bool SearchStep(const SearchArgs &g, const SeqView &v, Shared *sh, in
 // :1239-1346), then compaction of those frames in place.  On entry the frames up to
 // `end` are complete and frame `end` has its states but no arcs yet; on return
 // *s_top / *a_top are the ends of the arenas and the frame tables are updated.
-__device__ void PruneWindow(const SearchArgs &g, const SeqView &v, Shared *sh, int32_t seq,
+__device__ void PruneWindow(const SearchArgs &g, const SeqView &v, const Team &tm, int32_t seq,
                             int32_t begin, int32_t end, int32_t *s_top, int32_t *a_top) {
-  const int tid = threadIdx.x;
   const float kNegInf = -INFINITY;
   const int32_t gi = seq * g.a_stride;
   const int32_t g_final = g.a_rs1[gi + 1] - 1;  // last state of this sequence's graph
@@ -316,19 +394,19 @@ __device__ void PruneWindow(const SearchArgs &g, const SeqView &v, Shared *sh, i
 
   {  // frame `end`: backward score = -forward score, whatever the state
     const int32_t s0 = v.frame_s0[end], ns = *s_top - s0;
-    for (int32_t k = tid; k < ns; k += kSearchThreads) {
+    for (int32_t k = tm.tid; k < ns; k += tm.threads) {
       const float fwd = OrderedFloat(v.st_fwd[s0 + k]);
       v.st_bwd[s0 + k] = (fwd - fwd == 0.0f) ? -fwd : kNegInf;
     }
   }
-  __syncthreads();
+  tm.Sync();
 
   // backwards: arc and state survival, backward scores, new state numbers
   for (int32_t t = end - 1; t >= begin; --t) {
     const int32_t s0 = v.frame_s0[t], ns = v.frame_s0[t + 1] - s0, s_next = v.frame_s0[t + 1];
     int32_t kept = 0;
-    for (int32_t base = 0; base < ns; base += kSearchThreads) {
-      const int32_t k = base + tid;
+    for (int32_t base = 0; base < ns; base += tm.threads) {
+      const int32_t k = base + tm.tid;
       int32_t keep_state = 0;
       if (k < ns) {
         const float fwd = OrderedFloat(v.st_fwd[s0 + k]);
@@ -351,11 +429,11 @@ __device__ void PruneWindow(const SearchArgs &g, const SeqView &v, Shared *sh, i
         keep_state = (bwd != kNegInf) || t == begin;
       }
       int32_t tot;
-      const int32_t j = kept + BlockScan(keep_state, &tot, sh->scan);
+      const int32_t j = kept + tm.Scan(keep_state, &tot);
       if (k < ns) v.st_new[s0 + k] = keep_state ? j : -1;
       kept += tot;
     }
-    __syncthreads();
+    tm.Sync();
   }
 
   // forwards: move the surviving states and arcs down.  Reads of a chunk complete
@@ -366,10 +444,9 @@ __device__ void PruneWindow(const SearchArgs &g, const SeqView &v, Shared *sh, i
   for (int32_t t = begin; t < end; ++t) {
     const int32_t old_s1 = v.frame_s0[t + 1], old_a1 = v.frame_a0[t + 1];
     const int32_t ns = old_s1 - old_s0, na = old_a1 - old_a0;
-    __syncthreads();  // every thread has read the old offsets of frame t + 1
     int32_t s_run = 0, a_run = 0;
-    for (int32_t base = 0; base < ns; base += kSearchThreads) {
-      const int32_t k = base + tid;
+    for (int32_t base = 0; base < ns; base += tm.threads) {
+      const int32_t k = base + tm.tid;
       int32_t keep_state = 0, cnt = 0, as = 0, fwd = 0;
       float bwd = 0.0f;
       if (k < ns) {
@@ -381,8 +458,8 @@ __device__ void PruneWindow(const SearchArgs &g, const SeqView &v, Shared *sh, i
         for (int32_t p = p0; p < p1; ++p) cnt += v.arc_keep[p];
       }
       int32_t stot, atot;
-      const int32_t sj = s_run + BlockScan(keep_state, &stot, sh->scan);
-      const int32_t aj = a_run + BlockScan(cnt, &atot, sh->scan);
+      const int32_t sj = s_run + tm.Scan(keep_state, &stot);
+      const int32_t aj = a_run + tm.Scan(cnt, &atot);
       if (keep_state) {
         v.st_astate[ws + sj] = as;
         v.st_fwd[ws + sj] = fwd;
@@ -392,31 +469,39 @@ __device__ void PruneWindow(const SearchArgs &g, const SeqView &v, Shared *sh, i
       s_run += stot;
       a_run += atot;
     }
-    __syncthreads();
+    tm.Sync();
     int32_t moved = 0;
     const bool renumber = t + 1 < end;  // the states of frame `end` keep their numbers
-    for (int32_t base = 0; base < na; base += kSearchThreads) {
-      const int32_t q = base + tid;
-      int32_t keep = 0, aidx = 0, dest = 0;
-      float ll = 0.0f;
-      if (q < na) {
-        keep = v.arc_keep[old_a0 + q];
-        aidx = v.arc_aidx[old_a0 + q];
-        ll = v.arc_ll[old_a0 + q];
-        dest = v.arc_dest[old_a0 + q];
-        if (keep && renumber) dest = v.st_new[old_s1 + dest];
+    for (int32_t base = 0; base < na; base += tm.threads * kPer) {
+      const int32_t q0 = base + tm.tid * kPer;
+      int32_t aidx[kPer], dest[kPer];
+      float ll[kPer];
+      int32_t keep = 0;
+#pragma unroll
+      for (int i = 0; i < kPer; ++i) {
+        if (q0 + i < na && v.arc_keep[old_a0 + q0 + i]) {
+          keep |= 1 << i;
+          aidx[i] = v.arc_aidx[old_a0 + q0 + i];
+          ll[i] = v.arc_ll[old_a0 + q0 + i];
+          dest[i] = v.arc_dest[old_a0 + q0 + i];
+          if (renumber) dest[i] = v.st_new[old_s1 + dest[i]];
+        }
       }
       int32_t tot;
-      const int32_t j = moved + BlockScan(keep, &tot, sh->scan);
-      if (keep) {
-        v.arc_aidx[wa + j] = aidx;
-        v.arc_ll[wa + j] = ll;
-        v.arc_dest[wa + j] = dest;
+      int32_t j = moved + tm.Scan(__popc(keep), &tot);
+#pragma unroll
+      for (int i = 0; i < kPer; ++i) {
+        if (keep >> i & 1) {
+          v.arc_aidx[wa + j] = aidx[i];
+          v.arc_ll[wa + j] = ll[i];
+          v.arc_dest[wa + j] = dest[i];
+          ++j;
+        }
       }
       moved += tot;
     }
-    __syncthreads();
-    if (tid == 0) {
+    tm.Sync();
+    if (tm.tid == 0) {
       v.frame_s0[t] = ws;
       v.frame_a0[t] = wa;
     }
@@ -427,8 +512,8 @@ __device__ void PruneWindow(const SearchArgs &g, const SeqView &v, Shared *sh, i
   }
   // frame `end`: its states follow the compacted frames
   const int32_t ns_end = *s_top - old_s0;
-  for (int32_t base = 0; base < ns_end; base += kSearchThreads) {
-    const int32_t k = base + tid;
+  for (int32_t base = 0; base < ns_end; base += tm.threads) {
+    const int32_t k = base + tm.tid;
     int32_t as = 0, fwd = 0;
     float bwd = 0.0f;
     if (k < ns_end) {
@@ -436,29 +521,34 @@ __device__ void PruneWindow(const SearchArgs &g, const SeqView &v, Shared *sh, i
       fwd = v.st_fwd[old_s0 + k];
       bwd = v.st_bwd[old_s0 + k];
     }
-    __syncthreads();
+    tm.Sync();
     if (k < ns_end) {
       v.st_astate[ws + k] = as;
       v.st_fwd[ws + k] = fwd;
       v.st_bwd[ws + k] = bwd;
     }
   }
-  if (tid == 0) {
+  if (tm.tid == 0) {
     v.frame_s0[end] = ws;
     v.frame_a0[end] = wa;
     v.st_arc0[ws] = wa;  // closes the arc range of the last state of frame end - 1
   }
-  __syncthreads();
+  tm.Sync();
   *s_top = ws + ns_end;
   *a_top = wa;
 }
 
-// One CTA per sequence: all frames of the search with the pruning windows in the
+// One team per sequence: all frames of the search with the pruning windows in the
 // reference's schedule (:164-199, :213-229).
 __global__ void __launch_bounds__(kSearchThreads, 1) PrunedSearch(const SearchArgs g) {
   __shared__ Shared sh;
-  const int32_t seq = blockIdx.x;
-  const int tid = threadIdx.x;
+  if (threadIdx.x == 0) {
+    sh.phase_i = sh.phase_f = 0;
+    sh.beam = g.search_beam;
+  }
+  __syncthreads();
+  const Team tm(&sh);
+  const int32_t seq = blockIdx.x / tm.size;
   const SeqView v = ViewOf(g, seq);
   const int32_t row0 = g.b_rs[seq], final_t = g.b_rs[seq + 1] - row0;
   const int32_t T = g.T;
@@ -467,8 +557,7 @@ __global__ void __launch_bounds__(kSearchThreads, 1) PrunedSearch(const SearchAr
 
   // frame 0: the start state, if the graph has states (:435-472)
   int32_t s0 = 0, ns = g_states > 0 ? 1 : 0, a0 = 0;
-  if (tid == 0) {
-    sh.beam = g.search_beam;
+  if (tm.tid == 0) {
     v.frame_s0[0] = 0;
     v.frame_a0[0] = 0;
     if (ns) {
@@ -476,13 +565,13 @@ __global__ void __launch_bounds__(kSearchThreads, 1) PrunedSearch(const SearchAr
       v.st_fwd[0] = OrderedInt(0.0f);
     }
   }
-  __syncthreads();
+  tm.Sync();
   int32_t s_top = ns, a_top = 0;
   int32_t status = kSeqOk;
   int32_t next_end = kWindowShift;  // end of the next pruning window
   for (int32_t t = 0; t < T; ++t) {
     int32_t na, nn;
-    if (!SearchStep(g, v, &sh, seq, t, final_t, row0, s0, ns, a0, &na, &nn)) {
+    if (!SearchStep(g, v, tm, seq, t, final_t, row0, s0, ns, a0, &na, &nn)) {
       status = kSeqOverflow;
       break;
     }
@@ -491,21 +580,21 @@ __global__ void __launch_bounds__(kSearchThreads, 1) PrunedSearch(const SearchAr
     ns = nn;
     s_top = s0 + ns;
     a_top = a0;
-    if (tid == 0) {
+    if (tm.tid == 0) {
       v.frame_s0[t + 1] = s0;
       v.frame_a0[t + 1] = a0;
     }
-    __syncthreads();
+    tm.Sync();
     const int32_t this_end = next_end >= T ? T : next_end;
     if (t == this_end - 1) {
       const int32_t begin = max(0, next_end - kWindow);
-      PruneWindow(g, v, &sh, seq, begin, this_end, &s_top, &a_top);
+      PruneWindow(g, v, tm, seq, begin, this_end, &s_top, &a_top);
       s0 = s_top - ns;
       a0 = a_top;
       next_end += kWindowShift;
     }
   }
-  if (tid == 0) {
+  if (tm.tid == 0) {
     int32_t extra = 0;
     if (status == kSeqOk) {
       v.frame_s0[T + 1] = s_top;  // frame T has no arcs
@@ -523,6 +612,7 @@ __global__ void __launch_bounds__(kSearchThreads, 1) PrunedSearch(const SearchAr
     o[2] = extra;
     o[3] = status;
   }
+  tm.Sync();  // no CTA leaves while another may still read its shared memory
 }
 
 struct FormatArgs {
@@ -700,7 +790,30 @@ int32_t k2b200_intersect_dense_pruned_search(const k2b200_pruned_args *args, voi
               "NULL input pointer");
   const int32_t n = args->num_seqs;
   K2B_CUDA_OK(cudaMemsetAsync(L.g.winner, 0x7f, L.winner_bytes, stream));
-  { PrunedSearch<<<n, kSearchThreads, 0, stream>>>(L.g); NoteLaunch(); }
+  {
+    // CTAs per sequence: as many as keep the GPU filled, within the portable
+    // cluster size
+    int dev = 0, sms = 0;
+    K2B_CUDA_OK(cudaGetDevice(&dev));
+    K2B_CUDA_OK(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+    int32_t team = 1;
+    while (team < 8 && n * team * 2 <= sms) team *= 2;
+    if (args->team_ctas > 0) team = args->team_ctas;
+    K2B_REQUIRE(team == 1 || team == 2 || team == 4 || team == 8, "team_ctas must be 1, 2, 4 or 8");
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(n * team);
+    cfg.blockDim = dim3(kSearchThreads);
+    cfg.stream = stream;
+    cudaLaunchAttribute attr;
+    attr.id = cudaLaunchAttributeClusterDimension;
+    attr.val.clusterDim.x = team;
+    attr.val.clusterDim.y = 1;
+    attr.val.clusterDim.z = 1;
+    cfg.attrs = &attr;
+    cfg.numAttrs = 1;
+    K2B_CUDA_OK(cudaLaunchKernelEx(&cfg, PrunedSearch, L.g));
+    NoteLaunch();
+  }
   K2B_CUDA_OK(cudaGetLastError());
   std::vector<int32_t> h(4 * (size_t)n);
   K2B_CUDA_OK(cudaMemcpyAsync(h.data(), L.g.seq_out, sizeof(int32_t) * h.size(),

@@ -25,13 +25,14 @@ def k2():
     return k2_b200
 
 
-def run_gpu(k2, c, requires_grad=False):
+def run_gpu(k2, c, team_ctas=0):
     from gpu_util import dense_from_scores, fsa_to_host, host_to_fsa
     from k2_b200.autograd import _intersect_dense_pruned_arcs
     a = host_to_fsa(c["a"])
     dense = dense_from_scores(c["scores"], c["brs"])
     sb, ob, mn, mx, partial = c["params"]
-    ragged, ma, mb = _intersect_dense_pruned_arcs(a.arcs, dense, sb, ob, mn, mx, partial)
+    ragged, ma, mb = _intersect_dense_pruned_arcs(a.arcs, dense, sb, ob, mn, mx, partial,
+                                                  team_ctas)
     lat = k2.Fsa(ragged, _check=False)
     return lat, fsa_to_host(lat, ma, mb)
 
@@ -43,8 +44,9 @@ def test_small_cases_match_the_committed_reference_answers(k2):
     for name, c in cases.items():
         want = HostFsaVec(z[f"{name}.l_rs1"], z[f"{name}.l_rs2"], z[f"{name}.l_arcs"],
                           arc_map_a=z[f"{name}.map_a"], arc_map_b=z[f"{name}.map_b"])
-        _, got = run_gpu(k2, c)
-        same_fsa(got, want, name)
+        for team in (0, 1, 2, 8):
+            _, got = run_gpu(k2, c, team)
+            same_fsa(got, want, f"{name}, {team} CTAs per sequence")
 
 
 @pytest.mark.skipif(not ref.available(), reason="oracle/_ref/libk2ref.so not built")
@@ -63,8 +65,9 @@ def test_decoding_graph_many_windows(k2):
     for params in ((12.0, 5.0, 30, 400, False), (8.0, 4.0, 10, 60, True)):
         c = dict(a=g, scores=scores, brs=brs, params=params)
         want = ref.intersect_dense_pruned(g, scores, brs, *params)
-        lat, got = run_gpu(k2, c)
-        same_fsa(got, want, str(params))
+        for team in (1, 4):
+            lat, got = run_gpu(k2, c, team)
+            same_fsa(got, want, f"{params}, {team} CTAs per sequence")
         assert want.num_arcs > 1000
 
 
