@@ -270,6 +270,7 @@ def intersect_dense(a_fsas: Fsa, b_fsas: DenseFsaVec, output_beam: float,
 PRUNED_ARCS_TOTAL = 1 << 26
 PRUNED_ARCS_PER_SEQ = 1 << 21
 PRUNED_ARCS_MIN = 1 << 16
+_pruned_capacity = {}  # (device, num_seqs) -> capacity that the last call needed
 
 
 def _intersect_dense_pruned_arcs(a: RaggedArc, b: DenseFsaVec, search_beam: float,
@@ -289,6 +290,7 @@ def _intersect_dense_pruned_arcs(a: RaggedArc, b: DenseFsaVec, search_beam: floa
     h_brs = np.ascontiguousarray(b.h_row_splits, dtype=np.int32)
     num_seqs = h_brs.shape[0] - 1
     cap_a = max(PRUNED_ARCS_MIN, min(PRUNED_ARCS_PER_SEQ, PRUNED_ARCS_TOTAL // max(num_seqs, 1)))
+    cap_a = max(cap_a, _pruned_capacity.get((str(dev), num_seqs), 0))
     stream = _lib.stream_of(dev)
     i32 = dict(dtype=torch.int32, device=dev)
     while True:
@@ -311,6 +313,7 @@ def _intersect_dense_pruned_arcs(a: RaggedArc, b: DenseFsaVec, search_beam: floa
                 ctypes.byref(args), _lib.ptr(ws), nbytes.value, stream, ctypes.byref(ns),
                 ctypes.byref(na), ctypes.byref(full)))
         if not full.value:
+            _pruned_capacity[(str(dev), num_seqs)] = cap_a
             break
         del ws
         cap_a *= 4

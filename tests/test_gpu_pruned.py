@@ -123,9 +123,38 @@ def test_small_arena_is_grown(k2, monkeypatch):
     from k2_b200 import autograd
     monkeypatch.setattr(autograd, "PRUNED_ARCS_TOTAL", 1 << 8)
     monkeypatch.setattr(autograd, "PRUNED_ARCS_MIN", 1 << 6)
+    monkeypatch.setattr(autograd, "_pruned_capacity", {})
     c = pruned_cases(small=True)[3]
     z = np.load(GOLDEN)
     want = HostFsaVec(z["shared_wide.l_rs1"], z["shared_wide.l_rs2"], z["shared_wide.l_arcs"],
                       arc_map_a=z["shared_wide.map_a"], arc_map_b=z["shared_wide.map_b"])
     _, got = run_gpu(k2, c)
     same_fsa(got, want, "after growing the arena")
+    assert list(autograd._pruned_capacity.values())[0] > 1 << 6
+
+
+def test_best_path_agrees_with_the_exact_intersection_on_a_decoding_graph(k2):
+    """Scaled-down decoding configuration (20 000-state graph shared by 8 sequences of
+    100 frames): with a wide search beam the pruned lattice holds the same best path,
+    with the same score, as the exact intersect_dense lattice."""
+    from gpu_util import DEV
+    from k2_b200 import synthetic as syn
+    from k2_b200.fsa_algo import _fsa_vec_from_numpy
+    w = syn.hlg_decode(seed=3, scale=0.25, num_states=20000)
+    S = len(w.graph_row_splits2) - 1
+    shared = _fsa_vec_from_numpy(np.array([0, S]), w.graph_row_splits2, w.graph_arcs, DEV)
+    stacked = syn.build_graphs(w, DEV)
+    dense = k2.DenseFsaVec(w.log_probs.to(DEV), w.supervision_segments)
+    exact = k2.intersect_dense(stacked, dense, output_beam=8.0)
+    pruned = k2.intersect_dense_pruned(shared, dense, 40.0, 8.0, 30, 100000)
+    te = exact.get_tot_scores(use_double_scores=True, log_semiring=False)
+    tp = pruned.get_tot_scores(use_double_scores=True, log_semiring=False)
+    assert torch.isfinite(te).all()
+    assert torch.allclose(te, tp, rtol=1e-6, atol=1e-4)
+    be = k2.shortest_path(exact, use_double_scores=True)
+    bp = k2.shortest_path(pruned, use_double_scores=True)
+    assert torch.equal(be.arcs.values()[:, 2], bp.arcs.values()[:, 2])
+    # the search with everyday limits never scores above the exact best path
+    narrow = k2.intersect_dense_pruned(shared, dense, 20.0, 8.0, 30, 10000)
+    tn = narrow.get_tot_scores(use_double_scores=True, log_semiring=False)
+    assert (tn <= te + 1e-4).all()

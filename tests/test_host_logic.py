@@ -172,3 +172,37 @@ def test_workspace_sizing_and_validation_need_no_gpu():
     assert lib.k2b200_intersect_dense_workspace_bytes(ctypes.byref(sh), ctypes.byref(b1),
                                                       ctypes.byref(lv)) != 0
     assert b"a_shared" in lib.k2b200_last_error()
+
+
+def test_pruned_intersection_sizing_and_validation_need_no_gpu():
+    import ctypes
+    from k2_b200 import _lib
+    lib = _lib.lib
+    brs = np.array([0, 101, 181, 232], np.int32)
+
+    def args(**kw):
+        base = dict(num_fsas=1, num_states=5000, num_arcs=30000, rows=232, cols=41, num_seqs=3,
+                    h_b_row_splits=brs.ctypes.data, search_beam=20.0, output_beam=8.0,
+                    min_active_states=30, max_active_states=10000, allow_partial=0,
+                    max_states_per_seq=1 << 15, max_arcs_per_seq=1 << 16)
+        base.update(kw)
+        return _lib.PrunedArgs(**base)
+
+    nbytes, levels = ctypes.c_size_t(), ctypes.c_int64()
+    a = args()
+    assert lib.k2b200_intersect_dense_pruned_workspace_bytes(
+        ctypes.byref(a), ctypes.byref(nbytes), ctypes.byref(levels)) == 0
+    # layers: (longest sequence's rows + 2) per sequence
+    assert levels.value == 3 * (101 + 2)
+    # 17 bytes per arc, 20 per state, one table entry per (sequence, graph state)
+    arenas = 3 * (17 * (1 << 16) + 20 * ((1 << 15) + 1))
+    assert arenas + 3 * 5000 * 4 <= nbytes.value <= arenas + 3 * 5000 * 4 + (1 << 16)
+    for bad, msg in ((dict(search_beam=0.0), b"positive"),
+                     (dict(min_active_states=10, max_active_states=10), b"min_active_states"),
+                     (dict(num_fsas=2), b"one graph per sequence"),
+                     (dict(rows=233), b"do not cover"),
+                     (dict(max_arcs_per_seq=0), b"capacities")):
+        a = args(**bad)
+        assert lib.k2b200_intersect_dense_pruned_workspace_bytes(
+            ctypes.byref(a), ctypes.byref(nbytes), ctypes.byref(levels)) != 0
+        assert msg in lib.k2b200_last_error(), (bad, lib.k2b200_last_error())

@@ -82,3 +82,38 @@ def test_reference_rejects_what_the_oracle_rejects():
         ref.intersect_dense(a, scores, brs, 10.0, np.array([1, 0], np.int32))
     with pytest.raises(RuntimeError):
         oracle.intersect_dense(a, scores, brs, 10.0, np.array([1, 0], np.int32))
+
+
+def test_pruned_intersection_fixtures_are_the_reference_answers():
+    """tests/golden/pruned_cases.npz (what the GPU path is compared with) against the
+    reference library run now on the same seeded inputs."""
+    import os
+    from oracle.common import HostFsaVec
+    from pruned_util import pruned_cases
+    z = np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden",
+                             "pruned_cases.npz"))
+    for c in pruned_cases(small=True):
+        name = c["name"]
+        r = ref.intersect_dense_pruned(c["a"], c["scores"], c["brs"], *c["params"])
+        want = HostFsaVec(z[f"{name}.l_rs1"], z[f"{name}.l_rs2"], z[f"{name}.l_arcs"],
+                          arc_map_a=z[f"{name}.map_a"], arc_map_b=z[f"{name}.map_b"])
+        same_fsa(r, want, name)
+
+
+def test_pruned_intersection_with_wide_beams_is_the_exact_lattice_best_path():
+    """With beams that prune nothing the pruned search keeps a superset of the exact
+    lattice and the best path score is the same (tropical total of intersect_dense)."""
+    rng = np.random.default_rng(11)
+    for trial in range(10):
+        n = int(rng.integers(1, 4))
+        syms = [[int(x) for x in rng.integers(1, 5, size=int(rng.integers(1, 6)))]
+                for _ in range(n)]
+        g = oracle.ctc_graphs(syms, False)
+        scores, brs = random_dense(rng, n, 40, 5, low_rows=False)
+        exact = ref.intersect_dense(g, scores, brs, 1000.0, None)
+        pruned = ref.intersect_dense_pruned(g, scores, brs, 1000.0, 1000.0, 0, 100000)
+        te = ref.tot_scores_and_arc_post(exact, ref.forward_scores(exact, False, True),
+                                         ref.backward_scores(exact, False, True), True)[0]
+        tp = ref.tot_scores_and_arc_post(pruned, ref.forward_scores(pruned, False, True),
+                                         ref.backward_scores(pruned, False, True), True)[0]
+        np.testing.assert_allclose(te, tp, rtol=1e-6)
