@@ -42,6 +42,8 @@ def parse_args():
     p.add_argument("--workload", default="ctc_large")
     p.add_argument("--scale", type=float, default=1.0)
     p.add_argument("--no-cpu-baseline", action="store_true")
+    p.add_argument("--decode", action="store_true",
+                   help="time the decoding path instead: hlg_decode through intersect_dense_pruned")
     return p.parse_args()
 
 
@@ -125,6 +127,13 @@ def host_inputs(w):
     g = syn.build_graphs(w, "cpu")
     a = g.arcs
     graphs = HostFsaVec(a.h_row_splits1, a._row_splits2.numpy(), a.values().numpy())
+    scores, row_splits = host_scores(w)
+    return graphs, scores, row_splits
+
+
+def host_scores(w):
+    """The DenseFsaVec score matrix and row_splits of a workload as host arrays."""
+    import numpy as np
     seg = w.supervision_segments.numpy()
     N, T, C = w.log_probs.shape
     rows = int(seg[:, 2].sum() + len(seg))
@@ -137,7 +146,7 @@ def host_inputs(w):
         scores[r + d, 0] = 0.0
         r += d + 1
         row_splits[i + 1] = r
-    return graphs, scores, row_splits
+    return scores, row_splits
 
 
 def pick_cpu_impl():
@@ -503,9 +512,96 @@ def run_ours(args):
         dist.destroy_process_group()
 
 
+# --------------------------------------------------------------------------- decoding
+DECODE_PARAMS = dict(search_beam=20.0, output_beam=8.0, min_active_states=30,
+                     max_active_states=10000)
+
+
+def run_decode(args):
+    """The decoding configuration (a 200 000-state graph shared by 32 sequences of 500
+    frames): one step = intersect_dense_pruned + Viterbi best path + log-semiring total
+    scores.  An extra line beside the headline benchmark; single GPU.  With --impl
+    reference the reference's own CPU IntersectDensePruned runs on the first sequences
+    of the same batch (it is single-threaded)."""
+    import numpy as np
+
+    from k2_b200 import synthetic as syn
+    w = syn.hlg_decode(seed=0, scale=args.scale)
+    S = len(w.graph_row_splits2) - 1
+    n, t = int(w.log_probs.shape[0]), int(w.log_probs.shape[1])
+    config = {"workload": "hlg_decode (pruned)", "sequences": n, "frames_per_sequence": t,
+              "classes": int(w.log_probs.shape[2]), "graph_states": S,
+              "graph_arcs": int(len(w.graph_arcs)), **DECODE_PARAMS}
+    if args.impl == "reference":
+        from oracle import ref
+        from oracle.common import HostFsaVec
+        if not ref.available():
+            print(json.dumps({"impl": "reference", "unavailable":
+                              "oracle/_ref/libk2ref.so not built (needs the k2 checkout)"}))
+            return
+        m = min(n, 2)
+        scores, row_splits = host_scores(w)
+        rows = int(row_splits[m])
+        a = HostFsaVec(np.array([0, S], np.int32), w.graph_row_splits2.astype(np.int32),
+                       w.graph_arcs)
+        t0 = time.perf_counter()
+        lat = ref.intersect_dense_pruned(a, scores[:rows], row_splits[:m + 1],
+                                         *DECODE_PARAMS.values())
+        dt = time.perf_counter() - t0
+        print(json.dumps({"metric": "decode_frames_per_sec", "impl": "reference",
+                          "value": m * t / dt, "unit": "frames/s", "n_gpus": 0,
+                          "ms_per_step": dt * 1e3 * n / m, "higher_is_better": True,
+                          "config": config,
+                          "cpu_baseline": {"value": m * t / dt, "unit": "frames/s", "cores": 1,
+                                           "kind": "reference",
+                                           "sample": f"{m} of {n} sequences, lattice only "
+                                                     f"({lat.num_arcs} arcs)"}}))
+        return
+    import torch
+
+    import k2_b200 as k2
+    from k2_b200 import _lib
+    from k2_b200.fsa_algo import _fsa_vec_from_numpy
+    assert torch.cuda.is_available(), "bench.py needs a CUDA device (no CPU fallback)"
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    graph = _fsa_vec_from_numpy(np.array([0, S]), w.graph_row_splits2, w.graph_arcs, dev)
+    dense = k2.DenseFsaVec(w.log_probs.to(dev), w.supervision_segments)
+
+    def step():
+        lat = k2.intersect_dense_pruned(graph, dense, **DECODE_PARAMS)
+        best = k2.shortest_path(lat, use_double_scores=True)
+        tot = lat.get_tot_scores(use_double_scores=True, log_semiring=True)
+        return lat, best, tot
+
+    for _ in range(max(args.warmup, 3)):
+        lat, best, tot = step()
+    torch.cuda.synchronize()
+    clocks = ClockSampler(0)
+    clocks.start()
+    n0 = _lib.launch_count()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        lat, best, tot = step()
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / args.steps
+    launches = (_lib.launch_count() - n0) // args.steps
+    print(json.dumps({
+        "metric": "decode_frames_per_sec", "value": n * t / (ms * 1e-3), "unit": "frames/s",
+        "n_gpus": 1, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms,
+        "higher_is_better": True, "dtype": "f32", "data": "synthetic", "config": config,
+        "lattice": {"states": lat.arcs.num_states, "arcs": lat.arcs.num_elements()},
+        "best_path_arcs": best.arcs.num_elements(), "tot_scores_mean": float(tot.mean().item()),
+        "gpu_launches": int(launches), "clocks": clocks.stop()}))
+
+
 def main():
     args = parse_args()
-    if args.impl == "reference":
+    if args.decode:
+        run_decode(args)
+    elif args.impl == "reference":
         run_reference(args)
     else:
         run_ours(args)
