@@ -37,7 +37,6 @@ namespace {
 constexpr int kSearchThreads = 1024;
 constexpr int kWindow = 30;       // frames pruned per backward phase (:171)
 constexpr int kWindowShift = 20;  // frames between two phases (:172)
-constexpr int32_t kNoWinner = 0x7f7f7f7f;  // what a byte fill with 0x7f leaves
 
 // order-preserving float <-> int (k2/csrc/utils.h:609-624 plays the same role)
 __device__ __forceinline__ int32_t OrderedInt(float f) {
@@ -63,12 +62,12 @@ struct SearchArgs {
   int32_t allow_partial;
   // arenas, [num_seqs] slices of cap_s (+1) and cap_a elements
   int64_t cap_s, cap_a;
-  int32_t *st_astate, *st_fwd, *st_arc0, *st_new;
+  int32_t *st_astate, *st_fwd, *st_arc0, *st_new, *st_cnt;
   float *st_bwd;
   int32_t *arc_aidx, *arc_dest;
   float *arc_ll, *arc_end;
   uint8_t *arc_keep;
-  int32_t *winner;            // [num_seqs * a_states] (shared) or [a_states]
+  unsigned long long *winner;  // [num_seqs * a_states] (shared) or [a_states]
   int32_t *frame_s0, *frame_a0;  // [num_seqs][T + 2]
   int32_t *seq_out;           // [num_seqs][4]: states, arcs, extra final state, status
 };
@@ -84,9 +83,13 @@ enum : int32_t { kSeqOk = 0, kSeqOverflow = 1, kSeqManyFinal = 2 };
 struct Shared {
   int32_t scan[65];
   float fmax[33];
+  unsigned long long scan2[65];
+  unsigned long long team_l[2];
   int32_t team_i[2];  // this CTA's contribution to the team-wide scan / or
   float team_f[2];    // ... and to the team-wide max; two slots used alternately
-  int32_t phase_i, phase_f;
+  int32_t phase_i, phase_f, phase_l;
+  int32_t new_s0[kWindow], new_a0[kWindow];  // used by the first thread of the team only
+  int32_t wbest[kSearchThreads / 32][32], wcnt[kSearchThreads / 32][32];  // per warp
   float cutoff;
   float beam;
 };
@@ -156,6 +159,58 @@ struct Team {
     return before + ex;
   }
 
+  // the same for a pair of counts, both below 2^31 in total, packed into 64 bits
+  __device__ int32_t Scan2(int32_t a, int32_t b, int32_t *ex_b, int32_t *total_a,
+                           int32_t *total_b) const {
+    unsigned long long *s = sh->scan2;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const unsigned long long v = (unsigned long long)(uint32_t)a | ((unsigned long long)(uint32_t)b << 32);
+    unsigned long long inc = v;
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) {
+      unsigned long long o = __shfl_up_sync(0xffffffffu, inc, d);
+      if (lane >= d) inc += o;
+    }
+    if (lane == 31) s[warp] = inc;
+    __syncthreads();
+    if (warp == 0) {
+      unsigned long long w = s[lane];
+      unsigned long long winc = w;
+#pragma unroll
+      for (int d = 1; d < 32; d <<= 1) {
+        unsigned long long o = __shfl_up_sync(0xffffffffu, winc, d);
+        if (lane >= d) winc += o;
+      }
+      s[32 + lane] = winc - w;
+      if (lane == 31) s[64] = winc;
+    }
+    __syncthreads();
+    unsigned long long ex = s[32 + warp] + inc - v;
+    unsigned long long all = s[64];
+    if (size == 1) {
+      __syncthreads();
+    } else {
+      const int32_t slot = sh->phase_l & 1;
+      if (threadIdx.x == 0) sh->team_l[slot] = all;
+      cluster.sync();
+      unsigned long long before = 0, sum = 0;
+      for (int32_t r = 0; r < size; ++r) {
+        const unsigned long long x = *cluster.map_shared_rank(&sh->team_l[slot], r);
+        sum += x;
+        if (r < rank) before += x;
+      }
+      __syncthreads();
+      if (threadIdx.x == 0) sh->phase_l += 1;
+      __syncthreads();
+      ex += before;
+      all = sum;
+    }
+    *ex_b = (int32_t)(ex >> 32);
+    *total_a = (int32_t)(all & 0xffffffffu);
+    *total_b = (int32_t)(all >> 32);
+    return (int32_t)(ex & 0xffffffffu);
+  }
+
   __device__ float Max(float v) const {
     float *s = sh->fmax;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -194,12 +249,13 @@ struct Team {
 
 // Views of one sequence's slices of the arenas.
 struct SeqView {
-  int32_t *st_astate, *st_fwd, *st_arc0, *st_new;
+  int32_t *st_astate, *st_fwd, *st_arc0, *st_new, *st_cnt;
   float *st_bwd;
   int32_t *arc_aidx, *arc_dest;
   float *arc_ll, *arc_end;
   uint8_t *arc_keep;
-  int32_t *winner, *frame_s0, *frame_a0;
+  unsigned long long *winner;
+  int32_t *frame_s0, *frame_a0;
 };
 
 __device__ __forceinline__ SeqView ViewOf(const SearchArgs &g, int32_t seq) {
@@ -209,6 +265,7 @@ __device__ __forceinline__ SeqView ViewOf(const SearchArgs &g, int32_t seq) {
   v.st_fwd = g.st_fwd + so;
   v.st_arc0 = g.st_arc0 + so;
   v.st_new = g.st_new + so;
+  v.st_cnt = g.st_cnt + so;
   v.st_bwd = g.st_bwd + so;
   v.arc_aidx = g.arc_aidx + ao;
   v.arc_dest = g.arc_dest + ao;
@@ -248,33 +305,34 @@ __device__ float NextBeam(float dyn, float best, int32_t active, int32_t t, int3
   return dyn;
 }
 
-constexpr int kPer = 4;  // consecutive arcs per thread in the scan-heavy passes
+constexpr int kPer = 8;      // consecutive arcs per thread in the compaction pass
+constexpr int kPerScan = 8;  // ... and where the new states are numbered
+constexpr int kBatch = 4;    // arcs whose loads a thread issues together
+constexpr int kExpand = 2;   // ... in the arc expansion
 
-// One step of the search (GetArcs + PropagateForward, :778-1153): expands the arcs
-// leaving the ns states of frame t at [s0, s0 + ns), which start at arena position
-// a0, and creates the states of frame t + 1 behind them.  Returns false when an
-// arena is full.  *na_out / *ns_next: arcs of frame t and states of frame t + 1.
+// Entries of the direct table that replaces the reference's hash: the frame in the
+// high word, so that entries of earlier frames lose against any entry of this frame
+// and the table never needs clearing; in the low word either an arc (a smaller arc
+// index gives a larger value, so atomicMax keeps the first arc) or, with the top bit
+// set, the number of the state that arc created.
+__device__ __forceinline__ unsigned long long ArcEntry(int32_t t, int32_t q) {
+  return ((unsigned long long)(uint32_t)(t + 1) << 32) | (uint32_t)(0x7fffffff - q);
+}
+__device__ __forceinline__ unsigned long long StateEntry(int32_t t, int32_t j) {
+  return ((unsigned long long)(uint32_t)(t + 1) << 32) | 0x80000000u | (uint32_t)j;
+}
+
+// One step of the search (GetArcs + PropagateForward, :778-1153): expands the na arcs
+// leaving the ns states of frame t at [s0, s0 + ns) - their arc ranges (st_arc0,
+// starting at a0) were laid out when the states were created - and creates the states
+// of frame t + 1 behind them, with their arc ranges.  Returns false when an arena is
+// full.  *ns_next / *na_next: states of frame t + 1 and the arcs leaving them.
 __device__ bool SearchStep(const SearchArgs &g, const SeqView &v, const Team &tm, int32_t seq,
                            int32_t t, int32_t final_t, int32_t row0, int32_t s0, int32_t ns,
-                           int32_t a0, int32_t *na_out, int32_t *ns_next) {
+                           int32_t a0, int32_t na, int32_t *ns_next, int32_t *na_next) {
   Shared *sh = tm.sh;
   const float kNegInf = -INFINITY;
-  // arc ranges of the states (row_splits of [state][arc] on this frame)
-  int32_t na = 0;
-  for (int32_t base = 0; base < ns; base += tm.threads) {
-    const int32_t k = base + tm.tid;
-    int32_t deg = 0;
-    if (k < ns) {
-      const int32_t as = v.st_astate[s0 + k];
-      deg = g.a_rs2[as + 1] - g.a_rs2[as];
-    }
-    int32_t tot;
-    const int32_t ex = tm.Scan(deg, &tot);
-    if (k < ns) v.st_arc0[s0 + k] = a0 + na + ex;
-    na += tot;
-  }
   if ((int64_t)a0 + na > g.cap_a) return false;
-  if (tm.tid == 0) v.st_arc0[s0 + ns] = a0 + na;
 
   // graph of this sequence: its final state, for allow_partial (:861-871)
   const int32_t gi = seq * g.a_stride;
@@ -290,33 +348,73 @@ __device__ bool SearchStep(const SearchArgs &g, const SeqView &v, const Team &tm
     redirect = !tm.Any(has);
   }
 
-  // arcs: scores, destination (as a graph state) and the best end score (:858-905)
+  // arcs: scores, destination (as a graph state) and the best end score (:858-905).
+  // A warp takes 32 consecutive states; its lanes walk the arcs of those states as
+  // one flat range and find the state of an arc by a search over the 32 range
+  // starts held in registers, so the work per lane is even whatever the out-degrees.
   // (a row past the end is only asked for by a malformed graph whose arcs with
   // label -1 do not end in a state without arcs)
   const bool row_ok = row0 + t < g.rows;
   const float *row = g.scores + (int64_t)(row_ok ? row0 + t : 0) * g.cols;
   float best = kNegInf;
-  for (int32_t k = tm.tid; k < ns; k += tm.threads) {
-    const int32_t as = v.st_astate[s0 + k];
-    const float fwd = OrderedFloat(v.st_fwd[s0 + k]);
-    const int32_t ga0 = g.a_rs2[as], ga1 = g.a_rs2[as + 1];
-    int32_t p = v.st_arc0[s0 + k];
-    for (int32_t a = ga0; a < ga1; ++a, ++p) {
-      const Arc arc = g.a_arcs[a];
-      const uint32_t col = (uint32_t)(arc.label + 1);
-      float acoustic = (row_ok && col < (uint32_t)g.cols) ? row[col] : kNegInf;
-      int32_t dest = as + arc.dest - arc.src;
-      if (redirect) {
-        dest = g_final;
-        acoustic = 0.0f;
+  {
+    const int lane = threadIdx.x & 31;
+    const int32_t team_warp = tm.tid >> 5, team_warps = tm.threads >> 5;
+    for (int32_t kb = team_warp * 32; kb < ns; kb += team_warps * 32) {
+      const int32_t k = kb + lane;
+      int32_t as = 0, fwd = 0, p0 = 0x7fffffff, ga0 = 0;
+      if (k < ns) {
+        as = v.st_astate[s0 + k];
+        fwd = v.st_fwd[s0 + k];
+        p0 = v.st_arc0[s0 + k];
+        ga0 = g.a_rs2[as];
       }
-      const float ll = acoustic + arc.score;
-      const float end = fwd + ll;
-      v.arc_aidx[p] = a;
-      v.arc_ll[p] = ll;
-      v.arc_dest[p] = dest;
-      v.arc_end[p] = end;
-      best = fmaxf(best, end);
+      const int32_t first = __shfl_sync(0xffffffffu, p0, 0);
+      const int32_t last = v.st_arc0[s0 + min(kb + 32, ns)];
+      for (int32_t pb = first; pb < last; pb += 32 * kExpand) {
+        int32_t p[kExpand], j[kExpand], aidx[kExpand];
+        Arc arc[kExpand];
+#pragma unroll
+        for (int i = 0; i < kExpand; ++i) {
+          p[i] = pb + i * 32 + lane;
+          // largest j with p0[j] <= p (p0 is non-decreasing; absent states hold +inf)
+          int32_t lo = 0;
+#pragma unroll
+          for (int step = 16; step > 0; step >>= 1) {
+            const int32_t cand = __shfl_sync(0xffffffffu, p0, lo + step);
+            if (cand <= p[i]) lo += step;
+          }
+          j[i] = lo;
+          const int32_t jp0 = __shfl_sync(0xffffffffu, p0, lo);
+          const int32_t jga0 = __shfl_sync(0xffffffffu, ga0, lo);
+          aidx[i] = p[i] < last ? jga0 + (p[i] - jp0) : -1;
+        }
+#pragma unroll
+        for (int i = 0; i < kExpand; ++i) {
+          if (aidx[i] >= 0) arc[i] = g.a_arcs[aidx[i]];
+        }
+#pragma unroll
+        for (int i = 0; i < kExpand; ++i) {
+          const int32_t jas = __shfl_sync(0xffffffffu, as, j[i]);
+          const int32_t jfwd = __shfl_sync(0xffffffffu, fwd, j[i]);
+          if (aidx[i] >= 0) {
+            const uint32_t col = (uint32_t)(arc[i].label + 1);
+            float acoustic = (row_ok && col < (uint32_t)g.cols) ? row[col] : kNegInf;
+            int32_t dest = jas + arc[i].dest - arc[i].src;
+            if (redirect) {
+              dest = g_final;
+              acoustic = 0.0f;
+            }
+            const float ll = acoustic + arc[i].score;
+            const float end = OrderedFloat(jfwd) + ll;
+            v.arc_aidx[p[i]] = aidx[i];
+            v.arc_ll[p[i]] = ll;
+            v.arc_dest[p[i]] = dest;
+            v.arc_end[p[i]] = end;
+            best = fmaxf(best, end);
+          }
+        }
+      }
     }
   }
   best = tm.Max(best);  // also makes the arc records visible to the team
@@ -325,68 +423,145 @@ __device__ bool SearchStep(const SearchArgs &g, const SeqView &v, const Team &tm
   const float cutoff = sh->cutoff;
 
   // first arc above the cutoff into every destination state (:1005-1028)
-  for (int32_t q = tm.tid; q < na; q += tm.threads) {
-    if (v.arc_end[a0 + q] > cutoff) atomicMin(&v.winner[v.arc_dest[a0 + q]], q);
+  for (int32_t q0 = tm.tid; q0 < na; q0 += kBatch * tm.threads) {
+    float end[kBatch];
+    int32_t dest[kBatch];
+#pragma unroll
+    for (int i = 0; i < kBatch; ++i) {
+      const int32_t q = q0 + i * tm.threads;
+      end[i] = q < na ? v.arc_end[a0 + q] : kNegInf;
+      dest[i] = q < na ? v.arc_dest[a0 + q] : 0;
+    }
+#pragma unroll
+    for (int i = 0; i < kBatch; ++i) {
+      if (end[i] > cutoff) atomicMax(&v.winner[dest[i]], ArcEntry(t, q0 + i * tm.threads));
+    }
   }
   tm.Sync();
-  // number the new states in the order of their winning arcs (:1031-1100)
-  const int32_t s1 = s0 + ns;
-  int32_t nn = 0;
-  for (int32_t base = 0; base < na; base += tm.threads * kPer) {
-    const int32_t q0 = base + tm.tid * kPer;
-    int32_t dest[kPer];
-    int32_t won = 0;  // bit i: arc q0 + i created its destination state
+  // which arcs created their destination state, and how many arcs leave it: one
+  // byte per arc (0: none; else out-degree + 1, 255 standing for "254 or more")
+  for (int32_t q0 = tm.tid; q0 < na; q0 += kBatch * tm.threads) {
+    float end[kBatch];
+    int32_t dest[kBatch];
+    unsigned long long w[kBatch];
 #pragma unroll
-    for (int i = 0; i < kPer; ++i) {
-      dest[i] = 0;
-      if (q0 + i < na) {
-        dest[i] = v.arc_dest[a0 + q0 + i];
-        if (v.arc_end[a0 + q0 + i] > cutoff && v.winner[dest[i]] == q0 + i) won |= 1 << i;
+    for (int i = 0; i < kBatch; ++i) {
+      const int32_t q = q0 + i * tm.threads;
+      end[i] = q < na ? v.arc_end[a0 + q] : kNegInf;
+      dest[i] = q < na ? v.arc_dest[a0 + q] : 0;
+    }
+#pragma unroll
+    for (int i = 0; i < kBatch; ++i) w[i] = end[i] > cutoff ? v.winner[dest[i]] : 0ull;
+#pragma unroll
+    for (int i = 0; i < kBatch; ++i) {
+      const int32_t q = q0 + i * tm.threads;
+      if (q < na) {
+        uint8_t flag = 0;
+        if (end[i] > cutoff && w[i] == ArcEntry(t, q)) {
+          const int32_t deg = g.a_rs2[dest[i] + 1] - g.a_rs2[dest[i]];
+          flag = (uint8_t)(min(deg, 254) + 1);
+        }
+        v.arc_keep[a0 + q] = flag;
       }
     }
-    int32_t tot;
-    int32_t j = nn + tm.Scan(__popc(won), &tot);
+  }
+  tm.Sync();
+  // number the new states in the order of their winning arcs (:1031-1100) and lay
+  // out the arcs that will leave them
+  const int32_t s1 = s0 + ns, a1 = a0 + na;
+  int32_t nn = 0, na1 = 0;
+  for (int32_t base = 0; base < na; base += tm.threads * kPerScan) {
+    const int32_t q0 = base + tm.tid * kPerScan;
+    int32_t deg[kPerScan];
+    int32_t won = 0, degs = 0;  // bit i: arc q0 + i created its destination state
 #pragma unroll
-    for (int i = 0; i < kPer; ++i) {
-      if (won >> i & 1) {
-        if ((int64_t)s1 + j < g.cap_s) {
-          v.st_astate[s1 + j] = dest[i];
-          v.st_fwd[s1 + j] = OrderedInt(kNegInf);
-          v.winner[dest[i]] = -(j + 1);
+    for (int i = 0; i < kPerScan; ++i) {
+      deg[i] = 0;
+      const int32_t flag = q0 + i < na ? v.arc_keep[a0 + q0 + i] : 0;
+      if (flag) {
+        won |= 1 << i;
+        deg[i] = flag - 1;
+      }
+    }
+    if (won) {
+#pragma unroll
+      for (int i = 0; i < kPerScan; ++i) {
+        if (deg[i] == 254) {
+          const int32_t d = v.arc_dest[a0 + q0 + i];
+          deg[i] = g.a_rs2[d + 1] - g.a_rs2[d];
         }
-        ++j;
+        degs += deg[i];
+      }
+    }
+    int32_t tot, dtot, arcs_before;
+    int32_t j = nn + tm.Scan2(__popc(won), degs, &arcs_before, &tot, &dtot);
+    arcs_before += na1;
+    if (won) {
+#pragma unroll
+      for (int i = 0; i < kPerScan; ++i) {
+        if (won >> i & 1) {
+          const int32_t d = v.arc_dest[a0 + q0 + i];
+          const int32_t first = a1 + arcs_before;
+          if ((int64_t)s1 + j < g.cap_s && (int64_t)first + deg[i] <= g.cap_a) {
+            v.st_astate[s1 + j] = d;
+            v.st_fwd[s1 + j] = OrderedInt(kNegInf);
+            v.st_arc0[s1 + j] = first;
+            v.winner[d] = StateEntry(t, j);
+          }
+          arcs_before += deg[i];
+          ++j;
+        }
       }
     }
     nn += tot;
+    na1 += dtot;
   }
-  if ((int64_t)s1 + nn > g.cap_s) return false;
+  if ((int64_t)s1 + nn > g.cap_s || (int64_t)a1 + na1 > g.cap_a) return false;
+  if (tm.tid == 0) v.st_arc0[s1 + nn] = a1 + na1;
   tm.Sync();
   // destination index of every arc and the best score into every new state; an
   // arc below the cutoff still enters a state that another arc created (:1103-1138)
-  for (int32_t q = tm.tid; q < na; q += tm.threads) {
-    const int32_t w = v.winner[v.arc_dest[a0 + q]];
-    int32_t idx1 = -1;
-    if (w < 0) {
-      idx1 = -w - 1;
-      atomicMax(&v.st_fwd[s1 + idx1], OrderedInt(v.arc_end[a0 + q]));
+  for (int32_t q0 = tm.tid; q0 < na; q0 += kBatch * tm.threads) {
+    float end[kBatch];
+    int32_t dest[kBatch];
+    unsigned long long w[kBatch];
+#pragma unroll
+    for (int i = 0; i < kBatch; ++i) {
+      const int32_t q = q0 + i * tm.threads;
+      end[i] = q < na ? v.arc_end[a0 + q] : kNegInf;
+      dest[i] = q < na ? v.arc_dest[a0 + q] : -1;
     }
-    v.arc_dest[a0 + q] = idx1;
+#pragma unroll
+    for (int i = 0; i < kBatch; ++i) w[i] = dest[i] >= 0 ? v.winner[dest[i]] : 0ull;
+#pragma unroll
+    for (int i = 0; i < kBatch; ++i) {
+      const int32_t q = q0 + i * tm.threads;
+      if (q < na) {
+        int32_t idx1 = -1;
+        if ((uint32_t)(w[i] >> 32) == (uint32_t)(t + 1) && (w[i] & 0x80000000u)) {
+          idx1 = (int32_t)(w[i] & 0x7fffffffu);
+          atomicMax(&v.st_fwd[s1 + idx1], OrderedInt(end[i]));
+        }
+        v.arc_dest[a0 + q] = idx1;
+      }
+    }
   }
   tm.Sync();
-  for (int32_t j = tm.tid; j < nn; j += tm.threads) v.winner[v.st_astate[s1 + j]] = kNoWinner;
-  tm.Sync();
-  *na_out = na;
   *ns_next = nn;
+  *na_next = na1;
   return true;
 }
 
 // Backward pass over frames [begin, end) with the output beam (PruneTimeRange,
 // :1373-1634, with SetBackwardProbsFinal :1170-1193 and PropagateBackward
 // :1239-1346), then compaction of those frames in place.  On entry the frames up to
-// `end` are complete and frame `end` has its states but no arcs yet; on return
-// *s_top / *a_top are the ends of the arenas and the frame tables are updated.
+// `end` are complete and frame `end` has its states and the layout of the na_end arcs
+// that will leave them, but not the arcs; on return *s_top / *a_top are the ends of
+// the arenas and the frame tables are updated.
 __device__ void PruneWindow(const SearchArgs &g, const SeqView &v, const Team &tm, int32_t seq,
-                            int32_t begin, int32_t end, int32_t *s_top, int32_t *a_top) {
+                            int32_t begin, int32_t end, int32_t na_end, int32_t *s_top,
+                            int32_t *a_top) {
+  Shared *sh = tm.sh;
   const float kNegInf = -INFINITY;
   const int32_t gi = seq * g.a_stride;
   const int32_t g_final = g.a_rs1[gi + 1] - 1;  // last state of this sequence's graph
@@ -406,24 +581,60 @@ __device__ void PruneWindow(const SearchArgs &g, const SeqView &v, const Team &t
     const int32_t s0 = v.frame_s0[t], ns = v.frame_s0[t + 1] - s0, s_next = v.frame_s0[t + 1];
     int32_t kept = 0;
     for (int32_t base = 0; base < ns; base += tm.threads) {
+      // a warp takes 32 consecutive states and walks their arcs as one flat range
+      // (as in the search step); per-state maxima and counts gather in shared memory
       const int32_t k = base + tm.tid;
-      int32_t keep_state = 0;
+      const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+      int32_t keep_state = 0, p0 = 0x7fffffff;
+      float fwd = 0.0f;
       if (k < ns) {
-        const float fwd = OrderedFloat(v.st_fwd[s0 + k]);
-        const int32_t p0 = v.st_arc0[s0 + k], p1 = v.st_arc0[s0 + k + 1];
-        float best = kNegInf;
-        for (int32_t p = p0; p < p1; ++p) {
-          const int32_t d = v.arc_dest[p];
-          uint8_t keep = 0;
-          if (d >= 0) {
-            const float bl = v.arc_ll[p] + v.st_bwd[s_next + d];
-            if (bl + fwd >= -beam) {
-              keep = 1;
-              best = fmaxf(best, bl);
-            }
+        fwd = OrderedFloat(v.st_fwd[s0 + k]);
+        p0 = v.st_arc0[s0 + k];
+      }
+      sh->wbest[warp][lane] = OrderedInt(kNegInf);
+      sh->wcnt[warp][lane] = 0;
+      __syncwarp();
+      const int32_t first = __shfl_sync(0xffffffffu, p0, 0);
+      const int32_t last = v.st_arc0[s0 + min(k - lane + 32, ns)];
+      for (int32_t pb = first; pb < last; pb += 32 * kExpand) {
+        int32_t p[kExpand], j[kExpand], d[kExpand];
+        float ll[kExpand], nb[kExpand];
+#pragma unroll
+        for (int i = 0; i < kExpand; ++i) {
+          p[i] = pb + i * 32 + lane;
+          int32_t lo = 0;
+#pragma unroll
+          for (int step = 16; step > 0; step >>= 1) {
+            const int32_t cand = __shfl_sync(0xffffffffu, p0, lo + step);
+            if (cand <= p[i]) lo += step;
           }
-          v.arc_keep[p] = keep;
+          j[i] = lo;
+          d[i] = p[i] < last ? v.arc_dest[p[i]] : -1;
+          ll[i] = p[i] < last ? v.arc_ll[p[i]] : 0.0f;
         }
+#pragma unroll
+        for (int i = 0; i < kExpand; ++i) nb[i] = d[i] >= 0 ? v.st_bwd[s_next + d[i]] : kNegInf;
+#pragma unroll
+        for (int i = 0; i < kExpand; ++i) {
+          const float jfwd = __shfl_sync(0xffffffffu, fwd, j[i]);
+          if (p[i] < last) {
+            uint8_t keep = 0;
+            if (d[i] >= 0) {
+              const float bl = ll[i] + nb[i];
+              if (bl + jfwd >= -beam) {
+                keep = 1;
+                atomicMax(&sh->wbest[warp][j[i]], OrderedInt(bl));
+                atomicAdd(&sh->wcnt[warp][j[i]], 1);
+              }
+            }
+            v.arc_keep[p[i]] = keep;
+          }
+        }
+      }
+      __syncwarp();
+      if (k < ns) {
+        const float best = OrderedFloat(sh->wbest[warp][lane]);
+        v.st_cnt[s0 + k] = sh->wcnt[warp][lane];
         const float bwd = (v.st_astate[s0 + k] == g_final) ? -fwd : best;
         v.st_bwd[s0 + k] = bwd;
         keep_state = (bwd != kNegInf) || t == begin;
@@ -433,7 +644,7 @@ __device__ void PruneWindow(const SearchArgs &g, const SeqView &v, const Team &t
       if (k < ns) v.st_new[s0 + k] = keep_state ? j : -1;
       kept += tot;
     }
-    tm.Sync();
+    // (the barrier inside the last scan has published this frame's backward scores)
   }
 
   // forwards: move the surviving states and arcs down.  Reads of a chunk complete
@@ -454,12 +665,11 @@ __device__ void PruneWindow(const SearchArgs &g, const SeqView &v, const Team &t
         as = v.st_astate[old_s0 + k];
         fwd = v.st_fwd[old_s0 + k];
         bwd = v.st_bwd[old_s0 + k];
-        const int32_t p0 = v.st_arc0[old_s0 + k], p1 = v.st_arc0[old_s0 + k + 1];
-        for (int32_t p = p0; p < p1; ++p) cnt += v.arc_keep[p];
+        cnt = v.st_cnt[old_s0 + k];
       }
-      int32_t stot, atot;
-      const int32_t sj = s_run + tm.Scan(keep_state, &stot);
-      const int32_t aj = a_run + tm.Scan(cnt, &atot);
+      int32_t stot, atot, aj;
+      const int32_t sj = s_run + tm.Scan2(keep_state, cnt, &aj, &stot, &atot);
+      aj += a_run;
       if (keep_state) {
         v.st_astate[ws + sj] = as;
         v.st_fwd[ws + sj] = fwd;
@@ -469,7 +679,6 @@ __device__ void PruneWindow(const SearchArgs &g, const SeqView &v, const Team &t
       s_run += stot;
       a_run += atot;
     }
-    tm.Sync();
     int32_t moved = 0;
     const bool renumber = t + 1 < end;  // the states of frame `end` keep their numbers
     for (int32_t base = 0; base < na; base += tm.threads * kPer) {
@@ -500,38 +709,46 @@ __device__ void PruneWindow(const SearchArgs &g, const SeqView &v, const Team &t
       }
       moved += tot;
     }
-    tm.Sync();
+    // the new offsets go to the frame tables after the loop: a thread that runs
+    // ahead through empty frames must still find the old ones
     if (tm.tid == 0) {
-      v.frame_s0[t] = ws;
-      v.frame_a0[t] = wa;
+      sh->new_s0[t - begin] = ws;
+      sh->new_a0[t - begin] = wa;
     }
     ws += s_run;
     wa += a_run;
     old_s0 = old_s1;
     old_a0 = old_a1;
   }
-  // frame `end`: its states follow the compacted frames
+  // frame `end`: its states, and the layout of their arcs, follow the compacted frames
   const int32_t ns_end = *s_top - old_s0;
   for (int32_t base = 0; base < ns_end; base += tm.threads) {
     const int32_t k = base + tm.tid;
-    int32_t as = 0, fwd = 0;
+    int32_t as = 0, fwd = 0, arc0 = 0;
     float bwd = 0.0f;
     if (k < ns_end) {
       as = v.st_astate[old_s0 + k];
       fwd = v.st_fwd[old_s0 + k];
       bwd = v.st_bwd[old_s0 + k];
+      arc0 = v.st_arc0[old_s0 + k];
     }
     tm.Sync();
     if (k < ns_end) {
       v.st_astate[ws + k] = as;
       v.st_fwd[ws + k] = fwd;
       v.st_bwd[ws + k] = bwd;
+      v.st_arc0[ws + k] = arc0 - old_a0 + wa;
     }
   }
+  tm.Sync();  // every thread is past the old frame tables
   if (tm.tid == 0) {
+    for (int32_t t = begin; t < end; ++t) {
+      v.frame_s0[t] = sh->new_s0[t - begin];
+      v.frame_a0[t] = sh->new_a0[t - begin];
+    }
     v.frame_s0[end] = ws;
     v.frame_a0[end] = wa;
-    v.st_arc0[ws] = wa;  // closes the arc range of the last state of frame end - 1
+    v.st_arc0[ws + ns_end] = wa + na_end;  // closes the last arc range
   }
   tm.Sync();
   *s_top = ws + ns_end;
@@ -543,7 +760,7 @@ __device__ void PruneWindow(const SearchArgs &g, const SeqView &v, const Team &t
 __global__ void __launch_bounds__(kSearchThreads, 1) PrunedSearch(const SearchArgs g) {
   __shared__ Shared sh;
   if (threadIdx.x == 0) {
-    sh.phase_i = sh.phase_f = 0;
+    sh.phase_i = sh.phase_f = sh.phase_l = 0;
     sh.beam = g.search_beam;
   }
   __syncthreads();
@@ -557,12 +774,15 @@ __global__ void __launch_bounds__(kSearchThreads, 1) PrunedSearch(const SearchAr
 
   // frame 0: the start state, if the graph has states (:435-472)
   int32_t s0 = 0, ns = g_states > 0 ? 1 : 0, a0 = 0;
+  int32_t na = ns ? g.a_rs2[g_start + 1] - g.a_rs2[g_start] : 0;
   if (tm.tid == 0) {
     v.frame_s0[0] = 0;
     v.frame_a0[0] = 0;
+    v.st_arc0[0] = 0;
     if (ns) {
       v.st_astate[0] = g_start;
       v.st_fwd[0] = OrderedInt(0.0f);
+      v.st_arc0[1] = na;
     }
   }
   tm.Sync();
@@ -570,29 +790,32 @@ __global__ void __launch_bounds__(kSearchThreads, 1) PrunedSearch(const SearchAr
   int32_t status = kSeqOk;
   int32_t next_end = kWindowShift;  // end of the next pruning window
   for (int32_t t = 0; t < T; ++t) {
-    int32_t na, nn;
-    if (!SearchStep(g, v, tm, seq, t, final_t, row0, s0, ns, a0, &na, &nn)) {
+    if (tm.tid == 0) {  // published by the barriers inside the step
+      v.frame_s0[t + 1] = s0 + ns;
+      v.frame_a0[t + 1] = a0 + na;
+    }
+    int32_t nn, na1;
+    if (!SearchStep(g, v, tm, seq, t, final_t, row0, s0, ns, a0, na, &nn, &na1)) {
       status = kSeqOverflow;
       break;
     }
     s0 += ns;
     a0 += na;
     ns = nn;
+    na = na1;
     s_top = s0 + ns;
     a_top = a0;
-    if (tm.tid == 0) {
-      v.frame_s0[t + 1] = s0;
-      v.frame_a0[t + 1] = a0;
-    }
-    tm.Sync();
     const int32_t this_end = next_end >= T ? T : next_end;
     if (t == this_end - 1) {
       const int32_t begin = max(0, next_end - kWindow);
-      PruneWindow(g, v, tm, seq, begin, this_end, &s_top, &a_top);
+      PruneWindow(g, v, tm, seq, begin, this_end, na, &s_top, &a_top);
       s0 = s_top - ns;
       a0 = a_top;
       next_end += kWindowShift;
     }
+  }
+  if (status == kSeqOk) {  // the states of the last frame have no arcs in the lattice
+    for (int32_t k = tm.tid; k < ns; k += tm.threads) v.st_arc0[s0 + k] = a_top;
   }
   if (tm.tid == 0) {
     int32_t extra = 0;
@@ -741,15 +964,16 @@ int32_t MakePrunedLayout(const k2b200_pruned_args *a, char *ws, PrunedLayout *L)
   g.st_fwd = i32(ns);
   g.st_arc0 = i32(ns);
   g.st_new = i32(ns);
+  g.st_cnt = i32(ns);
   g.st_bwd = f32(ns);
   g.arc_aidx = i32(na);
   g.arc_dest = i32(na);
   g.arc_ll = f32(na);
   g.arc_end = f32(na);
   g.arc_keep = reinterpret_cast<uint8_t *>(ws + Take(&off, na));
-  L->winner_bytes = 4 * (g.a_stride ? (size_t)std::max(a->num_states, 1)
+  L->winner_bytes = 8 * (g.a_stride ? (size_t)std::max(a->num_states, 1)
                                     : n * (size_t)std::max(a->num_states, 1));
-  g.winner = reinterpret_cast<int32_t *>(ws + Take(&off, L->winner_bytes));
+  g.winner = reinterpret_cast<unsigned long long *>(ws + Take(&off, L->winner_bytes));
   g.frame_s0 = i32(n * ((size_t)T + 2));
   g.frame_a0 = i32(n * ((size_t)T + 2));
   g.seq_out = i32(4 * n);
@@ -789,7 +1013,7 @@ int32_t k2b200_intersect_dense_pruned_search(const k2b200_pruned_args *args, voi
                   (args->a_arcs || args->num_arcs == 0) && args->scores,
               "NULL input pointer");
   const int32_t n = args->num_seqs;
-  K2B_CUDA_OK(cudaMemsetAsync(L.g.winner, 0x7f, L.winner_bytes, stream));
+  K2B_CUDA_OK(cudaMemsetAsync(L.g.winner, 0, L.winner_bytes, stream));
   {
     // CTAs per sequence: as many as keep the GPU filled, within the portable
     // cluster size

@@ -194,9 +194,9 @@ def test_pruned_intersection_sizing_and_validation_need_no_gpu():
         ctypes.byref(a), ctypes.byref(nbytes), ctypes.byref(levels)) == 0
     # layers: (longest sequence's rows + 2) per sequence
     assert levels.value == 3 * (101 + 2)
-    # 17 bytes per arc, 20 per state, one table entry per (sequence, graph state)
-    arenas = 3 * (17 * (1 << 16) + 20 * ((1 << 15) + 1))
-    assert arenas + 3 * 5000 * 4 <= nbytes.value <= arenas + 3 * 5000 * 4 + (1 << 16)
+    # 17 bytes per arc, 24 per state, one 8-byte table entry per (sequence, graph state)
+    arenas = 3 * (17 * (1 << 16) + 24 * ((1 << 15) + 1))
+    assert arenas + 3 * 5000 * 8 <= nbytes.value <= arenas + 3 * 5000 * 8 + (1 << 16)
     for bad, msg in ((dict(search_beam=0.0), b"positive"),
                      (dict(min_active_states=10, max_active_states=10), b"min_active_states"),
                      (dict(num_fsas=2), b"one graph per sequence"),
