@@ -298,7 +298,10 @@ def run_ours(args):
     host_lp = w.log_probs.pin_memory()
     dev_lp = w.log_probs.to(dev)
     seg = w.supervision_segments
+    # per step the ranks all-reduce [loss, frames]; the pair is staged with one copy
     red = torch.zeros(2, dtype=torch.float64, device=dev)
+    red_src = torch.zeros(2, dtype=torch.float64, device=dev)
+    red_src[1] = float(frames)
 
     def step(lp_src, from_host):
         if from_host:
@@ -310,8 +313,8 @@ def run_ours(args):
         loss = k2.ctc_loss(graphs, dense, output_beam=w.output_beam, reduction="sum")
         loss.backward()
         if dist is not None:
-            red[0] = loss.detach().double()
-            red[1] = float(frames)
+            red_src[0:1].copy_(loss.detach().reshape(1))
+            red.copy_(red_src)
             dist.all_reduce(red)
             out = red[0]
         else:
