@@ -76,6 +76,9 @@ struct PhaseTimer {  // records start/stop events when profiling is enabled
 // plain event record/wait pairs, so they are also legal under stream capture.
 int32_t SideFork(cudaStream_t main, cudaStream_t *side);
 int32_t SideJoin(cudaStream_t main);
+// device -> host copy of a few bytes behind the side stream's work; blocks the host
+// until it (and not the main stream) is done
+int32_t SideReadBack(const void *device_src, size_t bytes, void *host_out);
 
 static inline size_t AlignUp(size_t x, size_t a = 256) { return (x + a - 1) / a * a; }
 

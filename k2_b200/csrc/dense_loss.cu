@@ -1720,31 +1720,33 @@ int32_t k2b200_dense_loss_forward(const k2b200_intersect_args *args, void *works
   }
   // The lattice is never built, but its size still decides the beam
   // (intersect_dense.cu:300-320).  The grid itself bounds it: count only when the
-  // bound does not already satisfy the limits.
+  // bound does not already satisfy the limits.  The count runs on the side stream
+  // beside the recursions, which start from the current beam at once; in the rare
+  // case that the sizes exceed the limits the beam shrinks and they run again.
   float beam = args->output_beam;
   long long arc_frames = 0;
   for (const FsaInfo &f : L.infos) arc_frames += (long long)f.tk * f.num_arcs;
-  if (L.grid_elems > args->max_states || arc_frames > args->max_arcs) {
-    long long h_totals[5];
-    K2B_FORWARD(PruneLoop(L, args, ws, stream, &beam, h_totals, /*sizes_only=*/true));
-  } else {
+  const bool need_count = L.grid_elems > args->max_states || arc_frames > args->max_arcs;
+  K2B_FORWARD(SideJoin(stream));  // the packed rows are ready before the recursions
+  for (int iter = 0;; ++iter) {
     K2B_FORWARD(LaunchCutoffs(L, args, ws, beam, stream));
-  }
-  if (beam_used) *beam_used = beam;
-  join_guard.armed = false;
-  K2B_FORWARD(SideJoin(stream));
-  {
-    PhaseTimer timer(kPhaseChain, stream);
+    if (need_count) {
+      K2B_FORWARD(SideFork(stream, &side));  // behind the cutoffs
+      PhaseTimer timer(kPhasePrune, side);
+      K2B_FORWARD(LaunchSizeCount(L, args, ws, side));
+    }
+    {
+      PhaseTimer timer(kPhaseChain, stream);
 #define K2B_CHAIN(DEG, MAXT)                                                              \
   (ls.stages == kChainGroup                                                               \
        ? LaunchChainLanes<DEG, MAXT, kChainGroup>(LL, args, ws, ls, tot_scores, stream)   \
        : LaunchChainLanes<DEG, MAXT, kChainGroupSmall>(LL, args, ws, ls, tot_scores, stream))
-    if (LL.k_deg == 3 && LL.threads <= 512) K2B_FORWARD(K2B_CHAIN(3, 512));
-    else if (LL.k_deg == 3) K2B_FORWARD(K2B_CHAIN(3, 1024));
-    else if (LL.k_deg == 4 && LL.threads <= 512) K2B_FORWARD(K2B_CHAIN(4, 512));
-    else if (LL.k_deg == 4) K2B_FORWARD(K2B_CHAIN(4, 1024));
-    else
-      K2B_FORWARD(LaunchChainMasked(LL, args, ws, tot_scores, stream));
+      if (LL.k_deg == 3 && LL.threads <= 512) K2B_FORWARD(K2B_CHAIN(3, 512));
+      else if (LL.k_deg == 3) K2B_FORWARD(K2B_CHAIN(3, 1024));
+      else if (LL.k_deg == 4 && LL.threads <= 512) K2B_FORWARD(K2B_CHAIN(4, 512));
+      else if (LL.k_deg == 4) K2B_FORWARD(K2B_CHAIN(4, 1024));
+      else
+        K2B_FORWARD(LaunchChainMasked(LL, args, ws, tot_scores, stream));
 #undef K2B_CHAIN
     // graphs the lane kernel skipped or gave up on
     K2B_CUDA_OK(cudaFuncSetAttribute(GridChain, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -1758,8 +1760,17 @@ int32_t k2b200_dense_loss_forward(const k2b200_intersect_args *args, void *works
         reinterpret_cast<const float *>(ws + L.off_cutoffs),
         reinterpret_cast<ProbState *>(ws + LL.off_alpha),
         reinterpret_cast<ProbState *>(ws + LL.off_beta), tot_scores, unfit, p); NoteLaunch(); }
+    }
+    K2B_CUDA_OK(cudaGetLastError());
+    if (!need_count) break;
+    long long h_totals[5];
+    K2B_FORWARD(SideReadBack(ws + L.off_totals, sizeof(h_totals), h_totals));
+    if (!ReduceBeam(args, h_totals, &beam)) break;
+    K2B_REQUIRE(iter < 200, "output beam reduction did not converge");
   }
-  K2B_CUDA_OK(cudaGetLastError());
+  if (beam_used) *beam_used = beam;
+  join_guard.armed = false;
+  K2B_FORWARD(SideJoin(stream));
   return kOk;
 }
 

@@ -613,6 +613,51 @@ int32_t LaunchCutoffs(const Layout &L, const k2b200_intersect_args *a, char *ws,
 // reference does (intersect_dense.cu:300-320 and :854-862) until the lattice fits
 // max_states / max_arcs.  One host synchronisation per iteration.  h_totals:
 // states, arcs, candidate arcs, largest layer in states and in arcs.
+// Counts the states and arcs that the current cutoffs keep into totals[0] / totals[2]
+// (the sizes the lattice would have), without numbering anything.
+int32_t LaunchSizeCount(const Layout &L, const k2b200_intersect_args *args, char *ws,
+                        cudaStream_t stream) {
+  const FsaInfo *d_infos = reinterpret_cast<const FsaInfo *>(ws + L.off_infos);
+  const float *cutoffs = reinterpret_cast<const float *>(ws + L.off_cutoffs);
+  const float *fwd = reinterpret_cast<const float *>(ws + L.off_fwd),
+              *bwd = reinterpret_cast<const float *>(ws + L.off_bwd);
+  long long *totals = reinterpret_cast<long long *>(ws + L.off_totals);
+  K2B_CUDA_OK(cudaMemsetAsync(totals, 0, 5 * sizeof(long long), stream));
+  if (L.grid_elems > 0)
+    for (int32_t first = 0; first < args->num_fsas; first += 65535) {
+      int64_t max_elems = (int64_t)(L.max_tk + 1) * L.max_states;
+      dim3 grid((unsigned)std::min<int64_t>(CeilDiv(max_elems, 256 * 16), 64),
+                std::min(args->num_fsas - first, 65535));
+      { CountStates<<<grid, 256, 0, stream>>>(
+          d_infos, args->a_row_splits2, fwd, bwd, cutoffs,
+          reinterpret_cast<unsigned long long *>(totals), first); NoteLaunch(); }
+    }
+  K2B_CUDA_OK(cudaGetLastError());
+  return kOk;
+}
+
+// The reference's retry rule (intersect_dense.cu:300-320 and :854-862): when the
+// lattice would exceed max_states or max_arcs the beam shrinks by
+// sqrt(limit / total), clamped to [0.25, 0.75] of itself.  Returns false when the
+// sizes are within the limits.
+bool ReduceBeam(const k2b200_intersect_args *args, const long long *h_totals, float *beam) {
+  long long limit = 0, total = 0;
+  if (h_totals[0] > args->max_states) {
+    limit = args->max_states;
+    total = h_totals[0];
+  } else if (h_totals[2] > args->max_arcs) {
+    limit = args->max_arcs;
+    total = h_totals[2];
+  } else {
+    return false;
+  }
+  float cur = *beam, next = cur * sqrt(limit * 1.0 / total);
+  if (next < cur * 0.25) next = cur * 0.25;
+  if (next > cur * 0.75) next = cur * 0.75;
+  *beam = next;
+  return true;
+}
+
 int32_t PruneLoop(const Layout &L, const k2b200_intersect_args *args, char *ws,
                   cudaStream_t stream, float *beam_io, long long *h_totals, bool sizes_only) {
   const FsaInfo *d_infos = reinterpret_cast<const FsaInfo *>(ws + L.off_infos);
@@ -632,16 +677,7 @@ int32_t PruneLoop(const Layout &L, const k2b200_intersect_args *args, char *ws,
     { Cutoffs<<<CeilDiv(args->num_fsas, 128), 128, 0, stream>>>(d_infos, args->num_fsas, fwd, bwd,
                                                               beam, cutoffs); NoteLaunch(); }
     if (sizes_only) {
-      K2B_CUDA_OK(cudaMemsetAsync(totals, 0, 5 * sizeof(long long), stream));
-      if (L.grid_elems > 0)
-        for (int32_t first = 0; first < args->num_fsas; first += 65535) {
-          int64_t max_elems = (int64_t)(L.max_tk + 1) * L.max_states;
-          dim3 grid((unsigned)std::min<int64_t>(CeilDiv(max_elems, 256 * 16), 64),
-                    std::min(args->num_fsas - first, 65535));
-          { CountStates<<<grid, 256, 0, stream>>>(
-              d_infos, args->a_row_splits2, fwd, bwd, cutoffs,
-              reinterpret_cast<unsigned long long *>(totals), first); NoteLaunch(); }
-        }
+      K2B_FORWARD(LaunchSizeCount(L, args, ws, stream));
     } else {
       if (L.total_words > 0)
         for (int32_t first = 0; first < args->num_fsas; first += 65535) {
@@ -661,21 +697,7 @@ int32_t PruneLoop(const Layout &L, const k2b200_intersect_args *args, char *ws,
     K2B_CUDA_OK(cudaMemcpyAsync(h_totals, totals, 5 * sizeof(long long), cudaMemcpyDeviceToHost,
                                 stream));
     K2B_CUDA_OK(cudaStreamSynchronize(stream));
-    // the reference's retry loop, intersect_dense.cu:300-320 and :854-862
-    long long limit = 0, total = 0;
-    if (h_totals[0] > args->max_states) {
-      limit = args->max_states;
-      total = h_totals[0];
-    } else if (h_totals[2] > args->max_arcs) {
-      limit = args->max_arcs;
-      total = h_totals[2];
-    } else {
-      break;
-    }
-    float cur = beam, next = cur * sqrt(limit * 1.0 / total);
-    if (next < cur * 0.25) next = cur * 0.25;
-    if (next > cur * 0.75) next = cur * 0.75;
-    beam = next;
+    if (!ReduceBeam(args, h_totals, &beam)) break;
     if (iter > 200) {
       SetError("output beam reduction did not converge");
       return kInvalidArgument;

@@ -42,6 +42,9 @@ int32_t RunViterbi(const Layout &L, const k2b200_intersect_args *a, char *ws,
                    cudaStream_t stream, bool plan_ready = false);
 // sizes_only: just the totals the beam reduction needs (states and candidate arcs),
 // no keep masks or numbering.
+int32_t LaunchSizeCount(const Layout &L, const k2b200_intersect_args *args, char *ws,
+                        cudaStream_t stream);
+bool ReduceBeam(const k2b200_intersect_args *args, const long long *h_totals, float *beam);
 int32_t PruneLoop(const Layout &L, const k2b200_intersect_args *args, char *ws,
                   cudaStream_t stream, float *beam_io, long long *h_totals,
                   bool sizes_only = false);

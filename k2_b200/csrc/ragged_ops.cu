@@ -89,8 +89,10 @@ double ReadPhase(int phase, long long *count) {
 namespace {
 struct SideState {
   cudaStream_t stream = nullptr;
-  cudaEvent_t fork_ev = nullptr, join_ev = nullptr;
+  cudaEvent_t fork_ev = nullptr, join_ev = nullptr, host_ev = nullptr;
+  void *pinned = nullptr;  // kSidePinnedBytes of page-locked host memory
 };
+constexpr size_t kSidePinnedBytes = 256;
 std::mutex g_side_mutex;
 std::vector<SideState> g_side;
 
@@ -103,6 +105,8 @@ int32_t SideOfCurrentDevice(SideState **out) {
     K2B_CUDA_OK(cudaStreamCreateWithFlags(&st.stream, cudaStreamNonBlocking));
     K2B_CUDA_OK(cudaEventCreateWithFlags(&st.fork_ev, cudaEventDisableTiming));
     K2B_CUDA_OK(cudaEventCreateWithFlags(&st.join_ev, cudaEventDisableTiming));
+    K2B_CUDA_OK(cudaEventCreateWithFlags(&st.host_ev, cudaEventDisableTiming));
+    K2B_CUDA_OK(cudaHostAlloc(&st.pinned, kSidePinnedBytes, cudaHostAllocDefault));
   }
   *out = &st;
   return kOk;
@@ -125,6 +129,21 @@ int32_t SideJoin(cudaStream_t main) {
   K2B_FORWARD(SideOfCurrentDevice(&st));
   K2B_CUDA_OK(cudaEventRecord(st->join_ev, st->stream));
   K2B_CUDA_OK(cudaStreamWaitEvent(main, st->join_ev, 0));
+  return kOk;
+}
+
+// Copies `bytes` (at most 256) of device memory to `host_out` behind the work queued
+// on the side stream, and blocks the host until that copy - not the main stream - is
+// done.
+int32_t SideReadBack(const void *device_src, size_t bytes, void *host_out) {
+  std::lock_guard<std::mutex> lock(g_side_mutex);
+  SideState *st;
+  K2B_FORWARD(SideOfCurrentDevice(&st));
+  K2B_REQUIRE(bytes <= kSidePinnedBytes, "SideReadBack: too many bytes");
+  K2B_CUDA_OK(cudaMemcpyAsync(st->pinned, device_src, bytes, cudaMemcpyDeviceToHost, st->stream));
+  K2B_CUDA_OK(cudaEventRecord(st->host_ev, st->stream));
+  K2B_CUDA_OK(cudaEventSynchronize(st->host_ev));
+  memcpy(host_out, st->pinned, bytes);
   return kOk;
 }
 
