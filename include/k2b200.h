@@ -482,6 +482,37 @@ int32_t k2b200_fsa_properties(const int32_t *row_splits1, const int32_t *row_ids
                               int32_t num_arcs, int32_t *properties, void *tmp,
                               void *stream);
 
+/* ---------------------------------------------------------------------------
+ * Derivatives through per-state scores, for callers that differentiate
+ * get_forward_scores / get_backward_scores / get_arc_post.
+ * Replace k2::BackpropGetForwardScores (k2/csrc/fsa_utils.cu:1638-1795),
+ * k2::BackpropGetBackwardScores (:1457-1624) and k2::BackpropGetArcPost
+ * (:1281-1334), bound as _k2.backprop_get_{forward,backward}_scores_{float,double}
+ * and _k2.backprop_get_arc_post_* (k2/python/csrc/torch/fsa.cu:293-366, :461-490).
+ *
+ * k2b200_fsa_scores_backprop: `scores` are the forward (forward != 0) or backward
+ * scores of `fsas` in the given semiring and type; state_deriv[num_states] holds
+ * dL/d(score) on entry and is overwritten with the accumulated per-state
+ * derivatives; arc_deriv[num_arcs] receives dL/d(arc score).  The view needs the
+ * layering; the backward direction also the incoming-arc index.  Tropical forward
+ * scores need entering_arcs[num_states] (from k2b200_fsa_scores); tropical backward
+ * scores need best_leaving_tmp[num_states] as scratch and row_ids1 in the view.
+ * One launch, one CTA per FSA walking its layers.
+ *
+ * k2b200_fsa_arc_post_backprop: forward_deriv[s] / backward_deriv[s] = sum of
+ * arc_post_deriv over the arcs leaving / entering s, except the final state's
+ * forward and the start state's backward derivative, which are -0.5 times the sum
+ * over all arcs of the FSA.
+ * ------------------------------------------------------------------------- */
+int32_t k2b200_fsa_scores_backprop(const k2b200_fsa_view *fsas, int32_t forward,
+                                   int32_t log_semiring, int32_t use_double,
+                                   const void *scores, const int32_t *entering_arcs,
+                                   void *state_deriv, void *arc_deriv,
+                                   int32_t *best_leaving_tmp, void *stream);
+int32_t k2b200_fsa_arc_post_backprop(const k2b200_fsa_view *fsas, int32_t use_double,
+                                     const void *arc_post_deriv, void *forward_deriv,
+                                     void *backward_deriv, void *stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -188,6 +188,103 @@ class _GetTotScoresFunction(torch.autograd.Function):
         return None, None, None, scores_grad
 
 
+def _backprop_scores(fsas: Fsa, forward: bool, log_semiring: bool, use_double_scores: bool,
+                     scores: torch.Tensor, scores_grad: torch.Tensor) -> torch.Tensor:
+    """dL/d(arc scores) from dL/d(forward or backward scores): the
+    `_k2.backprop_get_{forward,backward}_scores_*` calls
+    (k2/python/csrc/torch/fsa.cu:293-366)."""
+    arcs = fsas.arcs
+    dev = arcs.device
+    dtype = torch.float64 if use_double_scores else torch.float32
+    state_deriv = scores_grad.detach().to(dtype).contiguous().clone()
+    arc_deriv = torch.zeros(arcs.num_elements(), dtype=dtype, device=dev)
+    entering = best_tmp = None
+    if not log_semiring:
+        if forward:
+            entering = fsas._get_entering_arcs(use_double_scores)
+        else:
+            best_tmp = torch.empty(arcs.num_states, dtype=torch.int32, device=dev)
+    view, keep = arcs.view(want_incoming=not forward)
+    with torch.cuda.device(dev):
+        _lib.check(_lib.lib.k2b200_fsa_scores_backprop(
+            ctypes.byref(view), int(forward), int(log_semiring), int(use_double_scores),
+            _lib.ptr(scores.contiguous()), _lib.ptr(entering), _lib.ptr(state_deriv),
+            _lib.ptr(arc_deriv), _lib.ptr(best_tmp), _lib.stream_of(dev)))
+    del keep
+    return arc_deriv
+
+
+class _GetForwardScoresFunction(torch.autograd.Function):
+    """Contract of k2/python/k2/autograd.py:120-199."""
+
+    @staticmethod
+    def forward(ctx, fsas: Fsa, log_semiring: bool, use_double_scores: bool,
+                unused_scores: torch.Tensor) -> torch.Tensor:
+        forward_scores = fsas._get_forward_scores(use_double_scores=use_double_scores,
+                                                  log_semiring=log_semiring).detach()
+        ctx.fsas, ctx.log_semiring, ctx.use_double_scores = fsas, log_semiring, use_double_scores
+        ctx.save_for_backward(forward_scores)
+        return forward_scores
+
+    @staticmethod
+    def backward(ctx, forward_scores_grad: torch.Tensor):
+        forward_scores, = ctx.saved_tensors
+        scores_grad = _backprop_scores(ctx.fsas, True, ctx.log_semiring, ctx.use_double_scores,
+                                       forward_scores, forward_scores_grad)
+        return None, None, None, scores_grad
+
+
+class _GetBackwardScoresFunction(torch.autograd.Function):
+    """Contract of k2/python/k2/autograd.py:202-270."""
+
+    @staticmethod
+    def forward(ctx, fsas: Fsa, log_semiring: bool, use_double_scores: bool,
+                unused_scores: torch.Tensor) -> torch.Tensor:
+        backward_scores = fsas._get_backward_scores(use_double_scores=use_double_scores,
+                                                    log_semiring=log_semiring).detach()
+        ctx.fsas, ctx.log_semiring, ctx.use_double_scores = fsas, log_semiring, use_double_scores
+        ctx.save_for_backward(backward_scores)
+        return backward_scores
+
+    @staticmethod
+    def backward(ctx, backward_scores_grad: torch.Tensor):
+        backward_scores, = ctx.saved_tensors
+        scores_grad = _backprop_scores(ctx.fsas, False, ctx.log_semiring, ctx.use_double_scores,
+                                       backward_scores, backward_scores_grad)
+        return None, None, None, scores_grad
+
+
+class _GetArcPostFunction(torch.autograd.Function):
+    """Contract of k2/python/k2/autograd.py:273-347: the posteriors depend on the arc
+    scores directly and through the forward and backward scores, which are passed in
+    as differentiable tensors."""
+
+    @staticmethod
+    def forward(ctx, fsas: Fsa, log_semiring: bool, use_double_scores: bool,
+                unused_scores: torch.Tensor, forward_scores: torch.Tensor,
+                backward_scores: torch.Tensor) -> torch.Tensor:
+        arc_post = fsas._get_arc_post(use_double_scores=use_double_scores,
+                                      log_semiring=log_semiring).detach()
+        ctx.fsas, ctx.use_double_scores = fsas, use_double_scores
+        return arc_post
+
+    @staticmethod
+    def backward(ctx, arc_post_grad: torch.Tensor):
+        arcs = ctx.fsas.arcs
+        dev = arcs.device
+        dtype = torch.float64 if ctx.use_double_scores else torch.float32
+        arc_scores_grad = arc_post_grad.detach().to(dtype).contiguous().clone()
+        forward_grad = torch.zeros(arcs.num_states, dtype=dtype, device=dev)
+        backward_grad = torch.zeros(arcs.num_states, dtype=dtype, device=dev)
+        view, keep = arcs.view(want_incoming=True)
+        with torch.cuda.device(dev):
+            _lib.check(_lib.lib.k2b200_fsa_arc_post_backprop(
+                ctypes.byref(view), int(ctx.use_double_scores), _lib.ptr(arc_scores_grad),
+                _lib.ptr(forward_grad), _lib.ptr(backward_grad), _lib.stream_of(dev)))
+        del keep
+        return None, None, None, arc_scores_grad, forward_grad, backward_grad
+
+
 class _IntersectDenseFunction(torch.autograd.Function):
 
     @staticmethod

@@ -304,15 +304,27 @@ class Fsa(object):
         return _GetTotScoresFunction.apply(self, log_semiring, use_double_scores, self.scores)
 
     def get_forward_scores(self, use_double_scores: bool, log_semiring: bool) -> torch.Tensor:
-        """Forward score per state (fsa.py:626-644).  Not differentiable here:
-        only the total scores take part in autograd on this path."""
-        return self._get_forward_scores(use_double_scores, log_semiring).detach()
+        """Forward score per state (k2/python/k2/fsa.py:626-644); differentiable w.r.t.
+        `self.scores`."""
+        from .autograd import _GetForwardScoresFunction
+        return _GetForwardScoresFunction.apply(self, log_semiring, use_double_scores,
+                                               self.scores)
 
     def get_backward_scores(self, use_double_scores: bool, log_semiring: bool) -> torch.Tensor:
-        return self._get_backward_scores(use_double_scores, log_semiring).detach()
+        """Backward score per state (k2/python/k2/fsa.py:734-752); differentiable w.r.t.
+        `self.scores`."""
+        from .autograd import _GetBackwardScoresFunction
+        return _GetBackwardScoresFunction.apply(self, log_semiring, use_double_scores,
+                                                self.scores)
 
     def get_arc_post(self, use_double_scores: bool, log_semiring: bool) -> torch.Tensor:
-        return self._get_arc_post(use_double_scores, log_semiring).detach()
+        """Log posterior per arc (k2/python/k2/fsa.py:790-817); differentiable w.r.t.
+        `self.scores`, directly and through the forward and backward scores."""
+        from .autograd import _GetArcPostFunction
+        forward_scores = self.get_forward_scores(use_double_scores, log_semiring)
+        backward_scores = self.get_backward_scores(use_double_scores, log_semiring)
+        return _GetArcPostFunction.apply(self, log_semiring, use_double_scores, self.scores,
+                                         forward_scores, backward_scores)
 
     # ------------------------------------------------------------------ text form
     @classmethod

@@ -68,6 +68,10 @@ def lib():
                                            _f64p]
         L.kref_tot_scores_and_arc_post.argtypes = [ctypes.c_void_p, ctypes.c_int32, _f64p,
                                                    _f64p, _f64p, _f64p]
+        L.kref_backprop_scores.argtypes = [ctypes.c_void_p, ctypes.c_int32, ctypes.c_int32,
+                                           ctypes.c_int32, _f64p, _i32p, _f64p, _f64p]
+        L.kref_backprop_arc_post.argtypes = [ctypes.c_void_p, ctypes.c_int32, _f64p, _f64p,
+                                             _f64p]
         L.kref_shortest_path.argtypes = [ctypes.c_void_p, _i32p, _i32p, _i32p]
         L.kref_properties.argtypes = [ctypes.c_void_p, _i32p]
         _lib = L
@@ -176,6 +180,31 @@ def forward_scores(f: HostFsaVec, log_semiring=True, use_double=True,
                                  _p(ea, _i32p)) != 0:
         raise RuntimeError("k2 reference raised: " + _err())
     return (out, ea) if want_entering_arcs else out
+
+
+def backprop_scores(f: HostFsaVec, forward: bool, scores, deriv_in, log_semiring=True,
+                    use_double=True, entering_arcs=None):
+    """d(sum(deriv_in * scores)) / d(arc scores) for forward (or backward) scores."""
+    h = to_handle(f)
+    scores = np.ascontiguousarray(scores, np.float64)
+    deriv_in = np.ascontiguousarray(deriv_in, np.float64)
+    ea = None if entering_arcs is None else np.ascontiguousarray(entering_arcs, np.int32)
+    out = np.zeros(f.num_arcs, np.float64)
+    if lib().kref_backprop_scores(h.ptr, int(forward), int(log_semiring), int(use_double),
+                                  _p(scores, _f64p), _p(ea, _i32p), _p(deriv_in, _f64p),
+                                  _p(out, _f64p)) != 0:
+        raise RuntimeError("k2 reference raised: " + _err())
+    return out
+
+
+def backprop_arc_post(f: HostFsaVec, arc_post_deriv, use_double=True):
+    h = to_handle(f)
+    d = np.ascontiguousarray(arc_post_deriv, np.float64)
+    fd, bd = np.zeros(f.num_states, np.float64), np.zeros(f.num_states, np.float64)
+    if lib().kref_backprop_arc_post(h.ptr, int(use_double), _p(d, _f64p), _p(fd, _f64p),
+                                    _p(bd, _f64p)) != 0:
+        raise RuntimeError("k2 reference raised: " + _err())
+    return fd, bd
 
 
 def backward_scores(f: HostFsaVec, log_semiring=True, use_double=True):

@@ -92,6 +92,38 @@ struct FsaVecHandle {
     return ret;                         \
   }
 
+template <typename T>
+static k2::Array1<T> Narrow(const double *src, int32_t n) {
+  k2::Array1<T> a(k2::GetCpuContext(), n);
+  for (int32_t i = 0; i < n; ++i) a.Data()[i] = (T)src[i];
+  return a;
+}
+
+template <typename T>
+static void BackpropScoresT(k2::FsaVec &fsas, bool forward, bool log_semiring,
+                            const double *scores, const int32_t *entering_arcs,
+                            const double *deriv_in, double *arc_deriv) {
+  int32_t ns = fsas.TotSize(1), na = fsas.NumElements();
+  k2::Ragged<int32_t> state_batches = k2::GetStateBatches(fsas, true);
+  k2::Array1<T> sc = Narrow<T>(scores, ns), din = Narrow<T>(deriv_in, ns);
+  k2::Array1<T> out;
+  if (forward) {
+    k2::Ragged<int32_t> leaving = k2::GetLeavingArcIndexBatches(fsas, state_batches);
+    k2::Array1<int32_t> ea;
+    if (!log_semiring) ea = FromHost(entering_arcs, ns);
+    out = k2::BackpropGetForwardScores<T>(fsas, state_batches, leaving, log_semiring,
+                                          log_semiring ? nullptr : &ea, sc, din);
+  } else {
+    k2::Array1<int32_t> dest_states = k2::GetDestStates(fsas, true);
+    k2::Ragged<int32_t> incoming = k2::GetIncomingArcs(fsas, dest_states);
+    k2::Ragged<int32_t> entering =
+        k2::GetEnteringArcIndexBatches(fsas, incoming, state_batches);
+    out = k2::BackpropGetBackwardScores<T>(fsas, state_batches, entering, log_semiring, sc,
+                                           din);
+  }
+  for (int32_t i = 0; i < na; ++i) arc_deriv[i] = out.Data()[i];
+}
+
 extern "C" {
 
 const char *kref_last_error() { return g_last_error.c_str(); }
@@ -312,6 +344,47 @@ int32_t kref_tot_scores_and_arc_post(void *handle, int32_t use_double,
       k2::Array1<float> p = k2::GetArcPost<float>(fsas, f, b);
       for (int32_t i = 0; i < na; ++i) arc_post[i] = p.Data()[i];
     }
+  }
+  return 0;
+  KREF_CATCH(-1)
+}
+
+// Derivatives of forward / backward scores w.r.t. the arc scores
+// (k2/csrc/fsa_utils.cu:1638-1795 and :1457-1624).  scores / deriv_in: [num_states]
+// double (narrowed when use_double == 0); arc_deriv: [num_arcs] double.
+int32_t kref_backprop_scores(void *handle, int32_t forward, int32_t log_semiring,
+                             int32_t use_double, const double *scores,
+                             const int32_t *entering_arcs, const double *deriv_in,
+                             double *arc_deriv) {
+  KREF_TRY
+  k2::FsaVec &fsas = reinterpret_cast<FsaVecHandle *>(handle)->fsas;
+  if (use_double)
+    BackpropScoresT<double>(fsas, forward != 0, log_semiring != 0, scores, entering_arcs,
+                            deriv_in, arc_deriv);
+  else
+    BackpropScoresT<float>(fsas, forward != 0, log_semiring != 0, scores, entering_arcs,
+                           deriv_in, arc_deriv);
+  return 0;
+  KREF_CATCH(-1)
+}
+
+// Derivatives of the arc posteriors w.r.t. forward and backward scores
+// (k2/csrc/fsa_utils.cu:1281-1334).
+int32_t kref_backprop_arc_post(void *handle, int32_t use_double, const double *arc_post_deriv,
+                               double *forward_deriv, double *backward_deriv) {
+  KREF_TRY
+  k2::FsaVec &fsas = reinterpret_cast<FsaVecHandle *>(handle)->fsas;
+  int32_t ns = fsas.TotSize(1), na = fsas.NumElements();
+  k2::Array1<int32_t> dest_states = k2::GetDestStates(fsas, true);
+  k2::Ragged<int32_t> incoming = k2::GetIncomingArcs(fsas, dest_states);
+  if (use_double) {
+    k2::Array1<double> d = Narrow<double>(arc_post_deriv, na), f, b;
+    k2::BackpropGetArcPost<double>(fsas, incoming, d, &f, &b);
+    for (int32_t i = 0; i < ns; ++i) forward_deriv[i] = f.Data()[i], backward_deriv[i] = b.Data()[i];
+  } else {
+    k2::Array1<float> d = Narrow<float>(arc_post_deriv, na), f, b;
+    k2::BackpropGetArcPost<float>(fsas, incoming, d, &f, &b);
+    for (int32_t i = 0; i < ns; ++i) forward_deriv[i] = f.Data()[i], backward_deriv[i] = b.Data()[i];
   }
   return 0;
   KREF_CATCH(-1)
