@@ -53,8 +53,8 @@ def _check_properties(k2, w, graphs, log_probs, dense, lat, check_best=True):
     assert torch.equal(expect, lat.scores.detach())
     assert torch.equal(lat.labels, graphs.labels[map_a.long()])
     # forward total == backward total
-    fwd = lat.get_forward_scores(True, True)
-    bwd = lat.get_backward_scores(True, True)
+    fwd = lat.get_forward_scores(True, True).detach()
+    bwd = lat.get_backward_scores(True, True).detach()
     rs1 = lat.arcs.row_splits(1).long()
     nonempty = rs1[1:] > rs1[:-1]
     a_fin = fwd[(rs1[1:] - 1).clamp(min=0)][nonempty]
@@ -79,8 +79,8 @@ def _check_properties(k2, w, graphs, log_probs, dense, lat, check_best=True):
         path_tot = best.get_tot_scores(log_semiring=False, use_double_scores=True)
         assert torch.allclose(path_tot[nonempty], trop[nonempty], rtol=1e-9)
         # every kept arc lies within the beam of the best path (+ rounding)
-        tf = lat.get_forward_scores(True, False)
-        tb = lat.get_backward_scores(True, False)
+        tf = lat.get_forward_scores(True, False).detach()
+        tb = lat.get_backward_scores(True, False).detach()
         arcs = lat.arcs
         src = arcs.row_ids(2).long()
         fsa = arcs.row_ids(1)[src].long()

@@ -22,10 +22,10 @@ def test_cuda_path_reproduces_reference_fixtures(case):
                                     case["amap"], mode=mode)
         same_fsa(fsa_to_host(lat, ma, mb), case["lattice"], f"{case['name']} mode {mode}")
     for tag, log in (("log", True), ("trop", False)):
-        f = lat.get_forward_scores(True, log).cpu().numpy()
-        b = lat.get_backward_scores(True, log).cpu().numpy()
+        f = lat.get_forward_scores(True, log).detach().cpu().numpy()
+        b = lat.get_backward_scores(True, log).detach().cpu().numpy()
         t = lat.get_tot_scores(True, log).detach().cpu().numpy()
-        p = lat.get_arc_post(True, log).cpu().numpy()
+        p = lat.get_arc_post(True, log).detach().cpu().numpy()
         assert close(f, case[f"fwd_{tag}"], 1e-9, 1e-9) and close(b, case[f"bwd_{tag}"], 1e-9, 1e-9)
         assert close(t, case[f"tot_{tag}"], 1e-9, 1e-9)
         fin = np.isfinite(case[f"post_{tag}"])

@@ -82,10 +82,10 @@ def _check_scores(k2, lat, want):
             of = oracle.forward_scores(want, log_semiring, use_double)
             ob = oracle.backward_scores(want, log_semiring, use_double)
             ot, op = oracle.tot_scores_and_arc_post(want, of, ob, use_double)
-            f = lat.get_forward_scores(use_double, log_semiring).cpu().numpy()
-            b = lat.get_backward_scores(use_double, log_semiring).cpu().numpy()
+            f = lat.get_forward_scores(use_double, log_semiring).detach().cpu().numpy()
+            b = lat.get_backward_scores(use_double, log_semiring).detach().cpu().numpy()
             t = lat.get_tot_scores(use_double, log_semiring).detach().cpu().numpy()
-            p = lat.get_arc_post(use_double, log_semiring).cpu().numpy()
+            p = lat.get_arc_post(use_double, log_semiring).detach().cpu().numpy()
             assert close(f, of, **tol) and close(b, ob, **tol), (log_semiring, use_double)
             assert close(t, ot, **tol), (log_semiring, use_double)
             finite = np.isfinite(op)
