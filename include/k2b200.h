@@ -42,7 +42,8 @@ typedef enum {
 
 /* Text of the last error on the calling thread. */
 const char *k2b200_last_error(void);
-/* ABI version of the library (bumped on any signature change). */
+/* ABI version of the library (bumped on any signature change or new entry point;
+ * 3: pruned intersection, score derivatives, k2b200_upload_i32). */
 int32_t k2b200_abi_version(void);
 
 /* Benchmark bookkeeping (no counterpart in the reference's bindings; its

@@ -1,6 +1,8 @@
-"""The two autograd Functions of the path, with the reference's contracts
-(k2/python/k2/autograd.py:30-117 `_GetTotScoresFunction`, :511-664
-`_IntersectDenseFunction`), and `intersect_dense` itself (:751-824)."""
+"""The autograd Functions of the path, with the reference's contracts
+(k2/python/k2/autograd.py:30-117 `_GetTotScoresFunction`, :120-347 the per-state
+score and posterior Functions, :350-510 `_IntersectDensePrunedFunction`, :511-664
+`_IntersectDenseFunction`), `intersect_dense` (:751-824) and `intersect_dense_pruned`
+(:667-746), plus the lattice-free total scores that `ctc_loss` uses."""
 import ctypes
 from typing import List, Optional, Tuple
 
