@@ -13,11 +13,12 @@
 //     backward thread of the reference never changes what the forward pass reads,
 //     so the windows are simply run in order.
 //
-// Sequences are independent, so one CTA owns one sequence from the first frame to
-// the last: no host round trip per frame, no hash (a direct table per sequence,
-// indexed by graph state, plays its role) and no kernel waits on another.  States
-// and arcs of all frames of a sequence live in one arena, frame after frame, so the
-// pruned result is already in lattice order and the output pass is a copy.
+// Sequences are independent, so one team of CTAs (a thread-block cluster of 1 to 8)
+// owns one sequence from the first frame to the last: no host round trip per frame,
+// no hash (a direct table per sequence, indexed by graph state, plays its role) and
+// no kernel waits on another.  States and arcs of all frames of a sequence live in
+// one arena, frame after frame, so the pruned result is already in lattice order and
+// the output pass is a copy.
 #include <algorithm>
 #include <climits>
 #include <cmath>
@@ -38,7 +39,7 @@ constexpr int kSearchThreads = 1024;
 constexpr int kWindow = 30;       // frames pruned per backward phase (:171)
 constexpr int kWindowShift = 20;  // frames between two phases (:172)
 
-// order-preserving float <-> int (k2/csrc/utils.h:609-624 plays the same role)
+// order-preserving float <-> int (as k2/csrc/utils.h:406-414)
 __device__ __forceinline__ int32_t OrderedInt(float f) {
   int32_t i = __float_as_int(f);
   return i >= 0 ? i : i ^ 0x7fffffff;
