@@ -41,10 +41,20 @@ def parse_args():
     p.add_argument("--impl", default="ours", choices=["ours", "reference"])
     p.add_argument("--workload", default="ctc_large")
     p.add_argument("--scale", type=float, default=1.0)
+    p.add_argument("--utterances", type=int, default=None,
+                   help="lfmmi_den only: batch size, e.g. 16 = one GPU's share of 128 split 8 ways")
     p.add_argument("--no-cpu-baseline", action="store_true")
     p.add_argument("--decode", action="store_true",
                    help="time the decoding path instead: hlg_decode through intersect_dense_pruned")
     return p.parse_args()
+
+
+def make_workload(args, seed):
+    from k2_b200 import synthetic as syn
+    if args.utterances is not None:
+        assert args.workload == "lfmmi_den", "--utterances applies to lfmmi_den"
+        return syn.lfmmi_den(seed=seed, scale=args.scale, utterances=args.utterances)
+    return syn.WORKLOADS[args.workload](seed=seed, scale=args.scale)
 
 
 # --------------------------------------------------------------------------- clocks
@@ -218,7 +228,7 @@ def run_reference(args):
     if rank != 0:
         return
     from k2_b200 import synthetic as syn
-    w = syn.WORKLOADS[args.workload](seed=0, scale=args.scale)
+    w = make_workload(args, 0)
     impl_mod, kind = pick_cpu_impl()
     graphs, scores, row_splits = host_inputs(w)
     frames = w.num_frames
@@ -291,7 +301,7 @@ def run_ours(args):
         dist.init_process_group("nccl", device_id=dev)
 
     # every rank owns a whole batch (weak scaling); seeds differ per rank
-    w = syn.WORKLOADS[args.workload](seed=rank, scale=args.scale)
+    w = make_workload(args, rank)
     frames = w.num_frames
     graphs = syn.build_graphs(w, dev)
     graphs.arcs.incoming()  # graph preprocessing is cached across steps

@@ -137,8 +137,12 @@ def den_graph(seed: int = 0, num_phones: int = 71, successors: int = 30):
     return _pack_graph(src, dest, label, score, final + 1)
 
 
-def lfmmi_den(seed: int = 0, scale: float = 1.0) -> Workload:
+def lfmmi_den(seed: int = 0, scale: float = 1.0, utterances: Optional[int] = None) -> Workload:
+    """`utterances` overrides the batch size alone (e.g. 16: one GPU's share of the
+    batch of 128 split eight ways)."""
     n, t = max(1, int(128 * scale)), max(8, int(500 * scale))
+    if utterances is not None:
+        n = utterances
     gen = torch.Generator().manual_seed(seed)
     log_probs = _log_probs(gen, n, t, 72, 1.0)
     seg = _segments(np.full(n, t, dtype=np.int64))

@@ -158,3 +158,20 @@ def test_best_path_agrees_with_the_exact_intersection_on_a_decoding_graph(k2):
     narrow = k2.intersect_dense_pruned(shared, dense, 20.0, 8.0, 30, 10000)
     tn = narrow.get_tot_scores(use_double_scores=True, log_semiring=False)
     assert (tn <= te + 1e-4).all()
+
+
+@pytest.mark.skipif(not ref.available(), reason="oracle/_ref/libk2ref.so not built")
+def test_many_sequences_with_their_own_graphs(k2):
+    """More sequences than SMs (one CTA per sequence), one CTC graph each, lengths from
+    1 frame to several pruning windows."""
+    from oracle import oracle
+    rng = np.random.default_rng(9)
+    n = 200
+    syms = [[int(x) for x in rng.integers(1, 9, size=int(rng.integers(1, 12)))] for _ in range(n)]
+    scores, brs = random_dense(rng, n, 70, 9, low_rows=False)
+    assert np.diff(brs).min() == 2  # a sequence of a single frame
+    g = oracle.ctc_graphs(syms, False)
+    for params in ((20.0, 8.0, 0, 1000, False), (5.0, 3.0, 4, 12, True)):
+        want = ref.intersect_dense_pruned(g, scores, brs, *params)
+        _, got = run_gpu(k2, dict(a=g, scores=scores, brs=brs, params=params))
+        same_fsa(got, want, str(params))
