@@ -13,6 +13,7 @@ from . import _lib
 from .dense_fsa_vec import DenseFsaVec
 from .fsa import Fsa
 from .ragged import RaggedArc
+from .ragged_tensor import RaggedTensor
 
 # 0 = automatic, 1 = one launch per frame, 2 = persistent kernel (see include/k2b200.h)
 VITERBI_MODE = 0
@@ -32,10 +33,13 @@ def _index_add(index: torch.Tensor, value: torch.Tensor, in_out: torch.Tensor) -
     _lib.note_launches(1)
 
 
-def index_select(src: torch.Tensor, index: torch.Tensor) -> torch.Tensor:
+def index_select(src, index: torch.Tensor):
     """ans[i] = src[index[i]], 0 where index[i] == -1 (1-D int32 `src`;
-    k2/python/csrc/torch/index_select.cu:56-92)."""
+    k2/python/csrc/torch/index_select.cu:56-92).  A ragged attribute is indexed by
+    rows, -1 giving an empty list (k2/python/k2/autograd.py:586-593)."""
     assert index.dtype == torch.int32
+    if isinstance(src, RaggedTensor):
+        return src.index(index, axis=0)[0]
     if src.dtype != torch.int32 or src.ndim != 1:
         # other dtypes are carried with torch's own gather (attribute plumbing)
         ans = src.index_select(0, index.clamp(min=0).long())

@@ -18,6 +18,8 @@ import torch
 
 from . import _lib
 from .ragged import RaggedArc
+from .ragged_tensor import RaggedTensor
+from .ragged_tensor import cat as _ragged_cat
 
 # k2/csrc/fsa.h:75-101
 VALID = 0x01
@@ -79,7 +81,13 @@ class Fsa(object):
     def __setattr__(self, name: str, value: Any) -> None:
         assert name not in ('_tensor_attr', '_non_tensor_attr', 'arcs', '_cache', '_properties',
                             'properties')
-        if isinstance(value, torch.Tensor):
+        if isinstance(value, RaggedTensor):
+            # one list per arc, e.g. ragged aux_labels (k2/python/k2/fsa.py:389-396)
+            assert value.dim0 == self.arcs.values().shape[0]
+            assert value.device == self.device
+            assert name not in ('labels', 'scores')
+            self._tensor_attr[name] = value
+        elif isinstance(value, torch.Tensor):
             assert value.shape[0] == self.arcs.values().shape[0]
             assert value.device == self.device
             if name == 'labels':
@@ -466,5 +474,9 @@ def create_fsa_vec(fsas: List[Fsa]) -> Fsa:
         these = {n for n, _ in f.named_tensor_attr(include_scores=False) if n != 'labels'}
         names = these if names is None else names & these
     for name in sorted(names or []):
-        setattr(ans, name, torch.cat([getattr(f, name) for f in fsas], dim=0).to(dev))
+        parts = [getattr(f, name) for f in fsas]
+        if isinstance(parts[0], RaggedTensor):
+            setattr(ans, name, _ragged_cat(parts).to(dev))
+        else:
+            setattr(ans, name, torch.cat(parts, dim=0).to(dev))
     return ans

@@ -8,6 +8,7 @@ import numpy as np
 import torch
 
 from . import _lib
+from .autograd import index_select
 from .fsa import Fsa
 from .ragged import RaggedArc
 
@@ -177,7 +178,7 @@ def arc_sort(fsa: Fsa, ret_arc_map: bool = False):
     amap = torch.from_numpy(order).to(dev)
     for name, value in fsa.named_tensor_attr(include_scores=False):
         if name != 'labels':
-            setattr(ans, name, value[amap.long()])
+            setattr(ans, name, index_select(value, amap))
     for name, value in fsa.named_non_tensor_attr():
         setattr(ans, name, value)
     return (ans, amap) if ret_arc_map else ans
@@ -232,7 +233,7 @@ def shortest_path(fsa: Fsa, use_double_scores: bool) -> Fsa:
     ans = Fsa(arcs, _check=False)
     for name, value in fsa.named_tensor_attr(include_scores=False):
         if name != 'labels':
-            setattr(ans, name, value[best.long()])
+            setattr(ans, name, index_select(value, best))
     for name, value in fsa.named_non_tensor_attr():
         setattr(ans, name, value)
     ans._best_arc_map = best

@@ -412,3 +412,28 @@ def test_dense_fsa_vec_from_logits_matches_log_softmax(k2):
     assert (a.grad - b.grad).abs().max().item() <= 2e-5
     # frames outside every segment get no gradient
     assert float(b.grad[2, :10].abs().max()) == 0.0
+
+
+def test_ragged_attributes_follow_the_arc_maps(k2):
+    """A ragged attribute (a list per arc, like ragged aux_labels) is carried through
+    intersect_dense, intersect_dense_pruned, arc_sort and shortest_path by rows."""
+    from gpu_util import DEV, dense_from_scores, host_to_fsa, intersect_raw
+    rng = np.random.default_rng(12)
+    a = random_fsa_vec(rng, 3, max_states=8, max_arcs=24, max_label=3, allow_empty=False)
+    scores, brs = random_dense(rng, 3, 9, 4)
+    rows = [[int(x) for x in rng.integers(1, 50, size=int(rng.integers(0, 4)))]
+            for _ in range(a.num_arcs)]
+    fsa = host_to_fsa(a)
+    fsa.tokens = k2.RaggedTensor(rows, device=DEV)
+    dense = dense_from_scores(scores, brs)
+    _, map_a, _ = intersect_raw(fsa, dense, 100.0)
+    lat = k2.intersect_dense(fsa, dense, output_beam=100.0)
+    assert lat.tokens.tolist() == [rows[i] for i in map_a.cpu().tolist()]
+    best = k2.shortest_path(lat, use_double_scores=True)
+    picked = lat.tokens.tolist()
+    assert best.tokens.tolist() == [picked[i] for i in best._best_arc_map.cpu().tolist()]
+    pruned = k2.intersect_dense_pruned(fsa, dense, 50.0, 50.0, 0, 1000)
+    assert sorted(map(tuple, pruned.tokens.tolist())) == sorted(map(tuple, lat.tokens.tolist()))
+    srt, amap = k2.arc_sort(fsa, ret_arc_map=True)
+    assert srt.tokens.tolist() == [rows[i] for i in amap.cpu().tolist()]
+    assert fsa.to("cpu").tokens.tolist() == rows

@@ -206,3 +206,21 @@ def test_pruned_intersection_sizing_and_validation_need_no_gpu():
         assert lib.k2b200_intersect_dense_pruned_workspace_bytes(
             ctypes.byref(a), ctypes.byref(nbytes), ctypes.byref(levels)) != 0
         assert msg in lib.k2b200_last_error(), (bad, lib.k2b200_last_error())
+
+
+def test_ragged_attribute_tensor_on_cpu():
+    """RaggedTensor.index / remove_values_leq / cat against plain Python lists
+    (k2.RaggedTensor semantics: an index of -1 gives an empty list)."""
+    import torch
+    from k2_b200.ragged_tensor import RaggedTensor, cat
+    rng = np.random.default_rng(4)
+    rows = [[int(x) for x in rng.integers(-1, 9, size=int(rng.integers(0, 5)))] for _ in range(40)]
+    r = RaggedTensor(rows)
+    assert r.tolist() == rows and r.dim0 == 40 and r.numel() == sum(map(len, rows))
+    idx = rng.integers(-1, 40, size=100).astype(np.int32)
+    out, pos = r.index(torch.from_numpy(idx), need_value_indexes=True)
+    assert out.tolist() == [rows[i] if i >= 0 else [] for i in idx]
+    assert torch.equal(r.values[pos.long()], out.values)
+    assert r.remove_values_leq(0).tolist() == [[x for x in row if x > 0] for row in rows]
+    assert cat([r, out]).tolist() == rows + out.tolist()
+    assert r.clone() == r and RaggedTensor([[1], []]) != RaggedTensor([[1]])
