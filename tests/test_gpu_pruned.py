@@ -175,3 +175,35 @@ def test_many_sequences_with_their_own_graphs(k2):
         want = ref.intersect_dense_pruned(g, scores, brs, *params)
         _, got = run_gpu(k2, dict(a=g, scores=scores, brs=brs, params=params))
         same_fsa(got, want, str(params))
+
+
+def test_decode_helpers_recover_the_transcripts(k2):
+    """get_lattice / one_best_decoding / get_aux_labels (k2/python/k2/decode.py) on
+    log-probs peaked along a valid CTC alignment, with tensor and ragged aux_labels."""
+    from gpu_util import DEV
+    rng = np.random.default_rng(2)
+    texts = [[int(x) for x in rng.integers(1, 9, size=int(rng.integers(2, 7)))] for _ in range(4)]
+    T, C = 40, 9
+    logits = torch.full((len(texts), T, C), -4.0)
+    lens = []
+    for i, text in enumerate(texts):
+        t = 0
+        for sym in text:
+            logits[i, t, 0] = 4.0          # a blank, then the symbol twice
+            logits[i, t + 1, sym] = 4.0
+            logits[i, t + 2, sym] = 4.0
+            t += 3
+        logits[i, t:, 0] = 4.0
+        lens.append(min(T, t + 2 + i))
+    log_prob = torch.log_softmax(logits, -1).to(DEV)
+    graphs = k2.ctc_graph(texts, device=DEV)
+    lattice = k2.get_lattice(log_prob, torch.tensor(lens), graphs, search_beam=20, output_beam=8,
+                             min_active_states=0, max_active_states=1000)
+    best = k2.one_best_decoding(lattice)
+    assert k2.get_aux_labels(best) == texts
+    # the same with a list per arc instead of one symbol per arc
+    aux = graphs.aux_labels.cpu().tolist()
+    del graphs.aux_labels
+    graphs.aux_labels = k2.RaggedTensor([[x] if x != 0 else [] for x in aux], device=DEV)
+    lattice = k2.get_lattice(log_prob, torch.tensor(lens), graphs, min_active_states=0)
+    assert k2.get_aux_labels(k2.one_best_decoding(lattice)) == texts
