@@ -161,6 +161,44 @@ def linear_fsa(labels: Union[List[int], List[List[int]]],
     return ans
 
 
+def ctc_topo(max_token: int, modified: bool = False,
+             device: Optional[Union[torch.device, str]] = None) -> Fsa:
+    """The CTC topology over tokens 1..max_token with blank 0, as a single Fsa with
+    `aux_labels` (k2/python/k2/fsa_algo.py ctc_topo over k2::CtcTopo,
+    k2/csrc/fsa_algo.cu:732-817): all scores 0, the output symbol is emitted when a
+    token is entered.
+
+    Standard: states 0..max_token (state i = "last symbol was i", 0 for blank) plus the
+    final state; from every state an arc to every state j with label j (-1 into the
+    final state) and aux label 0 on self-loops, else j.
+    Modified: state 0 has a self-loop for every symbol and an arc to every token
+    state; a token state has its self-loop and an arc back to state 0, both with
+    aux label 0."""
+    states = max_token + 2
+    if modified:
+        n0 = states - 1
+        src = np.concatenate([np.zeros(2 * n0, np.int64), np.repeat(np.arange(1, states - 1), 2)])
+        dest0 = np.arange(1, states)
+        dest = np.concatenate([np.zeros(n0, np.int64), dest0,
+                               np.stack([np.arange(1, states - 1),
+                                         np.zeros(states - 2, np.int64)], 1).reshape(-1)])
+        lab0 = np.where(dest0 == states - 1, -1, dest0)
+        label = np.concatenate([np.arange(n0), lab0, np.repeat(np.arange(1, states - 1), 2)])
+        aux = np.concatenate([np.arange(n0), lab0, np.zeros(2 * (states - 2), np.int64)])
+    else:
+        i, j = np.meshgrid(np.arange(states - 1), np.arange(states), indexing="ij")
+        src, dest = i.reshape(-1), j.reshape(-1)
+        label = np.where(dest == states - 1, -1, dest)
+        aux = np.where(src == dest, 0, label)
+    rows = np.stack([src, dest, label, np.zeros_like(src)], 1)
+    rs2 = np.zeros(states + 1, np.int64)
+    np.add.at(rs2, src + 1, 1)
+    ans = _fsa_vec_from_numpy(np.asarray([0, states]), np.cumsum(rs2), rows, device or "cpu",
+                              aux_labels=aux)
+    ans.arcs.single = True
+    return ans
+
+
 def arc_sort(fsa: Fsa, ret_arc_map: bool = False):
     """Sort the arcs leaving each state by (label as uint32, dest_state)
     (k2/csrc/fsa.h:54-62, k2/csrc/fsa_algo.cu:852-867).  Graph preparation: runs

@@ -52,6 +52,8 @@ def lib():
                                        _i32p, _i32p, _i32p]
         L.kref_ctc_graphs.restype = ctypes.c_void_p
         L.kref_ctc_graphs.argtypes = [_i32p, ctypes.c_int32, _i32p, ctypes.c_int32]
+        L.kref_ctc_topo.restype = ctypes.c_void_p
+        L.kref_ctc_topo.argtypes = [ctypes.c_int32, ctypes.c_int32]
         L.kref_arc_sort.restype = ctypes.c_void_p
         L.kref_arc_sort.argtypes = [ctypes.c_void_p, _i32p]
         L.kref_intersect_dense.restype = ctypes.c_void_p
@@ -134,6 +136,10 @@ def ctc_graphs(symbols, modified=False) -> HostFsaVec:
     h = _Handle(lib().kref_ctc_graphs(_p(rs, _i32p), len(symbols), _p(vals, _i32p),
                                       int(modified)))
     return h.to_host(aux=True)
+
+
+def ctc_topo(max_token: int, modified=False) -> HostFsaVec:
+    return _Handle(lib().kref_ctc_topo(int(max_token), int(modified))).to_host(aux=True)
 
 
 def arc_sort(f: HostFsaVec):

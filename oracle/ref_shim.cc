@@ -191,6 +191,16 @@ void *kref_ctc_graphs(const int32_t *sym_row_splits, int32_t num_seqs,
   KREF_CATCH(nullptr)
 }
 
+// k2::CtcTopo (k2/csrc/fsa_algo.cu:732-817) as an FsaVec of one FSA, with aux labels.
+void *kref_ctc_topo(int32_t max_token, int32_t modified) {
+  KREF_TRY
+  auto *h = new FsaVecHandle;
+  k2::Fsa topo = k2::CtcTopo(k2::GetCpuContext(), max_token, modified != 0, &h->aux);
+  h->fsas = k2::FsaToFsaVec(topo);
+  return h;
+  KREF_CATCH(nullptr)
+}
+
 void *kref_arc_sort(void *handle, int32_t *arc_map /* [num_arcs] or NULL */) {
   KREF_TRY
   auto *h = reinterpret_cast<FsaVecHandle *>(handle);

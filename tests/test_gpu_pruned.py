@@ -207,3 +207,27 @@ def test_decode_helpers_recover_the_transcripts(k2):
     graphs.aux_labels = k2.RaggedTensor([[x] if x != 0 else [] for x in aux], device=DEV)
     lattice = k2.get_lattice(log_prob, torch.tensor(lens), graphs, min_active_states=0)
     assert k2.get_aux_labels(k2.one_best_decoding(lattice)) == texts
+
+
+def test_ctc_decoding_with_the_shared_topology(k2):
+    """get_lattice with H = ctc_topo shared by the batch: greedy-like CTC decoding of
+    peaked log-probs gives back the symbol sequences."""
+    from gpu_util import DEV
+    rng = np.random.default_rng(6)
+    C = 12
+    texts = [[int(x) for x in rng.integers(1, C, size=int(rng.integers(1, 8)))] for _ in range(5)]
+    T = 30
+    logits = torch.full((len(texts), T, C), -5.0)
+    for i, text in enumerate(texts):
+        t = 0
+        for sym in text:
+            logits[i, t, 0] = 5.0
+            logits[i, t + 1, sym] = 5.0
+            t += 2
+        logits[i, t:, 0] = 5.0
+    log_prob = torch.log_softmax(logits, -1).to(DEV)
+    lens = torch.full((len(texts),), T)
+    for modified in (False, True):
+        H = k2.ctc_topo(C - 1, modified=modified, device=DEV)
+        lattice = k2.get_lattice(log_prob, lens, H, min_active_states=0)
+        assert k2.get_aux_labels(k2.one_best_decoding(lattice)) == texts

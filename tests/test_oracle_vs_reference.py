@@ -117,3 +117,15 @@ def test_pruned_intersection_with_wide_beams_is_the_exact_lattice_best_path():
         tp = ref.tot_scores_and_arc_post(pruned, ref.forward_scores(pruned, False, True),
                                          ref.backward_scores(pruned, False, True), True)[0]
         np.testing.assert_allclose(te, tp, rtol=1e-6)
+
+
+def test_ctc_topo_is_the_reference_topology():
+    """k2_b200.ctc_topo (host-built graph) against k2::CtcTopo, arc for arc."""
+    import k2_b200 as k2
+    for max_token in (1, 2, 7, 30):
+        for modified in (False, True):
+            want = ref.ctc_topo(max_token, modified)
+            got = k2.ctc_topo(max_token, modified)
+            assert np.array_equal(got.arcs._row_splits2.numpy(), want.row_splits2)
+            assert np.array_equal(got.arcs.values().numpy(), want.arcs)
+            assert np.array_equal(got.aux_labels.numpy(), want.aux_labels)
