@@ -4,6 +4,10 @@
  * dense-intersection / total-score hot path.  It is the checker the CUDA path is
  * compared with in tests, in the smoke test and as the "port" CPU baseline.
  *
+ * Restated: CtcGraphs, IntersectDense, IntersectDensePruned (batch mode), forward and
+ * backward scores in both semirings, total scores, arc posteriors, ShortestPath, the
+ * basic properties.
+ *
  * Parity of this restatement is PINNED: tests/test_oracle_vs_reference.py
  * compares every function here with the reference's own CPU code (compiled by
  * oracle/Makefile into oracle/_ref/libk2ref.so) on seeded random inputs, and
@@ -347,6 +351,284 @@ K2oFsaVec *k2o_intersect_dense(const int32_t *a_rs1, int32_t num_fsas,
   out->num_arcs = na_out;
   for (int32_t i = 0; i < num_fsas; ++i) { free(fwd[i]); free(bwd[i]); }
   free(fwd); free(bwd); free(cutoff);
+  return out;
+}
+
+/* ------------------------------------------------------------------------
+ * IntersectDensePruned, batch mode: k2/csrc/intersect_dense_pruned.cu:41-1694 as its
+ * CPU build runs it, one sequence at a time (beam, cutoffs, state numbering and
+ * pruning windows are all per sequence).  Frames hold their states and arcs in
+ * growable arrays; the windows compact them in place.
+ * ---------------------------------------------------------------------- */
+typedef struct {
+  int32_t ns, na;     /* states and arcs of the frame */
+  int32_t *astate;    /* [ns] state in the graph (idx01) */
+  float *fwd, *bwd;   /* [ns] */
+  int32_t *arc0;      /* [ns+1] first arc of every state */
+  int32_t *aidx;      /* [na] arc in the graph (idx012) */
+  float *ll;          /* [na] arc.score + dense score */
+  int32_t *dest;      /* [na] state of the next frame, -1 if it was pruned */
+} PFrame;
+
+static void pframe_free(PFrame *f) {
+  free(f->astate); free(f->fwd); free(f->bwd); free(f->arc0); free(f->aidx); free(f->ll);
+  free(f->dest);
+  memset(f, 0, sizeof(*f));
+}
+
+/* GetPruningCutoffs, :687-767: the mixed float / double arithmetic is the reference's. */
+static float next_beam(float dyn, float best, int32_t active, int32_t t, int32_t final_t,
+                       float default_beam, float min_active, float max_active,
+                       float *cutoff) {
+  float cur_min = min_active;
+  if (t + 5 >= final_t) cur_min = fmaxf(min_active, max_active / 2);
+  if (active <= max_active) {
+    if (active >= cur_min || active == 0) {
+      dyn = 0.8 * dyn + 0.2 * default_beam;
+    } else {
+      if (dyn < default_beam) dyn = default_beam;
+      dyn *= 1.25;
+    }
+  } else if (t + 5 < final_t) {
+    if (dyn > default_beam) dyn = default_beam;
+    dyn *= 0.8;
+  }
+  if (t == final_t - 1) dyn = 1.0e+10;
+  *cutoff = best - dyn;
+  return dyn;
+}
+
+/* PruneTimeRange, :1373-1634 (SetBackwardProbsFinal :1170-1193, PropagateBackward
+ * :1239-1346), frames [begin, end) of one sequence. */
+static void prune_window(PFrame *fr, int32_t begin, int32_t end, int32_t g_final,
+                         float output_beam) {
+  PFrame *last = &fr[end];
+  for (int32_t k = 0; k < last->ns; ++k) {
+    float f = last->fwd[k];
+    last->bwd[k] = (f - f == 0) ? -f : -INFINITY;
+  }
+  int32_t *new_next = NULL; /* new numbers of the states of frame t + 1 */
+  for (int32_t t = end - 1; t >= begin; --t) {
+    PFrame *c = &fr[t], *n = &fr[t + 1];
+    int32_t *new_cur = (int32_t *)malloc(4 * (c->ns + 1));
+    uint8_t *keep_arc = (uint8_t *)malloc(c->na + 1);
+    int32_t kept_states = 0;
+    for (int32_t k = 0; k < c->ns; ++k) {
+      float best = -INFINITY;
+      for (int32_t p = c->arc0[k]; p < c->arc0[k + 1]; ++p) {
+        keep_arc[p] = 0;
+        if (c->dest[p] < 0) continue;
+        /* frame t + 1 has been compacted already: find the state under its new number
+         * (a state that was dropped there had a backward score of -inf) */
+        int32_t d = new_next ? new_next[c->dest[p]] : c->dest[p];
+        if (d < 0) continue;
+        float bl = c->ll[p] + n->bwd[d];
+        if (bl + c->fwd[k] >= -output_beam) {
+          keep_arc[p] = 1;
+          if (bl > best) best = bl;
+        }
+      }
+      c->bwd[k] = (c->astate[k] == g_final) ? -c->fwd[k] : best;
+      int32_t keep = (c->bwd[k] != -INFINITY) || t == begin;
+      new_cur[k] = keep ? kept_states++ : -1;
+    }
+    /* compaction of frame t: arcs first (their dest moves to the new numbering of
+     * frame t + 1, which was fixed in the previous iteration), then states */
+    int32_t wa = 0, ws = 0;
+    for (int32_t k = 0; k < c->ns; ++k) {
+      int32_t first = wa;
+      for (int32_t p = c->arc0[k]; p < c->arc0[k + 1]; ++p) {
+        if (!keep_arc[p]) continue;
+        c->aidx[wa] = c->aidx[p];
+        c->ll[wa] = c->ll[p];
+        c->dest[wa] = new_next ? new_next[c->dest[p]] : c->dest[p];
+        ++wa;
+      }
+      if (new_cur[k] >= 0) {
+        c->astate[ws] = c->astate[k];
+        c->fwd[ws] = c->fwd[k];
+        c->bwd[ws] = c->bwd[k];
+        c->arc0[ws] = first;
+        ++ws;
+      }
+    }
+    c->arc0[ws] = wa;
+    c->ns = ws;
+    c->na = wa;
+    free(keep_arc);
+    free(new_next);
+    new_next = new_cur;
+  }
+  free(new_next);
+}
+
+K2oFsaVec *k2o_intersect_dense_pruned(const int32_t *a_rs1, int32_t a_num_fsas,
+                                      const int32_t *a_rs2, const void *a_arcs_v,
+                                      const float *scores, int32_t rows, int32_t cols,
+                                      const int32_t *b_rs, int32_t num_seqs, float search_beam,
+                                      float output_beam, int32_t min_active,
+                                      int32_t max_active, int32_t allow_partial) {
+  const Arc *a_arcs = (const Arc *)a_arcs_v;
+  if (!(search_beam > 0) || !(output_beam > 0)) { g_err = "beams must be > 0"; return NULL; }
+  if (min_active < 0 || max_active <= min_active) { g_err = "bad active limits"; return NULL; }
+  if (a_num_fsas != num_seqs && a_num_fsas != 1) { g_err = "a_fsas.Dim0() mismatch"; return NULL; }
+  int32_t T = 0;
+  for (int32_t i = 0; i < num_seqs; ++i)
+    if (b_rs[i + 1] - b_rs[i] > T) T = b_rs[i + 1] - b_rs[i];
+
+  K2oFsaVec *out = (K2oFsaVec *)calloc(1, sizeof(K2oFsaVec));
+  out->num_fsas = num_seqs;
+  out->row_splits1 = (int32_t *)calloc(num_seqs + 1, 4);
+  int64_t cap_s = 1024, cap_a = 1024, tot_s = 0, tot_a = 0;
+  out->row_splits2 = (int32_t *)malloc(4 * (cap_s + 1));
+  out->arcs = (Arc *)malloc(sizeof(Arc) * cap_a);
+  out->arc_map_a = (int32_t *)malloc(4 * cap_a);
+  out->arc_map_b = (int32_t *)malloc(4 * cap_a);
+
+  for (int32_t i = 0; i < num_seqs; ++i) {
+    const int32_t gi = a_num_fsas == 1 ? 0 : i, g_start = a_rs1[gi],
+                  g_states = a_rs1[gi + 1] - g_start, g_final = a_rs1[gi + 1] - 1;
+    const int32_t row0 = b_rs[i], final_t = b_rs[i + 1] - row0;
+    PFrame *fr = (PFrame *)calloc(T + 2, sizeof(PFrame));
+    int32_t *slot = (int32_t *)malloc(4 * (g_states + 1)); /* graph state -> next-frame state */
+    for (int32_t s = 0; s < g_states; ++s) slot[s] = -1;
+    /* frame 0: InitialFrameInfo, :435-472 */
+    fr[0].ns = g_states > 0;
+    fr[0].astate = (int32_t *)malloc(4 * 2);
+    fr[0].fwd = (float *)malloc(4 * 2);
+    fr[0].bwd = (float *)malloc(4 * 2);
+    fr[0].astate[0] = g_start;
+    fr[0].fwd[0] = 0;
+    float beam = search_beam;
+    int32_t next_end = 20; /* :164-199: windows of 30 frames every 20 */
+    for (int32_t t = 0; t < T; ++t) {
+      PFrame *c = &fr[t], *n = &fr[t + 1];
+      /* GetArcs, :778-908 */
+      c->arc0 = (int32_t *)malloc(4 * (c->ns + 1));
+      int32_t na = 0;
+      for (int32_t k = 0; k < c->ns; ++k) {
+        c->arc0[k] = na;
+        na += a_rs2[c->astate[k] + 1] - a_rs2[c->astate[k]];
+      }
+      c->arc0[c->ns] = na;
+      c->na = na;
+      c->aidx = (int32_t *)malloc(4 * (na + 1));
+      c->ll = (float *)malloc(4 * (na + 1));
+      c->dest = (int32_t *)malloc(4 * (na + 1));
+      float *end = (float *)malloc(4 * (na + 1));
+      int32_t redirect = 0;
+      if (allow_partial && t == final_t - 1) {
+        redirect = 1;
+        for (int32_t k = 0; k < c->ns; ++k)
+          for (int32_t a = a_rs2[c->astate[k]]; a < a_rs2[c->astate[k] + 1]; ++a)
+            if (a_arcs[a].label == -1) redirect = 0;
+      }
+      float best = -INFINITY;
+      for (int32_t k = 0; k < c->ns; ++k) {
+        int32_t p = c->arc0[k];
+        for (int32_t a = a_rs2[c->astate[k]]; a < a_rs2[c->astate[k] + 1]; ++a, ++p) {
+          float acoustic = row0 + t < rows
+                               ? dense_score(scores, (int64_t)row0 + t, cols, a_arcs[a].label)
+                               : -INFINITY;
+          int32_t dest = c->astate[k] + a_arcs[a].dest - a_arcs[a].src;
+          if (redirect) {
+            dest = g_final;
+            acoustic = 0;
+          }
+          c->aidx[p] = a;
+          c->ll[p] = acoustic + a_arcs[a].score;
+          c->dest[p] = dest;
+          end[p] = c->fwd[k] + c->ll[p];
+          if (end[p] > best) best = end[p];
+        }
+      }
+      /* PropagateForward, :925-1153: the first arc above the cutoff creates a state */
+      float cutoff;
+      beam = next_beam(beam, best, c->ns, t, final_t, search_beam, (float)min_active,
+                       (float)max_active, &cutoff);
+      n->astate = (int32_t *)malloc(4 * (na + 2));
+      n->fwd = (float *)malloc(4 * (na + 2));
+      n->bwd = (float *)malloc(4 * (na + 2));
+      int32_t nn = 0;
+      for (int32_t p = 0; p < na; ++p) {
+        int32_t d = c->dest[p] - g_start;
+        if (end[p] > cutoff && slot[d] < 0) {
+          slot[d] = nn;
+          n->astate[nn] = c->dest[p];
+          n->fwd[nn] = -INFINITY;
+          ++nn;
+        }
+      }
+      for (int32_t p = 0; p < na; ++p) {
+        int32_t j = slot[c->dest[p] - g_start];
+        c->dest[p] = j;
+        if (j >= 0 && end[p] > n->fwd[j]) n->fwd[j] = end[p];
+      }
+      for (int32_t j = 0; j < nn; ++j) slot[n->astate[j] - g_start] = -1;
+      n->ns = nn;
+      free(end);
+      int32_t this_end = next_end >= T ? T : next_end;
+      if (t == this_end - 1) {
+        int32_t begin = next_end - 30 > 0 ? next_end - 30 : 0;
+        prune_window(fr, begin, this_end, g_final, output_beam);
+        next_end += 20;
+      }
+    }
+    fr[T].arc0 = (int32_t *)calloc(fr[T].ns + 1, 4); /* the last frame has no arcs */
+    /* FormatOutput, :474-657 */
+    int32_t seq_states = 0;
+    for (int32_t t = 0; t <= T; ++t) seq_states += fr[t].ns;
+    int32_t extra = (g_states > 0) && fr[final_t].ns == 0; /* :519-547 */
+    int32_t state_base = 0;
+    for (int32_t t = 0; t <= T; ++t) {
+      PFrame *c = &fr[t];
+      for (int32_t k = 0; k < c->ns; ++k) {
+        if (tot_s + 2 > cap_s) {
+          cap_s *= 2;
+          out->row_splits2 = (int32_t *)realloc(out->row_splits2, 4 * (cap_s + 1));
+        }
+        out->row_splits2[tot_s++] = (int32_t)tot_a;
+        for (int32_t p = c->arc0[k]; p < c->arc0[k + 1]; ++p) {
+          if (tot_a + 1 > cap_a) {
+            cap_a *= 2;
+            out->arcs = (Arc *)realloc(out->arcs, sizeof(Arc) * cap_a);
+            out->arc_map_a = (int32_t *)realloc(out->arc_map_a, 4 * cap_a);
+            out->arc_map_b = (int32_t *)realloc(out->arc_map_b, 4 * cap_a);
+          }
+          int32_t label = a_arcs[c->aidx[p]].label, map_a = c->aidx[p];
+          Arc arc;
+          arc.src = state_base + k;
+          arc.dest = state_base + c->ns + c->dest[p];
+          arc.label = label;
+          arc.score = c->ll[p];
+          if (t == final_t - 1 && label != -1) { /* allow_partial, :625-634 */
+            arc.label = -1;
+            map_a = -1;
+          }
+          out->arcs[tot_a] = arc;
+          out->arc_map_a[tot_a] = map_a;
+          out->arc_map_b[tot_a] = (row0 + t) * cols + label + 1;
+          ++tot_a;
+        }
+      }
+      state_base += c->ns;
+    }
+    if (extra) {
+      if (tot_s + 2 > cap_s) {
+        cap_s *= 2;
+        out->row_splits2 = (int32_t *)realloc(out->row_splits2, 4 * (cap_s + 1));
+      }
+      out->row_splits2[tot_s++] = (int32_t)tot_a;
+    }
+    (void)seq_states;
+    out->row_splits1[i + 1] = (int32_t)tot_s;
+    for (int32_t t = 0; t <= T + 1; ++t) pframe_free(&fr[t]);
+    free(fr);
+    free(slot);
+  }
+  out->row_splits2[tot_s] = (int32_t)tot_a;
+  out->num_states = (int32_t)tot_s;
+  out->num_arcs = (int32_t)tot_a;
   return out;
 }
 

@@ -56,6 +56,10 @@ def lib():
         L.k2o_intersect_dense.restype = _vp
         L.k2o_intersect_dense.argtypes = [_i32p, _i32, _i32p, _vp, _f32p, _i32, _i32, _i32p,
                                           _i32, _i32p, ctypes.c_float, _i32, _i32]
+        L.k2o_intersect_dense_pruned.restype = _vp
+        L.k2o_intersect_dense_pruned.argtypes = [
+            _i32p, _i32, _i32p, _vp, _f32p, _i32, _i32, _i32p, _i32, ctypes.c_float,
+            ctypes.c_float, _i32, _i32, _i32]
         L.k2o_forward_scores.argtypes = [_i32p, _i32, _i32p, _vp, _i32, _i32, _f64p, _i32p]
         L.k2o_backward_scores.argtypes = [_i32p, _i32, _i32p, _vp, _i32, _i32, _f64p]
         L.k2o_tot_scores_and_arc_post.argtypes = [_i32p, _i32, _i32p, _vp, _i32, _f64p, _f64p,
@@ -117,6 +121,20 @@ def intersect_dense(a: HostFsaVec, scores: np.ndarray, b_row_splits: np.ndarray,
         _p(rs1, _i32p), len(rs1) - 1, _p(rs2, _i32p), arcs.ctypes.data_as(_vp),
         _p(scores, _f32p), scores.shape[0], scores.shape[1], _p(brs, _i32p), len(brs) - 1,
         _p(m, _i32p), float(output_beam), int(max_states), int(max_arcs)), maps=True)
+
+
+def intersect_dense_pruned(a: HostFsaVec, scores: np.ndarray, b_row_splits: np.ndarray,
+                           search_beam: float, output_beam: float, min_active: int,
+                           max_active: int, allow_partial: bool = False) -> HostFsaVec:
+    """`a` holds one graph per sequence or a single graph shared by all."""
+    rs1, rs2, arcs = _fsa_args(a)
+    scores = np.ascontiguousarray(scores, np.float32)
+    brs = np.ascontiguousarray(b_row_splits, np.int32)
+    return _take(lib().k2o_intersect_dense_pruned(
+        _p(rs1, _i32p), len(rs1) - 1, _p(rs2, _i32p), arcs.ctypes.data_as(_vp),
+        _p(scores, _f32p), scores.shape[0], scores.shape[1], _p(brs, _i32p), len(brs) - 1,
+        float(search_beam), float(output_beam), int(min_active), int(max_active),
+        int(bool(allow_partial))), maps=True)
 
 
 def forward_scores(f: HostFsaVec, log_semiring=True, use_double=True,

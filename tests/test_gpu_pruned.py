@@ -1,15 +1,16 @@
-"""Pruned intersection (k2.intersect_dense_pruned) on the GPU against the reference's
-own CPU code: bit-identical lattices and arc maps.  The small cases are checked
-against committed answers (tests/golden/pruned_cases.npz, made by
-tests/golden/make_pruned_golden.py); the larger ones against the reference library
-itself when it has been built (oracle/_ref)."""
+"""Pruned intersection (k2.intersect_dense_pruned) on the GPU: bit-identical lattices
+and arc maps.  The small cases are checked against the reference's own answers
+(tests/golden/pruned_cases.npz, made by tests/golden/make_pruned_golden.py); the
+larger ones against the C restatement in oracle/ (itself pinned against the
+reference on CPU, tests/test_oracle_vs_reference.py) and, when it has been built,
+against the reference library too (oracle/_ref)."""
 import os
 
 import numpy as np
 import pytest
 import torch
 
-from oracle import ref
+from oracle import oracle, ref
 from oracle.common import HostFsaVec
 from pruned_util import decoding_graph, pruned_cases
 from util import random_dense, same_fsa
@@ -49,22 +50,23 @@ def test_small_cases_match_the_committed_reference_answers(k2):
             same_fsa(got, want, f"{name}, {team} CTAs per sequence")
 
 
-@pytest.mark.skipif(not ref.available(), reason="oracle/_ref/libk2ref.so not built")
-def test_larger_cases_match_the_reference_library(k2):
+def test_larger_cases_match_the_oracle_and_the_reference_library(k2):
     for c in pruned_cases(small=False):
-        want = ref.intersect_dense_pruned(c["a"], c["scores"], c["brs"], *c["params"])
+        want = oracle.intersect_dense_pruned(c["a"], c["scores"], c["brs"], *c["params"])
         _, got = run_gpu(k2, c)
         same_fsa(got, want, c["name"])
+        if ref.available():
+            same_fsa(got, ref.intersect_dense_pruned(c["a"], c["scores"], c["brs"],
+                                                     *c["params"]), c["name"] + " (reference)")
 
 
-@pytest.mark.skipif(not ref.available(), reason="oracle/_ref/libk2ref.so not built")
 def test_decoding_graph_many_windows(k2):
     rng = np.random.default_rng(5)
     g = decoding_graph(rng, 3000, 40, mean_degree=4.0)
     scores, brs = random_dense(rng, 6, 300, 40, scale=2.0, low_rows=False)
     for params in ((12.0, 5.0, 30, 400, False), (8.0, 4.0, 10, 60, True)):
         c = dict(a=g, scores=scores, brs=brs, params=params)
-        want = ref.intersect_dense_pruned(g, scores, brs, *params)
+        want = oracle.intersect_dense_pruned(g, scores, brs, *params)
         for team in (1, 4):
             lat, got = run_gpu(k2, c, team)
             same_fsa(got, want, f"{params}, {team} CTAs per sequence")
@@ -160,11 +162,9 @@ def test_best_path_agrees_with_the_exact_intersection_on_a_decoding_graph(k2):
     assert (tn <= te + 1e-4).all()
 
 
-@pytest.mark.skipif(not ref.available(), reason="oracle/_ref/libk2ref.so not built")
 def test_many_sequences_with_their_own_graphs(k2):
     """More sequences than SMs (one CTA per sequence), one CTC graph each, lengths from
     1 frame to several pruning windows."""
-    from oracle import oracle
     rng = np.random.default_rng(9)
     n = 200
     syms = [[int(x) for x in rng.integers(1, 9, size=int(rng.integers(1, 12)))] for _ in range(n)]
@@ -172,7 +172,7 @@ def test_many_sequences_with_their_own_graphs(k2):
     assert np.diff(brs).min() == 2  # a sequence of a single frame
     g = oracle.ctc_graphs(syms, False)
     for params in ((20.0, 8.0, 0, 1000, False), (5.0, 3.0, 4, 12, True)):
-        want = ref.intersect_dense_pruned(g, scores, brs, *params)
+        want = oracle.intersect_dense_pruned(g, scores, brs, *params)
         _, got = run_gpu(k2, dict(a=g, scores=scores, brs=brs, params=params))
         same_fsa(got, want, str(params))
 

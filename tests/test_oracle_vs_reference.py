@@ -129,3 +129,26 @@ def test_ctc_topo_is_the_reference_topology():
             assert np.array_equal(got.arcs._row_splits2.numpy(), want.row_splits2)
             assert np.array_equal(got.arcs.values().numpy(), want.arcs)
             assert np.array_equal(got.aux_labels.numpy(), want.aux_labels)
+
+
+def test_pruned_intersection_restatement_is_identical():
+    """oracle.intersect_dense_pruned (plain C) against the reference's
+    IntersectDensePruned: lattices and arc maps bit for bit, over per-sequence and
+    shared graphs, beams that bind and beams that do not, allow_partial."""
+    from pruned_util import decoding_graph, pruned_cases
+    cases = pruned_cases(small=True) + pruned_cases(small=False)
+    rng = np.random.default_rng(33)
+    for trial in range(40):
+        n = int(rng.integers(1, 6))
+        if trial % 3 == 0:
+            a = decoding_graph(rng, int(rng.integers(5, 80)), 5)
+        else:
+            a = random_fsa_vec(rng, n, max_states=14, max_arcs=60, max_label=4, allow_empty=True)
+        scores, brs = random_dense(rng, n, int(rng.integers(1, 75)), 5, low_rows=trial % 2 == 0)
+        params = (float(rng.choice([2.0, 6.0, 20.0])), float(rng.choice([1.0, 4.0, 8.0])),
+                  int(rng.integers(0, 4)), int(rng.integers(4, 40)), bool(trial % 4 == 1))
+        cases.append(dict(name=f"trial{trial}", a=a, scores=scores, brs=brs, params=params))
+    for c in cases:
+        r = ref.intersect_dense_pruned(c["a"], c["scores"], c["brs"], *c["params"])
+        o = oracle.intersect_dense_pruned(c["a"], c["scores"], c["brs"], *c["params"])
+        same_fsa(r, o, c["name"])
