@@ -347,6 +347,17 @@ int32_t k2b200_dense_loss_backward(const k2b200_intersect_args *args, void *work
                                    size_t workspace_bytes, const double *tot_grad,
                                    int32_t tot_grad_stride, float *grad_a, float *grad_b,
                                    void *stream);
+/* The same, with dL/d(scores) written straight into the layout of the log-probs the
+ * DenseFsaVec was made from (k2/python/k2/dense_fsa_vec.py:43-145), which saves the
+ * pass that the adjoint of that layout would otherwise make over both matrices:
+ * grad_log_probs is [.., num_classes] (zero-filled, num_classes = cols - 1) and
+ * log_prob_row[i] (device, one per graph) is the row of it that holds frame 0 of
+ * graph i's sequence, i.e. segment_index * frames_per_sequence + segment_start. */
+int32_t k2b200_dense_loss_backward_log_probs(const k2b200_intersect_args *args, void *workspace,
+                                             size_t workspace_bytes, const double *tot_grad,
+                                             int32_t tot_grad_stride, float *grad_a,
+                                             float *grad_log_probs, const int32_t *log_prob_row,
+                                             int32_t num_classes, void *stream);
 
 /* ---------------------------------------------------------------------------
  * Forward / backward scores of a layered (top-sorted, acyclic) FsaVec.

@@ -84,6 +84,8 @@ _sig("k2b200_profile_enable", None, [c_i32])
 _sig("k2b200_profile_read_ms", ctypes.c_double, [c_i32, ctypes.POINTER(c_i64)])
 _sig("k2b200_row_splits_to_row_ids", c_i32, [c_vp, c_i32, c_vp, c_i32, c_vp])
 _sig("k2b200_upload_i32", c_i32, [c_vp, c_i64, c_vp, c_vp])
+_sig("k2b200_dense_loss_backward_log_probs", c_i32,
+     [ctypes.POINTER(IntersectArgs), c_vp, c_sz, c_vp, c_i32, c_vp, c_vp, c_vp, c_i32, c_vp])
 _sig("k2b200_fsa_scores_backprop", c_i32,
      [ctypes.POINTER(FsaView), c_i32, c_i32, c_i32, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp])
 _sig("k2b200_fsa_arc_post_backprop", c_i32,
@@ -172,6 +174,7 @@ EXPORTED = [
     "k2b200_intersect_dense_pruned_workspace_bytes", "k2b200_intersect_dense_pruned_search",
     "k2b200_intersect_dense_pruned_emit",
     "k2b200_fsa_scores_backprop", "k2b200_fsa_arc_post_backprop",
+    "k2b200_dense_loss_backward_log_probs",
 ]
 
 

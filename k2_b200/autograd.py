@@ -536,6 +536,16 @@ class _DenseTotScoresFunction(torch.autograd.Function):
         ctx.dev = dev
         ctx.shape_a = unused_scores_a.shape
         ctx.shape_b = unused_scores_b.shape
+        # when the last argument is the log-prob tensor the DenseFsaVec was made from
+        # (not its score matrix), the backward writes the gradient in that layout
+        ctx.lp_row = None
+        src = b_fsas._source
+        if src is not None and unused_scores_b is src[0]:
+            key = None if a_to_b_map is None else tuple(keep[2].tolist())
+            if key not in b_fsas._source_rows:
+                rows = src[1] if key is None else src[1][keep[2]]
+                b_fsas._source_rows[key] = _lib.upload_i32(rows, dev)
+            ctx.lp_row = b_fsas._source_rows[key]
         ctx.output_beam_used = beam.value
         return tot if use_double_scores else tot.to(torch.float32)
 
@@ -548,9 +558,15 @@ class _DenseTotScoresFunction(torch.autograd.Function):
         grad_a = torch.zeros(ctx.shape_a, dtype=torch.float32, device=dev)
         grad_b = torch.zeros(ctx.shape_b, dtype=torch.float32, device=dev)
         with torch.cuda.device(dev):
-            _lib.check(_lib.lib.k2b200_dense_loss_backward(
-                ctypes.byref(ctx.args), _lib.ptr(ctx.ws), ctx.ws_bytes, _lib.ptr(tot_grad),
-                stride, _lib.ptr(grad_a), _lib.ptr(grad_b), _lib.stream_of(dev)))
+            if ctx.lp_row is None:
+                _lib.check(_lib.lib.k2b200_dense_loss_backward(
+                    ctypes.byref(ctx.args), _lib.ptr(ctx.ws), ctx.ws_bytes, _lib.ptr(tot_grad),
+                    stride, _lib.ptr(grad_a), _lib.ptr(grad_b), _lib.stream_of(dev)))
+            else:
+                _lib.check(_lib.lib.k2b200_dense_loss_backward_log_probs(
+                    ctypes.byref(ctx.args), _lib.ptr(ctx.ws), ctx.ws_bytes, _lib.ptr(tot_grad),
+                    stride, _lib.ptr(grad_a), _lib.ptr(grad_b), _lib.ptr(ctx.lp_row),
+                    ctx.shape_b[-1], _lib.stream_of(dev)))
         return None, None, None, None, None, None, None, grad_a, grad_b
 
 
@@ -573,7 +589,13 @@ def intersect_dense_tot_scores(a_fsas: Fsa, b_fsas: DenseFsaVec, output_beam: fl
     """`intersect_dense(a_fsas, b_fsas, output_beam, ...).get_tot_scores(
     log_semiring=True, use_double_scores=...)` in one step (the composition
     k2/python/k2/ctc_loss.py:86-140 makes), differentiable w.r.t. `a_fsas.scores`
-    and `b_fsas.scores`.  The lattice is not built."""
+    and `b_fsas.scores`.  The lattice is not built.  When `b_fsas` was made from a
+    log-prob tensor that takes part in autograd, the gradient goes to that tensor
+    directly rather than through the score matrix and the adjoint of its layout."""
+    scores_b = b_fsas.scores
+    src = b_fsas._source
+    if src is not None and src[0].requires_grad and src[0].dtype == torch.float32:
+        scores_b = src[0]
     return _DenseTotScoresFunction.apply(a_fsas, b_fsas, output_beam, max_states, max_arcs,
                                          use_double_scores, a_to_b_map, a_fsas.scores,
-                                         b_fsas.scores)
+                                         scores_b)

@@ -721,6 +721,42 @@ GridChainMasked(const FsaInfo *__restrict__ infos, int32_t n, int64_t total_leve
     tot[i] = last == 0.0 ? -INFINITY : log(last) + (double)K * 0.69314718055994530942;
 }
 
+// Writes the fixed-point sums gb[frame][col] of a CTA's frames (2^-31 units, times tg)
+// as dL/d(dense score): into the score matrix layout grad[(row0 + u0 + frame) * cols +
+// col], or - when lp_row0 >= 0 - straight into the layout of the log-probs the
+// DenseFsaVec was made from, grad[(lp_row0 + u0 + frame) * lp_cols + col - 1]: column 0
+// (the final-arc column) has no log-prob behind it and is dropped, as the adjoint of
+// the DenseFsaVec layout drops it.
+__device__ __forceinline__ void StoreDenseGrad(float *__restrict__ grad, int32_t row0, int32_t u0,
+                                               int32_t cols, const uint32_t *gb, int32_t elems,
+                                               float tg, int32_t exclusive_rows,
+                                               int32_t lp_row0, int32_t lp_cols, int32_t tid,
+                                               int32_t nt) {
+  if (lp_row0 < 0) {
+    float *grow = grad + ((int64_t)row0 + u0) * cols;
+    for (int32_t k = tid; k < elems; k += nt) {
+      const uint32_t fixed = gb[k];
+      if (fixed != 0u) {
+        const float v = tg * ((float)fixed * (1.0f / 2147483648.0f));
+        if (exclusive_rows) grow[k] = v; else atomicAdd(&grow[k], v);
+      }
+    }
+    return;
+  }
+  float *base = grad + ((int64_t)lp_row0 + u0) * lp_cols;
+  for (int32_t k = tid; k < elems; k += nt) {
+    const uint32_t fixed = gb[k];
+    if (fixed != 0u) {
+      const int32_t fl = k / cols, c = k - fl * cols;
+      if (c > 0) {
+        const float v = tg * ((float)fixed * (1.0f / 2147483648.0f));
+        float *p = base + (int64_t)fl * lp_cols + (c - 1);
+        if (exclusive_rows) *p = v; else atomicAdd(p, v);
+      }
+    }
+  }
+}
+
 // ---------------------------------------------------------------------------
 // Gradients.  grid = (frame chunks, pairs): frames do not depend on one another,
 // so the GPU is filled with (pair, chunk) CTAs and every warp of a CTA takes whole
@@ -754,7 +790,8 @@ GridGradWarp(const FsaInfo *__restrict__ infos, const Arc *__restrict__ arcs,
              const ProbState *__restrict__ beta, const double *__restrict__ tot_grad,
              int32_t tot_grad_stride, float *__restrict__ grad_a, float *__restrict__ grad_b,
              int32_t frames_per_cta, int32_t lanes_log2, int32_t s_pad, int32_t ga_in_smem,
-             int32_t exclusive_rows, const int32_t *__restrict__ only_noplan) {
+             int32_t exclusive_rows, const int32_t *__restrict__ only_noplan,
+             const int32_t *__restrict__ lp_row, int32_t lp_cols) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   const int32_t i = blockIdx.y;
   if (only_noplan != nullptr && !(only_noplan[i] & 1)) return;  // the lane kernel took it
@@ -876,14 +913,8 @@ GridGradWarp(const FsaInfo *__restrict__ infos, const Arc *__restrict__ arcs,
     }
   }
   __syncthreads();
-  float *grow = grad_b + ((int64_t)f.row0 + u0) * cols;
-  for (int32_t k = tid; k < gb_elems; k += nt) {
-    const uint32_t fixed = gb[k];
-    if (fixed != 0u) {
-      const float v = tg * ((float)fixed * (1.0f / 2147483648.0f));
-      if (exclusive_rows) grow[k] = v; else atomicAdd(&grow[k], v);
-    }
-  }
+  StoreDenseGrad(grad_b, f.row0, u0, cols, gb, gb_elems, tg, exclusive_rows,
+                 lp_row ? lp_row[i] : -1, lp_cols, tid, nt);
   if (ga_in_smem)
     for (int32_t k = tid; k < A; k += nt) {
       const uint32_t fixed = ga[k];
@@ -915,7 +946,7 @@ GridGradItems(const FsaInfo *__restrict__ infos, const Arc *__restrict__ arcs,
               const ProbState *__restrict__ beta, const double *__restrict__ tot_grad,
               int32_t tot_grad_stride, float *__restrict__ grad_a, float *__restrict__ grad_b,
               int32_t frames_per_cta, int32_t lanes_log2, int32_t ga_in_smem,
-              int32_t exclusive_rows) {
+              int32_t exclusive_rows, const int32_t *__restrict__ lp_row, int32_t lp_cols) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   __shared__ int32_t list_count;
   const int32_t i = blockIdx.y;
@@ -1036,14 +1067,8 @@ GridGradItems(const FsaInfo *__restrict__ infos, const Arc *__restrict__ arcs,
     __syncthreads();
     f0 = f1;
   }
-  float *grow = grad_b + ((int64_t)f.row0 + u0) * cols;
-  for (int32_t k = tid; k < nf * cols; k += nt) {
-    const uint32_t fixed = gb[k];
-    if (fixed != 0u) {
-      const float v = tg * ((float)fixed * (1.0f / 2147483648.0f));
-      if (exclusive_rows) grow[k] = v; else atomicAdd(&grow[k], v);
-    }
-  }
+  StoreDenseGrad(grad_b, f.row0, u0, cols, gb, nf * cols, tg, exclusive_rows,
+                 lp_row ? lp_row[i] : -1, lp_cols, tid, nt);
   if (ga_in_smem)
     for (int32_t k = tid; k < A; k += nt) {
       const uint32_t fixed = ga[k];
@@ -1072,7 +1097,7 @@ GridGradLanes(const FsaInfo *__restrict__ infos, int32_t n, const Arc *__restric
               int32_t tot_grad_stride, float *__restrict__ grad_a, float *__restrict__ grad_b,
               const int32_t *__restrict__ plan, const int32_t *__restrict__ unfit,
               int32_t frames_per_cta, int32_t sub_frames, int32_t s_pad,
-              int32_t exclusive_rows) {
+              int32_t exclusive_rows, const int32_t *__restrict__ lp_row, int32_t lp_cols) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   const int32_t i = blockIdx.y;
   if (unfit[i] & 1) return;  // no plan: the warp-per-frame kernel takes this graph
@@ -1218,14 +1243,8 @@ GridGradLanes(const FsaInfo *__restrict__ infos, int32_t n, const Arc *__restric
       }
     }
     __syncthreads();
-    float *grow = grad_b + ((int64_t)f.row0 + u0) * cols;
-    for (int32_t k = tid; k < nf * cols; k += nt) {
-      const uint32_t fixed = gb[k];
-      if (fixed != 0u) {
-        const float v = tg * ((float)fixed * (1.0f / 2147483648.0f));
-        if (exclusive_rows) grow[k] = v; else atomicAdd(&grow[k], v);
-      }
-    }
+    StoreDenseGrad(grad_b, f.row0, u0, cols, gb, nf * cols, tg, exclusive_rows,
+                   lp_row ? lp_row[i] : -1, lp_cols, tid, nt);
   }
   if (s >= 0) {
 #pragma unroll
@@ -1422,6 +1441,9 @@ struct LossLayout {
   DensePack pack;
   size_t off_dense, off_arc_factors, off_alpha, off_beta, off_masks, off_flags, total_bytes;
   bool exclusive_rows;
+  // set by the backward entry point: gradients go straight to the log-prob layout
+  const int32_t *lp_row = nullptr;  // per pair, log-prob row of its first frame
+  int32_t lp_cols = 0;
   int32_t k_deg;      // arcs per lane of the lane kernel
   bool identity;      // every degree <= k_deg: thread s owns state s, no plan
   int32_t threads;    // CTA size of the lane kernel
@@ -1569,7 +1591,8 @@ static int32_t LaunchGrad(const LossLayout &LL, const k2b200_intersect_args *arg
       reinterpret_cast<const float *>(ws + L.off_cutoffs),
       reinterpret_cast<const ProbState *>(ws + LL.off_alpha),
       reinterpret_cast<const ProbState *>(ws + LL.off_beta), tot_grad, stride, grad_a, grad_b,
-      frames, lg, s_pad, ga_in_smem, LL.exclusive_rows ? 1 : 0, only_noplan); NoteLaunch(); }
+      frames, lg, s_pad, ga_in_smem, LL.exclusive_rows ? 1 : 0, only_noplan, LL.lp_row,
+      LL.lp_cols); NoteLaunch(); }
   K2B_CUDA_OK(cudaGetLastError());
   return kOk;
 }
@@ -1606,7 +1629,7 @@ static int32_t LaunchGradItems(const LossLayout &LL, const k2b200_intersect_args
       reinterpret_cast<const float *>(ws + L.off_cutoffs),
       reinterpret_cast<const ProbState *>(ws + LL.off_alpha),
       reinterpret_cast<const ProbState *>(ws + LL.off_beta), tot_grad, stride, grad_a, grad_b,
-      frames, lg, ga_in_smem, LL.exclusive_rows ? 1 : 0); NoteLaunch(); }
+      frames, lg, ga_in_smem, LL.exclusive_rows ? 1 : 0, LL.lp_row, LL.lp_cols); NoteLaunch(); }
   K2B_CUDA_OK(cudaGetLastError());
   return kOk;
 }
@@ -1637,7 +1660,7 @@ static int32_t LaunchGradLanes(const LossLayout &LL, const k2b200_intersect_args
       reinterpret_cast<const ProbState *>(ws + LL.off_beta), tot_grad, stride, grad_a, grad_b,
       reinterpret_cast<const int32_t *>(ws + L.off_plan),
       reinterpret_cast<const int32_t *>(ws + L.off_unfit), frames, sub, s_pad,
-      LL.exclusive_rows ? 1 : 0); NoteLaunch(); }
+      LL.exclusive_rows ? 1 : 0, LL.lp_row, LL.lp_cols); NoteLaunch(); }
   K2B_CUDA_OK(cudaGetLastError());
   return kOk;
 }
@@ -1774,13 +1797,14 @@ int32_t k2b200_dense_loss_forward(const k2b200_intersect_args *args, void *works
   return kOk;
 }
 
-int32_t k2b200_dense_loss_backward(const k2b200_intersect_args *args, void *workspace,
-                                   size_t workspace_bytes, const double *tot_grad,
-                                   int32_t tot_grad_stride, float *grad_a, float *grad_b,
-                                   void *stream_v) {
-  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_v);
+static int32_t DenseLossBackward(const k2b200_intersect_args *args, void *workspace,
+                                 size_t workspace_bytes, const double *tot_grad,
+                                 int32_t tot_grad_stride, float *grad_a, float *grad_b,
+                                 const int32_t *lp_row, int32_t lp_cols, cudaStream_t stream) {
   LossLayout LL;
   K2B_FORWARD(MakeLossLayout(args, &LL));
+  LL.lp_row = lp_row;
+  LL.lp_cols = lp_cols;
   const Layout &L = LL.base;
   if (workspace == nullptr || workspace_bytes < LL.total_bytes) {
     SetError("workspace of %zu bytes is smaller than the %zu required", workspace_bytes,
@@ -1809,6 +1833,27 @@ int32_t k2b200_dense_loss_backward(const k2b200_intersect_args *args, void *work
                             stream);
   return LaunchGrad<false>(LL, args, ws, tot_grad, tot_grad_stride, grad_a, grad_b, only_noplan,
                            stream);
+}
+
+int32_t k2b200_dense_loss_backward(const k2b200_intersect_args *args, void *workspace,
+                                   size_t workspace_bytes, const double *tot_grad,
+                                   int32_t tot_grad_stride, float *grad_a, float *grad_b,
+                                   void *stream_v) {
+  return DenseLossBackward(args, workspace, workspace_bytes, tot_grad, tot_grad_stride, grad_a,
+                           grad_b, nullptr, 0, reinterpret_cast<cudaStream_t>(stream_v));
+}
+
+int32_t k2b200_dense_loss_backward_log_probs(const k2b200_intersect_args *args, void *workspace,
+                                             size_t workspace_bytes, const double *tot_grad,
+                                             int32_t tot_grad_stride, float *grad_a,
+                                             float *grad_log_probs, const int32_t *log_prob_row,
+                                             int32_t num_classes, void *stream_v) {
+  K2B_REQUIRE(log_prob_row != nullptr, "NULL log_prob_row");
+  K2B_REQUIRE(args != nullptr && num_classes == args->cols - 1,
+              "num_classes must be the score matrix's columns minus one");
+  return DenseLossBackward(args, workspace, workspace_bytes, tot_grad, tot_grad_stride, grad_a,
+                           grad_log_probs, log_prob_row, num_classes,
+                           reinterpret_cast<cudaStream_t>(stream_v));
 }
 
 }  // extern "C"

@@ -119,6 +119,11 @@ class DenseFsaVec(object):
             fn = _LogSoftmaxDenseFunction if _logits else _DenseFsaVecFunction
             scores = fn.apply(log_probs, meta[:k3].view(-1, 3), meta[k3:], rows, overlapping)
             self._init(scores, row_splits, meta[k3:])
+            if not _logits and not overlapping:
+                # what a loss needs to send its gradient straight to `log_probs`
+                # (k2b200_dense_loss_backward_log_probs): the tensor and, per
+                # sequence, the row of its first frame
+                self._source = (log_probs, first.astype(np.int32))
             return
         else:
             if _logits:
@@ -150,6 +155,8 @@ class DenseFsaVec(object):
     def _init(self, scores: torch.Tensor, h_row_splits: np.ndarray,
               d_row_splits: torch.Tensor = None) -> None:
         assert scores.is_contiguous()
+        self._source = None
+        self._source_rows = {}
         self.scores = scores  # for back propagation
         self.h_row_splits = np.ascontiguousarray(h_row_splits, dtype=np.int32)
         if d_row_splits is not None:

@@ -205,3 +205,39 @@ def test_ctc_graphs_with_more_than_512_states():
     dense = k2.DenseFsaVec(lp.to(DEV), segs)
     _compare(fsa_to_host(graphs), dense.scores.cpu().numpy(), dense.h_row_splits, 12.0,
              tag="long ctc")
+
+
+def test_gradient_goes_straight_to_the_log_probs():
+    """A DenseFsaVec made from a log-prob tensor hands the loss that tensor: the
+    gradient written in its layout is bit-identical to the one that travels through
+    the score matrix and the adjoint of the layout, with offsets, truncation, a
+    permuted and duplicated a_to_b_map."""
+    import k2_b200 as k2
+    rng = np.random.default_rng(8)
+    N, T, C = 5, 23, 7
+    lp0 = torch.log_softmax(torch.from_numpy(rng.normal(size=(N, T, C)).astype(np.float32)), -1)
+    seg = torch.tensor([[3, 0, 23], [0, 2, 20], [4, 1, 15], [1, 5, 9]], dtype=torch.int32)
+    texts = [[1, 2, 3], [4, 4], [5], [2, 6, 1]]
+    for a_to_b in (None, torch.tensor([0, 1, 1, 3, 3], dtype=torch.int32)):
+        n_graphs = 4 if a_to_b is None else 5
+        graphs = k2.ctc_graph((texts + [[3, 3, 1]])[:n_graphs], device=DEV)
+        grads = []
+        for direct in (True, False):
+            lp = lp0.clone().to(DEV).requires_grad_(True)
+            dense = k2.DenseFsaVec(lp, seg, allow_truncate=0)
+            assert dense._source is not None
+            if not direct:
+                dense._source = None
+            tot = k2.intersect_dense_tot_scores(graphs, dense, 10.0, a_to_b_map=a_to_b)
+            w = torch.linspace(0.5, 2.0, tot.numel(), device=DEV, dtype=tot.dtype)
+            (tot * w).sum().backward()
+            grads.append(lp.grad.clone())
+        assert torch.isfinite(grads[0]).all() and grads[0].abs().sum() > 0
+        if a_to_b is None:
+            assert torch.equal(grads[0], grads[1])
+        else:  # rows shared by two graphs are summed with atomics: order may differ
+            assert torch.allclose(grads[0], grads[1], rtol=1e-6, atol=1e-7)
+    # overlapping segments keep the route through the score matrix
+    lp = lp0.clone().to(DEV).requires_grad_(True)
+    over = k2.DenseFsaVec(lp, torch.tensor([[0, 0, 20], [0, 10, 13]], dtype=torch.int32))
+    assert over._source is None
