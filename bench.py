@@ -397,6 +397,15 @@ def run_ours(args):
     ms, wall, launches, _ = timed(args.steps, False)
     # the same steps again with per-phase events, for the roofline of the top kernel
     _, _, _, phases = timed(args.steps, False, profile=True)
+    # time inside this library's kernels per step on every rank (the step itself is
+    # the same on all ranks: the all-reduce keeps them in lockstep)
+    busy = sum(v[0] for k, v in phases.items() if k != "dense") / args.steps
+    busy_by_rank = [busy]
+    if dist is not None:
+        t = torch.zeros(world, dtype=torch.float64, device=dev)
+        t[rank] = busy
+        dist.all_reduce(t)
+        busy_by_rank = [float(x) for x in t.tolist()]
     for _ in range(2):
         step(host_lp, True)
     e2e_ms, e2e_wall, _, _ = timed(args.steps, True)
@@ -483,6 +492,7 @@ def run_ours(args):
         "path_frac_of_hbm": b_alg * args.steps / sec / 1e9 / hbm_peak,
         "wall_ms_per_step": 1e3 * wall / args.steps,
         "phases_ms_per_step": {k: v[0] / args.steps for k, v in phases.items()},
+        "kernel_ms_per_step_by_rank": busy_by_rank,
         "lattice": {"arcs": A_out, "states": S_out, "graph_arcs": A, "arc_frames": arc_frames},
         "roofline": {"kernel": phase_kernel[top], "bound": "hbm", "achieved": achieved,
                      "peak": hbm_peak, "unit": "GB/s", "frac": achieved / hbm_peak,
