@@ -300,6 +300,10 @@ def run_ours(args):
         import torch.distributed as dist
         dist.init_process_group("nccl", device_id=dev)
 
+    numa = {"bound": False}
+    if world > 1 and os.environ.get("K2B_NO_NUMA_BIND") is None:
+        from k2_b200.parallel import bind_to_gpu_numa_node
+        numa = bind_to_gpu_numa_node(dev)  # before the pinned host buffers are allocated
     # every rank owns a whole batch (weak scaling); seeds differ per rank
     w = make_workload(args, rank)
     frames = w.num_frames
@@ -493,6 +497,7 @@ def run_ours(args):
         "wall_ms_per_step": 1e3 * wall / args.steps,
         "phases_ms_per_step": {k: v[0] / args.steps for k, v in phases.items()},
         "kernel_ms_per_step_by_rank": busy_by_rank,
+        "numa": numa,
         "lattice": {"arcs": A_out, "states": S_out, "graph_arcs": A, "arc_frames": arc_frames},
         "roofline": {"kernel": phase_kernel[top], "bound": "hbm", "achieved": achieved,
                      "peak": hbm_peak, "unit": "GB/s", "frac": achieved / hbm_peak,

@@ -82,3 +82,36 @@ class HostPrefetcher:
         torch.cuda.current_stream(self.device).wait_event(self.ready[slot])
         self.taken += 1
         return self.bufs[slot]
+
+
+def bind_to_gpu_numa_node(device) -> dict:
+    """Restricts this process to the CPUs of the NUMA node its GPU hangs off, so that
+    pinned host buffers allocated afterwards (first touch) and the threads that feed
+    the GPU sit next to its PCIe root: with one process per GPU on a multi-socket host,
+    copies that cross the socket interconnect share its bandwidth with every other
+    rank.  Reads the node from sysfs; does nothing when the topology cannot be read or
+    the node's CPUs are not among those the process may use.  Returns what it did."""
+    import os
+    info = {"bound": False}
+    try:
+        props = torch.cuda.get_device_properties(torch.device(device))
+        bus = f"{props.pci_domain_id:04x}:{props.pci_bus_id:02x}:{props.pci_device_id:02x}.0"
+        with open(f"/sys/bus/pci/devices/{bus}/numa_node") as f:
+            node = int(f.read().strip())
+        info.update(pci=bus, node=node)
+        if node < 0:
+            return info
+        with open(f"/sys/devices/system/node/node{node}/cpulist") as f:
+            cpus = set()
+            for part in f.read().strip().split(","):
+                lo, _, hi = part.partition("-")
+                cpus.update(range(int(lo), int(hi or lo) + 1))
+        allowed = os.sched_getaffinity(0)
+        mine = cpus & allowed
+        info["cpus_on_node"] = len(mine)
+        if mine and mine != allowed:
+            os.sched_setaffinity(0, mine)
+            info["bound"] = True
+    except (OSError, ValueError, AttributeError, RuntimeError, AssertionError) as e:
+        info["error"] = str(e)
+    return info

@@ -224,3 +224,13 @@ def test_ragged_attribute_tensor_on_cpu():
     assert r.remove_values_leq(0).tolist() == [[x for x in row if x > 0] for row in rows]
     assert cat([r, out]).tolist() == rows + out.tolist()
     assert r.clone() == r and RaggedTensor([[1], []]) != RaggedTensor([[1]])
+
+
+def test_numa_binding_is_a_no_op_without_a_gpu_topology():
+    import os
+    from k2_b200.parallel import bind_to_gpu_numa_node
+    before = os.sched_getaffinity(0)
+    info = bind_to_gpu_numa_node("cuda:0")
+    assert info["bound"] is False or os.sched_getaffinity(0) <= before
+    if not info["bound"]:
+        assert os.sched_getaffinity(0) == before
