@@ -316,6 +316,69 @@ int32_t k2b200_intersect_dense_pruned_emit(const k2b200_pruned_args *args, void 
                                            const k2b200_lattice_out *out);
 
 /* ---------------------------------------------------------------------------
+ * Chunk-by-chunk decoding: the pruned intersection over a stream of chunks, each call
+ * returning the lattice of everything decoded so far.
+ * Replaces k2::OnlineDenseIntersecter::Decode (k2/csrc/intersect_dense_pruned.cu:
+ * 1739-1853; class k2/csrc/intersect_dense_pruned.h:168-204), bound as
+ * _k2.OnlineDenseIntersecter.decode (k2/python/csrc/torch/fsa_algo.cu:755-800).
+ * One graph is shared by all streams.  What a stream has decoded so far lives in
+ * caller-owned arrays (k2b200_online_stream, the counterpart of k2::DecodeStateInfo);
+ * a call loads them into the workspace, searches the chunk, prunes the last two
+ * frames of the history together with the chunk, closes the lattice with the final
+ * arcs that the chunk's extra row [0, -inf, ...] allows, and stores the streams back:
+ *   1. k2b200_online_decode_workspace_bytes(&args, &bytes)
+ *   2. k2b200_online_decode_load(&args, ws, i, &stream_i, cuda_stream) for every i
+ *   3. k2b200_online_decode_run(...): lattice sizes, per-stream (states, arcs)
+ *      counts for the new stream arrays, updated beams; arena_full = 1 asks for a
+ *      retry with larger max_*_per_seq (reload the streams)
+ *   4. k2b200_online_decode_emit(&args, ws, bytes, cuda_stream, &out)  (arc_map_b and
+ *      the layering are not produced)
+ *   5. k2b200_online_decode_store(&args, ws, i, &new_stream_i, cuda_stream)
+ * A new stream is: one state (the graph's start state, forward score 0), no arcs,
+ * history 0, frame tables {0, 1} and {0, 0}, beam = search_beam.
+ * ------------------------------------------------------------------------- */
+typedef struct {
+  int32_t num_states, num_arcs;
+  int32_t *astate;        /* [num_states] graph state */
+  int32_t *forward;       /* [num_states] forward score, order-preserving int form */
+  int32_t *arc0;          /* [num_states+1] first arc of every state */
+  int32_t *arc_graph;     /* [num_arcs] arc of the graph */
+  float *arc_score;       /* [num_arcs] */
+  int32_t *arc_dest;      /* [num_arcs] state of the next frame */
+  int32_t *frame_state0;  /* [history+2] first state of every frame */
+  int32_t *frame_arc0;    /* [history+2] first arc of every frame */
+} k2b200_online_stream;
+
+typedef struct {
+  int32_t num_states, num_arcs;   /* the one shared graph */
+  const int32_t *a_row_splits1;   /* [2] */
+  const int32_t *a_row_splits2;   /* [num_states+1] */
+  const void *a_arcs;
+  const float *scores;            /* the chunk: [rows, cols] */
+  int32_t rows, cols, num_seqs;
+  const int32_t *b_row_splits;    /* device [num_seqs+1], equal lengths */
+  const int32_t *h_b_row_splits;  /* HOST copy */
+  float search_beam, output_beam;
+  int32_t min_active_states, max_active_states, allow_partial;
+  const int32_t *h_hist;          /* HOST [num_seqs]: frames decoded so far per stream */
+  int64_t max_states_per_seq, max_arcs_per_seq;
+  int32_t team_ctas;              /* as in k2b200_pruned_args */
+} k2b200_online_args;
+
+int32_t k2b200_online_decode_workspace_bytes(const k2b200_online_args *args, size_t *bytes);
+int32_t k2b200_online_decode_load(const k2b200_online_args *args, void *workspace, int32_t seq,
+                                  const k2b200_online_stream *st, void *stream);
+int32_t k2b200_online_decode_run(const k2b200_online_args *args, void *workspace,
+                                 size_t workspace_bytes, void *stream, const float *h_beams_in,
+                                 float *h_beams_out, int32_t *h_counts, int32_t *num_states_out,
+                                 int32_t *num_arcs_out, int32_t *arena_full);
+int32_t k2b200_online_decode_emit(const k2b200_online_args *args, void *workspace,
+                                  size_t workspace_bytes, void *stream,
+                                  const k2b200_lattice_out *out);
+int32_t k2b200_online_decode_store(const k2b200_online_args *args, void *workspace, int32_t seq,
+                                   const k2b200_online_stream *st, void *stream);
+
+/* ---------------------------------------------------------------------------
  * Lattice-free total scores: the log-semiring total score of
  * intersect_dense(a_fsas, b_fsas, output_beam) for every graph, and its
  * gradients, without materialising the lattice.

@@ -8,5 +8,6 @@ from .decode import get_aux_labels, get_lattice, one_best_decoding  # noqa: F401
 from .dense_fsa_vec import DenseFsaVec  # noqa: F401
 from .fsa import Fsa, create_fsa_vec  # noqa: F401
 from .fsa_algo import arc_sort, ctc_graph, ctc_topo, linear_fsa, shortest_path  # noqa: F401
+from .online_dense_intersecter import DecodeStateInfo, OnlineDenseIntersecter  # noqa: F401
 from .ragged import RaggedArc  # noqa: F401
 from .ragged_tensor import RaggedTensor  # noqa: F401

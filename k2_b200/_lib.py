@@ -58,6 +58,27 @@ class PrunedArgs(ctypes.Structure):
     ]
 
 
+class OnlineStream(ctypes.Structure):
+    _fields_ = [
+        ("num_states", c_i32), ("num_arcs", c_i32),
+        ("astate", c_vp), ("forward", c_vp), ("arc0", c_vp), ("arc_graph", c_vp),
+        ("arc_score", c_vp), ("arc_dest", c_vp), ("frame_state0", c_vp), ("frame_arc0", c_vp),
+    ]
+
+
+class OnlineArgs(ctypes.Structure):
+    _fields_ = [
+        ("num_states", c_i32), ("num_arcs", c_i32),
+        ("a_row_splits1", c_vp), ("a_row_splits2", c_vp), ("a_arcs", c_vp),
+        ("scores", c_vp), ("rows", c_i32), ("cols", c_i32), ("num_seqs", c_i32),
+        ("b_row_splits", c_vp), ("h_b_row_splits", c_vp),
+        ("search_beam", c_f32), ("output_beam", c_f32),
+        ("min_active_states", c_i32), ("max_active_states", c_i32), ("allow_partial", c_i32),
+        ("h_hist", c_vp), ("max_states_per_seq", c_i64), ("max_arcs_per_seq", c_i64),
+        ("team_ctas", c_i32),
+    ]
+
+
 class FsaView(ctypes.Structure):
     _fields_ = [
         ("num_fsas", c_i32), ("num_states", c_i32), ("num_arcs", c_i32),
@@ -86,6 +107,17 @@ _sig("k2b200_row_splits_to_row_ids", c_i32, [c_vp, c_i32, c_vp, c_i32, c_vp])
 _sig("k2b200_upload_i32", c_i32, [c_vp, c_i64, c_vp, c_vp])
 _sig("k2b200_dense_loss_backward_log_probs", c_i32,
      [ctypes.POINTER(IntersectArgs), c_vp, c_sz, c_vp, c_i32, c_vp, c_vp, c_vp, c_i32, c_vp])
+_sig("k2b200_online_decode_workspace_bytes", c_i32,
+     [ctypes.POINTER(OnlineArgs), ctypes.POINTER(c_sz)])
+_sig("k2b200_online_decode_load", c_i32,
+     [ctypes.POINTER(OnlineArgs), c_vp, c_i32, ctypes.POINTER(OnlineStream), c_vp])
+_sig("k2b200_online_decode_run", c_i32,
+     [ctypes.POINTER(OnlineArgs), c_vp, c_sz, c_vp, c_vp, c_vp, c_vp, ctypes.POINTER(c_i32),
+      ctypes.POINTER(c_i32), ctypes.POINTER(c_i32)])
+_sig("k2b200_online_decode_emit", c_i32,
+     [ctypes.POINTER(OnlineArgs), c_vp, c_sz, c_vp, ctypes.POINTER(LatticeOut)])
+_sig("k2b200_online_decode_store", c_i32,
+     [ctypes.POINTER(OnlineArgs), c_vp, c_i32, ctypes.POINTER(OnlineStream), c_vp])
 _sig("k2b200_fsa_scores_backprop", c_i32,
      [ctypes.POINTER(FsaView), c_i32, c_i32, c_i32, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp])
 _sig("k2b200_fsa_arc_post_backprop", c_i32,
@@ -175,6 +207,8 @@ EXPORTED = [
     "k2b200_intersect_dense_pruned_emit",
     "k2b200_fsa_scores_backprop", "k2b200_fsa_arc_post_backprop",
     "k2b200_dense_loss_backward_log_probs",
+    "k2b200_online_decode_workspace_bytes", "k2b200_online_decode_load",
+    "k2b200_online_decode_run", "k2b200_online_decode_emit", "k2b200_online_decode_store",
 ]
 
 

@@ -561,7 +561,7 @@ __device__ bool SearchStep(const SearchArgs &g, const SeqView &v, const Team &tm
 // the arenas and the frame tables are updated.
 __device__ void PruneWindow(const SearchArgs &g, const SeqView &v, const Team &tm, int32_t seq,
                             int32_t begin, int32_t end, int32_t na_end, int32_t *s_top,
-                            int32_t *a_top) {
+                            int32_t *a_top, bool keep_all_at_begin = true) {
   Shared *sh = tm.sh;
   const float kNegInf = -INFINITY;
   const int32_t gi = seq * g.a_stride;
@@ -638,7 +638,7 @@ __device__ void PruneWindow(const SearchArgs &g, const SeqView &v, const Team &t
         v.st_cnt[s0 + k] = sh->wcnt[warp][lane];
         const float bwd = (v.st_astate[s0 + k] == g_final) ? -fwd : best;
         v.st_bwd[s0 + k] = bwd;
-        keep_state = (bwd != kNegInf) || t == begin;
+        keep_state = (bwd != kNegInf) || (t == begin && keep_all_at_begin);
       }
       int32_t tot;
       const int32_t j = kept + tm.Scan(keep_state, &tot);
@@ -904,6 +904,221 @@ __global__ void FormatPruned(const FormatArgs f) {
 }
 
 
+// ---------------------------------------------------------------------------
+// Chunk-by-chunk decoding (OnlineDenseIntersecter, k2/csrc/intersect_dense_pruned.cu:
+// 247-312 OnlineIntersect, :336-405 GetFinalFrame, :1739-1853 Decode).  Every stream
+// brings the frames it has decoded so far (loaded into its arena slice before the
+// launch); the kernel searches the frames of the chunk, prunes the last two frames of
+// the history together with the chunk (:274-277), and closes the lattice with the final
+// arcs that the extra row [0, -inf, ...] of the chunk allows.
+// ---------------------------------------------------------------------------
+struct OnlineArgs {
+  SearchArgs g;            // g.T + 2 = capacity of the frame tables
+  const int32_t *hist;     // [num_seqs] frames searched so far (index of the frontier)
+  const float *beam_in;    // [num_seqs]
+  float *beam_out;         // [num_seqs]
+  int32_t chunk;           // frames in this chunk
+  int32_t hist_max;        // longest history in the batch (the reference aligns streams
+                           // at their ends, so the pruning window is counted from there)
+};
+
+// Arc ranges of the states of a frame whose arcs are about to be expanded.
+__device__ int32_t LayoutFrame(const SearchArgs &g, const SeqView &v, const Team &tm, int32_t s0,
+                               int32_t ns, int32_t a0) {
+  int32_t na = 0;
+  for (int32_t base = 0; base < ns; base += tm.threads) {
+    const int32_t k = base + tm.tid;
+    int32_t deg = 0;
+    if (k < ns) {
+      const int32_t as = v.st_astate[s0 + k];
+      deg = g.a_rs2[as + 1] - g.a_rs2[as];
+    }
+    int32_t tot;
+    const int32_t ex = tm.Scan(deg, &tot);
+    if (k < ns) v.st_arc0[s0 + k] = a0 + na + ex;
+    na += tot;
+  }
+  if (tm.tid == 0) v.st_arc0[s0 + ns] = a0 + na;
+  tm.Sync();
+  return na;
+}
+
+// GetFinalFrame (:336-405): the arcs that leave the frontier on the extra row of the
+// chunk; only those with a finite score stay (label -1, or every arc when
+// allow_partial finds no final arc), all of them entering one final state.  Returns
+// their number, or -1 when the arena is full.
+__device__ int32_t FinalArcs(const SearchArgs &g, const SeqView &v, const Team &tm, int32_t seq,
+                             int32_t row, int32_t s0, int32_t ns, int32_t a0) {
+  const int32_t gi = seq * g.a_stride;
+  (void)gi;
+  const bool row_ok = row < g.rows;
+  const float *r = g.scores + (int64_t)(row_ok ? row : 0) * g.cols;
+  bool redirect = false;
+  if (g.allow_partial) {
+    int32_t has = 0;
+    for (int32_t k = tm.tid; k < ns; k += tm.threads) {
+      const int32_t as = v.st_astate[s0 + k];
+      for (int32_t a = g.a_rs2[as]; a < g.a_rs2[as + 1]; ++a) has |= (g.a_arcs[a].label == -1);
+    }
+    redirect = !tm.Any(has);
+  }
+  int32_t na = 0;
+  for (int32_t base = 0; base < ns; base += tm.threads) {
+    const int32_t k = base + tm.tid;
+    int32_t cnt = 0, as = 0;
+    if (k < ns) {
+      as = v.st_astate[s0 + k];
+      for (int32_t a = g.a_rs2[as]; a < g.a_rs2[as + 1]; ++a) {
+        const Arc arc = g.a_arcs[a];
+        const uint32_t col = (uint32_t)(arc.label + 1);
+        float acoustic = (row_ok && col < (uint32_t)g.cols) ? r[col] : -INFINITY;
+        if (redirect) acoustic = 0.0f;
+        const float ll = acoustic + arc.score;
+        cnt += (ll - ll == 0.0f);
+      }
+    }
+    int32_t tot;
+    const int32_t ex = tm.Scan(cnt, &tot);
+    const bool fits = (int64_t)a0 + na + tot <= g.cap_a;
+    if (k < ns && fits) {
+      int32_t p = a0 + na + ex;
+      v.st_arc0[s0 + k] = p;
+      for (int32_t a = g.a_rs2[as]; a < g.a_rs2[as + 1]; ++a) {
+        const Arc arc = g.a_arcs[a];
+        const uint32_t col = (uint32_t)(arc.label + 1);
+        float acoustic = (row_ok && col < (uint32_t)g.cols) ? r[col] : -INFINITY;
+        if (redirect) acoustic = 0.0f;
+        const float ll = acoustic + arc.score;
+        if (ll - ll == 0.0f) {
+          v.arc_aidx[p] = a;
+          v.arc_ll[p] = ll;
+          v.arc_dest[p] = 0;
+          ++p;
+        }
+      }
+    }
+    na += tot;
+    if (!fits) return -1;
+  }
+  if (tm.tid == 0) v.st_arc0[s0 + ns] = a0 + na;
+  tm.Sync();
+  return na;
+}
+
+__global__ void __launch_bounds__(kSearchThreads, 1) OnlineChunk(const OnlineArgs o) {
+  __shared__ Shared sh;
+  const SearchArgs &g = o.g;
+  const Team tm0(&sh);
+  const int32_t seq = blockIdx.x / tm0.size;
+  if (threadIdx.x == 0) {
+    sh.phase_i = sh.phase_f = sh.phase_l = 0;
+    sh.beam = o.beam_in[seq];
+  }
+  __syncthreads();
+  const Team tm(&sh);
+  const SeqView v = ViewOf(g, seq);
+  const int32_t row0 = g.b_rs[seq];
+  const int32_t h = o.hist[seq];
+  const int32_t kNoFinalFrame = 0x3fffffff;  // online: no end-of-sequence rules (:725-760)
+  // the frontier: the states of frame h; what was kept of its arcs (the final arcs of
+  // the previous chunk) is dropped and they are expanded again (:354-361)
+  int32_t s0 = v.frame_s0[h], ns = v.frame_s0[h + 1] - s0, a0 = v.frame_a0[h];
+  int32_t na = LayoutFrame(g, v, tm, s0, ns, a0);
+  int32_t s_top = s0 + ns, a_top = a0;
+  int32_t status = kSeqOk;
+  for (int32_t t = 0; t < o.chunk; ++t) {
+    if (tm.tid == 0) {
+      v.frame_s0[h + t + 1] = s0 + ns;
+      v.frame_a0[h + t + 1] = a0 + na;
+    }
+    int32_t nn, na1;
+    if (!SearchStep(g, v, tm, seq, t, kNoFinalFrame, row0, s0, ns, a0, na, &nn, &na1)) {
+      status = kSeqOverflow;
+      break;
+    }
+    s0 += ns;
+    a0 += na;
+    ns = nn;
+    na = na1;
+    s_top = s0 + ns;
+    a_top = a0;
+  }
+  const int32_t end = h + o.chunk;
+  if (status == kSeqOk) {
+    // PruneTimeRange(max(0, T_ - 2), T_ + chunk) in frames counted from the end of the
+    // longest history: a stream with a shorter one starts inside the window, and then
+    // its first frame is not the one whose states are all kept
+    const int32_t begin_aligned = max(0, o.hist_max - 2) - (o.hist_max - h);
+    PruneWindow(g, v, tm, seq, max(begin_aligned, 0), end, na, &s_top, &a_top,
+                begin_aligned >= 0);
+    s0 = s_top - ns;
+    a0 = a_top;
+    const int32_t nf = FinalArcs(g, v, tm, seq, row0 + o.chunk, s0, ns, a0);
+    if (nf < 0) {
+      status = kSeqOverflow;
+    } else {
+      a_top = a0 + nf;
+      if (tm.tid == 0) {
+        v.frame_s0[end + 1] = s_top;
+        v.frame_a0[end + 1] = a_top;
+        v.st_arc0[s_top] = a_top;
+      }
+    }
+  }
+  if (tm.tid == 0) {
+    int32_t *out = g.seq_out + 4 * seq;
+    out[0] = s_top;      // states without the final one
+    out[1] = a_top;
+    out[2] = end;        // frames: the frontier is frame `end`
+    out[3] = status;
+    o.beam_out[seq] = sh.beam;
+  }
+  tm.Sync();
+}
+
+// Lattice of one (stream, frame) per CTA, all frames so far plus one final state that
+// the final arcs enter (FormatOutput with online_decoding, :474-657; a stream without
+// final arcs gets the state all the same, :519-547).  No arc_map_b.
+__global__ void FormatOnline(const FormatArgs f, const int32_t *__restrict__ hist, int32_t chunk) {
+  const SearchArgs &g = f.g;
+  const int32_t seq = blockIdx.y, t = blockIdx.x;
+  const SeqView v = ViewOf(g, seq);
+  const int32_t end = hist[seq] + chunk;  // the frontier
+  if (t > end + 1) return;
+  const int32_t sb = f.out_rs1[seq], ab = f.arc_base[seq];
+  if (t == end + 1) {
+    if (threadIdx.x == 0) {
+      const int32_t s_top = v.frame_s0[end + 1];
+      f.row_ids1[sb + s_top] = seq;
+      f.row_splits2[sb + s_top] = ab + v.frame_a0[end + 1];
+      if (seq == g.num_seqs - 1) f.row_splits2[f.out_rs1[g.num_seqs]] = f.arc_base[g.num_seqs];
+    }
+    return;
+  }
+  const int32_t s0 = v.frame_s0[t], s1 = v.frame_s0[t + 1];
+  for (int32_t k = s0 + threadIdx.x; k < s1; k += blockDim.x) {
+    const int32_t p0 = v.st_arc0[k], p1 = v.st_arc0[k + 1];
+    f.row_ids1[sb + k] = seq;
+    f.row_splits2[sb + k] = ab + p0;
+    for (int32_t p = p0; p < p1; ++p) {
+      int32_t aidx = v.arc_aidx[p];
+      const int32_t graph_label = g.a_arcs[aidx].label;
+      Arc out;
+      out.src = k;
+      out.dest = s1 + v.arc_dest[p];
+      out.label = graph_label;
+      out.score = v.arc_ll[p];
+      if (t == end && graph_label != -1) {  // allow_partial (:625-634)
+        out.label = -1;
+        aidx = -1;
+      }
+      f.arcs[ab + p] = out;
+      f.row_ids2[ab + p] = sb + k;
+      f.arc_map_a[ab + p] = aidx;
+    }
+  }
+}
+
 // Carves the workspace.  Everything is sized from the arguments alone, so the
 // search and the output call agree on it.
 struct PrunedLayout {
@@ -980,6 +1195,74 @@ int32_t MakePrunedLayout(const k2b200_pruned_args *a, char *ws, PrunedLayout *L)
   g.seq_out = i32(4 * n);
   L->out_rs1 = i32(n + 1);
   L->arc_base = i32(n + 1);
+  L->bytes = off;
+  return kOk;
+}
+
+
+// The online entry points share the arena layout of the batch search: the frame
+// tables are sized for the longest history plus the chunk.
+struct OnlineLayout {
+  PrunedLayout base;
+  int32_t *hist;
+  float *beam_in, *beam_out;
+  int32_t chunk, hist_max;
+  size_t bytes;
+};
+
+int32_t MakeOnlineLayout(const k2b200_online_args *a, char *ws, OnlineLayout *L) {
+  K2B_REQUIRE(a != nullptr && a->h_hist != nullptr && a->h_b_row_splits != nullptr,
+              "NULL arguments");
+  K2B_REQUIRE(a->num_seqs >= 1, "num_seqs must be positive");
+  const int32_t rows0 = a->h_b_row_splits[1] - a->h_b_row_splits[0];
+  int32_t hist_max = 0;
+  for (int32_t i = 0; i < a->num_seqs; ++i) {
+    K2B_REQUIRE(a->h_b_row_splits[i + 1] - a->h_b_row_splits[i] == rows0,
+                "the streams of a chunk must all have the same number of frames");
+    K2B_REQUIRE(a->h_hist[i] >= 0, "negative history length");
+    hist_max = std::max(hist_max, a->h_hist[i]);
+  }
+  K2B_REQUIRE(rows0 >= 2, "a chunk needs at least one frame besides its final row");
+  // a batch-mode argument block whose longest sequence has hist_max + chunk rows gives
+  // frame tables of hist_max + chunk + 2 entries
+  k2b200_pruned_args p = {};
+  p.num_fsas = 1;
+  p.num_states = a->num_states;
+  p.num_arcs = a->num_arcs;
+  p.a_row_splits1 = a->a_row_splits1;
+  p.a_row_splits2 = a->a_row_splits2;
+  p.a_arcs = a->a_arcs;
+  p.scores = a->scores;
+  p.rows = a->rows;
+  p.cols = a->cols;
+  p.num_seqs = a->num_seqs;
+  p.b_row_splits = a->b_row_splits;
+  p.search_beam = a->search_beam;
+  p.output_beam = a->output_beam;
+  p.min_active_states = a->min_active_states;
+  p.max_active_states = a->max_active_states;
+  p.allow_partial = a->allow_partial;
+  p.max_states_per_seq = a->max_states_per_seq;
+  p.max_arcs_per_seq = a->max_arcs_per_seq;
+  std::vector<int32_t> fake(a->num_seqs + 1);
+  for (int32_t i = 0; i <= a->num_seqs; ++i) fake[i] = i * (hist_max + rows0 - 1);
+  p.h_b_row_splits = fake.data();
+  p.rows = fake[a->num_seqs];
+  K2B_FORWARD(MakePrunedLayout(&p, ws, &L->base));
+  SearchArgs &g = L->base.g;
+  g.rows = a->rows;
+  g.a_stride = 0;  // one graph, a table per stream
+  g.T = hist_max + rows0 - 1;
+  // the winner table of the batch layout was sized for a shared graph only when there is
+  // more than one sequence; make room for one table per stream in every case
+  size_t off = L->base.bytes;
+  L->base.winner_bytes = 8 * (size_t)a->num_seqs * (size_t)std::max(a->num_states, 1);
+  g.winner = reinterpret_cast<unsigned long long *>(ws + Take(&off, L->base.winner_bytes));
+  L->hist = reinterpret_cast<int32_t *>(ws + Take(&off, 4 * (size_t)a->num_seqs));
+  L->beam_in = reinterpret_cast<float *>(ws + Take(&off, 4 * (size_t)a->num_seqs));
+  L->beam_out = reinterpret_cast<float *>(ws + Take(&off, 4 * (size_t)a->num_seqs));
+  L->chunk = rows0 - 1;
+  L->hist_max = hist_max;
   L->bytes = off;
   return kOk;
 }
@@ -1100,6 +1383,176 @@ int32_t k2b200_intersect_dense_pruned_emit(const k2b200_pruned_args *args, void 
   dim3 grid(L.g.T + 2, args->num_seqs);
   { FormatPruned<<<grid, 128, 0, stream>>>(f); NoteLaunch(); }
   K2B_CUDA_OK(cudaGetLastError());
+  return kOk;
+}
+
+
+int32_t k2b200_online_decode_workspace_bytes(const k2b200_online_args *args, size_t *bytes) {
+  OnlineLayout L;
+  K2B_FORWARD(MakeOnlineLayout(args, nullptr, &L));
+  K2B_REQUIRE(bytes != nullptr, "NULL bytes");
+  *bytes = L.bytes;
+  return kOk;
+}
+
+// Copies what stream `seq` has decoded so far into its slice of the arenas.
+int32_t k2b200_online_decode_load(const k2b200_online_args *args, void *workspace, int32_t seq,
+                                  const k2b200_online_stream *st, void *stream_v) {
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_v);
+  OnlineLayout L;
+  K2B_FORWARD(MakeOnlineLayout(args, reinterpret_cast<char *>(workspace), &L));
+  K2B_REQUIRE(st != nullptr && seq >= 0 && seq < args->num_seqs, "bad stream");
+  const SearchArgs &g = L.base.g;
+  const int32_t h = args->h_hist[seq];
+  K2B_REQUIRE(st->num_states <= g.cap_s && st->num_arcs <= g.cap_a,
+              "the arena is smaller than what stream %d already holds", seq);
+  const int64_t so = (int64_t)seq * (g.cap_s + 1), ao = (int64_t)seq * g.cap_a,
+                fo = (int64_t)seq * (g.T + 2);
+  auto copy = [&](void *dst, const void *src, size_t n) {
+    return n == 0 ? cudaSuccess
+                  : cudaMemcpyAsync(dst, src, n, cudaMemcpyDeviceToDevice, stream);
+  };
+  K2B_CUDA_OK(copy(g.st_astate + so, st->astate, 4 * (size_t)st->num_states));
+  K2B_CUDA_OK(copy(g.st_fwd + so, st->forward, 4 * (size_t)st->num_states));
+  K2B_CUDA_OK(copy(g.st_arc0 + so, st->arc0, 4 * ((size_t)st->num_states + 1)));
+  K2B_CUDA_OK(copy(g.arc_aidx + ao, st->arc_graph, 4 * (size_t)st->num_arcs));
+  K2B_CUDA_OK(copy(g.arc_ll + ao, st->arc_score, 4 * (size_t)st->num_arcs));
+  K2B_CUDA_OK(copy(g.arc_dest + ao, st->arc_dest, 4 * (size_t)st->num_arcs));
+  K2B_CUDA_OK(copy(g.frame_s0 + fo, st->frame_state0, 4 * ((size_t)h + 2)));
+  K2B_CUDA_OK(copy(g.frame_a0 + fo, st->frame_arc0, 4 * ((size_t)h + 2)));
+  return kOk;
+}
+
+int32_t k2b200_online_decode_run(const k2b200_online_args *args, void *workspace,
+                                 size_t workspace_bytes, void *stream_v, const float *h_beams_in,
+                                 float *h_beams_out, int32_t *h_counts, int32_t *num_states_out,
+                                 int32_t *num_arcs_out, int32_t *arena_full) {
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_v);
+  OnlineLayout L;
+  K2B_FORWARD(MakeOnlineLayout(args, reinterpret_cast<char *>(workspace), &L));
+  K2B_REQUIRE(workspace != nullptr && workspace_bytes >= L.bytes, "workspace too small");
+  K2B_REQUIRE(h_beams_in && h_beams_out && h_counts && num_states_out && num_arcs_out &&
+                  arena_full, "NULL pointer");
+  const int32_t n = args->num_seqs;
+  K2B_CUDA_OK(cudaMemsetAsync(L.base.g.winner, 0, L.base.winner_bytes, stream));
+  K2B_FORWARD(UploadInts(args->h_hist, n, L.hist, stream));
+  K2B_FORWARD(UploadInts(reinterpret_cast<const int32_t *>(h_beams_in), n,
+                         reinterpret_cast<int32_t *>(L.beam_in), stream));
+  OnlineArgs o;
+  o.g = L.base.g;
+  o.hist = L.hist;
+  o.beam_in = L.beam_in;
+  o.beam_out = L.beam_out;
+  o.chunk = L.chunk;
+  o.hist_max = L.hist_max;
+  {
+    int dev = 0, sms = 0;
+    K2B_CUDA_OK(cudaGetDevice(&dev));
+    K2B_CUDA_OK(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+    int32_t team = 1;
+    while (team < 8 && n * team * 2 <= sms) team *= 2;
+    if (args->team_ctas > 0) team = args->team_ctas;
+    K2B_REQUIRE(team == 1 || team == 2 || team == 4 || team == 8, "team_ctas must be 1, 2, 4 or 8");
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(n * team);
+    cfg.blockDim = dim3(kSearchThreads);
+    cfg.stream = stream;
+    cudaLaunchAttribute attr;
+    attr.id = cudaLaunchAttributeClusterDimension;
+    attr.val.clusterDim.x = team;
+    attr.val.clusterDim.y = 1;
+    attr.val.clusterDim.z = 1;
+    cfg.attrs = &attr;
+    cfg.numAttrs = 1;
+    K2B_CUDA_OK(cudaLaunchKernelEx(&cfg, OnlineChunk, o));
+    NoteLaunch();
+  }
+  std::vector<int32_t> h(4 * (size_t)n);
+  K2B_CUDA_OK(cudaMemcpyAsync(h.data(), L.base.g.seq_out, sizeof(int32_t) * h.size(),
+                              cudaMemcpyDeviceToHost, stream));
+  K2B_CUDA_OK(cudaMemcpyAsync(h_beams_out, L.beam_out, sizeof(float) * n, cudaMemcpyDeviceToHost,
+                              stream));
+  K2B_CUDA_OK(cudaStreamSynchronize(stream));
+  std::vector<int32_t> bases(2 * ((size_t)n + 1));
+  int32_t *srs = bases.data(), *ars = bases.data() + n + 1;
+  int64_t ts = 0, ta = 0;
+  *arena_full = 0;
+  for (int32_t i = 0; i < n; ++i) {
+    if (h[4 * i + 3] == kSeqOverflow) *arena_full = 1;
+    h_counts[2 * i] = h[4 * i];
+    h_counts[2 * i + 1] = h[4 * i + 1];
+    srs[i] = (int32_t)ts;
+    ars[i] = (int32_t)ta;
+    ts += h[4 * i] + 1;  // one final state per stream
+    ta += h[4 * i + 1];
+  }
+  srs[n] = (int32_t)ts;
+  ars[n] = (int32_t)ta;
+  *num_states_out = *num_arcs_out = 0;
+  if (*arena_full) return kOk;
+  K2B_REQUIRE(ts < INT_MAX && ta < INT_MAX, "the lattice has too many states or arcs for int32");
+  K2B_FORWARD(UploadInts(srs, n + 1, L.base.out_rs1, stream));
+  K2B_FORWARD(UploadInts(ars, n + 1, L.base.arc_base, stream));
+  *num_states_out = (int32_t)ts;
+  *num_arcs_out = (int32_t)ta;
+  return kOk;
+}
+
+int32_t k2b200_online_decode_emit(const k2b200_online_args *args, void *workspace,
+                                  size_t workspace_bytes, void *stream_v,
+                                  const k2b200_lattice_out *out) {
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_v);
+  OnlineLayout L;
+  K2B_FORWARD(MakeOnlineLayout(args, reinterpret_cast<char *>(workspace), &L));
+  K2B_REQUIRE(workspace != nullptr && workspace_bytes >= L.bytes, "workspace too small");
+  K2B_REQUIRE(out && out->row_splits1 && out->row_ids1 && out->row_splits2 && out->row_ids2 &&
+                  out->arcs && out->arc_map_a, "NULL output pointer");
+  FormatArgs f;
+  f.g = L.base.g;
+  f.out_rs1 = L.base.out_rs1;
+  f.arc_base = L.base.arc_base;
+  f.row_ids1 = out->row_ids1;
+  f.row_splits2 = out->row_splits2;
+  f.row_ids2 = out->row_ids2;
+  f.arcs = reinterpret_cast<Arc *>(out->arcs);
+  f.arc_map_a = out->arc_map_a;
+  f.arc_map_b = nullptr;
+  f.level_offsets = nullptr;
+  f.level_splits = nullptr;
+  K2B_CUDA_OK(cudaMemcpyAsync(out->row_splits1, L.base.out_rs1,
+                              sizeof(int32_t) * (args->num_seqs + 1), cudaMemcpyDeviceToDevice,
+                              stream));
+  dim3 grid(L.base.g.T + 2, args->num_seqs);
+  { FormatOnline<<<grid, 128, 0, stream>>>(f, L.hist, L.chunk); NoteLaunch(); }
+  K2B_CUDA_OK(cudaGetLastError());
+  return kOk;
+}
+
+// Copies stream `seq` out of its arena slice: num_states / num_arcs as reported by
+// k2b200_online_decode_run, frame tables of (history + chunk + 2) entries.
+int32_t k2b200_online_decode_store(const k2b200_online_args *args, void *workspace, int32_t seq,
+                                   const k2b200_online_stream *st, void *stream_v) {
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_v);
+  OnlineLayout L;
+  K2B_FORWARD(MakeOnlineLayout(args, reinterpret_cast<char *>(workspace), &L));
+  K2B_REQUIRE(st != nullptr && seq >= 0 && seq < args->num_seqs, "bad stream");
+  const SearchArgs &g = L.base.g;
+  const int32_t h = args->h_hist[seq] + L.chunk;
+  const int64_t so = (int64_t)seq * (g.cap_s + 1), ao = (int64_t)seq * g.cap_a,
+                fo = (int64_t)seq * (g.T + 2);
+  auto copy = [&](const void *dst, const void *src, size_t n) {
+    return n == 0 ? cudaSuccess
+                  : cudaMemcpyAsync(const_cast<void *>(dst), src, n, cudaMemcpyDeviceToDevice,
+                                    stream);
+  };
+  K2B_CUDA_OK(copy(st->astate, g.st_astate + so, 4 * (size_t)st->num_states));
+  K2B_CUDA_OK(copy(st->forward, g.st_fwd + so, 4 * (size_t)st->num_states));
+  K2B_CUDA_OK(copy(st->arc0, g.st_arc0 + so, 4 * ((size_t)st->num_states + 1)));
+  K2B_CUDA_OK(copy(st->arc_graph, g.arc_aidx + ao, 4 * (size_t)st->num_arcs));
+  K2B_CUDA_OK(copy(st->arc_score, g.arc_ll + ao, 4 * (size_t)st->num_arcs));
+  K2B_CUDA_OK(copy(st->arc_dest, g.arc_dest + ao, 4 * (size_t)st->num_arcs));
+  K2B_CUDA_OK(copy(st->frame_state0, g.frame_s0 + fo, 4 * ((size_t)h + 2)));
+  K2B_CUDA_OK(copy(st->frame_arc0, g.frame_a0 + fo, 4 * ((size_t)h + 2)));
   return kOk;
 }
 

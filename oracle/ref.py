@@ -64,6 +64,18 @@ def lib():
         L.kref_intersect_dense_pruned.argtypes = [
             ctypes.c_void_p, _f32p, ctypes.c_int32, ctypes.c_int32, _i32p, ctypes.c_int32,
             ctypes.c_float, ctypes.c_float, ctypes.c_int32, ctypes.c_int32, ctypes.c_int32]
+        L.kref_online_create.restype = ctypes.c_void_p
+        L.kref_online_create.argtypes = [ctypes.c_void_p, ctypes.c_int32, ctypes.c_float,
+                                         ctypes.c_float, ctypes.c_int32, ctypes.c_int32,
+                                         ctypes.c_int32]
+        L.kref_online_free.argtypes = [ctypes.c_void_p]
+        L.kref_online_stream_free.argtypes = [ctypes.c_void_p]
+        L.kref_online_stream_beam.restype = ctypes.c_float
+        L.kref_online_stream_beam.argtypes = [ctypes.c_void_p]
+        L.kref_online_decode.restype = ctypes.c_void_p
+        L.kref_online_decode.argtypes = [ctypes.c_void_p, _f32p, ctypes.c_int32, ctypes.c_int32,
+                                         _i32p, ctypes.c_int32,
+                                         ctypes.POINTER(ctypes.c_void_p)]
         L.kref_forward_scores.argtypes = [ctypes.c_void_p, ctypes.c_int32, ctypes.c_int32,
                                           _f64p, _i32p]
         L.kref_backward_scores.argtypes = [ctypes.c_void_p, ctypes.c_int32, ctypes.c_int32,
@@ -110,7 +122,7 @@ class _Handle:
         arcs = np.zeros((na, 4), np.int32)
         auxa = np.zeros(na, np.int32) if aux else None
         ma = np.zeros(na, np.int32) if maps else None
-        mb = np.zeros(na, np.int32) if maps else None
+        mb = np.zeros(na, np.int32) if maps and maps != "a" else None
         lib().kref_fsavec_copy(self.ptr, _p(rs1, _i32p), _p(rs2, _i32p),
                                arcs.ctypes.data_as(ctypes.c_void_p), _p(auxa, _i32p),
                                _p(ma, _i32p), _p(mb, _i32p))
@@ -175,6 +187,34 @@ def intersect_dense_pruned(a: HostFsaVec, scores, b_row_splits, search_beam, out
         len(brs) - 1, float(search_beam), float(output_beam), int(min_active),
         int(max_active), int(bool(allow_partial))))
     return out.to_host(maps=True)
+
+
+class OnlineIntersecter:
+    """The reference's OnlineDenseIntersecter on CPU.  Streams are opaque handles
+    (None starts a new one); `decode` returns the lattice so far (arc_map_a only) and
+    the updated handles."""
+
+    def __init__(self, graph: HostFsaVec, num_seqs, search_beam, output_beam, min_active,
+                 max_active, allow_partial=True):
+        self._graph = to_handle(graph)
+        self._ptr = lib().kref_online_create(self._graph.ptr, int(num_seqs), float(search_beam),
+                                             float(output_beam), int(min_active),
+                                             int(max_active), int(bool(allow_partial)))
+        if not self._ptr:
+            raise RuntimeError("k2 reference raised: " + _err())
+
+    def decode(self, scores, b_row_splits, streams):
+        scores = np.ascontiguousarray(scores, np.float32)
+        brs = np.ascontiguousarray(b_row_splits, np.int32)
+        n = len(brs) - 1
+        arr = (ctypes.c_void_p * n)(*[s for s in streams])
+        out = _Handle(lib().kref_online_decode(self._ptr, _p(scores, _f32p), scores.shape[0],
+                                               scores.shape[1], _p(brs, _i32p), n, arr))
+        return out.to_host(maps="a"), [arr[i] for i in range(n)]
+
+    @staticmethod
+    def beam(stream) -> float:
+        return float(lib().kref_online_stream_beam(stream))
 
 
 def forward_scores(f: HostFsaVec, log_semiring=True, use_double=True,

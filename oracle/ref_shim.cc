@@ -26,6 +26,7 @@
 #include "k2/csrc/fsa.h"
 #include "k2/csrc/fsa_algo.h"
 #include "k2/csrc/fsa_utils.h"
+#include "k2/csrc/intersect_dense_pruned.h"
 #include "k2/csrc/ragged.h"
 #include "k2/csrc/ragged_ops.h"
 
@@ -265,6 +266,69 @@ void *kref_intersect_dense_pruned(void *a_handle, const float *scores, int32_t r
     k2::IntersectDensePruned(a->fsas, b, search_beam, output_beam, min_active,
                              max_active, allow_partial != 0, &out->fsas,
                              &out->arc_map_a, &out->arc_map_b);
+  } catch (...) {
+    delete out;
+    throw;
+  }
+  return out;
+  KREF_CATCH(nullptr)
+}
+
+// Online (chunk by chunk) pruned intersection, k2/csrc/intersect_dense_pruned.cu:1739-1853.
+// An intersecter handle owns the shared graph; a stream handle owns one
+// k2::DecodeStateInfo.  kref_online_decode takes the chunk's score matrix and one
+// stream handle per sequence (NULL starts a new stream and the new handle is written
+// back), and returns the lattice of everything decoded so far (arc_map_a only).
+struct OnlineHandle {
+  k2::FsaVec graph;
+  k2::OnlineDenseIntersecter *impl;
+};
+
+void *kref_online_create(void *a_handle, int32_t num_seqs, float search_beam,
+                         float output_beam, int32_t min_active, int32_t max_active,
+                         int32_t allow_partial) {
+  KREF_TRY
+  auto *h = new OnlineHandle;
+  h->graph = reinterpret_cast<FsaVecHandle *>(a_handle)->fsas;
+  h->impl = new k2::OnlineDenseIntersecter(h->graph, num_seqs, search_beam, output_beam,
+                                           min_active, max_active, allow_partial != 0);
+  return h;
+  KREF_CATCH(nullptr)
+}
+
+void kref_online_free(void *handle) {
+  auto *h = reinterpret_cast<OnlineHandle *>(handle);
+  delete h->impl;
+  delete h;
+}
+
+void kref_online_stream_free(void *stream) {
+  delete reinterpret_cast<k2::DecodeStateInfo *>(stream);
+}
+
+float kref_online_stream_beam(void *stream) {
+  return reinterpret_cast<k2::DecodeStateInfo *>(stream)->beam;
+}
+
+void *kref_online_decode(void *handle, const float *scores, int32_t rows, int32_t cols,
+                         const int32_t *b_row_splits, int32_t num_seqs, void **streams) {
+  KREF_TRY
+  auto *h = reinterpret_cast<OnlineHandle *>(handle);
+  k2::ContextPtr c = k2::GetCpuContext();
+  k2::Array2<float> sc(c, rows, cols);
+  if (rows * cols > 0)
+    memcpy(sc.Data(), scores, sizeof(float) * (size_t)rows * (size_t)cols);
+  k2::Array1<int32_t> brs = FromHost(b_row_splits, num_seqs + 1);
+  k2::RaggedShape bshape = k2::RaggedShape2(&brs, nullptr, rows);
+  k2::DenseFsaVec b(bshape, sc);
+  std::vector<k2::DecodeStateInfo *> states(num_seqs);
+  for (int32_t i = 0; i < num_seqs; ++i) {
+    if (streams[i] == nullptr) streams[i] = new k2::DecodeStateInfo();
+    states[i] = reinterpret_cast<k2::DecodeStateInfo *>(streams[i]);
+  }
+  auto *out = new FsaVecHandle;
+  try {
+    h->impl->Decode(b, &states, &out->fsas, &out->arc_map_a);
   } catch (...) {
     delete out;
     throw;
