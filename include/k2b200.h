@@ -273,7 +273,7 @@ int32_t k2b200_intersect_dense_emit(const k2b200_intersect_args *args, void *wor
  * sequence or a single graph shared by all sequences (num_fsas == 1).  States of
  * a frame are numbered as the reference's CPU build numbers them (by the first
  * arc that reaches them above the cutoff), so lattices and arc maps are
- * identical to it.  Online (chunk by chunk) decoding is not provided.
+ * identical to it.  Chunk-by-chunk decoding: k2b200_online_decode_* below.
  *
  * Protocol (one host synchronisation):
  *   1. k2b200_intersect_dense_pruned_workspace_bytes(&args, &bytes, &levels)

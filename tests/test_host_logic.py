@@ -234,3 +234,33 @@ def test_numa_binding_is_a_no_op_without_a_gpu_topology():
     assert info["bound"] is False or os.sched_getaffinity(0) <= before
     if not info["bound"]:
         assert os.sched_getaffinity(0) == before
+
+
+def test_online_decoding_sizing_and_validation_need_no_gpu():
+    import ctypes
+    from k2_b200 import _lib
+    lib = _lib.lib
+    brs = (np.arange(4) * 9).astype(np.int32)       # three streams, 8 frames + final row
+    hist = np.array([0, 24, 8], np.int32)
+
+    def args(**kw):
+        base = dict(num_states=500, num_arcs=3000, rows=27, cols=41, num_seqs=3,
+                    h_b_row_splits=brs.ctypes.data, search_beam=20.0, output_beam=8.0,
+                    min_active_states=30, max_active_states=10000, allow_partial=1,
+                    h_hist=hist.ctypes.data, max_states_per_seq=1 << 12,
+                    max_arcs_per_seq=1 << 13, team_ctas=0)
+        base.update(kw)
+        return _lib.OnlineArgs(**base)
+
+    nbytes = ctypes.c_size_t()
+    a = args()
+    assert lib.k2b200_online_decode_workspace_bytes(ctypes.byref(a), ctypes.byref(nbytes)) == 0
+    arenas = 3 * (17 * (1 << 13) + 24 * ((1 << 12) + 1))
+    assert nbytes.value >= arenas + 3 * 500 * 8 + 2 * 3 * (24 + 8 + 2) * 4
+    uneven = np.array([0, 9, 17, 26], np.int32)
+    for bad, msg in ((dict(h_b_row_splits=uneven.ctypes.data, rows=26), b"same number of frames"),
+                     (dict(search_beam=-1.0), b"positive")):
+        a = args(**bad)
+        assert lib.k2b200_online_decode_workspace_bytes(ctypes.byref(a),
+                                                        ctypes.byref(nbytes)) != 0
+        assert msg in lib.k2b200_last_error(), (bad, lib.k2b200_last_error())
