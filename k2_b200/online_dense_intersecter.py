@@ -18,12 +18,14 @@ from .ragged import RaggedArc
 class DecodeStateInfo:
     """What one stream has decoded so far (k2::DecodeStateInfo,
     k2/csrc/intersect_dense_pruned.h:113-137): the pruned frames as device arrays, the
-    number of frames and the current search beam.  `None` in the list given to `decode`
-    starts a new stream."""
+    number of frames and the current search beam.  `DecodeStateInfo()` (or `None`) in the
+    list given to `decode` starts a new stream."""
 
-    def __init__(self, tensors, frames: int, beam: float):
-        (self.astate, self.forward, self.arc0, self.arc_graph, self.arc_score, self.arc_dest,
-         self.frame_state0, self.frame_arc0) = tensors
+    def __init__(self, tensors=None, frames: int = 0, beam: Optional[float] = None):
+        self.is_new = tensors is None
+        if tensors is not None:
+            (self.astate, self.forward, self.arc0, self.arc_graph, self.arc_score,
+             self.arc_dest, self.frame_state0, self.frame_arc0) = tensors
         self.frames = frames
         self.beam = beam
 
@@ -86,7 +88,7 @@ class OnlineDenseIntersecter:
         n = dense_fsas.dim0()
         if len(decode_states) != n:
             raise RuntimeError(f"{len(decode_states)} decode states for {n} sequences")
-        states = [self._new_stream() if s is None else s for s in decode_states]
+        states = [self._new_stream() if s is None or s.is_new else s for s in decode_states]
         h_brs = np.ascontiguousarray(dense_fsas.h_row_splits, dtype=np.int32)
         h_hist = np.asarray([s.frames for s in states], dtype=np.int32)
         beams_in = np.asarray([s.beam for s in states], dtype=np.float32)

@@ -29,7 +29,8 @@ def chunk_scores(rng, n, frames, classes, scale=1.0):
     return sc, (np.arange(n + 1) * (frames + 1)).astype(np.int32)
 
 
-def run_both(k2, graph: HostFsaVec, params, schedule, frames, classes, seed, scale=1.0):
+def run_both(k2, graph: HostFsaVec, params, schedule, frames, classes, seed, scale=1.0,
+             small_arena=False):
     """schedule: per chunk, the list of stream ids in the batch (new ids start streams)."""
     from gpu_util import DEV, dense_from_scores, fsa_to_host, host_to_fsa
     rng = np.random.default_rng(seed)
@@ -37,6 +38,8 @@ def run_both(k2, graph: HostFsaVec, params, schedule, frames, classes, seed, sca
     theirs = ref.OnlineIntersecter(graph, n, *params)
     g = host_to_fsa(graph)
     ours = k2.OnlineDenseIntersecter(g, n, *params)
+    if small_arena:
+        ours._arcs_per_seq = 8  # every chunk overflows first and is retried
     their_streams, our_streams = {}, {}
     for k, ids in enumerate(schedule):
         sc, brs = chunk_scores(rng, n, frames, classes, scale)
@@ -61,6 +64,11 @@ def test_streams_that_start_together(k2):
     g = decoding_graph(rng, 300, 9, mean_degree=3.0)
     run_both(k2, g, (8.0, 4.0, 5, 60, True), [[0, 1, 2]] * 5, frames=16, classes=9, seed=2,
              scale=2.0)
+    lat = run_both(k2, g, (8.0, 4.0, 5, 60, True), [[0, 1, 2]] * 3, frames=16, classes=9, seed=2,
+                   scale=2.0, small_arena=True)
+    assert lat.arcs.num_elements() > 100
+    # more streams than SMs / 2: one CTA per stream
+    run_both(k2, g, (6.0, 3.0, 2, 30, True), [list(range(90))] * 2, frames=5, classes=9, seed=7)
 
 
 def test_streams_that_join_and_leave(k2):
@@ -92,7 +100,7 @@ def test_text_of_the_best_path_grows_with_the_chunks(k2):
         logits[0, t, sym] = 6.0
     log_prob = torch.log_softmax(logits, -1)
     dec = k2.OnlineDenseIntersecter(H, 1, 20.0, 8.0, 0, 1000)
-    states = [None]
+    states = [k2.DecodeStateInfo()]  # as the reference's own test starts its streams
     chunk = 6
     for k in range(T // chunk):
         lp = log_prob[:, k * chunk:(k + 1) * chunk].contiguous().to(DEV)
