@@ -377,6 +377,13 @@ int32_t k2b200_online_decode_emit(const k2b200_online_args *args, void *workspac
                                   const k2b200_lattice_out *out);
 int32_t k2b200_online_decode_store(const k2b200_online_args *args, void *workspace, int32_t seq,
                                    const k2b200_online_stream *st, void *stream);
+/* The same for all streams of the batch in one launch; `streams` is a HOST array of
+ * num_seqs descriptors (the store must come before the next load: the list of copies
+ * lives in the workspace). */
+int32_t k2b200_online_decode_load_all(const k2b200_online_args *args, void *workspace,
+                                      const k2b200_online_stream *streams, void *stream);
+int32_t k2b200_online_decode_store_all(const k2b200_online_args *args, void *workspace,
+                                       const k2b200_online_stream *streams, void *stream);
 
 /* ---------------------------------------------------------------------------
  * Lattice-free total scores: the log-semiring total score of

@@ -111,6 +111,10 @@ _sig("k2b200_online_decode_workspace_bytes", c_i32,
      [ctypes.POINTER(OnlineArgs), ctypes.POINTER(c_sz)])
 _sig("k2b200_online_decode_load", c_i32,
      [ctypes.POINTER(OnlineArgs), c_vp, c_i32, ctypes.POINTER(OnlineStream), c_vp])
+_sig("k2b200_online_decode_load_all", c_i32,
+     [ctypes.POINTER(OnlineArgs), c_vp, ctypes.POINTER(OnlineStream), c_vp])
+_sig("k2b200_online_decode_store_all", c_i32,
+     [ctypes.POINTER(OnlineArgs), c_vp, ctypes.POINTER(OnlineStream), c_vp])
 _sig("k2b200_online_decode_run", c_i32,
      [ctypes.POINTER(OnlineArgs), c_vp, c_sz, c_vp, c_vp, c_vp, c_vp, ctypes.POINTER(c_i32),
       ctypes.POINTER(c_i32), ctypes.POINTER(c_i32)])
@@ -209,6 +213,7 @@ EXPORTED = [
     "k2b200_dense_loss_backward_log_probs",
     "k2b200_online_decode_workspace_bytes", "k2b200_online_decode_load",
     "k2b200_online_decode_run", "k2b200_online_decode_emit", "k2b200_online_decode_store",
+    "k2b200_online_decode_load_all", "k2b200_online_decode_store_all",
 ]
 
 

@@ -1200,12 +1200,25 @@ int32_t MakePrunedLayout(const k2b200_pruned_args *a, char *ws, PrunedLayout *L)
 }
 
 
+// Many small device-to-device copies in one launch (the eight arrays of every stream):
+// one CTA per copy, 4-byte elements.
+struct CopyJob {
+  const int32_t *src;
+  int32_t *dst;
+  int64_t count;
+};
+__global__ void CopyMany(const CopyJob *__restrict__ jobs) {
+  const CopyJob j = jobs[blockIdx.x];
+  for (int64_t k = threadIdx.x; k < j.count; k += blockDim.x) j.dst[k] = j.src[k];
+}
+
 // The online entry points share the arena layout of the batch search: the frame
 // tables are sized for the longest history plus the chunk.
 struct OnlineLayout {
   PrunedLayout base;
   int32_t *hist;
   float *beam_in, *beam_out;
+  CopyJob *jobs;  // [8 * num_seqs]
   int32_t chunk, hist_max;
   size_t bytes;
 };
@@ -1261,6 +1274,7 @@ int32_t MakeOnlineLayout(const k2b200_online_args *a, char *ws, OnlineLayout *L)
   L->hist = reinterpret_cast<int32_t *>(ws + Take(&off, 4 * (size_t)a->num_seqs));
   L->beam_in = reinterpret_cast<float *>(ws + Take(&off, 4 * (size_t)a->num_seqs));
   L->beam_out = reinterpret_cast<float *>(ws + Take(&off, 4 * (size_t)a->num_seqs));
+  L->jobs = reinterpret_cast<CopyJob *>(ws + Take(&off, sizeof(CopyJob) * 8 * (size_t)a->num_seqs));
   L->chunk = rows0 - 1;
   L->hist_max = hist_max;
   L->bytes = off;
@@ -1554,6 +1568,60 @@ int32_t k2b200_online_decode_store(const k2b200_online_args *args, void *workspa
   K2B_CUDA_OK(copy(st->frame_state0, g.frame_s0 + fo, 4 * ((size_t)h + 2)));
   K2B_CUDA_OK(copy(st->frame_arc0, g.frame_a0 + fo, 4 * ((size_t)h + 2)));
   return kOk;
+}
+
+
+// All streams in one launch: `streams` is a HOST array of num_seqs descriptors.
+static int32_t CopyStreams(const k2b200_online_args *args, void *workspace,
+                           const k2b200_online_stream *streams, bool load, cudaStream_t stream) {
+  OnlineLayout L;
+  K2B_FORWARD(MakeOnlineLayout(args, reinterpret_cast<char *>(workspace), &L));
+  K2B_REQUIRE(streams != nullptr, "NULL streams");
+  const SearchArgs &g = L.base.g;
+  const int32_t n = args->num_seqs;
+  std::vector<CopyJob> jobs;
+  jobs.reserve(8 * (size_t)n);
+  for (int32_t i = 0; i < n; ++i) {
+    const k2b200_online_stream &st = streams[i];
+    K2B_REQUIRE(st.num_states <= g.cap_s && st.num_arcs <= g.cap_a,
+                "the arena is smaller than what stream %d holds", i);
+    const int64_t h = args->h_hist[i] + (load ? 0 : L.chunk);
+    const int64_t so = (int64_t)i * (g.cap_s + 1), ao = (int64_t)i * g.cap_a,
+                  fo = (int64_t)i * (g.T + 2);
+    struct { int32_t *arena; void *mine; int64_t count; } parts[8] = {
+        {g.st_astate + so, st.astate, st.num_states},
+        {g.st_fwd + so, st.forward, st.num_states},
+        {g.st_arc0 + so, st.arc0, (int64_t)st.num_states + 1},
+        {g.arc_aidx + ao, st.arc_graph, st.num_arcs},
+        {reinterpret_cast<int32_t *>(g.arc_ll + ao), st.arc_score, st.num_arcs},
+        {g.arc_dest + ao, st.arc_dest, st.num_arcs},
+        {g.frame_s0 + fo, st.frame_state0, h + 2},
+        {g.frame_a0 + fo, st.frame_arc0, h + 2}};
+    for (const auto &p : parts) {
+      CopyJob j;
+      j.src = load ? reinterpret_cast<const int32_t *>(p.mine) : p.arena;
+      j.dst = load ? p.arena : reinterpret_cast<int32_t *>(p.mine);
+      j.count = p.count;
+      jobs.push_back(j);
+    }
+  }
+  static_assert(sizeof(CopyJob) % 4 == 0, "jobs travel as 32-bit words");
+  K2B_FORWARD(UploadInts(reinterpret_cast<const int32_t *>(jobs.data()),
+                         (int64_t)(jobs.size() * sizeof(CopyJob) / 4),
+                         reinterpret_cast<int32_t *>(L.jobs), stream));
+  { CopyMany<<<(unsigned)jobs.size(), 256, 0, stream>>>(L.jobs); NoteLaunch(); }
+  K2B_CUDA_OK(cudaGetLastError());
+  return kOk;
+}
+
+int32_t k2b200_online_decode_load_all(const k2b200_online_args *args, void *workspace,
+                                      const k2b200_online_stream *streams, void *stream_v) {
+  return CopyStreams(args, workspace, streams, true, reinterpret_cast<cudaStream_t>(stream_v));
+}
+
+int32_t k2b200_online_decode_store_all(const k2b200_online_args *args, void *workspace,
+                                       const k2b200_online_stream *streams, void *stream_v) {
+  return CopyStreams(args, workspace, streams, false, reinterpret_cast<cudaStream_t>(stream_v));
 }
 
 }  // extern "C"

@@ -118,10 +118,9 @@ class OnlineDenseIntersecter:
             counts = np.zeros(2 * n, np.int32)
             ns, na, full = ctypes.c_int32(), ctypes.c_int32(), ctypes.c_int32()
             with torch.cuda.device(dev):
-                for i, s in enumerate(states):
-                    c = s._c()
-                    _lib.check(_lib.lib.k2b200_online_decode_load(
-                        ctypes.byref(args), _lib.ptr(ws), i, ctypes.byref(c), stream))
+                loads = (_lib.OnlineStream * n)(*[s._c() for s in states])
+                _lib.check(_lib.lib.k2b200_online_decode_load_all(
+                    ctypes.byref(args), _lib.ptr(ws), loads, stream))
                 _lib.check(_lib.lib.k2b200_online_decode_run(
                     ctypes.byref(args), _lib.ptr(ws), nbytes.value, stream,
                     beams_in.ctypes.data, beams_out.ctypes.data, counts.ctypes.data,
@@ -149,13 +148,21 @@ class OnlineDenseIntersecter:
                 level_offsets=None, level_splits=None)
             _lib.check(_lib.lib.k2b200_online_decode_emit(
                 ctypes.byref(args), _lib.ptr(ws), nbytes.value, stream, ctypes.byref(out)))
-            for i, s in enumerate(states):
-                st = _alloc_state(int(counts[2 * i]), int(counts[2 * i + 1]), s.frames + chunk,
-                                  float(beams_out[i]), dev)
-                c = st._c()
-                _lib.check(_lib.lib.k2b200_online_decode_store(
-                    ctypes.byref(args), _lib.ptr(ws), i, ctypes.byref(c), stream))
-                new_states.append(st)
+            # one allocation for the arrays of all streams of the batch
+            sizes = [(int(counts[2 * i]), int(counts[2 * i + 1]), s.frames + chunk)
+                     for i, s in enumerate(states)]
+            pool = torch.empty(sum(3 * a + 1 + 3 * b + 2 * (f + 2) for a, b, f in sizes) + 1, **i32)
+            at = 0
+            for i, (a, b, f) in enumerate(sizes):
+                parts = []
+                for count in (a, a, a + 1, b, b, b, f + 2, f + 2):
+                    parts.append(pool[at:at + count])
+                    at += count
+                parts[4] = parts[4].view(torch.float32)
+                new_states.append(DecodeStateInfo(tuple(parts), f, float(beams_out[i])))
+            stores = (_lib.OnlineStream * n)(*[s._c() for s in new_states])
+            _lib.check(_lib.lib.k2b200_online_decode_store_all(
+                ctypes.byref(args), _lib.ptr(ws), stores, stream))
         lattice = RaggedArc(values[:na], row_splits1, row_splits2, row_ids1[:ns], row_ids2[:na])
         arc_map_a = arc_map_a[:na]
         # attributes of the graph follow the arc map, as
