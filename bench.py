@@ -46,6 +46,9 @@ def parse_args():
     p.add_argument("--no-cpu-baseline", action="store_true")
     p.add_argument("--decode", action="store_true",
                    help="time the decoding path instead: hlg_decode through intersect_dense_pruned")
+    p.add_argument("--chunk", type=int, default=0,
+                   help="with --decode: decode chunk by chunk (OnlineDenseIntersecter), this many "
+                        "frames per chunk")
     return p.parse_args()
 
 
@@ -594,15 +597,40 @@ def run_decode(args):
     graph = _fsa_vec_from_numpy(np.array([0, S]), w.graph_row_splits2, w.graph_arcs, dev)
     dense = k2.DenseFsaVec(w.log_probs.to(dev), w.supervision_segments)
 
-    def step():
-        lat = k2.intersect_dense_pruned(graph, dense, **DECODE_PARAMS)
-        best = k2.shortest_path(lat, use_double_scores=True)
-        tot = lat.get_tot_scores(use_double_scores=True, log_semiring=True)
-        return lat, best, tot
+    if args.chunk > 0:
+        # streaming: one OnlineDenseIntersecter.decode per chunk, every call returning the
+        # lattice of everything decoded so far; a "step" is the whole batch, all chunks
+        lp = w.log_probs.to(dev)
+        seg = torch.tensor([[i, 0, args.chunk] for i in range(n)], dtype=torch.int32)
+        decoder = k2.OnlineDenseIntersecter(graph, n, *DECODE_PARAMS.values())
+        config["chunk_frames"] = args.chunk
+        chunk_ms = []
+
+        def step():
+            states = [None] * n
+            lat = None
+            for k in range(t // args.chunk):
+                x = lp[:, k * args.chunk:(k + 1) * args.chunk].contiguous()
+                c0, c1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                c0.record()
+                lat, states = decoder.decode(k2.DenseFsaVec(x, seg), states)
+                c1.record()
+                chunk_ms.append((c0, c1))
+            best = k2.shortest_path(lat, use_double_scores=True)
+            tot = lat.get_tot_scores(use_double_scores=True, log_semiring=True)
+            return lat, best, tot
+    else:
+        def step():
+            lat = k2.intersect_dense_pruned(graph, dense, **DECODE_PARAMS)
+            best = k2.shortest_path(lat, use_double_scores=True)
+            tot = lat.get_tot_scores(use_double_scores=True, log_semiring=True)
+            return lat, best, tot
 
     for _ in range(max(args.warmup, 3)):
         lat, best, tot = step()
     torch.cuda.synchronize()
+    if args.chunk > 0:
+        chunk_ms.clear()
     clocks = ClockSampler(0)
     clocks.start()
     n0 = _lib.launch_count()
@@ -614,7 +642,12 @@ def run_decode(args):
     torch.cuda.synchronize()
     ms = e0.elapsed_time(e1) / args.steps
     launches = (_lib.launch_count() - n0) // args.steps
+    extra = {}
+    if args.chunk > 0:
+        per = sorted(a.elapsed_time(b) for a, b in chunk_ms)
+        extra = {"ms_per_chunk_median": per[len(per) // 2], "ms_per_chunk_max": per[-1]}
     print(json.dumps({
+        **extra,
         "metric": "decode_frames_per_sec", "value": n * t / (ms * 1e-3), "unit": "frames/s",
         "n_gpus": 1, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms,
         "higher_is_better": True, "dtype": "f32", "data": "synthetic", "config": config,

@@ -331,8 +331,8 @@ int32_t k2b200_intersect_dense_pruned_emit(const k2b200_pruned_args *args, void 
  *   3. k2b200_online_decode_run(...): lattice sizes, per-stream (states, arcs)
  *      counts for the new stream arrays, updated beams; arena_full = 1 asks for a
  *      retry with larger max_*_per_seq (reload the streams)
- *   4. k2b200_online_decode_emit(&args, ws, bytes, cuda_stream, &out)  (arc_map_b and
- *      the layering are not produced)
+ *   4. k2b200_online_decode_emit(&args, ws, bytes, cuda_stream, &out)  (no arc_map_b;
+ *      the optional layering has sum_i (history_i + chunk + 2) layers)
  *   5. k2b200_online_decode_store(&args, ws, i, &new_stream_i, cuda_stream)
  * A new stream is: one state (the graph's start state, forward score 0), no arcs,
  * history 0, frame tables {0, 1} and {0, 0}, beam = search_beam.

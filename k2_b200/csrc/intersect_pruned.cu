@@ -1086,6 +1086,12 @@ __global__ void FormatOnline(const FormatArgs f, const int32_t *__restrict__ his
   const int32_t end = hist[seq] + chunk;  // the frontier
   if (t > end + 1) return;
   const int32_t sb = f.out_rs1[seq], ab = f.arc_base[seq];
+  if (f.level_splits != nullptr && threadIdx.x == 0) {
+    // frames are layers; the final state is a layer of its own
+    const int32_t lo = f.level_offsets[seq];
+    f.level_splits[lo + t] = sb + v.frame_s0[t];
+    if (seq == g.num_seqs - 1 && t == end + 1) f.level_splits[lo + t + 1] = f.out_rs1[g.num_seqs];
+  }
   if (t == end + 1) {
     if (threadIdx.x == 0) {
       const int32_t s_top = v.frame_s0[end + 1];
@@ -1531,8 +1537,17 @@ int32_t k2b200_online_decode_emit(const k2b200_online_args *args, void *workspac
   f.arcs = reinterpret_cast<Arc *>(out->arcs);
   f.arc_map_a = out->arc_map_a;
   f.arc_map_b = nullptr;
-  f.level_offsets = nullptr;
-  f.level_splits = nullptr;
+  K2B_REQUIRE((out->level_offsets == nullptr) == (out->level_splits == nullptr),
+              "level_offsets and level_splits go together");
+  f.level_offsets = out->level_offsets;
+  f.level_splits = out->level_splits;
+  if (out->level_offsets != nullptr) {
+    // stream i has (history + chunk + 2) layers: its frames and the final state
+    std::vector<int32_t> lo(args->num_seqs + 1, 0);
+    for (int32_t i = 0; i < args->num_seqs; ++i)
+      lo[i + 1] = lo[i] + args->h_hist[i] + L.chunk + 2;
+    K2B_FORWARD(UploadInts(lo.data(), args->num_seqs + 1, out->level_offsets, stream));
+  }
   K2B_CUDA_OK(cudaMemcpyAsync(out->row_splits1, L.base.out_rs1,
                               sizeof(int32_t) * (args->num_seqs + 1), cudaMemcpyDeviceToDevice,
                               stream));

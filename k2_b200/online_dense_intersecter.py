@@ -141,11 +141,13 @@ class OnlineDenseIntersecter:
             row_ids2 = torch.empty(na + 1, **i32)
             values = torch.empty((na + 1, 4), **i32)
             arc_map_a = torch.empty(na + 1, **i32)
+            level_offsets = torch.empty(n + 1, **i32)
+            level_splits = torch.empty(int(h_hist.sum()) + n * (chunk + 2) + 1, **i32)
             out = _lib.LatticeOut(
                 row_splits1=_lib.ptr(row_splits1), row_ids1=_lib.ptr(row_ids1),
                 row_splits2=_lib.ptr(row_splits2), row_ids2=_lib.ptr(row_ids2),
                 arcs=_lib.ptr(values), arc_map_a=_lib.ptr(arc_map_a), arc_map_b=None,
-                level_offsets=None, level_splits=None)
+                level_offsets=_lib.ptr(level_offsets), level_splits=_lib.ptr(level_splits))
             _lib.check(_lib.lib.k2b200_online_decode_emit(
                 ctypes.byref(args), _lib.ptr(ws), nbytes.value, stream, ctypes.byref(out)))
             # one allocation for the arrays of all streams of the batch
@@ -164,6 +166,7 @@ class OnlineDenseIntersecter:
             _lib.check(_lib.lib.k2b200_online_decode_store_all(
                 ctypes.byref(args), _lib.ptr(ws), stores, stream))
         lattice = RaggedArc(values[:na], row_splits1, row_splits2, row_ids1[:ns], row_ids2[:na])
+        lattice._levels = (level_offsets, level_splits)  # frames are layers
         arc_map_a = arc_map_a[:na]
         # attributes of the graph follow the arc map, as
         # k2.utils.fsa_from_unary_function_tensor does (k2/python/k2/utils.py)
