@@ -44,6 +44,8 @@ def parse_args():
     p.add_argument("--utterances", type=int, default=None,
                    help="lfmmi_den only: batch size, e.g. 16 = one GPU's share of 128 split 8 ways")
     p.add_argument("--no-cpu-baseline", action="store_true")
+    p.add_argument("--no-lfmmi-den", action="store_true",
+                   help="skip the LF-MMI denominator block of the default line")
     p.add_argument("--decode", action="store_true",
                    help="time the decoding path instead: hlg_decode through intersect_dense_pruned")
     p.add_argument("--chunk", type=int, default=0,
@@ -52,12 +54,24 @@ def parse_args():
     return p.parse_args()
 
 
-def make_workload(args, seed):
-    from k2_b200 import synthetic as syn
-    if args.utterances is not None:
-        assert args.workload == "lfmmi_den", "--utterances applies to lfmmi_den"
+def load_synthetic():
+    """k2_b200/synthetic.py loaded by path: the CPU arms make their inputs from it without
+    importing the package (and with it the CUDA library)."""
+    import importlib.util
+    spec = importlib.util.spec_from_file_location(
+        "_k2b200_synthetic", os.path.join(ROOT, "k2_b200", "synthetic.py"))
+    mod = importlib.util.module_from_spec(spec)
+    sys.modules[spec.name] = mod  # dataclasses look their module up by name
+    spec.loader.exec_module(mod)
+    return mod
+
+
+def make_workload(args, seed, syn=None, name=None):
+    syn = syn or load_synthetic()
+    name = name or args.workload
+    if name == "lfmmi_den" and args.utterances is not None:
         return syn.lfmmi_den(seed=seed, scale=args.scale, utterances=args.utterances)
-    return syn.WORKLOADS[args.workload](seed=seed, scale=args.scale)
+    return syn.WORKLOADS[name](seed=seed, scale=args.scale)
 
 
 # --------------------------------------------------------------------------- clocks
@@ -132,14 +146,21 @@ def cpu_reference_step(w, graphs_host, scores, row_splits, impl_mod):
     return dt, float(-tot.sum())
 
 
-def host_inputs(w):
-    """Graphs and the DenseFsaVec score matrix of a workload as host arrays."""
+def host_inputs(w, impl_mod):
+    """Graphs and the DenseFsaVec score matrix of a workload as host arrays, made with
+    numpy and the CPU implementation itself (no part of the CUDA package)."""
     import numpy as np
-    from k2_b200 import synthetic as syn
     from oracle.common import HostFsaVec
-    g = syn.build_graphs(w, "cpu")
-    a = g.arcs
-    graphs = HostFsaVec(a.h_row_splits1, a._row_splits2.numpy(), a.values().numpy())
+    if w.symbols is not None:
+        graphs = impl_mod.ctc_graphs(w.symbols, w.modified)
+    else:  # one graph, stacked once per utterance (the reference cannot share it)
+        n = w.supervision_segments.shape[0]
+        S, A = len(w.graph_row_splits2) - 1, len(w.graph_arcs)
+        rs1 = (np.arange(n + 1, dtype=np.int64) * S).astype(np.int32)
+        rs2 = (np.arange(n, dtype=np.int64)[:, None] * A +
+               w.graph_row_splits2[None, :-1]).reshape(-1)
+        rs2 = np.append(rs2, n * A).astype(np.int32)
+        graphs = HostFsaVec(rs1, rs2, np.tile(w.graph_arcs, (n, 1)))
     scores, row_splits = host_scores(w)
     return graphs, scores, row_splits
 
@@ -230,10 +251,9 @@ def run_reference(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    from k2_b200 import synthetic as syn
     w = make_workload(args, 0)
     impl_mod, kind = pick_cpu_impl()
-    graphs, scores, row_splits = host_inputs(w)
+    graphs, scores, row_splits = host_inputs(w, impl_mod)
     frames = w.num_frames
     # single thread, as the reference runs this path
     cpu_reference_step(w, graphs, scores, row_splits, impl_mod)
@@ -241,16 +261,13 @@ def run_reference(args):
                  for _ in range(2))
     # all host cores: one reference run per utterance shard
     cores = max(1, min(os.cpu_count() or 1, len(row_splits) - 1))
-    ms_steps = []
-    used = cores
     import multiprocessing as mp
     global _SHARDS
     shards = _shard_inputs(w, graphs, scores, row_splits, cores)
     _SHARDS = (w, impl_mod.__name__.split(".")[-1], shards)
     used = len(shards)
     with mp.get_context("fork").Pool(used) as pool:
-        for _ in range(max(args.warmup, 1) and 1):
-            pool.map(_run_shard, range(used))
+        pool.map(_run_shard, range(used))  # warm-up
         t0 = time.perf_counter()
         for _ in range(args.steps):
             pool.map(_run_shard, range(used))
@@ -284,6 +301,42 @@ def workload_config(w, args):
 
 
 # --------------------------------------------------------------------------- GPU arm
+def algorithmic_bytes(frames, N, T, C, A, A_out, S_out, lattice_written):
+    """Bytes that must cross HBM at least once per step: every supervised log-prob row
+    read once, the dense gradient written once (zeros included), the graph arcs once,
+    and - only when the timed path writes the lattice - its arcs, arc maps and rows."""
+    b = 4 * frames * C + 4 * N * T * C + 16 * A
+    if lattice_written:
+        b += 24 * A_out + 8 * S_out
+    return b
+
+
+def implementation_bytes(phase, kernel, frames, N, T, C, A, A_out, S_out, grid_states):
+    """What the kernels of a phase actually move per step by their design (reads and
+    writes they cannot avoid as written) - the figure ncu's DRAM traffic is checked
+    against, not a roofline denominator."""
+    R = frames
+    table = {
+        # every row by both directions, both grids written
+        "BandViterbi": 2 * 4 * R * C + 8 * grid_states,
+        # both grids read once (plus one row in sixteen again), the lists written
+        "BandPrep": int(8 * grid_states * 17 / 16) + 16 * S_out + 32 * S_out,
+        "BandChain": 2 * 16 * S_out + 2 * 12 * S_out,
+        "BandGrad": (16 + 24) * S_out + 32 * S_out,
+        "RegisterViterbi": 2 * 4 * R * C + 8 * grid_states,
+        "LanesViterbi": 2 * 4 * R * C + 8 * grid_states,
+        "GridChainLanes": 2 * 12 * R * C + 16 * grid_states + 32 * S_out,
+        "ArcMasks+GridChainMasked": 24 * R * C + 16 * grid_states + 32 * S_out,
+        "GridGradItems": 8 * grid_states + 32 * S_out + 12 * R * C + 4 * A_out,
+        "GridGradLanes": 8 * grid_states + 32 * S_out + 12 * R * C + 4 * A_out,
+        "GridGradWarp": 8 * grid_states + 32 * S_out + 12 * R * C + 4 * A_out,
+        "CountStates": 8 * grid_states,
+        "ProbScoresStaged": 16 * A_out + 16 * S_out,
+        "EmitLattice": 8 * grid_states + 24 * A_out + 8 * S_out,
+    }
+    return table.get(kernel)
+
+
 def run_ours(args):
     import numpy as np
     import torch
@@ -291,6 +344,7 @@ def run_ours(args):
     import k2_b200 as k2
     from k2_b200 import _lib
     from k2_b200 import synthetic as syn
+    from k2_b200.parallel import HostPrefetcher, shard_segments
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
@@ -308,70 +362,52 @@ def run_ours(args):
         from k2_b200.parallel import bind_to_gpu_numa_node
         numa = bind_to_gpu_numa_node(dev)  # before the pinned host buffers are allocated
     # every rank owns a whole batch (weak scaling); seeds differ per rank
-    w = make_workload(args, rank)
+    w = make_workload(args, rank, syn)
     frames = w.num_frames
     graphs = syn.build_graphs(w, dev)
-    graphs.arcs.incoming()  # graph preprocessing is cached across steps
     host_lp = w.log_probs.pin_memory()
     dev_lp = w.log_probs.to(dev)
     seg = w.supervision_segments
-    # per step the ranks all-reduce [loss, frames]; the pair is staged with one copy
+    # per step the ranks all-reduce [loss, frames] on a side stream, right after the
+    # total scores exist and beside the gradient kernels (the gradient of a summed loss
+    # does not depend on the other ranks)
     red = torch.zeros(2, dtype=torch.float64, device=dev)
-    red_src = torch.zeros(2, dtype=torch.float64, device=dev)
-    red_src[1] = float(frames)
+    red[1] = float(frames)
+    comm = torch.cuda.Stream(dev) if dist is not None else None
 
-    def step(lp_src, from_host):
-        if from_host:
-            lp = lp_src.to(dev, non_blocking=True)
-        else:
-            lp = lp_src
+    def loss_step(lp, g, segments, beam):
         lp = lp.detach().requires_grad_(True)
-        dense = k2.DenseFsaVec(lp, seg)
-        loss = k2.ctc_loss(graphs, dense, output_beam=w.output_beam, reduction="sum")
+        dense = k2.DenseFsaVec(lp, segments)
+        loss = k2.ctc_loss(g, dense, output_beam=beam, reduction="sum")
+        if dist is not None:
+            with torch.no_grad():
+                red[0:1].copy_(loss.detach().reshape(1))
+            comm.wait_stream(torch.cuda.current_stream(dev))
+            with torch.cuda.stream(comm):
+                dist.all_reduce(red)
         loss.backward()
         if dist is not None:
-            red_src[0:1].copy_(loss.detach().reshape(1))
-            red.copy_(red_src)
-            dist.all_reduce(red)
-            out = red[0]
-        else:
-            out = loss.detach()
-        if from_host:
-            return float(out.item()), lp.grad
-        return out, lp.grad
+            torch.cuda.current_stream(dev).wait_stream(comm)
+            return red[0], lp.grad
+        return loss.detach(), lp.grad
+
+    def step(lp):
+        return loss_step(lp, graphs, seg, w.output_beam)
 
     def barrier():
         if dist is not None:
             dist.barrier()
         torch.cuda.synchronize()
 
-    def timed_pipelined(nsteps):
-        """End to end as a training loop runs it: every step's log-probs are copied
-        from pinned host memory inside the timed region, on a copy stream, one step
-        ahead of the step that consumes them; every step's loss is read on the host."""
-        from k2_b200.parallel import HostPrefetcher
-        pf = HostPrefetcher(dev)
-        barrier()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
-        pf.submit(host_lp)
-        for k in range(nsteps):
-            lp = pf.get()
-            if k + 1 < nsteps:
-                pf.submit(host_lp)
-            out, _ = step(lp, False)
-            float(out.item())
-        e1.record()
-        barrier()
-        ms = e0.elapsed_time(e1)
-        if dist is not None:
-            t = torch.tensor([ms], dtype=torch.float64, device=dev)
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
-            ms = float(t.item())
-        return ms
+    def max_over_ranks(ms):
+        if dist is None:
+            return ms
+        t = torch.tensor([ms], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
 
-    def timed(nsteps, from_host, profile=False):
-        src = host_lp if from_host else dev_lp
+    def timed(nsteps, fn, profile=False):
+        """K steps of fn() between barriers; device time, max over ranks."""
         barrier()
         if profile:
             _lib.profile_enable(True)
@@ -380,7 +416,7 @@ def run_ours(args):
         t0 = time.perf_counter()
         e0.record()
         for _ in range(nsteps):
-            step(src, from_host)
+            fn()
         e1.record()
         barrier()
         wall = time.perf_counter() - t0
@@ -390,37 +426,112 @@ def run_ours(args):
         if profile:
             phases = _lib.profile_read()
             _lib.profile_enable(False)
-        if dist is not None:
-            t = torch.tensor([ms], dtype=torch.float64, device=dev)
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
-            ms = float(t.item())
-        return ms, wall, launches, phases
+        return max_over_ranks(ms), wall, launches, phases
+
+    def timed_from_host(nsteps, pipelined):
+        """End to end: every step's log-probs are copied from pinned host memory inside
+        the timed region and every step's loss is read on the host.  pipelined: the copy
+        of step k+1 runs on a copy stream while step k computes (HostPrefetcher), as a
+        training loop feeds the GPU; otherwise copy, compute and read-back follow one
+        another."""
+        pf = HostPrefetcher(dev)
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        if pipelined:
+            pf.submit(host_lp)
+        for k in range(nsteps):
+            if pipelined:
+                lp = pf.get()
+                if k + 1 < nsteps:
+                    pf.submit(host_lp)
+            else:
+                lp = host_lp.to(dev, non_blocking=True)
+            out, _ = step(lp)
+            float(out.item())
+        e1.record()
+        barrier()
+        return max_over_ranks(e0.elapsed_time(e1))
 
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()  # before the warm-up so that it is sampling by the timed region
-    for _ in range(max(args.warmup, 3)):
-        step(dev_lp, False)
-    ms, wall, launches, _ = timed(args.steps, False)
+    warm = max(args.warmup, 3)
+    for _ in range(warm):
+        step(dev_lp)
+    ms, wall, launches, _ = timed(args.steps, lambda: step(dev_lp))
     # the same steps again with per-phase events, for the roofline of the top kernel
-    _, _, _, phases = timed(args.steps, False, profile=True)
-    # time inside this library's kernels per step on every rank (the step itself is
-    # the same on all ranks: the all-reduce keeps them in lockstep)
-    busy = sum(v[0] for k, v in phases.items() if k != "dense") / args.steps
+    _, _, _, phases = timed(args.steps, lambda: step(dev_lp), profile=True)
+    kernels = _lib.profile_kernels()
+    # time inside this library's kernels per step on every rank
+    busy = sum(v[0] for k, v in phases.items()) / args.steps
     busy_by_rank = [busy]
     if dist is not None:
         t = torch.zeros(world, dtype=torch.float64, device=dev)
         t[rank] = busy
         dist.all_reduce(t)
         busy_by_rank = [float(x) for x in t.tolist()]
-    for _ in range(2):
-        step(host_lp, True)
-    e2e_ms, e2e_wall, _, _ = timed(args.steps, True)
-    timed_pipelined(2)
-    e2e_pipe_ms = timed_pipelined(args.steps)
+    timed_from_host(2, False)
+    serial_ms = timed_from_host(args.steps, False)
+    timed_from_host(2, True)
+    e2e_ms = timed_from_host(args.steps, True)
+
+    # cold graphs: a training loop sees new transcripts every batch, so the graphs are
+    # built (ctc_graph on the device) and prepared inside the step
+    cold_ms = None
+    if w.symbols is not None:
+        rng = np.random.default_rng(1234 + rank)
+        C = int(w.log_probs.shape[2])
+        fresh = [[rng.integers(1, C, size=len(s)).tolist() for s in w.symbols]
+                 for _ in range(args.steps + 2)]
+        it = iter(fresh)
+
+        def cold_step():
+            g = k2.ctc_graph(next(it), modified=w.modified, device=dev)
+            return loss_step(dev_lp, g, seg, w.output_beam)
+        cold_step()
+        cold_step()
+        cold_ms, _, _, _ = timed(args.steps, cold_step)
+
+    # ---- the LF-MMI denominator, ONE batch of 128 split by utterance over the ranks
+    # (strong split): each rank takes every world-th utterance of the duration-sorted
+    # batch, the shared graph is replicated, the only exchange is the 16-byte all-reduce
+    den = None
+    if args.workload == "ctc_large" and args.scale == 1.0 and not args.no_lfmmi_den:
+        wd = syn.lfmmi_den(seed=0)
+        d_seg, d_idx = shard_segments(wd.supervision_segments, world, rank)
+        # this rank's utterances, renumbered 0..n-1 in its own log-prob tensor
+        d_lp = wd.log_probs[torch.from_numpy(wd.supervision_segments[:, 0].numpy()[d_idx]
+                                             .astype(np.int64))].contiguous().to(dev)
+        d_seg = d_seg.clone()
+        d_seg[:, 0] = torch.arange(d_seg.shape[0], dtype=torch.int32)
+        sub = syn.Workload("lfmmi_den", wd.log_probs[:d_seg.shape[0]], d_seg, wd.output_beam,
+                           graph_row_splits2=wd.graph_row_splits2, graph_arcs=wd.graph_arcs)
+        d_graphs = syn.build_graphs(sub, dev)
+        d_frames_all = wd.num_frames
+        d_arc_frames = int(len(wd.graph_arcs)) * d_frames_all
+
+        def den_step():
+            return loss_step(d_lp, d_graphs, d_seg, wd.output_beam)
+        for _ in range(warm):
+            den_step()
+        d_ms, _, _, _ = timed(args.steps, den_step)
+        _, _, _, d_phases = timed(args.steps, den_step, profile=True)
+        d_kernels = _lib.profile_kernels()
+        Nd, Td, Cd = wd.log_probs.shape
+        d_alg = algorithmic_bytes(d_frames_all, Nd, Td, Cd, Nd * len(wd.graph_arcs), 0, 0, False)
+        den = {"workload": "lfmmi_den", "utterances": int(Nd), "utterances_per_gpu": int(d_seg.shape[0]),
+               "split": "strong: one batch of 128 split by utterance over the ranks",
+               "ms_per_step": d_ms / args.steps,
+               "frames_per_sec": d_frames_all * args.steps / (d_ms * 1e-3),
+               "arc_frames_per_sec": d_arc_frames * args.steps / (d_ms * 1e-3),
+               "algorithmic_bytes_per_step": d_alg,
+               "phases_ms_per_step": {k: v[0] / args.steps for k, v in d_phases.items() if v[0] > 0},
+               "kernels": {k: d_kernels[k] for k, v in d_phases.items() if v[0] > 0}}
+
     clocks = sampler.stop() if rank == 0 else None
 
-    # lattice size for the algorithmic-byte figure
+    # lattice size for the byte figures (what the lattice path would write)
     with torch.no_grad():
         dense = k2.DenseFsaVec(dev_lp, seg)
         lat = k2.intersect_dense(graphs, dense, w.output_beam)
@@ -429,37 +540,10 @@ def run_ours(args):
     A_out, S_out = lat.num_arcs, lat.arcs.num_states
     arc_frames = int(sum(int(graphs.arcs.h_arc_splits[i + 1] - graphs.arcs.h_arc_splits[i]) *
                          int(seg[i, 2]) for i in range(seg.shape[0])))
-    # whole path: rows once, dense gradient once, graph once, lattice once
-    b_alg = 4 * frames * C + 4 * N * T * C + 16 * A + 24 * A_out + 8 * S_out
-    # Algorithmic bytes of each phase's kernels (what must cross HBM at least once):
-    #   viterbi : every supervised row + the graph               4RC + 16A
-    #   scores  : lattice arcs + one score per state and direction 16A_out + 16S_out
-    #   prune/emit: the two Viterbi grids once + the lattice written
-    grid_bytes = 8 * sum(int(graphs.arcs.h_row_splits1[i + 1] - graphs.arcs.h_row_splits1[i]) *
-                         (int(seg[i, 2]) + 2) for i in range(seg.shape[0]))
-    phase_bytes = {
-        "viterbi": 4 * frames * C + 16 * A,
-        "scores": 16 * A_out + 16 * S_out,
-        "prune": grid_bytes,
-        "emit": grid_bytes + 24 * A_out + 8 * S_out,
-        # DenseFill + DenseBackward, and the repacking with exp() for the lattice-free loss
-        "dense": 8 * frames * C + 4 * N * T * C + 16 * frames * C,
-        "post": 40 * A_out,
-        "incoming": 24 * A_out,
-        # lattice-free loss: both recursions read the packed rows (12 bytes per element)
-        # and the two Viterbi grids and write one 16-byte value per surviving state
-        "chain": 2 * 12 * frames * C + 2 * grid_bytes + 32 * S_out,
-        # gradients: grids, surviving alpha/beta, packed rows, one write per dense element
-        # that a surviving arc touches
-        "grad": grid_bytes + 32 * S_out + 12 * frames * C + 4 * A_out,
-    }
-    planned = graphs.arcs.max_degree() > 4  # lanes assigned to states by a plan
-    phase_kernel = {"viterbi": "LanesViterbi" if planned else "RegisterViterbi",
-                    "scores": "ProbScoresStaged", "prune": "CountStates|CountKept",
-                    "emit": "EmitLattice", "dense": "DenseFill+DenseBackward+ExpDense",
-                    "post": "ArcPost+LogBackward+IndexAdd", "incoming": "BuildIncoming",
-                    "chain": "ArcMasks+GridChainMasked" if planned else "GridChainLanes",
-                    "grad": "GridGradLanes" if planned else "GridGradWarp"}
+    grid_states = sum(int(graphs.arcs.h_row_splits1[i + 1] - graphs.arcs.h_row_splits1[i]) *
+                      (int(seg[i, 2]) + 2) for i in range(seg.shape[0]))
+    lattice_written = phases["emit"][0] > 0
+    b_alg = algorithmic_bytes(frames, N, T, C, A, A_out, S_out, lattice_written)
     peaks = {}
     try:
         with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
@@ -468,17 +552,20 @@ def run_ours(args):
         pass
     hbm_peak = float(peaks.get("hbm_gbs", 6650.0))
     peak_src = "measured" if "hbm_gbs" in peaks else "fallback"
-    # the dominant phase of the timed region carries the roofline figure
+    # the dominant phase of the timed region carries the roofline figure: the path's
+    # algorithmic bytes per launch (one launch of it per step) over its duration
     top = max(phases, key=lambda k: phases[k][0])
     top_ms, top_n = phases[top]
-    top_avg_ms = top_ms / args.steps  # the phase's kernels of one step
-    achieved = phase_bytes[top] / (top_avg_ms * 1e-3) / 1e9 if top_avg_ms > 0 else 0.0
-    # dram read + write of one launch from the ncu capture of this workload (profiles/);
-    # known for ctc_large only
+    top_avg_ms = top_ms / args.steps
+    achieved = b_alg / (top_avg_ms * 1e-3) / 1e9 if top_avg_ms > 0 else 0.0
+    impl_b = implementation_bytes(top, kernels[top], frames, N, T, C, A, A_out, S_out, grid_states)
+    # dram read + write of one launch from the ncu capture of this workload (profiles/)
     traffic = None
     if w.name == "ctc_large" and args.scale == 1.0:
-        traffic = {"GridChainLanes": 928.2e6, "RegisterViterbi": 282.4e6,
-                   "ProbScoresStaged": 96.4e6}.get(phase_kernel[top])
+        traffic = NCU_TRAFFIC.get(kernels[top])
+    if den is not None:
+        den["path_gbs"] = den["algorithmic_bytes_per_step"] * args.steps / (d_ms * 1e-3) / 1e9
+        den["path_frac_of_hbm"] = den["path_gbs"] / (hbm_peak * world)
 
     if rank != 0:
         if dist is not None:
@@ -487,45 +574,56 @@ def run_ours(args):
 
     sec = ms * 1e-3
     value = world * frames * args.steps / sec
-    e2e_value = world * frames * args.steps / (e2e_ms * 1e-3)
     line = {
         "metric": "ctc_loss_fwd_bwd_frames_per_sec", "value": value, "unit": "frames/s",
-        "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
+        "n_gpus": world, "steps": args.steps, "warmup": warm,
         "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "f32+f64", "data": "synthetic",
         "config": workload_config(w, args),
         "arc_frames_per_sec": world * arc_frames * args.steps / sec,
+        # whole path: algorithmic bytes of a step over the step
         "path_gbs": b_alg * args.steps / sec / 1e9,
         "path_frac_of_hbm": b_alg * args.steps / sec / 1e9 / hbm_peak,
+        "algorithmic_bytes_per_step": b_alg,
+        "lattice_written": lattice_written,
         "wall_ms_per_step": 1e3 * wall / args.steps,
+        "cold_graphs_ms_per_step": None if cold_ms is None else cold_ms / args.steps,
         "phases_ms_per_step": {k: v[0] / args.steps for k, v in phases.items()},
+        "phase_kernels": {k: kernels[k] for k, v in phases.items() if v[0] > 0},
         "kernel_ms_per_step_by_rank": busy_by_rank,
         "numa": numa,
-        "lattice": {"arcs": A_out, "states": S_out, "graph_arcs": A, "arc_frames": arc_frames},
-        "roofline": {"kernel": phase_kernel[top], "bound": "hbm", "achieved": achieved,
+        "lattice": {"arcs": A_out, "states": S_out, "graph_arcs": A, "arc_frames": arc_frames,
+                    "grid_states": grid_states},
+        "roofline": {"kernel": kernels[top], "bound": "hbm", "achieved": achieved,
                      "peak": hbm_peak, "unit": "GB/s", "frac": achieved / hbm_peak,
-                     "peak_source": peak_src, "algorithmic_bytes_per_launch": phase_bytes[top],
+                     "peak_source": peak_src, "algorithmic_bytes_per_launch": b_alg,
                      "avg_launch_ms": top_avg_ms, "traffic": traffic,
+                     # what the kernel moves by its design over its time: DRAM utilisation,
+                     # not a roofline fraction
+                     "dram_utilisation": None if not impl_b or top_avg_ms <= 0 else
+                     impl_b / (top_avg_ms * 1e-3) / 1e9 / hbm_peak,
+                     "implementation_bytes_per_launch": impl_b,
                      "note": "latency-bound: a chain of T dependent frames per utterance; "
-                             "traffic is the ncu dram read+write of one launch on this "
-                             "workload (profiles/)"},
-        # algorithmic bytes of a phase over its time per step
-        "phase_gbs": {k: (phase_bytes[k] / (v[0] / args.steps * 1e-3) / 1e9 if v[0] > 0 else 0.0)
-                      for k, v in phases.items()},
-        # value: copy, compute and read-back of one step strictly after one another;
-        # pipelined_value: the same work per step with the copy of step k+1 overlapping
-        # step k (k2_b200.parallel.HostPrefetcher), as a training loop feeds the GPU
-        "e2e": {"value": e2e_value, "unit": "frames/s",
+                             "achieved = the path's algorithmic bytes per step over the "
+                             "dominant kernel's launch; traffic = ncu dram read+write of one "
+                             "launch on this workload (profiles/)"},
+        # value: the copy of step k+1 overlaps step k (k2_b200.parallel.HostPrefetcher), as
+        # a training loop feeds the GPU; serial_value: copy, compute and read-back of one
+        # step strictly after one another.  The loss (8 bytes) is read back every step;
+        # the gradient stays on the device, where the optimiser uses it.
+        "e2e": {"value": world * frames * args.steps / (e2e_ms * 1e-3), "unit": "frames/s",
                 "h2d_bytes_per_step": int(w.log_probs.numel() * 4), "d2h_bytes_per_step": 8,
                 "ms_per_step": e2e_ms / args.steps,
-                "pipelined_value": world * frames * args.steps / (e2e_pipe_ms * 1e-3),
-                "pipelined_ms_per_step": e2e_pipe_ms / args.steps},
+                "serial_value": world * frames * args.steps / (serial_ms * 1e-3),
+                "serial_ms_per_step": serial_ms / args.steps},
         "gpu_launches": int(launches),
         "clocks": clocks,
     }
+    if den is not None:
+        line["lfmmi_den"] = den
     if world == 1 and not args.no_cpu_baseline:
         impl_mod, kind = pick_cpu_impl()
-        graphs_h, scores_h, rs_h = host_inputs(w)
+        graphs_h, scores_h, rs_h = host_inputs(w, impl_mod)
         cpu_reference_step(w, graphs_h, scores_h, rs_h, impl_mod)
         single = min(cpu_reference_step(w, graphs_h, scores_h, rs_h, impl_mod)[0]
                      for _ in range(2))
@@ -543,6 +641,10 @@ def run_ours(args):
         dist.destroy_process_group()
 
 
+# ncu dram__bytes_read.sum + dram__bytes_write.sum of one launch on ctc_large (profiles/)
+NCU_TRAFFIC = {"GridChainLanes": 928.2e6, "RegisterViterbi": 282.4e6, "ProbScoresStaged": 96.4e6}
+
+
 # --------------------------------------------------------------------------- decoding
 DECODE_PARAMS = dict(search_beam=20.0, output_beam=8.0, min_active_states=30,
                      max_active_states=10000)
@@ -556,8 +658,7 @@ def run_decode(args):
     of the same batch (it is single-threaded)."""
     import numpy as np
 
-    from k2_b200 import synthetic as syn
-    w = syn.hlg_decode(seed=0, scale=args.scale)
+    w = load_synthetic().hlg_decode(seed=0, scale=args.scale)
     S = len(w.graph_row_splits2) - 1
     n, t = int(w.log_probs.shape[0]), int(w.log_probs.shape[1])
     config = {"workload": "hlg_decode (pruned)", "sequences": n, "frames_per_sequence": t,

@@ -43,7 +43,8 @@ typedef enum {
 /* Text of the last error on the calling thread. */
 const char *k2b200_last_error(void);
 /* ABI version of the library (bumped on any signature change or new entry point;
- * 3: pruned intersection, score derivatives, k2b200_upload_i32). */
+ * 3: pruned intersection, score derivatives, k2b200_upload_i32;
+ * 4: k2b200_band_*). */
 int32_t k2b200_abi_version(void);
 
 /* Benchmark bookkeeping (no counterpart in the reference's bindings; its
@@ -57,6 +58,8 @@ int32_t k2b200_abi_version(void);
  * scatter, 5 incoming-arc index, 6 DenseFsaVec construction and its backward,
  * 7 lattice-free alpha/beta recursion, 8 lattice-free gradients. */
 int64_t k2b200_kernel_launch_count(void);
+/* name of the kernel(s) that last ran under a phase ("" if none yet) */
+const char *k2b200_profile_kernel(int32_t phase);
 void k2b200_profile_enable(int32_t on);
 double k2b200_profile_read_ms(int32_t phase, int64_t *intervals);
 
@@ -428,6 +431,81 @@ int32_t k2b200_dense_loss_backward_log_probs(const k2b200_intersect_args *args, 
                                              int32_t tot_grad_stride, float *grad_a,
                                              float *grad_log_probs, const int32_t *log_prob_row,
                                              int32_t num_classes, void *stream);
+
+/* ---------------------------------------------------------------------------
+ * Lattice-free total scores for BAND graphs: the same chain as above,
+ *   k2::IntersectDense (k2/csrc/intersect_dense.cu:100-1073) ->
+ *   k2::GetForwardScores / GetBackwardScores / GetTotScores
+ *   (k2/csrc/fsa_utils.cu:1124-1454, :1809-1837) -> k2::GetArcPost (:1839-1901) ->
+ *   index_add through both arc maps (k2/python/k2/autograd.py:30-117, :511-664),
+ * specialised for graphs of the shape k2::CtcGraphs builds (k2/csrc/fsa_algo.cu:577-730):
+ * every arc goes from a state s to s, s+1 or s+2, there is at most one arc per (source,
+ * destination), and all arcs entering a state carry the same label.  The same states and
+ * arcs survive pruning as in the lattice (same fp32 tests, same beam reduction against
+ * max_states / max_arcs); sums run in float64 mantissa/exponent arithmetic, so any score
+ * range is handled.  The dense scores are read from the log-prob matrix the DenseFsaVec was
+ * made from (k2/python/k2/dense_fsa_vec.py:43-145), not from its [rows, C+1] score matrix:
+ * log_probs is [log_prob_rows, num_classes] contiguous float32, 16-byte aligned, with
+ * num_classes a multiple of 4, and graph i reads rows h_first_row[i] .. + h_frames[i] - 1;
+ * the extra final row of a sequence is implied.
+ *
+ *   k2b200_band_tables: per-state tables of a_fsas (band_states: tables_bytes' first size,
+ *     band_arcs: its second) and *status (device int32) bit 0 = some graph is not a band
+ *     graph, in which case the tables must not be used.  They depend on the graphs only and
+ *     can be kept for as long as the arcs do not change.
+ *   k2b200_band_loss_supported: *supported = 0 when the sizes do not fit (more than 512
+ *     states in a graph, unaligned rows, frames beyond shared memory);
+ *     k2b200_last_error() says which.  Host-side only.
+ *   k2b200_band_loss_forward: tot_scores[num_fsas] (device, float64; -inf for a graph
+ *     with no surviving path; NaN if a copy into shared memory timed out, see
+ *     k2b200_band_loss_status).  The workspace keeps what the backward needs.
+ *   k2b200_band_loss_backward: with tot_grad[i * tot_grad_stride] = dL/dtot[i] (device,
+ *     float64), ADDS dL/d(dense score) to grad_b[(grad_row0[i] + frame) * grad_pitch +
+ *     label + grad_col_off] (grad_row0: device, one per graph).  grad_col_off = 0,
+ *     grad_pitch = num_classes, grad_row0 = h_first_row gives the log-prob layout;
+ *     grad_col_off = 1, grad_pitch = num_classes + 1 and grad_row0 = first row of the
+ *     sequence the layout of the DenseFsaVec score matrix (including column 0 of the final
+ *     rows).  grad_a (may be NULL: not wanted) receives dL/d(arc score), added.
+ *   k2b200_band_loss_status: waits for `stream` and returns the status word of the last
+ *     forward call on this workspace: bit 1 = a bounded wait for a row copy gave up (the
+ *     results are invalid; nothing hangs or traps).
+ *   k2b200_debug_set_copy_wait_limit: polls of an mbarrier before such a wait gives up
+ *     (default 4 000 000; 0 makes every wait give up at once - for tests of that path;
+ *     negative restores the default).
+ * ------------------------------------------------------------------------- */
+typedef struct {
+  int32_t num_fsas, num_states;
+  const int32_t *a_row_splits2;   /* [num_states+1] */
+  const int32_t *h_a_row_splits1; /* HOST [num_fsas+1] */
+  const int32_t *h_a_arc_splits;  /* HOST [num_fsas+1] */
+  const void *band_states;        /* from k2b200_band_tables */
+  const void *band_arcs;
+  const float *log_probs;         /* [log_prob_rows, num_classes] */
+  int64_t log_prob_rows;
+  int32_t num_classes;
+  const int32_t *h_first_row;     /* HOST [num_fsas] */
+  const int32_t *h_frames;        /* HOST [num_fsas], non-increasing */
+  float output_beam;
+  int32_t max_states, max_arcs;
+} k2b200_band_loss_args;
+
+int32_t k2b200_band_tables_bytes(int32_t num_states, size_t *states_bytes, size_t *arcs_bytes);
+int32_t k2b200_band_tables(const int32_t *row_splits1, int32_t num_fsas,
+                           const int32_t *row_splits2, const void *arcs, int32_t num_states,
+                           void *band_states, void *band_arcs, int32_t *status, void *stream);
+int32_t k2b200_band_loss_supported(const k2b200_band_loss_args *args, int32_t *supported);
+int32_t k2b200_band_loss_workspace_bytes(const k2b200_band_loss_args *args, size_t *bytes);
+int32_t k2b200_band_loss_forward(const k2b200_band_loss_args *args, void *workspace,
+                                 size_t workspace_bytes, void *stream, double *tot_scores,
+                                 float *beam_used);
+int32_t k2b200_band_loss_backward(const k2b200_band_loss_args *args, void *workspace,
+                                  size_t workspace_bytes, const double *tot_grad,
+                                  int32_t tot_grad_stride, float *grad_a, float *grad_b,
+                                  const int32_t *grad_row0, int32_t grad_pitch,
+                                  int32_t grad_col_off, void *stream);
+int32_t k2b200_band_loss_status(const k2b200_band_loss_args *args, void *workspace,
+                                size_t workspace_bytes, void *stream, int32_t *status);
+void k2b200_debug_set_copy_wait_limit(int32_t polls);
 
 /* ---------------------------------------------------------------------------
  * Forward / backward scores of a layered (top-sorted, acyclic) FsaVec.

@@ -38,6 +38,17 @@ class IntersectArgs(ctypes.Structure):
     ]
 
 
+class BandLossArgs(ctypes.Structure):
+    _fields_ = [
+        ("num_fsas", c_i32), ("num_states", c_i32),
+        ("a_row_splits2", c_vp), ("h_a_row_splits1", c_vp), ("h_a_arc_splits", c_vp),
+        ("band_states", c_vp), ("band_arcs", c_vp),
+        ("log_probs", c_vp), ("log_prob_rows", c_i64), ("num_classes", c_i32),
+        ("h_first_row", c_vp), ("h_frames", c_vp),
+        ("output_beam", c_f32), ("max_states", c_i32), ("max_arcs", c_i32),
+    ]
+
+
 class LatticeOut(ctypes.Structure):
     _fields_ = [
         ("row_splits1", c_vp), ("row_ids1", c_vp), ("row_splits2", c_vp), ("row_ids2", c_vp),
@@ -102,6 +113,7 @@ _sig("k2b200_last_error", ctypes.c_char_p, [])
 _sig("k2b200_abi_version", c_i32, [])
 _sig("k2b200_kernel_launch_count", c_i64, [])
 _sig("k2b200_profile_enable", None, [c_i32])
+_sig("k2b200_profile_kernel", ctypes.c_char_p, [c_i32])
 _sig("k2b200_profile_read_ms", ctypes.c_double, [c_i32, ctypes.POINTER(c_i64)])
 _sig("k2b200_row_splits_to_row_ids", c_i32, [c_vp, c_i32, c_vp, c_i32, c_vp])
 _sig("k2b200_upload_i32", c_i32, [c_vp, c_i64, c_vp, c_vp])
@@ -156,6 +168,20 @@ _sig("k2b200_dense_loss_forward", c_i32,
      [ctypes.POINTER(IntersectArgs), c_vp, c_sz, c_vp, c_vp, ctypes.POINTER(c_f32)])
 _sig("k2b200_dense_loss_backward", c_i32,
      [ctypes.POINTER(IntersectArgs), c_vp, c_sz, c_vp, c_i32, c_vp, c_vp, c_vp])
+_sig("k2b200_band_tables_bytes", c_i32, [c_i32, ctypes.POINTER(c_sz), ctypes.POINTER(c_sz)])
+_sig("k2b200_band_tables", c_i32, [c_vp, c_i32, c_vp, c_vp, c_i32, c_vp, c_vp, c_vp, c_vp])
+_sig("k2b200_band_loss_supported", c_i32,
+     [ctypes.POINTER(BandLossArgs), ctypes.POINTER(c_i32)])
+_sig("k2b200_band_loss_workspace_bytes", c_i32,
+     [ctypes.POINTER(BandLossArgs), ctypes.POINTER(c_sz)])
+_sig("k2b200_band_loss_forward", c_i32,
+     [ctypes.POINTER(BandLossArgs), c_vp, c_sz, c_vp, c_vp, ctypes.POINTER(c_f32)])
+_sig("k2b200_band_loss_backward", c_i32,
+     [ctypes.POINTER(BandLossArgs), c_vp, c_sz, c_vp, c_i32, c_vp, c_vp, c_vp, c_i32, c_i32,
+      c_vp])
+_sig("k2b200_band_loss_status", c_i32,
+     [ctypes.POINTER(BandLossArgs), c_vp, c_sz, c_vp, ctypes.POINTER(c_i32)])
+_sig("k2b200_debug_set_copy_wait_limit", None, [c_i32])
 _sig("k2b200_fsa_levels_tmp_bytes", c_sz, [c_i32])
 _sig("k2b200_fsa_levels", c_i32,
      [c_vp, c_vp, c_vp, c_vp, c_i32, c_i32, c_i32, c_vp, c_vp, c_vp, c_vp, c_vp])
@@ -190,7 +216,7 @@ _sig("k2b200_fsa_properties", c_i32,
 
 EXPORTED = [
     "k2b200_last_error", "k2b200_abi_version", "k2b200_kernel_launch_count",
-    "k2b200_profile_enable", "k2b200_profile_read_ms", "k2b200_row_splits_to_row_ids",
+    "k2b200_profile_enable", "k2b200_profile_kernel", "k2b200_profile_read_ms", "k2b200_row_splits_to_row_ids",
     "k2b200_upload_i32",
     "k2b200_exclusive_sum_tmp_bytes", "k2b200_exclusive_sum",
     "k2b200_exclusive_sum_static_max_len", "k2b200_exclusive_sum_static", "k2b200_fsa_incoming_tmp_bytes",
@@ -214,6 +240,10 @@ EXPORTED = [
     "k2b200_online_decode_workspace_bytes", "k2b200_online_decode_load",
     "k2b200_online_decode_run", "k2b200_online_decode_emit", "k2b200_online_decode_store",
     "k2b200_online_decode_load_all", "k2b200_online_decode_store_all",
+    "k2b200_band_tables_bytes", "k2b200_band_tables", "k2b200_band_loss_supported",
+    "k2b200_band_loss_workspace_bytes", "k2b200_band_loss_forward",
+    "k2b200_band_loss_backward", "k2b200_band_loss_status",
+    "k2b200_debug_set_copy_wait_limit",
 ]
 
 
@@ -270,15 +300,16 @@ def launch_count() -> int:
     return int(lib.k2b200_kernel_launch_count())
 
 
-def note_launches(n: int) -> None:  # kept for callers; the library counts itself
-    pass
-
-
 PHASES = ["viterbi", "prune", "emit", "scores", "post", "incoming", "dense", "chain", "grad"]
 
 
 def profile_enable(on: bool) -> None:
     lib.k2b200_profile_enable(int(on))
+
+
+def profile_kernels():
+    """{phase: name of the kernel(s) that last ran under it}."""
+    return {name: lib.k2b200_profile_kernel(k).decode() for k, name in enumerate(PHASES)}
 
 
 def profile_read():

@@ -30,7 +30,6 @@ def _index_add(index: torch.Tensor, value: torch.Tensor, in_out: torch.Tensor) -
         _lib.check(_lib.lib.k2b200_index_add(_lib.ptr(index), _lib.ptr(value), index.numel(),
                                               _lib.ptr(in_out), in_out.numel(),
                                               _lib.stream_of(in_out.device)))
-    _lib.note_launches(1)
 
 
 def index_select(src, index: torch.Tensor):
@@ -51,7 +50,6 @@ def index_select(src, index: torch.Tensor):
         _lib.check(_lib.lib.k2b200_index_select_i32(_lib.ptr(src), src.numel(), _lib.ptr(index),
                                                      index.numel(), _lib.ptr(out),
                                                      _lib.stream_of(src.device)))
-    _lib.note_launches(1)
     return out
 
 
@@ -190,7 +188,6 @@ class _GetTotScoresFunction(torch.autograd.Function):
                     _lib.ptr(rid1), _lib.ptr(rid2), na, int(use_double_scores),
                     _lib.ptr(arc_post), _lib.ptr(tot_scores_grad), stride,
                     _lib.ptr(scores_grad), _lib.stream_of(dev)))
-        _lib.note_launches(1)
         return None, None, None, scores_grad
 
 
@@ -570,12 +567,143 @@ class _DenseTotScoresFunction(torch.autograd.Function):
         return None, None, None, None, None, None, None, grad_a, grad_b
 
 
+# ---------------------------------------------------------------------------
+# Band graphs (CTC): the lattice-free loss reads the log-probs in place
+# ---------------------------------------------------------------------------
+# When True, every band-path forward is followed by a host wait and a look at the
+# status word of the kernels; a bounded wait that gave up then sends the call to the
+# general lattice-free path instead of returning NaN totals.
+BAND_VERIFY = False
+_band_state = {"status": 0}  # status word of the last verified band-path forward
+
+
+def _band_loss_args(a_fsas: Fsa, b_fsas: DenseFsaVec, a_to_b_map: Optional[torch.Tensor],
+                    output_beam: float, max_states: int, max_arcs: int):
+    """(args, keep-alive objects, host map) of the k2b200_band_loss_* entry points, or
+    None when they do not apply: `b_fsas` must come from a float32 CUDA log-prob tensor
+    with 16-byte aligned rows and the graphs must be band graphs of at most 512 states."""
+    src = b_fsas._source
+    a = a_fsas.arcs
+    if src is None or not a.values().is_cuda:
+        return None
+    lp = src[0]
+    if not (lp.is_cuda and lp.dtype == torch.float32 and lp.is_contiguous()
+            and lp.device == a.device and lp.shape[-1] % 4 == 0 and lp.data_ptr() % 16 == 0):
+        return None
+    h_map = None
+    if a_to_b_map is not None:
+        assert a_to_b_map.ndim == 1 and a_to_b_map.dtype == torch.int32
+        h_map = np.ascontiguousarray(a_to_b_map.detach().cpu().numpy(), dtype=np.int32)
+        if h_map.shape[0] != a.num_fsas:
+            raise RuntimeError(
+                f"a_fsas.Dim0() ({a.num_fsas}) != a_to_b_map.Dim() ({h_map.shape[0]})")
+        if h_map.size and (h_map.min() < 0 or h_map.max() >= b_fsas.dim0()
+                           or np.any(np.diff(h_map) < 0)):
+            return None  # the general path reports the error
+    elif a.num_fsas != b_fsas.dim0():
+        return None
+    h_rs1 = np.ascontiguousarray(a.h_row_splits1, dtype=np.int32)
+    if int(np.diff(h_rs1).max(initial=0)) > 512:
+        return None
+    states, arcs, ok = a.band_tables()
+    if not ok:
+        return None
+    frames = np.diff(b_fsas.h_row_splits) - 1
+    first = src[1]
+    if h_map is not None:
+        frames, first = frames[h_map], first[h_map]
+    frames = np.ascontiguousarray(frames, dtype=np.int32)
+    first = np.ascontiguousarray(first, dtype=np.int32)
+    h_as = np.ascontiguousarray(a.h_arc_splits, dtype=np.int32)
+    args = _lib.BandLossArgs(
+        num_fsas=a.num_fsas, num_states=a.num_states, a_row_splits2=_lib.ptr(a._row_splits2),
+        h_a_row_splits1=h_rs1.ctypes.data, h_a_arc_splits=h_as.ctypes.data,
+        band_states=_lib.ptr(states), band_arcs=_lib.ptr(arcs), log_probs=_lib.ptr(lp),
+        log_prob_rows=lp.numel() // lp.shape[-1], num_classes=lp.shape[-1],
+        h_first_row=first.ctypes.data, h_frames=frames.ctypes.data,
+        output_beam=float(output_beam), max_states=int(min(max_states, 2**31 - 1)),
+        max_arcs=int(min(max_arcs, 2**31 - 1)))
+    ok = ctypes.c_int32()
+    _lib.check(_lib.lib.k2b200_band_loss_supported(ctypes.byref(args), ctypes.byref(ok)))
+    if not ok.value:
+        return None
+    return args, (h_rs1, h_as, frames, first, states, arcs, lp, a), h_map
+
+
+class _BandTotScoresFunction(torch.autograd.Function):
+    """`_DenseTotScoresFunction` for band graphs (`k2b200_band_loss_*`): same values,
+    the dense scores read straight from the log-prob tensor."""
+
+    @staticmethod
+    def forward(ctx, a_fsas: Fsa, b_fsas: DenseFsaVec, band, use_double_scores: bool,
+                unused_scores_a: torch.Tensor, unused_scores_b: torch.Tensor) -> torch.Tensor:
+        args, keep, h_map = band
+        dev = a_fsas.arcs.device
+        nbytes = ctypes.c_size_t()
+        _lib.check(_lib.lib.k2b200_band_loss_workspace_bytes(ctypes.byref(args),
+                                                              ctypes.byref(nbytes)))
+        ws = torch.empty(nbytes.value, dtype=torch.uint8, device=dev)
+        tot = torch.empty(a_fsas.arcs.num_fsas, dtype=torch.float64, device=dev)
+        beam = ctypes.c_float()
+        with torch.cuda.device(dev):
+            _lib.check(_lib.lib.k2b200_band_loss_forward(
+                ctypes.byref(args), _lib.ptr(ws), nbytes.value, _lib.stream_of(dev),
+                _lib.ptr(tot), ctypes.byref(beam)))
+            _band_state["status"] = 0
+            if BAND_VERIFY:
+                status = ctypes.c_int32()
+                _lib.check(_lib.lib.k2b200_band_loss_status(
+                    ctypes.byref(args), _lib.ptr(ws), nbytes.value, _lib.stream_of(dev),
+                    ctypes.byref(status)))
+                _band_state["status"] = status.value
+        ctx.args, ctx.keep, ctx.ws, ctx.ws_bytes, ctx.dev = args, keep, ws, nbytes.value, dev
+        ctx.shape_a, ctx.shape_b = unused_scores_a.shape, unused_scores_b.shape
+        src = b_fsas._source
+        key = None if h_map is None else tuple(h_map.tolist())
+        if unused_scores_b is src[0]:  # gradient in the layout of the log-probs
+            if key not in b_fsas._source_rows:
+                b_fsas._source_rows[key] = _lib.upload_i32(keep[3], dev)
+            ctx.grad_rows = b_fsas._source_rows[key]
+            ctx.grad_pitch, ctx.grad_col_off = int(args.num_classes), 0
+        else:                          # in the layout of the score matrix
+            rows = b_fsas.h_row_splits[:-1] if h_map is None else b_fsas.h_row_splits[h_map]
+            ctx.grad_rows = _lib.upload_i32(rows, dev)
+            ctx.grad_pitch, ctx.grad_col_off = int(args.num_classes) + 1, 1
+        ctx.output_beam_used = beam.value
+        return tot if use_double_scores else tot.to(torch.float32)
+
+    @staticmethod
+    def backward(ctx, tot_grad: torch.Tensor):
+        dev = ctx.dev
+        if tot_grad.dtype != torch.float64:
+            tot_grad = tot_grad.to(torch.float64)
+        stride = tot_grad.stride(0) if tot_grad.numel() > 0 else 0
+        grad_a = None
+        if ctx.needs_input_grad[4]:
+            grad_a = torch.zeros(ctx.shape_a, dtype=torch.float32, device=dev)
+        grad_b = torch.zeros(ctx.shape_b, dtype=torch.float32, device=dev)
+        with torch.cuda.device(dev):
+            _lib.check(_lib.lib.k2b200_band_loss_backward(
+                ctypes.byref(ctx.args), _lib.ptr(ctx.ws), ctx.ws_bytes, _lib.ptr(tot_grad),
+                stride, _lib.ptr(grad_a), _lib.ptr(grad_b), _lib.ptr(ctx.grad_rows),
+                ctx.grad_pitch, ctx.grad_col_off, _lib.stream_of(dev)))
+        return None, None, None, None, grad_a, grad_b
+
+
+def band_loss_supported(a_fsas: Fsa, b_fsas: DenseFsaVec,
+                        a_to_b_map: Optional[torch.Tensor] = None) -> bool:
+    """Can `intersect_dense_tot_scores` take the band-graph kernels for these inputs?"""
+    return _band_loss_args(a_fsas, b_fsas, a_to_b_map, 1.0, 1, 1) is not None
+
+
 def dense_loss_supported(a_fsas: Fsa, b_fsas: DenseFsaVec,
                          a_to_b_map: Optional[torch.Tensor] = None) -> bool:
     """Can `intersect_dense_tot_scores` handle these inputs (CUDA tensors, graphs
     small enough for the shared-memory recursion)?"""
-    if not (a_fsas.arcs.values().is_cuda and b_fsas.scores.is_cuda):
+    if not (a_fsas.arcs.values().is_cuda and b_fsas.device.type == "cuda"):
         return False
+    if band_loss_supported(a_fsas, b_fsas, a_to_b_map):
+        return True
     args, _keep, _, _ = _make_intersect_args(a_fsas.arcs, b_fsas, a_to_b_map, 1.0, 1, 1)
     ok = ctypes.c_int32()
     _lib.check(_lib.lib.k2b200_dense_loss_supported(ctypes.byref(args), ctypes.byref(ok)))
@@ -585,17 +713,30 @@ def dense_loss_supported(a_fsas: Fsa, b_fsas: DenseFsaVec,
 def intersect_dense_tot_scores(a_fsas: Fsa, b_fsas: DenseFsaVec, output_beam: float,
                                max_states: int = 15000000, max_arcs: int = 1073741824,
                                a_to_b_map: Optional[torch.Tensor] = None,
-                               use_double_scores: bool = True) -> torch.Tensor:
+                               use_double_scores: bool = True,
+                               band: bool = True) -> torch.Tensor:
     """`intersect_dense(a_fsas, b_fsas, output_beam, ...).get_tot_scores(
     log_semiring=True, use_double_scores=...)` in one step (the composition
     k2/python/k2/ctc_loss.py:86-140 makes), differentiable w.r.t. `a_fsas.scores`
     and `b_fsas.scores`.  The lattice is not built.  When `b_fsas` was made from a
     log-prob tensor that takes part in autograd, the gradient goes to that tensor
-    directly rather than through the score matrix and the adjoint of its layout."""
-    scores_b = b_fsas.scores
+    directly rather than through the score matrix and the adjoint of its layout.
+    Band graphs (CTC) take kernels of their own that read the log-probs in place
+    (`band=False` keeps them on the general kernels)."""
     src = b_fsas._source
-    if src is not None and src[0].requires_grad and src[0].dtype == torch.float32:
-        scores_b = src[0]
+    from_log_probs = src is not None and src[0].requires_grad and src[0].dtype == torch.float32
+    args = _band_loss_args(a_fsas, b_fsas, a_to_b_map, output_beam, max_states,
+                           max_arcs) if band else None
+    if args is not None:
+        # without autograd on the log-probs the gradient (if any) is that of the score
+        # matrix, which then exists anyway
+        scores_b = src[0] if (from_log_probs or b_fsas._scores is None) else b_fsas.scores
+        tot = _BandTotScoresFunction.apply(a_fsas, b_fsas, args, use_double_scores,
+                                           a_fsas.scores, scores_b)
+        if not (BAND_VERIFY and _band_state["status"] & 2):
+            return tot
+        # a bounded wait of the band kernels gave up: the general kernels take the call
+    scores_b = src[0] if from_log_probs else b_fsas.scores
     return _DenseTotScoresFunction.apply(a_fsas, b_fsas, output_beam, max_states, max_arcs,
                                          use_double_scores, a_to_b_map, a_fsas.scores,
                                          scores_b)

@@ -59,6 +59,9 @@ void NoteLaunch(int n = 1);
 enum Phase : int { kPhaseViterbi = 0, kPhasePrune, kPhaseEmit, kPhaseScores, kPhasePost,
                    kPhaseIncoming, kPhaseDense, kPhaseChain, kPhaseGrad, kNumPhases };
 long long LaunchCount();
+// Name of the kernel(s) that last ran under a phase, for whoever reads the phase times.
+void NotePhaseKernel(int phase, const char *name);
+const char *PhaseKernel(int phase);
 void SetProfiling(bool on);
 double ReadPhase(int phase, long long *count);
 struct PhaseTimer {  // records start/stop events when profiling is enabled

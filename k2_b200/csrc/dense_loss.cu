@@ -1756,6 +1756,7 @@ int32_t k2b200_dense_loss_forward(const k2b200_intersect_args *args, void *works
     if (need_count) {
       K2B_FORWARD(SideFork(stream, &side));  // behind the cutoffs
       PhaseTimer timer(kPhasePrune, side);
+      NotePhaseKernel(kPhasePrune, "CountStates");
       K2B_FORWARD(LaunchSizeCount(L, args, ws, side));
     }
     {
@@ -1764,6 +1765,7 @@ int32_t k2b200_dense_loss_forward(const k2b200_intersect_args *args, void *works
   (ls.stages == kChainGroup                                                               \
        ? LaunchChainLanes<DEG, MAXT, kChainGroup>(LL, args, ws, ls, tot_scores, stream)   \
        : LaunchChainLanes<DEG, MAXT, kChainGroupSmall>(LL, args, ws, ls, tot_scores, stream))
+      NotePhaseKernel(kPhaseChain, LL.identity ? "GridChainLanes" : "ArcMasks+GridChainMasked");
       if (LL.k_deg == 3 && LL.threads <= 512) K2B_FORWARD(K2B_CHAIN(3, 512));
       else if (LL.k_deg == 3) K2B_FORWARD(K2B_CHAIN(3, 1024));
       else if (LL.k_deg == 4 && LL.threads <= 512) K2B_FORWARD(K2B_CHAIN(4, 512));
@@ -1820,6 +1822,9 @@ static int32_t DenseLossBackward(const k2b200_intersect_args *args, void *worksp
         reinterpret_cast<const Arc *>(args->a_arcs), args->num_arcs,
         reinterpret_cast<ArcFactor *>(ws + LL.off_arc_factors)); NoteLaunch(); }
   const int32_t *only_noplan = nullptr;
+  NotePhaseKernel(kPhaseGrad, !LL.identity ? "GridGradLanes"
+                              : (L.max_states > 256 && L.max_states <= 1024) ? "GridGradItems"
+                                                                             : "GridGradWarp");
   if (!LL.identity) {
     K2B_FORWARD(LaunchGradLanes(LL, args, ws, tot_grad, tot_grad_stride, grad_a, grad_b, stream));
     only_noplan = reinterpret_cast<const int32_t *>(ws + L.off_unfit);

@@ -514,12 +514,14 @@ int32_t RunViterbi(const Layout &L, const k2b200_intersect_args *a, char *ws, cu
   if (mode == 3) {
     K2B_REQUIRE(RegisterViterbiFits(L, a),
                 "viterbi_mode=3 needs a_max_degree <= 4 and at most 1024 states per graph");
+    NotePhaseKernel(kPhaseViterbi, "RegisterViterbi");
     return LaunchRegisterViterbi(L, a, d_infos, fwd, bwd, stream);
   }
   if (mode == 4) {
     K2B_REQUIRE(L.lane_plan, "viterbi_mode=4 needs graphs of at most %d states that fit in "
                 "shared memory, with some state of more than four arcs", kLaneThreads);
     if (!plan_ready) K2B_FORWARD(LaunchPlanLanes(L, a, ws, stream));
+    NotePhaseKernel(kPhaseViterbi, "LanesViterbi");
     const int32_t *unfit = reinterpret_cast<const int32_t *>(ws + L.off_unfit);
     K2B_FORWARD(LaunchLanesViterbi(L, a, d_infos, fwd, bwd,
                                    reinterpret_cast<const int32_t *>(ws + L.off_plan), unfit,
@@ -529,9 +531,11 @@ int32_t RunViterbi(const Layout &L, const k2b200_intersect_args *a, char *ws, cu
   if (mode == 2) {
     K2B_REQUIRE(PersistentViterbiFits(L, a),
                 "viterbi_mode=2 requested but a graph does not fit in shared memory");
+    NotePhaseKernel(kPhaseViterbi, "PersistentViterbi");
     return LaunchPersistentViterbi(L, a, d_infos, fwd, bwd, stream);
   }
   const Arc *arcs = reinterpret_cast<const Arc *>(a->a_arcs);
+  NotePhaseKernel(kPhaseViterbi, "ViterbiStep");
   dim3 init_grid(CeilDiv(L.max_states, 256), a->num_fsas);
   { ViterbiInit<<<init_grid, 256, 0, stream>>>(d_infos, fwd, bwd); NoteLaunch(); }
   // lanes per state from the mean degree of the batch

@@ -32,6 +32,14 @@ static std::atomic<long long> g_launches{0};
 void NoteLaunch(int n) { g_launches.fetch_add(n, std::memory_order_relaxed); }
 long long LaunchCount() { return g_launches.load(std::memory_order_relaxed); }
 
+static const char *g_phase_kernel[kNumPhases] = {};
+void NotePhaseKernel(int phase, const char *name) {
+  if (phase >= 0 && phase < kNumPhases) g_phase_kernel[phase] = name;
+}
+const char *PhaseKernel(int phase) {
+  return (phase >= 0 && phase < kNumPhases && g_phase_kernel[phase]) ? g_phase_kernel[phase] : "";
+}
+
 namespace {
 struct EventPair { cudaEvent_t start, stop; };
 struct PhaseLog {

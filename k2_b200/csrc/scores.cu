@@ -237,9 +237,10 @@ static int32_t LaunchScores(const k2b200_fsa_view *v, int32_t log_semiring, Real
 extern "C" {
 
 const char *k2b200_last_error(void) { return LastError(); }
-int32_t k2b200_abi_version(void) { return 3; }
+int32_t k2b200_abi_version(void) { return 4; }
 int64_t k2b200_kernel_launch_count(void) { return LaunchCount(); }
 void k2b200_profile_enable(int32_t on) { SetProfiling(on != 0); }
+const char *k2b200_profile_kernel(int32_t phase) { return PhaseKernel(phase); }
 double k2b200_profile_read_ms(int32_t phase, int64_t *intervals) {
   long long n = 0;
   double ms = (phase >= 0 && phase < kNumPhases) ? ReadPhase(phase, &n) : 0.0;

@@ -4,7 +4,8 @@ from typing import Optional
 import torch
 import torch.nn as nn
 
-from .autograd import dense_loss_supported, intersect_dense, intersect_dense_tot_scores
+from .autograd import (band_loss_supported, dense_loss_supported, intersect_dense,
+                       intersect_dense_tot_scores)
 from .dense_fsa_vec import DenseFsaVec
 from .fsa import Fsa
 
@@ -13,9 +14,9 @@ from .fsa import Fsa
 # are computed without building it when the graphs allow; set to False to force
 # the reference's intersect_dense + get_tot_scores sequence.
 FUSED_LOSS = True
-# The lattice-free path exponentiates every element of the dense matrix and streams
-# whole rows through shared memory; with very many classes, of which a graph uses
-# few, building the (small) lattice is cheaper.
+# Outside the band-graph kernels (CTC graphs), the lattice-free path exponentiates
+# every element of the dense matrix and streams whole rows through shared memory; with
+# very many classes, of which a graph uses few, building the (small) lattice is cheaper.
 FUSED_MAX_CLASSES = 2048
 
 
@@ -34,9 +35,10 @@ class CtcLoss(nn.Module):
     def forward(self, decoding_graph: Fsa, dense_fsa_vec: DenseFsaVec,
                 delay_penalty: float = 0.0,
                 target_lengths: Optional[torch.Tensor] = None) -> torch.Tensor:
-        if (FUSED_LOSS and delay_penalty <= 0.0
-                and dense_fsa_vec.scores.shape[1] <= FUSED_MAX_CLASSES
-                and dense_loss_supported(decoding_graph, dense_fsa_vec)):
+        if FUSED_LOSS and delay_penalty <= 0.0 and (
+                band_loss_supported(decoding_graph, dense_fsa_vec)
+                or (dense_fsa_vec.num_cols <= FUSED_MAX_CLASSES
+                    and dense_loss_supported(decoding_graph, dense_fsa_vec))):
             tot_scores = intersect_dense_tot_scores(
                 decoding_graph, dense_fsa_vec, self.output_beam,
                 use_double_scores=self.use_double_scores)

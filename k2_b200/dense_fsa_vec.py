@@ -117,11 +117,15 @@ class DenseFsaVec(object):
             meta = _lib.upload_i32(np.concatenate([eff.reshape(-1), row_splits]), device)
             k3 = 3 * seg.shape[0]
             fn = _LogSoftmaxDenseFunction if _logits else _DenseFsaVecFunction
-            scores = fn.apply(log_probs, meta[:k3].view(-1, 3), meta[k3:], rows, overlapping)
-            self._init(scores, row_splits, meta[k3:])
+            # The score matrix is laid out on first use: a loss that reads the
+            # log-probs directly (k2b200_band_loss_*) never needs it.
+            self._init(None, row_splits, meta[k3:], device=device, num_cols=C + 1)
+            self._make_scores = lambda: fn.apply(log_probs, meta[:k3].view(-1, 3), meta[k3:],
+                                                 rows, overlapping)
             if not _logits and not overlapping:
-                # what a loss needs to send its gradient straight to `log_probs`
-                # (k2b200_dense_loss_backward_log_probs): the tensor and, per
+                # what a loss needs to read `log_probs` in place and to send its
+                # gradient straight to it (k2b200_band_loss_*,
+                # k2b200_dense_loss_backward_log_probs): the tensor and, per
                 # sequence, the row of its first frame
                 self._source = (log_probs, first.astype(np.int32))
             return
@@ -153,19 +157,43 @@ class DenseFsaVec(object):
         return cls(logits, supervision_segments, allow_truncate, _logits=True)
 
     def _init(self, scores: torch.Tensor, h_row_splits: np.ndarray,
-              d_row_splits: torch.Tensor = None) -> None:
-        assert scores.is_contiguous()
+              d_row_splits: torch.Tensor = None, device=None, num_cols: int = 0) -> None:
+        assert scores is None or scores.is_contiguous()
         self._source = None
         self._source_rows = {}
-        self.scores = scores  # for back propagation
+        self._make_scores = None
+        self._scores = scores  # for back propagation
+        self._device = scores.device if scores is not None else torch.device(device)
+        self._num_cols = scores.shape[1] if scores is not None else num_cols
         self.h_row_splits = np.ascontiguousarray(h_row_splits, dtype=np.int32)
         if d_row_splits is not None:
             self.row_splits = d_row_splits
-        elif scores.is_cuda:
-            self.row_splits = _lib.upload_i32(self.h_row_splits, scores.device)
+        elif self._device.type == "cuda":
+            self.row_splits = _lib.upload_i32(self.h_row_splits, self._device)
         else:
             self.row_splits = torch.from_numpy(self.h_row_splits)
         self._duration = torch.from_numpy(np.diff(self.h_row_splits) - 1)
+
+    @property
+    def scores(self) -> torch.Tensor:
+        """The [sum_i (T_i + 1), C + 1] score matrix (k2/csrc/fsa.h:138-185)."""
+        if self._scores is None:
+            self._scores = self._make_scores()
+            self._make_scores = None
+        return self._scores
+
+    @scores.setter
+    def scores(self, value: torch.Tensor) -> None:
+        assert value.is_contiguous()
+        self._scores = value
+        self._make_scores = None
+        self._source = None  # no longer the layout of the tensor it was made from
+        self._source_rows = {}
+
+    @property
+    def num_cols(self) -> int:
+        """Columns of the score matrix: classes + 1."""
+        return self._num_cols
 
     @classmethod
     def _from_dense_fsa_vec(cls, scores: torch.Tensor, h_row_splits) -> 'DenseFsaVec':
@@ -186,14 +214,14 @@ class DenseFsaVec(object):
 
     @property
     def device(self) -> torch.device:
-        return self.scores.device
+        return self._device
 
     def to(self, device) -> 'DenseFsaVec':
         device = torch.device(device)
-        if device == self.scores.device:
+        if device == self._device:
             return self
         return DenseFsaVec._from_dense_fsa_vec(self.scores.to(device), self.h_row_splits)
 
     def __str__(self) -> str:
         return (f"k2_b200.DenseFsaVec(num_seqs={self.dim0()}, "
-                f"scores={tuple(self.scores.shape)}, device={self.device})")
+                f"scores=({int(self.h_row_splits[-1])}, {self._num_cols}), device={self.device})")

@@ -284,7 +284,6 @@ class Fsa(object):
                 _lib.check(_lib.lib.k2b200_fsa_tot_scores(
                     _lib.ptr(arcs._row_splits1), arcs.num_fsas, int(use_double_scores),
                     _lib.ptr(fwd), _lib.ptr(tot), _lib.stream_of(fwd.device)))
-            _lib.note_launches(1)
             self._cache[key] = tot
         return self._cache[key]
 
@@ -301,7 +300,6 @@ class Fsa(object):
                     _lib.ptr(arcs.row_ids(2 - arcs.single)), _lib.ptr(arcs.values()),
                     arcs.num_fsas, arcs.num_elements(), int(use_double_scores), _lib.ptr(fwd),
                     _lib.ptr(bwd), _lib.ptr(post), _lib.stream_of(fwd.device)))
-            _lib.note_launches(1)
             self._cache[key] = post
         return self._cache[key]
 

@@ -135,6 +135,8 @@ def _ctc_graph_cuda(lens: np.ndarray, sym: np.ndarray, modified: bool, device) -
             _lib.stream_of(device)))
     arcs = RaggedArc(values, rs1, rs2, h_row_splits1=h_rs1.astype(np.int32),
                      h_arc_splits=h_arc_splits.astype(np.int32))
+    # CTC graphs are band graphs (RaggedArc.band_tables) for as long as nobody edits them
+    arcs._band_by_construction = (values.data_ptr(), values._version)
     # valid, non-empty, not top-sorted (self-loops), epsilon arcs present (blank = 0),
     # accessible and co-accessible by construction: the bits the host path computes
     return Fsa(arcs, aux_labels=aux, _check=False)
@@ -235,7 +237,6 @@ def _shortest_path_arcs(fsa: Fsa, use_double_scores: bool) -> Tuple[torch.Tensor
         _lib.check(_lib.lib.k2b200_shortest_path(
             _lib.ptr(arcs._row_splits1), _lib.ptr(arcs.values()), _lib.ptr(entering), nf,
             _lib.ptr(path_splits), _lib.ptr(best), _lib.ptr(tmp), _lib.stream_of(dev)))
-    _lib.note_launches(5)
     total = int(path_splits[nf].item())
     return path_splits, best[:total]
 

@@ -37,6 +37,7 @@ class RaggedArc:
         self._h_arc_splits = h_arc_splits
         # lazily built device-side helpers
         self._incoming = None  # (in_splits, in_arcs, in_src, in_score)
+        self._incoming_key = None
         self._levels = None    # (level_offsets, level_splits) of a layered FsaVec
         # (strict, max_layers, max_layer_states, max_layer_arcs): set for lattices
         # whose arcs all go from one layer to the next, with bounds on layer sizes
@@ -132,7 +133,8 @@ class RaggedArc:
         Cached; the reference recomputes the index on every intersect_dense call
         (k2/csrc/intersect_dense.cu:139-142).  The cache is dropped when the
         scores or labels of the owning Fsa are re-assigned."""
-        if self._incoming is None:
+        key = (self._values.data_ptr(), self._values._version)
+        if self._incoming is None or self._incoming_key != key:
             _lib.require_cuda(self._values, "arcs")
             ns, na = self.num_states, self.num_elements()
             dev = self.device
@@ -148,7 +150,42 @@ class RaggedArc:
                     buf[1].data_ptr(), buf[2].data_ptr(), _lib.ptr(tmp), _lib.stream_of(dev)))
             self._incoming = (in_splits, buf[0, :na], buf[1, :na],
                               buf[2, :na].view(torch.float32))
+            self._incoming_key = key
         return self._incoming
+
+    def band_tables(self):
+        """(band_states, band_arcs, ok): the per-state tables of k2b200_band_tables
+        for this FsaVec, and whether every graph is a band graph (arcs from a state s
+        to s, s+1 or s+2 only, one arc per (source, destination), one label per
+        destination) - the shape of CTC graphs.  Cached per version of the arc
+        tensor.  Graphs that `ctc_graph` wrote are band graphs by construction; for
+        any other FsaVec the answer costs one host read, once."""
+        vals = self._values
+        key = (vals.data_ptr(), vals._version)
+        cached = getattr(self, "_band", None)
+        if cached is not None and cached[0] == key:
+            return cached[1]
+        _lib.require_cuda(vals, "arcs")
+        dev = self.device
+        ns = self.num_states
+        sb, ab = _lib.c_sz(), _lib.c_sz()
+        import ctypes
+        _lib.check(_lib.lib.k2b200_band_tables_bytes(ns, ctypes.byref(sb), ctypes.byref(ab)))
+        states = torch.empty(sb.value, dtype=torch.uint8, device=dev)
+        arcs = torch.empty(ab.value, dtype=torch.uint8, device=dev)
+        status = torch.empty(1, dtype=torch.int32, device=dev)
+        with torch.cuda.device(dev):
+            _lib.check(_lib.lib.k2b200_band_tables(
+                _lib.ptr(self._row_splits1), self.num_fsas, _lib.ptr(self._row_splits2),
+                _lib.ptr(vals), ns, _lib.ptr(states), _lib.ptr(arcs), _lib.ptr(status),
+                _lib.stream_of(dev)))
+        if getattr(self, "_band_by_construction", None) == key:
+            ok = True
+        else:
+            ok = (int(status.item()) & 1) == 0
+        ans = (states, arcs, ok)
+        self._band = (key, ans)
+        return ans
 
     def replicated(self, min_bytes: int = 32 << 20) -> bool:
         """Is every FSA of this FsaVec an exact copy of FSA 0 (states, arcs and
@@ -251,7 +288,6 @@ def _gpu_levels(arcs: RaggedArc):
             _lib.ptr(arcs._row_splits1), _lib.ptr(arcs._row_splits2), _lib.ptr(rid2),
             _lib.ptr(arcs._values), nf, ns, na, _lib.ptr(offsets), _lib.ptr(splits),
             _lib.ptr(status), _lib.ptr(tmp), _lib.stream_of(dev)))
-    _lib.note_launches(4)
     total, bad = (int(v) for v in offsets[nf:].tolist())
     if bad:
         raise RuntimeError("forward/backward scores need a top-sorted, acyclic FsaVec")

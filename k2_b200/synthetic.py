@@ -29,6 +29,8 @@ class Workload:
     # explicit graph (one FSA, shared by every utterance): row_splits2, arcs [A,4]
     graph_row_splits2: Optional[np.ndarray] = None
     graph_arcs: Optional[np.ndarray] = None
+    # LF-MMI: per-utterance transcripts of the numerator graphs (CTC graphs over phones)
+    num_symbols: Optional[List[List[int]]] = None
     meta: Dict = field(default_factory=dict)
 
     @property
@@ -147,7 +149,12 @@ def lfmmi_den(seed: int = 0, scale: float = 1.0, utterances: Optional[int] = Non
     log_probs = _log_probs(gen, n, t, 72, 1.0)
     seg = _segments(np.full(n, t, dtype=np.int64))
     rs2, arcs = den_graph(seed)
+    # numerator graphs: CTC graphs of random phone strings of 40..100 phones (tokens 1..71),
+    # drawn after the log-probs so that those keep their bytes
+    lens = torch.randint(max(1, int(40 * scale)), max(2, int(100 * scale)) + 1, (n,), generator=gen)
+    num_symbols = [torch.randint(1, 72, (int(l),), generator=gen).tolist() for l in lens]
     return Workload("lfmmi_den", log_probs, seg, 8.0, graph_row_splits2=rs2, graph_arcs=arcs,
+                    num_symbols=num_symbols,
                     meta=dict(N=n, T=t, C=72, graph_states=len(rs2) - 1, graph_arcs=len(arcs)))
 
 
@@ -190,6 +197,39 @@ def hlg_decode(seed: int = 0, scale: float = 1.0, num_states: Optional[int] = No
     rs2, arcs = decoding_graph(seed, num_states, 500)
     return Workload("hlg_decode", log_probs, seg, 8.0, graph_row_splits2=rs2, graph_arcs=arcs,
                     meta=dict(N=n, T=t, C=500, graph_states=len(rs2) - 1, graph_arcs=len(arcs)))
+
+
+def num_den_graphs(w: Workload):
+    """Host arrays of the LF-MMI graph pair set of a workload: for every utterance its
+    numerator graph (the CTC graph of its phone string) followed by the shared
+    denominator graph - 2N graphs [num_0, den_0, num_1, den_1, ...] that go with
+    a_to_b_map = [0, 0, 1, 1, ...], both graphs of an utterance reading the same rows of
+    the dense scores (k2/csrc/intersect_dense.cu:80-92).  Returns (row_splits1,
+    row_splits2, arcs [A, 4], a_to_b_map)."""
+    assert w.num_symbols is not None and w.graph_arcs is not None
+    n = w.supervision_segments.shape[0]
+    den_rs2 = np.asarray(w.graph_row_splits2, dtype=np.int64)
+    den_arcs = np.asarray(w.graph_arcs, dtype=np.int32)
+    rs1, rs2, arcs = [0], [0], []
+
+    def append(g_rs2, g_arcs):
+        rs2.extend((g_rs2[1:] + rs2[-1]).tolist())
+        arcs.append(g_arcs)
+        rs1.append(rs1[-1] + len(g_rs2) - 1)
+
+    from .fsa_algo import ctc_graph
+    num = ctc_graph(w.num_symbols, modified=False, device="cpu").arcs
+    n_rs1 = np.asarray(num.h_row_splits1, dtype=np.int64)
+    n_rs2 = num.row_splits(2).numpy().astype(np.int64)
+    n_arcs = num.values().numpy()
+    for i in range(n):
+        s0, s1 = int(n_rs1[i]), int(n_rs1[i + 1])
+        a0, a1 = int(n_rs2[s0]), int(n_rs2[s1])
+        append(n_rs2[s0:s1 + 1] - a0, n_arcs[a0:a1])
+        append(den_rs2, den_arcs)
+    a_to_b_map = np.repeat(np.arange(n, dtype=np.int32), 2)
+    return (np.asarray(rs1, dtype=np.int32), np.asarray(rs2, dtype=np.int32),
+            np.concatenate(arcs), a_to_b_map)
 
 
 WORKLOADS = {
