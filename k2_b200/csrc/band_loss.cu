@@ -11,20 +11,23 @@
 // has neighbours only, and the states that survive pruning on a frame are few (a few tens out of
 // hundreds).  The kernels are built on that:
 //
-//   BandViterbi   one WARP per (graph, direction) walks all frames: a lane owns K consecutive
-//                 states in registers, neighbours come by two shuffles, the log-prob row of the
-//                 frame arrives in a shared-memory ring by one bulk copy (TMA, mbarrier) issued
-//                 many frames ahead.  No block barrier, no shared-memory traffic for scores.
+//   BandViterbi   one small CTA per (graph, direction) walks all frames: a thread owns four
+//                 consecutive states in registers, neighbours come by two shuffles (and a
+//                 two-float hand-over between warps), the log-prob row of the frame arrives in a
+//                 shared-memory ring by one bulk copy (TMA, mbarrier) issued many frames ahead.
 //                 Same fp32 expressions as the reference: (prev + arc.score) + dense, then max.
 //   BandPrep      all (graph, frame) levels in parallel: the reference's keep tests
 //                 (intersect_dense.cu:289-296, 430-471) on the two Viterbi grids, then per level
-//                 the COMPACT list of surviving states with, per state, exp(dense score) as
-//                 mantissa/exponent and one bit per entering / leaving arc that survives.
-//   BandChain     one warp per (graph, direction) walks the levels over the compact lists only:
-//                 a lane takes one surviving state, reads its neighbours' alpha (beta) of the
-//                 previous level from shared memory by state number, and adds the surviving arcs
-//                 in mantissa/exponent arithmetic (no exp/log on the chain, any score range).
-//                 The lists arrive through a ring of per-lane asynchronous copies.
+//                 the COMPACT list of surviving states with, per state and entering arc, the
+//                 factor exp(arc score) * exp(dense score) if the arc survives and 0 otherwise.
+//   BandChain     one warp per (graph, direction) walks the levels over the lists only: a lane
+//                 takes one surviving state, reads its neighbours' alpha (beta) of the previous
+//                 level from shared memory by state number: three multiply-adds per state and
+//                 level, no exp or log, no test.  The lists arrive by bulk copies.  Values of a
+//                 level share a power-of-two scale that follows the data.
+//   BandChainExact  the same recursion with a (mantissa, exponent) pair per state, for the
+//                 graphs whose scores leave what a double with a per-level scale can hold; it
+//                 runs after BandChain and returns at once for every other graph.
 //   BandGrad      all levels in parallel: posterior of (level, state) = alpha * beta / Z is the
 //                 gradient of that state's dense score; optionally arc posteriors for the
 //                 gradient of the graph's arc scores.
@@ -45,13 +48,18 @@
 namespace k2b {
 
 constexpr int32_t kNoLabel = INT32_MIN;
-constexpr int kBandMaxStates = 512;   // K = 16 states per lane
-constexpr int kBandMaxDepth = 16;     // dense rows in flight per Viterbi warp
-constexpr int kRingItems = 64;        // list entries per level staged ahead of the chain
-constexpr int kChainAhead = 12;       // levels in flight in the chain kernel
+constexpr int kBandMaxStates = 512;
+constexpr int kVitK = 4;              // states per thread of BandViterbi
+constexpr int kPrepK = 16;            // states per lane of BandPrep's row scan
 constexpr int kPrepLevels = 16;       // levels per warp of BandPrep
-constexpr int kGradLevels = 8;        // levels per warp of BandGrad
+constexpr int kRescale = 8;           // levels between changes of the shared scale
+constexpr int kGradLevels = 4;        // levels per warp of BandGrad
 constexpr int kDrainPolls = 4000000;  // bounded wait for copies in flight when a kernel gives up
+
+// bits of the status word
+constexpr int32_t kStatusNotBand = 1, kStatusLate = 2;
+// bits of unfit[i]: the lean recursion cannot represent this graph's numbers
+constexpr int32_t kUnfitFactors = 1, kUnfitRange = 2;
 
 static int32_t g_wait_limit = 4000000;  // polls of an mbarrier before a kernel gives up
 
@@ -78,15 +86,46 @@ struct __align__(16) BandArc {
   int32_t k;
   int32_t arc;
 };
-// Entry of a level's list of surviving states.
+// Entry of a level's list of surviving states (level l, state s): pw[d] = exp(score of
+// the arc from state s - d) * exp(dense score of s's label on frame l - 1) if that arc
+// survives between levels l - 1 and l, else 0.
 struct __align__(16) BandItem {
-  double pm;        // exp(dense score of the state on the frame before) = pm * 2^pe
-  int32_t pe;
-  uint8_t inb;      // bit d: the arc from state s - d of the level before survives
-  uint8_t outb;     // bit d: the arc to state s + d of the next level survives
-  uint16_t s;       // state
+  double pw[3];
+  int32_t label;
+  uint16_t s;
+  uint8_t inb;   // bit d: the arc from state s - d of the level before survives
+  uint8_t outb;  // bit d: the arc to state s + d of the next level survives
 };
-static_assert(sizeof(BandItem) == 16, "BandItem must be 16 bytes");
+static_assert(sizeof(BandItem) == 32, "BandItem must be 32 bytes");
+constexpr int kOutbByte = 31;
+
+// alpha of the final state on the last level (= Z) of a graph, as m * 2^e
+struct __align__(16) BandTotal {
+  double m;
+  int32_t e;
+  int32_t pad;
+};
+
+__device__ __forceinline__ double Pow2Clamp(int32_t e) {
+  if (e < -1000) return 0.0;
+  e = e > 1000 ? 1000 : e;
+  return __longlong_as_double((long long)(1023 + e) << 52);
+}
+
+// Polls an mbarrier at most `limit` times.
+__device__ __forceinline__ bool WaitSlot(uint64_t *bar, unsigned parity, int32_t limit) {
+  for (int32_t k = 0; k < limit; ++k)
+    if (MbarTryWait(bar, parity)) return true;
+  return false;
+}
+
+// Dense score of a state with `label` on dense row `row` of a sequence of T frames whose
+// frame 0 is at lp0 (the row T is the implied final row).
+__device__ __forceinline__ float BandDense(const float *__restrict__ lp0, int32_t C, int32_t T,
+                                           int32_t row, int32_t label) {
+  if (row < T) return (label >= 0 && label < C) ? __ldg(lp0 + (int64_t)row * C + label) : -INFINITY;
+  return label == -1 ? 0.0f : -INFINITY;
+}
 
 // ---------------------------------------------------------------------------
 // Tables of a band graph, and the check that it is one.  One thread per state.
@@ -140,147 +179,183 @@ __global__ void BandTables(const int32_t *__restrict__ row_splits1, int32_t num_
     tabf[(int64_t)idx * 3 + d] = fa;
   }
   tab[idx] = st;
-  if (bad) atomicOr(status, 1);
+  if (bad) atomicOr(status, kStatusNotBand);
 }
 
 // ---------------------------------------------------------------------------
-// Viterbi forward / backward.  grid = (2 directions, pairs), one warp per CTA.
+// Viterbi forward / backward.  grid = (2 directions, pairs).
 // Level l (0 .. T + 1) of the forward grid: best score of any path from the start state
 // at level 0 to the state at level l; of the backward grid: from the state at level l to
 // the final state at level T + 1.  The step between levels l and l + 1 consumes dense row l
 // (row T being the implied final row).
+//
+// A thread holds four consecutive states in registers.  A warp OWNS the states of its
+// last 32 - H lanes and recomputes, in its first H lanes, the 4H states before them (the
+// mirror image walking backward): a state depends on itself and its two predecessors, so
+// what the warp computes for its own states stays exact for 2H frames without hearing
+// from its neighbour.  Frames are therefore taken in batches of F = 2H: the log-prob rows
+// of a batch are contiguous and arrive by ONE bulk copy (TMA, completion on an mbarrier)
+// requested batches ahead, the warps exchange their boundary states through shared memory
+// once per batch, and the frames of a batch run without any wait, barrier or
+// shared-memory store: per frame four shared-memory reads, two shuffles, the adds and
+// maxima, one 16-byte store.  Same fp32 expressions as the reference:
+// (prev + arc.score) + dense, then max.
 // ---------------------------------------------------------------------------
-template <int K>
-__device__ __forceinline__ void StoreRow(float *__restrict__ row, int32_t s0, int32_t pitch,
-                                         const float (&v)[K]) {
-#pragma unroll
-  for (int c = 0; c < K / 4; ++c)
-    if (s0 + 4 * c < pitch)
-      *reinterpret_cast<float4 *>(row + s0 + 4 * c) =
-          make_float4(v[4 * c], v[4 * c + 1], v[4 * c + 2], v[4 * c + 3]);
-}
-
-template <int K>
-__device__ __forceinline__ void LoadRow(const float *__restrict__ row, int32_t s0, int32_t pitch,
-                                        float (&v)[K]) {
-#pragma unroll
-  for (int c = 0; c < K / 4; ++c) {
-    float4 x = make_float4(-INFINITY, -INFINITY, -INFINITY, -INFINITY);
-    if (s0 + 4 * c < pitch) x = *reinterpret_cast<const float4 *>(row + s0 + 4 * c);
-    v[4 * c] = x.x;
-    v[4 * c + 1] = x.y;
-    v[4 * c + 2] = x.z;
-    v[4 * c + 3] = x.w;
-  }
-}
-
 __device__ __forceinline__ float Max3(float a, float b, float c) { return fmaxf(fmaxf(a, b), c); }
 
-// Polls an mbarrier at most `limit` times.
-__device__ __forceinline__ bool WaitSlot(uint64_t *bar, unsigned parity, int32_t limit) {
-  for (int32_t k = 0; k < limit; ++k)
-    if (MbarTryWait(bar, parity)) return true;
-  return false;
-}
+constexpr int kVitMaxBatches = 4;  // batches of rows in flight
+constexpr int kVitMaxWarps = 8;
 
-template <int K>
-__global__ void __launch_bounds__(32)
+__global__ void __launch_bounds__(32 * kVitMaxWarps)
 BandViterbi(const BandInfo *__restrict__ infos, const BandState *__restrict__ tab,
             const float *__restrict__ lp, int32_t C, float *__restrict__ vf,
-            float *__restrict__ vb, int32_t depth, int32_t slot_floats, int32_t wait_limit,
-            int32_t *__restrict__ status) {
+            float *__restrict__ vb, int32_t F, int32_t nbatch, int32_t xch_pad,
+            int32_t wait_limit, int32_t *__restrict__ status) {
+  constexpr int K = kVitK;
   extern __shared__ __align__(16) unsigned char smem_raw[];
-  __shared__ __align__(8) uint64_t full[kBandMaxDepth];
+  __shared__ __align__(8) uint64_t full[kVitMaxBatches];
+  __shared__ int32_t any_late;
   constexpr unsigned kAll = 0xffffffffu;
   const int dir = blockIdx.x;
   const BandInfo f = infos[blockIdx.y];
-  const int lane = threadIdx.x;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int32_t S = f.num_states, T = f.frames, pitch = f.pitch;
   if (S == 0) return;
-  float *ring = reinterpret_cast<float *>(smem_raw);  // [depth][slot_floats]
-  // a slot: four floats of -inf (what a state without a usable label reads), then the row
-  for (int32_t k = lane; k < depth * 4; k += 32) ring[(k >> 2) * slot_floats + (k & 3)] = -INFINITY;
-  if (lane == 0) {
-    for (int st = 0; st < depth; ++st) MbarInit(&full[st], 1);
+  const int32_t H = F >> 1;         // lanes that recompute the neighbour's states
+  const int32_t own = 32 - H;       // lanes whose states this warp owns
+  float *ring = reinterpret_cast<float *>(smem_raw);                    // [nbatch][F][C]
+  float *xch = ring + (size_t)nbatch * F * C;                           // [2][xch_pad], state s at s + 4H
+  if (tid == 0) {
+    for (int st = 0; st < nbatch; ++st) MbarInit(&full[st], 1);
     MbarInitFence();
+    any_late = 0;
   }
-  __syncwarp();
-  const unsigned row_bytes = 4u * (unsigned)C;
+  for (int32_t k = tid; k < 2 * xch_pad; k += blockDim.x) xch[k] = -INFINITY;
+  __syncthreads();
+  const int32_t num_batches = (T + F - 1) / F;
   const float *lp0 = lp + (int64_t)f.lp_row * C;
-  // rows in the order this direction consumes them: i = 0 .. T - 1
   int32_t issued = 0;
-  auto issue = [&](int32_t i) {  // lane 0 only
-    if (i >= T) return;
-    const int32_t row = dir == 0 ? i : T - 1 - i;
-    const int32_t slot = i % depth;
-    MbarArriveExpectTx(&full[slot], row_bytes);
-    BulkCopyG2S(ring + (size_t)slot * slot_floats + 4, lp0 + (int64_t)row * C, row_bytes,
-                &full[slot]);
-    issued = i + 1;
+  auto issue = [&]() {  // thread 0 only: the rows of the next batch into the next slot
+    if (issued >= num_batches) return;
+    const int32_t q = issued;
+    // batch q: forward rows [qF, min((q+1)F, T)); backward rows [max(T-(q+1)F, 0), T-qF)
+    const int32_t r0 = dir == 0 ? q * F : max(T - (q + 1) * F, 0);
+    const int32_t r1 = dir == 0 ? min((q + 1) * F, T) : T - q * F;
+    const unsigned bytes = (unsigned)(r1 - r0) * 4u * (unsigned)C;
+    const int32_t slot = q % nbatch;
+    MbarArriveExpectTx(&full[slot], bytes);
+    BulkCopyG2S(ring + (size_t)slot * F * C, lp0 + (int64_t)r0 * C, bytes, &full[slot]);
+    ++issued;
   };
-  if (lane == 0)
-    for (int32_t i = 0; i < depth; ++i) issue(i);
+  if (tid == 0)
+    for (int32_t q = 0; q < nbatch; ++q) issue();
 
-  const int32_t s0 = lane * K;
-  float *grid = (dir == 0 ? vf : vb) + f.grid_off;
+  // first state of this lane: forward, the recomputed states come first; backward, last
+  const int32_t s0 = warp * own * K + (dir == 0 ? (lane - H) * K : lane * K);
+  const bool mine = dir == 0 ? lane >= H : lane < own;   // a lane that owns its states
+  const bool stores = mine && s0 < pitch;
+  float *grid = (dir == 0 ? vf : vb) + f.grid_off + s0;
   bool late = false;
-  float v[K];
+  float v[K] = {0.0f, 0.0f, 0.0f, 0.0f};
+  // exchange of boundary states: owners publish, recomputing lanes pick up
+  auto exchange = [&](int32_t which) {
+    float *x = xch + (size_t)which * xch_pad + 4 * H;
+    if (mine && s0 < xch_pad - 4 * H - 3)
+      *reinterpret_cast<float4 *>(x + s0) = make_float4(v[0], v[1], v[2], v[3]);
+    __syncthreads();
+    if (!mine && s0 + 4 * H >= 0 && s0 < xch_pad - 4 * H - 3) {
+      const float4 t = *reinterpret_cast<const float4 *>(x + s0);
+      v[0] = t.x;
+      v[1] = t.y;
+      v[2] = t.z;
+      v[3] = t.w;
+    }
+  };
   if (dir == 0) {
     // ---- forward: state s from s, s - 1, s - 2 ----------------------------------
-    float w0[K], w1[K], w2[K];
+    float w0[K], w1[K], w2[K];     // on the frames; -inf for a state whose label has no column
+    float f0[K], f1[K], f2[K];     // on the implied final row: only arcs labelled -1 score
     int32_t col[K];
-    uint32_t fin = 0;
 #pragma unroll
     for (int k = 0; k < K; ++k) {
       const int32_t s = s0 + k;
-      w0[k] = w1[k] = w2[k] = -INFINITY;
+      w0[k] = w1[k] = w2[k] = f0[k] = f1[k] = f2[k] = -INFINITY;
       col[k] = 0;
-      if (s < S) {
+      if (s >= 0 && s < S) {
         const BandState t = tab[f.state_off + s];
-        w0[k] = t.w[0];
-        w1[k] = t.w[1];
-        w2[k] = t.w[2];
-        if (t.label >= 0 && t.label < C) col[k] = 4 + t.label;
-        if (t.label == -1) fin |= 1u << k;
+        if (t.label >= 0 && t.label < C) {
+          col[k] = t.label;
+          w0[k] = t.w[0];
+          w1[k] = t.w[1];
+          w2[k] = t.w[2];
+        } else if (t.label == -1) {
+          f0[k] = t.w[0];
+          f1[k] = t.w[1];
+          f2[k] = t.w[2];
+        }
       }
       v[k] = s == 0 ? 0.0f : -INFINITY;
     }
-    StoreRow<K>(grid, s0, pitch, v);
-    for (int32_t l = 1; l <= T + 1; ++l) {
-      const int32_t i = l - 1;  // dense row
-      float x[K];
-      if (l <= T) {
-        const int32_t slot = i % depth;
-        if (!late) late = !WaitSlot(&full[slot], (unsigned)(i / depth) & 1u, wait_limit);
-        const float *rowbuf = ring + (size_t)slot * slot_floats;
+    if (stores) *reinterpret_cast<float4 *>(grid) = make_float4(v[0], v[1], v[2], v[3]);
+    int32_t xpar = 0;
+    for (int32_t q = 0; q < num_batches; ++q) {
+      const int32_t slot = q % nbatch;
+      if (!late) late = !WaitSlot(&full[slot], (unsigned)(q / nbatch) & 1u, wait_limit);
+      if (q > 0) {
+        exchange(xpar);  // its barrier also says: every warp has finished batch q - 1
+        xpar ^= 1;
+        if (tid == 0 && !late) issue();  // into the slot batch q - 1 used
+      }
+      const int32_t nf = min(F, T - q * F);
+      const float *rowbuf = ring + (size_t)slot * F * C;
+#pragma unroll 4
+      for (int32_t r = 0; r < nf; ++r, rowbuf += C) {
+        float x[K];
 #pragma unroll
         for (int k = 0; k < K; ++k) x[k] = rowbuf[col[k]];
-      } else {
+        float h1 = __shfl_up_sync(kAll, v[K - 1], 1), h2 = __shfl_up_sync(kAll, v[K - 2], 1);
+        if (lane == 0) h1 = h2 = -INFINITY;
+        float nv[K];
 #pragma unroll
-        for (int k = 0; k < K; ++k) x[k] = (fin >> k) & 1u ? 0.0f : -INFINITY;
+        for (int k = 0; k < K; ++k) {
+          const float a = v[k];
+          const float b = k >= 1 ? v[k >= 1 ? k - 1 : 0] : h1;
+          const float c = k >= 2 ? v[k >= 2 ? k - 2 : 0] : (k == 1 ? h1 : h2);
+          const float m = Max3(__fadd_rn(a, w0[k]), __fadd_rn(b, w1[k]), __fadd_rn(c, w2[k]));
+          nv[k] = __fadd_rn(m, x[k]);
+        }
+#pragma unroll
+        for (int k = 0; k < K; ++k) v[k] = nv[k];
+        grid += pitch;
+        if (stores) *reinterpret_cast<float4 *>(grid) = make_float4(v[0], v[1], v[2], v[3]);
       }
+    }
+    // the implied final row: level T + 1
+    exchange(xpar);
+    {
       float h1 = __shfl_up_sync(kAll, v[K - 1], 1), h2 = __shfl_up_sync(kAll, v[K - 2], 1);
       if (lane == 0) h1 = h2 = -INFINITY;
       float nv[K];
 #pragma unroll
       for (int k = 0; k < K; ++k) {
         const float a = v[k];
-        const float b = k >= 1 ? v[k - 1] : h1;
-        const float c = k >= 2 ? v[k - 2] : (k == 1 ? h1 : h2);
-        const float m = Max3(__fadd_rn(a, w0[k]), __fadd_rn(b, w1[k]), __fadd_rn(c, w2[k]));
-        nv[k] = __fadd_rn(m, x[k]);
+        const float b = k >= 1 ? v[k >= 1 ? k - 1 : 0] : h1;
+        const float c = k >= 2 ? v[k >= 2 ? k - 2 : 0] : (k == 1 ? h1 : h2);
+        const float m = Max3(__fadd_rn(a, f0[k]), __fadd_rn(b, f1[k]), __fadd_rn(c, f2[k]));
+        nv[k] = __fadd_rn(m, 0.0f);
       }
-      __syncwarp();  // every lane has read its scores of this row
-      if (lane == 0 && !late) issue(i + depth);
-#pragma unroll
-      for (int k = 0; k < K; ++k) v[k] = nv[k];
-      StoreRow<K>(grid + (int64_t)l * pitch, s0, pitch, v);
+      grid += pitch;
+      if (stores) *reinterpret_cast<float4 *>(grid) = make_float4(nv[0], nv[1], nv[2], nv[3]);
     }
   } else {
     // ---- backward: state s to s, s + 1, s + 2 -----------------------------------
-    float wo[K][3];       // score of the arc s -> s + d
+    float wo[K][3];   // score of the arc s -> s + d on the frames (-inf: its label has no column)
+    float fo[K][3];   // on the implied final row
     int32_t col[K + 2];   // of states s0 .. s0 + K + 1
-    uint32_t fin = 0;
+#pragma unroll
+    for (int k = 0; k < K; ++k)
+#pragma unroll
+      for (int d = 0; d < 3; ++d) wo[k][d] = fo[k][d] = -INFINITY;
 #pragma unroll
     for (int k = 0; k < K + 2; ++k) {
       const int32_t s = s0 + k;
@@ -289,75 +364,108 @@ BandViterbi(const BandInfo *__restrict__ infos, const BandState *__restrict__ ta
       t.w[0] = t.w[1] = t.w[2] = -INFINITY;
       t.label = kNoLabel;
       if (s < S) t = tab[f.state_off + s];
-      if (t.label >= 0 && t.label < C) col[k] = 4 + t.label;
-      if (t.label == -1) fin |= 1u << k;
+      const bool frame_label = t.label >= 0 && t.label < C;
+      if (frame_label) col[k] = t.label;
 #pragma unroll
       for (int d = 0; d < 3; ++d)
-        if (k - d >= 0 && k - d < K) wo[k - d][d] = t.w[d];
+        if (k - d >= 0 && k - d < K) {
+          if (frame_label) wo[k - d >= 0 ? k - d : 0][d] = t.w[d];
+          else if (t.label == -1) fo[k - d >= 0 ? k - d : 0][d] = t.w[d];
+        }
     }
 #pragma unroll
     for (int k = 0; k < K; ++k) v[k] = (s0 + k == S - 1) ? 0.0f : -INFINITY;
-    StoreRow<K>(grid + (int64_t)(T + 1) * pitch, s0, pitch, v);
-    for (int32_t l = T; l >= 0; --l) {  // level l from level l + 1 through dense row l
-      const int32_t i = T - 1 - l;      // order of consumption (-1: the implied final row)
-      float x[K + 2];
-      if (l < T) {
-        const int32_t slot = i % depth;
-        if (!late) late = !WaitSlot(&full[slot], (unsigned)(i / depth) & 1u, wait_limit);
-        const float *rowbuf = ring + (size_t)slot * slot_floats;
-#pragma unroll
-        for (int k = 0; k < K + 2; ++k) x[k] = rowbuf[col[k]];
-      } else {
-#pragma unroll
-        for (int k = 0; k < K + 2; ++k) x[k] = (fin >> k) & 1u ? 0.0f : -INFINITY;
-      }
+    grid += (int64_t)(T + 1) * pitch;
+    if (stores) *reinterpret_cast<float4 *>(grid) = make_float4(v[0], v[1], v[2], v[3]);
+    {  // level T from level T + 1 through the implied final row (nothing to exchange yet:
+       // only the final state is not -inf, and every lane knows it)
       float g1 = __shfl_down_sync(kAll, v[0], 1), g2 = __shfl_down_sync(kAll, v[1], 1);
       if (lane == 31) g1 = g2 = -INFINITY;
       float nv[K];
 #pragma unroll
       for (int k = 0; k < K; ++k) {
         const float a = v[k];
-        const float b = k + 1 < K ? v[k + 1] : g1;
-        const float c = k + 2 < K ? v[k + 2] : (k + 2 == K ? g1 : g2);
-        nv[k] = Max3(__fadd_rn(__fadd_rn(a, wo[k][0]), x[k]),
-                     __fadd_rn(__fadd_rn(b, wo[k][1]), x[k + 1]),
-                     __fadd_rn(__fadd_rn(c, wo[k][2]), x[k + 2]));
+        const float b = k + 1 < K ? v[k + 1 < K ? k + 1 : 0] : g1;
+        const float c = k + 2 < K ? v[k + 2 < K ? k + 2 : 0] : (k + 2 == K ? g1 : g2);
+        nv[k] = Max3(__fadd_rn(__fadd_rn(a, fo[k][0]), 0.0f), __fadd_rn(__fadd_rn(b, fo[k][1]), 0.0f),
+                     __fadd_rn(__fadd_rn(c, fo[k][2]), 0.0f));
       }
-      __syncwarp();
-      if (lane == 0 && !late && l < T) issue(i + depth);
 #pragma unroll
       for (int k = 0; k < K; ++k) v[k] = nv[k];
-      StoreRow<K>(grid + (int64_t)l * pitch, s0, pitch, v);
+      grid -= pitch;
+      if (stores) *reinterpret_cast<float4 *>(grid) = make_float4(v[0], v[1], v[2], v[3]);
+    }
+    int32_t xpar = 0;
+    for (int32_t q = 0; q < num_batches; ++q) {
+      const int32_t slot = q % nbatch;
+      if (!late) late = !WaitSlot(&full[slot], (unsigned)(q / nbatch) & 1u, wait_limit);
+      exchange(xpar);  // also: every warp has finished batch q - 1
+      xpar ^= 1;
+      if (q > 0 && tid == 0 && !late) issue();
+      const int32_t r1 = T - q * F, r0 = max(T - (q + 1) * F, 0);
+      const float *rowbuf = ring + (size_t)slot * F * C + (size_t)(r1 - 1 - r0) * C;
+#pragma unroll 4
+      for (int32_t r = r1 - 1; r >= r0; --r, rowbuf -= C) {  // level r from level r + 1
+        float x[K + 2];
+#pragma unroll
+        for (int k = 0; k < K + 2; ++k) x[k] = rowbuf[col[k]];
+        float g1 = __shfl_down_sync(kAll, v[0], 1), g2 = __shfl_down_sync(kAll, v[1], 1);
+        if (lane == 31) g1 = g2 = -INFINITY;
+        float nv[K];
+#pragma unroll
+        for (int k = 0; k < K; ++k) {
+          const float a = v[k];
+          const float b = k + 1 < K ? v[k + 1 < K ? k + 1 : 0] : g1;
+          const float c = k + 2 < K ? v[k + 2 < K ? k + 2 : 0] : (k + 2 == K ? g1 : g2);
+          nv[k] = Max3(__fadd_rn(__fadd_rn(a, wo[k][0]), x[k]),
+                       __fadd_rn(__fadd_rn(b, wo[k][1]), x[k + 1]),
+                       __fadd_rn(__fadd_rn(c, wo[k][2]), x[k + 2]));
+        }
+#pragma unroll
+        for (int k = 0; k < K; ++k) v[k] = nv[k];
+        grid -= pitch;
+        if (stores) *reinterpret_cast<float4 *>(grid) = make_float4(v[0], v[1], v[2], v[3]);
+      }
     }
   }
-  if (__any_sync(kAll, late)) {
+  if (late) any_late = 1;
+  __syncthreads();
+  if (any_late) {
     // A copy did not arrive in time: the grids hold garbage.  Say so, and let the copies
     // that are still in flight towards this CTA's shared memory land before it retires.
-    if (lane == 0) {
-      atomicOr(status, 2);
-      for (int32_t i = max(0, issued - depth); i < issued; ++i)
-        WaitSlot(&full[i % depth], (unsigned)(i / depth) & 1u, kDrainPolls);
+    if (tid == 0) {
+      atomicOr(status, kStatusLate);
+      for (int32_t q = max(0, issued - nbatch); q < issued; ++q)
+        WaitSlot(&full[q % nbatch], (unsigned)(q / nbatch) & 1u, kDrainPolls);
     }
-    __syncwarp();
+    __syncthreads();
   }
 }
 
 // ---------------------------------------------------------------------------
-// Keep tests and the per-level lists.  grid = (level chunks, pairs), a warp per chunk of
-// kPrepLevels levels; lane owns K consecutive states as in BandViterbi.  A warp writes the
-// complete entries of the levels it owns, for which it also needs the surviving arcs into
-// the level after its last (recomputed from one more row of each grid).
-// totals[0] += surviving states, totals[2] += the arcs leaving them (the sizes the beam
-// reduction looks at, intersect_dense.cu:289-320).
+// Keep tests and the per-level lists.  grid = (level chunks, pairs), 4 warps per CTA, a
+// warp per chunk of kPrepLevels levels.  Per level the warp
+//   1. scans the two Viterbi rows (a lane reads 16 consecutive states of each; the rows of
+//      the next level are requested before this level is worked on), marks the surviving
+//      states and writes them, in state order, to a list in shared memory;
+//   2. takes the list one state per lane: arc tests against the rows of the level before,
+//      the dense score of the state's label, the factors of the entry;
+//   3. gives the entries of the level before their leaving-arc bits, which are the
+//      entering-arc bits of this level seen from the source.
+// A warp writes the complete entries of the levels it owns, so it also runs steps 1-2 for
+// the level after its last.  totals[0] += surviving states, totals[2] += the arcs leaving
+// them (the sizes the beam reduction looks at, intersect_dense.cu:289-320).
 // ---------------------------------------------------------------------------
-template <int K>
 __global__ void __launch_bounds__(128)
 BandPrep(const BandInfo *__restrict__ infos, const BandState *__restrict__ tab,
-         const int32_t *__restrict__ a_row_splits2, const float *__restrict__ lp, int32_t C,
-         const float *__restrict__ vf, const float *__restrict__ vb, float beam,
-         BandItem *__restrict__ items, int32_t *__restrict__ counts,
-         float *__restrict__ cutoffs, unsigned long long *__restrict__ totals) {
+         const BandArc *__restrict__ tabf, const int32_t *__restrict__ a_row_splits2,
+         const float *__restrict__ lp, int32_t C, const float *__restrict__ vf,
+         const float *__restrict__ vb, float beam, BandItem *__restrict__ items,
+         int2 *__restrict__ lists, float *__restrict__ cutoffs,
+         unsigned long long *__restrict__ totals, int32_t *__restrict__ unfit, int32_t s_pad) {
+  constexpr int K = kPrepK;
   constexpr unsigned kAll = 0xffffffffu;
+  extern __shared__ __align__(16) unsigned char smem_raw[];
   const int32_t i = blockIdx.y;
   const BandInfo f = infos[i];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -366,6 +474,11 @@ BandPrep(const BandInfo *__restrict__ infos, const BandState *__restrict__ tab,
   const int32_t a = (blockIdx.x * 4 + warp) * kPrepLevels;  // owns levels a .. b - 1
   if (a > T + 1) return;
   const int32_t b = min(a + kPrepLevels, T + 2);
+  // per warp: entering-arc bits of the current level by state (zero outside the list),
+  // and the lists of the current and the previous level
+  unsigned char *inb_sm = smem_raw + (size_t)warp * (s_pad + 4 * s_pad);
+  uint16_t *list_sm = reinterpret_cast<uint16_t *>(inb_sm + s_pad);  // [2][s_pad]
+  for (int32_t k = lane; k < s_pad; k += 32) inb_sm[k] = 0;
   const float *fg = vf + f.grid_off, *bg = vb + f.grid_off;
   float cutoff;
   {
@@ -373,122 +486,123 @@ BandPrep(const BandInfo *__restrict__ infos, const BandState *__restrict__ tab,
     cutoff = __fsub_rn(start < end ? start : end, beam);
   }
   if (a == 0 && lane == 0) cutoffs[i] = cutoff;
-  const int32_t s0 = lane * K;
-  float w[K][3];
-  int32_t label[K];
-#pragma unroll
-  for (int k = 0; k < K; ++k) {
-    BandState t;
-    t.w[0] = t.w[1] = t.w[2] = -INFINITY;
-    t.label = kNoLabel;
-    if (s0 + k < S) t = tab[f.state_off + s0 + k];
-    w[k][0] = t.w[0];
-    w[k][1] = t.w[1];
-    w[k][2] = t.w[2];
-    label[k] = t.label;
-  }
   const float *lp0 = lp + (int64_t)f.lp_row * C;
-  float Fp[K], Bp[K];
-  uint32_t keep_p = 0;
+  const int32_t s0 = lane * K;
+  const int32_t last = min(b, T + 1);  // last level looked at
+  float4 Fc[K / 4], Bc[K / 4];
+  auto load_rows = [&](int32_t l, float4 (&F)[K / 4], float4 (&B)[K / 4]) {
 #pragma unroll
-  for (int k = 0; k < K; ++k) Fp[k] = Bp[k] = -INFINITY;
-  if (a >= 1) {
-    LoadRow<K>(fg + (int64_t)(a - 1) * pitch, s0, pitch, Fp);
-    LoadRow<K>(bg + (int64_t)(a - 1) * pitch, s0, pitch, Bp);
-#pragma unroll
-    for (int k = 0; k < K; ++k)
-      if (__fadd_rn(Fp[k], Bp[k]) > cutoff) keep_p |= 1u << k;
-  }
-  int32_t base_p = 0;  // list position of this lane's first surviving state, level before
+    for (int c = 0; c < K / 4; ++c) {
+      F[c] = B[c] = make_float4(-INFINITY, -INFINITY, -INFINITY, -INFINITY);
+      if (l <= last && s0 + 4 * c < pitch) {
+        F[c] = *reinterpret_cast<const float4 *>(fg + (int64_t)l * pitch + s0 + 4 * c);
+        B[c] = *reinterpret_cast<const float4 *>(bg + (int64_t)l * pitch + s0 + 4 * c);
+      }
+    }
+  };
+  load_rows(a, Fc, Bc);
+  int32_t n_prev = 0;
+  // the lists of a warp's levels lie one after the other from the start of its chunk
+  // (a chunk has room for all states of all its levels); lists[level] = (start, size)
+  int32_t run = a * pitch, prev_start = 0;
   uint32_t n_states = 0, n_cand = 0;
-  for (int32_t l = a; l <= b && l <= T + 1; ++l) {
+  bool risky = false;
+  __syncwarp();
+  for (int32_t l = a; l <= last; ++l) {
     const bool own = l < b;
-    float Fc[K], Bc[K];
-    LoadRow<K>(fg + (int64_t)l * pitch, s0, pitch, Fc);
-    LoadRow<K>(bg + (int64_t)l * pitch, s0, pitch, Bc);
-    uint32_t keep_c = 0;
+    float4 Fn[K / 4], Bn[K / 4];
+    load_rows(l + 1, Fn, Bn);  // in flight while this level is worked on
+    uint16_t *cur_list = list_sm + (l & 1) * s_pad, *prev_list = list_sm + ((l & 1) ^ 1) * s_pad;
+    // ---- 1. surviving states ------------------------------------------------------
+    uint32_t keep = 0;
 #pragma unroll
-    for (int k = 0; k < K; ++k)
-      if (__fadd_rn(Fc[k], Bc[k]) > cutoff) keep_c |= 1u << k;
-    const uint32_t lanes_c = __ballot_sync(kAll, keep_c != 0);
-    // position of this lane's survivors in the level's list
-    int32_t cnt = __popc(keep_c), incl = cnt;
+    for (int c = 0; c < K / 4; ++c) {
+      if (__fadd_rn(Fc[c].x, Bc[c].x) > cutoff) keep |= 1u << (4 * c);
+      if (__fadd_rn(Fc[c].y, Bc[c].y) > cutoff) keep |= 2u << (4 * c);
+      if (__fadd_rn(Fc[c].z, Bc[c].z) > cutoff) keep |= 4u << (4 * c);
+      if (__fadd_rn(Fc[c].w, Bc[c].w) > cutoff) keep |= 8u << (4 * c);
+    }
+    const int32_t mine = __popc(keep);
+    int32_t incl = mine;
 #pragma unroll
     for (int d = 1; d < 32; d <<= 1) {
       const int32_t o = __shfl_up_sync(kAll, incl, d);
       if (lane >= d) incl += o;
     }
-    const int32_t base_c = incl - cnt;
-    const int32_t n_c = __shfl_sync(kAll, incl, 31);
-    // the two states before this lane's first, from the previous lane
-    float hF1 = __shfl_up_sync(kAll, Fp[K - 1], 1), hF2 = __shfl_up_sync(kAll, Fp[K - 2], 1);
-    uint32_t hk = __shfl_up_sync(kAll, keep_p, 1);
-    if (lane == 0) {
-      hF1 = hF2 = -INFINITY;
-      hk = 0;
+    const int32_t n = __shfl_sync(kAll, incl, 31);
+    {
+      int32_t pos = incl - mine;
+      for (uint32_t m = keep; m; m &= m - 1) cur_list[pos++] = (uint16_t)(s0 + __ffs(m) - 1);
     }
-    uint32_t inb[K];
-    BandItem *out = items + f.grid_off + (int64_t)l * pitch;
-#pragma unroll
-    for (int k = 0; k < K; ++k) {
-      inb[k] = 0;
-      if (!((keep_c >> k) & 1u)) continue;
-      float x = -INFINITY;
+    __syncwarp();
+    // ---- 2. one surviving state per lane ----------------------------------------------
+    BandItem *out = items + f.grid_off + run;
+    const float *fprev = fg + (int64_t)(l - 1) * pitch, *bprev = bg + (int64_t)(l - 1) * pitch;
+    const float *bcur = bg + (int64_t)l * pitch;
+    for (int32_t j = lane; j < n; j += 32) {
+      const int32_t s = cur_list[j];
+      const BandState t = tab[f.state_off + s];
+      uint32_t inb = 0;
+      BandItem it;
+      it.pw[0] = it.pw[1] = it.pw[2] = 0.0;
       if (l >= 1) {
-        const int32_t row = l - 1;
-        if (row < T) {
-          if (label[k] >= 0 && label[k] < C) x = __ldg(lp0 + (int64_t)row * C + label[k]);
-        } else if (label[k] == -1) {
-          x = 0.0f;
-        }
+        const float x = BandDense(lp0, C, T, l - 1, t.label);
+        const float bc = bcur[s];
+        const double p = exp((double)x);
 #pragma unroll
         for (int d = 0; d < 3; ++d) {
-          const float srcF = k - d >= 0 ? Fp[k - d > 0 ? k - d : 0] : (k - d == -1 ? hF1 : hF2);
-          const bool kept = k - d >= 0 ? (keep_p >> (k - d > 0 ? k - d : 0)) & 1u
-                                       : (hk >> (K + k - d)) & 1u;
-          const float sc = __fadd_rn(w[k][d], x);
-          const float through = __fadd_rn(__fadd_rn(srcF, sc), Bc[k]);
-          if (kept && through > cutoff) inb[k] |= 1u << d;
+          if (s - d < 0) continue;
+          const float sf = fprev[s - d];
+          const bool kept = __fadd_rn(sf, bprev[s - d]) > cutoff;
+          const float sc = __fadd_rn(t.w[d], x);
+          if (kept && __fadd_rn(__fadd_rn(sf, sc), bc) > cutoff) {
+            inb |= 1u << d;
+            if (own) {
+              const BandArc arc = tabf[(int64_t)(f.state_off + s) * 3 + d];
+              it.pw[d] = arc.f * Pow2Clamp(arc.k) * p;
+              // outside what a double holds with a scale that follows the data every few
+              // levels: such graphs go to the (mantissa, exponent) recursion
+              if (!(x >= -60.0f) || arc.k > 60 || arc.k < -90) risky = true;
+            }
+          }
         }
       }
+      if (inb) inb_sm[s] = (unsigned char)inb;
       if (own) {
-        BandItem it;
-        ExpToMantExp(x, &it.pm, &it.pe);
-        it.inb = (uint8_t)inb[k];
+        it.label = t.label;
+        it.s = (uint16_t)s;
+        it.inb = (uint8_t)inb;
         it.outb = 0;
-        it.s = (uint16_t)(s0 + k);
-        out[base_c + __popc(keep_c & ((1u << k) - 1u))] = it;
-        ++n_states;
-        const int32_t idx = f.state_off + s0 + k;
+        out[j] = it;
+        const int32_t idx = f.state_off + s;
         n_cand += a_row_splits2[idx + 1] - a_row_splits2[idx];
       }
     }
-    if (own && lane == 0) counts[f.level_off + l] = n_c;
-    // arcs leaving the states of level l - 1 (owned when l - 1 >= a): bit d of state s is
-    // bit d of the entering arcs of state s + d on this level
-    if (l - 1 >= a && __any_sync(kAll, keep_p != 0) && lanes_c != 0) {
-      uint32_t n1 = __shfl_down_sync(kAll, inb[0], 1), n2 = __shfl_down_sync(kAll, inb[1], 1);
-      if (lane == 31) n1 = n2 = 0;
-      unsigned char *prev_bytes =
-          reinterpret_cast<unsigned char *>(items + f.grid_off + (int64_t)(l - 1) * pitch);
-#pragma unroll
-      for (int k = 0; k < K; ++k) {
-        if (!((keep_p >> k) & 1u)) continue;
-        const uint32_t i1 = k + 1 < K ? inb[k + 1 < K ? k + 1 : 0] : n1;
-        const uint32_t i2 = k + 2 < K ? inb[k + 2 < K ? k + 2 : 0] : (k + 2 == K ? n1 : n2);
-        const uint32_t ob = (inb[k] & 1u) | (i1 & 2u) | (i2 & 4u);
-        if (ob)
-          prev_bytes[(size_t)(base_p + __popc(keep_p & ((1u << k) - 1u))) * sizeof(BandItem) + 13] =
-              (unsigned char)ob;
+    if (own) {
+      n_states += lane == 0 ? n : 0;
+      if (lane == 0) lists[f.level_off + l] = make_int2(run, n);
+    }
+    __syncwarp();
+    // ---- 3. leaving-arc bits of the level before ---------------------------------------
+    if (l - 1 >= a && n > 0) {
+      unsigned char *prev_bytes = reinterpret_cast<unsigned char *>(items + f.grid_off + prev_start);
+      for (int32_t j = lane; j < n_prev; j += 32) {
+        const int32_t s = prev_list[j];
+        const uint32_t ob = (inb_sm[s] & 1u) | (inb_sm[s + 1] & 2u) | (inb_sm[s + 2] & 4u);
+        if (ob) prev_bytes[(size_t)j * sizeof(BandItem) + kOutbByte] = (unsigned char)ob;
       }
     }
+    __syncwarp();
+    for (int32_t j = lane; j < n; j += 32) inb_sm[cur_list[j]] = 0;
+    __syncwarp();
 #pragma unroll
-    for (int k = 0; k < K; ++k) {
-      Fp[k] = Fc[k];
-      Bp[k] = Bc[k];
+    for (int c = 0; c < K / 4; ++c) {
+      Fc[c] = Fn[c];
+      Bc[c] = Bn[c];
     }
-    keep_p = keep_c;
-    base_p = base_c;
+    n_prev = n;
+    prev_start = run;
+    run += n;
   }
 #pragma unroll
   for (int d = 16; d > 0; d >>= 1) {
@@ -499,80 +613,313 @@ BandPrep(const BandInfo *__restrict__ infos, const BandState *__restrict__ tab,
     atomicAdd(&totals[0], (unsigned long long)n_states);
     atomicAdd(&totals[2], (unsigned long long)n_cand);
   }
+  if (__any_sync(kAll, risky) && lane == 0) atomicOr(&unfit[i], kUnfitFactors);
 }
 
 // ---------------------------------------------------------------------------
 // alpha (dir 0) and beta (dir 1) over the lists.  grid = (2, pairs), one warp per CTA.
-//   alpha_0[start] = 1;  alpha_l[s] = p_l[s] * sum_d [arc s-d -> s survives] e^w alpha_{l-1}[s-d]
-//   beta_{T+1}[final] = 1;  beta_l[s] = sum_d [arc s -> s+d survives] e^w p_{l+1}[s+d] beta_{l+1}[s+d]
-// Values are m * 2^e with m in [1, 2) or 0.  Shared memory holds, by state number, the
-// values of the previous level (for beta: already multiplied by p) in two buffers used in
-// turn; an entry of the buffer read is current whenever the arc bit that selects it is set.
-// Outputs: alpha / beta (mantissas and exponents) at the list positions, tot[i].
+//   alpha_0[start] = 1;          alpha_l[s] = sum_d pw_l[s][d] * alpha_{l-1}[s-d]
+//   beta_{T+1}[final] = 1;       beta_l[s]  = sum_d [arc s -> s+d survives] pw_{l+1}[s+d][d] * beta_{l+1}[s+d]
+// Shared memory holds, by state number, what the previous level hands on - alpha itself,
+// or for beta the three products pw[d] * beta of every state - in two buffers used in
+// turn.  An entry that is read and counts is always current: a factor that is not zero, or
+// a leaving-arc bit that is set, names a state of the previous level's list.  Stale
+// entries are finite numbers, multiplied by a factor of zero or not selected.
+// The lists of kPrepLevels consecutive levels are contiguous in memory (BandPrep): they
+// arrive by one bulk copy per chunk, requested chunks ahead, so a level waits for nothing
+// but the warp's own previous level.
+// The values of a level are stored divided by 2^K; K changes every kRescale levels by the
+// exponent of the largest value of the level before.  A value that is not zero and below
+// 2^-900 (or above 2^900) marks the graph in `unfit` for the (mantissa, exponent) variant
+// (kExact), which runs afterwards and returns at once for every other graph.
+// Outputs: alpha / beta at the list positions, K per level, tot[i], total[i].
 // ---------------------------------------------------------------------------
+constexpr int kChainSlots = 3;                  // chunks in flight
+constexpr int kSlotItems = kPrepLevels * 40;    // entries of a chunk staged in shared memory
+
+// The ring of chunks: lane 0 requests, every lane waits.
+struct ChunkRing {
+  uint64_t *full;          // [kChainSlots]
+  BandItem *slots;         // [kChainSlots][kSlotItems]
+  const BandItem *items0;  // the pair's lists
+  const int2 *lst;         // (start, size) of every level, in shared memory
+  int32_t pitch, L, num_chunks, dir, issued;
+  __device__ __forceinline__ int32_t ChunkOf(int32_t q) const {
+    return dir == 0 ? q : num_chunks - 1 - q;
+  }
+  // entries of a chunk's lists (they are contiguous from the chunk's start)
+  __device__ __forceinline__ int32_t ChunkItems(int32_t c) const {
+    const int32_t l1 = min((c + 1) * kPrepLevels, L) - 1;
+    return lst[l1].x + lst[l1].y - c * kPrepLevels * pitch;
+  }
+  __device__ __forceinline__ void Issue() {  // lane 0: the next chunk into the next slot
+    if (issued >= num_chunks) return;
+    const int32_t c = ChunkOf(issued), slot = issued % kChainSlots;
+    // at least one entry, so that the slot's barrier completes once per use
+    const int32_t n = max(min(ChunkItems(c), kSlotItems), 1);
+    const unsigned bytes = (unsigned)n * (unsigned)sizeof(BandItem);
+    MbarArriveExpectTx(&full[slot], bytes);
+    BulkCopyG2S(slots + (size_t)slot * kSlotItems, items0 + (int64_t)c * kPrepLevels * pitch,
+                bytes, &full[slot]);
+    ++issued;
+  }
+  __device__ __forceinline__ void Drain() {  // lane 0, after giving up
+    for (int32_t k = max(0, issued - kChainSlots); k < issued; ++k)
+      WaitSlot(&full[k % kChainSlots], (unsigned)(k / kChainSlots) & 1u, kDrainPolls);
+  }
+};
+
 __global__ void __launch_bounds__(32)
-BandChain(const BandInfo *__restrict__ infos, const BandArc *__restrict__ tabf,
-          const BandItem *__restrict__ items, const int32_t *__restrict__ counts,
-          double *__restrict__ am, int32_t *__restrict__ ae, double *__restrict__ bm,
-          int32_t *__restrict__ be, double *__restrict__ tot, const int32_t *__restrict__ status,
-          int32_t st_pad, int32_t lv_pad) {
+BandChainLean(const BandInfo *__restrict__ infos, const BandItem *__restrict__ items,
+              const int2 *__restrict__ lists, double *__restrict__ am, double *__restrict__ bm,
+              int32_t *__restrict__ a_scale, int32_t *__restrict__ b_scale,
+              double *__restrict__ tot, BandTotal *__restrict__ total,
+              int32_t *__restrict__ unfit, int32_t *__restrict__ status, int32_t st_pad,
+              int32_t lv_pad, int32_t wait_limit) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
+  __shared__ __align__(8) uint64_t full[kChainSlots];
+  constexpr unsigned kAll = 0xffffffffu;
   const int dir = blockIdx.x;
   const int32_t i = blockIdx.y;
   const BandInfo f = infos[i];
   const int lane = threadIdx.x;
   const int32_t S = f.num_states, T = f.frames, pitch = f.pitch, L = T + 2;
-  if (dir == 0 && lane == 0) tot[i] = -INFINITY;
-  if (S == 0) return;
-  ProbState *st = reinterpret_cast<ProbState *>(smem_raw);            // [2][st_pad], state s at s + 2
-  BandArc *af = reinterpret_cast<BandArc *>(st + 2 * st_pad);         // [st_pad][3]
-  BandItem *ring = reinterpret_cast<BandItem *>(af + 3 * st_pad);     // [kChainAhead][kRingItems]
-  int32_t *cnt = reinterpret_cast<int32_t *>(ring + kChainAhead * kRingItems);  // [lv_pad]
-  for (int32_t l = lane; l < L; l += 32) cnt[l] = counts[f.level_off + l];
-  for (int32_t k = lane; k < 3 * st_pad; k += 32) {
-    BandArc z;
-    z.f = 0.0;
-    z.k = kZeroExp;
-    z.arc = -1;
-    af[k] = k < 3 * S ? tabf[(int64_t)f.state_off * 3 + k] : z;
+  if (dir == 0 && lane == 0) {
+    tot[i] = -INFINITY;
+    BandTotal z;
+    z.m = 0.0;
+    z.e = 0;
+    z.pad = 0;
+    total[i] = z;
   }
+  if (S == 0) return;
+  BandItem *ring = reinterpret_cast<BandItem *>(smem_raw);                 // [slots][kSlotItems]
+  int2 *lst = reinterpret_cast<int2 *>(ring + kChainSlots * kSlotItems);   // [lv_pad]
+  // alpha: [2][st_pad] by state (s at s + 2); beta: [2][st_pad][3] products by state
+  double *vals = reinterpret_cast<double *>(lst + lv_pad);
+  for (int32_t l = lane; l < L; l += 32) lst[l] = lists[f.level_off + l];
+  const int32_t buf_elems = st_pad * (dir == 0 ? 1 : 3);
+  for (int32_t k = lane; k < 2 * buf_elems; k += 32) vals[k] = 0.0;
+  if (lane == 0) {
+    for (int st = 0; st < kChainSlots; ++st) MbarInit(&full[st], 1);
+    MbarInitFence();
+  }
+  __syncwarp();
+  ChunkRing rg;
+  rg.full = full;
+  rg.slots = ring;
+  rg.items0 = items + f.grid_off;
+  rg.lst = lst;
+  rg.pitch = pitch;
+  rg.L = L;
+  rg.num_chunks = (L + kPrepLevels - 1) / kPrepLevels;
+  rg.dir = dir;
+  rg.issued = 0;
+  if (lane == 0)
+    for (int32_t k = 0; k < kChainSlots; ++k) rg.Issue();
+  double *om = (dir == 0 ? am : bm) + f.grid_off;
+  int32_t *oscale = (dir == 0 ? a_scale : b_scale) + f.level_off;
+  // The first level holds one state with the value 1: the start state walking forward,
+  // the final state walking backward.  It is written here, so that the loop below has no
+  // special case; the loop then skips the first level of the first chunk.
+  {
+    const int32_t l0 = dir == 0 ? 0 : L - 1;
+    const int2 ls = lst[l0];
+    if (lane < ls.y) {  // the list has at most that one state
+      const BandItem it = rg.items0[ls.x + lane];
+      const double v = it.s == (dir == 0 ? 0 : S - 1) ? 1.0 : 0.0;
+      om[ls.x + lane] = v;
+      if (dir == 0) {
+        vals[2 + it.s] = v;
+      } else {
+        double *o = vals + 6 + 3 * it.s;
+        o[0] = it.pw[0] * v;
+        o[1] = it.pw[1] * v;
+        o[2] = it.pw[2] * v;
+      }
+    }
+    if (lane == 0) oscale[l0] = 0;
+  }
+  __syncwarp();
+  int32_t Ksh = 0;       // the stored values of a level are divided by 2^Ksh
+  int32_t hi_max = 0;    // largest high word among the values since the last rescaling
+  bool bad = false, late = false;
+  int32_t step = 1;      // levels done; buffer (step & 1) receives the level of this step
+  for (int32_t q = 0; q < rg.num_chunks; ++q) {
+    const int32_t c = rg.ChunkOf(q), slot = q % kChainSlots;
+    if (!late) late = !WaitSlot(&full[slot], (unsigned)(q / kChainSlots) & 1u, wait_limit);
+    // a list that did not arrive must not be walked (its state numbers index shared memory)
+    late = __any_sync(kAll, late);
+    if (late) break;
+    const int32_t chunk_start = c * kPrepLevels * pitch;
+    const int32_t l_lo = c * kPrepLevels, nl = min(l_lo + kPrepLevels, L) - l_lo;
+    // a chunk beyond the slot's capacity is read from global memory
+    const bool fits = rg.ChunkItems(c) <= kSlotItems;
+    const BandItem *src = fits ? ring + (size_t)slot * kSlotItems - chunk_start : rg.items0;
+    const int32_t k0 = q == 0 ? 1 : 0;  // the very first level is done
+    const int32_t dl = dir == 0 ? 1 : -1;
+    int32_t l = dir == 0 ? l_lo + k0 : l_lo + nl - 1 - k0;
+    int2 ls = make_int2(0, 0);
+    BandItem it;
+    it.s = 0;
+    if (k0 < nl) {
+      ls = lst[l];
+      if (lane < ls.y) it = src[ls.x + lane];
+    }
+#pragma unroll 2
+    for (int32_t k = k0; k < nl; ++k, ++step, l += dl) {
+      // ---- the next level's entry is requested before this level's arithmetic --------
+      int2 ls_next = make_int2(0, 0);
+      BandItem it_next;
+      it_next.s = 0;
+      if (k + 1 < nl) {
+        ls_next = lst[l + dl];
+        if (lane < ls_next.y) it_next = src[ls_next.x + lane];
+      }
+      double *cur = vals + (step & 1) * buf_elems;
+      const double *prv = vals + ((step & 1) ^ 1) * buf_elems;
+      // every kRescale-th step the scale follows the largest value since the last time
+      double scale = 1.0;
+      if ((step & (kRescale - 1)) == 0) {
+        const int32_t hm = __reduce_max_sync(kAll, hi_max);
+        const int32_t e = hm > 0 ? (hm >> 20) - 1023 : 0;
+        Ksh += e;
+        scale = __longlong_as_double((long long)(1023 - e) << 52);
+        hi_max = 0;
+      }
+      if (lane == 0) oscale[l] = Ksh;
+      for (int32_t j = lane; j < ls.y; j += 32) {
+        if (j >= 32) it = src[ls.x + j];  // a level of more than 32 states
+        const int32_t s = it.s;
+        double v;
+        if (dir == 0) {
+          const double *p = prv + 2 + s;
+          v = fma(it.pw[2], p[-2], fma(it.pw[1], p[-1], it.pw[0] * p[0])) * scale;
+          cur[2 + s] = v;
+        } else {
+          const double *p = prv + 6 + 3 * s;
+          const double c0 = p[0], c1 = p[4], c2 = p[8];
+          v = ((it.outb & 1u ? c0 : 0.0) + (it.outb & 2u ? c1 : 0.0) +
+               (it.outb & 4u ? c2 : 0.0)) * scale;
+          double *o = cur + 6 + 3 * s;
+          o[0] = it.pw[0] * v;
+          o[1] = it.pw[1] * v;
+          o[2] = it.pw[2] * v;
+        }
+        om[ls.x + j] = v;
+        const int32_t hi = __double2hiint(v);  // v >= 0
+        hi_max = max(hi_max, hi);
+        // a listed state whose entering arcs all fail their tests is a true zero; any other
+        // value must keep clear of the ends of a double's range
+        bad |= v != 0.0 && (uint32_t)(hi - ((1023 - 900) << 20)) >= (uint32_t)(1800 << 20);
+      }
+      __syncwarp();  // the level is complete
+      ls = ls_next;
+      it = it_next;
+    }
+    if (lane == 0) rg.Issue();  // the chunk is done with: its slot takes the next one
+  }
+  if (late) {
+    if (lane == 0) {
+      atomicOr(status, kStatusLate);
+      rg.Drain();
+    }
+    __syncwarp();
+  }
+  if (__any_sync(kAll, bad) && lane == 0) atomicOr(&unfit[i], kUnfitRange);
+  if (dir == 0 && lane == 0) {
+    // alpha of the final state on the last level, if that state survived
+    const int2 ls = lst[L - 1];
+    const double v = ls.y > 0 ? vals[((step - 1) & 1) * buf_elems + 2 + (S - 1)] : 0.0;
+    if (*status & kStatusLate) {
+      tot[i] = nan("");
+    } else if (!late && v > 0.0 && rg.items0[ls.x].s == S - 1) {
+      tot[i] = log(v) + (double)Ksh * 0.69314718055994530942;
+      BandTotal z;
+      z.m = v;
+      z.e = Ksh;
+      z.pad = 0;
+      total[i] = z;
+    }
+  }
+}
+
+// The same recursion with a (mantissa, exponent) pair per state, for the graphs marked in
+// `unfit`; every other graph returns at once.  exp(dense score) is recomputed from the
+// log-probs, the arc factors come from the graph's tables: no range limit.
+__global__ void __launch_bounds__(32)
+BandChainExact(const BandInfo *__restrict__ infos, const BandArc *__restrict__ tabf,
+               const float *__restrict__ lp, int32_t C, const BandItem *__restrict__ items,
+               const int2 *__restrict__ lists, double *__restrict__ am,
+               int32_t *__restrict__ ae, double *__restrict__ bm, int32_t *__restrict__ be,
+               double *__restrict__ tot, BandTotal *__restrict__ total,
+               const int32_t *__restrict__ unfit, int32_t *__restrict__ status, int32_t st_pad,
+               int32_t lv_pad, int32_t wait_limit) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  __shared__ __align__(8) uint64_t full[kChainSlots];
+  constexpr unsigned kAll = 0xffffffffu;
+  const int dir = blockIdx.x;
+  const int32_t i = blockIdx.y;
+  if (unfit[i] == 0) return;  // the lean recursion served this graph
+  const BandInfo f = infos[i];
+  const int lane = threadIdx.x;
+  const int32_t S = f.num_states, T = f.frames, pitch = f.pitch, L = T + 2;
+  if (S == 0) return;
+  BandItem *ring = reinterpret_cast<BandItem *>(smem_raw);
+  int2 *lst = reinterpret_cast<int2 *>(ring + kChainSlots * kSlotItems);
+  ProbState *vals = reinterpret_cast<ProbState *>(lst + lv_pad);  // [2][st_pad], state s at s + 2
+  for (int32_t l = lane; l < L; l += 32) lst[l] = lists[f.level_off + l];
   for (int32_t k = lane; k < 2 * st_pad; k += 32) {
     ProbState z;
     z.m = 0.0;
     z.e = kZeroExp;
     z.pad = 0;
-    st[k] = z;
+    vals[k] = z;
+  }
+  if (lane == 0) {
+    for (int st = 0; st < kChainSlots; ++st) MbarInit(&full[st], 1);
+    MbarInitFence();
   }
   __syncwarp();
-  const BandItem *items0 = items + f.grid_off;
-  auto level_of = [&](int32_t step) { return dir == 0 ? step : L - 1 - step; };
-  auto prefetch = [&](int32_t step) {
-    if (step < L) {
-      const int32_t l = level_of(step);
-      const int32_t n = min(cnt[l], kRingItems);
-      const BandItem *src = items0 + (int64_t)l * pitch;
-      BandItem *dst = ring + (step % kChainAhead) * kRingItems;
-      for (int32_t j = lane; j < n; j += 32) CpAsync16(dst + j, src + j);
-    }
-    CpAsyncCommit();
-  };
-  for (int32_t step = 0; step < kChainAhead - 1; ++step) prefetch(step);
+  ChunkRing rg;
+  rg.full = full;
+  rg.slots = ring;
+  rg.items0 = items + f.grid_off;
+  rg.lst = lst;
+  rg.pitch = pitch;
+  rg.L = L;
+  rg.num_chunks = (L + kPrepLevels - 1) / kPrepLevels;
+  rg.dir = dir;
+  rg.issued = 0;
+  if (lane == 0)
+    for (int32_t k = 0; k < kChainSlots; ++k) rg.Issue();
+  const float *lp0 = lp + (int64_t)f.lp_row * C;
+  const BandArc *my_arcs = tabf + (int64_t)f.state_off * 3;
   double *om = (dir == 0 ? am : bm) + f.grid_off;
   int32_t *oe = (dir == 0 ? ae : be) + f.grid_off;
-  for (int32_t step = 0; step < L; ++step) {
-    prefetch(step + kChainAhead - 1);
-    CpAsyncWait<kChainAhead - 1>();
-    const int32_t l = level_of(step);
-    const int32_t n = cnt[l];
-    ProbState *cur = st + (step & 1) * st_pad + 2;
-    const ProbState *prv = st + ((step & 1) ^ 1) * st_pad + 2;
-    const BandItem *slot = ring + (step % kChainAhead) * kRingItems;
-    const int64_t row = (int64_t)l * pitch;
-    for (int32_t j0 = 0; j0 < n; j0 += 32) {
-      const int32_t j = j0 + lane;
-      if (j < n) {
-        const BandItem it = j < kRingItems ? slot[j] : items0[row + j];
+  bool late = false;
+  int32_t step = 0;
+  for (int32_t q = 0; q < rg.num_chunks; ++q) {
+    const int32_t c = rg.ChunkOf(q), slot = q % kChainSlots;
+    if (!late) late = !WaitSlot(&full[slot], (unsigned)(q / kChainSlots) & 1u, wait_limit);
+    late = __any_sync(kAll, late);
+    if (late) break;
+    const int32_t chunk_start = c * kPrepLevels * pitch;
+    const int32_t l_lo = c * kPrepLevels, nl = min(l_lo + kPrepLevels, L) - l_lo;
+    const bool fits = rg.ChunkItems(c) <= kSlotItems;
+    const BandItem *src = fits ? ring + (size_t)slot * kSlotItems - chunk_start : rg.items0;
+    for (int32_t k = 0; k < nl; ++k, ++step) {
+      const int32_t l = dir == 0 ? l_lo + k : l_lo + nl - 1 - k;
+      const int2 ls = lst[l];
+      ProbState *cur = vals + (step & 1) * st_pad + 2;
+      const ProbState *prv = vals + ((step & 1) ^ 1) * st_pad + 2;
+      for (int32_t j = lane; j < ls.y; j += 32) {
+        const BandItem it = src[ls.x + j];
         const int32_t s = it.s;
+        // exp(dense score) of this state's label on frame l - 1
+        double pm = 0.0;
+        int32_t pe = kZeroExp;
+        if (l >= 1) ExpToMantExp(BandDense(lp0, C, T, l - 1, it.label), &pm, &pe);
         double m;
         int32_t e;
         if (step == 0) {
@@ -585,44 +932,60 @@ BandChain(const BandInfo *__restrict__ infos, const BandArc *__restrict__ tabf,
           int32_t x[3];
 #pragma unroll
           for (int d = 0; d < 3; ++d) {
-            const ProbState q = dir == 0 ? prv[s - d] : prv[s + d];
-            const BandArc arc = dir == 0 ? af[3 * s + d] : af[3 * (s + d) + d];
-            double td = q.m * arc.f;
-            td = (bits >> d) & 1u ? td : 0.0;
-            t[d] = td;
-            x[d] = td != 0.0 ? q.e + arc.k : kZeroExp;
+            // forward: alpha of the source; backward: beta * p of the destination
+            t[d] = 0.0;
+            x[d] = kZeroExp;
+            if ((bits >> d) & 1u) {  // the bit names an arc of this graph
+              const ProbState qs = dir == 0 ? prv[s - d] : prv[s + d];
+              const BandArc arc = dir == 0 ? my_arcs[3 * s + d] : my_arcs[3 * (s + d) + d];
+              t[d] = qs.m * arc.f;
+              if (t[d] != 0.0) x[d] = qs.e + arc.k;
+            }
           }
           const int32_t E = max(x[0], max(x[1], x[2]));
           const double sum =
               ScaleDown(t[0], x[0] - E) + ScaleDown(t[1], x[1] - E) + ScaleDown(t[2], x[2] - E);
           e = E;
           if (dir == 0) {
-            e += it.pe;
-            m = Renorm(sum * it.pm, &e);
+            e += pe;
+            m = Renorm(sum * pm, &e);
           } else {
             m = Renorm(sum, &e);
           }
         }
-        om[row + j] = m;
-        oe[row + j] = e;
+        om[ls.x + j] = m;
+        oe[ls.x + j] = e;
         ProbState r;
         r.pad = 0;
         if (dir == 0) {
           r.m = m;
           r.e = e;
-          if (l == T + 1 && s == S - 1)
+          if (l == T + 1 && s == S - 1) {
             tot[i] = m == 0.0 ? -INFINITY : log(m) + (double)e * 0.69314718055994530942;
+            BandTotal z;
+            z.m = m;
+            z.e = e;
+            z.pad = 0;
+            total[i] = z;
+          }
         } else {  // what the level below adds: beta * p
-          r.e = e + it.pe;
-          r.m = Renorm(m * it.pm, &r.e);
+          r.e = e + pe;
+          r.m = Renorm(m * pm, &r.e);
         }
         cur[s] = r;
       }
+      __syncwarp();  // the level is complete
+    }
+    if (lane == 0) rg.Issue();
+  }
+  if (late) {
+    if (lane == 0) {
+      atomicOr(status, kStatusLate);
+      rg.Drain();
     }
     __syncwarp();
   }
-  CpAsyncWait<0>();
-  if (dir == 0 && lane == 0 && *status != 0) tot[i] = nan("");
+  if (dir == 0 && lane == 0 && (*status & kStatusLate)) tot[i] = nan("");
 }
 
 // ---------------------------------------------------------------------------
@@ -634,97 +997,118 @@ BandChain(const BandInfo *__restrict__ infos, const BandArc *__restrict__ tabf,
 // alpha_{l-1}[src] e^w p_l[dest] beta_l[dest] / Z, is added to grad_a[arc]; the warp keeps
 // alpha of the level before by state number in shared memory for that.
 // ---------------------------------------------------------------------------
-__device__ __forceinline__ double Pow2Clamp(int32_t e) {
-  if (e < -1000) return 0.0;
-  e = e > 1000 ? 1000 : e;
-  return __longlong_as_double((long long)(1023 + e) << 52);
-}
-
 template <bool kArcs>
 __global__ void __launch_bounds__(128)
-BandGrad(const BandInfo *__restrict__ infos, const BandState *__restrict__ tab,
-         const BandArc *__restrict__ tabf, const BandItem *__restrict__ items,
-         const int32_t *__restrict__ counts, const double *__restrict__ am,
+BandGrad(const BandInfo *__restrict__ infos, const BandArc *__restrict__ tabf,
+         const float *__restrict__ lp, const BandItem *__restrict__ items,
+         const int2 *__restrict__ lists, const double *__restrict__ am,
          const int32_t *__restrict__ ae, const double *__restrict__ bm,
-         const int32_t *__restrict__ be, const double *__restrict__ tot_grad,
+         const int32_t *__restrict__ be, const int32_t *__restrict__ a_scale,
+         const int32_t *__restrict__ b_scale, const BandTotal *__restrict__ total,
+         const int32_t *__restrict__ unfit, const double *__restrict__ tot_grad,
          int32_t tot_grad_stride, float *__restrict__ grad_a, float *__restrict__ grad_b,
          const int32_t *__restrict__ grad_row0, int32_t grad_pitch, int32_t grad_col_off,
-         int32_t C, int32_t st_pad, int32_t exclusive_rows) {
+         int32_t C, int32_t st_pad) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   constexpr unsigned kAll = 0xffffffffu;
   const int32_t i = blockIdx.y;
   const BandInfo f = infos[i];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const int32_t S = f.num_states, T = f.frames, pitch = f.pitch;
+  const int32_t S = f.num_states, T = f.frames;
   if (S == 0) return;
   const int32_t a = 1 + (blockIdx.x * 4 + warp) * kGradLevels;  // levels a .. b - 1
   if (a > T + 1) return;
   const int32_t b = min(a + kGradLevels, T + 2);
-  const int32_t *cnt = counts + f.level_off;
+  const BandTotal z = total[i];
+  if (z.m == 0.0) return;  // no path survives: all gradients are zero
+  const double zinv = 1.0 / z.m;
+  const bool exact = unfit[i] != 0;  // per-state exponents instead of per-level scales
+  const int2 *lst = lists + f.level_off;
   const BandItem *items0 = items + f.grid_off;
   const double *am0 = am + f.grid_off, *bm0 = bm + f.grid_off;
   const int32_t *ae0 = ae + f.grid_off, *be0 = be + f.grid_off;
-  // Z = alpha of the final state on the last level: the last entry of that level's list
-  const int32_t n_last = cnt[T + 1];
-  if (n_last == 0) return;
-  const int64_t zpos = (int64_t)(T + 1) * pitch + n_last - 1;
-  if (items0[zpos].s != S - 1) return;
-  const double zm = am0[zpos];
-  if (zm == 0.0) return;
-  const double zinv = 1.0 / zm;
-  const int32_t ze = ae0[zpos];
+  const int32_t *as0 = a_scale + f.level_off, *bs0 = b_scale + f.level_off;
   const double tg = tot_grad[(int64_t)i * tot_grad_stride];
   const int64_t row0 = grad_row0[i];
+  const float *lp0 = lp + (int64_t)f.lp_row * C;
   ProbState *prev = nullptr;  // alpha of the level before, state s at s + 2
-  if (kArcs) {
-    prev = reinterpret_cast<ProbState *>(smem_raw) + (size_t)warp * st_pad + 2;
-    const int32_t l = a - 1, n = cnt[l];
+  auto stage_alpha = [&](int32_t l) {
+    const int32_t n = lst[l].y;
+    const int64_t row = lst[l].x;
     for (int32_t j = lane; j < n; j += 32) {
       ProbState q;
-      q.m = am0[(int64_t)l * pitch + j];
-      q.e = ae0[(int64_t)l * pitch + j];
+      q.m = am0[row + j];
+      q.e = exact ? ae0[row + j] : as0[l];
       q.pad = 0;
-      prev[items0[(int64_t)l * pitch + j].s] = q;
+      prev[items0[row + j].s] = q;
     }
+  };
+  if (kArcs) {
+    prev = reinterpret_cast<ProbState *>(smem_raw) + (size_t)warp * st_pad + 2;
+    stage_alpha(a - 1);
     __syncwarp();
   }
-  for (int32_t l = a; l < b; ++l) {
-    const int32_t n = cnt[l];
-    const int64_t row = (int64_t)l * pitch;
+  // the first 32 entries of the chunk's levels are requested together, before any is used
+  int2 ls4[kGradLevels];
+  BandItem it4[kGradLevels];
+  double al4[kGradLevels], be4[kGradLevels];
+#pragma unroll
+  for (int u = 0; u < kGradLevels; ++u) {
+    ls4[u] = a + u < b ? lst[a + u] : make_int2(0, 0);
+    al4[u] = be4[u] = 0.0;
+    it4[u].s = 0;
+  }
+#pragma unroll
+  for (int u = 0; u < kGradLevels; ++u)
+    if (lane < ls4[u].y) {
+      it4[u] = items0[ls4[u].x + lane];
+      al4[u] = am0[ls4[u].x + lane];
+      be4[u] = bm0[ls4[u].x + lane];
+    }
+#pragma unroll
+  for (int u = 0; u < kGradLevels; ++u) {
+    const int32_t l = a + u;
+    if (l >= b) break;
+    const int32_t n = ls4[u].y;
+    const int64_t row = ls4[u].x;
+    const int32_t ea_l = as0[l], eb_l = bs0[l];
     for (int32_t j0 = 0; j0 < n; j0 += 32) {
       const int32_t j = j0 + lane;
       float g = 0.0f;
       int32_t key = -1 - lane;  // lanes with nothing to add are groups of their own
       if (j < n) {
-        const BandItem it = items0[row + j];
-        const double alm = am0[row + j], bem = bm0[row + j];
+        const BandItem it = j0 == 0 ? it4[u] : items0[row + j];
+        const double alm = j0 == 0 ? al4[u] : am0[row + j], bem = j0 == 0 ? be4[u] : bm0[row + j];
         if (alm != 0.0 && bem != 0.0) {
-          const int32_t ale = ae0[row + j], bee = be0[row + j];
-          const int32_t s = it.s;
-          const int32_t label = tab[f.state_off + s].label;
-          const int32_t col = label + grad_col_off;
-          if (label != kNoLabel && label < C && col >= 0) {
-            const double post = alm * bem * zinv * Pow2Clamp(ale + bee - ze);
+          const int32_t ale = exact ? ae0[row + j] : ea_l, bee = exact ? be0[row + j] : eb_l;
+          const int32_t col = it.label + grad_col_off;
+          if (it.label != kNoLabel && it.label < C && col >= 0) {
+            const double post = alm * bem * zinv * Pow2Clamp(ale + bee - z.e);
             g = (float)(tg * post);
             key = col;
           }
           if (kArcs) {
+            const int32_t s = it.s;
+            double pm;
+            int32_t pe;
+            ExpToMantExp(BandDense(lp0, C, T, l - 1, it.label), &pm, &pe);
 #pragma unroll
             for (int d = 0; d < 3; ++d) {
               if (!((it.inb >> d) & 1u)) continue;
               const ProbState q = prev[s - d];
               const BandArc arc = tabf[(int64_t)(f.state_off + s) * 3 + d];
               // two steps, so that no intermediate product leaves the range of a double
-              const double post = (q.m * arc.f * it.pm) * (bem * zinv) *
-                                  Pow2Clamp(q.e + arc.k + it.pe + bee - ze);
+              const double post = (q.m * arc.f * pm) * (bem * zinv) *
+                                  Pow2Clamp(q.e + arc.k + pe + bee - z.e);
               if (post != 0.0) atomicAdd(grad_a + arc.arc, (float)(tg * post));
             }
           }
         }
       }
       // States with the same label (the blank states of a CTC graph) add to the same
-      // element: their lanes are summed in lane order and one of them writes, so the
-      // dense gradient does not depend on the order in which atomics would land.
+      // element: their lanes are summed in lane order and one of them adds the sum, so
+      // an element receives one addition per 32 states of a level, from one warp, in
+      // program order.
       const uint32_t grp = __match_any_sync(kAll, key);
       const int32_t members = __popc(grp);
       const int32_t rounds = __reduce_max_sync(kAll, key >= 0 ? members : 0);
@@ -734,21 +1118,12 @@ BandGrad(const BandInfo *__restrict__ infos, const BandState *__restrict__ tab,
         const float v = __shfl_sync(kAll, g, (int)(src & 31u));
         if (r < members) sum += v;
       }
-      if (key >= 0 && lane == __ffs(grp) - 1) {
-        float *p = grad_b + (row0 + l - 1) * grad_pitch + key;
-        if (exclusive_rows) *p += sum; else atomicAdd(p, sum);
-      }
-      __syncwarp();  // a later part of the level may add to the same elements
+      if (key >= 0 && lane == __ffs(grp) - 1 && sum != 0.0f)
+        atomicAdd(grad_b + (row0 + l - 1) * grad_pitch + key, sum);
     }
     if (kArcs) {
       __syncwarp();  // the level before has been read
-      for (int32_t j = lane; j < n; j += 32) {
-        ProbState q;
-        q.m = am0[row + j];
-        q.e = ae0[row + j];
-        q.pad = 0;
-        prev[items0[row + j].s] = q;
-      }
+      stage_alpha(l);
       __syncwarp();
     }
   }
@@ -762,11 +1137,12 @@ struct BandLayout {
   int64_t grid_elems = 0, levels = 0;
   long long arc_frames = 0;
   int32_t max_states = 0, max_frames = 0;
-  int K = 4;
-  int32_t depth = 0, slot_floats = 0, st_pad = 0, lv_pad = 0;
-  size_t chain_smem = 0, viterbi_smem = 0;
-  size_t off_infos, off_vf, off_vb, off_items, off_counts, off_cutoffs, off_am, off_ae, off_bm,
-      off_be, off_totals, off_status, total_bytes;  // off_status = off_totals + 40
+  int32_t vit_threads = 32, vit_frames = 0, vit_batches = 0, xch_pad = 0;
+  int32_t st_pad = 0, lv_pad = 0;
+  size_t chain_smem = 0, viterbi_smem = 0, prep_smem = 0;
+  size_t off_infos, off_vf, off_vb, off_items, off_lists, off_cutoffs, off_am, off_ae, off_bm,
+      off_be, off_a_scale, off_b_scale, off_total, off_unfit, off_totals, off_status,
+      total_bytes;  // off_status = off_totals + 40
   bool ok = true;
   const char *why = "";
   bool exclusive_rows = true;  // no two graphs on one sequence (they would share gradient rows)
@@ -787,7 +1163,7 @@ static int32_t MakeBandLayout(const k2b200_band_loss_args *a, BandLayout *L) {
     BandInfo &f = L->infos[i];
     f.state_off = a->h_a_row_splits1[i];
     f.num_states = a->h_a_row_splits1[i + 1] - f.state_off;
-    f.pitch = (f.num_states + 3) & ~3;
+    f.pitch = std::max((f.num_states + 3) & ~3, 4);
     f.frames = a->h_frames[i];
     K2B_REQUIRE(f.frames >= 0, "sequence of graph %d has a negative number of frames", i);
     if (i > 0)
@@ -814,25 +1190,36 @@ static int32_t MakeBandLayout(const k2b200_band_loss_args *a, BandLayout *L) {
   }
   L->grid_elems = grid;
   L->levels = levels;
-  L->K = L->max_states <= 128 ? 4 : (L->max_states <= 256 ? 8 : 16);
-  // shared memory of the kernels
-  L->slot_floats = 4 + ((a->num_classes + 3) & ~3);
-  const size_t slot_bytes = sizeof(float) * (size_t)L->slot_floats;
-  L->depth = (int32_t)std::min<size_t>(kBandMaxDepth, kBandSmemBudget / slot_bytes);
-  L->viterbi_smem = slot_bytes * (size_t)std::max(L->depth, 1);
+  // BandViterbi: frames per batch (even, at most 16) so that at least two batches of rows
+  // fit in shared memory, up to three batches within ~100 KB so that two CTAs share an SM
+  {
+    const size_t row_bytes = sizeof(float) * (size_t)a->num_classes;
+    int32_t F = 16;
+    while (F > 2 && 2 * F * row_bytes > kBandSmemBudget - 8192) F >>= 1;
+    L->vit_frames = F;
+    L->vit_batches = (int32_t)std::max<size_t>(
+        2, std::min<size_t>(3, (100 * 1024) / std::max<size_t>(F * row_bytes, 1)));
+    const int32_t own_states = (32 - F / 2) * kVitK;
+    const int32_t warps = std::max(1, CeilDiv(std::max(L->max_states, 1), own_states));
+    L->vit_threads = 32 * warps;
+    L->xch_pad = (warps * own_states + 4 * kVitK * (F / 2) + 3) & ~3;
+    L->viterbi_smem = (size_t)L->vit_batches * F * row_bytes + sizeof(float) * 2 * (size_t)L->xch_pad;
+    if (warps > kVitMaxWarps || 2 * F * row_bytes > kBandSmemBudget - 8192) {
+      L->ok = false;
+      L->why = "too many states or classes for the Viterbi kernel";
+    }
+  }
   L->st_pad = ((L->max_states + 4) + 3) & ~3;
   L->lv_pad = (L->max_frames + 2 + 3) & ~3;
-  L->chain_smem = sizeof(ProbState) * 2 * (size_t)L->st_pad + sizeof(BandArc) * 3 * (size_t)L->st_pad +
-                  sizeof(BandItem) * kChainAhead * kRingItems + sizeof(int32_t) * (size_t)L->lv_pad;
+  L->prep_smem = (size_t)4 * 5 * L->st_pad;
+  L->chain_smem = sizeof(BandItem) * kChainSlots * kSlotItems + sizeof(int2) * (size_t)L->lv_pad +
+                  (size_t)48 * L->st_pad;
   if (L->max_states > kBandMaxStates) {
     L->ok = false;
     L->why = "a graph has more than 512 states";
   } else if (a->num_classes % 4 != 0 || (reinterpret_cast<uintptr_t>(a->log_probs) & 15) != 0) {
     L->ok = false;
     L->why = "rows of the log-prob matrix are not 16-byte aligned";
-  } else if (L->depth < 2) {
-    L->ok = false;
-    L->why = "too many classes for the row ring";
   } else if (L->chain_smem > kBandSmemBudget) {
     L->ok = false;
     L->why = "too many frames for the level table in shared memory";
@@ -850,47 +1237,19 @@ static int32_t MakeBandLayout(const k2b200_band_loss_args *a, BandLayout *L) {
   L->off_vf = take(sizeof(float) * (size_t)grid);
   L->off_vb = take(sizeof(float) * (size_t)grid);
   L->off_items = take(sizeof(BandItem) * (size_t)grid);
-  L->off_counts = take(sizeof(int32_t) * (size_t)levels);
+  L->off_lists = take(sizeof(int2) * (size_t)levels);
   L->off_cutoffs = take(sizeof(float) * a->num_fsas);
   L->off_am = take(sizeof(double) * (size_t)grid);
   L->off_ae = take(sizeof(int32_t) * (size_t)grid);
   L->off_bm = take(sizeof(double) * (size_t)grid);
   L->off_be = take(sizeof(int32_t) * (size_t)grid);
+  L->off_a_scale = take(sizeof(int32_t) * (size_t)levels);
+  L->off_b_scale = take(sizeof(int32_t) * (size_t)levels);
+  L->off_total = take(sizeof(BandTotal) * a->num_fsas);
+  L->off_unfit = take(sizeof(int32_t) * a->num_fsas);
   L->off_totals = take(64);  // five 64-bit totals, then the status word
   L->off_status = L->off_totals + 5 * sizeof(long long);
   L->total_bytes = off;
-  return kOk;
-}
-
-template <int K>
-static int32_t LaunchBandViterbi(const BandLayout &L, const k2b200_band_loss_args *a, char *ws,
-                                 cudaStream_t stream) {
-  K2B_CUDA_OK(cudaFuncSetAttribute(BandViterbi<K>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                   (int)L.viterbi_smem));
-  dim3 grid(2, a->num_fsas);
-  { BandViterbi<K><<<grid, 32, L.viterbi_smem, stream>>>(
-      reinterpret_cast<const BandInfo *>(ws + L.off_infos),
-      reinterpret_cast<const BandState *>(a->band_states), a->log_probs, a->num_classes,
-      reinterpret_cast<float *>(ws + L.off_vf), reinterpret_cast<float *>(ws + L.off_vb), L.depth,
-      L.slot_floats, g_wait_limit, reinterpret_cast<int32_t *>(ws + L.off_status)); NoteLaunch(); }
-  K2B_CUDA_OK(cudaGetLastError());
-  return kOk;
-}
-
-template <int K>
-static int32_t LaunchBandPrep(const BandLayout &L, const k2b200_band_loss_args *a, char *ws,
-                              float beam, cudaStream_t stream) {
-  dim3 grid(CeilDiv(L.max_frames + 2, 4 * kPrepLevels), a->num_fsas);
-  { BandPrep<K><<<grid, 128, 0, stream>>>(
-      reinterpret_cast<const BandInfo *>(ws + L.off_infos),
-      reinterpret_cast<const BandState *>(a->band_states), a->a_row_splits2, a->log_probs,
-      a->num_classes, reinterpret_cast<const float *>(ws + L.off_vf),
-      reinterpret_cast<const float *>(ws + L.off_vb), beam,
-      reinterpret_cast<BandItem *>(ws + L.off_items),
-      reinterpret_cast<int32_t *>(ws + L.off_counts),
-      reinterpret_cast<float *>(ws + L.off_cutoffs),
-      reinterpret_cast<unsigned long long *>(ws + L.off_totals)); NoteLaunch(); }
-  K2B_CUDA_OK(cudaGetLastError());
   return kOk;
 }
 
@@ -912,6 +1271,33 @@ static bool BandReduceBeam(const k2b200_band_loss_args *a, const long long *h_to
   if (next > cur * 0.75) next = cur * 0.75;
   *beam = next;
   return true;
+}
+
+static int32_t LaunchBandChains(const BandLayout &L, const k2b200_band_loss_args *args, char *ws,
+                                double *tot_scores, cudaStream_t stream) {
+  K2B_CUDA_OK(cudaFuncSetAttribute(BandChainLean, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                   (int)L.chain_smem));
+  K2B_CUDA_OK(cudaFuncSetAttribute(BandChainExact, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                   (int)L.chain_smem));
+  dim3 grid(2, args->num_fsas);
+  const BandInfo *infos = reinterpret_cast<const BandInfo *>(ws + L.off_infos);
+  const BandItem *items = reinterpret_cast<const BandItem *>(ws + L.off_items);
+  const int2 *lists = reinterpret_cast<const int2 *>(ws + L.off_lists);
+  double *am = reinterpret_cast<double *>(ws + L.off_am), *bm = reinterpret_cast<double *>(ws + L.off_bm);
+  BandTotal *total = reinterpret_cast<BandTotal *>(ws + L.off_total);
+  int32_t *unfit = reinterpret_cast<int32_t *>(ws + L.off_unfit);
+  int32_t *status = reinterpret_cast<int32_t *>(ws + L.off_status);
+  { BandChainLean<<<grid, 32, L.chain_smem, stream>>>(
+      infos, items, lists, am, bm, reinterpret_cast<int32_t *>(ws + L.off_a_scale),
+      reinterpret_cast<int32_t *>(ws + L.off_b_scale), tot_scores, total, unfit, status, L.st_pad,
+      L.lv_pad, g_wait_limit); NoteLaunch(); }
+  { BandChainExact<<<grid, 32, L.chain_smem, stream>>>(
+      infos, reinterpret_cast<const BandArc *>(args->band_arcs), args->log_probs,
+      args->num_classes, items, lists, am, reinterpret_cast<int32_t *>(ws + L.off_ae), bm,
+      reinterpret_cast<int32_t *>(ws + L.off_be), tot_scores, total, unfit, status, L.st_pad,
+      L.lv_pad, g_wait_limit); NoteLaunch(); }
+  K2B_CUDA_OK(cudaGetLastError());
+  return kOk;
 }
 
 }  // namespace k2b
@@ -988,9 +1374,16 @@ int32_t k2b200_band_loss_forward(const k2b200_band_loss_args *args, void *worksp
   {
     PhaseTimer timer(kPhaseViterbi, stream);
     NotePhaseKernel(kPhaseViterbi, "BandViterbi");
-    if (L.K == 4) K2B_FORWARD(LaunchBandViterbi<4>(L, args, ws, stream));
-    else if (L.K == 8) K2B_FORWARD(LaunchBandViterbi<8>(L, args, ws, stream));
-    else K2B_FORWARD(LaunchBandViterbi<16>(L, args, ws, stream));
+    K2B_CUDA_OK(cudaFuncSetAttribute(BandViterbi, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     (int)L.viterbi_smem));
+    dim3 grid(2, args->num_fsas);
+    { BandViterbi<<<grid, L.vit_threads, L.viterbi_smem, stream>>>(
+        reinterpret_cast<const BandInfo *>(ws + L.off_infos),
+        reinterpret_cast<const BandState *>(args->band_states), args->log_probs,
+        args->num_classes, reinterpret_cast<float *>(ws + L.off_vf),
+        reinterpret_cast<float *>(ws + L.off_vb), L.vit_frames, L.vit_batches, L.xch_pad,
+        g_wait_limit, reinterpret_cast<int32_t *>(ws + L.off_status)); NoteLaunch(); }
+    K2B_CUDA_OK(cudaGetLastError());
   }
   // The lattice is never built, but its size still decides the beam
   // (intersect_dense.cu:300-320).  The grid bounds it: the host reads the counts only
@@ -998,38 +1391,37 @@ int32_t k2b200_band_loss_forward(const k2b200_band_loss_args *args, void *worksp
   // recursions, which in the rare case of a reduction run again.
   const bool need_count = L.grid_elems > args->max_states || L.arc_frames > args->max_arcs;
   float beam = args->output_beam;
-  K2B_CUDA_OK(cudaFuncSetAttribute(BandChain, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                   (int)L.chain_smem));
   for (int iter = 0;; ++iter) {
     K2B_CUDA_OK(cudaMemsetAsync(ws + L.off_totals, 0, 5 * sizeof(long long), stream));
+    K2B_CUDA_OK(cudaMemsetAsync(ws + L.off_unfit, 0, sizeof(int32_t) * args->num_fsas, stream));
     {
       PhaseTimer timer(kPhasePrune, stream);
       NotePhaseKernel(kPhasePrune, "BandPrep");
-      if (L.K == 4) K2B_FORWARD(LaunchBandPrep<4>(L, args, ws, beam, stream));
-      else if (L.K == 8) K2B_FORWARD(LaunchBandPrep<8>(L, args, ws, beam, stream));
-      else K2B_FORWARD(LaunchBandPrep<16>(L, args, ws, beam, stream));
+      dim3 grid(CeilDiv(L.max_frames + 2, 4 * kPrepLevels), args->num_fsas);
+      { BandPrep<<<grid, 128, L.prep_smem, stream>>>(
+          reinterpret_cast<const BandInfo *>(ws + L.off_infos),
+          reinterpret_cast<const BandState *>(args->band_states),
+          reinterpret_cast<const BandArc *>(args->band_arcs), args->a_row_splits2,
+          args->log_probs, args->num_classes, reinterpret_cast<const float *>(ws + L.off_vf),
+          reinterpret_cast<const float *>(ws + L.off_vb), beam,
+          reinterpret_cast<BandItem *>(ws + L.off_items),
+          reinterpret_cast<int2 *>(ws + L.off_lists),
+          reinterpret_cast<float *>(ws + L.off_cutoffs),
+          reinterpret_cast<unsigned long long *>(ws + L.off_totals),
+          reinterpret_cast<int32_t *>(ws + L.off_unfit), L.st_pad); NoteLaunch(); }
+      K2B_CUDA_OK(cudaGetLastError());
     }
     cudaStream_t side = nullptr;
     if (need_count) K2B_FORWARD(SideFork(stream, &side));  // behind the counts, before the chain
     {
       PhaseTimer timer(kPhaseChain, stream);
       NotePhaseKernel(kPhaseChain, "BandChain");
-      dim3 grid(2, args->num_fsas);
-      { BandChain<<<grid, 32, L.chain_smem, stream>>>(
-          reinterpret_cast<const BandInfo *>(ws + L.off_infos),
-          reinterpret_cast<const BandArc *>(args->band_arcs),
-          reinterpret_cast<const BandItem *>(ws + L.off_items),
-          reinterpret_cast<const int32_t *>(ws + L.off_counts),
-          reinterpret_cast<double *>(ws + L.off_am), reinterpret_cast<int32_t *>(ws + L.off_ae),
-          reinterpret_cast<double *>(ws + L.off_bm), reinterpret_cast<int32_t *>(ws + L.off_be),
-          tot_scores, reinterpret_cast<const int32_t *>(ws + L.off_status), L.st_pad, L.lv_pad);
-        NoteLaunch(); }
-      K2B_CUDA_OK(cudaGetLastError());
+      K2B_FORWARD(LaunchBandChains(L, args, ws, tot_scores, stream));
     }
     if (!need_count) break;
     long long h_totals[6];
     K2B_FORWARD(SideReadBack(ws + L.off_totals, sizeof(h_totals), h_totals));
-    K2B_REQUIRE((h_totals[5] & 2) == 0,
+    K2B_REQUIRE((h_totals[5] & kStatusLate) == 0,
                 "a copy of log-prob rows into shared memory did not complete in time");
     if (!BandReduceBeam(args, h_totals, &beam)) break;
     K2B_REQUIRE(iter < 200, "output beam reduction did not converge");
@@ -1061,16 +1453,18 @@ int32_t k2b200_band_loss_backward(const k2b200_band_loss_args *args, void *works
 #define K2B_BAND_GRAD(ARCS, SMEM)                                                             \
   { BandGrad<ARCS><<<grid, 128, SMEM, stream>>>(                                              \
       reinterpret_cast<const BandInfo *>(ws + L.off_infos),                                   \
-      reinterpret_cast<const BandState *>(args->band_states),                                 \
-      reinterpret_cast<const BandArc *>(args->band_arcs),                                     \
+      reinterpret_cast<const BandArc *>(args->band_arcs), args->log_probs,                    \
       reinterpret_cast<const BandItem *>(ws + L.off_items),                                   \
-      reinterpret_cast<const int32_t *>(ws + L.off_counts),                                   \
+      reinterpret_cast<const int2 *>(ws + L.off_lists),                                       \
       reinterpret_cast<const double *>(ws + L.off_am),                                        \
       reinterpret_cast<const int32_t *>(ws + L.off_ae),                                       \
       reinterpret_cast<const double *>(ws + L.off_bm),                                        \
-      reinterpret_cast<const int32_t *>(ws + L.off_be), tot_grad, tot_grad_stride, grad_a,    \
-      grad_b, grad_row0, grad_pitch, grad_col_off, args->num_classes, L.st_pad,              \
-      L.exclusive_rows ? 1 : 0); NoteLaunch(); }
+      reinterpret_cast<const int32_t *>(ws + L.off_be),                                       \
+      reinterpret_cast<const int32_t *>(ws + L.off_a_scale),                                  \
+      reinterpret_cast<const int32_t *>(ws + L.off_b_scale),                                  \
+      reinterpret_cast<const BandTotal *>(ws + L.off_total),                                  \
+      reinterpret_cast<const int32_t *>(ws + L.off_unfit), tot_grad, tot_grad_stride, grad_a, \
+      grad_b, grad_row0, grad_pitch, grad_col_off, args->num_classes, L.st_pad); NoteLaunch(); }
   if (grad_a != nullptr) {
     const size_t smem = sizeof(ProbState) * 4 * (size_t)L.st_pad;
     K2B_BAND_GRAD(true, smem)

@@ -791,9 +791,11 @@ GridGradWarp(const FsaInfo *__restrict__ infos, const Arc *__restrict__ arcs,
              int32_t tot_grad_stride, float *__restrict__ grad_a, float *__restrict__ grad_b,
              int32_t frames_per_cta, int32_t lanes_log2, int32_t s_pad, int32_t ga_in_smem,
              int32_t exclusive_rows, const int32_t *__restrict__ only_noplan,
-             const int32_t *__restrict__ lp_row, int32_t lp_cols) {
+             const int32_t *__restrict__ lp_row, int32_t lp_cols,
+             const int32_t *__restrict__ served) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   const int32_t i = blockIdx.y;
+  if (served != nullptr && *served) return;  // GridGradStates wrote the gradients
   if (only_noplan != nullptr && !(only_noplan[i] & 1)) return;  // the lane kernel took it
   const FsaInfo f = infos[i];
   const int32_t S = f.num_states, A = f.num_arcs, Tk = f.tk, cols = dp.cols;
@@ -905,6 +907,7 @@ GridGradWarp(const FsaInfo *__restrict__ infos, const Arc *__restrict__ arcs,
           if (prod == 0.0) continue;
           const float post = (float)(prod * Pow2Clamped(e1 + ae + af.k + bexp + zk));
           atomicAdd(&gbrow[c], __float2uint_rn(post * 2147483648.0f));
+          if (grad_a == nullptr) continue;
           if (ga_in_smem) atomicAdd(&ga[k], __float2uint_rn(post * 67108864.0f));
           else atomicAdd(&grad_a[f.arc_off + f.arc_out_off + k], tg * post);
         }
@@ -915,7 +918,7 @@ GridGradWarp(const FsaInfo *__restrict__ infos, const Arc *__restrict__ arcs,
   __syncthreads();
   StoreDenseGrad(grad_b, f.row0, u0, cols, gb, gb_elems, tg, exclusive_rows,
                  lp_row ? lp_row[i] : -1, lp_cols, tid, nt);
-  if (ga_in_smem)
+  if (ga_in_smem && grad_a != nullptr)
     for (int32_t k = tid; k < A; k += nt) {
       const uint32_t fixed = ga[k];
       if (fixed != 0u)
@@ -946,10 +949,12 @@ GridGradItems(const FsaInfo *__restrict__ infos, const Arc *__restrict__ arcs,
               const ProbState *__restrict__ beta, const double *__restrict__ tot_grad,
               int32_t tot_grad_stride, float *__restrict__ grad_a, float *__restrict__ grad_b,
               int32_t frames_per_cta, int32_t lanes_log2, int32_t ga_in_smem,
-              int32_t exclusive_rows, const int32_t *__restrict__ lp_row, int32_t lp_cols) {
+              int32_t exclusive_rows, const int32_t *__restrict__ lp_row, int32_t lp_cols,
+              const int32_t *__restrict__ served) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   __shared__ int32_t list_count;
   const int32_t i = blockIdx.y;
+  if (served != nullptr && *served) return;  // GridGradStates wrote the gradients
   const FsaInfo f = infos[i];
   const int32_t S = f.num_states, A = f.num_arcs, Tk = f.tk, cols = dp.cols;
   const int32_t u0 = blockIdx.x * frames_per_cta;
@@ -1060,6 +1065,7 @@ GridGradItems(const FsaInfo *__restrict__ infos, const Arc *__restrict__ arcs,
         if (prod == 0.0) continue;
         const float post = (float)(prod * Pow2Clamped(e1 + ae + af.k + b.e));
         atomicAdd(&gbrow[c], __float2uint_rn(post * 2147483648.0f));
+        if (grad_a == nullptr) continue;
         if (ga_in_smem) atomicAdd(&ga[k], __float2uint_rn(post * 67108864.0f));
         else atomicAdd(&grad_a[f.arc_off + f.arc_out_off + k], tg * post);
       }
@@ -1069,7 +1075,7 @@ GridGradItems(const FsaInfo *__restrict__ infos, const Arc *__restrict__ arcs,
   }
   StoreDenseGrad(grad_b, f.row0, u0, cols, gb, nf * cols, tg, exclusive_rows,
                  lp_row ? lp_row[i] : -1, lp_cols, tid, nt);
-  if (ga_in_smem)
+  if (ga_in_smem && grad_a != nullptr)
     for (int32_t k = tid; k < A; k += nt) {
       const uint32_t fixed = ga[k];
       if (fixed != 0u)
@@ -1097,9 +1103,11 @@ GridGradLanes(const FsaInfo *__restrict__ infos, int32_t n, const Arc *__restric
               int32_t tot_grad_stride, float *__restrict__ grad_a, float *__restrict__ grad_b,
               const int32_t *__restrict__ plan, const int32_t *__restrict__ unfit,
               int32_t frames_per_cta, int32_t sub_frames, int32_t s_pad,
-              int32_t exclusive_rows, const int32_t *__restrict__ lp_row, int32_t lp_cols) {
+              int32_t exclusive_rows, const int32_t *__restrict__ lp_row, int32_t lp_cols,
+              const int32_t *__restrict__ served) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   const int32_t i = blockIdx.y;
+  if (served != nullptr && *served) return;  // GridGradStates wrote the gradients
   if (unfit[i] & 1) return;  // no plan: the warp-per-frame kernel takes this graph
   const FsaInfo f = infos[i];
   const int32_t S = f.num_states, Tk = f.tk, cols = dp.cols;
@@ -1246,7 +1254,7 @@ GridGradLanes(const FsaInfo *__restrict__ infos, int32_t n, const Arc *__restric
     StoreDenseGrad(grad_b, f.row0, u0, cols, gb, nf * cols, tg, exclusive_rows,
                    lp_row ? lp_row[i] : -1, lp_cols, tid, nt);
   }
-  if (s >= 0) {
+  if (s >= 0 && grad_a != nullptr) {
 #pragma unroll
     for (int j = 0; j < kDeg; ++j)
       if (ga[j] != 0.0f) atomicAdd(&grad_a[first_arc + f.arc_out_off + j * G], tg * ga[j]);
@@ -1434,12 +1442,91 @@ GridChain(const FsaInfo *__restrict__ infos, const Arc *__restrict__ arcs,
 }
 
 // ---------------------------------------------------------------------------
+// Gradient of the dense scores from STATE posteriors.  When all arcs that enter a state
+// carry the same label (CTC graphs, the LF-MMI denominator graph: a state "is" a symbol),
+// the posteriors of the arcs entering (level l, state s) add up to alpha_l[s] * beta_l[s] / Z,
+// and all of them belong to one element of the dense matrix: no arc has to be visited.
+// StateInLabels finds the label of every state and whether the property holds for the
+// whole batch (*one_label, initialised to 1 by the caller); GridGradStates then serves a
+// backward call that does not want the gradient of the arc scores, and returns at once
+// otherwise.  grid = (frame chunks, pairs); sums per (frame, column) in shared memory in
+// fixed point, as in the arc-posterior kernels.
+// ---------------------------------------------------------------------------
+constexpr int32_t kNoInLabel = INT32_MIN;
+
+__global__ void StateInLabels(const Arc *__restrict__ arcs, const int32_t *__restrict__ in_splits,
+                              const int32_t *__restrict__ in_arcs, int32_t num_states,
+                              int32_t *__restrict__ state_label, int32_t *__restrict__ one_label) {
+  const int32_t s = blockIdx.x * blockDim.x + threadIdx.x;
+  if (s >= num_states) return;
+  int32_t label = kNoInLabel;
+  bool same = true;
+  for (int32_t k = in_splits[s]; k < in_splits[s + 1]; ++k) {
+    const int32_t lab = arcs[in_arcs[k]].label;
+    if (label == kNoInLabel) label = lab;
+    else if (lab != label) same = false;
+  }
+  state_label[s] = label;
+  if (!same) atomicAnd(one_label, 0);
+}
+
+__global__ void __launch_bounds__(256)
+GridGradStates(const FsaInfo *__restrict__ infos, const int32_t *__restrict__ state_label,
+               const int32_t *__restrict__ one_label, int32_t cols,
+               const ProbState *__restrict__ alpha, const ProbState *__restrict__ beta,
+               const double *__restrict__ tot_grad, int32_t tot_grad_stride,
+               float *__restrict__ grad_b, int32_t frames_per_cta, int32_t exclusive_rows,
+               const int32_t *__restrict__ lp_row, int32_t lp_cols) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  if (!*one_label) return;  // the arc-posterior kernels take the call
+  const int32_t i = blockIdx.y;
+  const FsaInfo f = infos[i];
+  const int32_t S = f.num_states, Tk = f.tk;
+  const int32_t u0 = blockIdx.x * frames_per_cta;  // frames u0 .. u1 - 1 = levels u0 + 1 .. u1
+  if (S == 0 || u0 >= Tk) return;
+  const int32_t u1 = min(u0 + frames_per_cta, Tk);
+  const int tid = threadIdx.x, nt = blockDim.x;
+  uint32_t *gb = reinterpret_cast<uint32_t *>(smem_raw);  // [frames_per_cta][cols], 2^-31 units
+  const ProbState *al = alpha + f.grid_off, *be = beta + f.grid_off;
+  const ProbState z = al[(int64_t)Tk * S + (S - 1)];
+  if (z.m == 0.0) return;  // no path survives: all gradients are zero
+  int32_t zex;
+  const double zm = SplitExp(z.m, &zex);
+  const double zinv = 1.0 / zm;
+  const int32_t zk = -(z.e + zex);
+  const float tg = (float)tot_grad[(int64_t)i * tot_grad_stride];
+  const int32_t elems = (u1 - u0) * cols;
+  for (int32_t k = tid; k < elems; k += nt) gb[k] = 0u;
+  __syncthreads();
+  const int32_t *labels = state_label + f.state_off;
+  for (int32_t k = tid; k < (u1 - u0) * S; k += nt) {
+    const int32_t fr = k / S, s = k - fr * S;
+    const int32_t c = labels[s] + 1;
+    if (c < 0 || c >= cols) continue;
+    const int64_t gi = (int64_t)(u0 + fr + 1) * S + s;
+    const ProbState a = al[gi];
+    if (a.m == 0.0) continue;
+    const ProbState b = be[gi];
+    if (b.m == 0.0) continue;
+    const float post = (float)(a.m * b.m * zinv * Pow2Clamped(a.e + b.e + zk));
+    if (post != 0.0f) atomicAdd(&gb[fr * cols + c], __float2uint_rn(post * 2147483648.0f));
+  }
+  __syncthreads();
+  StoreDenseGrad(grad_b, f.row0, u0, cols, gb, elems, tg, exclusive_rows,
+                 lp_row ? lp_row[i] : -1, lp_cols, tid, nt);
+}
+
+// ---------------------------------------------------------------------------
 // host side
 // ---------------------------------------------------------------------------
 struct LossLayout {
   Layout base;
   DensePack pack;
-  size_t off_dense, off_arc_factors, off_alpha, off_beta, off_masks, off_flags, total_bytes;
+  size_t off_dense, off_arc_factors, off_alpha, off_beta, off_masks, off_flags, off_state_label,
+      off_one_label, total_bytes;
+  // set by the backward entry point when the state-posterior kernel may serve the call:
+  // the flag the arc-posterior kernels look at before doing anything
+  const int32_t *served = nullptr;
   bool exclusive_rows;
   // set by the backward entry point: gradients go straight to the log-prob layout
   const int32_t *lp_row = nullptr;  // per pair, log-prob row of its first frame
@@ -1468,6 +1555,8 @@ static int32_t MakeLossLayout(const k2b200_intersect_args *a, LossLayout *LL) {
   // arc survival bytes, planned graphs only: [2 directions][levels][lanes]
   LL->off_masks = take(LL->identity ? 0 : (size_t)2 * LL->base.total_levels * kLaneThreads + 16);
   LL->off_flags = take(sizeof(int32_t));
+  LL->off_state_label = take(sizeof(int32_t) * (size_t)std::max(a->num_states, 1));
+  LL->off_one_label = take(sizeof(int32_t));
   LL->total_bytes = off;
   // two graphs on one sequence write the same rows of the dense gradient
   LL->exclusive_rows = true;
@@ -1592,7 +1681,7 @@ static int32_t LaunchGrad(const LossLayout &LL, const k2b200_intersect_args *arg
       reinterpret_cast<const ProbState *>(ws + LL.off_alpha),
       reinterpret_cast<const ProbState *>(ws + LL.off_beta), tot_grad, stride, grad_a, grad_b,
       frames, lg, s_pad, ga_in_smem, LL.exclusive_rows ? 1 : 0, only_noplan, LL.lp_row,
-      LL.lp_cols); NoteLaunch(); }
+      LL.lp_cols, LL.served); NoteLaunch(); }
   K2B_CUDA_OK(cudaGetLastError());
   return kOk;
 }
@@ -1629,7 +1718,8 @@ static int32_t LaunchGradItems(const LossLayout &LL, const k2b200_intersect_args
       reinterpret_cast<const float *>(ws + L.off_cutoffs),
       reinterpret_cast<const ProbState *>(ws + LL.off_alpha),
       reinterpret_cast<const ProbState *>(ws + LL.off_beta), tot_grad, stride, grad_a, grad_b,
-      frames, lg, ga_in_smem, LL.exclusive_rows ? 1 : 0, LL.lp_row, LL.lp_cols); NoteLaunch(); }
+      frames, lg, ga_in_smem, LL.exclusive_rows ? 1 : 0, LL.lp_row, LL.lp_cols, LL.served);
+    NoteLaunch(); }
   K2B_CUDA_OK(cudaGetLastError());
   return kOk;
 }
@@ -1660,7 +1750,7 @@ static int32_t LaunchGradLanes(const LossLayout &LL, const k2b200_intersect_args
       reinterpret_cast<const ProbState *>(ws + LL.off_beta), tot_grad, stride, grad_a, grad_b,
       reinterpret_cast<const int32_t *>(ws + L.off_plan),
       reinterpret_cast<const int32_t *>(ws + L.off_unfit), frames, sub, s_pad,
-      LL.exclusive_rows ? 1 : 0, LL.lp_row, LL.lp_cols); NoteLaunch(); }
+      LL.exclusive_rows ? 1 : 0, LL.lp_row, LL.lp_cols, LL.served); NoteLaunch(); }
   K2B_CUDA_OK(cudaGetLastError());
   return kOk;
 }
@@ -1730,6 +1820,13 @@ int32_t k2b200_dense_loss_forward(const k2b200_intersect_args *args, void *works
   K2B_FORWARD(SideFork(stream, &side));
   join_guard.armed = true;
   K2B_FORWARD(LaunchPlanLanes(L, args, ws, stream));
+  // the label of every state and whether a state has one (for the backward pass)
+  K2B_CUDA_OK(cudaMemsetAsync(ws + LL.off_one_label, 0xff, sizeof(int32_t), stream));
+  if (args->num_states > 0)
+    { StateInLabels<<<CeilDiv(args->num_states, 256), 256, 0, stream>>>(
+        reinterpret_cast<const Arc *>(args->a_arcs), args->a_in_splits, args->a_in_arcs,
+        args->num_states, reinterpret_cast<int32_t *>(ws + LL.off_state_label),
+        reinterpret_cast<int32_t *>(ws + LL.off_one_label)); NoteLaunch(); }
   {
     PhaseTimer timer(kPhaseViterbi, stream);
     K2B_FORWARD(RunViterbi(L, args, ws, stream, /*plan_ready=*/true));
@@ -1813,10 +1910,29 @@ static int32_t DenseLossBackward(const k2b200_intersect_args *args, void *worksp
              LL.total_bytes);
     return kWorkspaceTooSmall;
   }
-  K2B_REQUIRE(tot_grad && grad_a && grad_b, "NULL device pointer");
+  K2B_REQUIRE(tot_grad && grad_b, "NULL device pointer");
   if (L.max_states == 0 || L.max_tk == 0) return kOk;
   char *ws = reinterpret_cast<char *>(workspace);
   PhaseTimer timer(kPhaseGrad, stream);
+  if (grad_a == nullptr) {
+    // only the dense gradient is wanted: state posteriors give it when every state has
+    // one label; the kernels below look at the same flag and return if it did
+    LL.served = reinterpret_cast<const int32_t *>(ws + LL.off_one_label);
+    int32_t frames = 32;
+    while (frames > 1 && sizeof(uint32_t) * (size_t)frames * args->cols > 64 * 1024) frames >>= 1;
+    const size_t smem = sizeof(uint32_t) * (size_t)frames * args->cols;
+    K2B_REQUIRE(smem <= kChainSmemBudget, "too many columns for the fused loss path");
+    K2B_CUDA_OK(cudaFuncSetAttribute(GridGradStates, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     (int)smem));
+    dim3 grid(CeilDiv(L.max_tk, frames), args->num_fsas);
+    { GridGradStates<<<grid, 256, smem, stream>>>(
+        reinterpret_cast<const FsaInfo *>(ws + L.off_infos),
+        reinterpret_cast<const int32_t *>(ws + LL.off_state_label), LL.served, args->cols,
+        reinterpret_cast<const ProbState *>(ws + LL.off_alpha),
+        reinterpret_cast<const ProbState *>(ws + LL.off_beta), tot_grad, tot_grad_stride, grad_b,
+        frames, LL.exclusive_rows ? 1 : 0, LL.lp_row, LL.lp_cols); NoteLaunch(); }
+    K2B_CUDA_OK(cudaGetLastError());
+  }
   if (args->num_arcs > 0)
     { ExpArcs<<<CeilDiv(args->num_arcs, 256), 256, 0, stream>>>(
         reinterpret_cast<const Arc *>(args->a_arcs), args->num_arcs,
