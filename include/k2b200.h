@@ -409,7 +409,10 @@ int32_t k2b200_online_decode_store_all(const k2b200_online_args *args, void *wor
  *     (device, float64), ADDS dL/d(arc score) to grad_a[num_arcs] and
  *     dL/d(scores) to grad_b[rows * cols]; both must be zero-filled (or hold
  *     gradients to accumulate onto) and the workspace must be the one the forward
- *     call filled, with the same args.
+ *     call filled, with the same args.  grad_a may be NULL when the gradient of the
+ *     arc scores is not wanted; for graphs in which all arcs entering a state carry
+ *     the same label the dense gradient then comes from state posteriors
+ *     (alpha * beta / Z per surviving state) and no arc is visited.
  * ------------------------------------------------------------------------- */
 int32_t k2b200_dense_loss_supported(const k2b200_intersect_args *args, int32_t *supported);
 int32_t k2b200_dense_loss_workspace_bytes(const k2b200_intersect_args *args, size_t *bytes);

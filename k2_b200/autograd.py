@@ -552,7 +552,11 @@ class _DenseTotScoresFunction(torch.autograd.Function):
         if tot_grad.dtype != torch.float64:
             tot_grad = tot_grad.to(torch.float64)
         stride = tot_grad.stride(0) if tot_grad.numel() > 0 else 0
-        grad_a = torch.zeros(ctx.shape_a, dtype=torch.float32, device=dev)
+        # without a gradient for the graph scores the library may take the dense gradient
+        # from state posteriors (graphs in which a state has one label)
+        grad_a = None
+        if ctx.needs_input_grad[7]:
+            grad_a = torch.zeros(ctx.shape_a, dtype=torch.float32, device=dev)
         grad_b = torch.zeros(ctx.shape_b, dtype=torch.float32, device=dev)
         with torch.cuda.device(dev):
             if ctx.lp_row is None:

@@ -52,7 +52,6 @@ constexpr int kBandMaxStates = 512;
 constexpr int kVitK = 4;              // states per thread of BandViterbi
 constexpr int kPrepK = 16;            // states per lane of BandPrep's row scan
 constexpr int kPrepLevels = 16;       // levels per warp of BandPrep
-constexpr int kRescale = 8;           // levels between changes of the shared scale
 constexpr int kGradLevels = 4;        // levels per warp of BandGrad
 constexpr int kDrainPolls = 4000000;  // bounded wait for copies in flight when a kernel gives up
 
@@ -72,6 +71,9 @@ struct BandInfo {
   int32_t lp_row;      // row of the log-prob matrix that holds frame 0
   int32_t level_off;   // sum over earlier pairs of (T + 2)
   int64_t grid_off;    // sum over earlier pairs of (T + 2) * pitch
+  int32_t mpitch;      // S rounded up to a multiple of 8: row pitch of this pair's meta grid
+  int32_t pad;
+  int64_t meta_off;    // sum over earlier pairs of (T + 2) * mpitch
 };
 
 // Per state (idx01): the arcs entering it.  w[d] = score of the arc from state s - d
@@ -86,18 +88,19 @@ struct __align__(16) BandArc {
   int32_t k;
   int32_t arc;
 };
-// Entry of a level's list of surviving states (level l, state s): pw[d] = exp(score of
-// the arc from state s - d) * exp(dense score of s's label on frame l - 1) if that arc
-// survives between levels l - 1 and l, else 0.
-struct __align__(16) BandItem {
-  double pw[3];
-  int32_t label;
-  uint16_t s;
-  uint8_t inb;   // bit d: the arc from state s - d of the level before survives
-  uint8_t outb;  // bit d: the arc to state s + d of the next level survives
+// Entry of a level's list of surviving states.
+struct __align__(8) BandItem {
+  int32_t label;  // of the arcs entering the state
+  uint16_t s;     // the state
+  uint8_t inb;    // bit d: the arc from state s - d of the level before survives
+  uint8_t outb;   // bit d: the arc to state s + d of the next level survives
 };
-static_assert(sizeof(BandItem) == 32, "BandItem must be 32 bytes");
-constexpr int kOutbByte = 31;
+static_assert(sizeof(BandItem) == 8, "BandItem must be 8 bytes");
+constexpr int kOutbByte = 7;
+// The same per (level, state) for ALL states, in 16 bits: bit 15 = the state survives,
+// bits 0-8 = its position in the level's list, bits 9-11 = inb, bits 12-14 = outb.
+constexpr uint32_t kMetaKept = 0x8000u, kMetaPos = 0x1ffu;
+constexpr int kMetaInShift = 9, kMetaOutShift = 12;
 
 // alpha of the final state on the last level (= Z) of a graph, as m * 2^e
 struct __align__(16) BandTotal {
@@ -443,42 +446,50 @@ BandViterbi(const BandInfo *__restrict__ infos, const BandState *__restrict__ ta
 }
 
 // ---------------------------------------------------------------------------
-// Keep tests and the per-level lists.  grid = (level chunks, pairs), 4 warps per CTA, a
-// warp per chunk of kPrepLevels levels.  Per level the warp
+// Keep tests.  grid = (level chunks, pairs), 4 warps per CTA, a warp per chunk of
+// kPrepLevels levels.  Per level the warp
 //   1. scans the two Viterbi rows (a lane reads 16 consecutive states of each; the rows of
 //      the next level are requested before this level is worked on), marks the surviving
 //      states and writes them, in state order, to a list in shared memory;
-//   2. takes the list one state per lane: arc tests against the rows of the level before,
-//      the dense score of the state's label, the factors of the entry;
-//   3. gives the entries of the level before their leaving-arc bits, which are the
-//      entering-arc bits of this level seen from the source.
-// A warp writes the complete entries of the levels it owns, so it also runs steps 1-2 for
-// the level after its last.  totals[0] += surviving states, totals[2] += the arcs leaving
-// them (the sizes the beam reduction looks at, intersect_dense.cu:289-320).
+//   2. takes the list one state per lane: the reference's arc tests
+//      (intersect_dense.cu:430-471) against the rows of the level before and the dense
+//      score of the state's label give the entering-arc bits;
+//   3. gives the states of the level before their leaving-arc bits, which are the
+//      entering-arc bits of this level seen from the source, and writes that level out.
+// Two forms of the result: per level the compact LIST of surviving states (for the
+// gradients and the exact recursion), and a 16-bit META word per (level, state) for all
+// states (for the dense recursion).  A warp writes the complete entries of the levels it
+// owns, so it also runs steps 1-2 for the level after its last.  totals[0] += surviving
+// states, totals[2] += the arcs leaving them (the sizes the beam reduction looks at,
+// intersect_dense.cu:289-320).  unfit[i] is set when a surviving arc has a score outside
+// what the dense recursion's arithmetic accepts.
 // ---------------------------------------------------------------------------
+constexpr float kMinLeanDense = -20.0f;   // dense score of a surviving arc
+constexpr float kMaxLeanArc = 10.0f;      // |arc score| of a surviving arc
+
 __global__ void __launch_bounds__(128)
 BandPrep(const BandInfo *__restrict__ infos, const BandState *__restrict__ tab,
-         const BandArc *__restrict__ tabf, const int32_t *__restrict__ a_row_splits2,
-         const float *__restrict__ lp, int32_t C, const float *__restrict__ vf,
-         const float *__restrict__ vb, float beam, BandItem *__restrict__ items,
-         int2 *__restrict__ lists, float *__restrict__ cutoffs,
-         unsigned long long *__restrict__ totals, int32_t *__restrict__ unfit, int32_t s_pad) {
+         const int32_t *__restrict__ a_row_splits2, const float *__restrict__ lp, int32_t C,
+         const float *__restrict__ vf, const float *__restrict__ vb, float beam,
+         BandItem *__restrict__ items, int2 *__restrict__ lists, uint16_t *__restrict__ meta,
+         float *__restrict__ cutoffs, unsigned long long *__restrict__ totals,
+         int32_t *__restrict__ unfit, int32_t s_pad) {
   constexpr int K = kPrepK;
   constexpr unsigned kAll = 0xffffffffu;
   extern __shared__ __align__(16) unsigned char smem_raw[];
   const int32_t i = blockIdx.y;
   const BandInfo f = infos[i];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const int32_t S = f.num_states, T = f.frames, pitch = f.pitch;
+  const int32_t S = f.num_states, T = f.frames, pitch = f.pitch, mpitch = f.mpitch;
   if (S == 0) return;
   const int32_t a = (blockIdx.x * 4 + warp) * kPrepLevels;  // owns levels a .. b - 1
   if (a > T + 1) return;
   const int32_t b = min(a + kPrepLevels, T + 2);
-  // per warp: entering-arc bits of the current level by state (zero outside the list),
-  // and the lists of the current and the previous level
-  unsigned char *inb_sm = smem_raw + (size_t)warp * (s_pad + 4 * s_pad);
-  uint16_t *list_sm = reinterpret_cast<uint16_t *>(inb_sm + s_pad);  // [2][s_pad]
-  for (int32_t k = lane; k < s_pad; k += 32) inb_sm[k] = 0;
+  // per warp: the meta words of the current and the previous level by state (zero
+  // outside the lists), and the two lists
+  uint16_t *meta_sm = reinterpret_cast<uint16_t *>(smem_raw) + (size_t)warp * 4 * s_pad;  // [2][s_pad]
+  uint16_t *list_sm = meta_sm + 2 * s_pad;                                                // [2][s_pad]
+  for (int32_t k = lane; k < 2 * s_pad; k += 32) meta_sm[k] = 0;
   const float *fg = vf + f.grid_off, *bg = vb + f.grid_off;
   float cutoff;
   {
@@ -500,6 +511,16 @@ BandPrep(const BandInfo *__restrict__ infos, const BandState *__restrict__ tab,
       }
     }
   };
+  // the meta words of a level, all states: every lane writes its 16 (two 16-byte stores)
+  uint16_t *meta0 = meta + f.meta_off;
+  auto flush_meta = [&](int32_t l, const uint16_t *row_sm) {
+    if (s0 < mpitch) {
+      uint4 *dst = reinterpret_cast<uint4 *>(meta0 + (int64_t)l * mpitch + s0);
+      const uint4 *src = reinterpret_cast<const uint4 *>(row_sm + s0);
+      dst[0] = src[0];
+      if (s0 + 8 < mpitch) dst[1] = src[1];
+    }
+  };
   load_rows(a, Fc, Bc);
   int32_t n_prev = 0;
   // the lists of a warp's levels lie one after the other from the start of its chunk
@@ -513,6 +534,7 @@ BandPrep(const BandInfo *__restrict__ infos, const BandState *__restrict__ tab,
     float4 Fn[K / 4], Bn[K / 4];
     load_rows(l + 1, Fn, Bn);  // in flight while this level is worked on
     uint16_t *cur_list = list_sm + (l & 1) * s_pad, *prev_list = list_sm + ((l & 1) ^ 1) * s_pad;
+    uint16_t *cur_meta = meta_sm + (l & 1) * s_pad, *prev_meta = meta_sm + ((l & 1) ^ 1) * s_pad;
     // ---- 1. surviving states ------------------------------------------------------
     uint32_t keep = 0;
 #pragma unroll
@@ -543,12 +565,9 @@ BandPrep(const BandInfo *__restrict__ infos, const BandState *__restrict__ tab,
       const int32_t s = cur_list[j];
       const BandState t = tab[f.state_off + s];
       uint32_t inb = 0;
-      BandItem it;
-      it.pw[0] = it.pw[1] = it.pw[2] = 0.0;
       if (l >= 1) {
         const float x = BandDense(lp0, C, T, l - 1, t.label);
         const float bc = bcur[s];
-        const double p = exp((double)x);
 #pragma unroll
         for (int d = 0; d < 3; ++d) {
           if (s - d < 0) continue;
@@ -557,18 +576,15 @@ BandPrep(const BandInfo *__restrict__ infos, const BandState *__restrict__ tab,
           const float sc = __fadd_rn(t.w[d], x);
           if (kept && __fadd_rn(__fadd_rn(sf, sc), bc) > cutoff) {
             inb |= 1u << d;
-            if (own) {
-              const BandArc arc = tabf[(int64_t)(f.state_off + s) * 3 + d];
-              it.pw[d] = arc.f * Pow2Clamp(arc.k) * p;
-              // outside what a double holds with a scale that follows the data every few
-              // levels: such graphs go to the (mantissa, exponent) recursion
-              if (!(x >= -60.0f) || arc.k > 60 || arc.k < -90) risky = true;
-            }
+            // outside what doubles with a scale that follows the data every few levels
+            // hold: such graphs go to the (mantissa, exponent) recursion
+            if (!(x >= kMinLeanDense) || !(fabsf(t.w[d]) <= kMaxLeanArc)) risky = true;
           }
         }
       }
-      if (inb) inb_sm[s] = (unsigned char)inb;
+      cur_meta[s] = (uint16_t)(kMetaKept | (uint32_t)j | (inb << kMetaInShift));
       if (own) {
+        BandItem it;
         it.label = t.label;
         it.s = (uint16_t)s;
         it.inb = (uint8_t)inb;
@@ -583,17 +599,25 @@ BandPrep(const BandInfo *__restrict__ infos, const BandState *__restrict__ tab,
       if (lane == 0) lists[f.level_off + l] = make_int2(run, n);
     }
     __syncwarp();
-    // ---- 3. leaving-arc bits of the level before ---------------------------------------
-    if (l - 1 >= a && n > 0) {
+    // ---- 3. leaving-arc bits of the level before; that level is then complete -----------
+    if (l - 1 >= a) {
       unsigned char *prev_bytes = reinterpret_cast<unsigned char *>(items + f.grid_off + prev_start);
       for (int32_t j = lane; j < n_prev; j += 32) {
         const int32_t s = prev_list[j];
-        const uint32_t ob = (inb_sm[s] & 1u) | (inb_sm[s + 1] & 2u) | (inb_sm[s + 2] & 4u);
-        if (ob) prev_bytes[(size_t)j * sizeof(BandItem) + kOutbByte] = (unsigned char)ob;
+        const uint32_t ob = ((cur_meta[s] >> kMetaInShift) & 1u) |
+                            ((cur_meta[s + 1] >> kMetaInShift) & 2u) |
+                            ((cur_meta[s + 2] >> kMetaInShift) & 4u);
+        if (ob) {
+          prev_bytes[(size_t)j * sizeof(BandItem) + kOutbByte] = (unsigned char)ob;
+          prev_meta[s] = (uint16_t)(prev_meta[s] | (ob << kMetaOutShift));
+        }
       }
+      __syncwarp();
+      flush_meta(l - 1, prev_meta);
     }
     __syncwarp();
-    for (int32_t j = lane; j < n; j += 32) inb_sm[cur_list[j]] = 0;
+    // the previous level's words go back to zero for the level after this one
+    for (int32_t j = lane; j < n_prev; j += 32) prev_meta[prev_list[j]] = 0;
     __syncwarp();
 #pragma unroll
     for (int c = 0; c < K / 4; ++c) {
@@ -604,6 +628,8 @@ BandPrep(const BandInfo *__restrict__ infos, const BandState *__restrict__ tab,
     prev_start = run;
     run += n;
   }
+  // the last level of all has no leaving arcs: it is complete as it stands
+  if (b == T + 2) flush_meta(T + 1, meta_sm + ((T + 1) & 1) * s_pad);
 #pragma unroll
   for (int d = 16; d > 0; d >>= 1) {
     n_states += __shfl_xor_sync(kAll, n_states, d);
@@ -617,27 +643,364 @@ BandPrep(const BandInfo *__restrict__ infos, const BandState *__restrict__ tab,
 }
 
 // ---------------------------------------------------------------------------
-// alpha (dir 0) and beta (dir 1) over the lists.  grid = (2, pairs), one warp per CTA.
-//   alpha_0[start] = 1;          alpha_l[s] = sum_d pw_l[s][d] * alpha_{l-1}[s-d]
-//   beta_{T+1}[final] = 1;       beta_l[s]  = sum_d [arc s -> s+d survives] pw_{l+1}[s+d][d] * beta_{l+1}[s+d]
-// Shared memory holds, by state number, what the previous level hands on - alpha itself,
-// or for beta the three products pw[d] * beta of every state - in two buffers used in
-// turn.  An entry that is read and counts is always current: a factor that is not zero, or
-// a leaving-arc bit that is set, names a state of the previous level's list.  Stale
-// entries are finite numbers, multiplied by a factor of zero or not selected.
-// The lists of kPrepLevels consecutive levels are contiguous in memory (BandPrep): they
-// arrive by one bulk copy per chunk, requested chunks ahead, so a level waits for nothing
-// but the warp's own previous level.
-// The values of a level are stored divided by 2^K; K changes every kRescale levels by the
-// exponent of the largest value of the level before.  A value that is not zero and below
-// 2^-900 (or above 2^900) marks the graph in `unfit` for the (mantissa, exponent) variant
-// (kExact), which runs afterwards and returns at once for every other graph.
-// Outputs: alpha / beta at the list positions, K per level, tot[i], total[i].
+// alpha (dir 0) and beta (dir 1) over ALL states of a graph, in the shape of BandViterbi:
+// a thread holds four consecutive states in registers, a warp recomputes its neighbour's
+// boundary states so that a batch of F frames needs no exchange, the log-prob rows and
+// the meta rows of a batch arrive by two bulk copies requested batches ahead.
+//   alpha_0[start] = 1;     alpha_l[s] = p_l[s] * sum_d [arc s-d -> s survives] e^w alpha_{l-1}[s-d]
+//   beta_{T+1}[final] = 1;  beta_l[s]  = sum_d [arc s -> s+d survives] e^w p_{l+1}[s+d] beta_{l+1}[s+d]
+// with p_l[s] = exp(dense score of s's label on frame l - 1) and the survival bits of
+// BandPrep.  Most states of a level do not survive (their bits are zero, their value is
+// zero): the work on them is wasted, yet it costs nothing on the critical path - a chain
+// of T dependent steps, which this form keeps in registers and shuffles, without lists,
+// indexed shared-memory traffic or per-level synchronisation.
+// Values are doubles divided by 2^K; K changes every eight frames (where the warps exchange
+// boundary states, and once between) by the exponent of the largest value.  The value of a
+// surviving state is stored at its position in the level's list (am / bm), K per level
+// (a_scale / b_scale).  A non-zero value of a surviving state below 2^-600 marks the graph
+// in `unfit` for BandChainExact; BandPrep marks the graphs whose scores could take a value
+// from above 2^-600 to nothing within eight frames.
 // ---------------------------------------------------------------------------
-constexpr int kChainSlots = 3;                  // chunks in flight
-constexpr int kSlotItems = kPrepLevels * 40;    // entries of a chunk staged in shared memory
+constexpr int kHalfBatch = 8;                   // frames into a batch at which the scale changes again
+constexpr int kChainSlots = 3;                  // chunks in flight (BandChainExact)
+constexpr int kSlotItems = kPrepLevels * 128;   // entries of a chunk staged in shared memory
 
-// The ring of chunks: lane 0 requests, every lane waits.
+__device__ __forceinline__ double ExpDenseFast(float x) {
+  // exp(x) to float precision (2^-22): the same factor enters alpha, beta and Z.  For the
+  // scores of surviving arcs (above kMinLeanDense) the result is a normal float; what
+  // flushes to zero belongs to arcs that do not survive.
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x * 1.4426950408889634f));
+  return (double)y;
+}
+
+__global__ void __launch_bounds__(32 * kVitMaxWarps)
+BandChainDense(const BandInfo *__restrict__ infos, const BandState *__restrict__ tab,
+               const float *__restrict__ lp, int32_t C, const uint16_t *__restrict__ meta,
+               const int2 *__restrict__ lists, double *__restrict__ am, double *__restrict__ bm,
+               int32_t *__restrict__ a_scale, int32_t *__restrict__ b_scale,
+               double *__restrict__ tot, BandTotal *__restrict__ total,
+               int32_t *__restrict__ unfit, int32_t *__restrict__ status, int32_t F,
+               int32_t nbatch, int32_t xch_pad, int32_t mrow, int32_t lv_pad,
+               int32_t wait_limit) {
+  constexpr int K = kVitK;
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  __shared__ __align__(8) uint64_t full[kVitMaxBatches];
+  __shared__ int32_t wmax[2][kVitMaxWarps];
+  __shared__ int32_t any_late, any_bad;
+  constexpr unsigned kAll = 0xffffffffu;
+  const int dir = blockIdx.x;
+  const int32_t i = blockIdx.y;
+  const BandInfo f = infos[i];
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nwarps = blockDim.x >> 5;
+  const int32_t S = f.num_states, T = f.frames, mpitch = f.mpitch, L = T + 2;
+  if (dir == 0 && tid == 0) {
+    tot[i] = -INFINITY;
+    BandTotal z;
+    z.m = 0.0;
+    z.e = 0;
+    z.pad = 0;
+    total[i] = z;
+  }
+  if (S == 0) return;
+  const int32_t H = F >> 1, own = 32 - H;
+  // shared memory: per batch F log-prob rows and F meta rows; the exchange buffers; the
+  // start of every level's list
+  float *ring = reinterpret_cast<float *>(smem_raw);                                // [nbatch][F][C]
+  // a slot has room for F meta rows of mrow (>= every mpitch) words; a batch's rows are
+  // staged as they lie in memory, at this pair's pitch
+  uint16_t *mring = reinterpret_cast<uint16_t *>(ring + (size_t)nbatch * F * C);    // [nbatch][F][mrow]
+  double *xch = reinterpret_cast<double *>(mring + (size_t)nbatch * F * mrow);      // [2][xch_pad], s at s + 4H
+  int32_t *lstart = reinterpret_cast<int32_t *>(xch + 2 * xch_pad);                 // [lv_pad]
+  for (int32_t l = tid; l < L; l += blockDim.x) lstart[l] = lists[f.level_off + l].x;
+  for (int32_t k = tid; k < 2 * xch_pad; k += blockDim.x) xch[k] = 0.0;
+  if (tid == 0) {
+    for (int st = 0; st < nbatch; ++st) MbarInit(&full[st], 1);
+    MbarInitFence();
+    any_late = 0;
+    any_bad = 0;
+  }
+  __syncthreads();
+  const int32_t num_batches = (T + F - 1) / F;
+  const float *lp0 = lp + (int64_t)f.lp_row * C;
+  const uint16_t *meta0 = meta + f.meta_off;
+  int32_t issued = 0;
+  // Batch q, forward: steps to levels qF + 1 .. : log-prob rows [qF, ...), meta rows one up.
+  // Backward: steps to levels T - 1 - qF down: log-prob rows and meta rows [T - (q+1)F, T - qF).
+  auto issue = [&]() {  // thread 0 only
+    if (issued >= num_batches) return;
+    const int32_t q = issued;
+    const int32_t r0 = dir == 0 ? q * F : max(T - (q + 1) * F, 0);
+    const int32_t r1 = dir == 0 ? min((q + 1) * F, T) : T - q * F;
+    const int32_t m0 = dir == 0 ? r0 + 1 : r0;  // first meta row
+    const unsigned lp_bytes = (unsigned)(r1 - r0) * 4u * (unsigned)C;
+    const unsigned m_bytes = (unsigned)(r1 - r0) * 2u * (unsigned)mpitch;
+    const int32_t slot = q % nbatch;
+    MbarArriveExpectTx(&full[slot], lp_bytes + m_bytes);
+    BulkCopyG2S(ring + (size_t)slot * F * C, lp0 + (int64_t)r0 * C, lp_bytes, &full[slot]);
+    // meta rows of one pair are contiguous at pitch mpitch: staged as they lie
+    BulkCopyG2S(mring + (size_t)slot * F * mrow, meta0 + (int64_t)m0 * mpitch, m_bytes,
+                &full[slot]);
+    ++issued;
+  };
+  if (tid == 0)
+    for (int32_t q = 0; q < nbatch; ++q) issue();
+
+  const int32_t s0 = warp * own * K + (dir == 0 ? (lane - H) * K : lane * K);
+  const bool mine = dir == 0 ? lane >= H : lane < own;   // a lane that owns its states
+  const bool has_meta = s0 >= 0 && s0 < mpitch;          // its states exist in the meta rows
+  double *out = (dir == 0 ? am : bm) + f.grid_off;
+  int32_t *oscale = (dir == 0 ? a_scale : b_scale) + f.level_off;
+  bool late = false, bad = false;
+  int32_t Ksh = 0;
+  double v[K] = {0.0, 0.0, 0.0, 0.0};
+  // arc factors exp(w) and dense columns of this thread's states
+  double e0[K], e1[K], e2[K];   // forward: arcs into s from s, s-1, s-2; backward: out of s to s, s+1, s+2
+  int32_t col[K];
+  uint32_t fin = 0;             // states whose label is the final symbol
+#pragma unroll
+  for (int k = 0; k < K; ++k) {
+    e0[k] = e1[k] = e2[k] = 0.0;
+    col[k] = 0;
+  }
+  if (dir == 0) {
+#pragma unroll
+    for (int k = 0; k < K; ++k) {
+      const int32_t s = s0 + k;
+      if (s >= 0 && s < S) {
+        const BandState t = tab[f.state_off + s];
+        e0[k] = exp((double)t.w[0]);
+        e1[k] = exp((double)t.w[1]);
+        e2[k] = exp((double)t.w[2]);
+        if (t.label >= 0 && t.label < C) col[k] = t.label;
+        if (t.label == -1) fin |= 1u << k;
+      }
+    }
+  } else {
+#pragma unroll
+    for (int k = 0; k < K + 2; ++k) {
+      const int32_t s = s0 + k;
+      if (s >= 0 && s < S) {
+        const BandState t = tab[f.state_off + s];
+        if (k < K) {
+          if (t.label >= 0 && t.label < C) col[k] = t.label;
+          if (t.label == -1) fin |= 1u << k;
+        }
+        // the arc s - d -> s seen from its source, state s - d = s0 + k - d
+        if (k < K) e0[k] = exp((double)t.w[0]);
+        if (k - 1 >= 0 && k - 1 < K) e1[k - 1 >= 0 ? k - 1 : 0] = exp((double)t.w[1]);
+        if (k - 2 >= 0 && k - 2 < K) e2[k - 2 >= 0 ? k - 2 : 0] = exp((double)t.w[2]);
+      }
+    }
+  }
+  // Change of scale: every thread divides its values by 2^e, e the exponent of the largest
+  // value an owner holds.  With `swap` the owners also publish their values and the
+  // recomputing lanes pick them up (once per batch); without, only the scale changes
+  // (once more in the middle of a batch).  One barrier either way.
+  constexpr uint32_t kTinyHi = ((1023 - 600) << 20) - 1;  // high word of 2^-600, less one
+  // smallest (high word - 1) among the values this thread computed, zeros apart (as an
+  // unsigned number the high word 0 of a zero becomes the largest value)
+  uint32_t min_hi = 0xffffffffu;
+  int32_t xpar = 0;
+  auto rescale = [&](bool swap) {
+    double *x = xch + (size_t)xpar * xch_pad + 4 * H;
+    int32_t hm = 0;
+    if (mine) {
+#pragma unroll
+      for (int k = 0; k < K; ++k) hm = max(hm, __double2hiint(v[k]));
+      if (swap && s0 >= 0 && s0 < xch_pad - 4 * H - 3) {
+#pragma unroll
+        for (int k = 0; k < K; ++k) x[s0 + k] = v[k];
+      }
+    }
+    hm = __reduce_max_sync(kAll, hm);
+    if (lane == 0) wmax[xpar][warp] = hm;
+    // a value that is not zero must have stayed clear of the end of the range (values
+    // this thread recomputed for its neighbour count too: they are the same numbers)
+    bad |= min_hi < kTinyHi;
+    __syncthreads();
+    if (swap && !mine && s0 + 4 * H >= 0 && s0 < xch_pad - 4 * H - 3) {
+#pragma unroll
+      for (int k = 0; k < K; ++k) v[k] = x[s0 + k];
+    }
+    int32_t cm = 0;
+    for (int32_t w = 0; w < nwarps; ++w) cm = max(cm, wmax[xpar][w]);
+    const int32_t e = cm > 0 ? (cm >> 20) - 1023 : 0;
+    const double scale = __longlong_as_double((long long)(1023 - e) << 52);
+#pragma unroll
+    for (int k = 0; k < K; ++k) v[k] *= scale;
+    Ksh += e;
+    xpar ^= 1;
+  };
+  // the values of a thread's surviving states go to consecutive list positions when all
+  // four survive (the usual case inside the band)
+  auto store4 = [&](int32_t l, uint2 m4, const double (&x)[K]) {
+    if (!mine) return;
+    const uint32_t all = m4.x & m4.y & (kMetaKept | (kMetaKept << 16));
+    double *o = out + lstart[l];
+    if (all == (kMetaKept | (kMetaKept << 16))) {
+      o += m4.x & kMetaPos;
+      o[0] = x[0];
+      o[1] = x[1];
+      o[2] = x[2];
+      o[3] = x[3];
+    } else if ((m4.x | m4.y) & (kMetaKept | (kMetaKept << 16))) {
+#pragma unroll
+      for (int k = 0; k < K; ++k) {
+        const uint32_t m = (k < 2 ? m4.x : m4.y) >> (16 * (k & 1)) & 0xffffu;
+        if (m & kMetaKept) o[m & kMetaPos] = x[k];
+      }
+    }
+  };
+  // one step of the forward recursion to level l; p = exp(dense score) of this thread's
+  // states on frame l - 1, m4 = their meta words on level l
+  auto forward_step = [&](int32_t l, const double (&p)[K], uint2 m4) {
+    double h1 = __shfl_up_sync(kAll, v[K - 1], 1), h2 = __shfl_up_sync(kAll, v[K - 2], 1);
+    if (lane == 0) h1 = h2 = 0.0;
+    double nv[K];
+#pragma unroll
+    for (int k = 0; k < K; ++k) {
+      const uint32_t m = (k < 2 ? m4.x : m4.y) >> (16 * (k & 1));
+      const double a = v[k];
+      const double b = k >= 1 ? v[k >= 1 ? k - 1 : 0] : h1;
+      const double c = k >= 2 ? v[k >= 2 ? k - 2 : 0] : (k == 1 ? h1 : h2);
+      double acc = 0.0;
+      if (m & (1u << kMetaInShift)) acc = e0[k] * a;
+      if (m & (2u << kMetaInShift)) acc = fma(e1[k], b, acc);
+      if (m & (4u << kMetaInShift)) acc = fma(e2[k], c, acc);
+      nv[k] = acc * p[k];
+      min_hi = min(min_hi, (uint32_t)__double2hiint(nv[k]) - 1u);
+    }
+    store4(l, m4, nv);
+#pragma unroll
+    for (int k = 0; k < K; ++k) v[k] = nv[k];
+  };
+  auto backward_step = [&](int32_t l, const double (&p)[K], uint2 m4) {
+    // what the sources add: beta * p of the level above, own and the next lane's first two
+    double bp[K + 2];
+#pragma unroll
+    for (int k = 0; k < K; ++k) bp[k] = v[k] * p[k];
+    bp[K] = __shfl_down_sync(kAll, bp[0], 1);
+    bp[K + 1] = __shfl_down_sync(kAll, bp[1], 1);
+    if (lane == 31) bp[K] = bp[K + 1] = 0.0;
+#pragma unroll
+    for (int k = 0; k < K; ++k) {
+      const uint32_t m = (k < 2 ? m4.x : m4.y) >> (16 * (k & 1));
+      double acc = 0.0;
+      if (m & (1u << kMetaOutShift)) acc = e0[k] * bp[k];
+      if (m & (2u << kMetaOutShift)) acc = fma(e1[k], bp[k + 1], acc);
+      if (m & (4u << kMetaOutShift)) acc = fma(e2[k], bp[k + 2], acc);
+      v[k] = acc;
+      min_hi = min(min_hi, (uint32_t)__double2hiint(acc) - 1u);
+    }
+    store4(l, m4, v);
+  };
+  auto meta_of = [&](const uint16_t *row) {  // this thread's four words of a meta row
+    return has_meta ? *reinterpret_cast<const uint2 *>(row + s0) : make_uint2(0u, 0u);
+  };
+  if (dir == 0) {
+    // level 0: the start state holds 1
+#pragma unroll
+    for (int k = 0; k < K; ++k) v[k] = s0 + k == 0 ? 1.0 : 0.0;
+    {
+      const uint2 m4 = meta_of(meta0);
+      if (mine && s0 == 0 && (m4.x & kMetaKept)) out[lstart[0] + (int32_t)(m4.x & kMetaPos)] = 1.0;
+      if (tid == 0) oscale[0] = 0;
+    }
+    for (int32_t q = 0; q < num_batches; ++q) {
+      const int32_t slot = q % nbatch;
+      if (!late) late = !WaitSlot(&full[slot], (unsigned)(q / nbatch) & 1u, wait_limit);
+      if (q > 0) {
+        rescale(true);  // its barrier also says: every warp has finished batch q - 1
+        if (tid == 0 && !late) issue();
+      }
+      const int32_t nf = min(F, T - q * F);
+      const float *rowbuf = ring + (size_t)slot * F * C;
+      const uint16_t *mbuf = mring + (size_t)slot * F * mrow;
+      for (int32_t r = 0; r < nf; ++r, rowbuf += C, mbuf += mpitch) {
+        if (r == kHalfBatch) rescale(false);
+        if (tid == 0) oscale[q * F + r + 1] = Ksh;
+        double p[K];
+#pragma unroll
+        for (int k = 0; k < K; ++k) p[k] = ExpDenseFast(rowbuf[col[k]]);
+        forward_step(q * F + r + 1, p, meta_of(mbuf));
+      }
+    }
+    // the implied final row: level T + 1
+    rescale(true);
+    {
+      if (tid == 0) oscale[T + 1] = Ksh;
+      double p[K];
+#pragma unroll
+      for (int k = 0; k < K; ++k) p[k] = (fin >> k) & 1u ? 1.0 : 0.0;
+      forward_step(T + 1, p, meta_of(meta0 + (int64_t)(T + 1) * mpitch));
+    }
+    if (mine && S - 1 >= s0 && S - 1 < s0 + K) {
+      double z = 0.0;
+#pragma unroll
+      for (int k = 0; k < K; ++k)
+        if (s0 + k == S - 1) z = v[k];
+      if (z > 0.0 && !late) {
+        tot[i] = log(z) + (double)Ksh * 0.69314718055994530942;
+        BandTotal zt;
+        zt.m = z;
+        zt.e = Ksh;
+        zt.pad = 0;
+        total[i] = zt;
+      }
+    }
+  } else {
+    // level T + 1: the final state holds 1; then level T through the implied final row
+#pragma unroll
+    for (int k = 0; k < K; ++k) v[k] = s0 + k == S - 1 ? 1.0 : 0.0;
+    {
+      const uint2 m4 = meta_of(meta0 + (int64_t)(T + 1) * mpitch);
+#pragma unroll
+      for (int k = 0; k < K; ++k) {
+        const uint32_t m = (k < 2 ? m4.x : m4.y) >> (16 * (k & 1)) & 0xffffu;
+        if (mine && s0 + k == S - 1 && (m & kMetaKept))
+          out[lstart[T + 1] + (int32_t)(m & kMetaPos)] = 1.0;
+      }
+      if (tid == 0) oscale[T + 1] = oscale[T] = 0;
+      double p[K];
+#pragma unroll
+      for (int k = 0; k < K; ++k) p[k] = (fin >> k) & 1u ? 1.0 : 0.0;
+      backward_step(T, p, meta_of(meta0 + (int64_t)T * mpitch));
+    }
+    for (int32_t q = 0; q < num_batches; ++q) {
+      const int32_t slot = q % nbatch;
+      if (!late) late = !WaitSlot(&full[slot], (unsigned)(q / nbatch) & 1u, wait_limit);
+      rescale(true);  // also: every warp has finished batch q - 1
+      if (q > 0 && tid == 0 && !late) issue();
+      const int32_t r1 = T - q * F, r0 = max(T - (q + 1) * F, 0);
+      const float *rowbuf = ring + (size_t)slot * F * C + (size_t)(r1 - 1 - r0) * C;
+      const uint16_t *mbuf = mring + (size_t)slot * F * mrow + (size_t)(r1 - 1 - r0) * mpitch;
+      for (int32_t r = r1 - 1; r >= r0; --r, rowbuf -= C, mbuf -= mpitch) {  // level r from r + 1
+        if (r1 - 1 - r == kHalfBatch) rescale(false);
+        if (tid == 0) oscale[r] = Ksh;
+        double p[K];
+#pragma unroll
+        for (int k = 0; k < K; ++k) p[k] = ExpDenseFast(rowbuf[col[k]]);
+        backward_step(r, p, meta_of(mbuf));
+      }
+    }
+  }
+  if (late) any_late = 1;
+  if (bad || min_hi < kTinyHi) any_bad = 1;
+  __syncthreads();
+  if (any_late) {
+    if (tid == 0) {
+      atomicOr(status, kStatusLate);
+      for (int32_t q = max(0, issued - nbatch); q < issued; ++q)
+        WaitSlot(&full[q % nbatch], (unsigned)(q / nbatch) & 1u, kDrainPolls);
+    }
+    __syncthreads();
+  }
+  if (tid == 0 && any_bad) atomicOr(&unfit[i], kUnfitRange);
+  if (dir == 0 && tid == 0 && (*status & kStatusLate)) tot[i] = nan("");
+}
+
+// The ring of chunks of BandChainExact: lane 0 requests, every lane waits.
 struct ChunkRing {
   uint64_t *full;          // [kChainSlots]
   BandItem *slots;         // [kChainSlots][kSlotItems]
@@ -655,8 +1018,9 @@ struct ChunkRing {
   __device__ __forceinline__ void Issue() {  // lane 0: the next chunk into the next slot
     if (issued >= num_chunks) return;
     const int32_t c = ChunkOf(issued), slot = issued % kChainSlots;
-    // at least one entry, so that the slot's barrier completes once per use
-    const int32_t n = max(min(ChunkItems(c), kSlotItems), 1);
+    // an even number of entries (16 bytes), at least two, so that the copy is legal and the
+    // slot's barrier completes once per use; a chunk starts on a multiple of four entries
+    const int32_t n = max((min(ChunkItems(c), kSlotItems) + 1) & ~1, 2);
     const unsigned bytes = (unsigned)n * (unsigned)sizeof(BandItem);
     MbarArriveExpectTx(&full[slot], bytes);
     BulkCopyG2S(slots + (size_t)slot * kSlotItems, items0 + (int64_t)c * kPrepLevels * pitch,
@@ -668,181 +1032,6 @@ struct ChunkRing {
       WaitSlot(&full[k % kChainSlots], (unsigned)(k / kChainSlots) & 1u, kDrainPolls);
   }
 };
-
-__global__ void __launch_bounds__(32)
-BandChainLean(const BandInfo *__restrict__ infos, const BandItem *__restrict__ items,
-              const int2 *__restrict__ lists, double *__restrict__ am, double *__restrict__ bm,
-              int32_t *__restrict__ a_scale, int32_t *__restrict__ b_scale,
-              double *__restrict__ tot, BandTotal *__restrict__ total,
-              int32_t *__restrict__ unfit, int32_t *__restrict__ status, int32_t st_pad,
-              int32_t lv_pad, int32_t wait_limit) {
-  extern __shared__ __align__(16) unsigned char smem_raw[];
-  __shared__ __align__(8) uint64_t full[kChainSlots];
-  constexpr unsigned kAll = 0xffffffffu;
-  const int dir = blockIdx.x;
-  const int32_t i = blockIdx.y;
-  const BandInfo f = infos[i];
-  const int lane = threadIdx.x;
-  const int32_t S = f.num_states, T = f.frames, pitch = f.pitch, L = T + 2;
-  if (dir == 0 && lane == 0) {
-    tot[i] = -INFINITY;
-    BandTotal z;
-    z.m = 0.0;
-    z.e = 0;
-    z.pad = 0;
-    total[i] = z;
-  }
-  if (S == 0) return;
-  BandItem *ring = reinterpret_cast<BandItem *>(smem_raw);                 // [slots][kSlotItems]
-  int2 *lst = reinterpret_cast<int2 *>(ring + kChainSlots * kSlotItems);   // [lv_pad]
-  // alpha: [2][st_pad] by state (s at s + 2); beta: [2][st_pad][3] products by state
-  double *vals = reinterpret_cast<double *>(lst + lv_pad);
-  for (int32_t l = lane; l < L; l += 32) lst[l] = lists[f.level_off + l];
-  const int32_t buf_elems = st_pad * (dir == 0 ? 1 : 3);
-  for (int32_t k = lane; k < 2 * buf_elems; k += 32) vals[k] = 0.0;
-  if (lane == 0) {
-    for (int st = 0; st < kChainSlots; ++st) MbarInit(&full[st], 1);
-    MbarInitFence();
-  }
-  __syncwarp();
-  ChunkRing rg;
-  rg.full = full;
-  rg.slots = ring;
-  rg.items0 = items + f.grid_off;
-  rg.lst = lst;
-  rg.pitch = pitch;
-  rg.L = L;
-  rg.num_chunks = (L + kPrepLevels - 1) / kPrepLevels;
-  rg.dir = dir;
-  rg.issued = 0;
-  if (lane == 0)
-    for (int32_t k = 0; k < kChainSlots; ++k) rg.Issue();
-  double *om = (dir == 0 ? am : bm) + f.grid_off;
-  int32_t *oscale = (dir == 0 ? a_scale : b_scale) + f.level_off;
-  // The first level holds one state with the value 1: the start state walking forward,
-  // the final state walking backward.  It is written here, so that the loop below has no
-  // special case; the loop then skips the first level of the first chunk.
-  {
-    const int32_t l0 = dir == 0 ? 0 : L - 1;
-    const int2 ls = lst[l0];
-    if (lane < ls.y) {  // the list has at most that one state
-      const BandItem it = rg.items0[ls.x + lane];
-      const double v = it.s == (dir == 0 ? 0 : S - 1) ? 1.0 : 0.0;
-      om[ls.x + lane] = v;
-      if (dir == 0) {
-        vals[2 + it.s] = v;
-      } else {
-        double *o = vals + 6 + 3 * it.s;
-        o[0] = it.pw[0] * v;
-        o[1] = it.pw[1] * v;
-        o[2] = it.pw[2] * v;
-      }
-    }
-    if (lane == 0) oscale[l0] = 0;
-  }
-  __syncwarp();
-  int32_t Ksh = 0;       // the stored values of a level are divided by 2^Ksh
-  int32_t hi_max = 0;    // largest high word among the values since the last rescaling
-  bool bad = false, late = false;
-  int32_t step = 1;      // levels done; buffer (step & 1) receives the level of this step
-  for (int32_t q = 0; q < rg.num_chunks; ++q) {
-    const int32_t c = rg.ChunkOf(q), slot = q % kChainSlots;
-    if (!late) late = !WaitSlot(&full[slot], (unsigned)(q / kChainSlots) & 1u, wait_limit);
-    // a list that did not arrive must not be walked (its state numbers index shared memory)
-    late = __any_sync(kAll, late);
-    if (late) break;
-    const int32_t chunk_start = c * kPrepLevels * pitch;
-    const int32_t l_lo = c * kPrepLevels, nl = min(l_lo + kPrepLevels, L) - l_lo;
-    // a chunk beyond the slot's capacity is read from global memory
-    const bool fits = rg.ChunkItems(c) <= kSlotItems;
-    const BandItem *src = fits ? ring + (size_t)slot * kSlotItems - chunk_start : rg.items0;
-    const int32_t k0 = q == 0 ? 1 : 0;  // the very first level is done
-    const int32_t dl = dir == 0 ? 1 : -1;
-    int32_t l = dir == 0 ? l_lo + k0 : l_lo + nl - 1 - k0;
-    int2 ls = make_int2(0, 0);
-    BandItem it;
-    it.s = 0;
-    if (k0 < nl) {
-      ls = lst[l];
-      if (lane < ls.y) it = src[ls.x + lane];
-    }
-#pragma unroll 2
-    for (int32_t k = k0; k < nl; ++k, ++step, l += dl) {
-      // ---- the next level's entry is requested before this level's arithmetic --------
-      int2 ls_next = make_int2(0, 0);
-      BandItem it_next;
-      it_next.s = 0;
-      if (k + 1 < nl) {
-        ls_next = lst[l + dl];
-        if (lane < ls_next.y) it_next = src[ls_next.x + lane];
-      }
-      double *cur = vals + (step & 1) * buf_elems;
-      const double *prv = vals + ((step & 1) ^ 1) * buf_elems;
-      // every kRescale-th step the scale follows the largest value since the last time
-      double scale = 1.0;
-      if ((step & (kRescale - 1)) == 0) {
-        const int32_t hm = __reduce_max_sync(kAll, hi_max);
-        const int32_t e = hm > 0 ? (hm >> 20) - 1023 : 0;
-        Ksh += e;
-        scale = __longlong_as_double((long long)(1023 - e) << 52);
-        hi_max = 0;
-      }
-      if (lane == 0) oscale[l] = Ksh;
-      for (int32_t j = lane; j < ls.y; j += 32) {
-        if (j >= 32) it = src[ls.x + j];  // a level of more than 32 states
-        const int32_t s = it.s;
-        double v;
-        if (dir == 0) {
-          const double *p = prv + 2 + s;
-          v = fma(it.pw[2], p[-2], fma(it.pw[1], p[-1], it.pw[0] * p[0])) * scale;
-          cur[2 + s] = v;
-        } else {
-          const double *p = prv + 6 + 3 * s;
-          const double c0 = p[0], c1 = p[4], c2 = p[8];
-          v = ((it.outb & 1u ? c0 : 0.0) + (it.outb & 2u ? c1 : 0.0) +
-               (it.outb & 4u ? c2 : 0.0)) * scale;
-          double *o = cur + 6 + 3 * s;
-          o[0] = it.pw[0] * v;
-          o[1] = it.pw[1] * v;
-          o[2] = it.pw[2] * v;
-        }
-        om[ls.x + j] = v;
-        const int32_t hi = __double2hiint(v);  // v >= 0
-        hi_max = max(hi_max, hi);
-        // a listed state whose entering arcs all fail their tests is a true zero; any other
-        // value must keep clear of the ends of a double's range
-        bad |= v != 0.0 && (uint32_t)(hi - ((1023 - 900) << 20)) >= (uint32_t)(1800 << 20);
-      }
-      __syncwarp();  // the level is complete
-      ls = ls_next;
-      it = it_next;
-    }
-    if (lane == 0) rg.Issue();  // the chunk is done with: its slot takes the next one
-  }
-  if (late) {
-    if (lane == 0) {
-      atomicOr(status, kStatusLate);
-      rg.Drain();
-    }
-    __syncwarp();
-  }
-  if (__any_sync(kAll, bad) && lane == 0) atomicOr(&unfit[i], kUnfitRange);
-  if (dir == 0 && lane == 0) {
-    // alpha of the final state on the last level, if that state survived
-    const int2 ls = lst[L - 1];
-    const double v = ls.y > 0 ? vals[((step - 1) & 1) * buf_elems + 2 + (S - 1)] : 0.0;
-    if (*status & kStatusLate) {
-      tot[i] = nan("");
-    } else if (!late && v > 0.0 && rg.items0[ls.x].s == S - 1) {
-      tot[i] = log(v) + (double)Ksh * 0.69314718055994530942;
-      BandTotal z;
-      z.m = v;
-      z.e = Ksh;
-      z.pad = 0;
-      total[i] = z;
-    }
-  }
-}
 
 // The same recursion with a (mantissa, exponent) pair per state, for the graphs marked in
 // `unfit`; every other graph returns at once.  exp(dense score) is recomputed from the
@@ -1138,9 +1327,10 @@ struct BandLayout {
   long long arc_frames = 0;
   int32_t max_states = 0, max_frames = 0;
   int32_t vit_threads = 32, vit_frames = 0, vit_batches = 0, xch_pad = 0;
+  int32_t chain_batches = 0, mrow = 0;
   int32_t st_pad = 0, lv_pad = 0;
-  size_t chain_smem = 0, viterbi_smem = 0, prep_smem = 0;
-  size_t off_infos, off_vf, off_vb, off_items, off_lists, off_cutoffs, off_am, off_ae, off_bm,
+  size_t chain_smem = 0, exact_smem = 0, viterbi_smem = 0, prep_smem = 0;
+  size_t off_infos, off_vf, off_vb, off_items, off_lists, off_meta, off_cutoffs, off_am, off_ae, off_bm,
       off_be, off_a_scale, off_b_scale, off_total, off_unfit, off_totals, off_status,
       total_bytes;  // off_status = off_totals + 40
   bool ok = true;
@@ -1158,7 +1348,7 @@ static int32_t MakeBandLayout(const k2b200_band_loss_args *a, BandLayout *L) {
               "host arrays of the batch description are required");
   K2B_REQUIRE(a->num_classes > 0, "empty log-prob matrix");
   L->infos.resize(a->num_fsas);
-  int64_t grid = 0, levels = 0;
+  int64_t grid = 0, levels = 0, meta_words = 0;
   for (int32_t i = 0; i < a->num_fsas; ++i) {
     BandInfo &f = L->infos[i];
     f.state_off = a->h_a_row_splits1[i];
@@ -1177,7 +1367,11 @@ static int32_t MakeBandLayout(const k2b200_band_loss_args *a, BandLayout *L) {
     if (i > 0 && f.lp_row == a->h_first_row[i - 1]) L->exclusive_rows = false;
     f.level_off = (int32_t)levels;
     f.grid_off = grid;
+    f.mpitch = std::max((f.num_states + 7) & ~7, 8);
+    f.pad = 0;
+    f.meta_off = meta_words;
     grid += (int64_t)(f.frames + 2) * f.pitch;
+    meta_words += (int64_t)(f.frames + 2) * f.mpitch;
     levels += f.frames + 2;
     L->max_states = std::max(L->max_states, f.num_states);
     L->max_frames = std::max(L->max_frames, f.frames);
@@ -1209,20 +1403,28 @@ static int32_t MakeBandLayout(const k2b200_band_loss_args *a, BandLayout *L) {
       L->why = "too many states or classes for the Viterbi kernel";
     }
   }
-  L->st_pad = ((L->max_states + 4) + 3) & ~3;
+  L->st_pad = ((L->max_states + 4) + 15) & ~15;
   L->lv_pad = (L->max_frames + 2 + 3) & ~3;
-  L->prep_smem = (size_t)4 * 5 * L->st_pad;
-  L->chain_smem = sizeof(BandItem) * kChainSlots * kSlotItems + sizeof(int2) * (size_t)L->lv_pad +
-                  (size_t)48 * L->st_pad;
+  L->prep_smem = (size_t)4 * 8 * L->st_pad;
+  L->exact_smem = sizeof(BandItem) * kChainSlots * kSlotItems + sizeof(int2) * (size_t)L->lv_pad +
+                  sizeof(ProbState) * 2 * (size_t)L->st_pad;
+  {  // BandChainDense: the Viterbi kernel's batches plus the meta rows
+    L->mrow = std::max((L->max_states + 7) & ~7, 8);
+    const size_t batch_bytes =
+        (size_t)L->vit_frames * (sizeof(float) * (size_t)a->num_classes + 2 * (size_t)L->mrow);
+    const size_t fixed = sizeof(double) * 2 * (size_t)L->xch_pad + sizeof(int32_t) * (size_t)L->lv_pad;
+    L->chain_batches = kBandSmemBudget >= fixed + 3 * batch_bytes ? 3 : 2;
+    L->chain_smem = fixed + (size_t)L->chain_batches * batch_bytes;
+  }
   if (L->max_states > kBandMaxStates) {
     L->ok = false;
     L->why = "a graph has more than 512 states";
   } else if (a->num_classes % 4 != 0 || (reinterpret_cast<uintptr_t>(a->log_probs) & 15) != 0) {
     L->ok = false;
     L->why = "rows of the log-prob matrix are not 16-byte aligned";
-  } else if (L->chain_smem > kBandSmemBudget) {
+  } else if (L->chain_smem > kBandSmemBudget + 16384 || L->exact_smem > kBandSmemBudget) {
     L->ok = false;
-    L->why = "too many frames for the level table in shared memory";
+    L->why = "too many frames, states or classes for the shared memory of the recursions";
   } else if (a->num_fsas > 65535) {
     L->ok = false;
     L->why = "more than 65535 graphs";
@@ -1238,6 +1440,7 @@ static int32_t MakeBandLayout(const k2b200_band_loss_args *a, BandLayout *L) {
   L->off_vb = take(sizeof(float) * (size_t)grid);
   L->off_items = take(sizeof(BandItem) * (size_t)grid);
   L->off_lists = take(sizeof(int2) * (size_t)levels);
+  L->off_meta = take(sizeof(uint16_t) * (size_t)meta_words);
   L->off_cutoffs = take(sizeof(float) * a->num_fsas);
   L->off_am = take(sizeof(double) * (size_t)grid);
   L->off_ae = take(sizeof(int32_t) * (size_t)grid);
@@ -1275,10 +1478,10 @@ static bool BandReduceBeam(const k2b200_band_loss_args *a, const long long *h_to
 
 static int32_t LaunchBandChains(const BandLayout &L, const k2b200_band_loss_args *args, char *ws,
                                 double *tot_scores, cudaStream_t stream) {
-  K2B_CUDA_OK(cudaFuncSetAttribute(BandChainLean, cudaFuncAttributeMaxDynamicSharedMemorySize,
+  K2B_CUDA_OK(cudaFuncSetAttribute(BandChainDense, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                    (int)L.chain_smem));
   K2B_CUDA_OK(cudaFuncSetAttribute(BandChainExact, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                   (int)L.chain_smem));
+                                   (int)L.exact_smem));
   dim3 grid(2, args->num_fsas);
   const BandInfo *infos = reinterpret_cast<const BandInfo *>(ws + L.off_infos);
   const BandItem *items = reinterpret_cast<const BandItem *>(ws + L.off_items);
@@ -1287,11 +1490,13 @@ static int32_t LaunchBandChains(const BandLayout &L, const k2b200_band_loss_args
   BandTotal *total = reinterpret_cast<BandTotal *>(ws + L.off_total);
   int32_t *unfit = reinterpret_cast<int32_t *>(ws + L.off_unfit);
   int32_t *status = reinterpret_cast<int32_t *>(ws + L.off_status);
-  { BandChainLean<<<grid, 32, L.chain_smem, stream>>>(
-      infos, items, lists, am, bm, reinterpret_cast<int32_t *>(ws + L.off_a_scale),
-      reinterpret_cast<int32_t *>(ws + L.off_b_scale), tot_scores, total, unfit, status, L.st_pad,
-      L.lv_pad, g_wait_limit); NoteLaunch(); }
-  { BandChainExact<<<grid, 32, L.chain_smem, stream>>>(
+  { BandChainDense<<<grid, L.vit_threads, L.chain_smem, stream>>>(
+      infos, reinterpret_cast<const BandState *>(args->band_states), args->log_probs,
+      args->num_classes, reinterpret_cast<const uint16_t *>(ws + L.off_meta), lists, am, bm,
+      reinterpret_cast<int32_t *>(ws + L.off_a_scale),
+      reinterpret_cast<int32_t *>(ws + L.off_b_scale), tot_scores, total, unfit, status,
+      L.vit_frames, L.chain_batches, L.xch_pad, L.mrow, L.lv_pad, g_wait_limit); NoteLaunch(); }
+  { BandChainExact<<<grid, 32, L.exact_smem, stream>>>(
       infos, reinterpret_cast<const BandArc *>(args->band_arcs), args->log_probs,
       args->num_classes, items, lists, am, reinterpret_cast<int32_t *>(ws + L.off_ae), bm,
       reinterpret_cast<int32_t *>(ws + L.off_be), tot_scores, total, unfit, status, L.st_pad,
@@ -1400,12 +1605,12 @@ int32_t k2b200_band_loss_forward(const k2b200_band_loss_args *args, void *worksp
       dim3 grid(CeilDiv(L.max_frames + 2, 4 * kPrepLevels), args->num_fsas);
       { BandPrep<<<grid, 128, L.prep_smem, stream>>>(
           reinterpret_cast<const BandInfo *>(ws + L.off_infos),
-          reinterpret_cast<const BandState *>(args->band_states),
-          reinterpret_cast<const BandArc *>(args->band_arcs), args->a_row_splits2,
+          reinterpret_cast<const BandState *>(args->band_states), args->a_row_splits2,
           args->log_probs, args->num_classes, reinterpret_cast<const float *>(ws + L.off_vf),
           reinterpret_cast<const float *>(ws + L.off_vb), beam,
           reinterpret_cast<BandItem *>(ws + L.off_items),
           reinterpret_cast<int2 *>(ws + L.off_lists),
+          reinterpret_cast<uint16_t *>(ws + L.off_meta),
           reinterpret_cast<float *>(ws + L.off_cutoffs),
           reinterpret_cast<unsigned long long *>(ws + L.off_totals),
           reinterpret_cast<int32_t *>(ws + L.off_unfit), L.st_pad); NoteLaunch(); }
@@ -1415,7 +1620,7 @@ int32_t k2b200_band_loss_forward(const k2b200_band_loss_args *args, void *worksp
     if (need_count) K2B_FORWARD(SideFork(stream, &side));  // behind the counts, before the chain
     {
       PhaseTimer timer(kPhaseChain, stream);
-      NotePhaseKernel(kPhaseChain, "BandChain");
+      NotePhaseKernel(kPhaseChain, "BandChainDense");
       K2B_FORWARD(LaunchBandChains(L, args, ws, tot_scores, stream));
     }
     if (!need_count) break;

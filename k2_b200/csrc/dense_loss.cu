@@ -1473,6 +1473,8 @@ __global__ void StateInLabels(const Arc *__restrict__ arcs, const int32_t *__res
 __global__ void __launch_bounds__(256)
 GridGradStates(const FsaInfo *__restrict__ infos, const int32_t *__restrict__ state_label,
                const int32_t *__restrict__ one_label, int32_t cols,
+               const float *__restrict__ vfwd, const float *__restrict__ vbwd,
+               const float *__restrict__ cutoffs,
                const ProbState *__restrict__ alpha, const ProbState *__restrict__ beta,
                const double *__restrict__ tot_grad, int32_t tot_grad_stride,
                float *__restrict__ grad_b, int32_t frames_per_cta, int32_t exclusive_rows,
@@ -1499,11 +1501,15 @@ GridGradStates(const FsaInfo *__restrict__ infos, const int32_t *__restrict__ st
   for (int32_t k = tid; k < elems; k += nt) gb[k] = 0u;
   __syncthreads();
   const int32_t *labels = state_label + f.state_off;
+  const float cutoff = cutoffs[i];
+  const float *fgrid = vfwd + f.grid_off, *bgrid = vbwd + f.grid_off;
   for (int32_t k = tid; k < (u1 - u0) * S; k += nt) {
     const int32_t fr = k / S, s = k - fr * S;
     const int32_t c = labels[s] + 1;
     if (c < 0 || c >= cols) continue;
     const int64_t gi = (int64_t)(u0 + fr + 1) * S + s;
+    // the recursions of some graphs leave the grids of pruned states unwritten
+    if (!(__fadd_rn(fgrid[gi], bgrid[gi]) > cutoff)) continue;
     const ProbState a = al[gi];
     if (a.m == 0.0) continue;
     const ProbState b = be[gi];
@@ -1928,6 +1934,9 @@ static int32_t DenseLossBackward(const k2b200_intersect_args *args, void *worksp
     { GridGradStates<<<grid, 256, smem, stream>>>(
         reinterpret_cast<const FsaInfo *>(ws + L.off_infos),
         reinterpret_cast<const int32_t *>(ws + LL.off_state_label), LL.served, args->cols,
+        reinterpret_cast<const float *>(ws + L.off_fwd),
+        reinterpret_cast<const float *>(ws + L.off_bwd),
+        reinterpret_cast<const float *>(ws + L.off_cutoffs),
         reinterpret_cast<const ProbState *>(ws + LL.off_alpha),
         reinterpret_cast<const ProbState *>(ws + LL.off_beta), tot_grad, tot_grad_stride, grad_b,
         frames, LL.exclusive_rows ? 1 : 0, LL.lp_row, LL.lp_cols); NoteLaunch(); }
@@ -1938,7 +1947,8 @@ static int32_t DenseLossBackward(const k2b200_intersect_args *args, void *worksp
         reinterpret_cast<const Arc *>(args->a_arcs), args->num_arcs,
         reinterpret_cast<ArcFactor *>(ws + LL.off_arc_factors)); NoteLaunch(); }
   const int32_t *only_noplan = nullptr;
-  NotePhaseKernel(kPhaseGrad, !LL.identity ? "GridGradLanes"
+  NotePhaseKernel(kPhaseGrad, grad_a == nullptr ? "GridGradStates (arc posteriors when a state has several labels)"
+                              : !LL.identity ? "GridGradLanes"
                               : (L.max_states > 256 && L.max_states <= 1024) ? "GridGradItems"
                                                                              : "GridGradWarp");
   if (!LL.identity) {

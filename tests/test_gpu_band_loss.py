@@ -216,9 +216,10 @@ def test_same_numbers_as_the_general_kernels_and_the_lattice():
         lp, seg = random_log_probs(rng, n, 25, 16)
         tot1, ga1, gb1 = run(a, lp, seg, 6.0, band=True)
         tot0, ga0, gb0 = run(a, lp, seg, 6.0, band=False)
-        assert close(tot1, tot0, rtol=1e-9, atol=1e-9)
-        assert np.abs(ga1 - ga0).max(initial=0) <= 2e-6
-        assert np.abs(gb1 - gb0).max(initial=0) <= 2e-6
+        # the band kernels take exp(dense score) to float precision
+        assert close(tot1, tot0, rtol=1e-7, atol=1e-6)
+        assert np.abs(ga1 - ga0).max(initial=0) <= 1e-5
+        assert np.abs(gb1 - gb0).max(initial=0) <= 1e-5
         dense = k2.DenseFsaVec(lp.to(DEV), seg)
         lat = k2.intersect_dense(host_to_fsa(a), dense, 6.0)
         tot2 = lat.get_tot_scores(log_semiring=True, use_double_scores=True).cpu().numpy()

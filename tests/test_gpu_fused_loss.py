@@ -17,11 +17,12 @@ pytestmark = pytest.mark.gpu
 DEV = "cuda:0"
 
 
-def _fused(a_host, scores, brs, beam, amap=None, tot_grad=None, use_double=True, **limits):
+def _fused(a_host, scores, brs, beam, amap=None, tot_grad=None, use_double=True,
+           want_grad_a=True, **limits):
     import k2_b200 as k2
     from gpu_util import dense_from_scores, host_to_fsa
     fsa = host_to_fsa(a_host)
-    fsa.scores.requires_grad_(True)
+    fsa.scores.requires_grad_(want_grad_a)
     dense = dense_from_scores(scores, brs, requires_grad=True)
     m = None if amap is None else torch.as_tensor(amap, dtype=torch.int32)
     assert k2.dense_loss_supported(fsa, dense, m)
@@ -32,7 +33,8 @@ def _fused(a_host, scores, brs, beam, amap=None, tot_grad=None, use_double=True,
     finite = torch.isfinite(tot)
     if bool(finite.any()):
         (tot[finite] * g[finite]).sum().backward()
-        ga, gb = fsa.scores.grad.cpu().numpy(), dense.scores.grad.cpu().numpy()
+        gb = dense.scores.grad.cpu().numpy()
+        ga = fsa.scores.grad.cpu().numpy() if want_grad_a else None
     else:
         ga = np.zeros(a_host.num_arcs, np.float32)
         gb = np.zeros(scores.shape, np.float32)
@@ -78,6 +80,35 @@ def test_extreme_scores_take_the_per_state_exponent_kernels():
         else:
             a.arcs[::3, 3] = np.float32(-np.inf).view(np.int32)
         _compare(a, scores, brs, 1.0e4 if trial % 3 else 50.0, tag=f"extreme {trial}")
+
+
+def test_dense_gradient_alone():
+    # without a gradient for the graph scores: graphs in which every state has one label
+    # (CTC graphs, the LF-MMI denominator graph) take it from state posteriors, all others
+    # from the arc posteriors as before; same numbers either way
+    from gpu_util import fsa_to_host
+    from k2_b200 import synthetic as syn
+    import k2_b200 as k2
+    rng = np.random.default_rng(31)
+    for trial in range(12):
+        n = int(rng.integers(1, 6))
+        a = random_fsa_vec(rng, n, acyclic=bool(trial % 2))
+        scores, brs = random_dense(rng, n, 10, 5)
+        amap = np.sort(rng.integers(0, n, size=n)).astype(np.int32) if trial % 4 == 0 else None
+        tot_grad = rng.normal(size=n)
+        want = oracle.loss_path(a, scores, brs, 5.0, amap, tot_grad=tot_grad)
+        tot, ga, gb = _fused(a, scores, brs, 5.0, amap, tot_grad, want_grad_a=False)
+        assert close(tot, want["tot_scores"], rtol=1e-6, atol=1e-6)
+        assert np.abs(gb - want["grad_b"]).max(initial=0) <= 1e-4, trial
+    for name in ("ctc_small", "lfmmi_den"):
+        w = syn.WORKLOADS[name](scale=0.25)
+        graphs = syn.build_graphs(w, DEV)
+        dense = k2.DenseFsaVec(w.log_probs.to(DEV), w.supervision_segments)
+        a, scores, brs = fsa_to_host(graphs), dense.scores.cpu().numpy(), dense.h_row_splits
+        want = oracle.loss_path(a, scores, brs, w.output_beam)
+        tot, _, gb = _fused(a, scores, brs, w.output_beam, want_grad_a=False)
+        assert close(tot, want["tot_scores"], rtol=1e-6, atol=1e-6)
+        assert np.abs(gb - want["grad_b"]).max(initial=0) <= 1e-4, name
 
 
 def test_micro_example():
