@@ -464,7 +464,8 @@ int32_t k2b200_dense_loss_backward_log_probs(const k2b200_intersect_args *args, 
  *     k2b200_band_loss_status).  The workspace keeps what the backward needs.
  *   k2b200_band_loss_backward: with tot_grad[i * tot_grad_stride] = dL/dtot[i] (device,
  *     float64), ADDS dL/d(dense score) to grad_b[(grad_row0[i] + frame) * grad_pitch +
- *     label + grad_col_off] (grad_row0: device, one per graph).  grad_col_off = 0,
+ *     label + grad_col_off] (grad_row0: device, one per graph; NULL = h_first_row as the
+ *     forward call was given it).  grad_col_off = 0,
  *     grad_pitch = num_classes, grad_row0 = h_first_row gives the log-prob layout;
  *     grad_col_off = 1, grad_pitch = num_classes + 1 and grad_row0 = first row of the
  *     sequence the layout of the DenseFsaVec score matrix (including column 0 of the final

@@ -4,6 +4,7 @@ There is no CPU path and no fallback: importing this module fails loudly when th
 CUDA library has not been built.
 """
 import ctypes
+import threading
 import os
 
 import torch
@@ -273,6 +274,64 @@ def ptr(t) -> int:
 
 def stream_of(device) -> int:
     return torch.cuda.current_stream(device).cuda_stream
+
+
+# Workspaces of the loss calls are a gigabyte or more and live from a forward to its
+# backward.  Handed back to torch's caching allocator they get split for smaller tensors,
+# after which the next step needs a fresh cudaMalloc, which waits for the whole device.
+# So the last few are kept here, per device and stream (a workspace that comes back
+# may still be read by kernels queued on that stream; the next user queues behind them).
+_WS_POOL_MIN = 32 << 20   # smaller ones go through torch's allocator
+_WS_POOL_KEEP = 3         # idle workspaces kept per (device, stream)
+_ws_idle = {}
+_ws_lock = threading.Lock()
+
+
+class Workspace(object):
+    """A device byte buffer that returns to the pool when the last reference goes."""
+    __slots__ = ("tensor", "_key")
+
+    def __init__(self, tensor: torch.Tensor, key) -> None:
+        self.tensor = tensor
+        self._key = key
+
+    def __del__(self):
+        try:
+            if self._key is None:
+                return
+            with _ws_lock:
+                idle = _ws_idle.setdefault(self._key, [])
+                idle.append(self.tensor)
+                if len(idle) > _WS_POOL_KEEP:
+                    idle.sort(key=lambda t: t.numel())
+                    idle.pop(0)
+        except Exception:  # interpreter shutdown
+            pass
+
+
+def workspace(nbytes: int, device) -> Workspace:
+    """A buffer of at least `nbytes` bytes on `device` for the current stream."""
+    device = torch.device(device)
+    if nbytes < _WS_POOL_MIN:
+        return Workspace(torch.empty(max(nbytes, 1), dtype=torch.uint8, device=device), None)
+    key = (device.index, stream_of(device))
+    with _ws_lock:
+        idle = _ws_idle.get(key, [])
+        best = None
+        for k, t in enumerate(idle):
+            if nbytes <= t.numel() <= 2 * nbytes and (best is None or
+                                                      t.numel() < idle[best].numel()):
+                best = k
+        if best is not None:
+            return Workspace(idle.pop(best), key)
+    # some headroom, so that a slightly larger batch still fits
+    return Workspace(torch.empty(nbytes + nbytes // 8, dtype=torch.uint8, device=device), key)
+
+
+def release_workspaces() -> None:
+    """Gives the idle workspaces back to torch's allocator."""
+    with _ws_lock:
+        _ws_idle.clear()
 
 
 def upload_i32(arr, device) -> torch.Tensor:

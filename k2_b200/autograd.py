@@ -522,7 +522,8 @@ class _DenseTotScoresFunction(torch.autograd.Function):
         nbytes = ctypes.c_size_t()
         _lib.check(_lib.lib.k2b200_dense_loss_workspace_bytes(ctypes.byref(args),
                                                                ctypes.byref(nbytes)))
-        ws = torch.empty(nbytes.value, dtype=torch.uint8, device=dev)
+        lease = _lib.workspace(nbytes.value, dev)
+        ws = lease.tensor
         tot = torch.empty(a_fsas.arcs.num_fsas, dtype=torch.float64, device=dev)
         beam = ctypes.c_float()
         with torch.cuda.device(dev):
@@ -530,6 +531,7 @@ class _DenseTotScoresFunction(torch.autograd.Function):
                 ctypes.byref(args), _lib.ptr(ws), nbytes.value, _lib.stream_of(dev),
                 _lib.ptr(tot), ctypes.byref(beam)))
         ctx.args, ctx.keep, ctx.ws, ctx.ws_bytes = args, (keep, a_fsas.arcs), ws, nbytes.value
+        ctx.lease = lease
         ctx.dev = dev
         ctx.shape_a = unused_scores_a.shape
         ctx.shape_b = unused_scores_b.shape
@@ -586,6 +588,29 @@ def _band_loss_args(a_fsas: Fsa, b_fsas: DenseFsaVec, a_to_b_map: Optional[torch
     """(args, keep-alive objects, host map) of the k2b200_band_loss_* entry points, or
     None when they do not apply: `b_fsas` must come from a float32 CUDA log-prob tensor
     with 16-byte aligned rows and the graphs must be band graphs of at most 512 states."""
+    src = b_fsas._source
+    a = a_fsas.arcs
+    cached = b_fsas._band_args
+    version = (a.values()._version, None if a_to_b_map is None else a_to_b_map._version)
+    if (cached is not None and cached[0] is a and cached[1] is a_to_b_map
+            and cached[3] == version):
+        # same graphs, same sequences: only the limits can differ
+        if cached[2] is None:
+            return None
+        args0, keep, h_map = cached[2]
+        args = _lib.BandLossArgs.from_buffer_copy(args0)
+        args.output_beam = float(output_beam)
+        args.max_states = int(min(max_states, 2**31 - 1))
+        args.max_arcs = int(min(max_arcs, 2**31 - 1))
+        return args, keep, h_map
+    ans = _band_loss_args_uncached(a_fsas, b_fsas, a_to_b_map, output_beam, max_states, max_arcs)
+    b_fsas._band_args = (a, a_to_b_map, ans, version)
+    return ans
+
+
+def _band_loss_args_uncached(a_fsas: Fsa, b_fsas: DenseFsaVec,
+                             a_to_b_map: Optional[torch.Tensor], output_beam: float,
+                             max_states: int, max_arcs: int):
     src = b_fsas._source
     a = a_fsas.arcs
     if src is None or not a.values().is_cuda:
@@ -646,7 +671,8 @@ class _BandTotScoresFunction(torch.autograd.Function):
         nbytes = ctypes.c_size_t()
         _lib.check(_lib.lib.k2b200_band_loss_workspace_bytes(ctypes.byref(args),
                                                               ctypes.byref(nbytes)))
-        ws = torch.empty(nbytes.value, dtype=torch.uint8, device=dev)
+        lease = _lib.workspace(nbytes.value, dev)
+        ws = lease.tensor
         tot = torch.empty(a_fsas.arcs.num_fsas, dtype=torch.float64, device=dev)
         beam = ctypes.c_float()
         with torch.cuda.device(dev):
@@ -661,13 +687,11 @@ class _BandTotScoresFunction(torch.autograd.Function):
                     ctypes.byref(status)))
                 _band_state["status"] = status.value
         ctx.args, ctx.keep, ctx.ws, ctx.ws_bytes, ctx.dev = args, keep, ws, nbytes.value, dev
+        ctx.lease = lease
         ctx.shape_a, ctx.shape_b = unused_scores_a.shape, unused_scores_b.shape
         src = b_fsas._source
-        key = None if h_map is None else tuple(h_map.tolist())
         if unused_scores_b is src[0]:  # gradient in the layout of the log-probs
-            if key not in b_fsas._source_rows:
-                b_fsas._source_rows[key] = _lib.upload_i32(keep[3], dev)
-            ctx.grad_rows = b_fsas._source_rows[key]
+            ctx.grad_rows = None       # the rows the forward read
             ctx.grad_pitch, ctx.grad_col_off = int(args.num_classes), 0
         else:                          # in the layout of the score matrix
             rows = b_fsas.h_row_splits[:-1] if h_map is None else b_fsas.h_row_splits[h_map]

@@ -19,15 +19,19 @@
 //   BandPrep      all (graph, frame) levels in parallel: the reference's keep tests
 //                 (intersect_dense.cu:289-296, 430-471) on the two Viterbi grids, then per level
 //                 the COMPACT list of surviving states with, per state and entering arc, the
-//                 factor exp(arc score) * exp(dense score) if the arc survives and 0 otherwise.
-//   BandChain     one warp per (graph, direction) walks the levels over the lists only: a lane
-//                 takes one surviving state, reads its neighbours' alpha (beta) of the previous
-//                 level from shared memory by state number: three multiply-adds per state and
-//                 level, no exp or log, no test.  The lists arrive by bulk copies.  Values of a
-//                 level share a power-of-two scale that follows the data.
-//   BandChainExact  the same recursion with a (mantissa, exponent) pair per state, for the
-//                 graphs whose scores leave what a double with a per-level scale can hold; it
-//                 runs after BandChain and returns at once for every other graph.
+//                 factor exp(arc score) * exp(dense score) if the arc survives and 0 otherwise,
+//                 and the list positions of the states the arcs come from and go to.
+//   BandChainLists  one warp per (graph, direction) walks the levels over the lists only: a lane
+//                 holds the value of one surviving state, an entry names the list positions of
+//                 its neighbours on the previous level, whose values come by shuffles: three
+//                 multiply-adds per state and level, no exp or log, no test, no shared-memory
+//                 traffic for values.  The lists arrive by bulk copies.  Values of a level
+//                 share a power-of-two scale that follows the data.
+//   BandChainExact  the same recursion with a (mantissa, exponent) pair per state, by state
+//                 number in shared memory, for the graphs whose scores leave what a double
+//                 with a per-level scale can hold or whose levels are wider than the registers
+//                 of a warp; it runs after BandChainLists and returns at once for every other
+//                 graph.
 //   BandGrad      all levels in parallel: posterior of (level, state) = alpha * beta / Z is the
 //                 gradient of that state's dense score; optionally arc posteriors for the
 //                 gradient of the graph's arc scores.
@@ -66,14 +70,11 @@ static int32_t g_wait_limit = 4000000;  // polls of an mbarrier before a kernel 
 struct BandInfo {
   int32_t state_off;   // first state (idx01) of the graph in a_fsas
   int32_t num_states;  // S
-  int32_t pitch;       // S rounded up to a multiple of 4: row pitch of this pair's grids
+  int32_t pitch;       // 32 * (S / 32 + 1): row pitch of this pair's grids; a padded list fits
   int32_t frames;      // T
   int32_t lp_row;      // row of the log-prob matrix that holds frame 0
   int32_t level_off;   // sum over earlier pairs of (T + 2)
   int64_t grid_off;    // sum over earlier pairs of (T + 2) * pitch
-  int32_t mpitch;      // S rounded up to a multiple of 8: row pitch of this pair's meta grid
-  int32_t pad;
-  int64_t meta_off;    // sum over earlier pairs of (T + 2) * mpitch
 };
 
 // Per state (idx01): the arcs entering it.  w[d] = score of the arc from state s - d
@@ -97,10 +98,28 @@ struct __align__(8) BandItem {
 };
 static_assert(sizeof(BandItem) == 8, "BandItem must be 8 bytes");
 constexpr int kOutbByte = 7;
-// The same per (level, state) for ALL states, in 16 bits: bit 15 = the state survives,
-// bits 0-8 = its position in the level's list, bits 9-11 = inb, bits 12-14 = outb.
+// What the recursions read per list entry (level l, state s):
+//   pw[d]  = exp(score of the arc from state s - d) * exp(dense score of s's label on
+//            frame l - 1) if that arc survives between levels l - 1 and l, else 0;
+//   src[d] = position, in the list of level l - 1, of state s - d (0 when pw[d] is 0);
+//   dst[d] = position, in the list of level l + 1, of state s + d if the arc to it
+//            survives (whose factor is pw[d] of THAT entry), else kNoDst.
+// The lists of the kPrepLevels levels of a chunk are padded to the same multiple of 32 entries,
+// larger than the longest of them: a padding entry has pw = 0, src = 0 and dst = kNoDst, and
+// kNoDst (lane 31 of the last register) always names a padding entry of the next level.
+struct __align__(16) BandFactor {
+  double pw[3];
+  uint8_t src[4];  // [3] unused
+  uint8_t dst[4];  // [3] unused
+};
+static_assert(sizeof(BandFactor) == 32, "BandFactor must be 32 bytes");
+constexpr int kDstByte = 28;
+constexpr uint32_t kNoDst = 255;
+constexpr int kMaxListed = 95;  // entries of a level that the register recursion handles
+// words of BandPrep's per-state scratch: bit 15 = the state survives, bits 0-8 = its
+// position in the level's list, bits 9-11 = entering-arc bits
 constexpr uint32_t kMetaKept = 0x8000u, kMetaPos = 0x1ffu;
-constexpr int kMetaInShift = 9, kMetaOutShift = 12;
+constexpr int kMetaInShift = 9;
 
 // alpha of the final state on the last level (= Z) of a graph, as m * 2^e
 struct __align__(16) BandTotal {
@@ -446,50 +465,30 @@ BandViterbi(const BandInfo *__restrict__ infos, const BandState *__restrict__ ta
 }
 
 // ---------------------------------------------------------------------------
-// Keep tests.  grid = (level chunks, pairs), 4 warps per CTA, a warp per chunk of
-// kPrepLevels levels.  Per level the warp
-//   1. scans the two Viterbi rows (a lane reads 16 consecutive states of each; the rows of
-//      the next level are requested before this level is worked on), marks the surviving
-//      states and writes them, in state order, to a list in shared memory;
-//   2. takes the list one state per lane: the reference's arc tests
-//      (intersect_dense.cu:430-471) against the rows of the level before and the dense
-//      score of the state's label give the entering-arc bits;
-//   3. gives the states of the level before their leaving-arc bits, which are the
-//      entering-arc bits of this level seen from the source, and writes that level out.
-// Two forms of the result: per level the compact LIST of surviving states (for the
-// gradients and the exact recursion), and a 16-bit META word per (level, state) for all
-// states (for the dense recursion).  A warp writes the complete entries of the levels it
-// owns, so it also runs steps 1-2 for the level after its last.  totals[0] += surviving
-// states, totals[2] += the arcs leaving them (the sizes the beam reduction looks at,
-// intersect_dense.cu:289-320).  unfit[i] is set when a surviving arc has a score outside
-// what the dense recursion's arithmetic accepts.
+// Which states survive (intersect_dense.cu:289-296): state s of level l is kept iff
+// vf[l][s] + vb[l][s] > cutoff.  grid = (level chunks, pairs), a warp per kKeepLevels levels;
+// lane j looks at states 16 j .. 16 j + 15 and writes their keep bits as one 16-bit word,
+// keep[(level_off + l) * 32 + j].  totals[0] += surviving states, totals[2] += the arcs
+// leaving them: the sizes the beam reduction looks at (intersect_dense.cu:289-320), which
+// the host can read while the kernels behind this one run.
 // ---------------------------------------------------------------------------
-constexpr float kMinLeanDense = -20.0f;   // dense score of a surviving arc
-constexpr float kMaxLeanArc = 10.0f;      // |arc score| of a surviving arc
+constexpr int kKeepLevels = 8;
 
 __global__ void __launch_bounds__(128)
-BandPrep(const BandInfo *__restrict__ infos, const BandState *__restrict__ tab,
-         const int32_t *__restrict__ a_row_splits2, const float *__restrict__ lp, int32_t C,
+BandKeep(const BandInfo *__restrict__ infos, const int32_t *__restrict__ a_row_splits2,
          const float *__restrict__ vf, const float *__restrict__ vb, float beam,
-         BandItem *__restrict__ items, int2 *__restrict__ lists, uint16_t *__restrict__ meta,
-         float *__restrict__ cutoffs, unsigned long long *__restrict__ totals,
-         int32_t *__restrict__ unfit, int32_t s_pad) {
+         uint16_t *__restrict__ keep_bits, float *__restrict__ cutoffs,
+         unsigned long long *__restrict__ totals) {
   constexpr int K = kPrepK;
   constexpr unsigned kAll = 0xffffffffu;
-  extern __shared__ __align__(16) unsigned char smem_raw[];
   const int32_t i = blockIdx.y;
   const BandInfo f = infos[i];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const int32_t S = f.num_states, T = f.frames, pitch = f.pitch, mpitch = f.mpitch;
+  const int32_t S = f.num_states, T = f.frames, pitch = f.pitch;
   if (S == 0) return;
-  const int32_t a = (blockIdx.x * 4 + warp) * kPrepLevels;  // owns levels a .. b - 1
+  const int32_t a = (blockIdx.x * 4 + warp) * kKeepLevels;
   if (a > T + 1) return;
-  const int32_t b = min(a + kPrepLevels, T + 2);
-  // per warp: the meta words of the current and the previous level by state (zero
-  // outside the lists), and the two lists
-  uint16_t *meta_sm = reinterpret_cast<uint16_t *>(smem_raw) + (size_t)warp * 4 * s_pad;  // [2][s_pad]
-  uint16_t *list_sm = meta_sm + 2 * s_pad;                                                // [2][s_pad]
-  for (int32_t k = lane; k < 2 * s_pad; k += 32) meta_sm[k] = 0;
+  const int32_t b = min(a + kKeepLevels, T + 2);
   const float *fg = vf + f.grid_off, *bg = vb + f.grid_off;
   float cutoff;
   {
@@ -497,53 +496,118 @@ BandPrep(const BandInfo *__restrict__ infos, const BandState *__restrict__ tab,
     cutoff = __fsub_rn(start < end ? start : end, beam);
   }
   if (a == 0 && lane == 0) cutoffs[i] = cutoff;
-  const float *lp0 = lp + (int64_t)f.lp_row * C;
   const int32_t s0 = lane * K;
-  const int32_t last = min(b, T + 1);  // last level looked at
-  float4 Fc[K / 4], Bc[K / 4];
-  auto load_rows = [&](int32_t l, float4 (&F)[K / 4], float4 (&B)[K / 4]) {
-#pragma unroll
-    for (int c = 0; c < K / 4; ++c) {
-      F[c] = B[c] = make_float4(-INFINITY, -INFINITY, -INFINITY, -INFINITY);
-      if (l <= last && s0 + 4 * c < pitch) {
-        F[c] = *reinterpret_cast<const float4 *>(fg + (int64_t)l * pitch + s0 + 4 * c);
-        B[c] = *reinterpret_cast<const float4 *>(bg + (int64_t)l * pitch + s0 + 4 * c);
-      }
-    }
-  };
-  // the meta words of a level, all states: every lane writes its 16 (two 16-byte stores)
-  uint16_t *meta0 = meta + f.meta_off;
-  auto flush_meta = [&](int32_t l, const uint16_t *row_sm) {
-    if (s0 < mpitch) {
-      uint4 *dst = reinterpret_cast<uint4 *>(meta0 + (int64_t)l * mpitch + s0);
-      const uint4 *src = reinterpret_cast<const uint4 *>(row_sm + s0);
-      dst[0] = src[0];
-      if (s0 + 8 < mpitch) dst[1] = src[1];
-    }
-  };
-  load_rows(a, Fc, Bc);
-  int32_t n_prev = 0;
-  // the lists of a warp's levels lie one after the other from the start of its chunk
-  // (a chunk has room for all states of all its levels); lists[level] = (start, size)
-  int32_t run = a * pitch, prev_start = 0;
   uint32_t n_states = 0, n_cand = 0;
-  bool risky = false;
-  __syncwarp();
-  for (int32_t l = a; l <= last; ++l) {
-    const bool own = l < b;
-    float4 Fn[K / 4], Bn[K / 4];
-    load_rows(l + 1, Fn, Bn);  // in flight while this level is worked on
-    uint16_t *cur_list = list_sm + (l & 1) * s_pad, *prev_list = list_sm + ((l & 1) ^ 1) * s_pad;
-    uint16_t *cur_meta = meta_sm + (l & 1) * s_pad, *prev_meta = meta_sm + ((l & 1) ^ 1) * s_pad;
-    // ---- 1. surviving states ------------------------------------------------------
+#pragma unroll 4
+  for (int32_t l = a; l < b; ++l) {
     uint32_t keep = 0;
 #pragma unroll
     for (int c = 0; c < K / 4; ++c) {
-      if (__fadd_rn(Fc[c].x, Bc[c].x) > cutoff) keep |= 1u << (4 * c);
-      if (__fadd_rn(Fc[c].y, Bc[c].y) > cutoff) keep |= 2u << (4 * c);
-      if (__fadd_rn(Fc[c].z, Bc[c].z) > cutoff) keep |= 4u << (4 * c);
-      if (__fadd_rn(Fc[c].w, Bc[c].w) > cutoff) keep |= 8u << (4 * c);
+      if (s0 + 4 * c >= S) continue;
+      const float4 F = *reinterpret_cast<const float4 *>(fg + (int64_t)l * pitch + s0 + 4 * c);
+      const float4 B = *reinterpret_cast<const float4 *>(bg + (int64_t)l * pitch + s0 + 4 * c);
+      if (__fadd_rn(F.x, B.x) > cutoff) keep |= 1u << (4 * c);
+      if (__fadd_rn(F.y, B.y) > cutoff) keep |= 2u << (4 * c);
+      if (__fadd_rn(F.z, B.z) > cutoff) keep |= 4u << (4 * c);
+      if (__fadd_rn(F.w, B.w) > cutoff) keep |= 8u << (4 * c);
     }
+    keep_bits[(int64_t)(f.level_off + l) * 32 + lane] = (uint16_t)keep;
+    n_states += __popc(keep);
+    for (uint32_t m = keep; m; m &= m - 1) {
+      const int32_t idx = f.state_off + s0 + __ffs(m) - 1;
+      n_cand += __ldg(a_row_splits2 + idx + 1) - __ldg(a_row_splits2 + idx);
+    }
+  }
+#pragma unroll
+  for (int d = 16; d > 0; d >>= 1) {
+    n_states += __shfl_xor_sync(kAll, n_states, d);
+    n_cand += __shfl_xor_sync(kAll, n_cand, d);
+  }
+  if (lane == 0 && (n_states | n_cand)) {
+    atomicAdd(&totals[0], (unsigned long long)n_states);
+    atomicAdd(&totals[2], (unsigned long long)n_cand);
+  }
+}
+
+// ---------------------------------------------------------------------------
+// Keep tests.  grid = (level chunks, pairs), 4 warps per CTA, a warp per chunk of
+// kPrepLevels levels.  Per level the warp
+//   1. scans the two Viterbi rows (a lane reads 16 consecutive states of each; the rows of
+//      the next level are requested before this level is worked on), marks the surviving
+//      states and writes them, in state order, to a list in shared memory;
+//   2. takes the list one state per lane: the reference's arc tests
+//      (intersect_dense.cu:430-471) against the rows of the level before and the dense
+//      score of the state's label give the entering-arc bits, the factors and where in the
+//      previous list the sources are;
+//   3. gives the entries of the level before their leaving-arc bits and destinations, which
+//      are the entering arcs of this level seen from the source.
+// Per level the result is the compact list of surviving states: a BandItem (label, state,
+// bits) and a BandFactor per entry.  A warp writes the complete entries of the levels it
+// owns, so it also runs step 1 for the level before its first and steps 1-2 for the level
+// after its last.  totals[0] += surviving states, totals[2] += the arcs leaving them (the
+// sizes the beam reduction looks at, intersect_dense.cu:289-320).  unfit[i] is set when the
+// register recursion cannot take graph i: a score outside its arithmetic, or a level with
+// more than kMaxListed surviving states.
+// ---------------------------------------------------------------------------
+constexpr float kMinLeanDense = -60.0f;   // dense score of a surviving arc
+constexpr int32_t kMaxLeanArcExp = 60, kMinLeanArcExp = -90;  // binary exponent of exp(arc score)
+
+__global__ void __launch_bounds__(128)
+BandPrep(const BandInfo *__restrict__ infos, const BandState *__restrict__ tab,
+         const BandArc *__restrict__ tabf, const uint16_t *__restrict__ keep_bits,
+         const float *__restrict__ lp, int32_t C, const float *__restrict__ vf,
+         const float *__restrict__ vb, const float *__restrict__ cutoffs,
+         BandItem *__restrict__ items, BandFactor *__restrict__ factors,
+         int2 *__restrict__ lists, int32_t *__restrict__ chunk_r, int32_t *__restrict__ unfit,
+         int32_t s_pad) {
+  constexpr int K = kPrepK;
+  constexpr unsigned kAll = 0xffffffffu;
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  const int32_t i = blockIdx.y;
+  const BandInfo f = infos[i];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int32_t S = f.num_states, T = f.frames, pitch = f.pitch;
+  if (S == 0) return;
+  const int32_t a = (blockIdx.x * 4 + warp) * kPrepLevels;  // owns levels a .. b - 1
+  if (a > T + 1) return;
+  const int32_t b = min(a + kPrepLevels, T + 2);
+  // per warp: a word per state for the current and the previous level (zero outside the
+  // lists), and the two lists
+  uint16_t *meta_sm = reinterpret_cast<uint16_t *>(smem_raw) +
+                      (size_t)warp * (4 * s_pad + 32 * (kPrepLevels + 2));  // [2][s_pad]
+  uint16_t *list_sm = meta_sm + 2 * s_pad;                                  // [2][s_pad]
+  uint16_t *keep_sm = list_sm + 2 * s_pad;  // [kPrepLevels + 2][32]: the lanes' keep bits
+  for (int32_t k = lane; k < 2 * s_pad; k += 32) meta_sm[k] = 0;
+  const float *fg = vf + f.grid_off, *bg = vb + f.grid_off;
+  const float cutoff = cutoffs[i];
+  const float *lp0 = lp + (int64_t)f.lp_row * C;
+  const int32_t s0 = lane * K;
+  const int32_t first = max(a - 1, 0);  // first level looked at (its list only)
+  const int32_t last = min(b, T + 1);   // last level looked at
+  // ---- 0. the keep bits of every level this warp looks at; the longest list of its own
+  // levels decides how many entries every level of the chunk gets --------------------------
+  int32_t longest = 0;
+#pragma unroll 6
+  for (int32_t l = first; l <= last; ++l) {
+    const uint32_t keep = keep_bits[(int64_t)(f.level_off + l) * 32 + lane];
+    keep_sm[(l - first) * 32 + lane] = (uint16_t)keep;
+    const int32_t n = __reduce_add_sync(kAll, __popc(keep));
+    if (l >= a && l < b) longest = max(longest, n);
+  }
+  const int32_t padded = 32 * (longest / 32 + 1);  // entries per level of this chunk
+  if (lane == 0) chunk_r[f.level_off + a] = padded / 32;
+  int32_t n_prev = 0;
+  // the lists of a warp's levels lie `padded` entries apart from the start of its chunk
+  // (pitch >= padded); lists[level] = (start, size)
+  int32_t run = a * pitch, prev_start = 0;
+  bool risky = false;
+  __syncwarp();
+  for (int32_t l = first; l <= last; ++l) {
+    const bool own = l >= a && l < b;
+    uint16_t *cur_list = list_sm + (l & 1) * s_pad, *prev_list = list_sm + ((l & 1) ^ 1) * s_pad;
+    uint16_t *cur_meta = meta_sm + (l & 1) * s_pad, *prev_meta = meta_sm + ((l & 1) ^ 1) * s_pad;
+    // ---- 1. surviving states ------------------------------------------------------
+    const uint32_t keep = keep_sm[(l - first) * 32 + lane];
     const int32_t mine = __popc(keep);
     int32_t incl = mine;
 #pragma unroll
@@ -554,457 +618,136 @@ BandPrep(const BandInfo *__restrict__ infos, const BandState *__restrict__ tab,
     const int32_t n = __shfl_sync(kAll, incl, 31);
     {
       int32_t pos = incl - mine;
-      for (uint32_t m = keep; m; m &= m - 1) cur_list[pos++] = (uint16_t)(s0 + __ffs(m) - 1);
+      for (uint32_t m = keep; m; m &= m - 1) {
+        const int32_t s = s0 + __ffs(m) - 1;
+        cur_list[pos] = (uint16_t)s;
+        cur_meta[s] = (uint16_t)(kMetaKept | (uint32_t)pos);
+        ++pos;
+      }
     }
+    if (n > kMaxListed) risky = true;
     __syncwarp();
-    // ---- 2. one surviving state per lane ----------------------------------------------
-    BandItem *out = items + f.grid_off + run;
-    const float *fprev = fg + (int64_t)(l - 1) * pitch, *bprev = bg + (int64_t)(l - 1) * pitch;
-    const float *bcur = bg + (int64_t)l * pitch;
-    for (int32_t j = lane; j < n; j += 32) {
-      const int32_t s = cur_list[j];
-      const BandState t = tab[f.state_off + s];
-      uint32_t inb = 0;
-      if (l >= 1) {
-        const float x = BandDense(lp0, C, T, l - 1, t.label);
-        const float bc = bcur[s];
+    if (l >= a) {
+      // ---- 2. one surviving state per lane ------------------------------------------
+      BandItem *out = items + f.grid_off + run;
+      BandFactor *fout = factors + f.grid_off + run;
+      const float *fprev = fg + (int64_t)(l - 1) * pitch, *bprev = bg + (int64_t)(l - 1) * pitch;
+      const float *bcur = bg + (int64_t)l * pitch;
+      for (int32_t j = lane; j < n; j += 32) {
+        const int32_t s = cur_list[j];
+        const BandState t = tab[f.state_off + s];
+        uint32_t inb = 0;
+        BandFactor fa;
+        fa.pw[0] = fa.pw[1] = fa.pw[2] = 0.0;
+        fa.src[0] = fa.src[1] = fa.src[2] = fa.src[3] = 0;
+        fa.dst[0] = fa.dst[1] = fa.dst[2] = fa.dst[3] = (uint8_t)kNoDst;
+        if (l >= 1) {
+          const float x = BandDense(lp0, C, T, l - 1, t.label);
+          const float bc = bcur[s];
+          const double p = exp((double)x);
 #pragma unroll
-        for (int d = 0; d < 3; ++d) {
-          if (s - d < 0) continue;
-          const float sf = fprev[s - d];
-          const bool kept = __fadd_rn(sf, bprev[s - d]) > cutoff;
-          const float sc = __fadd_rn(t.w[d], x);
-          if (kept && __fadd_rn(__fadd_rn(sf, sc), bc) > cutoff) {
-            inb |= 1u << d;
-            // outside what doubles with a scale that follows the data every few levels
-            // hold: such graphs go to the (mantissa, exponent) recursion
-            if (!(x >= kMinLeanDense) || !(fabsf(t.w[d]) <= kMaxLeanArc)) risky = true;
+          for (int d = 0; d < 3; ++d) {
+            if (s - d < 0) continue;
+            const float sf = fprev[s - d];
+            const bool kept = __fadd_rn(sf, bprev[s - d]) > cutoff;
+            const float sc = __fadd_rn(t.w[d], x);
+            if (kept && __fadd_rn(__fadd_rn(sf, sc), bc) > cutoff) {
+              inb |= 1u << d;
+              if (own) {
+                const BandArc arc = tabf[(int64_t)(f.state_off + s) * 3 + d];
+                fa.pw[d] = arc.f * Pow2Clamp(arc.k) * p;
+                fa.src[d] = (uint8_t)(prev_meta[s - d] & kMetaPos);
+                // outside what doubles with a scale that follows the data every few
+                // levels hold: such graphs go to the (mantissa, exponent) recursion
+                if (!(x >= kMinLeanDense) || arc.k > kMaxLeanArcExp || arc.k < kMinLeanArcExp)
+                  risky = true;
+              }
+            }
           }
         }
-      }
-      cur_meta[s] = (uint16_t)(kMetaKept | (uint32_t)j | (inb << kMetaInShift));
-      if (own) {
-        BandItem it;
-        it.label = t.label;
-        it.s = (uint16_t)s;
-        it.inb = (uint8_t)inb;
-        it.outb = 0;
-        out[j] = it;
-        const int32_t idx = f.state_off + s;
-        n_cand += a_row_splits2[idx + 1] - a_row_splits2[idx];
-      }
-    }
-    if (own) {
-      n_states += lane == 0 ? n : 0;
-      if (lane == 0) lists[f.level_off + l] = make_int2(run, n);
-    }
-    __syncwarp();
-    // ---- 3. leaving-arc bits of the level before; that level is then complete -----------
-    if (l - 1 >= a) {
-      unsigned char *prev_bytes = reinterpret_cast<unsigned char *>(items + f.grid_off + prev_start);
-      for (int32_t j = lane; j < n_prev; j += 32) {
-        const int32_t s = prev_list[j];
-        const uint32_t ob = ((cur_meta[s] >> kMetaInShift) & 1u) |
-                            ((cur_meta[s + 1] >> kMetaInShift) & 2u) |
-                            ((cur_meta[s + 2] >> kMetaInShift) & 4u);
-        if (ob) {
-          prev_bytes[(size_t)j * sizeof(BandItem) + kOutbByte] = (unsigned char)ob;
-          prev_meta[s] = (uint16_t)(prev_meta[s] | (ob << kMetaOutShift));
+        cur_meta[s] = (uint16_t)(cur_meta[s] | (inb << kMetaInShift));
+        if (own) {
+          BandItem it;
+          it.label = t.label;
+          it.s = (uint16_t)s;
+          it.inb = (uint8_t)inb;
+          it.outb = 0;
+          out[j] = it;
+          fout[j] = fa;
         }
       }
+      if (own) {
+        BandFactor none;
+        none.pw[0] = none.pw[1] = none.pw[2] = 0.0;
+        none.src[0] = none.src[1] = none.src[2] = none.src[3] = 0;
+        none.dst[0] = none.dst[1] = none.dst[2] = none.dst[3] = (uint8_t)kNoDst;
+        for (int32_t j = n + lane; j < padded; j += 32) fout[j] = none;
+        if (lane == 0) lists[f.level_off + l] = make_int2(run, n);
+      }
       __syncwarp();
-      flush_meta(l - 1, prev_meta);
+      // ---- 3. leaving arcs of the level before --------------------------------------------
+      if (l - 1 >= a) {
+        unsigned char *ibytes = reinterpret_cast<unsigned char *>(items + f.grid_off + prev_start);
+        unsigned char *fbytes = reinterpret_cast<unsigned char *>(factors + f.grid_off + prev_start);
+        for (int32_t j = lane; j < n_prev; j += 32) {
+          const int32_t s = prev_list[j];
+          uint32_t ob = 0;
+#pragma unroll
+          for (int d = 0; d < 3; ++d) {
+            const uint32_t m = cur_meta[s + d];
+            if ((m >> (kMetaInShift + d)) & 1u) {
+              ob |= 1u << d;
+              fbytes[(size_t)j * sizeof(BandFactor) + kDstByte + d] = (unsigned char)(m & kMetaPos);
+            }
+          }
+          if (ob) ibytes[(size_t)j * sizeof(BandItem) + kOutbByte] = (unsigned char)ob;
+        }
+      }
     }
     __syncwarp();
     // the previous level's words go back to zero for the level after this one
     for (int32_t j = lane; j < n_prev; j += 32) prev_meta[prev_list[j]] = 0;
     __syncwarp();
-#pragma unroll
-    for (int c = 0; c < K / 4; ++c) {
-      Fc[c] = Fn[c];
-      Bc[c] = Bn[c];
-    }
     n_prev = n;
-    prev_start = run;
-    run += n;
-  }
-  // the last level of all has no leaving arcs: it is complete as it stands
-  if (b == T + 2) flush_meta(T + 1, meta_sm + ((T + 1) & 1) * s_pad);
-#pragma unroll
-  for (int d = 16; d > 0; d >>= 1) {
-    n_states += __shfl_xor_sync(kAll, n_states, d);
-    n_cand += __shfl_xor_sync(kAll, n_cand, d);
-  }
-  if (lane == 0 && (n_states | n_cand)) {
-    atomicAdd(&totals[0], (unsigned long long)n_states);
-    atomicAdd(&totals[2], (unsigned long long)n_cand);
+    if (l >= a) {
+      prev_start = run;
+      run += padded;
+    }
   }
   if (__any_sync(kAll, risky) && lane == 0) atomicOr(&unfit[i], kUnfitFactors);
 }
 
 // ---------------------------------------------------------------------------
-// alpha (dir 0) and beta (dir 1) over ALL states of a graph, in the shape of BandViterbi:
-// a thread holds four consecutive states in registers, a warp recomputes its neighbour's
-// boundary states so that a batch of F frames needs no exchange, the log-prob rows and
-// the meta rows of a batch arrive by two bulk copies requested batches ahead.
-//   alpha_0[start] = 1;     alpha_l[s] = p_l[s] * sum_d [arc s-d -> s survives] e^w alpha_{l-1}[s-d]
-//   beta_{T+1}[final] = 1;  beta_l[s]  = sum_d [arc s -> s+d survives] e^w p_{l+1}[s+d] beta_{l+1}[s+d]
-// with p_l[s] = exp(dense score of s's label on frame l - 1) and the survival bits of
-// BandPrep.  Most states of a level do not survive (their bits are zero, their value is
-// zero): the work on them is wasted, yet it costs nothing on the critical path - a chain
-// of T dependent steps, which this form keeps in registers and shuffles, without lists,
-// indexed shared-memory traffic or per-level synchronisation.
-// Values are doubles divided by 2^K; K changes every eight frames (where the warps exchange
-// boundary states, and once between) by the exponent of the largest value.  The value of a
-// surviving state is stored at its position in the level's list (am / bm), K per level
-// (a_scale / b_scale).  A non-zero value of a surviving state below 2^-600 marks the graph
-// in `unfit` for BandChainExact; BandPrep marks the graphs whose scores could take a value
-// from above 2^-600 to nothing within eight frames.
+// alpha (dir 0) and beta (dir 1) over the lists, in registers.  grid = (2, pairs), one warp
+// per CTA.  Lane j holds the value of entry j (and j + 32, j + 64) of the current level's
+// list; an entry says at which POSITIONS of the previous list its neighbours are, so the
+// values it needs come by shuffles from the lanes that hold them:
+//   alpha_l[j] = sum_d pw_l[j][d] * alpha_{l-1}[src_l[j][d]]
+//   beta_l[j]  = sum_d (pw_{l+1}[.][d] * beta_{l+1}[.]) at position dst_l[j][d]
+// Every level of a chunk of kPrepLevels levels has the same padded number of entries, 32 per
+// register, so inside a chunk every address is a constant: the fifteen levels after a
+// chunk's first are straight-line code, per level two 16-byte loads from shared memory, six
+// shuffles, three multiply-adds and a store per register: no test (an absent neighbour is
+// a padding entry, whose value is 0), no address arithmetic, no synchronisation.  The chunks
+// arrive in a ring in shared memory by one bulk copy each, requested chunks ahead.
+// The values of a level are stored divided by 2^K; K changes every kRescale levels by the
+// exponent of the largest value since the last change.  A value that is not zero and
+// below 2^-900 (or a value above 2^900) marks the graph in `unfit` for BandChainExact,
+// like the graphs BandPrep marked, which return at once here.
+// Outputs: alpha / beta at the list positions, K per level, tot[i], total[i].
 // ---------------------------------------------------------------------------
-constexpr int kHalfBatch = 8;                   // frames into a batch at which the scale changes again
-constexpr int kChainSlots = 3;                  // chunks in flight (BandChainExact)
-constexpr int kSlotItems = kPrepLevels * 128;   // entries of a chunk staged in shared memory
+constexpr int kRescale = 8;                     // levels between changes of the shared scale
+constexpr int kChainSlots = 3;                  // chunks in flight
+constexpr int kFacSlot = kPrepLevels * 96;      // BandFactor entries of a chunk: 16 levels of 3 x 32
+constexpr int kChainMaxChunks = 4096;           // of a graph: 65534 frames
+constexpr int kSlotItems = kPrepLevels * 128;   // BandItem entries likewise (BandChainExact)
 
-__device__ __forceinline__ double ExpDenseFast(float x) {
-  // exp(x) to float precision (2^-22): the same factor enters alpha, beta and Z.  For the
-  // scores of surviving arcs (above kMinLeanDense) the result is a normal float; what
-  // flushes to zero belongs to arcs that do not survive.
-  float y;
-  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x * 1.4426950408889634f));
-  return (double)y;
-}
-
-__global__ void __launch_bounds__(32 * kVitMaxWarps)
-BandChainDense(const BandInfo *__restrict__ infos, const BandState *__restrict__ tab,
-               const float *__restrict__ lp, int32_t C, const uint16_t *__restrict__ meta,
-               const int2 *__restrict__ lists, double *__restrict__ am, double *__restrict__ bm,
-               int32_t *__restrict__ a_scale, int32_t *__restrict__ b_scale,
-               double *__restrict__ tot, BandTotal *__restrict__ total,
-               int32_t *__restrict__ unfit, int32_t *__restrict__ status, int32_t F,
-               int32_t nbatch, int32_t xch_pad, int32_t mrow, int32_t lv_pad,
-               int32_t wait_limit) {
-  constexpr int K = kVitK;
-  extern __shared__ __align__(16) unsigned char smem_raw[];
-  __shared__ __align__(8) uint64_t full[kVitMaxBatches];
-  __shared__ int32_t wmax[2][kVitMaxWarps];
-  __shared__ int32_t any_late, any_bad;
-  constexpr unsigned kAll = 0xffffffffu;
-  const int dir = blockIdx.x;
-  const int32_t i = blockIdx.y;
-  const BandInfo f = infos[i];
-  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nwarps = blockDim.x >> 5;
-  const int32_t S = f.num_states, T = f.frames, mpitch = f.mpitch, L = T + 2;
-  if (dir == 0 && tid == 0) {
-    tot[i] = -INFINITY;
-    BandTotal z;
-    z.m = 0.0;
-    z.e = 0;
-    z.pad = 0;
-    total[i] = z;
-  }
-  if (S == 0) return;
-  const int32_t H = F >> 1, own = 32 - H;
-  // shared memory: per batch F log-prob rows and F meta rows; the exchange buffers; the
-  // start of every level's list
-  float *ring = reinterpret_cast<float *>(smem_raw);                                // [nbatch][F][C]
-  // a slot has room for F meta rows of mrow (>= every mpitch) words; a batch's rows are
-  // staged as they lie in memory, at this pair's pitch
-  uint16_t *mring = reinterpret_cast<uint16_t *>(ring + (size_t)nbatch * F * C);    // [nbatch][F][mrow]
-  double *xch = reinterpret_cast<double *>(mring + (size_t)nbatch * F * mrow);      // [2][xch_pad], s at s + 4H
-  int32_t *lstart = reinterpret_cast<int32_t *>(xch + 2 * xch_pad);                 // [lv_pad]
-  for (int32_t l = tid; l < L; l += blockDim.x) lstart[l] = lists[f.level_off + l].x;
-  for (int32_t k = tid; k < 2 * xch_pad; k += blockDim.x) xch[k] = 0.0;
-  if (tid == 0) {
-    for (int st = 0; st < nbatch; ++st) MbarInit(&full[st], 1);
-    MbarInitFence();
-    any_late = 0;
-    any_bad = 0;
-  }
-  __syncthreads();
-  const int32_t num_batches = (T + F - 1) / F;
-  const float *lp0 = lp + (int64_t)f.lp_row * C;
-  const uint16_t *meta0 = meta + f.meta_off;
-  int32_t issued = 0;
-  // Batch q, forward: steps to levels qF + 1 .. : log-prob rows [qF, ...), meta rows one up.
-  // Backward: steps to levels T - 1 - qF down: log-prob rows and meta rows [T - (q+1)F, T - qF).
-  auto issue = [&]() {  // thread 0 only
-    if (issued >= num_batches) return;
-    const int32_t q = issued;
-    const int32_t r0 = dir == 0 ? q * F : max(T - (q + 1) * F, 0);
-    const int32_t r1 = dir == 0 ? min((q + 1) * F, T) : T - q * F;
-    const int32_t m0 = dir == 0 ? r0 + 1 : r0;  // first meta row
-    const unsigned lp_bytes = (unsigned)(r1 - r0) * 4u * (unsigned)C;
-    const unsigned m_bytes = (unsigned)(r1 - r0) * 2u * (unsigned)mpitch;
-    const int32_t slot = q % nbatch;
-    MbarArriveExpectTx(&full[slot], lp_bytes + m_bytes);
-    BulkCopyG2S(ring + (size_t)slot * F * C, lp0 + (int64_t)r0 * C, lp_bytes, &full[slot]);
-    // meta rows of one pair are contiguous at pitch mpitch: staged as they lie
-    BulkCopyG2S(mring + (size_t)slot * F * mrow, meta0 + (int64_t)m0 * mpitch, m_bytes,
-                &full[slot]);
-    ++issued;
-  };
-  if (tid == 0)
-    for (int32_t q = 0; q < nbatch; ++q) issue();
-
-  const int32_t s0 = warp * own * K + (dir == 0 ? (lane - H) * K : lane * K);
-  const bool mine = dir == 0 ? lane >= H : lane < own;   // a lane that owns its states
-  const bool has_meta = s0 >= 0 && s0 < mpitch;          // its states exist in the meta rows
-  double *out = (dir == 0 ? am : bm) + f.grid_off;
-  int32_t *oscale = (dir == 0 ? a_scale : b_scale) + f.level_off;
-  bool late = false, bad = false;
-  int32_t Ksh = 0;
-  double v[K] = {0.0, 0.0, 0.0, 0.0};
-  // arc factors exp(w) and dense columns of this thread's states
-  double e0[K], e1[K], e2[K];   // forward: arcs into s from s, s-1, s-2; backward: out of s to s, s+1, s+2
-  int32_t col[K];
-  uint32_t fin = 0;             // states whose label is the final symbol
-#pragma unroll
-  for (int k = 0; k < K; ++k) {
-    e0[k] = e1[k] = e2[k] = 0.0;
-    col[k] = 0;
-  }
-  if (dir == 0) {
-#pragma unroll
-    for (int k = 0; k < K; ++k) {
-      const int32_t s = s0 + k;
-      if (s >= 0 && s < S) {
-        const BandState t = tab[f.state_off + s];
-        e0[k] = exp((double)t.w[0]);
-        e1[k] = exp((double)t.w[1]);
-        e2[k] = exp((double)t.w[2]);
-        if (t.label >= 0 && t.label < C) col[k] = t.label;
-        if (t.label == -1) fin |= 1u << k;
-      }
-    }
-  } else {
-#pragma unroll
-    for (int k = 0; k < K + 2; ++k) {
-      const int32_t s = s0 + k;
-      if (s >= 0 && s < S) {
-        const BandState t = tab[f.state_off + s];
-        if (k < K) {
-          if (t.label >= 0 && t.label < C) col[k] = t.label;
-          if (t.label == -1) fin |= 1u << k;
-        }
-        // the arc s - d -> s seen from its source, state s - d = s0 + k - d
-        if (k < K) e0[k] = exp((double)t.w[0]);
-        if (k - 1 >= 0 && k - 1 < K) e1[k - 1 >= 0 ? k - 1 : 0] = exp((double)t.w[1]);
-        if (k - 2 >= 0 && k - 2 < K) e2[k - 2 >= 0 ? k - 2 : 0] = exp((double)t.w[2]);
-      }
-    }
-  }
-  // Change of scale: every thread divides its values by 2^e, e the exponent of the largest
-  // value an owner holds.  With `swap` the owners also publish their values and the
-  // recomputing lanes pick them up (once per batch); without, only the scale changes
-  // (once more in the middle of a batch).  One barrier either way.
-  constexpr uint32_t kTinyHi = ((1023 - 600) << 20) - 1;  // high word of 2^-600, less one
-  // smallest (high word - 1) among the values this thread computed, zeros apart (as an
-  // unsigned number the high word 0 of a zero becomes the largest value)
-  uint32_t min_hi = 0xffffffffu;
-  int32_t xpar = 0;
-  auto rescale = [&](bool swap) {
-    double *x = xch + (size_t)xpar * xch_pad + 4 * H;
-    int32_t hm = 0;
-    if (mine) {
-#pragma unroll
-      for (int k = 0; k < K; ++k) hm = max(hm, __double2hiint(v[k]));
-      if (swap && s0 >= 0 && s0 < xch_pad - 4 * H - 3) {
-#pragma unroll
-        for (int k = 0; k < K; ++k) x[s0 + k] = v[k];
-      }
-    }
-    hm = __reduce_max_sync(kAll, hm);
-    if (lane == 0) wmax[xpar][warp] = hm;
-    // a value that is not zero must have stayed clear of the end of the range (values
-    // this thread recomputed for its neighbour count too: they are the same numbers)
-    bad |= min_hi < kTinyHi;
-    __syncthreads();
-    if (swap && !mine && s0 + 4 * H >= 0 && s0 < xch_pad - 4 * H - 3) {
-#pragma unroll
-      for (int k = 0; k < K; ++k) v[k] = x[s0 + k];
-    }
-    int32_t cm = 0;
-    for (int32_t w = 0; w < nwarps; ++w) cm = max(cm, wmax[xpar][w]);
-    const int32_t e = cm > 0 ? (cm >> 20) - 1023 : 0;
-    const double scale = __longlong_as_double((long long)(1023 - e) << 52);
-#pragma unroll
-    for (int k = 0; k < K; ++k) v[k] *= scale;
-    Ksh += e;
-    xpar ^= 1;
-  };
-  // the values of a thread's surviving states go to consecutive list positions when all
-  // four survive (the usual case inside the band)
-  auto store4 = [&](int32_t l, uint2 m4, const double (&x)[K]) {
-    if (!mine) return;
-    const uint32_t all = m4.x & m4.y & (kMetaKept | (kMetaKept << 16));
-    double *o = out + lstart[l];
-    if (all == (kMetaKept | (kMetaKept << 16))) {
-      o += m4.x & kMetaPos;
-      o[0] = x[0];
-      o[1] = x[1];
-      o[2] = x[2];
-      o[3] = x[3];
-    } else if ((m4.x | m4.y) & (kMetaKept | (kMetaKept << 16))) {
-#pragma unroll
-      for (int k = 0; k < K; ++k) {
-        const uint32_t m = (k < 2 ? m4.x : m4.y) >> (16 * (k & 1)) & 0xffffu;
-        if (m & kMetaKept) o[m & kMetaPos] = x[k];
-      }
-    }
-  };
-  // one step of the forward recursion to level l; p = exp(dense score) of this thread's
-  // states on frame l - 1, m4 = their meta words on level l
-  auto forward_step = [&](int32_t l, const double (&p)[K], uint2 m4) {
-    double h1 = __shfl_up_sync(kAll, v[K - 1], 1), h2 = __shfl_up_sync(kAll, v[K - 2], 1);
-    if (lane == 0) h1 = h2 = 0.0;
-    double nv[K];
-#pragma unroll
-    for (int k = 0; k < K; ++k) {
-      const uint32_t m = (k < 2 ? m4.x : m4.y) >> (16 * (k & 1));
-      const double a = v[k];
-      const double b = k >= 1 ? v[k >= 1 ? k - 1 : 0] : h1;
-      const double c = k >= 2 ? v[k >= 2 ? k - 2 : 0] : (k == 1 ? h1 : h2);
-      double acc = 0.0;
-      if (m & (1u << kMetaInShift)) acc = e0[k] * a;
-      if (m & (2u << kMetaInShift)) acc = fma(e1[k], b, acc);
-      if (m & (4u << kMetaInShift)) acc = fma(e2[k], c, acc);
-      nv[k] = acc * p[k];
-      min_hi = min(min_hi, (uint32_t)__double2hiint(nv[k]) - 1u);
-    }
-    store4(l, m4, nv);
-#pragma unroll
-    for (int k = 0; k < K; ++k) v[k] = nv[k];
-  };
-  auto backward_step = [&](int32_t l, const double (&p)[K], uint2 m4) {
-    // what the sources add: beta * p of the level above, own and the next lane's first two
-    double bp[K + 2];
-#pragma unroll
-    for (int k = 0; k < K; ++k) bp[k] = v[k] * p[k];
-    bp[K] = __shfl_down_sync(kAll, bp[0], 1);
-    bp[K + 1] = __shfl_down_sync(kAll, bp[1], 1);
-    if (lane == 31) bp[K] = bp[K + 1] = 0.0;
-#pragma unroll
-    for (int k = 0; k < K; ++k) {
-      const uint32_t m = (k < 2 ? m4.x : m4.y) >> (16 * (k & 1));
-      double acc = 0.0;
-      if (m & (1u << kMetaOutShift)) acc = e0[k] * bp[k];
-      if (m & (2u << kMetaOutShift)) acc = fma(e1[k], bp[k + 1], acc);
-      if (m & (4u << kMetaOutShift)) acc = fma(e2[k], bp[k + 2], acc);
-      v[k] = acc;
-      min_hi = min(min_hi, (uint32_t)__double2hiint(acc) - 1u);
-    }
-    store4(l, m4, v);
-  };
-  auto meta_of = [&](const uint16_t *row) {  // this thread's four words of a meta row
-    return has_meta ? *reinterpret_cast<const uint2 *>(row + s0) : make_uint2(0u, 0u);
-  };
-  if (dir == 0) {
-    // level 0: the start state holds 1
-#pragma unroll
-    for (int k = 0; k < K; ++k) v[k] = s0 + k == 0 ? 1.0 : 0.0;
-    {
-      const uint2 m4 = meta_of(meta0);
-      if (mine && s0 == 0 && (m4.x & kMetaKept)) out[lstart[0] + (int32_t)(m4.x & kMetaPos)] = 1.0;
-      if (tid == 0) oscale[0] = 0;
-    }
-    for (int32_t q = 0; q < num_batches; ++q) {
-      const int32_t slot = q % nbatch;
-      if (!late) late = !WaitSlot(&full[slot], (unsigned)(q / nbatch) & 1u, wait_limit);
-      if (q > 0) {
-        rescale(true);  // its barrier also says: every warp has finished batch q - 1
-        if (tid == 0 && !late) issue();
-      }
-      const int32_t nf = min(F, T - q * F);
-      const float *rowbuf = ring + (size_t)slot * F * C;
-      const uint16_t *mbuf = mring + (size_t)slot * F * mrow;
-      for (int32_t r = 0; r < nf; ++r, rowbuf += C, mbuf += mpitch) {
-        if (r == kHalfBatch) rescale(false);
-        if (tid == 0) oscale[q * F + r + 1] = Ksh;
-        double p[K];
-#pragma unroll
-        for (int k = 0; k < K; ++k) p[k] = ExpDenseFast(rowbuf[col[k]]);
-        forward_step(q * F + r + 1, p, meta_of(mbuf));
-      }
-    }
-    // the implied final row: level T + 1
-    rescale(true);
-    {
-      if (tid == 0) oscale[T + 1] = Ksh;
-      double p[K];
-#pragma unroll
-      for (int k = 0; k < K; ++k) p[k] = (fin >> k) & 1u ? 1.0 : 0.0;
-      forward_step(T + 1, p, meta_of(meta0 + (int64_t)(T + 1) * mpitch));
-    }
-    if (mine && S - 1 >= s0 && S - 1 < s0 + K) {
-      double z = 0.0;
-#pragma unroll
-      for (int k = 0; k < K; ++k)
-        if (s0 + k == S - 1) z = v[k];
-      if (z > 0.0 && !late) {
-        tot[i] = log(z) + (double)Ksh * 0.69314718055994530942;
-        BandTotal zt;
-        zt.m = z;
-        zt.e = Ksh;
-        zt.pad = 0;
-        total[i] = zt;
-      }
-    }
-  } else {
-    // level T + 1: the final state holds 1; then level T through the implied final row
-#pragma unroll
-    for (int k = 0; k < K; ++k) v[k] = s0 + k == S - 1 ? 1.0 : 0.0;
-    {
-      const uint2 m4 = meta_of(meta0 + (int64_t)(T + 1) * mpitch);
-#pragma unroll
-      for (int k = 0; k < K; ++k) {
-        const uint32_t m = (k < 2 ? m4.x : m4.y) >> (16 * (k & 1)) & 0xffffu;
-        if (mine && s0 + k == S - 1 && (m & kMetaKept))
-          out[lstart[T + 1] + (int32_t)(m & kMetaPos)] = 1.0;
-      }
-      if (tid == 0) oscale[T + 1] = oscale[T] = 0;
-      double p[K];
-#pragma unroll
-      for (int k = 0; k < K; ++k) p[k] = (fin >> k) & 1u ? 1.0 : 0.0;
-      backward_step(T, p, meta_of(meta0 + (int64_t)T * mpitch));
-    }
-    for (int32_t q = 0; q < num_batches; ++q) {
-      const int32_t slot = q % nbatch;
-      if (!late) late = !WaitSlot(&full[slot], (unsigned)(q / nbatch) & 1u, wait_limit);
-      rescale(true);  // also: every warp has finished batch q - 1
-      if (q > 0 && tid == 0 && !late) issue();
-      const int32_t r1 = T - q * F, r0 = max(T - (q + 1) * F, 0);
-      const float *rowbuf = ring + (size_t)slot * F * C + (size_t)(r1 - 1 - r0) * C;
-      const uint16_t *mbuf = mring + (size_t)slot * F * mrow + (size_t)(r1 - 1 - r0) * mpitch;
-      for (int32_t r = r1 - 1; r >= r0; --r, rowbuf -= C, mbuf -= mpitch) {  // level r from r + 1
-        if (r1 - 1 - r == kHalfBatch) rescale(false);
-        if (tid == 0) oscale[r] = Ksh;
-        double p[K];
-#pragma unroll
-        for (int k = 0; k < K; ++k) p[k] = ExpDenseFast(rowbuf[col[k]]);
-        backward_step(r, p, meta_of(mbuf));
-      }
-    }
-  }
-  if (late) any_late = 1;
-  if (bad || min_hi < kTinyHi) any_bad = 1;
-  __syncthreads();
-  if (any_late) {
-    if (tid == 0) {
-      atomicOr(status, kStatusLate);
-      for (int32_t q = max(0, issued - nbatch); q < issued; ++q)
-        WaitSlot(&full[q % nbatch], (unsigned)(q / nbatch) & 1u, kDrainPolls);
-    }
-    __syncthreads();
-  }
-  if (tid == 0 && any_bad) atomicOr(&unfit[i], kUnfitRange);
-  if (dir == 0 && tid == 0 && (*status & kStatusLate)) tot[i] = nan("");
-}
-
-// The ring of chunks of BandChainExact: lane 0 requests, every lane waits.
+// The ring of chunks: lane 0 requests, every lane waits.
+template <typename Item, int kCap>
 struct ChunkRing {
   uint64_t *full;          // [kChainSlots]
-  BandItem *slots;         // [kChainSlots][kSlotItems]
-  const BandItem *items0;  // the pair's lists
+  Item *slots;             // [kChainSlots][kCap]
+  const Item *items0;      // the pair's lists
   const int2 *lst;         // (start, size) of every level, in shared memory
   int32_t pitch, L, num_chunks, dir, issued;
   __device__ __forceinline__ int32_t ChunkOf(int32_t q) const {
@@ -1018,13 +761,15 @@ struct ChunkRing {
   __device__ __forceinline__ void Issue() {  // lane 0: the next chunk into the next slot
     if (issued >= num_chunks) return;
     const int32_t c = ChunkOf(issued), slot = issued % kChainSlots;
-    // an even number of entries (16 bytes), at least two, so that the copy is legal and the
-    // slot's barrier completes once per use; a chunk starts on a multiple of four entries
-    const int32_t n = max((min(ChunkItems(c), kSlotItems) + 1) & ~1, 2);
-    const unsigned bytes = (unsigned)n * (unsigned)sizeof(BandItem);
+    // a multiple of 16 bytes, at least 16, so that the copy is legal and the slot's barrier
+    // completes once per use (a chunk starts on a multiple of four entries and has room for
+    // at least four)
+    constexpr int32_t kPer16 = sizeof(Item) >= 16 ? 1 : 16 / sizeof(Item);
+    const int32_t n = max((min(ChunkItems(c), kCap) + kPer16 - 1) / kPer16 * kPer16, kPer16);
+    const unsigned bytes = (unsigned)n * (unsigned)sizeof(Item);
     MbarArriveExpectTx(&full[slot], bytes);
-    BulkCopyG2S(slots + (size_t)slot * kSlotItems, items0 + (int64_t)c * kPrepLevels * pitch,
-                bytes, &full[slot]);
+    BulkCopyG2S(slots + (size_t)slot * kCap, items0 + (int64_t)c * kPrepLevels * pitch, bytes,
+                &full[slot]);
     ++issued;
   }
   __device__ __forceinline__ void Drain() {  // lane 0, after giving up
@@ -1032,6 +777,265 @@ struct ChunkRing {
       WaitSlot(&full[k % kChainSlots], (unsigned)(k / kChainSlots) & 1u, kDrainPolls);
   }
 };
+
+// One level of the walk.  `rec` = this lane's entry of the level's first 32 (in shared
+// memory), `out` = where its value goes; RC registers per lane on this level, RP on the one
+// walked before.  v = values of the level before (forward), pc[d] = the products
+// pw[d] * value of the level before (backward); both are replaced by this level's.
+template <int DIR, int RC, int RP, bool kScaled>
+__device__ __forceinline__ void ChainLevel(const BandFactor *rec, double *__restrict__ out,
+                                           double scale, double (&v)[3], double (&pc)[3][3],
+                                           int32_t &hi_max, uint32_t &min_hi) {
+  constexpr unsigned kAll = 0xffffffffu;
+  double nv[RC], pw[RC][3];
+#pragma unroll
+  for (int r = 0; r < RC; ++r) {
+    const double2 p01 = *reinterpret_cast<const double2 *>(rec + 32 * r);
+    const int4 q = *(reinterpret_cast<const int4 *>(rec + 32 * r) + 1);
+    pw[r][0] = p01.x;
+    pw[r][1] = p01.y;
+    pw[r][2] = __hiloint2double(q.y, q.x);
+    const uint32_t word = DIR == 0 ? (uint32_t)q.z : (uint32_t)q.w;
+    double x[3];
+#pragma unroll
+    for (int d = 0; d < 3; ++d) {
+      // a shuffle looks at the low five bits of the lane only
+      const uint32_t pos = RP == 1 ? word >> (8 * d) : (word >> (8 * d)) & 0xffu;
+      x[d] = __shfl_sync(kAll, DIR == 0 ? v[0] : pc[d][0], (int)pos);
+      if (RP > 1) {
+        const double x1 = __shfl_sync(kAll, DIR == 0 ? v[1] : pc[d][1], (int)pos);
+        x[d] = pos >= 32u ? x1 : x[d];
+      }
+      if (RP > 2) {
+        const double x2 = __shfl_sync(kAll, DIR == 0 ? v[2] : pc[d][2], (int)pos);
+        x[d] = pos >= 64u ? x2 : x[d];
+      }
+    }
+    double acc;
+    if (DIR == 0) acc = fma(pw[r][0], x[0], fma(pw[r][1], x[1], pw[r][2] * x[2]));
+    else acc = (x[0] + x[1]) + x[2];
+    nv[r] = kScaled ? acc * scale : acc;
+  }
+#pragma unroll
+  for (int r = 0; r < RC; ++r) {
+    out[32 * r] = nv[r];
+    const int32_t hi = __double2hiint(nv[r]);  // values are not negative
+    hi_max = max(hi_max, hi);
+    min_hi = min(min_hi, (uint32_t)hi - 1u);  // a zero does not count
+    v[r] = nv[r];
+    if (DIR == 1) {
+      pc[0][r] = pw[r][0] * nv[r];
+      pc[1][r] = pw[r][1] * nv[r];
+      pc[2][r] = pw[r][2] * nv[r];
+    }
+  }
+}
+
+// The same with the register counts known at run time only.
+template <int DIR>
+__device__ __forceinline__ void ChainLevelAny(int32_t rc, int32_t rp, const BandFactor *rec,
+                                              double *__restrict__ out, double scale,
+                                              double (&v)[3], double (&pc)[3][3],
+                                              int32_t &hi_max, uint32_t &min_hi) {
+  switch (rc * 4 + rp) {
+    case 5: ChainLevel<DIR, 1, 1, true>(rec, out, scale, v, pc, hi_max, min_hi); break;
+    case 6: ChainLevel<DIR, 1, 2, true>(rec, out, scale, v, pc, hi_max, min_hi); break;
+    case 7: ChainLevel<DIR, 1, 3, true>(rec, out, scale, v, pc, hi_max, min_hi); break;
+    case 9: ChainLevel<DIR, 2, 1, true>(rec, out, scale, v, pc, hi_max, min_hi); break;
+    case 10: ChainLevel<DIR, 2, 2, true>(rec, out, scale, v, pc, hi_max, min_hi); break;
+    case 11: ChainLevel<DIR, 2, 3, true>(rec, out, scale, v, pc, hi_max, min_hi); break;
+    case 13: ChainLevel<DIR, 3, 1, true>(rec, out, scale, v, pc, hi_max, min_hi); break;
+    case 14: ChainLevel<DIR, 3, 2, true>(rec, out, scale, v, pc, hi_max, min_hi); break;
+    default: ChainLevel<DIR, 3, 3, true>(rec, out, scale, v, pc, hi_max, min_hi); break;
+  }
+}
+
+// The new scale after kRescale levels: the exponent of the largest value since the last one.
+__device__ __forceinline__ double ChainRescale(int32_t &hi_max, int32_t &Ksh) {
+  const int32_t hm = __reduce_max_sync(0xffffffffu, hi_max);
+  const int32_t e = hm > 0 ? (hm >> 20) - 1023 : 0;
+  Ksh += e;
+  hi_max = 0;
+  return __longlong_as_double((long long)(1023 - e) << 52);
+}
+
+// Levels 1 .. 15 (in walking order) of a full chunk with RC registers per lane, unrolled.
+template <int DIR, int RC>
+__device__ __forceinline__ void ChainRest(const BandFactor *base, double *__restrict__ ob,
+                                          int32_t *__restrict__ osc, int lane, double (&v)[3],
+                                          double (&pc)[3][3], int32_t &hi_max, uint32_t &min_hi,
+                                          int32_t &Ksh) {
+#pragma unroll
+  for (int kk = 1; kk < kPrepLevels; ++kk) {
+    const int m = DIR == 0 ? kk : kPrepLevels - 1 - kk;
+    if (kk == kRescale) {
+      const double scale = ChainRescale(hi_max, Ksh);
+      ChainLevel<DIR, RC, RC, true>(base + m * 32 * RC, ob + m * 32 * RC, scale, v, pc, hi_max,
+                                    min_hi);
+    } else {
+      ChainLevel<DIR, RC, RC, false>(base + m * 32 * RC, ob + m * 32 * RC, 1.0, v, pc, hi_max,
+                                     min_hi);
+    }
+    if (lane == 0) osc[m] = Ksh;
+  }
+}
+
+template <int DIR>
+__device__ __forceinline__ void ChainWalk(const BandInfo &f, int32_t i, BandFactor *ring,
+                                          unsigned char *crc, uint64_t *full,
+                                          const BandFactor *__restrict__ factors,
+                                          const int32_t *__restrict__ chunk_r,
+                                          double *__restrict__ om, int32_t *__restrict__ oscale,
+                                          double *__restrict__ tot, BandTotal *__restrict__ total,
+                                          int32_t *__restrict__ unfit,
+                                          int32_t *__restrict__ status, int32_t wait_limit) {
+  constexpr unsigned kAll = 0xffffffffu;
+  const int lane = threadIdx.x;
+  const int32_t T = f.frames, pitch = f.pitch, L = T + 2;
+  const int32_t num_chunks = (L + kPrepLevels - 1) / kPrepLevels;
+  for (int32_t c = lane; c < num_chunks; c += 32)
+    crc[c] = (unsigned char)chunk_r[f.level_off + c * kPrepLevels];
+  if (lane == 0) {
+    for (int st = 0; st < kChainSlots; ++st) MbarInit(&full[st], 1);
+    MbarInitFence();
+  }
+  __syncwarp();
+  const BandFactor *fac0 = factors + f.grid_off;
+  om += f.grid_off;
+  oscale += f.level_off;
+  int32_t issued = 0;
+  // lane 0: the next chunk (in walking order) into the next slot; a chunk is
+  // levels * 32 * registers entries, a multiple of 1 KB
+  auto issue = [&]() {
+    if (issued >= num_chunks) return;
+    const int32_t c = DIR == 0 ? issued : num_chunks - 1 - issued, slot = issued % kChainSlots;
+    const int32_t nl = min((c + 1) * kPrepLevels, L) - c * kPrepLevels;
+    const unsigned bytes = (unsigned)(nl * 32 * (int32_t)crc[c]) * (unsigned)sizeof(BandFactor);
+    MbarArriveExpectTx(&full[slot], bytes);
+    BulkCopyG2S(ring + (size_t)slot * kFacSlot, fac0 + (int64_t)c * kPrepLevels * pitch, bytes,
+                &full[slot]);
+    ++issued;
+  };
+  if (lane == 0)
+    for (int32_t k = 0; k < kChainSlots; ++k) issue();
+  double v[3] = {0.0, 0.0, 0.0}, pc[3][3];
+#pragma unroll
+  for (int d = 0; d < 3; ++d) pc[d][0] = pc[d][1] = pc[d][2] = 0.0;
+  int32_t Ksh = 0;
+  int32_t hi_max = 0;              // largest high word since the last change of scale
+  uint32_t min_hi = 0xffffffffu;   // smallest (high word - 1), zeros apart
+  bool late = false;
+  int32_t rp = 1;
+  for (int32_t q = 0; q < num_chunks; ++q) {
+    const int32_t c = DIR == 0 ? q : num_chunks - 1 - q, slot = q % kChainSlots;
+    late = !WaitSlot(&full[slot], (unsigned)(q / kChainSlots) & 1u, wait_limit);
+    late = __any_sync(kAll, late);
+    if (late) break;
+    const int32_t l_lo = c * kPrepLevels, nl = min(l_lo + kPrepLevels, L) - l_lo;
+    const int32_t rc = crc[c];
+    const BandFactor *base = ring + (size_t)slot * kFacSlot + lane;
+    double *ob = om + (int64_t)l_lo * pitch + lane;
+    int32_t *osc = oscale + l_lo;
+    // the chunk's first level meets the registers of the chunk before; the levels of a
+    // short chunk (the last of a graph) are taken the same way
+    int32_t kk = 0;
+    do {
+      const int32_t m = DIR == 0 ? kk : nl - 1 - kk, l = l_lo + m;
+      const BandFactor *rec = base + m * 32 * rc;
+      double *out = ob + m * 32 * rc;
+      if (q == 0 && kk == 0) {
+        // the first level holds one state, with the value 1: the start state walking
+        // forward, the final state walking backward
+        v[0] = lane == 0 ? 1.0 : 0.0;
+        v[1] = v[2] = 0.0;
+#pragma unroll
+        for (int r = 0; r < 3; ++r) {
+          if (r >= rc) break;  // uniform
+          out[32 * r] = v[r];
+          if (DIR == 1) {
+            const BandFactor e = rec[32 * r];
+            pc[0][r] = e.pw[0] * v[r];
+            pc[1][r] = e.pw[1] * v[r];
+            pc[2][r] = e.pw[2] * v[r];
+          }
+        }
+      } else {
+        double scale = 1.0;
+        if ((l & (kRescale - 1)) == (DIR == 0 ? 0 : kRescale - 1)) scale = ChainRescale(hi_max, Ksh);
+        ChainLevelAny<DIR>(rc, kk == 0 ? rp : rc, rec, out, scale, v, pc, hi_max, min_hi);
+      }
+      if (lane == 0) osc[m] = Ksh;
+      ++kk;
+    } while (kk < nl && nl != kPrepLevels);
+    if (nl == kPrepLevels) {
+      if (rc == 1) ChainRest<DIR, 1>(base, ob, osc, lane, v, pc, hi_max, min_hi, Ksh);
+      else if (rc == 2) ChainRest<DIR, 2>(base, ob, osc, lane, v, pc, hi_max, min_hi, Ksh);
+      else ChainRest<DIR, 3>(base, ob, osc, lane, v, pc, hi_max, min_hi, Ksh);
+    }
+    rp = rc;
+    __syncwarp();  // every lane has read the slot
+    if (lane == 0) issue();  // the chunk is done with: its slot takes the next one
+  }
+  if (late) {
+    if (lane == 0) {
+      atomicOr(status, kStatusLate);
+      for (int32_t k = max(0, issued - kChainSlots); k < issued; ++k)
+        WaitSlot(&full[k % kChainSlots], (unsigned)(k / kChainSlots) & 1u, kDrainPolls);
+    }
+    __syncwarp();
+  }
+  {
+    // values that are not zero must have kept clear of the ends of a double's range
+    const int32_t hm = __reduce_max_sync(kAll, hi_max);
+    const uint32_t hn = __reduce_min_sync(kAll, min_hi);
+    if ((hm >= ((1023 + 900) << 20) || hn < (uint32_t)(((1023 - 900) << 20) - 1)) && lane == 0)
+      atomicOr(&unfit[i], kUnfitRange);
+  }
+  if (DIR == 0 && lane == 0) {
+    const double last = v[0];  // entry 0 of the last level is the final state
+    if (*status & kStatusLate) {
+      tot[i] = nan("");
+    } else if (!late && last > 0.0) {
+      tot[i] = log(last) + (double)Ksh * 0.69314718055994530942;
+      BandTotal z;
+      z.m = last;
+      z.e = Ksh;
+      z.pad = 0;
+      total[i] = z;
+    }
+  }
+}
+
+__global__ void __launch_bounds__(32)
+BandChainLists(const BandInfo *__restrict__ infos, const BandFactor *__restrict__ factors,
+               const int32_t *__restrict__ chunk_r, double *__restrict__ am,
+               double *__restrict__ bm, int32_t *__restrict__ a_scale,
+               int32_t *__restrict__ b_scale, double *__restrict__ tot,
+               BandTotal *__restrict__ total, int32_t *__restrict__ unfit,
+               int32_t *__restrict__ status, int32_t wait_limit) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  __shared__ __align__(8) uint64_t full[kChainSlots];
+  __shared__ unsigned char crc[kChainMaxChunks];
+  const int dir = blockIdx.x;
+  const int32_t i = blockIdx.y;
+  const BandInfo f = infos[i];
+  if (dir == 0 && threadIdx.x == 0) {
+    tot[i] = -INFINITY;
+    BandTotal z;
+    z.m = 0.0;
+    z.e = 0;
+    z.pad = 0;
+    total[i] = z;
+  }
+  if (f.num_states == 0 || unfit[i] != 0) return;  // BandChainExact takes the graphs BandPrep marked
+  BandFactor *ring = reinterpret_cast<BandFactor *>(smem_raw);  // [slots][kFacSlot]
+  if (dir == 0)
+    ChainWalk<0>(f, i, ring, crc, full, factors, chunk_r, am, a_scale, tot, total, unfit, status,
+                 wait_limit);
+  else
+    ChainWalk<1>(f, i, ring, crc, full, factors, chunk_r, bm, b_scale, tot, total, unfit, status,
+                 wait_limit);
+}
 
 // The same recursion with a (mantissa, exponent) pair per state, for the graphs marked in
 // `unfit`; every other graph returns at once.  exp(dense score) is recomputed from the
@@ -1070,7 +1074,7 @@ BandChainExact(const BandInfo *__restrict__ infos, const BandArc *__restrict__ t
     MbarInitFence();
   }
   __syncwarp();
-  ChunkRing rg;
+  ChunkRing<BandItem, kSlotItems> rg;
   rg.full = full;
   rg.slots = ring;
   rg.items0 = items + f.grid_off;
@@ -1199,7 +1203,6 @@ BandGrad(const BandInfo *__restrict__ infos, const BandArc *__restrict__ tabf,
          const int32_t *__restrict__ grad_row0, int32_t grad_pitch, int32_t grad_col_off,
          int32_t C, int32_t st_pad) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
-  constexpr unsigned kAll = 0xffffffffu;
   const int32_t i = blockIdx.y;
   const BandInfo f = infos[i];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -1218,8 +1221,13 @@ BandGrad(const BandInfo *__restrict__ infos, const BandArc *__restrict__ tabf,
   const int32_t *ae0 = ae + f.grid_off, *be0 = be + f.grid_off;
   const int32_t *as0 = a_scale + f.level_off, *bs0 = b_scale + f.level_off;
   const double tg = tot_grad[(int64_t)i * tot_grad_stride];
-  const int64_t row0 = grad_row0[i];
+  const int64_t row0 = grad_row0 != nullptr ? grad_row0[i] : f.lp_row;
   const float *lp0 = lp + (int64_t)f.lp_row * C;
+  // this warp's row of sums, one per column of the gradient (all zero between levels)
+  const int32_t cols = C + grad_col_off;
+  uint32_t *sums = reinterpret_cast<uint32_t *>(smem_raw) + (size_t)warp * cols;
+  for (int32_t k = lane; k < cols; k += 32) sums[k] = 0u;
+  __syncwarp();
   ProbState *prev = nullptr;  // alpha of the level before, state s at s + 2
   auto stage_alpha = [&](int32_t l) {
     const int32_t n = lst[l].y;
@@ -1233,7 +1241,8 @@ BandGrad(const BandInfo *__restrict__ infos, const BandArc *__restrict__ tabf,
     }
   };
   if (kArcs) {
-    prev = reinterpret_cast<ProbState *>(smem_raw) + (size_t)warp * st_pad + 2;
+    prev = reinterpret_cast<ProbState *>(smem_raw + (((size_t)4 * cols * sizeof(uint32_t) + 15) & ~(size_t)15)) +
+           (size_t)warp * st_pad + 2;
     stage_alpha(a - 1);
     __syncwarp();
   }
@@ -1272,8 +1281,7 @@ BandGrad(const BandInfo *__restrict__ infos, const BandArc *__restrict__ tabf,
           const int32_t ale = exact ? ae0[row + j] : ea_l, bee = exact ? be0[row + j] : eb_l;
           const int32_t col = it.label + grad_col_off;
           if (it.label != kNoLabel && it.label < C && col >= 0) {
-            const double post = alm * bem * zinv * Pow2Clamp(ale + bee - z.e);
-            g = (float)(tg * post);
+            g = (float)(alm * bem * zinv * Pow2Clamp(ale + bee - z.e));
             key = col;
           }
           if (kArcs) {
@@ -1295,20 +1303,20 @@ BandGrad(const BandInfo *__restrict__ infos, const BandArc *__restrict__ tabf,
         }
       }
       // States with the same label (the blank states of a CTC graph) add to the same
-      // element: their lanes are summed in lane order and one of them adds the sum, so
-      // an element receives one addition per 32 states of a level, from one warp, in
-      // program order.
-      const uint32_t grp = __match_any_sync(kAll, key);
-      const int32_t members = __popc(grp);
-      const int32_t rounds = __reduce_max_sync(kAll, key >= 0 ? members : 0);
-      float sum = 0.0f;
-      for (int32_t r = 0; r < rounds; ++r) {
-        const uint32_t src = __fns(grp, 0, r + 1);
-        const float v = __shfl_sync(kAll, g, (int)(src & 31u));
-        if (r < members) sum += v;
+      // element.  Their posteriors are summed in this warp's row of shared memory, in fixed
+      // point (2^-31 units: a sum of posteriors of one frame is at most 1) with integer
+      // atomics - native in shared memory, and independent of the order of the additions -
+      // then every lane takes the sum of its column out of the row, which leaves the row
+      // zero again, and whoever got it adds it to the gradient.
+      if (key >= 0) atomicAdd(&sums[key], __float2uint_rn(g * 2147483648.0f));
+      __syncwarp();
+      if (key >= 0) {
+        const uint32_t fixed = atomicExch(&sums[key], 0u);
+        if (fixed != 0u)
+          atomicAdd(grad_b + (row0 + l - 1) * grad_pitch + key,
+                    (float)tg * ((float)fixed * (1.0f / 2147483648.0f)));
       }
-      if (key >= 0 && lane == __ffs(grp) - 1 && sum != 0.0f)
-        atomicAdd(grad_b + (row0 + l - 1) * grad_pitch + key, sum);
+      __syncwarp();
     }
     if (kArcs) {
       __syncwarp();  // the level before has been read
@@ -1323,14 +1331,13 @@ BandGrad(const BandInfo *__restrict__ infos, const BandArc *__restrict__ tabf,
 // ---------------------------------------------------------------------------
 struct BandLayout {
   std::vector<BandInfo> infos;
-  int64_t grid_elems = 0, levels = 0;
+  int64_t grid_elems = 0, grid_states = 0, levels = 0;
   long long arc_frames = 0;
   int32_t max_states = 0, max_frames = 0;
   int32_t vit_threads = 32, vit_frames = 0, vit_batches = 0, xch_pad = 0;
-  int32_t chain_batches = 0, mrow = 0;
   int32_t st_pad = 0, lv_pad = 0;
   size_t chain_smem = 0, exact_smem = 0, viterbi_smem = 0, prep_smem = 0;
-  size_t off_infos, off_vf, off_vb, off_items, off_lists, off_meta, off_cutoffs, off_am, off_ae, off_bm,
+  size_t off_infos, off_vf, off_vb, off_items, off_factors, off_lists, off_chunk_r, off_keep, off_cutoffs, off_am, off_ae, off_bm,
       off_be, off_a_scale, off_b_scale, off_total, off_unfit, off_totals, off_status,
       total_bytes;  // off_status = off_totals + 40
   bool ok = true;
@@ -1348,12 +1355,12 @@ static int32_t MakeBandLayout(const k2b200_band_loss_args *a, BandLayout *L) {
               "host arrays of the batch description are required");
   K2B_REQUIRE(a->num_classes > 0, "empty log-prob matrix");
   L->infos.resize(a->num_fsas);
-  int64_t grid = 0, levels = 0, meta_words = 0;
+  int64_t grid = 0, levels = 0;
   for (int32_t i = 0; i < a->num_fsas; ++i) {
     BandInfo &f = L->infos[i];
     f.state_off = a->h_a_row_splits1[i];
     f.num_states = a->h_a_row_splits1[i + 1] - f.state_off;
-    f.pitch = std::max((f.num_states + 3) & ~3, 4);
+    f.pitch = 32 * (f.num_states / 32 + 1);
     f.frames = a->h_frames[i];
     K2B_REQUIRE(f.frames >= 0, "sequence of graph %d has a negative number of frames", i);
     if (i > 0)
@@ -1367,11 +1374,8 @@ static int32_t MakeBandLayout(const k2b200_band_loss_args *a, BandLayout *L) {
     if (i > 0 && f.lp_row == a->h_first_row[i - 1]) L->exclusive_rows = false;
     f.level_off = (int32_t)levels;
     f.grid_off = grid;
-    f.mpitch = std::max((f.num_states + 7) & ~7, 8);
-    f.pad = 0;
-    f.meta_off = meta_words;
     grid += (int64_t)(f.frames + 2) * f.pitch;
-    meta_words += (int64_t)(f.frames + 2) * f.mpitch;
+    L->grid_states += (int64_t)(f.frames + 2) * f.num_states;
     levels += f.frames + 2;
     L->max_states = std::max(L->max_states, f.num_states);
     L->max_frames = std::max(L->max_frames, f.frames);
@@ -1405,26 +1409,22 @@ static int32_t MakeBandLayout(const k2b200_band_loss_args *a, BandLayout *L) {
   }
   L->st_pad = ((L->max_states + 4) + 15) & ~15;
   L->lv_pad = (L->max_frames + 2 + 3) & ~3;
-  L->prep_smem = (size_t)4 * 8 * L->st_pad;
+  L->prep_smem = (size_t)4 * (8 * L->st_pad + 64 * (kPrepLevels + 2));
   L->exact_smem = sizeof(BandItem) * kChainSlots * kSlotItems + sizeof(int2) * (size_t)L->lv_pad +
                   sizeof(ProbState) * 2 * (size_t)L->st_pad;
-  {  // BandChainDense: the Viterbi kernel's batches plus the meta rows
-    L->mrow = std::max((L->max_states + 7) & ~7, 8);
-    const size_t batch_bytes =
-        (size_t)L->vit_frames * (sizeof(float) * (size_t)a->num_classes + 2 * (size_t)L->mrow);
-    const size_t fixed = sizeof(double) * 2 * (size_t)L->xch_pad + sizeof(int32_t) * (size_t)L->lv_pad;
-    L->chain_batches = kBandSmemBudget >= fixed + 3 * batch_bytes ? 3 : 2;
-    L->chain_smem = fixed + (size_t)L->chain_batches * batch_bytes;
-  }
+  L->chain_smem = sizeof(BandFactor) * kChainSlots * kFacSlot;
   if (L->max_states > kBandMaxStates) {
     L->ok = false;
     L->why = "a graph has more than 512 states";
   } else if (a->num_classes % 4 != 0 || (reinterpret_cast<uintptr_t>(a->log_probs) & 15) != 0) {
     L->ok = false;
     L->why = "rows of the log-prob matrix are not 16-byte aligned";
-  } else if (L->chain_smem > kBandSmemBudget + 16384 || L->exact_smem > kBandSmemBudget) {
+  } else if (L->chain_smem > kBandSmemBudget || L->exact_smem > kBandSmemBudget) {
     L->ok = false;
     L->why = "too many frames, states or classes for the shared memory of the recursions";
+  } else if (L->max_frames + 2 > kChainMaxChunks * kPrepLevels) {
+    L->ok = false;
+    L->why = "a sequence has more than 65534 frames";
   } else if (a->num_fsas > 65535) {
     L->ok = false;
     L->why = "more than 65535 graphs";
@@ -1440,7 +1440,9 @@ static int32_t MakeBandLayout(const k2b200_band_loss_args *a, BandLayout *L) {
   L->off_vb = take(sizeof(float) * (size_t)grid);
   L->off_items = take(sizeof(BandItem) * (size_t)grid);
   L->off_lists = take(sizeof(int2) * (size_t)levels);
-  L->off_meta = take(sizeof(uint16_t) * (size_t)meta_words);
+  L->off_chunk_r = take(sizeof(int32_t) * (size_t)levels);
+  L->off_keep = take(sizeof(uint16_t) * 32 * (size_t)levels);
+  L->off_factors = take(sizeof(BandFactor) * (size_t)grid);
   L->off_cutoffs = take(sizeof(float) * a->num_fsas);
   L->off_am = take(sizeof(double) * (size_t)grid);
   L->off_ae = take(sizeof(int32_t) * (size_t)grid);
@@ -1478,7 +1480,7 @@ static bool BandReduceBeam(const k2b200_band_loss_args *a, const long long *h_to
 
 static int32_t LaunchBandChains(const BandLayout &L, const k2b200_band_loss_args *args, char *ws,
                                 double *tot_scores, cudaStream_t stream) {
-  K2B_CUDA_OK(cudaFuncSetAttribute(BandChainDense, cudaFuncAttributeMaxDynamicSharedMemorySize,
+  K2B_CUDA_OK(cudaFuncSetAttribute(BandChainLists, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                    (int)L.chain_smem));
   K2B_CUDA_OK(cudaFuncSetAttribute(BandChainExact, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                    (int)L.exact_smem));
@@ -1490,12 +1492,12 @@ static int32_t LaunchBandChains(const BandLayout &L, const k2b200_band_loss_args
   BandTotal *total = reinterpret_cast<BandTotal *>(ws + L.off_total);
   int32_t *unfit = reinterpret_cast<int32_t *>(ws + L.off_unfit);
   int32_t *status = reinterpret_cast<int32_t *>(ws + L.off_status);
-  { BandChainDense<<<grid, L.vit_threads, L.chain_smem, stream>>>(
-      infos, reinterpret_cast<const BandState *>(args->band_states), args->log_probs,
-      args->num_classes, reinterpret_cast<const uint16_t *>(ws + L.off_meta), lists, am, bm,
+  { BandChainLists<<<grid, 32, L.chain_smem, stream>>>(
+      infos, reinterpret_cast<const BandFactor *>(ws + L.off_factors),
+      reinterpret_cast<const int32_t *>(ws + L.off_chunk_r), am, bm,
       reinterpret_cast<int32_t *>(ws + L.off_a_scale),
       reinterpret_cast<int32_t *>(ws + L.off_b_scale), tot_scores, total, unfit, status,
-      L.vit_frames, L.chain_batches, L.xch_pad, L.mrow, L.lv_pad, g_wait_limit); NoteLaunch(); }
+      g_wait_limit); NoteLaunch(); }
   { BandChainExact<<<grid, 32, L.exact_smem, stream>>>(
       infos, reinterpret_cast<const BandArc *>(args->band_arcs), args->log_probs,
       args->num_classes, items, lists, am, reinterpret_cast<int32_t *>(ws + L.off_ae), bm,
@@ -1594,33 +1596,44 @@ int32_t k2b200_band_loss_forward(const k2b200_band_loss_args *args, void *worksp
   // (intersect_dense.cu:300-320).  The grid bounds it: the host reads the counts only
   // when that bound does not already satisfy the limits, and after it has launched the
   // recursions, which in the rare case of a reduction run again.
-  const bool need_count = L.grid_elems > args->max_states || L.arc_frames > args->max_arcs;
+  const bool need_count = L.grid_states > args->max_states || L.arc_frames > args->max_arcs;
   float beam = args->output_beam;
   for (int iter = 0;; ++iter) {
     K2B_CUDA_OK(cudaMemsetAsync(ws + L.off_totals, 0, 5 * sizeof(long long), stream));
     K2B_CUDA_OK(cudaMemsetAsync(ws + L.off_unfit, 0, sizeof(int32_t) * args->num_fsas, stream));
+    cudaStream_t side = nullptr;
     {
       PhaseTimer timer(kPhasePrune, stream);
-      NotePhaseKernel(kPhasePrune, "BandPrep");
+      NotePhaseKernel(kPhasePrune, "BandKeep+BandPrep");
+      dim3 kgrid(CeilDiv(L.max_frames + 2, 4 * kKeepLevels), args->num_fsas);
+      { BandKeep<<<kgrid, 128, 0, stream>>>(
+          reinterpret_cast<const BandInfo *>(ws + L.off_infos), args->a_row_splits2,
+          reinterpret_cast<const float *>(ws + L.off_vf),
+          reinterpret_cast<const float *>(ws + L.off_vb), beam,
+          reinterpret_cast<uint16_t *>(ws + L.off_keep),
+          reinterpret_cast<float *>(ws + L.off_cutoffs),
+          reinterpret_cast<unsigned long long *>(ws + L.off_totals)); NoteLaunch(); }
+      // the host reads the counts behind BandKeep, while what follows runs
+      if (need_count) K2B_FORWARD(SideFork(stream, &side));
       dim3 grid(CeilDiv(L.max_frames + 2, 4 * kPrepLevels), args->num_fsas);
       { BandPrep<<<grid, 128, L.prep_smem, stream>>>(
           reinterpret_cast<const BandInfo *>(ws + L.off_infos),
-          reinterpret_cast<const BandState *>(args->band_states), args->a_row_splits2,
-          args->log_probs, args->num_classes, reinterpret_cast<const float *>(ws + L.off_vf),
-          reinterpret_cast<const float *>(ws + L.off_vb), beam,
+          reinterpret_cast<const BandState *>(args->band_states),
+          reinterpret_cast<const BandArc *>(args->band_arcs),
+          reinterpret_cast<const uint16_t *>(ws + L.off_keep), args->log_probs,
+          args->num_classes, reinterpret_cast<const float *>(ws + L.off_vf),
+          reinterpret_cast<const float *>(ws + L.off_vb),
+          reinterpret_cast<const float *>(ws + L.off_cutoffs),
           reinterpret_cast<BandItem *>(ws + L.off_items),
+          reinterpret_cast<BandFactor *>(ws + L.off_factors),
           reinterpret_cast<int2 *>(ws + L.off_lists),
-          reinterpret_cast<uint16_t *>(ws + L.off_meta),
-          reinterpret_cast<float *>(ws + L.off_cutoffs),
-          reinterpret_cast<unsigned long long *>(ws + L.off_totals),
+          reinterpret_cast<int32_t *>(ws + L.off_chunk_r),
           reinterpret_cast<int32_t *>(ws + L.off_unfit), L.st_pad); NoteLaunch(); }
       K2B_CUDA_OK(cudaGetLastError());
     }
-    cudaStream_t side = nullptr;
-    if (need_count) K2B_FORWARD(SideFork(stream, &side));  // behind the counts, before the chain
     {
       PhaseTimer timer(kPhaseChain, stream);
-      NotePhaseKernel(kPhaseChain, "BandChainDense");
+      NotePhaseKernel(kPhaseChain, "BandChainLists");
       K2B_FORWARD(LaunchBandChains(L, args, ws, tot_scores, stream));
     }
     if (!need_count) break;
@@ -1649,7 +1662,7 @@ int32_t k2b200_band_loss_backward(const k2b200_band_loss_args *args, void *works
              L.total_bytes);
     return kWorkspaceTooSmall;
   }
-  K2B_REQUIRE(tot_grad && grad_b && grad_row0, "NULL device pointer");
+  K2B_REQUIRE(tot_grad && grad_b, "NULL device pointer");
   K2B_REQUIRE(grad_col_off == 0 || grad_col_off == 1, "grad_col_off must be 0 or 1");
   char *ws = reinterpret_cast<char *>(workspace);
   PhaseTimer timer(kPhaseGrad, stream);
@@ -1670,11 +1683,19 @@ int32_t k2b200_band_loss_backward(const k2b200_band_loss_args *args, void *works
       reinterpret_cast<const BandTotal *>(ws + L.off_total),                                  \
       reinterpret_cast<const int32_t *>(ws + L.off_unfit), tot_grad, tot_grad_stride, grad_a, \
       grad_b, grad_row0, grad_pitch, grad_col_off, args->num_classes, L.st_pad); NoteLaunch(); }
+  const size_t sums_bytes =
+      (sizeof(uint32_t) * 4 * (size_t)(args->num_classes + grad_col_off) + 15) & ~(size_t)15;
+  K2B_REQUIRE(sums_bytes + sizeof(ProbState) * 4 * (size_t)L.st_pad <= kBandSmemBudget,
+              "too many classes for the gradient kernel");
   if (grad_a != nullptr) {
-    const size_t smem = sizeof(ProbState) * 4 * (size_t)L.st_pad;
+    const size_t smem = sums_bytes + sizeof(ProbState) * 4 * (size_t)L.st_pad;
+    K2B_CUDA_OK(cudaFuncSetAttribute(BandGrad<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     (int)smem));
     K2B_BAND_GRAD(true, smem)
   } else {
-    K2B_BAND_GRAD(false, 0)
+    K2B_CUDA_OK(cudaFuncSetAttribute(BandGrad<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     (int)sums_bytes));
+    K2B_BAND_GRAD(false, sums_bytes)
   }
 #undef K2B_BAND_GRAD
   K2B_CUDA_OK(cudaGetLastError());

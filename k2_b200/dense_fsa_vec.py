@@ -114,14 +114,14 @@ class DenseFsaVec(object):
             order = np.argsort(first, kind="stable")
             overlapping = bool(np.any((first + dur)[order][:-1] > first[order][1:]))
             eff = np.stack([seg[:, 0], seg[:, 1], dur], axis=1).astype(np.int32)
-            meta = _lib.upload_i32(np.concatenate([eff.reshape(-1), row_splits]), device)
-            k3 = 3 * seg.shape[0]
             fn = _LogSoftmaxDenseFunction if _logits else _DenseFsaVecFunction
-            # The score matrix is laid out on first use: a loss that reads the
-            # log-probs directly (k2b200_band_loss_*) never needs it.
-            self._init(None, row_splits, meta[k3:], device=device, num_cols=C + 1)
-            self._make_scores = lambda: fn.apply(log_probs, meta[:k3].view(-1, 3), meta[k3:],
-                                                 rows, overlapping)
+            # The score matrix, and the device copy of the row splits, are made on first
+            # use: a loss that reads the log-probs directly (k2b200_band_loss_*) needs
+            # neither.
+            self._init(None, row_splits, device=device, num_cols=C + 1)
+            # (no closure over self: a reference cycle would keep the log-probs and
+            # their gradient alive until the cycle collector runs)
+            self._make_scores = (fn, log_probs, eff, rows, overlapping)
             if not _logits and not overlapping:
                 # what a loss needs to read `log_probs` in place and to send its
                 # gradient straight to it (k2b200_band_loss_*,
@@ -166,19 +166,27 @@ class DenseFsaVec(object):
         self._device = scores.device if scores is not None else torch.device(device)
         self._num_cols = scores.shape[1] if scores is not None else num_cols
         self.h_row_splits = np.ascontiguousarray(h_row_splits, dtype=np.int32)
-        if d_row_splits is not None:
-            self.row_splits = d_row_splits
-        elif self._device.type == "cuda":
-            self.row_splits = _lib.upload_i32(self.h_row_splits, self._device)
-        else:
-            self.row_splits = torch.from_numpy(self.h_row_splits)
-        self._duration = torch.from_numpy(np.diff(self.h_row_splits) - 1)
+        self._row_splits = d_row_splits
+        self._duration = None
+        self._band_args = None  # the last k2b200_band_loss_* arguments made from this object
+
+    @property
+    def row_splits(self) -> torch.Tensor:
+        """Row splits of the score matrix on `device` (made on first use)."""
+        if self._row_splits is None:
+            if self._device.type == "cuda":
+                self._row_splits = _lib.upload_i32(self.h_row_splits, self._device)
+            else:
+                self._row_splits = torch.from_numpy(self.h_row_splits)
+        return self._row_splits
 
     @property
     def scores(self) -> torch.Tensor:
         """The [sum_i (T_i + 1), C + 1] score matrix (k2/csrc/fsa.h:138-185)."""
         if self._scores is None:
-            self._scores = self._make_scores()
+            fn, log_probs, eff, rows, overlapping = self._make_scores
+            segments = _lib.upload_i32(eff.reshape(-1), self._device).view(-1, 3)
+            self._scores = fn.apply(log_probs, segments, self.row_splits, rows, overlapping)
             self._make_scores = None
         return self._scores
 
@@ -189,6 +197,7 @@ class DenseFsaVec(object):
         self._make_scores = None
         self._source = None  # no longer the layout of the tensor it was made from
         self._source_rows = {}
+        self._band_args = None
 
     @property
     def num_cols(self) -> int:
@@ -207,6 +216,8 @@ class DenseFsaVec(object):
     @property
     def duration(self) -> torch.Tensor:
         """Number of frames of each sequence (on CPU), without the extra row."""
+        if self._duration is None:
+            self._duration = torch.from_numpy(np.diff(self.h_row_splits) - 1)
         return self._duration
 
     def dim0(self) -> int:
