@@ -371,24 +371,25 @@ def run_ours(args):
     # per step the ranks all-reduce [loss, frames] on a side stream, right after the
     # total scores exist and beside the gradient kernels (the gradient of a summed loss
     # does not depend on the other ranks)
-    red = torch.zeros(2, dtype=torch.float64, device=dev)
-    red[1] = float(frames)
-    comm = torch.cuda.Stream(dev) if dist is not None else None
+    from k2_b200.parallel import LossReducer, PeerLossReducer
+    reducer = None
+    if dist is not None:  # K2B_NCCL_REDUCE=1: the collective library instead of peer stores
+        reducer = (LossReducer(dev) if os.environ.get("K2B_NCCL_REDUCE")
+                   else PeerLossReducer(dev))
+    frames_of = {}
 
     def loss_step(lp, g, segments, beam):
         lp = lp.detach().requires_grad_(True)
         dense = k2.DenseFsaVec(lp, segments)
         loss = k2.ctc_loss(g, dense, output_beam=beam, reduction="sum")
-        if dist is not None:
-            with torch.no_grad():
-                red[0:1].copy_(loss.detach().reshape(1))
-            comm.wait_stream(torch.cuda.current_stream(dev))
-            with torch.cuda.stream(comm):
-                dist.all_reduce(red)
+        if reducer is not None:
+            nf = frames_of.get(id(segments))
+            if nf is None:
+                nf = frames_of[id(segments)] = int(segments[:, 2].sum())
+            reducer.submit(loss, nf)
         loss.backward()
-        if dist is not None:
-            torch.cuda.current_stream(dev).wait_stream(comm)
-            return red[0], lp.grad
+        if reducer is not None:
+            return reducer.result()[0], lp.grad
         return loss.detach(), lp.grad
 
     def step(lp):
@@ -567,6 +568,12 @@ def run_ours(args):
         den["path_gbs"] = den["algorithmic_bytes_per_step"] * args.steps / (d_ms * 1e-3) / 1e9
         den["path_frac_of_hbm"] = den["path_gbs"] / (hbm_peak * world)
 
+    # a bounded wait of the loss exchange that gave up would have made the totals invalid
+    reduce_status = reducer.status() if isinstance(reducer, PeerLossReducer) else 0
+    assert reduce_status == 0, "the exchange of (loss, frames) between the ranks timed out"
+    if dist is not None:
+        dist.barrier()
+        reducer.close()
     if rank != 0:
         if dist is not None:
             dist.destroy_process_group()

@@ -677,6 +677,39 @@ int32_t k2b200_fsa_arc_post_backprop(const k2b200_fsa_view *fsas, int32_t use_do
                                      const void *arc_post_deriv, void *forward_deriv,
                                      void *backward_deriv, void *stream);
 
+/* ---------------------------------------------------------------------------
+ * Sum of a rank's losses and the all-reduce of (loss, frames) over the GPUs of a node,
+ * in one kernel over peer memory.  Replaces the `-1 * tot_scores` ... `.sum()` of
+ * k2/python/k2/ctc_loss.py:72-84 together with the trainer's all-reduce of the summed
+ * loss and the frame count (the reference leaves that collective to the training
+ * script); utterances are independent, so it is the only exchange of the path.
+ *
+ *   k2b200_peer_reduce_create: allocates this rank's exchange buffer on the current device,
+ *     zeroed, and returns its address and a K2B200_IPC_HANDLE_BYTES-byte handle that the
+ *     other processes of the node pass to k2b200_peer_reduce_open (exchange the handles over
+ *     any host channel, e.g. the process group's store) to map it; _close unmaps, _destroy
+ *     frees.  With one rank no handle needs to travel.
+ *   k2b200_loss_sum_all_reduce: out[0] = sum over ranks of sign * sum(values[0..n)),
+ *     out[1] = sum over ranks of num_frames (device, float64), the same bits on every rank.
+ *     values: device, float32 (values_are_f32 != 0) or float64.  bufs[world]: host array,
+ *     bufs[r] = rank r's buffer as mapped in this process (bufs[rank] = the own one).
+ *     seq: 1, 2, 3, ... - the same on every rank for the same step.  Every rank of the world
+ *     must make the call; a rank's launch waits (occupying one CTA) for the others'.  That
+ *     wait is bounded: after poll_limit polls (negative: the default, a few seconds) bit 0
+ *     of the status word is set and out is invalid; nothing hangs or traps.
+ *   k2b200_peer_reduce_status: waits for `stream`, returns the status word.
+ * ------------------------------------------------------------------------- */
+#define K2B200_IPC_HANDLE_BYTES 64
+int32_t k2b200_peer_reduce_create(void **local_buf, void *ipc_handle_out);
+int32_t k2b200_peer_reduce_open(const void *ipc_handle, void **peer_buf);
+int32_t k2b200_peer_reduce_close(void *peer_buf);
+int32_t k2b200_peer_reduce_destroy(void *local_buf);
+int32_t k2b200_loss_sum_all_reduce(const void *values, int32_t n, int32_t values_are_f32,
+                                   double sign, double num_frames, void *const *bufs,
+                                   int32_t rank, int32_t world, uint64_t seq,
+                                   int32_t poll_limit, double *out, void *stream);
+int32_t k2b200_peer_reduce_status(void *local_buf, void *stream, int32_t *status);
+
 #ifdef __cplusplus
 }
 #endif

@@ -215,6 +215,15 @@ _sig("k2b200_fsa_properties_tmp_bytes", c_sz, [c_i32, c_i32])
 _sig("k2b200_fsa_properties", c_i32,
      [c_vp, c_vp, c_vp, c_vp, c_vp, c_i32, c_i32, c_i32, c_vp, c_vp, c_vp])
 
+_sig("k2b200_peer_reduce_create", c_i32, [ctypes.POINTER(c_vp), c_vp])
+_sig("k2b200_peer_reduce_open", c_i32, [c_vp, ctypes.POINTER(c_vp)])
+_sig("k2b200_peer_reduce_close", c_i32, [c_vp])
+_sig("k2b200_peer_reduce_destroy", c_i32, [c_vp])
+_sig("k2b200_loss_sum_all_reduce", c_i32,
+     [c_vp, c_i32, c_i32, ctypes.c_double, ctypes.c_double, ctypes.POINTER(c_vp), c_i32, c_i32,
+      ctypes.c_uint64, c_i32, c_vp, c_vp])
+_sig("k2b200_peer_reduce_status", c_i32, [c_vp, c_vp, ctypes.POINTER(c_i32)])
+
 EXPORTED = [
     "k2b200_last_error", "k2b200_abi_version", "k2b200_kernel_launch_count",
     "k2b200_profile_enable", "k2b200_profile_kernel", "k2b200_profile_read_ms", "k2b200_row_splits_to_row_ids",
@@ -238,6 +247,8 @@ EXPORTED = [
     "k2b200_intersect_dense_pruned_emit",
     "k2b200_fsa_scores_backprop", "k2b200_fsa_arc_post_backprop",
     "k2b200_dense_loss_backward_log_probs",
+    "k2b200_peer_reduce_create", "k2b200_peer_reduce_open", "k2b200_peer_reduce_close",
+    "k2b200_peer_reduce_destroy", "k2b200_loss_sum_all_reduce", "k2b200_peer_reduce_status",
     "k2b200_online_decode_workspace_bytes", "k2b200_online_decode_load",
     "k2b200_online_decode_run", "k2b200_online_decode_emit", "k2b200_online_decode_store",
     "k2b200_online_decode_load_all", "k2b200_online_decode_store_all",

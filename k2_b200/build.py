@@ -52,7 +52,8 @@ def build(force: bool = False, verbose: bool = False) -> str:
         if p.returncode != 0:
             raise RuntimeError("nvcc failed: " + " ".join(cmd))
     subprocess.check_call([nvcc, "-shared", "-o", LIB_PATH] + objs +
-                          ["-ccbin", "/usr/bin/g++", "-gencode", "arch=compute_100a,code=sm_100a"])
+                          ["-ccbin", "/usr/bin/g++", "-gencode", "arch=compute_100a,code=sm_100a",
+                           "-ldl"])
     return LIB_PATH
 
 

@@ -523,10 +523,15 @@ ArcMasks(const FsaInfo *__restrict__ infos, int32_t n, int64_t total_levels,
 // The alpha / beta recursion for planned graphs, driven by the masks of ArcMasks:
 // same arithmetic and ring as GridChainLanes, but a frame needs no Viterbi score and
 // no test - one mask byte per lane says which of its arcs to add.  A ring slot holds
-// the exp() part of the packed dense row and the frame's row of mask bytes.  Every
-// state is written to the grid (0 for pruned ones).
+// the exp() part of the packed dense row (kPBytes reserved for it) and the frame's row of
+// mask bytes.  Slots and state buffers have compile-time sizes and the frame loop is
+// unrolled over the ring, so every shared-memory address is a register (an arc's byte
+// offset, fixed for the whole call) plus a constant.  When all arcs of a warp's lanes carry
+// one label (walking forward in a graph where every state has one entering label),
+// exp(dense score) multiplies the sum once per state instead of every term.  Every state
+// is written to the grid (0 for pruned ones).
 // ---------------------------------------------------------------------------
-template <int kDeg, int kU>
+template <int kDeg, int kU, int kPBytes>
 __global__ void __launch_bounds__(kLaneThreads)
 GridChainMasked(const FsaInfo *__restrict__ infos, int32_t n, int64_t total_levels,
                 const Arc *__restrict__ arcs, const int32_t *__restrict__ a_row_splits2,
@@ -551,10 +556,12 @@ GridChainMasked(const FsaInfo *__restrict__ infos, int32_t n, int64_t total_leve
     if (dir == 0 && tid == 0) tot[i] = -INFINITY;
     return;
   }
-  const uint32_t p_bytes = 8u * (uint32_t)dp.cols2;
-  const uint32_t slot_bytes = p_bytes + (uint32_t)kLaneThreads;
+  (void)s_pad;
+  constexpr int kSPad = kLaneThreads;  // a planned graph has at most that many states
+  const uint32_t p_bytes = 8u * (uint32_t)dp.cols2;  // <= kPBytes
+  constexpr uint32_t slot_bytes = (uint32_t)kPBytes + (uint32_t)kLaneThreads;
   unsigned char *ring = smem_raw;                                            // [kU][slot_bytes]
-  double *pv = reinterpret_cast<double *>(ring + (size_t)kU * slot_bytes);   // [2][s_pad]
+  double *pv = reinterpret_cast<double *>(ring + (size_t)kU * slot_bytes);   // [2][kSPad]
   int32_t s = -1, g = 0, G = 1;
   {
     const int32_t code = plan[((int64_t)dir * n + i) * kLaneThreads + tid];
@@ -564,12 +571,16 @@ GridChainMasked(const FsaInfo *__restrict__ infos, int32_t n, int64_t total_leve
       G = code >> 24;
     }
   }
-  int32_t other_col[kDeg];
+  // byte offsets of an arc's neighbour in a state buffer and of its column in a dense row
+  uint32_t other_off[kDeg], col_off[kDeg];
   double ew[kDeg];
   bool risky = false;
+  int32_t col0 = -1;
+  bool same = true;
 #pragma unroll
   for (int j = 0; j < kDeg; ++j) {
-    other_col[j] = cols << 16;
+    other_off[j] = 0;
+    col_off[j] = 8u * (uint32_t)cols;  // the padding column: 0
     ew[j] = 0.0;
   }
   if (s >= 0) {
@@ -582,13 +593,18 @@ GridChainMasked(const FsaInfo *__restrict__ infos, int32_t n, int64_t total_leve
         const Arc arc = arcs[dir == 0 ? in_arcs[k] : k];
         const int32_t c = arc.label + 1;
         if (c >= 0 && c < cols && arc.score != -INFINITY) {
-          other_col[j] = (dir == 0 ? arc.src : arc.dest) | (c << 16);
+          other_off[j] = 8u * (uint32_t)(dir == 0 ? arc.src : arc.dest);
+          col_off[j] = 8u * (uint32_t)c;
           ew[j] = exp((double)arc.score);
           if (!(fabsf(arc.score) <= kMaxAbsArcScore)) risky = true;
+          if (col0 < 0) col0 = c;
+          else if (c != col0) same = false;
         }
       }
     }
   }
+  const bool hoist = __all_sync(0xffffffffu, same);
+  const uint32_t col0_off = 8u * (uint32_t)(col0 < 0 ? 0 : col0);  // no arc: the sum is 0
   if (tid == 0) {
     for (int st = 0; st < kU; ++st) MbarInit(&full[st], 1);
     emax = kNone;
@@ -625,7 +641,7 @@ GridChainMasked(const FsaInfo *__restrict__ infos, int32_t n, int64_t total_leve
     unsigned char *dst = ring + (size_t)slot * slot_bytes;
     MbarArriveExpectTx(&full[slot], p_bytes + (unsigned)kLaneThreads);
     BulkCopyG2S(dst, dense_p + row * dp.pitch, p_bytes, &full[slot]);
-    BulkCopyG2S(dst + p_bytes, mask0 + r * kLaneThreads, (unsigned)kLaneThreads, &full[slot]);
+    BulkCopyG2S(dst + kPBytes, mask0 + r * kLaneThreads, (unsigned)kLaneThreads, &full[slot]);
   };
   if (tid == 0)
     for (int32_t step = 1; step < kU; ++step) issue_row(step, step - 1);
@@ -635,7 +651,6 @@ GridChainMasked(const FsaInfo *__restrict__ infos, int32_t n, int64_t total_leve
   double last = 0.0;
   int32_t K = 0;
   unsigned parity = 0;
-  uint32_t rec_off = 0;
   bool gave_up = false;
   for (int32_t t0 = 1; t0 <= Tk && !gave_up; t0 += kU) {
 #pragma unroll
@@ -658,21 +673,31 @@ GridChainMasked(const FsaInfo *__restrict__ infos, int32_t n, int64_t total_leve
         K += shift;
         scale = __longlong_as_double((long long)(1023 - shift) << 52);
       }
-      const double *prev = pv + (u & 1) * s_pad;
-      double *cur = pv + ((u + 1) & 1) * s_pad;
-      rec_off = u == 0 ? 0u : rec_off + slot_bytes;
-      asm volatile("" : "+r"(rec_off));
-      const double *prow = reinterpret_cast<const double *>(ring + rec_off);
-      const uint32_t m = (ring + rec_off + p_bytes)[tid];
+      const unsigned char *prev = reinterpret_cast<const unsigned char *>(pv + (u & 1) * kSPad);
+      double *cur = pv + ((u + 1) & 1) * kSPad;
+      const unsigned char *prow = ring + u * slot_bytes;
+      const uint32_t m = (prow + kPBytes)[tid];
+      auto at = [](const unsigned char *base, uint32_t off) {
+        return *reinterpret_cast<const double *>(base + off);
+      };
       double sum = 0.0;
       if (__any_sync(0xffffffffu, m != 0)) {
         double sum1 = 0.0;  // two partial sums: half the chain of dependent additions
+        if (hoist) {
 #pragma unroll
-        for (int j = 0; j < kDeg; j += 2) {
-          if (m & (1u << j))
-            sum += prev[other_col[j] & 0xffff] * ew[j] * prow[other_col[j] >> 16];
-          if (j + 1 < kDeg && (m & (2u << j)))
-            sum1 += prev[other_col[j + 1] & 0xffff] * ew[j + 1] * prow[other_col[j + 1] >> 16];
+          for (int j = 0; j < kDeg; j += 2) {
+            if (m & (1u << j)) sum = fma(at(prev, other_off[j]), ew[j], sum);
+            if (j + 1 < kDeg && (m & (2u << j)))
+              sum1 = fma(at(prev, other_off[j + 1]), ew[j + 1], sum1);
+          }
+        } else {
+#pragma unroll
+          for (int j = 0; j < kDeg; j += 2) {
+            if (m & (1u << j))
+              sum = fma(at(prev, other_off[j]) * ew[j], at(prow, col_off[j]), sum);
+            if (j + 1 < kDeg && (m & (2u << j)))
+              sum1 = fma(at(prev, other_off[j + 1]) * ew[j + 1], at(prow, col_off[j + 1]), sum1);
+          }
         }
         sum += sum1;
 #pragma unroll
@@ -682,6 +707,7 @@ GridChainMasked(const FsaInfo *__restrict__ infos, int32_t n, int64_t total_leve
             if (g + d < G) sum += so;
           }
         }
+        if (hoist) sum *= at(prow, col0_off);
       }
       const double v = u == 0 ? sum * scale : sum;
       const int32_t vhi = __double2hiint(v);
@@ -1634,18 +1660,29 @@ static int32_t LaunchChainMasked(const LossLayout &LL, const k2b200_intersect_ar
   }
   {
     constexpr int kU = kChainGroup;
-    const size_t smem = (size_t)kU * (8 * (size_t)LL.pack.cols2 + kLaneThreads) +
-                        sizeof(double) * 2 * s_pad;
-    K2B_REQUIRE(smem <= kChainSmemBudget, "too many columns for the fused loss path");
-    K2B_CUDA_OK(cudaFuncSetAttribute(GridChainMasked<kLaneDeg, kU>,
-                                     cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    const size_t p_bytes = 8 * (size_t)LL.pack.cols2;
     dim3 grid(2, args->num_fsas);
-    { GridChainMasked<kLaneDeg, kU><<<grid, kLaneThreads, smem, stream>>>(
-        d_infos, args->num_fsas, L.total_levels, arcs, args->a_row_splits2, args->a_in_splits,
-        args->a_in_arcs, dense, LL.pack, masks, fwd, bwd, cutoffs,
-        reinterpret_cast<ProbState *>(ws + LL.off_alpha),
-        reinterpret_cast<ProbState *>(ws + LL.off_beta), tot, plan, unfit, s_pad);
-      NoteLaunch(); }
+#define K2B_CHAIN_MASKED(PBYTES)                                                              \
+    {                                                                                         \
+      const size_t smem = (size_t)kU * ((PBYTES) + kLaneThreads) +                            \
+                          sizeof(double) * 2 * kLaneThreads;                                  \
+      K2B_REQUIRE(smem <= kChainSmemBudget, "too many columns for the fused loss path");      \
+      K2B_CUDA_OK(cudaFuncSetAttribute(GridChainMasked<kLaneDeg, kU, PBYTES>,                 \
+                                       cudaFuncAttributeMaxDynamicSharedMemorySize,           \
+                                       (int)smem));                                           \
+      { GridChainMasked<kLaneDeg, kU, PBYTES><<<grid, kLaneThreads, smem, stream>>>(          \
+          d_infos, args->num_fsas, L.total_levels, arcs, args->a_row_splits2,                 \
+          args->a_in_splits, args->a_in_arcs, dense, LL.pack, masks, fwd, bwd, cutoffs,       \
+          reinterpret_cast<ProbState *>(ws + LL.off_alpha),                                   \
+          reinterpret_cast<ProbState *>(ws + LL.off_beta), tot, plan, unfit, s_pad);          \
+        NoteLaunch(); }                                                                       \
+    }
+    // room for the exp() part of a dense row, in four sizes
+    if (p_bytes <= 768) K2B_CHAIN_MASKED(768)
+    else if (p_bytes <= 2048) K2B_CHAIN_MASKED(2048)
+    else if (p_bytes <= 8192) K2B_CHAIN_MASKED(8192)
+    else K2B_CHAIN_MASKED(35840)
+#undef K2B_CHAIN_MASKED
   }
   K2B_CUDA_OK(cudaGetLastError());
   return kOk;

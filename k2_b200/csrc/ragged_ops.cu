@@ -3,6 +3,7 @@
 // the place of the cub / moderngpu wrappers the reference leans on
 // (k2/csrc/utils_inl.h:40-90 ExclusiveSum, k2/csrc/utils.cu:75-200
 // RowSplitsToRowIds, k2/csrc/fsa_utils.cu:901-928 GetIncomingArcs).
+#include <nvtx3/nvToolsExt.h>
 #include <atomic>
 #include <cstring>
 #include <mutex>
@@ -57,7 +58,14 @@ void SetProfiling(bool on) {
   for (auto &p : g_phase) p.used = 0;
 }
 
+// NVTX ranges (as the reference's NVTX_RANGE, k2/csrc/nvtx.h:31-61) around the same phases:
+// no-ops unless a tool that injects an NVTX library is attached.
+static const char *const kPhaseNames[kNumPhases] = {
+    "k2b200:viterbi", "k2b200:prune", "k2b200:emit", "k2b200:scores", "k2b200:posteriors",
+    "k2b200:incoming", "k2b200:dense", "k2b200:chain", "k2b200:grad"};
+
 PhaseTimer::PhaseTimer(int phase, cudaStream_t stream) : phase_(phase), stream_(stream), slot_(-1) {
+  nvtxRangePushA(kPhaseNames[phase]);
   std::lock_guard<std::mutex> lock(g_prof_mutex);
   if (!g_profiling) return;
   PhaseLog &log = g_phase[phase];
@@ -70,6 +78,7 @@ PhaseTimer::PhaseTimer(int phase, cudaStream_t stream) : phase_(phase), stream_(
   cudaEventRecord(log.pool[slot_].start, stream);
 }
 PhaseTimer::~PhaseTimer() {
+  nvtxRangePop();
   if (slot_ < 0) return;
   std::lock_guard<std::mutex> lock(g_prof_mutex);
   cudaEventRecord(g_phase[phase_].pool[slot_].stop, stream_);

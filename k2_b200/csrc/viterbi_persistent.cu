@@ -340,15 +340,26 @@ int32_t LaunchPlanLanes(const Layout &L, const k2b200_intersect_args *a, char *w
 // ---------------------------------------------------------------------------
 // Viterbi recursion with planned lanes: as RegisterViterbi, but the arcs of a state
 // are spread over the G(s) lanes its plan gives it, which take the max by shuffles.
+// The rows of dense scores arrive in a ring in shared memory by 4-byte cp.async, kVitAhead
+// frames ahead (rows of C + 1 floats are not 16-byte aligned).  The frame loop is unrolled
+// over the ring, so a frame costs a lane, per arc, a load of the neighbour's score and of
+// the dense score at constant offsets, two additions and a max.  When all arcs of a warp's
+// lanes carry the label of their state (walking forward in a graph where every state has
+// one entering label) the dense score is added once per state, after the max: rounding is
+// monotonic, so max_j fl(y_j + x) = fl(max_j y_j + x), bit for bit.
 // Graphs marked unfit are skipped (PersistentViterbi handles them).
 // ---------------------------------------------------------------------------
-template <int kDeg, int kRegPrefetch>
+constexpr int kVitRing = 8;   // slots of the row ring = frames per unrolled group
+constexpr int kVitAhead = 6;  // rows requested ahead of the frame that uses them
+
+template <int kDeg>
 __global__ void __launch_bounds__(kLaneThreads)
 LanesViterbi(const FsaInfo *__restrict__ infos, int32_t n, const Arc *__restrict__ arcs,
              const int32_t *__restrict__ a_row_splits2, const int32_t *__restrict__ in_splits,
              const int32_t *__restrict__ in_arcs, const float *__restrict__ scores,
-             int32_t cols, float *__restrict__ fwd, float *__restrict__ bwd,
+             int32_t cols, int32_t cols_pad, float *__restrict__ fwd, float *__restrict__ bwd,
              const int32_t *__restrict__ plan, const int32_t *__restrict__ unfit) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
   __shared__ float buf[2][kLaneThreads];
   const int32_t i = blockIdx.y;
   if (unfit[i] & 1) return;
@@ -356,7 +367,8 @@ LanesViterbi(const FsaInfo *__restrict__ infos, int32_t n, const Arc *__restrict
   const int dir = blockIdx.x;
   const int32_t S = f.num_states, Tk = f.tk;
   if (S == 0) return;
-  const int tid = threadIdx.x;
+  const int tid = threadIdx.x, nt = blockDim.x;
+  float *ring = reinterpret_cast<float *>(smem_raw);  // [kVitRing][cols_pad]
   int32_t s = -1, g = 0, G = 1;
   {
     const int32_t code = plan[((int64_t)dir * n + i) * kLaneThreads + tid];
@@ -368,6 +380,8 @@ LanesViterbi(const FsaInfo *__restrict__ infos, int32_t n, const Arc *__restrict
   }
   int32_t other[kDeg], col[kDeg];
   float w[kDeg];
+  int32_t col0 = -1;
+  bool same = true;
 #pragma unroll
   for (int j = 0; j < kDeg; ++j) {
     other[j] = 0;
@@ -387,56 +401,75 @@ LanesViterbi(const FsaInfo *__restrict__ infos, int32_t n, const Arc *__restrict
         if (c >= 0 && c < cols) {
           col[j] = c;
           w[j] = arc.score;
+          if (col0 < 0) col0 = c;
+          else if (c != col0) same = false;
         }
       }
     }
   }
+  if (col0 < 0) col0 = 0;
+  const bool hoist = __all_sync(0xffffffffu, same);
+  const int32_t g_max = __reduce_max_sync(0xffffffffu, G);  // widest lane group of this warp
   // step t (1..Tk) consumes dense row t-1 (forward) or Tk-t (backward)
   const float *base = scores + (int64_t)f.row0 * cols;
-  auto row_of = [&](int32_t step) {
-    step = step > Tk ? Tk : step;
-    return dir == 0 ? step - 1 : Tk - step;
+  auto issue_row = [&](int32_t step, int32_t slot) {
+    if (step <= Tk) {
+      const float *src = base + (int64_t)(dir == 0 ? step - 1 : Tk - step) * cols;
+      float *dst = ring + slot * cols_pad;
+      for (int32_t c = tid; c < cols; c += nt) CpAsync4(dst + c, src + c);
+    }
+    CpAsyncCommit();
   };
-  float x[kDeg][kRegPrefetch];
-#pragma unroll
-  for (int d = 0; d < kRegPrefetch; ++d) {
-    const int32_t r = row_of(1 + d) * cols;
-#pragma unroll
-    for (int j = 0; j < kDeg; ++j) x[j][d] = __ldg(base + r + col[j]);
-  }
+  for (int32_t step = 1; step <= kVitAhead; ++step) issue_row(step, (step - 1) % kVitRing);
   float *grid = (dir == 0 ? fwd : bwd) + f.grid_off;
-  for (int32_t q = tid; q < S; q += blockDim.x) {
+  for (int32_t q = tid; q < S; q += nt) {
     const float v = (dir == 0 ? (q == 0) : (q == S - 1)) ? 0.0f : -INFINITY;
     buf[0][q] = v;
     grid[(int64_t)(dir == 0 ? 0 : Tk) * S + q] = v;
   }
-  for (int32_t t0 = 1; t0 <= Tk; t0 += kRegPrefetch) {
+  const int64_t stride = dir == 0 ? (int64_t)S : -(int64_t)S;
+  float *gout = grid + (dir == 0 ? 1 : Tk - 1) * (int64_t)S + (s >= 0 ? s : 0);
+  const bool writer = s >= 0 && g == 0;
+  for (int32_t t0 = 1; t0 <= Tk; t0 += kVitRing) {
 #pragma unroll
-    for (int u = 0; u < kRegPrefetch; ++u) {
+    for (int u = 0; u < kVitRing; ++u) {
       const int32_t t = t0 + u;
       if (t > Tk) break;
-      __syncthreads();
-      const float *cur = buf[(t - 1) & 1];
+      CpAsyncWait<kVitAhead - 1>();  // this thread's part of row t has landed
+      __syncthreads();               // ... everyone's has; the scores of step t - 1 are complete
+      issue_row(t + kVitAhead, (u + kVitAhead) % kVitRing);
+      const float *cur = buf[u & 1];  // t0 is odd: (t - 1) & 1 == u & 1
+      const float *row = ring + u * cols_pad;
       float best = -INFINITY;
+      if (hoist) {
 #pragma unroll
-      for (int j = 0; j < kDeg; ++j) {
-        const float v = __fadd_rn(__fadd_rn(cur[other[j]], w[j]), x[j][u]);
-        best = v > best ? v : best;
+        for (int j = 0; j < kDeg; ++j) {
+          const float v = __fadd_rn(cur[other[j]], w[j]);
+          best = v > best ? v : best;
+        }
+      } else {
+#pragma unroll
+        for (int j = 0; j < kDeg; ++j) {
+          const float v = __fadd_rn(__fadd_rn(cur[other[j]], w[j]), row[col[j]]);
+          best = v > best ? v : best;
+        }
       }
-      const int32_t r = row_of(t + kRegPrefetch) * cols;
-#pragma unroll
-      for (int j = 0; j < kDeg; ++j) x[j][u] = __ldg(base + r + col[j]);
 #pragma unroll
       for (int32_t d = 16; d > 0; d >>= 1) {
-        const float o = __shfl_down_sync(0xffffffffu, best, d);
-        if (g + d < G) best = o > best ? o : best;
+        if (d < g_max) {  // warp-uniform
+          const float o = __shfl_down_sync(0xffffffffu, best, d);
+          if (g + d < G) best = o > best ? o : best;
+        }
       }
-      if (s >= 0 && g == 0) {
-        buf[t & 1][s] = best;
-        grid[(int64_t)(dir == 0 ? t : Tk - t) * S + s] = best;
+      if (writer) {
+        if (hoist) best = __fadd_rn(best, row[col0]);
+        buf[(u + 1) & 1][s] = best;
+        *gout = best;
       }
+      gout += stride;
     }
   }
+  CpAsyncWait<0>();
 }
 
 int32_t LaunchLanesViterbi(const Layout &L, const k2b200_intersect_args *a,
@@ -444,9 +477,15 @@ int32_t LaunchLanesViterbi(const Layout &L, const k2b200_intersect_args *a,
                            const int32_t *unfit, cudaStream_t stream) {
   (void)L;
   dim3 grid(2, a->num_fsas);
-  { LanesViterbi<kLaneDeg, 4><<<grid, kLaneThreads, 0, stream>>>(
+  const int32_t cols_pad = (a->cols + 3) & ~3;
+  const size_t smem = sizeof(float) * kVitRing * (size_t)cols_pad;
+  K2B_REQUIRE(smem <= 200 * 1024, "too many columns for the lane Viterbi kernel");
+  K2B_CUDA_OK(cudaFuncSetAttribute(LanesViterbi<kLaneDeg>,
+                                   cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  { LanesViterbi<kLaneDeg><<<grid, kLaneThreads, smem, stream>>>(
       d_infos, a->num_fsas, reinterpret_cast<const Arc *>(a->a_arcs), a->a_row_splits2,
-      a->a_in_splits, a->a_in_arcs, a->scores, a->cols, fwd, bwd, plan, unfit); NoteLaunch(); }
+      a->a_in_splits, a->a_in_arcs, a->scores, a->cols, cols_pad, fwd, bwd, plan, unfit);
+    NoteLaunch(); }
   K2B_CUDA_OK(cudaGetLastError());
   return kOk;
 }

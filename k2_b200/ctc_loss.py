@@ -83,11 +83,19 @@ class CtcLoss(nn.Module):
             return loss.mean()
 
 
+_modules = {}
+
+
 def ctc_loss(decoding_graph: Fsa, dense_fsa_vec: DenseFsaVec, output_beam: float = 10,
              delay_penalty: float = 0.0, reduction: str = "sum",
              use_double_scores: bool = True,
              target_lengths: Optional[torch.Tensor] = None) -> torch.Tensor:
-    m = CtcLoss(output_beam=output_beam, reduction=reduction,
-                use_double_scores=use_double_scores)
+    key = (output_beam, reduction, use_double_scores)
+    m = _modules.get(key)
+    if m is None:  # the module has no state beyond its three settings
+        if len(_modules) >= 64:
+            _modules.clear()
+        m = _modules[key] = CtcLoss(output_beam=output_beam, reduction=reduction,
+                                    use_double_scores=use_double_scores)
     return m(decoding_graph=decoding_graph, dense_fsa_vec=dense_fsa_vec,
              delay_penalty=delay_penalty, target_lengths=target_lengths)

@@ -96,13 +96,16 @@ class DenseFsaVec(object):
 
         N, T, C = log_probs.shape
         seg = supervision_segments.numpy().astype(np.int64)
-        assert np.all((seg[:, 0] >= 0) & (seg[:, 0] < N))
-        assert np.all((seg[:, 1] >= 0) & (seg[:, 1] < T))
-        assert np.all(seg[:, 2] >= 0)
-        assert np.all(seg[:, 1] + seg[:, 2] <= T + allow_truncate)
+        num_segs = seg.shape[0]
+        seq, start, end = seg[:, 0], seg[:, 1], seg[:, 1] + seg[:, 2]
+        if num_segs:
+            assert seq.min() >= 0 and seq.max() < N
+            assert start.min() >= 0 and start.max() < T
+            assert seg[:, 2].min() >= 0
+            assert end.max() <= T + allow_truncate
         # durations after truncation; every segment gets one extra (final) row
-        dur = np.minimum(seg[:, 1] + seg[:, 2], T) - seg[:, 1]
-        row_splits = np.zeros(seg.shape[0] + 1, dtype=np.int32)
+        dur = np.minimum(end, T) - start
+        row_splits = np.zeros(num_segs + 1, dtype=np.int32)
         np.cumsum(dur + 1, out=row_splits[1:])
         rows = int(row_splits[-1])
         device = log_probs.device
@@ -110,10 +113,13 @@ class DenseFsaVec(object):
         if log_probs.is_cuda:
             # one kernel writes the whole matrix; two segments that touch the same
             # frame make the backward use atomic adds
-            first = seg[:, 0] * T + seg[:, 1]
-            order = np.argsort(first, kind="stable")
-            overlapping = bool(np.any((first + dur)[order][:-1] > first[order][1:]))
-            eff = np.stack([seg[:, 0], seg[:, 1], dur], axis=1).astype(np.int32)
+            first = seq * T + start
+            if num_segs == 0 or np.bincount(seq, minlength=N).max() <= 1:
+                overlapping = False  # at most one segment per sequence
+            else:
+                order = np.argsort(first, kind="stable")
+                overlapping = bool(np.any((first + dur)[order][:-1] > first[order][1:]))
+            eff = np.stack([seq, start, dur], axis=1).astype(np.int32)
             fn = _LogSoftmaxDenseFunction if _logits else _DenseFsaVecFunction
             # The score matrix, and the device copy of the row splits, are made on first
             # use: a loss that reads the log-probs directly (k2b200_band_loss_*) needs

@@ -37,6 +37,196 @@ def all_reduce_loss(loss_sum: torch.Tensor, num_frames: int, group=None) -> Tupl
     return buf[0], int(round(buf[1].item()))
 
 
+class LossReducer:
+    """The per-step all-reduce of [sum of losses, frames], enqueued by a helper thread.
+
+    Launching a collective costs the host about as much as launching all gradient
+    kernels of a step; when the host is what paces the loop that shows in full.  So
+    `submit` (called as soon as the loss exists) only records an event and hands the
+    job over; the helper thread enqueues the all-reduce on a side stream behind that
+    event while the caller goes on to launch the backward pass, and `result` makes the
+    caller's stream wait for the collective::
+
+        reducer = LossReducer(device)
+        loss = k2.ctc_loss(...)
+        reducer.submit(loss, num_frames)
+        loss.backward()                      # gradient kernels and collective overlap
+        total_loss, total_frames = reducer.result()   # device tensors, no host wait
+
+    The gradient of a summed loss does not depend on the other ranks, so nothing
+    waits for the collective but the consumer of the totals.  On CPU tensors (gloo)
+    the helper thread runs the collective itself."""
+
+    def __init__(self, device, group=None):
+        import queue
+        import threading
+        self.device = torch.device(device)
+        self.group = group
+        self.cuda = self.device.type == "cuda"
+        self.bufs = [torch.zeros(2, dtype=torch.float64, device=self.device) for _ in range(2)]
+        self.unit = torch.tensor([1.0, 0.0], dtype=torch.float64, device=self.device)
+        self.step = 0
+        self.stream = torch.cuda.Stream(self.device) if self.cuda else None
+        self.ready = torch.cuda.Event() if self.cuda else None
+        self.jobs = queue.SimpleQueue()
+        self.done = threading.Event()
+        self.error = None
+        self.pending = False
+        self.thread = threading.Thread(target=self._run, name="k2b200-loss-reducer", daemon=True)
+        self.thread.start()
+
+    def _run(self):
+        import torch.distributed as dist
+        if self.cuda:
+            torch.cuda.set_device(self.device)
+        while True:
+            buf = self.jobs.get()
+            if buf is None:
+                return
+            try:
+                if self.cuda:
+                    self.stream.wait_event(self.ready)
+                    with torch.cuda.stream(self.stream):
+                        dist.all_reduce(buf, group=self.group)
+                else:
+                    dist.all_reduce(buf, group=self.group)
+            except Exception as e:  # handed to the caller by result()
+                self.error = e
+            self.done.set()
+
+    def submit(self, loss_sum: torch.Tensor, num_frames: int) -> None:
+        assert not self.pending, "result() of the previous step has not been taken"
+        buf = self.bufs[self.step & 1]
+        with torch.no_grad():
+            # [loss, 0] then + [0, frames]: two small kernels, no allocation
+            torch.mul(self.unit, loss_sum.detach().reshape(()), out=buf)
+            buf[1] += float(num_frames)
+        if self.cuda:
+            self.ready.record(torch.cuda.current_stream(self.device))
+        self.pending = True
+        self.jobs.put(buf)
+
+    def result(self) -> Tuple[torch.Tensor, torch.Tensor]:
+        """(total loss, total frames) as 0-dim float64 tensors on the device; the current
+        stream waits for the collective, the host only for its launch."""
+        assert self.pending, "nothing submitted"
+        self.done.wait()
+        self.done.clear()
+        self.pending = False
+        if self.error is not None:
+            e, self.error = self.error, None
+            raise e
+        buf = self.bufs[self.step & 1]
+        self.step += 1
+        if self.cuda:
+            torch.cuda.current_stream(self.device).wait_stream(self.stream)
+        return buf[0], buf[1]
+
+    def close(self) -> None:
+        self.jobs.put(None)
+        self.thread.join(timeout=5)
+
+
+class PeerLossReducer:
+    """`LossReducer` over peer memory: one kernel of this library
+    (`k2b200_loss_sum_all_reduce`) sums the rank's losses and exchanges (loss, frames)
+    with the other GPUs of the node by stores into their memory - no collective library
+    on the step, a single launch from the thread that feeds the GPU::
+
+        reducer = PeerLossReducer(device)          # once; the process group is used to
+        ...                                        # exchange the buffers' handles
+        loss = k2.ctc_loss(..., reduction="sum")   # or the per-utterance losses
+        reducer.submit(loss, num_frames)           # side stream, behind the loss
+        loss.backward()
+        total_loss, total_frames = reducer.result()
+
+    All ranks of `group` must be processes of one node, one GPU each."""
+
+    def __init__(self, device, group=None, poll_limit: int = -1):
+        import ctypes
+        import torch.distributed as dist
+        from . import _lib
+        self._lib, self._ct = _lib, ctypes
+        self.device = torch.device(device)
+        self.poll_limit = poll_limit
+        on = dist.is_available() and dist.is_initialized()
+        self.rank = dist.get_rank(group) if on else 0
+        self.world = dist.get_world_size(group) if on else 1
+        with torch.cuda.device(self.device):
+            local = ctypes.c_void_p()
+            handle = ctypes.create_string_buffer(64)
+            _lib.check(_lib.lib.k2b200_peer_reduce_create(ctypes.byref(local), handle))
+            self.local = local.value
+            handles = [None] * self.world
+            if self.world > 1:
+                dist.all_gather_object(handles, bytes(handle.raw), group=group)
+            self.bufs = (ctypes.c_void_p * self.world)()
+            self.opened = []
+            for r in range(self.world):
+                if r == self.rank:
+                    self.bufs[r] = self.local
+                else:
+                    p = ctypes.c_void_p()
+                    _lib.check(_lib.lib.k2b200_peer_reduce_open(handles[r], ctypes.byref(p)))
+                    self.bufs[r] = p.value
+                    self.opened.append(p.value)
+            if self.world > 1:
+                dist.barrier(group=group)  # every rank has mapped every buffer
+        self.stream = torch.cuda.Stream(self.device)
+        self.ready = torch.cuda.Event()
+        self.out = [torch.zeros(2, dtype=torch.float64, device=self.device) for _ in range(2)]
+        self.seq = 0
+        self.pending = False
+
+    def submit(self, losses: torch.Tensor, num_frames: int, sign: float = 1.0) -> None:
+        """losses: a 0-dim or 1-dim float32 / float64 device tensor; its sum times `sign`
+        is this rank's loss."""
+        assert not self.pending, "result() of the previous step has not been taken"
+        losses = losses.detach()
+        assert losses.is_cuda and losses.dtype in (torch.float32, torch.float64)
+        if not losses.is_contiguous():
+            losses = losses.contiguous()
+        self.seq += 1
+        main = torch.cuda.current_stream(self.device)
+        self.ready.record(main)
+        self.stream.wait_event(self.ready)
+        losses.record_stream(self.stream)
+        with torch.cuda.device(self.device):
+            self._lib.check(self._lib.lib.k2b200_loss_sum_all_reduce(
+                losses.data_ptr(), losses.numel(), int(losses.dtype == torch.float32),
+                float(sign), float(num_frames), self.bufs, self.rank, self.world, self.seq,
+                self.poll_limit, self.out[self.seq & 1].data_ptr(), self.stream.cuda_stream))
+        self.pending = True
+
+    def result(self) -> Tuple[torch.Tensor, torch.Tensor]:
+        """(total loss, total frames), 0-dim float64 device tensors; the current stream
+        waits for the exchange, the host does not."""
+        assert self.pending, "nothing submitted"
+        self.pending = False
+        torch.cuda.current_stream(self.device).wait_stream(self.stream)
+        out = self.out[self.seq & 1]
+        return out[0], out[1]
+
+    def status(self) -> int:
+        """Waits for the exchange stream; bit 0 = a bounded wait for a peer gave up (the
+        totals of that step are invalid)."""
+        st = self._ct.c_int32()
+        with torch.cuda.device(self.device):
+            self._lib.check(self._lib.lib.k2b200_peer_reduce_status(
+                self.local, self.stream.cuda_stream, self._ct.byref(st)))
+        return st.value
+
+    def close(self) -> None:
+        with torch.cuda.device(self.device):
+            torch.cuda.synchronize(self.device)
+            for p in self.opened:
+                self._lib.check(self._lib.lib.k2b200_peer_reduce_close(p))
+            self.opened = []
+            if self.local:
+                self._lib.check(self._lib.lib.k2b200_peer_reduce_destroy(self.local))
+                self.local = None
+
+
 class HostPrefetcher:
     """Double-buffered host -> device input pipeline for a training loop: the copy
     of batch k+1 (from pinned host memory, on its own stream) runs while batch k is

@@ -130,3 +130,31 @@ def test_a_rank_that_dies_before_the_all_reduce_gives_an_error_not_a_hang(tmp_pa
     outcome, seconds = open(tmp_path / "outcome.txt").read().split()
     assert outcome.startswith("error:"), outcome
     assert float(seconds) < 60
+
+
+def _reducer_worker(rank, world, port, out_dir):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    from k2_b200 import parallel
+    reducer = parallel.LossReducer("cpu")
+    got = []
+    for step in range(3):
+        loss = torch.tensor(float(10 * step + rank + 1))
+        reducer.submit(loss, 100 * (rank + 1) + step)
+        tot_loss, tot_frames = reducer.result()
+        got += [float(tot_loss), float(tot_frames)]
+    reducer.close()
+    np.save(os.path.join(out_dir, f"q{rank}.npy"), np.array(got))
+    dist.destroy_process_group()
+
+
+def test_loss_reducer_thread(tmp_path):
+    """The helper-thread all-reduce gives every rank the totals of every step."""
+    port = _free_port()
+    mp.spawn(_reducer_worker, args=(2, port, str(tmp_path)), nprocs=2, join=True)
+    r0, r1 = np.load(tmp_path / "q0.npy"), np.load(tmp_path / "q1.npy")
+    want = []
+    for step in range(3):
+        want += [float(20 * step + 3), float(300 + 2 * step)]
+    assert r0.tolist() == r1.tolist() == want
