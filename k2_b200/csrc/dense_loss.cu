@@ -409,9 +409,11 @@ GridChainLanes(const FsaInfo *__restrict__ infos, int32_t n, const Arc *__restri
 // scores of its rows in shared memory.  Also enforces kMinDenseScore (on every finite
 // element of the rows, a little stricter than on surviving arcs only).
 // ---------------------------------------------------------------------------
-constexpr int kMaskRows = 32;  // rows per CTA
-
-template <int kDeg>
+// The state pitch of the staged scores and the rows per CTA are compile-time, and the row loop
+// is unrolled, so the score of an arc's other end is one load at (byte offset of that state,
+// fixed for the call) + constant.  Walking forward in a graph where every state has one
+// entering label the dense score of a lane's arcs is one load per row.
+template <int kDeg, int kSPad, int kMaskRows>
 __global__ void __launch_bounds__(kLaneThreads)
 ArcMasks(const FsaInfo *__restrict__ infos, int32_t n, int64_t total_levels,
          const Arc *__restrict__ arcs, const int32_t *__restrict__ a_row_splits2,
@@ -419,8 +421,9 @@ ArcMasks(const FsaInfo *__restrict__ infos, int32_t n, int64_t total_levels,
          const unsigned char *__restrict__ dense, DensePack dp,
          const float *__restrict__ vfwd, const float *__restrict__ vbwd,
          const float *__restrict__ cutoffs, const int32_t *__restrict__ plan,
-         int32_t *__restrict__ unfit, unsigned char *__restrict__ masks, int32_t s_pad) {
+         int32_t *__restrict__ unfit, unsigned char *__restrict__ masks) {
   static_assert(kDeg <= 8, "one byte per lane");
+  constexpr int32_t s_pad = kSPad;
   extern __shared__ __align__(16) unsigned char smem_raw[];
   const int32_t i = blockIdx.y, dir = blockIdx.z;
   if (unfit[i] & 1) return;
@@ -463,11 +466,15 @@ ArcMasks(const FsaInfo *__restrict__ infos, int32_t n, int64_t total_levels,
       G = code >> 24;
     }
   }
-  int32_t other_col[kDeg];
+  // byte offsets of an arc's other end in a level of staged scores and of its column in a row
+  uint32_t other_off[kDeg], col_off[kDeg];
   float w[kDeg];
+  int32_t col0 = -1;
+  bool same = true;
 #pragma unroll
   for (int j = 0; j < kDeg; ++j) {
-    other_col[j] = cols << 16;
+    other_off[j] = 0;
+    col_off[j] = 0;
     w[j] = -INFINITY;
   }
   if (s >= 0) {
@@ -480,41 +487,67 @@ ArcMasks(const FsaInfo *__restrict__ infos, int32_t n, int64_t total_levels,
         const Arc arc = arcs[dir == 0 ? in_arcs[k] : k];
         const int32_t c = arc.label + 1;
         if (c >= 0 && c < cols && arc.score != -INFINITY) {
-          other_col[j] = (dir == 0 ? arc.src : arc.dest) | (c << 16);
+          other_off[j] = 4u * (uint32_t)(dir == 0 ? arc.src : arc.dest);
+          col_off[j] = 4u * (uint32_t)c;
           w[j] = arc.score;
+          if (col0 < 0) col0 = c;
+          else if (c != col0) same = false;
         }
       }
     }
   }
+  const bool hoist = __all_sync(0xffffffffu, same);
+  const uint32_t col0_off = 4u * (uint32_t)(col0 < 0 ? 0 : col0);
   __syncthreads();
-  // slots that no lane of this warp uses are skipped (lanes of a warp hold states of
-  // similar degree)
-  uint32_t used = 0;
+  // (a slot without an arc has w = -inf: it fails the test like any pruned arc)
+  unsigned char *out = masks + ((int64_t)dir * total_levels + f.level_off + r0) * kLaneThreads + tid;
+  const int32_t s_ld = s >= 0 ? s : 0;
+  // dir 0: arcs from level k into level k + 1 (own); dir 1: from level k (own) to k + 1
+  const float *own_p = (dir == 0 ? bo + s_pad : fo) + s_ld;
+  const unsigned char *oth_p = reinterpret_cast<const unsigned char *>(dir == 0 ? fo : bo + s_pad);
+  const unsigned char *lp_p = reinterpret_cast<const unsigned char *>(lp);
+  const uint32_t lp_stride = 4u * (uint32_t)dp.cols4;
+  auto at = [](const unsigned char *base, uint32_t off) {
+    return *reinterpret_cast<const float *>(base + off);
+  };
+  constexpr int kUnroll = 4;
+  static_assert(kMaskRows % kUnroll == 0, "rows per CTA");
+  for (int32_t k0 = 0; k0 < nf; k0 += kUnroll) {
 #pragma unroll
-  for (int j = 0; j < kDeg; ++j)
-    if (__any_sync(0xffffffffu, w[j] != -INFINITY)) used |= 1u << j;
-  unsigned char *out = masks + ((int64_t)dir * total_levels + f.level_off + r0) * kLaneThreads;
-  for (int32_t k = 0; k < nf; ++k) {
-    uint32_t bits = 0;
-    if (s >= 0) {
-      // dir 0: arcs from level k into level k + 1 (own); dir 1: from level k (own) to k + 1
-      const float own = dir == 0 ? bo[(k + 1) * s_pad + s] : fo[k * s_pad + s];
+    for (int u = 0; u < kUnroll; ++u) {
+      if (k0 + u >= nf) break;
+      uint32_t bits = 0;
+      const float own = s >= 0 ? own_p[u * s_pad] : -INFINITY;
       if (own != -INFINITY) {
-        const float *oth = dir == 0 ? fo + k * s_pad : bo + (k + 1) * s_pad;
-        const float *lprow = lp + k * dp.cols4;
+        const unsigned char *oth = oth_p + u * (4 * s_pad);
+        const unsigned char *lprow = lp_p + u * lp_stride;
+        if (hoist) {
+          const float x = at(lprow, col0_off);
 #pragma unroll
-        for (int j = 0; j < kDeg; ++j) {
-          if (!(used & (1u << j))) continue;  // warp-uniform
-          const int32_t o_idx = other_col[j] & 0xffff, c = other_col[j] >> 16;
-          const float sc = __fadd_rn(w[j], lprow[c]);
-          const float o = oth[o_idx];
-          const float through = dir == 0 ? __fadd_rn(__fadd_rn(o, sc), own)
-                                         : __fadd_rn(__fadd_rn(own, sc), o);
-          if (through > cutoff) bits |= 1u << j;
+          for (int j = 0; j < kDeg; ++j) {
+            const float sc = __fadd_rn(w[j], x);
+            const float o = at(oth, other_off[j]);
+            const float through = dir == 0 ? __fadd_rn(__fadd_rn(o, sc), own)
+                                           : __fadd_rn(__fadd_rn(own, sc), o);
+            if (through > cutoff) bits |= 1u << j;
+          }
+        } else {
+#pragma unroll
+          for (int j = 0; j < kDeg; ++j) {
+            const float sc = __fadd_rn(w[j], at(lprow, col_off[j]));
+            const float o = at(oth, other_off[j]);
+            const float through = dir == 0 ? __fadd_rn(__fadd_rn(o, sc), own)
+                                           : __fadd_rn(__fadd_rn(own, sc), o);
+            if (through > cutoff) bits |= 1u << j;
+          }
         }
       }
+      out[(int64_t)u * kLaneThreads] = (unsigned char)bits;
     }
-    out[(int64_t)k * kLaneThreads + tid] = (unsigned char)bits;
+    own_p += kUnroll * s_pad;
+    oth_p += kUnroll * 4 * s_pad;
+    lp_p += kUnroll * lp_stride;
+    out += (int64_t)kUnroll * kLaneThreads;
   }
   if (__syncthreads_or(risky) && tid == 0) atomicOr(&unfit[i], 2);
 }
@@ -1647,16 +1680,25 @@ static int32_t LaunchChainMasked(const LossLayout &LL, const k2b200_intersect_ar
   int32_t *unfit = reinterpret_cast<int32_t *>(ws + L.off_unfit);
   unsigned char *masks = reinterpret_cast<unsigned char *>(ws + LL.off_masks);
   {
-    const size_t smem = sizeof(float) * ((size_t)2 * (kMaskRows + 1) * s_pad +
-                                         (size_t)kMaskRows * LL.pack.cols4);
-    K2B_REQUIRE(smem <= kChainSmemBudget, "too many columns for the fused loss path");
-    K2B_CUDA_OK(cudaFuncSetAttribute(ArcMasks<kLaneDeg>,
-                                     cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    dim3 grid(CeilDiv(L.max_tk + 1, kMaskRows), args->num_fsas, 2);
-    { ArcMasks<kLaneDeg><<<grid, kLaneThreads, smem, stream>>>(
-        d_infos, args->num_fsas, L.total_levels, arcs, args->a_row_splits2, args->a_in_splits,
-        args->a_in_arcs, dense, LL.pack, fwd, bwd, cutoffs, plan, unfit, masks, s_pad);
-      NoteLaunch(); }
+#define K2B_ARC_MASKS(SPAD, ROWS)                                                              \
+    {                                                                                          \
+      const size_t smem = sizeof(float) * ((size_t)2 * ((ROWS) + 1) * (SPAD) +                 \
+                                           (size_t)(ROWS) * LL.pack.cols4);                    \
+      K2B_REQUIRE(smem <= kChainSmemBudget, "too many columns for the fused loss path");       \
+      K2B_CUDA_OK(cudaFuncSetAttribute(ArcMasks<kLaneDeg, SPAD, ROWS>,                         \
+                                       cudaFuncAttributeMaxDynamicSharedMemorySize,            \
+                                       (int)smem));                                            \
+      dim3 grid(CeilDiv(L.max_tk + 1, (ROWS)), args->num_fsas, 2);                             \
+      { ArcMasks<kLaneDeg, SPAD, ROWS><<<grid, kLaneThreads, smem, stream>>>(                  \
+          d_infos, args->num_fsas, L.total_levels, arcs, args->a_row_splits2,                  \
+          args->a_in_splits, args->a_in_arcs, dense, LL.pack, fwd, bwd, cutoffs, plan, unfit,  \
+          masks); NoteLaunch(); }                                                              \
+    }
+    // state pitch of the staged Viterbi scores, in three sizes
+    if (L.max_states <= 192) K2B_ARC_MASKS(192, 32)
+    else if (L.max_states <= 384) K2B_ARC_MASKS(384, 32)
+    else K2B_ARC_MASKS(768, 16)
+#undef K2B_ARC_MASKS
   }
   {
     constexpr int kU = kChainGroup;
@@ -1863,17 +1905,18 @@ int32_t k2b200_dense_loss_forward(const k2b200_intersect_args *args, void *works
   K2B_FORWARD(SideFork(stream, &side));
   join_guard.armed = true;
   K2B_FORWARD(LaunchPlanLanes(L, args, ws, stream));
-  // the label of every state and whether a state has one (for the backward pass)
-  K2B_CUDA_OK(cudaMemsetAsync(ws + LL.off_one_label, 0xff, sizeof(int32_t), stream));
-  if (args->num_states > 0)
-    { StateInLabels<<<CeilDiv(args->num_states, 256), 256, 0, stream>>>(
-        reinterpret_cast<const Arc *>(args->a_arcs), args->a_in_splits, args->a_in_arcs,
-        args->num_states, reinterpret_cast<int32_t *>(ws + LL.off_state_label),
-        reinterpret_cast<int32_t *>(ws + LL.off_one_label)); NoteLaunch(); }
   {
     PhaseTimer timer(kPhaseViterbi, stream);
     K2B_FORWARD(RunViterbi(L, args, ws, stream, /*plan_ready=*/true));
   }
+  // the label of every state and whether a state has one (for the backward pass): beside
+  // the Viterbi kernels, like the repacking
+  K2B_CUDA_OK(cudaMemsetAsync(ws + LL.off_one_label, 0xff, sizeof(int32_t), side));
+  if (args->num_states > 0)
+    { StateInLabels<<<CeilDiv(args->num_states, 256), 256, 0, side>>>(
+        reinterpret_cast<const Arc *>(args->a_arcs), args->a_in_splits, args->a_in_arcs,
+        args->num_states, reinterpret_cast<int32_t *>(ws + LL.off_state_label),
+        reinterpret_cast<int32_t *>(ws + LL.off_one_label)); NoteLaunch(); }
   {
     PhaseTimer timer(kPhaseDense, side);  // repacking belongs with the dense matrix
     const int64_t n_dense = (int64_t)args->rows * LL.pack.cols4;
