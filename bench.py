@@ -296,8 +296,9 @@ def workload_config(w, args):
     return {"workload": w.name, "utterances": int(w.log_probs.shape[0]),
             "max_frames": int(w.log_probs.shape[1]), "classes": int(w.log_probs.shape[2]),
             "frames": w.num_frames, "output_beam": w.output_beam, "scale": args.scale,
-            "l2": "working set per step (~650 MB: log-probs, score matrix, both gradients, "
-                  "Viterbi grids) exceeds the 126 MB L2; no explicit flush"}
+            "l2": "inputs larger than L2: a step touches the log-probs and their gradient "
+                  "(128 MB each at ctc_large), the two Viterbi grids and the lists of surviving "
+                  "states, several times the 126 MB L2; no explicit flush"}
 
 
 # --------------------------------------------------------------------------- GPU arm
@@ -319,10 +320,16 @@ def implementation_bytes(phase, kernel, frames, N, T, C, A, A_out, S_out, grid_s
     table = {
         # every row by both directions, both grids written
         "BandViterbi": 2 * 4 * R * C + 8 * grid_states,
-        # both grids read once (plus one row in sixteen again), the lists written
-        "BandPrep": int(8 * grid_states * 17 / 16) + 16 * S_out + 32 * S_out,
-        "BandChain": 2 * 16 * S_out + 2 * 12 * S_out,
-        "BandGrad": (16 + 24) * S_out + 32 * S_out,
+        # BandKeep reads both grids and writes 64 bytes of keep bits per level; BandPrep reads
+        # them back, per surviving state two table entries and five grid values, and writes a
+        # list entry (8 bytes) and a factor record (32 bytes) per entry of the padded lists
+        # (at least 32 entries per level)
+        "BandKeep+BandPrep": 8 * grid_states + 128 * (R + 2 * N) + 84 * S_out +
+                             40 * max(S_out, 32 * (R + 2 * N)),
+        # both directions read the factor records and write a value per padded entry
+        "BandChainLists": 2 * 40 * max(S_out, 32 * (R + 2 * N)),
+        # list entry, alpha and beta per surviving state, a gradient element per (frame, label)
+        "BandGrad": 24 * S_out + 4 * S_out,
         "RegisterViterbi": 2 * 4 * R * C + 8 * grid_states,
         "LanesViterbi": 2 * 4 * R * C + 8 * grid_states,
         "GridChainLanes": 2 * 12 * R * C + 16 * grid_states + 32 * S_out,
@@ -649,7 +656,8 @@ def run_ours(args):
 
 
 # ncu dram__bytes_read.sum + dram__bytes_write.sum of one launch on ctc_large (profiles/)
-NCU_TRAFFIC = {"GridChainLanes": 928.2e6, "RegisterViterbi": 282.4e6, "ProbScoresStaged": 96.4e6}
+NCU_TRAFFIC = {"BandViterbi": 289.0e6, "BandKeep+BandPrep": 295.8e6, "BandChainLists": 99.1e6,
+               "BandGrad": 78.1e6}
 
 
 # --------------------------------------------------------------------------- decoding

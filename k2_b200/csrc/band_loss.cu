@@ -467,19 +467,21 @@ BandViterbi(const BandInfo *__restrict__ infos, const BandState *__restrict__ ta
 // ---------------------------------------------------------------------------
 // Which states survive (intersect_dense.cu:289-296): state s of level l is kept iff
 // vf[l][s] + vb[l][s] > cutoff.  grid = (level chunks, pairs), a warp per kKeepLevels levels;
-// lane j looks at states 16 j .. 16 j + 15 and writes their keep bits as one 16-bit word,
-// keep[(level_off + l) * 32 + j].  totals[0] += surviving states, totals[2] += the arcs
+// lane j looks at states K j .. K j + K - 1 (K = 16, or 8 when no graph has more than 256
+// states, which keeps more lanes busy) and writes their keep bits: bit (s & 15) of the 16-bit
+// word keep[(level_off + l) * 32 + s / 16] is the bit of state s.  totals[0] += surviving states, totals[2] += the arcs
 // leaving them: the sizes the beam reduction looks at (intersect_dense.cu:289-320), which
 // the host can read while the kernels behind this one run.
 // ---------------------------------------------------------------------------
 constexpr int kKeepLevels = 8;
 
+template <int K>
 __global__ void __launch_bounds__(128)
 BandKeep(const BandInfo *__restrict__ infos, const int32_t *__restrict__ a_row_splits2,
          const float *__restrict__ vf, const float *__restrict__ vb, float beam,
          uint16_t *__restrict__ keep_bits, float *__restrict__ cutoffs,
          unsigned long long *__restrict__ totals) {
-  constexpr int K = kPrepK;
+  static_assert(K == 8 || K == 16, "keep bits are stored as bytes or 16-bit words");
   constexpr unsigned kAll = 0xffffffffu;
   const int32_t i = blockIdx.y;
   const BandInfo f = infos[i];
@@ -511,7 +513,13 @@ BandKeep(const BandInfo *__restrict__ infos, const int32_t *__restrict__ a_row_s
       if (__fadd_rn(F.z, B.z) > cutoff) keep |= 4u << (4 * c);
       if (__fadd_rn(F.w, B.w) > cutoff) keep |= 8u << (4 * c);
     }
-    keep_bits[(int64_t)(f.level_off + l) * 32 + lane] = (uint16_t)keep;
+    if (K == 16) {
+      keep_bits[(int64_t)(f.level_off + l) * 32 + lane] = (uint16_t)keep;
+    } else {  // the same layout byte by byte; states 256 .. 511 do not exist
+      unsigned char *row = reinterpret_cast<unsigned char *>(keep_bits + (int64_t)(f.level_off + l) * 32);
+      row[lane] = (unsigned char)keep;
+      row[32 + lane] = 0;
+    }
     n_states += __popc(keep);
     for (uint32_t m = keep; m; m &= m - 1) {
       const int32_t idx = f.state_off + s0 + __ffs(m) - 1;
@@ -1606,13 +1614,16 @@ int32_t k2b200_band_loss_forward(const k2b200_band_loss_args *args, void *worksp
       PhaseTimer timer(kPhasePrune, stream);
       NotePhaseKernel(kPhasePrune, "BandKeep+BandPrep");
       dim3 kgrid(CeilDiv(L.max_frames + 2, 4 * kKeepLevels), args->num_fsas);
-      { BandKeep<<<kgrid, 128, 0, stream>>>(
-          reinterpret_cast<const BandInfo *>(ws + L.off_infos), args->a_row_splits2,
-          reinterpret_cast<const float *>(ws + L.off_vf),
-          reinterpret_cast<const float *>(ws + L.off_vb), beam,
-          reinterpret_cast<uint16_t *>(ws + L.off_keep),
-          reinterpret_cast<float *>(ws + L.off_cutoffs),
+#define K2B_BAND_KEEP(KK)                                                                   \
+      { BandKeep<KK><<<kgrid, 128, 0, stream>>>(                                                \
+          reinterpret_cast<const BandInfo *>(ws + L.off_infos), args->a_row_splits2,            \
+          reinterpret_cast<const float *>(ws + L.off_vf),                                       \
+          reinterpret_cast<const float *>(ws + L.off_vb), beam,                                 \
+          reinterpret_cast<uint16_t *>(ws + L.off_keep),                                        \
+          reinterpret_cast<float *>(ws + L.off_cutoffs),                                        \
           reinterpret_cast<unsigned long long *>(ws + L.off_totals)); NoteLaunch(); }
+      if (L.max_states <= 256) K2B_BAND_KEEP(8) else K2B_BAND_KEEP(kPrepK)
+#undef K2B_BAND_KEEP
       // the host reads the counts behind BandKeep, while what follows runs
       if (need_count) K2B_FORWARD(SideFork(stream, &side));
       dim3 grid(CeilDiv(L.max_frames + 2, 4 * kPrepLevels), args->num_fsas);
