@@ -64,7 +64,6 @@ constexpr int32_t kStatusNotBand = 1, kStatusLate = 2;
 // bits of unfit[i]: the lean recursion cannot represent this graph's numbers
 constexpr int32_t kUnfitFactors = 1, kUnfitRange = 2;
 
-static int32_t g_wait_limit = 4000000;  // polls of an mbarrier before a kernel gives up
 
 // Per (graph, sequence) pair; built on the host, uploaded once per call.
 struct BandInfo {
@@ -1505,12 +1504,12 @@ static int32_t LaunchBandChains(const BandLayout &L, const k2b200_band_loss_args
       reinterpret_cast<const int32_t *>(ws + L.off_chunk_r), am, bm,
       reinterpret_cast<int32_t *>(ws + L.off_a_scale),
       reinterpret_cast<int32_t *>(ws + L.off_b_scale), tot_scores, total, unfit, status,
-      g_wait_limit); NoteLaunch(); }
+      CopyWaitLimit()); NoteLaunch(); }
   { BandChainExact<<<grid, 32, L.exact_smem, stream>>>(
       infos, reinterpret_cast<const BandArc *>(args->band_arcs), args->log_probs,
       args->num_classes, items, lists, am, reinterpret_cast<int32_t *>(ws + L.off_ae), bm,
       reinterpret_cast<int32_t *>(ws + L.off_be), tot_scores, total, unfit, status, L.st_pad,
-      L.lv_pad, g_wait_limit); NoteLaunch(); }
+      L.lv_pad, CopyWaitLimit()); NoteLaunch(); }
   K2B_CUDA_OK(cudaGetLastError());
   return kOk;
 }
@@ -1521,7 +1520,7 @@ using namespace k2b;
 
 extern "C" {
 
-void k2b200_debug_set_copy_wait_limit(int32_t polls) { g_wait_limit = polls < 0 ? 4000000 : polls; }
+void k2b200_debug_set_copy_wait_limit(int32_t polls) { SetCopyWaitLimit(polls); }
 
 int32_t k2b200_band_tables_bytes(int32_t num_states, size_t *states_bytes, size_t *arcs_bytes) {
   K2B_REQUIRE(states_bytes && arcs_bytes, "NULL output pointer");
@@ -1597,7 +1596,7 @@ int32_t k2b200_band_loss_forward(const k2b200_band_loss_args *args, void *worksp
         reinterpret_cast<const BandState *>(args->band_states), args->log_probs,
         args->num_classes, reinterpret_cast<float *>(ws + L.off_vf),
         reinterpret_cast<float *>(ws + L.off_vb), L.vit_frames, L.vit_batches, L.xch_pad,
-        g_wait_limit, reinterpret_cast<int32_t *>(ws + L.off_status)); NoteLaunch(); }
+        CopyWaitLimit(), reinterpret_cast<int32_t *>(ws + L.off_status)); NoteLaunch(); }
     K2B_CUDA_OK(cudaGetLastError());
   }
   // The lattice is never built, but its size still decides the beam

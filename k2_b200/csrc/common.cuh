@@ -62,6 +62,10 @@ long long LaunchCount();
 // Name of the kernel(s) that last ran under a phase, for whoever reads the phase times.
 void NotePhaseKernel(int phase, const char *name);
 const char *PhaseKernel(int phase);
+// Polls of an mbarrier before a kernel's wait for a copy gives up (a test hook lowers it:
+// k2b200_debug_set_copy_wait_limit).
+int32_t CopyWaitLimit();
+void SetCopyWaitLimit(int32_t polls);
 void SetProfiling(bool on);
 double ReadPhase(int phase, long long *count);
 struct PhaseTimer {  // records start/stop events when profiling is enabled

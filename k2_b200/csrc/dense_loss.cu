@@ -177,7 +177,7 @@ GridChainLanes(const FsaInfo *__restrict__ infos, int32_t n, const Arc *__restri
                const float *__restrict__ cutoffs, ProbState *__restrict__ alpha,
                ProbState *__restrict__ beta, double *__restrict__ tot,
                int32_t *__restrict__ unfit, const int32_t *__restrict__ low_flag,
-               LaneSmem sm) {
+               LaneSmem sm, int32_t wait_limit) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   __shared__ __align__(8) uint64_t full[kU];
   __shared__ int32_t emax;  // largest exponent among the values of a group's last level
@@ -299,15 +299,17 @@ GridChainLanes(const FsaInfo *__restrict__ infos, int32_t n, const Arc *__restri
   int32_t skip = (int32_t)(((reinterpret_cast<uintptr_t>(fgrid) >> 2) + (uintptr_t)(first * S)) & 3);
   const int32_t skip_step = (int32_t)(step_stride & 3);
   bool gave_up = false;
+  int32_t t_fail = 0;
   for (int32_t t0 = 1; t0 <= Tk && !gave_up; t0 += kU) {
 #pragma unroll
     for (int u = 0; u < kU; ++u) {
       const int32_t t = t0 + u;
       if (t > Tk) break;
-      const bool late = !MbarTryWait(&full[u], parity) && !MbarWaitBounded(&full[u], parity);
+      const bool late = !MbarTryWait(&full[u], parity) && !MbarWaitBounded(&full[u], parity, wait_limit);
       // the previous frame is complete; nobody reads its ring slot any more
       if (__syncthreads_or(late)) {  // uniform
         gave_up = true;
+        t_fail = t;
         break;
       }
       if (producer) {
@@ -380,9 +382,10 @@ GridChainLanes(const FsaInfo *__restrict__ infos, int32_t n, const Arc *__restri
   if (gave_up) {
     if (tid == 0) {
       atomicOr(&unfit[i], 2);
-      // copies may still be in flight towards this CTA's shared memory: give them
-      // a bounded while before the CTA retires
-      for (int k = 0; k < 1000; ++k) __nanosleep(1000);
+      // copies may still be in flight towards this CTA's shared memory (the rows of steps
+      // t_fail .. t_fail + kU - 2): wait for each, with a limit, before the CTA retires
+      for (int32_t k = t_fail; k <= min(t_fail + kU - 2, Tk); ++k)
+        MbarWaitBounded(&full[(k - 1) % kU], (unsigned)((k - 1) / kU) & 1u);
     }
     __syncthreads();
     return;
@@ -574,7 +577,7 @@ GridChainMasked(const FsaInfo *__restrict__ infos, int32_t n, int64_t total_leve
                 const float *__restrict__ vbwd, const float *__restrict__ cutoffs,
                 ProbState *__restrict__ alpha, ProbState *__restrict__ beta,
                 double *__restrict__ tot, const int32_t *__restrict__ plan,
-                int32_t *__restrict__ unfit, int32_t s_pad) {
+                int32_t *__restrict__ unfit, int32_t s_pad, int32_t wait_limit) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   __shared__ __align__(8) uint64_t full[kU];
   __shared__ int32_t emax;
@@ -685,14 +688,16 @@ GridChainMasked(const FsaInfo *__restrict__ infos, int32_t n, int64_t total_leve
   int32_t K = 0;
   unsigned parity = 0;
   bool gave_up = false;
+  int32_t t_fail = 0;
   for (int32_t t0 = 1; t0 <= Tk && !gave_up; t0 += kU) {
 #pragma unroll
     for (int u = 0; u < kU; ++u) {
       const int32_t t = t0 + u;
       if (t > Tk) break;
-      const bool late = !MbarTryWait(&full[u], parity) && !MbarWaitBounded(&full[u], parity);
+      const bool late = !MbarTryWait(&full[u], parity) && !MbarWaitBounded(&full[u], parity, wait_limit);
       if (__syncthreads_or(late)) {  // uniform
         gave_up = true;
+        t_fail = t;
         break;
       }
       if (tid == 0) {
@@ -767,7 +772,9 @@ GridChainMasked(const FsaInfo *__restrict__ infos, int32_t n, int64_t total_leve
   if (gave_up) {
     if (tid == 0) {
       atomicOr(&unfit[i], 2);
-      for (int k = 0; k < 1000; ++k) __nanosleep(1000);  // copies still in flight
+      // the copies still in flight (steps t_fail .. t_fail + kU - 2) land before the CTA retires
+      for (int32_t k = t_fail; k <= min(t_fail + kU - 2, Tk); ++k)
+        MbarWaitBounded(&full[(k - 1) % kU], (unsigned)((k - 1) / kU) & 1u);
     }
     __syncthreads();
     return;
@@ -1660,7 +1667,7 @@ static int32_t LaunchChainLanes(const LossLayout &LL, const k2b200_intersect_arg
       reinterpret_cast<ProbState *>(ws + LL.off_alpha),
       reinterpret_cast<ProbState *>(ws + LL.off_beta), tot,
       reinterpret_cast<int32_t *>(ws + L.off_unfit),
-      reinterpret_cast<const int32_t *>(ws + LL.off_flags), ls); NoteLaunch(); }
+      reinterpret_cast<const int32_t *>(ws + LL.off_flags), ls, CopyWaitLimit()); NoteLaunch(); }
   K2B_CUDA_OK(cudaGetLastError());
   return kOk;
 }
@@ -1716,14 +1723,15 @@ static int32_t LaunchChainMasked(const LossLayout &LL, const k2b200_intersect_ar
           d_infos, args->num_fsas, L.total_levels, arcs, args->a_row_splits2,                 \
           args->a_in_splits, args->a_in_arcs, dense, LL.pack, masks, fwd, bwd, cutoffs,       \
           reinterpret_cast<ProbState *>(ws + LL.off_alpha),                                   \
-          reinterpret_cast<ProbState *>(ws + LL.off_beta), tot, plan, unfit, s_pad);          \
+          reinterpret_cast<ProbState *>(ws + LL.off_beta), tot, plan, unfit, s_pad,           \
+          CopyWaitLimit());                                                                   \
         NoteLaunch(); }                                                                       \
     }
     // room for the exp() part of a dense row, in four sizes
     if (p_bytes <= 768) K2B_CHAIN_MASKED(768)
     else if (p_bytes <= 2048) K2B_CHAIN_MASKED(2048)
     else if (p_bytes <= 8192) K2B_CHAIN_MASKED(8192)
-    else K2B_CHAIN_MASKED(35840)
+    else K2B_CHAIN_MASKED(33792)
 #undef K2B_CHAIN_MASKED
   }
   K2B_CUDA_OK(cudaGetLastError());

@@ -33,6 +33,12 @@ static std::atomic<long long> g_launches{0};
 void NoteLaunch(int n) { g_launches.fetch_add(n, std::memory_order_relaxed); }
 long long LaunchCount() { return g_launches.load(std::memory_order_relaxed); }
 
+static std::atomic<int32_t> g_copy_wait_limit{4000000};
+int32_t CopyWaitLimit() { return g_copy_wait_limit.load(std::memory_order_relaxed); }
+void SetCopyWaitLimit(int32_t polls) {
+  g_copy_wait_limit.store(polls < 0 ? 4000000 : polls, std::memory_order_relaxed);
+}
+
 static const char *g_phase_kernel[kNumPhases] = {};
 void NotePhaseKernel(int phase, const char *name) {
   if (phase >= 0 && phase < kNumPhases) g_phase_kernel[phase] = name;

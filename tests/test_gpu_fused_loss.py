@@ -192,6 +192,24 @@ def _star_graph(rng, fan, tail_states, num_labels):
     return rows, final + 1
 
 
+def _stars(rng, fans):
+    """An FsaVec of star graphs, one per entry of `fans`."""
+    from oracle.common import HostFsaVec, make_arcs
+    rs1, rs2, arcs = [0], [0], []
+    for fan in fans:
+        rows, ns = _star_graph(rng, fan, 6, 5)
+        base = len(arcs)
+        src = np.array([r[0] for r in rows])
+        for s in range(ns):
+            rs2.append(base + int(np.sum(src <= s)))
+        arcs.extend(rows)
+        rs1.append(rs1[-1] + ns)
+    r = np.array(arcs, dtype=np.float64)
+    return HostFsaVec(np.asarray(rs1, np.int32), np.asarray(rs2, np.int32),
+                      make_arcs(r[:, 0].astype(np.int32), r[:, 1].astype(np.int32),
+                                r[:, 2].astype(np.int32), r[:, 3].astype(np.float32)))
+
+
 def test_graphs_a_plan_cannot_place_take_the_fallback_kernels():
     # one graph with a 300-arc state (no lane plan possible: > 32 lanes of 8 arcs)
     # next to ordinary ones: plan-less graphs go through PersistentViterbi, GridChain
@@ -272,3 +290,26 @@ def test_gradient_goes_straight_to_the_log_probs():
     lp = lp0.clone().to(DEV).requires_grad_(True)
     over = k2.DenseFsaVec(lp, torch.tensor([[0, 0, 20], [0, 10, 13]], dtype=torch.int32))
     assert over._source is None
+
+
+def test_bounded_waits_of_the_lane_kernels_expire_and_the_fallback_takes_over():
+    """With a poll limit of 0 the waits of GridChainLanes / GridChainMasked for their row
+    copies run out: they flag the graph and return (nothing traps or hangs), the
+    shared-memory fallback launched behind them recomputes it, and totals and gradients
+    are the oracle's - for graphs on identity lanes and for graphs on a lane plan."""
+    from k2_b200 import _lib
+    rng = np.random.default_rng(77)
+    cases = []
+    for trial in range(4):  # degree <= 4: identity lanes (GridChainLanes)
+        n = int(rng.integers(1, 4))
+        cases.append((random_fsa_vec(rng, n, acyclic=bool(trial % 2)),) + random_dense(rng, n, 12, 5))
+    # states of 12 and 40 arcs: a lane plan (GridChainMasked)
+    cases.append((_stars(rng, (12, 40)),) + random_dense(rng, 2, 14, 5, low_rows=False))
+    try:
+        _lib.lib.k2b200_debug_set_copy_wait_limit(0)
+        for k, (a, scores, brs) in enumerate(cases):
+            _compare(a, scores, brs, 10.0, tag=f"wait limit 0, case {k}")
+    finally:
+        _lib.lib.k2b200_debug_set_copy_wait_limit(-1)
+    for k, (a, scores, brs) in enumerate(cases):
+        _compare(a, scores, brs, 10.0, tag=f"default limit, case {k}")
