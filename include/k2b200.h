@@ -225,7 +225,10 @@ typedef struct {
   /* 0 = choose automatically, 1 = one launch per frame (any graph size),
    * 2 = persistent frame-synchronous kernel (graphs that fit in shared memory),
    * 3 = persistent kernel with the arcs in registers (needs a_max_degree <= 4
-   *     and at most 1024 states per graph) */
+   *     and at most 1024 states per graph), 4 = persistent kernel with a lane plan
+   *     (graphs of at most 768 states with states of more than four arcs),
+   * 5 = one launch per frame with the sequences on the lanes of a warp (needs a_shared
+   *     and at least two sequences; what 0 chooses for a shared graph too large for 2-4) */
   int32_t viterbi_mode;
   /* largest number of arcs entering or leaving any state of a_fsas; 0 = unknown
    * (then mode 3 is never chosen) */

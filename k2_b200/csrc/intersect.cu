@@ -115,6 +115,12 @@ int32_t MakeLayout(const k2b200_intersect_args *a, Layout *L) {
   L->lane_plan = LanePlanApplies(*L, a);
   L->off_plan = take(L->lane_plan ? sizeof(int32_t) * 2 * (size_t)a->num_fsas * kLaneThreads : 0);
   L->off_unfit = take(sizeof(int32_t) * (size_t)a->num_fsas);
+  // a shared graph too large for the one-CTA kernels: sequences on the lanes of a warp
+  L->shared_vit = (a->viterbi_mode == 5 ||
+                   (a->viterbi_mode == 0 && !RegisterViterbiFits(*L, a) && !L->lane_plan &&
+                    !PersistentViterbiFits(*L, a))) &&
+                  SharedViterbiApplies(*L, a);
+  L->off_shared_vit = take(L->shared_vit ? SharedViterbiBytes(*L, a) : 0);
   L->total_bytes = off;
   return kOk;
 }
@@ -254,10 +260,18 @@ CountKept(const FsaInfo *__restrict__ infos, int32_t n, int64_t total_words,
   if (rel0 >= pair_words) break;  // warp-uniform
   float fs[kWordsPerWarp], bs[kWordsPerWarp];
   int32_t ts[kWordsPerWarp], ss[kWordsPerWarp];
+  // (level, word) of the warp's first word by one 32-bit division (a pair has fewer than
+  // 2^31 words), of the following ones by stepping
+  int32_t t_run = (int32_t)((uint32_t)rel0 / (uint32_t)f.words);
+  int32_t w_run = (int32_t)((uint32_t)rel0 - (uint32_t)t_run * (uint32_t)f.words);
 #pragma unroll
   for (int u = 0; u < kWordsPerWarp; ++u) {
     const int64_t rel = rel0 + u;
-    const int32_t t = (int32_t)(rel / f.words), s = (int32_t)(rel - (int64_t)t * f.words) * 32 + lane;
+    const int32_t t = t_run, s = w_run * 32 + lane;
+    if (++w_run == f.words) {
+      w_run = 0;
+      ++t_run;
+    }
     ts[u] = t;
     ss[u] = s;
     const bool in = rel < pair_words && s < S;
@@ -382,7 +396,8 @@ EmitWord(const FsaInfo &f, int32_t i, int32_t n, int64_t rel, float cutoff, int 
          const float *__restrict__ bwd, const uint32_t *__restrict__ mask,
          const int2 *__restrict__ bases, const k2b200_lattice_out &out) {
   const int64_t w = f.word_off + rel;
-  const int32_t t = (int32_t)(rel / f.words), wi = (int32_t)(rel % f.words), s = wi * 32 + lane;
+  const int32_t t = (int32_t)((uint32_t)rel / (uint32_t)f.words),
+                wi = (int32_t)((uint32_t)rel - (uint32_t)t * (uint32_t)f.words), s = wi * 32 + lane;
   const uint32_t m = mask[w];
   if (m == 0 && wi != 0) return;  // nothing kept in this word and no layer boundary to record
   const int32_t S = f.num_states;
@@ -533,6 +548,12 @@ int32_t RunViterbi(const Layout &L, const k2b200_intersect_args *a, char *ws, cu
                 "viterbi_mode=2 requested but a graph does not fit in shared memory");
     NotePhaseKernel(kPhaseViterbi, "PersistentViterbi");
     return LaunchPersistentViterbi(L, a, d_infos, fwd, bwd, stream);
+  }
+  if (mode == 5) K2B_REQUIRE(L.shared_vit, "viterbi_mode=5 needs one graph shared by all sequences "
+                             "(a_shared) and at least two of them");
+  if (L.shared_vit) {
+    NotePhaseKernel(kPhaseViterbi, "SharedViterbiStep");
+    return LaunchSharedViterbi(L, a, ws + L.off_shared_vit, d_infos, fwd, bwd, stream);
   }
   const Arc *arcs = reinterpret_cast<const Arc *>(a->a_arcs);
   NotePhaseKernel(kPhaseViterbi, "ViterbiStep");

@@ -29,7 +29,10 @@ struct Layout {
   int32_t max_states = 0, max_tk = 0, max_arcs = 0;
   // byte offsets into the workspace
   size_t off_infos, off_cutoffs, off_fwd, off_bwd, off_mask, off_counts, off_scan_tmp,
-      off_block_cand, off_totals, off_plan, off_unfit, total_bytes;
+      off_block_cand, off_totals, off_plan, off_unfit, off_shared_vit, total_bytes;
+  // one large graph shared by all sequences: the sequence-per-lane Viterbi kernels and their
+  // transposed buffers (viterbi_shared.cu)
+  bool shared_vit = false;
   // graphs with states of more than four arcs, small enough for one CTA: lanes are
   // assigned to states by a plan (viterbi_persistent.cu)
   bool lane_plan = false;
@@ -51,6 +54,12 @@ int32_t PruneLoop(const Layout &L, const k2b200_intersect_args *args, char *ws,
 // cutoffs[i] = min(best forward, best backward total) - beam, from the Viterbi grids
 int32_t LaunchCutoffs(const Layout &L, const k2b200_intersect_args *a, char *ws, float beam,
                       cudaStream_t stream);
+
+// viterbi_shared.cu
+bool SharedViterbiApplies(const Layout &L, const k2b200_intersect_args *a);
+size_t SharedViterbiBytes(const Layout &L, const k2b200_intersect_args *a);
+int32_t LaunchSharedViterbi(const Layout &L, const k2b200_intersect_args *a, char *region,
+                            const FsaInfo *d_infos, float *fwd, float *bwd, cudaStream_t stream);
 
 // viterbi_persistent.cu
 bool PersistentViterbiFits(const Layout &L, const k2b200_intersect_args *a);

@@ -437,3 +437,36 @@ def test_ragged_attributes_follow_the_arc_maps(k2):
     srt, amap = k2.arc_sort(fsa, ret_arc_map=True)
     assert srt.tokens.tolist() == [rows[i] for i in amap.cpu().tolist()]
     assert fsa.to("cpu").tokens.tolist() == rows
+
+
+def test_shared_graph_viterbi_with_sequences_on_lanes(k2):
+    # viterbi_mode 5 (what a large shared decoding graph gets): a warp per state, its lanes
+    # are the sequences.  Lattices must be bit-identical to the oracle's for batches that
+    # fill part of a group of 32, more than one group, sequences of different lengths and
+    # states with more than 32 entering arcs.
+    from gpu_util import dense_from_scores, fsa_to_host, host_to_fsa, intersect_raw
+    from k2_b200 import autograd
+    from oracle.common import HostFsaVec
+    rng = np.random.default_rng(53)
+    autograd.SHARED_GRAPH_MIN_BYTES = 0
+    try:
+        for n, max_states, max_arcs in ((2, 12, 40), (5, 45, 400), (33, 70, 300), (70, 20, 900),
+                                       (3, 6, 1400), (34, 9, 2500)):  # the last two: states of > 128 arcs
+            one = random_fsa_vec(rng, 1, max_states=max_states, max_arcs=max_arcs, acyclic=False,
+                                 allow_empty=False)
+            S, A = one.num_states, one.num_arcs
+            rs1 = (np.arange(n + 1) * S).astype(np.int32)
+            rs2 = np.concatenate([one.row_splits2[:-1] + i * A for i in range(n)] +
+                                 [[n * A]]).astype(np.int32)
+            a = HostFsaVec(rs1, rs2, np.tile(one.arcs, (n, 1)))
+            scores, brs = random_dense(rng, n, 11, 5, low_rows=False)
+            fsa = host_to_fsa(a)
+            assert fsa.arcs.replicated(0)
+            for beam in (3.0, 20.0):
+                want = oracle.intersect_dense(a, scores, brs, beam)
+                lat, ma, mb = intersect_raw(fsa, dense_from_scores(scores, brs), beam, mode=5)
+                same_fsa(fsa_to_host(lat, ma, mb), want, f"mode 5, n={n}, beam={beam}")
+                lat1, ma1, mb1 = intersect_raw(fsa, dense_from_scores(scores, brs), beam, mode=1)
+                same_fsa(fsa_to_host(lat1, ma1, mb1), want, f"mode 1, n={n}, beam={beam}")
+    finally:
+        autograd.SHARED_GRAPH_MIN_BYTES = 32 << 20
