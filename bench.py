@@ -43,6 +43,8 @@ def parse_args():
     p.add_argument("--scale", type=float, default=1.0)
     p.add_argument("--utterances", type=int, default=None,
                    help="lfmmi_den only: batch size, e.g. 16 = one GPU's share of 128 split 8 ways")
+    p.add_argument("--max-frames", type=int, default=None,
+                   help="cut every sequence of the workload to its first frames (profiling)")
     p.add_argument("--no-cpu-baseline", action="store_true")
     p.add_argument("--no-lfmmi-den", action="store_true",
                    help="skip the LF-MMI denominator block of the default line")
@@ -71,7 +73,17 @@ def make_workload(args, seed, syn=None, name=None):
     name = name or args.workload
     if name == "lfmmi_den" and args.utterances is not None:
         return syn.lfmmi_den(seed=seed, scale=args.scale, utterances=args.utterances)
-    return syn.WORKLOADS[name](seed=seed, scale=args.scale)
+    w = syn.WORKLOADS[name](seed=seed, scale=args.scale)
+    if getattr(args, "max_frames", None):
+        # the same batch cut to its first frames: a case small enough for an ncu capture of
+        # a workload whose grids would otherwise hold tens of GB
+        import dataclasses
+        t = int(args.max_frames)
+        seg = w.supervision_segments.clone()
+        seg[:, 2] = seg[:, 2].clamp(max=t)
+        w = dataclasses.replace(w, log_probs=w.log_probs[:, :t].contiguous(),
+                                supervision_segments=seg)
+    return w
 
 
 # --------------------------------------------------------------------------- clocks
