@@ -397,7 +397,7 @@ def run_ours(args):
                    else PeerLossReducer(dev))
     frames_of = {}
 
-    def loss_step(lp, g, segments, beam):
+    def loss_step(lp, g, segments, beam, read_totals=False):
         lp = lp.detach().requires_grad_(True)
         dense = k2.DenseFsaVec(lp, segments)
         loss = k2.ctc_loss(g, dense, output_beam=beam, reduction="sum")
@@ -408,11 +408,15 @@ def run_ours(args):
             reducer.submit(loss, nf)
         loss.backward()
         if reducer is not None:
+            # the totals are consumed on the host (logging): a step that does not read them
+            # does not make its stream wait for the other ranks either
+            if isinstance(reducer, PeerLossReducer):
+                return reducer.result(join=read_totals)[0], lp.grad
             return reducer.result()[0], lp.grad
         return loss.detach(), lp.grad
 
-    def step(lp):
-        return loss_step(lp, graphs, seg, w.output_beam)
+    def step(lp, read_totals=False):
+        return loss_step(lp, graphs, seg, w.output_beam, read_totals)
 
     def barrier():
         if dist is not None:
@@ -467,7 +471,7 @@ def run_ours(args):
                     pf.submit(host_lp)
             else:
                 lp = host_lp.to(dev, non_blocking=True)
-            out, _ = step(lp)
+            out, _ = step(lp, read_totals=True)
             float(out.item())
         e1.record()
         barrier()

@@ -4,6 +4,8 @@
 k2::ShortestPath, fsa_algo.cu:869-1144)."""
 from typing import List, Optional, Tuple, Union
 
+import itertools
+
 import numpy as np
 import torch
 
@@ -40,9 +42,9 @@ def ctc_graph(symbols: List[List[int]], modified: bool = False,
     holds the symbol on the arcs that enter a symbol state (fsa_algo.cu:672-727).
     """
     n = len(symbols)
-    lens = np.asarray([len(s) for s in symbols], dtype=np.int64)
+    lens = np.fromiter(map(len, symbols), dtype=np.int64, count=n)
     tot = int(lens.sum())
-    sym = np.asarray([x for s in symbols for x in s], dtype=np.int64).reshape(-1)
+    sym = np.fromiter(itertools.chain.from_iterable(symbols), dtype=np.int64, count=tot)
     assert not np.any(sym == -1), "symbols must not contain -1"
     if torch.device(device).type == "cuda":
         return _ctc_graph_cuda(lens, sym, modified, torch.device(device))

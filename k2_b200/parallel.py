@@ -198,12 +198,16 @@ class PeerLossReducer:
                 self.poll_limit, self.out[self.seq & 1].data_ptr(), self.stream.cuda_stream))
         self.pending = True
 
-    def result(self) -> Tuple[torch.Tensor, torch.Tensor]:
-        """(total loss, total frames), 0-dim float64 device tensors; the current stream
-        waits for the exchange, the host does not."""
+    def result(self, join: bool = True) -> Tuple[torch.Tensor, torch.Tensor]:
+        """(total loss, total frames), 0-dim float64 device tensors.  With `join` the current
+        stream waits for the exchange (the host does not), so whatever is queued next may
+        read them; without it they are only valid after `self.stream` has been waited for
+        (a trainer that logs the totals every so many steps joins then, and the ranks do not
+        run in lockstep in between).  The buffers are reused two steps later."""
         assert self.pending, "nothing submitted"
         self.pending = False
-        torch.cuda.current_stream(self.device).wait_stream(self.stream)
+        if join:
+            torch.cuda.current_stream(self.device).wait_stream(self.stream)
         out = self.out[self.seq & 1]
         return out[0], out[1]
 
