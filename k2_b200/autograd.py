@@ -599,6 +599,7 @@ def _band_loss_args(a_fsas: Fsa, b_fsas: DenseFsaVec, a_to_b_map: Optional[torch
             return None
         args0, keep, h_map = cached[2]
         args = _lib.BandLossArgs.from_buffer_copy(args0)
+        args.ws_bytes = args0.ws_bytes
         args.output_beam = float(output_beam)
         args.max_states = int(min(max_states, 2**31 - 1))
         args.max_arcs = int(min(max_arcs, 2**31 - 1))
@@ -656,6 +657,9 @@ def _band_loss_args_uncached(a_fsas: Fsa, b_fsas: DenseFsaVec,
     _lib.check(_lib.lib.k2b200_band_loss_supported(ctypes.byref(args), ctypes.byref(ok)))
     if not ok.value:
         return None
+    nbytes = ctypes.c_size_t()
+    _lib.check(_lib.lib.k2b200_band_loss_workspace_bytes(ctypes.byref(args), ctypes.byref(nbytes)))
+    args.ws_bytes = nbytes.value  # a Python attribute beside the C fields: depends on the sizes only
     return args, (h_rs1, h_as, frames, first, states, arcs, lp, a), h_map
 
 
@@ -668,9 +672,7 @@ class _BandTotScoresFunction(torch.autograd.Function):
                 unused_scores_a: torch.Tensor, unused_scores_b: torch.Tensor) -> torch.Tensor:
         args, keep, h_map = band
         dev = a_fsas.arcs.device
-        nbytes = ctypes.c_size_t()
-        _lib.check(_lib.lib.k2b200_band_loss_workspace_bytes(ctypes.byref(args),
-                                                              ctypes.byref(nbytes)))
+        nbytes = ctypes.c_size_t(args.ws_bytes)
         lease = _lib.workspace(nbytes.value, dev)
         ws = lease.tensor
         tot = torch.empty(a_fsas.arcs.num_fsas, dtype=torch.float64, device=dev)

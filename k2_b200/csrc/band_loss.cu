@@ -55,7 +55,8 @@ constexpr int32_t kNoLabel = INT32_MIN;
 constexpr int kBandMaxStates = 512;
 constexpr int kVitK = 4;              // states per thread of BandViterbi
 constexpr int kPrepK = 16;            // states per lane of BandPrep's row scan
-constexpr int kPrepLevels = 16;       // levels per warp of BandPrep
+constexpr int kPrepLevels = 16;       // levels per chunk: their lists share one padded size
+constexpr int kPrepSub = 8;           // levels per warp of BandPrep
 constexpr int kGradLevels = 4;        // levels per warp of BandGrad
 constexpr int kDrainPolls = 4000000;  // bounded wait for copies in flight when a kernel gives up
 
@@ -575,9 +576,11 @@ BandPrep(const BandInfo *__restrict__ infos, const BandState *__restrict__ tab,
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int32_t S = f.num_states, T = f.frames, pitch = f.pitch;
   if (S == 0) return;
-  const int32_t a = (blockIdx.x * 4 + warp) * kPrepLevels;  // owns levels a .. b - 1
+  // a warp owns kPrepSub levels a .. b - 1, part of the chunk of kPrepLevels levels ca .. cb - 1
+  const int32_t a = (blockIdx.x * 4 + warp) * kPrepSub;
   if (a > T + 1) return;
-  const int32_t b = min(a + kPrepLevels, T + 2);
+  const int32_t b = min(a + kPrepSub, T + 2);
+  const int32_t ca = a / kPrepLevels * kPrepLevels, cb = min(ca + kPrepLevels, T + 2);
   // per warp: a word per state for the current and the previous level (zero outside the
   // lists), and the two lists
   uint16_t *meta_sm = reinterpret_cast<uint16_t *>(smem_raw) +
@@ -591,22 +594,24 @@ BandPrep(const BandInfo *__restrict__ infos, const BandState *__restrict__ tab,
   const int32_t s0 = lane * K;
   const int32_t first = max(a - 1, 0);  // first level looked at (its list only)
   const int32_t last = min(b, T + 1);   // last level looked at
-  // ---- 0. the keep bits of every level this warp looks at; the longest list of its own
-  // levels decides how many entries every level of the chunk gets --------------------------
+  // ---- 0. the keep bits of every level this warp looks at; the longest list of the
+  // CHUNK's levels decides how many entries every level of the chunk gets (every warp of a
+  // chunk finds the same number) ----------------------------------------------------------
   int32_t longest = 0;
+  const int32_t lo = min(first, ca), hi = max(last, cb - 1);
 #pragma unroll 6
-  for (int32_t l = first; l <= last; ++l) {
+  for (int32_t l = lo; l <= hi; ++l) {
     const uint32_t keep = keep_bits[(int64_t)(f.level_off + l) * 32 + lane];
-    keep_sm[(l - first) * 32 + lane] = (uint16_t)keep;
+    if (l >= first && l <= last) keep_sm[(l - first) * 32 + lane] = (uint16_t)keep;
     const int32_t n = __reduce_add_sync(kAll, __popc(keep));
-    if (l >= a && l < b) longest = max(longest, n);
+    if (l >= ca && l < cb) longest = max(longest, n);
   }
   const int32_t padded = 32 * (longest / 32 + 1);  // entries per level of this chunk
-  if (lane == 0) chunk_r[f.level_off + a] = padded / 32;
+  if (lane == 0 && a == ca) chunk_r[f.level_off + ca] = padded / 32;
   int32_t n_prev = 0;
   // the lists of a warp's levels lie `padded` entries apart from the start of its chunk
   // (pitch >= padded); lists[level] = (start, size)
-  int32_t run = a * pitch, prev_start = 0;
+  int32_t run = ca * pitch + (a - ca) * padded, prev_start = 0;
   bool risky = false;
   __syncwarp();
   for (int32_t l = first; l <= last; ++l) {
@@ -1584,7 +1589,9 @@ int32_t k2b200_band_loss_forward(const k2b200_band_loss_args *args, void *worksp
   K2B_FORWARD(UploadInts(reinterpret_cast<const int32_t *>(L.infos.data()),
                          (int64_t)L.infos.size() * (sizeof(BandInfo) / sizeof(int32_t)),
                          reinterpret_cast<int32_t *>(ws + L.off_infos), stream));
-  K2B_CUDA_OK(cudaMemsetAsync(ws + L.off_status, 0, 8, stream));
+  // unfit words, totals and the status word lie one after the other: one clear for the first
+  // pass (a repeated pass clears the first two again, not the status of the Viterbi kernels)
+  K2B_CUDA_OK(cudaMemsetAsync(ws + L.off_unfit, 0, L.off_totals + 64 - L.off_unfit, stream));
   {
     PhaseTimer timer(kPhaseViterbi, stream);
     NotePhaseKernel(kPhaseViterbi, "BandViterbi");
@@ -1606,8 +1613,10 @@ int32_t k2b200_band_loss_forward(const k2b200_band_loss_args *args, void *worksp
   const bool need_count = L.grid_states > args->max_states || L.arc_frames > args->max_arcs;
   float beam = args->output_beam;
   for (int iter = 0;; ++iter) {
-    K2B_CUDA_OK(cudaMemsetAsync(ws + L.off_totals, 0, 5 * sizeof(long long), stream));
-    K2B_CUDA_OK(cudaMemsetAsync(ws + L.off_unfit, 0, sizeof(int32_t) * args->num_fsas, stream));
+    if (iter > 0) {
+      K2B_CUDA_OK(cudaMemsetAsync(ws + L.off_totals, 0, 5 * sizeof(long long), stream));
+      K2B_CUDA_OK(cudaMemsetAsync(ws + L.off_unfit, 0, sizeof(int32_t) * args->num_fsas, stream));
+    }
     cudaStream_t side = nullptr;
     {
       PhaseTimer timer(kPhasePrune, stream);
@@ -1625,7 +1634,7 @@ int32_t k2b200_band_loss_forward(const k2b200_band_loss_args *args, void *worksp
 #undef K2B_BAND_KEEP
       // the host reads the counts behind BandKeep, while what follows runs
       if (need_count) K2B_FORWARD(SideFork(stream, &side));
-      dim3 grid(CeilDiv(L.max_frames + 2, 4 * kPrepLevels), args->num_fsas);
+      dim3 grid(CeilDiv(L.max_frames + 2, 4 * kPrepSub), args->num_fsas);
       { BandPrep<<<grid, 128, L.prep_smem, stream>>>(
           reinterpret_cast<const BandInfo *>(ws + L.off_infos),
           reinterpret_cast<const BandState *>(args->band_states),

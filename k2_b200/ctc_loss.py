@@ -71,6 +71,11 @@ class CtcLoss(nn.Module):
 
     def _reduce(self, tot_scores: torch.Tensor,
                 target_lengths: Optional[torch.Tensor]) -> torch.Tensor:
+        if self.reduction == "sum":
+            # (-1 * tot_scores).to(float32).sum() of the reference in two kernels: the
+            # reduction casts every element before adding, and negation commutes with
+            # rounding, so the bits are the same
+            return -tot_scores.sum(dtype=torch.float32)
         loss = -1 * tot_scores
         loss = loss.to(torch.float32)
         if self.reduction == "none":
