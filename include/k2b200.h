@@ -44,7 +44,8 @@ typedef enum {
 const char *k2b200_last_error(void);
 /* ABI version of the library (bumped on any signature change or new entry point;
  * 3: pruned intersection, score derivatives, k2b200_upload_i32;
- * 4: k2b200_band_*). */
+ * 4: k2b200_band_*;
+ * 5: k2b200_peer_reduce_*, k2b200_loss_sum_all_reduce, zero_fill in k2b200_band_loss_args). */
 int32_t k2b200_abi_version(void);
 
 /* Benchmark bookkeeping (no counterpart in the reference's bindings; its
@@ -494,6 +495,12 @@ typedef struct {
   const int32_t *h_frames;        /* HOST [num_fsas], non-increasing */
   float output_beam;
   int32_t max_states, max_arcs;
+  /* Optional (forward only): zero_fill_bytes bytes at zero_fill (device) are cleared beside
+   * the recursions, which leave most SMs idle - meant for the gradient buffer that the
+   * backward call adds into, so that its zero-fill costs no time of its own.  The clear is
+   * complete, in stream order, when the forward call's work on `stream` is.  NULL: none. */
+  void *zero_fill;
+  size_t zero_fill_bytes;
 } k2b200_band_loss_args;
 
 int32_t k2b200_band_tables_bytes(int32_t num_states, size_t *states_bytes, size_t *arcs_bytes);

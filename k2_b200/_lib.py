@@ -47,6 +47,7 @@ class BandLossArgs(ctypes.Structure):
         ("log_probs", c_vp), ("log_prob_rows", c_i64), ("num_classes", c_i32),
         ("h_first_row", c_vp), ("h_frames", c_vp),
         ("output_beam", c_f32), ("max_states", c_i32), ("max_arcs", c_i32),
+        ("zero_fill", c_vp), ("zero_fill_bytes", c_sz),
     ]
 
 

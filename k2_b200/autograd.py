@@ -600,6 +600,7 @@ def _band_loss_args(a_fsas: Fsa, b_fsas: DenseFsaVec, a_to_b_map: Optional[torch
         args0, keep, h_map = cached[2]
         args = _lib.BandLossArgs.from_buffer_copy(args0)
         args.ws_bytes = args0.ws_bytes
+        args.zero_fill, args.zero_fill_bytes = None, 0
         args.output_beam = float(output_beam)
         args.max_states = int(min(max_states, 2**31 - 1))
         args.max_arcs = int(min(max_arcs, 2**31 - 1))
@@ -677,6 +678,14 @@ class _BandTotScoresFunction(torch.autograd.Function):
         ws = lease.tensor
         tot = torch.empty(a_fsas.arcs.num_fsas, dtype=torch.float64, device=dev)
         beam = ctypes.c_float()
+        # the gradient of the log-probs, when the backward will want it: the forward call
+        # clears it beside its recursions, so the backward has no zero-fill of its own
+        ctx.grad_b = None
+        args.zero_fill, args.zero_fill_bytes = None, 0
+        if ctx.needs_input_grad[5] and unused_scores_b is b_fsas._source[0]:
+            ctx.grad_b = torch.empty(unused_scores_b.shape, dtype=torch.float32, device=dev)
+            args.zero_fill = ctx.grad_b.data_ptr()
+            args.zero_fill_bytes = ctx.grad_b.numel() * 4
         with torch.cuda.device(dev):
             _lib.check(_lib.lib.k2b200_band_loss_forward(
                 ctypes.byref(args), _lib.ptr(ws), nbytes.value, _lib.stream_of(dev),
@@ -711,7 +720,9 @@ class _BandTotScoresFunction(torch.autograd.Function):
         grad_a = None
         if ctx.needs_input_grad[4]:
             grad_a = torch.zeros(ctx.shape_a, dtype=torch.float32, device=dev)
-        grad_b = torch.zeros(ctx.shape_b, dtype=torch.float32, device=dev)
+        grad_b, ctx.grad_b = ctx.grad_b, None  # cleared by the forward call; used once
+        if grad_b is None:
+            grad_b = torch.zeros(ctx.shape_b, dtype=torch.float32, device=dev)
         with torch.cuda.device(dev):
             _lib.check(_lib.lib.k2b200_band_loss_backward(
                 ctypes.byref(ctx.args), _lib.ptr(ctx.ws), ctx.ws_bytes, _lib.ptr(tot_grad),

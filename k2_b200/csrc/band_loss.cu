@@ -1612,7 +1612,14 @@ int32_t k2b200_band_loss_forward(const k2b200_band_loss_args *args, void *worksp
   // recursions, which in the rare case of a reduction run again.
   const bool need_count = L.grid_states > args->max_states || L.arc_frames > args->max_arcs;
   float beam = args->output_beam;
+  bool join_side = false;
+  struct JoinOnExit {  // also on error returns: the caller may free the buffer being cleared
+    cudaStream_t main;
+    bool *armed;
+    ~JoinOnExit() { if (*armed) SideJoin(main); }
+  } join_guard{stream, &join_side};
   for (int iter = 0;; ++iter) {
+    SideReadBackScope readback;
     if (iter > 0) {
       K2B_CUDA_OK(cudaMemsetAsync(ws + L.off_totals, 0, 5 * sizeof(long long), stream));
       K2B_CUDA_OK(cudaMemsetAsync(ws + L.off_unfit, 0, sizeof(int32_t) * args->num_fsas, stream));
@@ -1633,7 +1640,10 @@ int32_t k2b200_band_loss_forward(const k2b200_band_loss_args *args, void *worksp
       if (L.max_states <= 256) K2B_BAND_KEEP(8) else K2B_BAND_KEEP(kPrepK)
 #undef K2B_BAND_KEEP
       // the host reads the counts behind BandKeep, while what follows runs
-      if (need_count) K2B_FORWARD(SideFork(stream, &side));
+      if (need_count) {
+        K2B_FORWARD(SideFork(stream, &side));
+        K2B_FORWARD(readback.Begin(ws + L.off_totals, sizeof(long long) * 6));
+      }
       dim3 grid(CeilDiv(L.max_frames + 2, 4 * kPrepSub), args->num_fsas);
       { BandPrep<<<grid, 128, L.prep_smem, stream>>>(
           reinterpret_cast<const BandInfo *>(ws + L.off_infos),
@@ -1650,6 +1660,13 @@ int32_t k2b200_band_loss_forward(const k2b200_band_loss_args *args, void *worksp
           reinterpret_cast<int32_t *>(ws + L.off_unfit), L.st_pad); NoteLaunch(); }
       K2B_CUDA_OK(cudaGetLastError());
     }
+    if (iter == 0 && args->zero_fill != nullptr && args->zero_fill_bytes > 0) {
+      // behind BandPrep, beside the recursions (one warp per graph and direction: the SMs
+      // are all but idle); joined below
+      K2B_FORWARD(SideFork(stream, &side));
+      K2B_CUDA_OK(cudaMemsetAsync(args->zero_fill, 0, args->zero_fill_bytes, side));
+      join_side = true;
+    }
     {
       PhaseTimer timer(kPhaseChain, stream);
       NotePhaseKernel(kPhaseChain, "BandChainLists");
@@ -1657,7 +1674,7 @@ int32_t k2b200_band_loss_forward(const k2b200_band_loss_args *args, void *worksp
     }
     if (!need_count) break;
     long long h_totals[6];
-    K2B_FORWARD(SideReadBack(ws + L.off_totals, sizeof(h_totals), h_totals));
+    K2B_FORWARD(readback.End(h_totals));
     K2B_REQUIRE((h_totals[5] & kStatusLate) == 0,
                 "a copy of log-prob rows into shared memory did not complete in time");
     if (!BandReduceBeam(args, h_totals, &beam)) break;

@@ -86,6 +86,17 @@ int32_t SideJoin(cudaStream_t main);
 // device -> host copy of a few bytes behind the side stream's work; blocks the host
 // until it (and not the main stream) is done
 int32_t SideReadBack(const void *device_src, size_t bytes, void *host_out);
+// The same in two steps: Begin queues the copy behind what the side stream has been given
+// so far, End waits for it on the host - so that work queued on the side stream in between
+// does not delay the answer.  One read-back at a time per process (the scope holds a lock).
+struct SideReadBackScope {
+  SideReadBackScope() = default;
+  ~SideReadBackScope();
+  int32_t Begin(const void *device_src, size_t bytes);
+  int32_t End(void *host_out);
+  size_t bytes_ = 0;
+  bool held_ = false;
+};
 
 static inline size_t AlignUp(size_t x, size_t a = 256) { return (x + a - 1) / a * a; }
 

@@ -112,7 +112,7 @@ double ReadPhase(int phase, long long *count) {
 namespace {
 struct SideState {
   cudaStream_t stream = nullptr;
-  cudaEvent_t fork_ev = nullptr, join_ev = nullptr, host_ev = nullptr;
+  cudaEvent_t fork_ev = nullptr, join_ev = nullptr, host_ev = nullptr, scope_ev = nullptr;
   void *pinned = nullptr;  // kSidePinnedBytes of page-locked host memory
 };
 constexpr size_t kSidePinnedBytes = 256;
@@ -129,6 +129,7 @@ int32_t SideOfCurrentDevice(SideState **out) {
     K2B_CUDA_OK(cudaEventCreateWithFlags(&st.fork_ev, cudaEventDisableTiming));
     K2B_CUDA_OK(cudaEventCreateWithFlags(&st.join_ev, cudaEventDisableTiming));
     K2B_CUDA_OK(cudaEventCreateWithFlags(&st.host_ev, cudaEventDisableTiming));
+    K2B_CUDA_OK(cudaEventCreateWithFlags(&st.scope_ev, cudaEventDisableTiming));
     K2B_CUDA_OK(cudaHostAlloc(&st.pinned, kSidePinnedBytes, cudaHostAllocDefault));
   }
   *out = &st;
@@ -162,12 +163,48 @@ int32_t SideReadBack(const void *device_src, size_t bytes, void *host_out) {
   std::lock_guard<std::mutex> lock(g_side_mutex);
   SideState *st;
   K2B_FORWARD(SideOfCurrentDevice(&st));
-  K2B_REQUIRE(bytes <= kSidePinnedBytes, "SideReadBack: too many bytes");
+  K2B_REQUIRE(bytes <= kSidePinnedBytes / 2, "SideReadBack: too many bytes");
   K2B_CUDA_OK(cudaMemcpyAsync(st->pinned, device_src, bytes, cudaMemcpyDeviceToHost, st->stream));
   K2B_CUDA_OK(cudaEventRecord(st->host_ev, st->stream));
   K2B_CUDA_OK(cudaEventSynchronize(st->host_ev));
   memcpy(host_out, st->pinned, bytes);
   return kOk;
+}
+
+static std::mutex g_readback_mutex;  // held from Begin to End (or to the scope's end)
+
+int32_t SideReadBackScope::Begin(const void *device_src, size_t bytes) {
+  K2B_REQUIRE(!held_, "SideReadBackScope::Begin called twice");
+  K2B_REQUIRE(bytes <= kSidePinnedBytes / 2, "SideReadBackScope: too many bytes");
+  g_readback_mutex.lock();
+  held_ = true;
+  bytes_ = bytes;
+  std::lock_guard<std::mutex> lock(g_side_mutex);
+  SideState *st;
+  K2B_FORWARD(SideOfCurrentDevice(&st));
+  // the second half of the pinned buffer: SideReadBack uses the first
+  K2B_CUDA_OK(cudaMemcpyAsync(static_cast<char *>(st->pinned) + kSidePinnedBytes / 2, device_src,
+                              bytes, cudaMemcpyDeviceToHost, st->stream));
+  K2B_CUDA_OK(cudaEventRecord(st->scope_ev, st->stream));
+  return kOk;
+}
+
+int32_t SideReadBackScope::End(void *host_out) {
+  K2B_REQUIRE(held_, "SideReadBackScope::End without Begin");
+  SideState *st;
+  {
+    std::lock_guard<std::mutex> lock(g_side_mutex);
+    K2B_FORWARD(SideOfCurrentDevice(&st));
+  }
+  K2B_CUDA_OK(cudaEventSynchronize(st->scope_ev));
+  memcpy(host_out, static_cast<char *>(st->pinned) + kSidePinnedBytes / 2, bytes_);
+  held_ = false;
+  g_readback_mutex.unlock();
+  return kOk;
+}
+
+SideReadBackScope::~SideReadBackScope() {
+  if (held_) g_readback_mutex.unlock();
 }
 
 // ----------------------------------------------------------------------------

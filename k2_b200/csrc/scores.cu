@@ -237,7 +237,7 @@ static int32_t LaunchScores(const k2b200_fsa_view *v, int32_t log_semiring, Real
 extern "C" {
 
 const char *k2b200_last_error(void) { return LastError(); }
-int32_t k2b200_abi_version(void) { return 4; }
+int32_t k2b200_abi_version(void) { return 5; }
 int64_t k2b200_kernel_launch_count(void) { return LaunchCount(); }
 void k2b200_profile_enable(int32_t on) { SetProfiling(on != 0); }
 const char *k2b200_profile_kernel(int32_t phase) { return PhaseKernel(phase); }

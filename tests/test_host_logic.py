@@ -26,7 +26,7 @@ def test_library_exports_every_declared_symbol():
     from k2_b200 import _lib
     assert sorted(_lib.EXPORTED) == [d for d in declared if d in _lib.EXPORTED]
     assert set(declared) == set(_lib.EXPORTED)
-    assert lib.k2b200_abi_version() == 4
+    assert lib.k2b200_abi_version() == 5
 
 
 def test_no_cpu_path():
