@@ -180,7 +180,8 @@ GridChainLanes(const FsaInfo *__restrict__ infos, int32_t n, const Arc *__restri
                LaneSmem sm, int32_t wait_limit) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   __shared__ __align__(8) uint64_t full[kU];
-  __shared__ int32_t emax;  // largest exponent among the values of a group's last level
+  __shared__ int32_t emax;
+  __shared__ int32_t t_fail_sm;  // step whose wait gave up  // largest exponent among the values of a group's last level
   constexpr int32_t kNone = INT32_MIN;
   const int32_t i = blockIdx.y;
   const int dir = blockIdx.x;
@@ -299,17 +300,19 @@ GridChainLanes(const FsaInfo *__restrict__ infos, int32_t n, const Arc *__restri
   int32_t skip = (int32_t)(((reinterpret_cast<uintptr_t>(fgrid) >> 2) + (uintptr_t)(first * S)) & 3);
   const int32_t skip_step = (int32_t)(step_stride & 3);
   bool gave_up = false;
-  int32_t t_fail = 0;
   for (int32_t t0 = 1; t0 <= Tk && !gave_up; t0 += kU) {
 #pragma unroll
     for (int u = 0; u < kU; ++u) {
       const int32_t t = t0 + u;
       if (t > Tk) break;
-      const bool late = !MbarTryWait(&full[u], parity) && !MbarWaitBounded(&full[u], parity, wait_limit);
+      // (the usual limit as a constant: the polling loop the compiler makes of it is the cheaper one)
+      const bool late = !MbarTryWait(&full[u], parity) &&
+                        !(wait_limit == 4000000 ? MbarWaitBounded(&full[u], parity)
+                                                : MbarWaitBounded(&full[u], parity, wait_limit));
       // the previous frame is complete; nobody reads its ring slot any more
       if (__syncthreads_or(late)) {  // uniform
         gave_up = true;
-        t_fail = t;
+        if (tid == 0) t_fail_sm = t;  // shared memory: nothing of it stays live in the loop
         break;
       }
       if (producer) {
@@ -384,6 +387,7 @@ GridChainLanes(const FsaInfo *__restrict__ infos, int32_t n, const Arc *__restri
       atomicOr(&unfit[i], 2);
       // copies may still be in flight towards this CTA's shared memory (the rows of steps
       // t_fail .. t_fail + kU - 2): wait for each, with a limit, before the CTA retires
+      const int32_t t_fail = t_fail_sm;
       for (int32_t k = t_fail; k <= min(t_fail + kU - 2, Tk); ++k)
         MbarWaitBounded(&full[(k - 1) % kU], (unsigned)((k - 1) / kU) & 1u);
     }
@@ -581,6 +585,7 @@ GridChainMasked(const FsaInfo *__restrict__ infos, int32_t n, int64_t total_leve
   extern __shared__ __align__(16) unsigned char smem_raw[];
   __shared__ __align__(8) uint64_t full[kU];
   __shared__ int32_t emax;
+  __shared__ int32_t t_fail_sm;  // step whose wait gave up
   constexpr int32_t kNone = INT32_MIN;
   const int32_t i = blockIdx.y;
   const int dir = blockIdx.x;
@@ -688,16 +693,18 @@ GridChainMasked(const FsaInfo *__restrict__ infos, int32_t n, int64_t total_leve
   int32_t K = 0;
   unsigned parity = 0;
   bool gave_up = false;
-  int32_t t_fail = 0;
   for (int32_t t0 = 1; t0 <= Tk && !gave_up; t0 += kU) {
 #pragma unroll
     for (int u = 0; u < kU; ++u) {
       const int32_t t = t0 + u;
       if (t > Tk) break;
-      const bool late = !MbarTryWait(&full[u], parity) && !MbarWaitBounded(&full[u], parity, wait_limit);
+      // (the usual limit as a constant: the polling loop the compiler makes of it is the cheaper one)
+      const bool late = !MbarTryWait(&full[u], parity) &&
+                        !(wait_limit == 4000000 ? MbarWaitBounded(&full[u], parity)
+                                                : MbarWaitBounded(&full[u], parity, wait_limit));
       if (__syncthreads_or(late)) {  // uniform
         gave_up = true;
-        t_fail = t;
+        if (tid == 0) t_fail_sm = t;  // shared memory: nothing of it stays live in the loop
         break;
       }
       if (tid == 0) {
@@ -773,6 +780,7 @@ GridChainMasked(const FsaInfo *__restrict__ infos, int32_t n, int64_t total_leve
     if (tid == 0) {
       atomicOr(&unfit[i], 2);
       // the copies still in flight (steps t_fail .. t_fail + kU - 2) land before the CTA retires
+      const int32_t t_fail = t_fail_sm;
       for (int32_t k = t_fail; k <= min(t_fail + kU - 2, Tk); ++k)
         MbarWaitBounded(&full[(k - 1) % kU], (unsigned)((k - 1) / kU) & 1u);
     }
