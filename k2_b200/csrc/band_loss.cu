@@ -871,25 +871,42 @@ __device__ __forceinline__ double ChainRescale(int32_t &hi_max, int32_t &Ksh) {
   return __longlong_as_double((long long)(1023 - e) << 52);
 }
 
-// Levels 1 .. 15 (in walking order) of a full chunk with RC registers per lane, unrolled.
+// Levels 1 .. 15 (in walking order) of a full chunk with RC registers per lane: seven levels,
+// the level that changes the scale, seven levels.  kChainUnroll levels of straight-line code per
+// loop iteration: a single warp has nobody to hide an instruction-cache miss behind, so the
+// code of a chunk should stay small.
+constexpr int kChainUnroll = 1;  // (fully unrolled: 178 us for ctc_large; 1: 147 us)
+
 template <int DIR, int RC>
 __device__ __forceinline__ void ChainRest(const BandFactor *base, double *__restrict__ ob,
                                           int32_t *__restrict__ osc, int lane, double (&v)[3],
                                           double (&pc)[3][3], int32_t &hi_max, uint32_t &min_hi,
                                           int32_t &Ksh) {
-#pragma unroll
-  for (int kk = 1; kk < kPrepLevels; ++kk) {
-    const int m = DIR == 0 ? kk : kPrepLevels - 1 - kk;
-    if (kk == kRescale) {
-      const double scale = ChainRescale(hi_max, Ksh);
-      ChainLevel<DIR, RC, RC, true>(base + m * 32 * RC, ob + m * 32 * RC, scale, v, pc, hi_max,
-                                    min_hi);
-    } else {
-      ChainLevel<DIR, RC, RC, false>(base + m * 32 * RC, ob + m * 32 * RC, 1.0, v, pc, hi_max,
-                                     min_hi);
+  static_assert(kPrepLevels == 2 * kRescale, "a chunk is two groups of kRescale levels");
+  constexpr int kStep = DIR == 0 ? 1 : -1;
+  auto plain = [&](int kk_first) {  // kRescale - 1 levels without a change of scale
+    const int m0 = DIR == 0 ? kk_first : kPrepLevels - 1 - kk_first;
+    const BandFactor *r = base + m0 * 32 * RC;
+    double *o = ob + m0 * 32 * RC;
+    int32_t *sc = osc + m0;
+#pragma unroll kChainUnroll
+    for (int k = 0; k < kRescale - 1; ++k) {
+      ChainLevel<DIR, RC, RC, false>(r, o, 1.0, v, pc, hi_max, min_hi);
+      if (lane == 0) *sc = Ksh;
+      r += kStep * 32 * RC;
+      o += kStep * 32 * RC;
+      sc += kStep;
     }
+  };
+  plain(1);
+  {
+    const int m = DIR == 0 ? kRescale : kPrepLevels - 1 - kRescale;
+    const double scale = ChainRescale(hi_max, Ksh);
+    ChainLevel<DIR, RC, RC, true>(base + m * 32 * RC, ob + m * 32 * RC, scale, v, pc, hi_max,
+                                  min_hi);
     if (lane == 0) osc[m] = Ksh;
   }
+  plain(kRescale + 1);
 }
 
 template <int DIR>

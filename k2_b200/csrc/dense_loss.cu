@@ -23,6 +23,7 @@
 // exp() of the dense scores is taken once per element in a parallel pass
 // (ExpDense) shared by both recursions and the gradient pass.
 #include <algorithm>
+#include <type_traits>
 
 #include "cp_async.cuh"
 #include "intersect_internal.cuh"
@@ -571,7 +572,9 @@ ArcMasks(const FsaInfo *__restrict__ infos, int32_t n, int64_t total_levels,
 // exp(dense score) multiplies the sum once per state instead of every term.  Every state
 // is written to the grid (0 for pruned ones).
 // ---------------------------------------------------------------------------
-template <int kDeg, int kU, int kPBytes>
+constexpr int kMaskedBatches = 3;  // batches of kU frames in the ring
+
+template <int kDeg, int kU>
 __global__ void __launch_bounds__(kLaneThreads)
 GridChainMasked(const FsaInfo *__restrict__ infos, int32_t n, int64_t total_levels,
                 const Arc *__restrict__ arcs, const int32_t *__restrict__ a_row_splits2,
@@ -583,9 +586,9 @@ GridChainMasked(const FsaInfo *__restrict__ infos, int32_t n, int64_t total_leve
                 double *__restrict__ tot, const int32_t *__restrict__ plan,
                 int32_t *__restrict__ unfit, int32_t s_pad, int32_t wait_limit) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
-  __shared__ __align__(8) uint64_t full[kU];
+  __shared__ __align__(8) uint64_t full[kMaskedBatches];
   __shared__ int32_t emax;
-  __shared__ int32_t t_fail_sm;  // step whose wait gave up
+  __shared__ int32_t t_fail_sm;  // batch whose wait gave up
   constexpr int32_t kNone = INT32_MIN;
   const int32_t i = blockIdx.y;
   const int dir = blockIdx.x;
@@ -599,10 +602,10 @@ GridChainMasked(const FsaInfo *__restrict__ infos, int32_t n, int64_t total_leve
   }
   (void)s_pad;
   constexpr int kSPad = kLaneThreads;  // a planned graph has at most that many states
-  const uint32_t p_bytes = 8u * (uint32_t)dp.cols2;  // <= kPBytes
-  constexpr uint32_t slot_bytes = (uint32_t)kPBytes + (uint32_t)kLaneThreads;
-  unsigned char *ring = smem_raw;                                            // [kU][slot_bytes]
-  double *pv = reinterpret_cast<double *>(ring + (size_t)kU * slot_bytes);   // [2][kSPad]
+  // a batch: kU packed dense rows, then kU rows of mask bytes
+  const uint32_t batch_bytes = (uint32_t)kU * ((uint32_t)dp.pitch + (uint32_t)kLaneThreads);
+  unsigned char *ring = smem_raw;                                  // [kMaskedBatches][batch_bytes]
+  double *pv = reinterpret_cast<double *>(ring + (size_t)kMaskedBatches * batch_bytes);  // [2][kSPad]
   int32_t s = -1, g = 0, G = 1;
   {
     const int32_t code = plan[((int64_t)dir * n + i) * kLaneThreads + tid];
@@ -644,10 +647,10 @@ GridChainMasked(const FsaInfo *__restrict__ infos, int32_t n, int64_t total_leve
       }
     }
   }
-  const bool hoist = __all_sync(0xffffffffu, same);
+  const bool hoist = __syncthreads_and(same);  // uniform over the CTA
   const uint32_t col0_off = 8u * (uint32_t)(col0 < 0 ? 0 : col0);  // no arc: the sum is 0
   if (tid == 0) {
-    for (int st = 0; st < kU; ++st) MbarInit(&full[st], 1);
+    for (int st = 0; st < kMaskedBatches; ++st) MbarInit(&full[st], 1);
     emax = kNone;
     MbarInitFence();
   }
@@ -673,116 +676,139 @@ GridChainMasked(const FsaInfo *__restrict__ infos, int32_t n, int64_t total_leve
   }
   __syncthreads();
   const int64_t step_stride = dir == 0 ? (int64_t)S : -(int64_t)S;
-  const unsigned char *dense_p = dense + (int64_t)f.row0 * dp.pitch + 4 * dp.cols4;
+  const unsigned char *dense_rows = dense + (int64_t)f.row0 * dp.pitch;
+  const uint32_t row_bytes = (uint32_t)dp.pitch, lp_bytes = 4u * (uint32_t)dp.cols4;
   const unsigned char *mask0 = masks + ((int64_t)dir * total_levels + f.level_off) * kLaneThreads;
-  auto issue_row = [&](int32_t step, int32_t slot) {  // thread 0 only
-    if (step > Tk) return;
-    const int64_t row = dir == 0 ? step - 1 : Tk - step;  // dense row
-    const int64_t r = dir == 0 ? step : Tk - step;        // mask row
-    unsigned char *dst = ring + (size_t)slot * slot_bytes;
-    MbarArriveExpectTx(&full[slot], p_bytes + (unsigned)kLaneThreads);
-    BulkCopyG2S(dst, dense_p + row * dp.pitch, p_bytes, &full[slot]);
-    BulkCopyG2S(dst + kPBytes, mask0 + r * kLaneThreads, (unsigned)kLaneThreads, &full[slot]);
+  const int32_t num_batches = (Tk + kU - 1) / kU;
+  // thread 0: the rows of steps b * kU + 1 .. of batch b, as two copies.  Walking forward the
+  // dense rows and the mask rows of consecutive steps ascend, walking backward they descend:
+  // either way they are one block of memory; frame u of the batch is row u of the block
+  // (forward) or row nf - 1 - u (backward).
+  auto issue_batch = [&](int32_t b) {
+    if (b >= num_batches) return;
+    const int32_t t_first = b * kU + 1, nf = min(kU, Tk - b * kU);
+    const int64_t row_lo = dir == 0 ? t_first - 1 : Tk - t_first - nf + 1;  // dense rows
+    const int64_t r_lo = dir == 0 ? t_first : Tk - t_first - nf + 1;        // mask rows
+    const int32_t slot = b % kMaskedBatches;
+    unsigned char *dst = ring + (size_t)slot * batch_bytes;
+    MbarArriveExpectTx(&full[slot], (unsigned)nf * (row_bytes + (unsigned)kLaneThreads));
+    BulkCopyG2S(dst, dense_rows + row_lo * row_bytes, (unsigned)nf * row_bytes, &full[slot]);
+    BulkCopyG2S(dst + kU * row_bytes, mask0 + r_lo * kLaneThreads, (unsigned)nf * kLaneThreads,
+                &full[slot]);
   };
   if (tid == 0)
-    for (int32_t step = 1; step < kU; ++step) issue_row(step, step - 1);
+    for (int32_t b = 0; b < kMaskedBatches - 1; ++b) issue_batch(b);
   const int32_t g_max = __reduce_max_sync(0xffffffffu, G);  // widest lane group of this warp
   const int32_t s_ld = s >= 0 ? s : 0;
   int64_t pos = (dir == 0 ? 1 : Tk - 1) * (int64_t)S + s_ld;
   double last = 0.0;
   int32_t K = 0;
-  unsigned parity = 0;
   bool gave_up = false;
-  for (int32_t t0 = 1; t0 <= Tk && !gave_up; t0 += kU) {
-#pragma unroll
-    for (int u = 0; u < kU; ++u) {
-      const int32_t t = t0 + u;
-      if (t > Tk) break;
+  // the frame loop once per kind of CTA, so that the unrolled code of only one is fetched
+  auto frames = [&](auto hoist_tag) {
+    constexpr bool kHoist = decltype(hoist_tag)::value;
+    for (int32_t b = 0; b < num_batches; ++b) {
+      const int32_t slot = b % kMaskedBatches;
+      const unsigned parity = (unsigned)(b / kMaskedBatches) & 1u;
       // (the usual limit as a constant: the polling loop the compiler makes of it is the cheaper one)
-      const bool late = !MbarTryWait(&full[u], parity) &&
-                        !(wait_limit == 4000000 ? MbarWaitBounded(&full[u], parity)
-                                                : MbarWaitBounded(&full[u], parity, wait_limit));
+      const bool late = !MbarTryWait(&full[slot], parity) &&
+                        !(wait_limit == 4000000 ? MbarWaitBounded(&full[slot], parity)
+                                                : MbarWaitBounded(&full[slot], parity, wait_limit));
+      // also: the last frame of the batch before is complete; nobody reads its slot any more
       if (__syncthreads_or(late)) {  // uniform
         gave_up = true;
-        if (tid == 0) t_fail_sm = t;  // shared memory: nothing of it stays live in the loop
+        if (tid == 0) t_fail_sm = b;  // shared memory: nothing of it stays live in the loop
         break;
       }
-      if (tid == 0) {
-        issue_row(t + kU - 1, (u + kU - 1) % kU);
-        if (u == 1) emax = kNone;
-      }
-      double scale = 1.0;
-      if (u == 0) {
-        const int32_t e_prev = emax;
-        const int32_t shift = e_prev == kNone ? 0 : e_prev;
-        K += shift;
-        scale = __longlong_as_double((long long)(1023 - shift) << 52);
-      }
-      const unsigned char *prev = reinterpret_cast<const unsigned char *>(pv + (u & 1) * kSPad);
-      double *cur = pv + ((u + 1) & 1) * kSPad;
-      const unsigned char *prow = ring + u * slot_bytes;
-      const uint32_t m = (prow + kPBytes)[tid];
-      auto at = [](const unsigned char *base, uint32_t off) {
-        return *reinterpret_cast<const double *>(base + off);
-      };
-      double sum = 0.0;
-      if (__any_sync(0xffffffffu, m != 0)) {
-        double sum1 = 0.0;  // two partial sums: half the chain of dependent additions
-        if (hoist) {
+      if (tid == 0) issue_batch(b + kMaskedBatches - 1);
+      const unsigned char *base = ring + (size_t)slot * batch_bytes;
+      const int32_t nf = min(kU, Tk - b * kU);
+      const int pb = (kU % 2 == 0) ? 0 : (b & 1);  // parity of the state buffers at the batch's start
 #pragma unroll
-          for (int j = 0; j < kDeg; j += 2) {
-            if (m & (1u << j)) sum = fma(at(prev, other_off[j]), ew[j], sum);
-            if (j + 1 < kDeg && (m & (2u << j)))
-              sum1 = fma(at(prev, other_off[j + 1]), ew[j + 1], sum1);
-          }
-        } else {
-#pragma unroll
-          for (int j = 0; j < kDeg; j += 2) {
-            if (m & (1u << j))
-              sum = fma(at(prev, other_off[j]) * ew[j], at(prow, col_off[j]), sum);
-            if (j + 1 < kDeg && (m & (2u << j)))
-              sum1 = fma(at(prev, other_off[j + 1]) * ew[j + 1], at(prow, col_off[j + 1]), sum1);
-          }
+      for (int u = 0; u < kU; ++u) {
+        if (u >= nf) break;
+        if (u > 0) __syncthreads();  // the values of the frame before are complete
+        if (tid == 0 && u == (kU > 1 ? 1 : 0) && kU > 1) emax = kNone;  // read during frame 0
+        double scale = 1.0;
+        if (u == 0) {
+          const int32_t e_prev = emax;
+          const int32_t shift = e_prev == kNone ? 0 : e_prev;
+          K += shift;
+          scale = __longlong_as_double((long long)(1023 - shift) << 52);
         }
-        sum += sum1;
+        const unsigned char *prev = reinterpret_cast<const unsigned char *>(pv + ((pb + u) & 1) * kSPad);
+        double *cur = pv + ((pb + u + 1) & 1) * kSPad;
+        const int32_t idx = dir == 0 ? u : nf - 1 - u;
+        const unsigned char *prow = base + (uint32_t)idx * row_bytes + lp_bytes;
+        const uint32_t m = (base + kU * row_bytes + (uint32_t)idx * kLaneThreads)[tid];
+        auto at = [](const unsigned char *p0, uint32_t off) {
+          return *reinterpret_cast<const double *>(p0 + off);
+        };
+        double sum = 0.0;
+        if (__any_sync(0xffffffffu, m != 0)) {
+          double sum1 = 0.0;  // two partial sums: half the chain of dependent additions
+          if (kHoist) {
 #pragma unroll
-        for (int32_t d = 16; d > 0; d >>= 1) {
-          if (d < g_max) {  // warp-uniform: no group of this warp is that wide
-            const double so = __shfl_down_sync(0xffffffffu, sum, d);
-            if (g + d < G) sum += so;
+            for (int j = 0; j < kDeg; j += 2) {
+              if (m & (1u << j)) sum = fma(at(prev, other_off[j]), ew[j], sum);
+              if (j + 1 < kDeg && (m & (2u << j)))
+                sum1 = fma(at(prev, other_off[j + 1]), ew[j + 1], sum1);
+            }
+          } else {
+#pragma unroll
+            for (int j = 0; j < kDeg; j += 2) {
+              if (m & (1u << j))
+                sum = fma(at(prev, other_off[j]) * ew[j], at(prow, col_off[j]), sum);
+              if (j + 1 < kDeg && (m & (2u << j)))
+                sum1 = fma(at(prev, other_off[j + 1]) * ew[j + 1], at(prow, col_off[j + 1]), sum1);
+            }
           }
+          sum += sum1;
+#pragma unroll
+          for (int32_t d = 16; d > 0; d >>= 1) {
+            if (d < g_max) {  // warp-uniform: no group of this warp is that wide
+              const double so = __shfl_down_sync(0xffffffffu, sum, d);
+              if (g + d < G) sum += so;
+            }
+          }
+          if (kHoist) sum *= at(prow, col0_off);
         }
-        if (hoist) sum *= at(prow, col0_off);
-      }
-      const double v = u == 0 ? sum * scale : sum;
-      const int32_t vhi = __double2hiint(v);
-      if (s >= 0 && g == 0) {
-        cur[s] = v;
-        ProbState r;
-        r.m = v;
-        r.e = K;
-        r.pad = 0;
-        out[pos] = r;
-        last = v;
-        risky |= v != 0.0 && vhi < ((1023 + kMinExponent) << 20);
-      }
-      pos += step_stride;
-      if (u == kU - 1) {
-        int32_t ex = (s >= 0 && g == 0 && v != 0.0) ? (vhi >> 20) - 1023 : kNone;
-        ex = __reduce_max_sync(0xffffffffu, ex);
-        if ((tid & 31) == 0 && ex != kNone) atomicMax(&emax, ex);
+        const double v = u == 0 ? sum * scale : sum;
+        const int32_t vhi = __double2hiint(v);
+        if (s >= 0 && g == 0) {
+          cur[s] = v;
+          ProbState r;
+          r.m = v;
+          r.e = K;
+          r.pad = 0;
+          out[pos] = r;
+          last = v;
+          risky |= v != 0.0 && vhi < ((1023 + kMinExponent) << 20);
+        }
+        pos += step_stride;
+        if (u == kU - 1) {  // the next batch renormalises by this level's largest value
+          if (kU == 1) {    // no frame in between in which to reset the maximum
+            __syncthreads();
+            if (tid == 0) emax = kNone;
+            __syncthreads();
+          }
+          int32_t ex = (s >= 0 && g == 0 && v != 0.0) ? (vhi >> 20) - 1023 : kNone;
+          ex = __reduce_max_sync(0xffffffffu, ex);
+          if ((tid & 31) == 0 && ex != kNone) atomicMax(&emax, ex);
+        }
       }
     }
-    parity ^= 1u;
-  }
+  };
+  if (hoist) frames(std::true_type{}); else frames(std::false_type{});
   const int32_t any_risky = __syncthreads_or(risky);
   if (gave_up) {
     if (tid == 0) {
       atomicOr(&unfit[i], 2);
-      // the copies still in flight (steps t_fail .. t_fail + kU - 2) land before the CTA retires
-      const int32_t t_fail = t_fail_sm;
-      for (int32_t k = t_fail; k <= min(t_fail + kU - 2, Tk); ++k)
-        MbarWaitBounded(&full[(k - 1) % kU], (unsigned)((k - 1) / kU) & 1u);
+      // the copies still in flight (batches b_fail .. b_fail + kMaskedBatches - 2) land before
+      // the CTA retires
+      const int32_t b_fail = t_fail_sm;
+      for (int32_t b = b_fail; b <= min(b_fail + kMaskedBatches - 2, num_batches - 1); ++b)
+        MbarWaitBounded(&full[b % kMaskedBatches], (unsigned)(b / kMaskedBatches) & 1u);
     }
     __syncthreads();
     return;
@@ -1716,18 +1742,15 @@ static int32_t LaunchChainMasked(const LossLayout &LL, const k2b200_intersect_ar
 #undef K2B_ARC_MASKS
   }
   {
-    constexpr int kU = kChainGroup;
-    const size_t p_bytes = 8 * (size_t)LL.pack.cols2;
     dim3 grid(2, args->num_fsas);
-#define K2B_CHAIN_MASKED(PBYTES)                                                              \
+#define K2B_CHAIN_MASKED(KU)                                                                  \
     {                                                                                         \
-      const size_t smem = (size_t)kU * ((PBYTES) + kLaneThreads) +                            \
+      const size_t smem = (size_t)kMaskedBatches * (KU) * ((size_t)LL.pack.pitch + kLaneThreads) + \
                           sizeof(double) * 2 * kLaneThreads;                                  \
-      K2B_REQUIRE(smem <= kChainSmemBudget, "too many columns for the fused loss path");      \
-      K2B_CUDA_OK(cudaFuncSetAttribute(GridChainMasked<kLaneDeg, kU, PBYTES>,                 \
+      K2B_CUDA_OK(cudaFuncSetAttribute(GridChainMasked<kLaneDeg, KU>,                         \
                                        cudaFuncAttributeMaxDynamicSharedMemorySize,           \
                                        (int)smem));                                           \
-      { GridChainMasked<kLaneDeg, kU, PBYTES><<<grid, kLaneThreads, smem, stream>>>(          \
+      { GridChainMasked<kLaneDeg, KU><<<grid, kLaneThreads, smem, stream>>>(                  \
           d_infos, args->num_fsas, L.total_levels, arcs, args->a_row_splits2,                 \
           args->a_in_splits, args->a_in_arcs, dense, LL.pack, masks, fwd, bwd, cutoffs,       \
           reinterpret_cast<ProbState *>(ws + LL.off_alpha),                                   \
@@ -1735,11 +1758,14 @@ static int32_t LaunchChainMasked(const LossLayout &LL, const k2b200_intersect_ar
           CopyWaitLimit());                                                                   \
         NoteLaunch(); }                                                                       \
     }
-    // room for the exp() part of a dense row, in four sizes
-    if (p_bytes <= 768) K2B_CHAIN_MASKED(768)
-    else if (p_bytes <= 2048) K2B_CHAIN_MASKED(2048)
-    else if (p_bytes <= 8192) K2B_CHAIN_MASKED(8192)
-    else K2B_CHAIN_MASKED(33792)
+    // frames per batch (one bulk copy of dense rows and one of mask rows each): as many as
+    // three batches of them leave room for in shared memory
+    const size_t per_frame = (size_t)kMaskedBatches * ((size_t)LL.pack.pitch + kLaneThreads);
+    const size_t room = kChainSmemBudget - sizeof(double) * 2 * kLaneThreads;
+    K2B_REQUIRE(per_frame <= room, "too many columns for the fused loss path");
+    if (4 * per_frame <= room) K2B_CHAIN_MASKED(4)
+    else if (2 * per_frame <= room) K2B_CHAIN_MASKED(2)
+    else K2B_CHAIN_MASKED(1)
 #undef K2B_CHAIN_MASKED
   }
   K2B_CUDA_OK(cudaGetLastError());

@@ -13,6 +13,8 @@
 #include <algorithm>
 #include <vector>
 
+#include <type_traits>
+
 #include "cp_async.cuh"
 #include "intersect_internal.cuh"
 
@@ -349,11 +351,16 @@ int32_t LaunchPlanLanes(const Layout &L, const k2b200_intersect_args *a, char *w
 // monotonic, so max_j fl(y_j + x) = fl(max_j y_j + x), bit for bit.
 // Graphs marked unfit are skipped (PersistentViterbi handles them).
 // ---------------------------------------------------------------------------
-constexpr int kVitRing = 8;   // slots of the row ring = frames per unrolled group
-constexpr int kVitAhead = 6;  // rows requested ahead of the frame that uses them
+constexpr int kVitRing = 4;   // slots of the row ring = frames per unrolled group
+constexpr int kVitAhead = 3;  // rows requested ahead of the frame that uses them
 
-template <int kDeg>
-__global__ void __launch_bounds__(kLaneThreads)
+// kV: plan lanes per thread.  Thread t of a CTA of kLaneThreads / kV threads works for the
+// plan's lanes t, t + blockDim, ...: a multiple of 32 apart, so the lanes of a plan warp stay
+// the lanes of one warp and the shuffles of a group work as before.  Fewer, fatter warps:
+// the per-frame cost of a warp that does not depend on its arcs (barrier, row ring, loop) is
+// paid fewer times, and the gathers of a thread's lanes are in flight together.
+template <int kDeg, int kV>
+__global__ void __launch_bounds__(kLaneThreads / kV)
 LanesViterbi(const FsaInfo *__restrict__ infos, int32_t n, const Arc *__restrict__ arcs,
              const int32_t *__restrict__ a_row_splits2, const int32_t *__restrict__ in_splits,
              const int32_t *__restrict__ in_arcs, const float *__restrict__ scores,
@@ -367,49 +374,53 @@ LanesViterbi(const FsaInfo *__restrict__ infos, int32_t n, const Arc *__restrict
   const int dir = blockIdx.x;
   const int32_t S = f.num_states, Tk = f.tk;
   if (S == 0) return;
-  const int tid = threadIdx.x, nt = blockDim.x;
+  const int tid = threadIdx.x, nt = blockDim.x;  // nt == kLaneThreads / kV
   float *ring = reinterpret_cast<float *>(smem_raw);  // [kVitRing][cols_pad]
-  int32_t s = -1, g = 0, G = 1;
-  {
-    const int32_t code = plan[((int64_t)dir * n + i) * kLaneThreads + tid];
-    if (code >= 0) {
-      s = code & 0xffff;
-      g = (code >> 16) & 0xff;
-      G = code >> 24;
-    }
-  }
-  int32_t other[kDeg], col[kDeg];
-  float w[kDeg];
-  int32_t col0 = -1;
+  int32_t s[kV], g[kV], G[kV], g_max[kV], col0[kV];
+  int32_t other[kV][kDeg], col[kV][kDeg];
+  float w[kV][kDeg];
   bool same = true;
 #pragma unroll
-  for (int j = 0; j < kDeg; ++j) {
-    other[j] = 0;
-    col[j] = 0;
-    w[j] = -INFINITY;
-  }
-  if (s >= 0) {
-    const int32_t *splits = dir == 0 ? in_splits : a_row_splits2;
-    const int32_t a0 = splits[f.state_off + s], a1 = splits[f.state_off + s + 1];
+  for (int v = 0; v < kV; ++v) {
+    s[v] = -1;
+    g[v] = 0;
+    G[v] = 1;
+    col0[v] = -1;
+    const int32_t code = plan[((int64_t)dir * n + i) * kLaneThreads + tid + v * nt];
+    if (code >= 0) {
+      s[v] = code & 0xffff;
+      g[v] = (code >> 16) & 0xff;
+      G[v] = code >> 24;
+    }
 #pragma unroll
     for (int j = 0; j < kDeg; ++j) {
-      const int32_t k = a0 + g + j * G;
-      if (k < a1) {
-        const Arc arc = arcs[dir == 0 ? in_arcs[k] : k];
-        other[j] = dir == 0 ? arc.src : arc.dest;
-        const int32_t c = arc.label + 1;
-        if (c >= 0 && c < cols) {
-          col[j] = c;
-          w[j] = arc.score;
-          if (col0 < 0) col0 = c;
-          else if (c != col0) same = false;
+      other[v][j] = 0;
+      col[v][j] = 0;
+      w[v][j] = -INFINITY;
+    }
+    if (s[v] >= 0) {
+      const int32_t *splits = dir == 0 ? in_splits : a_row_splits2;
+      const int32_t a0 = splits[f.state_off + s[v]], a1 = splits[f.state_off + s[v] + 1];
+#pragma unroll
+      for (int j = 0; j < kDeg; ++j) {
+        const int32_t k = a0 + g[v] + j * G[v];
+        if (k < a1) {
+          const Arc arc = arcs[dir == 0 ? in_arcs[k] : k];
+          other[v][j] = dir == 0 ? arc.src : arc.dest;
+          const int32_t c = arc.label + 1;
+          if (c >= 0 && c < cols) {
+            col[v][j] = c;
+            w[v][j] = arc.score;
+            if (col0[v] < 0) col0[v] = c;
+            else if (c != col0[v]) same = false;
+          }
         }
       }
     }
+    if (col0[v] < 0) col0[v] = 0;
+    g_max[v] = __reduce_max_sync(0xffffffffu, G[v]);  // widest lane group of this plan warp
   }
-  if (col0 < 0) col0 = 0;
-  const bool hoist = __all_sync(0xffffffffu, same);
-  const int32_t g_max = __reduce_max_sync(0xffffffffu, G);  // widest lane group of this warp
+  const bool hoist = __syncthreads_and(same);  // uniform over the CTA
   // step t (1..Tk) consumes dense row t-1 (forward) or Tk-t (backward)
   const float *base = scores + (int64_t)f.row0 * cols;
   auto issue_row = [&](int32_t step, int32_t slot) {
@@ -423,52 +434,63 @@ LanesViterbi(const FsaInfo *__restrict__ infos, int32_t n, const Arc *__restrict
   for (int32_t step = 1; step <= kVitAhead; ++step) issue_row(step, (step - 1) % kVitRing);
   float *grid = (dir == 0 ? fwd : bwd) + f.grid_off;
   for (int32_t q = tid; q < S; q += nt) {
-    const float v = (dir == 0 ? (q == 0) : (q == S - 1)) ? 0.0f : -INFINITY;
-    buf[0][q] = v;
-    grid[(int64_t)(dir == 0 ? 0 : Tk) * S + q] = v;
+    const float v0 = (dir == 0 ? (q == 0) : (q == S - 1)) ? 0.0f : -INFINITY;
+    buf[0][q] = v0;
+    grid[(int64_t)(dir == 0 ? 0 : Tk) * S + q] = v0;
   }
   const int64_t stride = dir == 0 ? (int64_t)S : -(int64_t)S;
-  float *gout = grid + (dir == 0 ? 1 : Tk - 1) * (int64_t)S + (s >= 0 ? s : 0);
-  const bool writer = s >= 0 && g == 0;
+  float *gout = grid + (dir == 0 ? 1 : Tk - 1) * (int64_t)S;
+  // the frame loop once per kind of CTA, so that the unrolled code of only one is fetched
+  auto frames = [&](auto hoist_tag) {
+    constexpr bool kHoist = decltype(hoist_tag)::value;
   for (int32_t t0 = 1; t0 <= Tk; t0 += kVitRing) {
 #pragma unroll
-    for (int u = 0; u < kVitRing; ++u) {
-      const int32_t t = t0 + u;
-      if (t > Tk) break;
-      CpAsyncWait<kVitAhead - 1>();  // this thread's part of row t has landed
-      __syncthreads();               // ... everyone's has; the scores of step t - 1 are complete
-      issue_row(t + kVitAhead, (u + kVitAhead) % kVitRing);
-      const float *cur = buf[u & 1];  // t0 is odd: (t - 1) & 1 == u & 1
-      const float *row = ring + u * cols_pad;
-      float best = -INFINITY;
-      if (hoist) {
+      for (int u = 0; u < kVitRing; ++u) {
+        const int32_t t = t0 + u;
+        if (t > Tk) break;
+        CpAsyncWait<kVitAhead - 1>();  // this thread's part of row t has landed
+        __syncthreads();               // ... everyone's has; the scores of step t - 1 are complete
+        issue_row(t + kVitAhead, (u + kVitAhead) % kVitRing);
+        const float *cur = buf[u & 1];  // t0 is odd: (t - 1) & 1 == u & 1
+        const float *row = ring + u * cols_pad;
+        float best[kV];
 #pragma unroll
-        for (int j = 0; j < kDeg; ++j) {
-          const float v = __fadd_rn(cur[other[j]], w[j]);
-          best = v > best ? v : best;
-        }
-      } else {
+        for (int v = 0; v < kV; ++v) {
+          best[v] = -INFINITY;
+          if (kHoist) {
 #pragma unroll
-        for (int j = 0; j < kDeg; ++j) {
-          const float v = __fadd_rn(__fadd_rn(cur[other[j]], w[j]), row[col[j]]);
-          best = v > best ? v : best;
-        }
-      }
+            for (int j = 0; j < kDeg; ++j) {
+              const float x = __fadd_rn(cur[other[v][j]], w[v][j]);
+              best[v] = x > best[v] ? x : best[v];
+            }
+          } else {
 #pragma unroll
-      for (int32_t d = 16; d > 0; d >>= 1) {
-        if (d < g_max) {  // warp-uniform
-          const float o = __shfl_down_sync(0xffffffffu, best, d);
-          if (g + d < G) best = o > best ? o : best;
+            for (int j = 0; j < kDeg; ++j) {
+              const float x = __fadd_rn(__fadd_rn(cur[other[v][j]], w[v][j]), row[col[v][j]]);
+              best[v] = x > best[v] ? x : best[v];
+            }
+          }
         }
+#pragma unroll
+        for (int v = 0; v < kV; ++v) {
+#pragma unroll
+          for (int32_t d = 16; d > 0; d >>= 1) {
+            if (d < g_max[v]) {  // warp-uniform
+              const float o = __shfl_down_sync(0xffffffffu, best[v], d);
+              if (g[v] + d < G[v]) best[v] = o > best[v] ? o : best[v];
+            }
+          }
+          if (s[v] >= 0 && g[v] == 0) {
+            if (kHoist) best[v] = __fadd_rn(best[v], row[col0[v]]);
+            buf[(u + 1) & 1][s[v]] = best[v];
+            gout[s[v]] = best[v];
+          }
+        }
+        gout += stride;
       }
-      if (writer) {
-        if (hoist) best = __fadd_rn(best, row[col0]);
-        buf[(u + 1) & 1][s] = best;
-        *gout = best;
-      }
-      gout += stride;
     }
-  }
+  };
+  if (hoist) frames(std::true_type{}); else frames(std::false_type{});
   CpAsyncWait<0>();
 }
 
@@ -480,9 +502,10 @@ int32_t LaunchLanesViterbi(const Layout &L, const k2b200_intersect_args *a,
   const int32_t cols_pad = (a->cols + 3) & ~3;
   const size_t smem = sizeof(float) * kVitRing * (size_t)cols_pad;
   K2B_REQUIRE(smem <= 200 * 1024, "too many columns for the lane Viterbi kernel");
-  K2B_CUDA_OK(cudaFuncSetAttribute(LanesViterbi<kLaneDeg>,
+  constexpr int kV = 1;  // plan lanes per thread (2 was slower: 0.39 against 0.30 ms at 500 frames)
+  K2B_CUDA_OK(cudaFuncSetAttribute(LanesViterbi<kLaneDeg, kV>,
                                    cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-  { LanesViterbi<kLaneDeg><<<grid, kLaneThreads, smem, stream>>>(
+  { LanesViterbi<kLaneDeg, kV><<<grid, kLaneThreads / kV, smem, stream>>>(
       d_infos, a->num_fsas, reinterpret_cast<const Arc *>(a->a_arcs), a->a_row_splits2,
       a->a_in_splits, a->a_in_arcs, a->scores, a->cols, cols_pad, fwd, bwd, plan, unfit);
     NoteLaunch(); }
