@@ -480,7 +480,7 @@ __global__ void __launch_bounds__(128)
 BandKeep(const BandInfo *__restrict__ infos, const int32_t *__restrict__ a_row_splits2,
          const float *__restrict__ vf, const float *__restrict__ vb, float beam,
          uint16_t *__restrict__ keep_bits, float *__restrict__ cutoffs,
-         unsigned long long *__restrict__ totals) {
+         unsigned long long *__restrict__ totals, int32_t count_arcs) {
   static_assert(K == 8 || K == 16, "keep bits are stored as bytes or 16-bit words");
   constexpr unsigned kAll = 0xffffffffu;
   const int32_t i = blockIdx.y;
@@ -521,9 +521,11 @@ BandKeep(const BandInfo *__restrict__ infos, const int32_t *__restrict__ a_row_s
       row[32 + lane] = 0;
     }
     n_states += __popc(keep);
-    for (uint32_t m = keep; m; m &= m - 1) {
-      const int32_t idx = f.state_off + s0 + __ffs(m) - 1;
-      n_cand += __ldg(a_row_splits2 + idx + 1) - __ldg(a_row_splits2 + idx);
+    if (count_arcs) {  // uniform; the host leaves it out when no count could reach max_arcs
+      for (uint32_t m = keep; m; m &= m - 1) {
+        const int32_t idx = f.state_off + s0 + __ffs(m) - 1;
+        n_cand += __ldg(a_row_splits2 + idx + 1) - __ldg(a_row_splits2 + idx);
+      }
     }
   }
 #pragma unroll
@@ -1653,7 +1655,8 @@ int32_t k2b200_band_loss_forward(const k2b200_band_loss_args *args, void *worksp
           reinterpret_cast<const float *>(ws + L.off_vb), beam,                                 \
           reinterpret_cast<uint16_t *>(ws + L.off_keep),                                        \
           reinterpret_cast<float *>(ws + L.off_cutoffs),                                        \
-          reinterpret_cast<unsigned long long *>(ws + L.off_totals)); NoteLaunch(); }
+          reinterpret_cast<unsigned long long *>(ws + L.off_totals),                            \
+          L.arc_frames > args->max_arcs ? 1 : 0); NoteLaunch(); }
       if (L.max_states <= 256) K2B_BAND_KEEP(8) else K2B_BAND_KEEP(kPrepK)
 #undef K2B_BAND_KEEP
       // the host reads the counts behind BandKeep, while what follows runs
