@@ -672,8 +672,8 @@ def run_ours(args):
 
 
 # ncu dram__bytes_read.sum + dram__bytes_write.sum of one launch on ctc_large (profiles/)
-NCU_TRAFFIC = {"BandViterbi": 289.1e6, "BandKeep+BandPrep": 296.6e6, "BandChainLists": 99.3e6,
-               "BandGrad": 78.3e6}
+NCU_TRAFFIC = {"BandViterbi": 289.5e6, "BandKeep+BandPrep": 296.5e6, "BandChainLists": 99.4e6,
+               "BandGrad": 77.8e6}
 
 
 # --------------------------------------------------------------------------- decoding
