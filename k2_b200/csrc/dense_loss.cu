@@ -562,15 +562,16 @@ ArcMasks(const FsaInfo *__restrict__ infos, int32_t n, int64_t total_levels,
 
 // ---------------------------------------------------------------------------
 // The alpha / beta recursion for planned graphs, driven by the masks of ArcMasks:
-// same arithmetic and ring as GridChainLanes, but a frame needs no Viterbi score and
-// no test - one mask byte per lane says which of its arcs to add.  A ring slot holds
-// the exp() part of the packed dense row (kPBytes reserved for it) and the frame's row of
-// mask bytes.  Slots and state buffers have compile-time sizes and the frame loop is
-// unrolled over the ring, so every shared-memory address is a register (an arc's byte
-// offset, fixed for the whole call) plus a constant.  When all arcs of a warp's lanes carry
-// one label (walking forward in a graph where every state has one entering label),
-// exp(dense score) multiplies the sum once per state instead of every term.  Every state
-// is written to the grid (0 for pruned ones).
+// same arithmetic as GridChainLanes, but a frame needs no Viterbi score and no test - one
+// mask byte per lane says which of its arcs to add.  The packed dense rows and the rows of
+// mask bytes of kU consecutive frames are one block of memory each (ascending walking
+// forward, descending walking backward): a batch of kU frames arrives by TWO bulk copies,
+// three batches in a ring (a pair of copies per frame kept thread 0, and with it every
+// barrier, busy).  The frames of a batch are unrolled; there is one frame loop per kind
+// of CTA (see kHoist) so that the code a CTA runs stays small.  When all arcs of a CTA's
+// lanes carry the label of their state (walking forward in a graph where every state has
+// one entering label), exp(dense score) multiplies the sum once per state instead of every
+// term.  Every state is written to the grid (0 for pruned ones).
 // ---------------------------------------------------------------------------
 constexpr int kMaskedBatches = 3;  // batches of kU frames in the ring
 
