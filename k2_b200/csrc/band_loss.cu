@@ -1697,7 +1697,11 @@ int32_t k2b200_band_loss_forward(const k2b200_band_loss_args *args, void *worksp
     K2B_FORWARD(readback.End(h_totals));
     K2B_REQUIRE((h_totals[5] & kStatusLate) == 0,
                 "a copy of log-prob rows into shared memory did not complete in time");
+    const float beam_before = beam;
     if (!BandReduceBeam(args, h_totals, &beam)) break;
+    K2B_LOG(kLogInfo, "band loss: %lld states / %lld arcs exceed max_states %d / max_arcs %d, "
+            "output beam %g -> %g", h_totals[0], h_totals[2], args->max_states, args->max_arcs,
+            (double)beam_before, (double)beam);
     K2B_REQUIRE(iter < 200, "output beam reduction did not converge");
   }
   if (beam_used) *beam_used = beam;
@@ -1768,6 +1772,9 @@ int32_t k2b200_band_loss_status(const k2b200_band_loss_args *args, void *workspa
   K2B_CUDA_OK(cudaMemcpyAsync(status, reinterpret_cast<char *>(workspace) + L.off_status,
                               sizeof(int32_t), cudaMemcpyDeviceToHost, stream));
   K2B_CUDA_OK(cudaStreamSynchronize(stream));
+  if (*status & kStatusLate)
+    K2B_LOG(kLogWarning, "band loss: a bounded wait for a copy into shared memory gave up; the "
+            "results of that call are invalid");
   return kOk;
 }
 

@@ -29,6 +29,18 @@ enum Status : int32_t {
 void SetError(const char *fmt, ...);
 const char *LastError();
 
+// Log lines on stderr, filtered by the environment variable K2_LOG_LEVEL (TRACE, DEBUG, INFO,
+// WARNING, ERROR or FATAL; default INFO), as the reference's logger (k2/csrc/log.h:297-352).
+// The library logs rare events only - a beam reduction, a graph sent to a fallback kernel,
+// a bounded wait that gave up - never anything per call on the usual path.
+enum LogLevel : int { kLogTrace = 0, kLogDebug, kLogInfo, kLogWarning, kLogError, kLogFatal };
+bool LogEnabled(LogLevel level);
+void LogLine(LogLevel level, const char *fmt, ...);
+#define K2B_LOG(level, ...)                                             \
+  do {                                                                  \
+    if (::k2b::LogEnabled(level)) ::k2b::LogLine(level, __VA_ARGS__);   \
+  } while (0)
+
 #define K2B_CUDA_OK(expr)                                                      \
   do {                                                                         \
     cudaError_t e__ = (expr);                                                  \

@@ -2016,7 +2016,11 @@ int32_t k2b200_dense_loss_forward(const k2b200_intersect_args *args, void *works
     if (!need_count) break;
     long long h_totals[5];
     K2B_FORWARD(SideReadBack(ws + L.off_totals, sizeof(h_totals), h_totals));
+    const float beam_before = beam;
     if (!ReduceBeam(args, h_totals, &beam)) break;
+    K2B_LOG(kLogInfo, "dense loss: %lld states / %lld arcs exceed max_states %d / max_arcs %d, "
+            "output beam %g -> %g", h_totals[0], h_totals[2], args->max_states, args->max_arcs,
+            (double)beam_before, (double)beam);
     K2B_REQUIRE(iter < 200, "output beam reduction did not converge");
   }
   if (beam_used) *beam_used = beam;

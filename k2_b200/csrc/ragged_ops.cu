@@ -6,6 +6,9 @@
 #include <nvtx3/nvToolsExt.h>
 #include <atomic>
 #include <cstring>
+#include <cstdlib>
+#include <strings.h>
+#include <cstdio>
 #include <mutex>
 #include <vector>
 
@@ -25,6 +28,31 @@ void SetError(const char *fmt, ...) {
   va_end(ap);
 }
 const char *LastError() { return g_error; }
+
+// ----------------------------------------------------------------------------
+// logger
+// ----------------------------------------------------------------------------
+static int ReadLogLevel() {
+  const char *v = getenv("K2_LOG_LEVEL");
+  if (v == nullptr) return kLogInfo;
+  static const char *const names[] = {"TRACE", "DEBUG", "INFO", "WARNING", "ERROR", "FATAL"};
+  for (int k = 0; k < 6; ++k)
+    if (strcasecmp(v, names[k]) == 0) return k;
+  return kLogInfo;
+}
+bool LogEnabled(LogLevel level) {
+  static const int threshold = ReadLogLevel();
+  return (int)level >= threshold;
+}
+void LogLine(LogLevel level, const char *fmt, ...) {
+  static const char kTag[] = "TDIWEF";
+  char line[1024];
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(line, sizeof(line), fmt, ap);
+  va_end(ap);
+  fprintf(stderr, "[%c] k2b200: %s\n", kTag[level], line);
+}
 
 // ----------------------------------------------------------------------------
 // launch counter and phase timers
