@@ -162,16 +162,30 @@ class PeerLossReducer:
                 dist.all_gather_object(handles, bytes(handle.raw), group=group)
             self.bufs = (ctypes.c_void_p * self.world)()
             self.opened = []
-            for r in range(self.world):
-                if r == self.rank:
-                    self.bufs[r] = self.local
-                else:
-                    p = ctypes.c_void_p()
-                    _lib.check(_lib.lib.k2b200_peer_reduce_open(handles[r], ctypes.byref(p)))
-                    self.bufs[r] = p.value
-                    self.opened.append(p.value)
+            error = None
+            try:
+                for r in range(self.world):
+                    if r == self.rank:
+                        self.bufs[r] = self.local
+                    else:
+                        p = ctypes.c_void_p()
+                        _lib.check(_lib.lib.k2b200_peer_reduce_open(handles[r], ctypes.byref(p)))
+                        self.bufs[r] = p.value
+                        self.opened.append(p.value)
+            except RuntimeError as e:  # e.g. no peer access between two of the GPUs
+                error = e
             if self.world > 1:
-                dist.barrier(group=group)  # every rank has mapped every buffer
+                # every rank has mapped every buffer - or none goes on: a rank that failed must
+                # not leave the others waiting for it in the first exchange
+                ok = torch.tensor([0 if error is not None else 1], dtype=torch.int32,
+                                  device=self.device)
+                dist.all_reduce(ok, op=dist.ReduceOp.MIN, group=group)
+                if int(ok.item()) == 0:
+                    self.close()
+                    raise RuntimeError("PeerLossReducer: a rank could not map a peer's buffer"
+                                       + (f" ({error})" if error is not None else ""))
+            elif error is not None:
+                raise error
         self.stream = torch.cuda.Stream(self.device)
         self.ready = torch.cuda.Event()
         self.out = [torch.zeros(2, dtype=torch.float64, device=self.device) for _ in range(2)]
