@@ -706,7 +706,10 @@ int32_t k2b200_fsa_arc_post_backprop(const k2b200_fsa_view *fsas, int32_t use_do
  *     seq: 1, 2, 3, ... - the same on every rank for the same step.  Every rank of the world
  *     must make the call; a rank's launch waits (occupying one CTA) for the others'.  That
  *     wait is bounded: after poll_limit polls (negative: the default, a few seconds) bit 0
- *     of the status word is set and out is invalid; nothing hangs or traps.
+ *     of the status word is set and out is invalid; nothing hangs or traps.  With
+ *     after_stream not NULL (and not `stream`) the launch on `stream` is ordered behind
+ *     everything after_stream holds at the time of the call: the stream that computes
+ *     `values` never waits for another rank, the exchange runs beside it.
  *   k2b200_peer_reduce_status: waits for `stream`, returns the status word.
  * ------------------------------------------------------------------------- */
 #define K2B200_IPC_HANDLE_BYTES 64
@@ -717,7 +720,8 @@ int32_t k2b200_peer_reduce_destroy(void *local_buf);
 int32_t k2b200_loss_sum_all_reduce(const void *values, int32_t n, int32_t values_are_f32,
                                    double sign, double num_frames, void *const *bufs,
                                    int32_t rank, int32_t world, uint64_t seq,
-                                   int32_t poll_limit, double *out, void *stream);
+                                   int32_t poll_limit, double *out, void *stream,
+                                   void *after_stream);
 int32_t k2b200_peer_reduce_status(void *local_buf, void *stream, int32_t *status);
 
 #ifdef __cplusplus

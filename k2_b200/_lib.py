@@ -222,7 +222,7 @@ _sig("k2b200_peer_reduce_close", c_i32, [c_vp])
 _sig("k2b200_peer_reduce_destroy", c_i32, [c_vp])
 _sig("k2b200_loss_sum_all_reduce", c_i32,
      [c_vp, c_i32, c_i32, ctypes.c_double, ctypes.c_double, ctypes.POINTER(c_vp), c_i32, c_i32,
-      ctypes.c_uint64, c_i32, c_vp, c_vp])
+      ctypes.c_uint64, c_i32, c_vp, c_vp, c_vp])
 _sig("k2b200_peer_reduce_status", c_i32, [c_vp, c_vp, ctypes.POINTER(c_i32)])
 
 EXPORTED = [

@@ -105,6 +105,20 @@ LossSumAllReduce(const T *__restrict__ values, int32_t n, double sign, double fr
   }
 }
 
+// One event per device and host thread for ordering a launch behind another stream (a wait
+// takes the event's state at the time of the call, so the event is reused right away).
+int32_t ForkEvent(cudaEvent_t *ev) {
+  constexpr int kMaxDevices = 64;
+  thread_local cudaEvent_t events[kMaxDevices] = {nullptr};
+  int dev = 0;
+  K2B_CUDA_OK(cudaGetDevice(&dev));
+  K2B_REQUIRE(dev >= 0 && dev < kMaxDevices, "device ordinal %d", dev);
+  if (events[dev] == nullptr)
+    K2B_CUDA_OK(cudaEventCreateWithFlags(&events[dev], cudaEventDisableTiming));
+  *ev = events[dev];
+  return kOk;
+}
+
 }  // namespace k2b
 
 using namespace k2b;
@@ -146,8 +160,10 @@ int32_t k2b200_peer_reduce_destroy(void *local_buf) {
 int32_t k2b200_loss_sum_all_reduce(const void *values, int32_t n, int32_t values_are_f32,
                                    double sign, double num_frames, void *const *bufs,
                                    int32_t rank, int32_t world, uint64_t seq,
-                                   int32_t poll_limit, double *out, void *stream_v) {
+                                   int32_t poll_limit, double *out, void *stream_v,
+                                   void *after_stream_v) {
   cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_v);
+  cudaStream_t after = reinterpret_cast<cudaStream_t>(after_stream_v);
   K2B_REQUIRE(values && bufs && out, "NULL pointer");
   K2B_REQUIRE(world >= 1 && world <= kMaxPeers, "world size %d outside 1..%d", world, kMaxPeers);
   K2B_REQUIRE(rank >= 0 && rank < world, "rank %d outside the world of %d", rank, world);
@@ -161,6 +177,13 @@ int32_t k2b200_loss_sum_all_reduce(const void *values, int32_t n, int32_t values
   int32_t *status = reinterpret_cast<int32_t *>(reinterpret_cast<char *>(bufs[rank]) +
                                                 sizeof(PeerSlot) * 2 * kMaxPeers);
   if (poll_limit < 0) poll_limit = 20000000;  // a few seconds
+  if (after != nullptr && after != stream) {
+    // behind what `after` holds now (the kernels that produce `values`)
+    cudaEvent_t ev = nullptr;
+    K2B_FORWARD(ForkEvent(&ev));
+    K2B_CUDA_OK(cudaEventRecord(ev, after));
+    K2B_CUDA_OK(cudaStreamWaitEvent(stream, ev, 0));
+  }
   if (values_are_f32) {
     LossSumAllReduce<float><<<1, kPeerThreads, 0, stream>>>(
         reinterpret_cast<const float *>(values), n, sign, num_frames, peers, rank, world,

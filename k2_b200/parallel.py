@@ -187,29 +187,37 @@ class PeerLossReducer:
             elif error is not None:
                 raise error
         self.stream = torch.cuda.Stream(self.device)
-        self.ready = torch.cuda.Event()
         self.out = [torch.zeros(2, dtype=torch.float64, device=self.device) for _ in range(2)]
+        # what a step needs, looked up once: the host side of a step is a single call
+        self._stream = self.stream.cuda_stream
+        self._out_ptr = [t.data_ptr() for t in self.out]
+        self._out = [(t[0], t[1]) for t in self.out]
+        self._call = _lib.lib.k2b200_loss_sum_all_reduce
+        self._index = self.device.index if self.device.index is not None \
+            else torch.cuda.current_device()
         self.seq = 0
         self.pending = False
 
     def submit(self, losses: torch.Tensor, num_frames: int, sign: float = 1.0) -> None:
         """losses: a 0-dim or 1-dim float32 / float64 device tensor; its sum times `sign`
-        is this rank's loss."""
+        is this rank's loss.  The exchange is queued on the reducer's stream behind what the
+        current stream holds."""
         assert not self.pending, "result() of the previous step has not been taken"
-        losses = losses.detach()
         assert losses.is_cuda and losses.dtype in (torch.float32, torch.float64)
         if not losses.is_contiguous():
             losses = losses.contiguous()
         self.seq += 1
-        main = torch.cuda.current_stream(self.device)
-        self.ready.record(main)
-        self.stream.wait_event(self.ready)
         losses.record_stream(self.stream)
-        with torch.cuda.device(self.device):
-            self._lib.check(self._lib.lib.k2b200_loss_sum_all_reduce(
-                losses.data_ptr(), losses.numel(), int(losses.dtype == torch.float32),
-                float(sign), float(num_frames), self.bufs, self.rank, self.world, self.seq,
-                self.poll_limit, self.out[self.seq & 1].data_ptr(), self.stream.cuda_stream))
+        args = (losses.data_ptr(), losses.numel(), losses.dtype == torch.float32, sign,
+                num_frames, self.bufs, self.rank, self.world, self.seq, self.poll_limit,
+                self._out_ptr[self.seq & 1], self._stream)
+        if torch.cuda.current_device() == self._index:
+            rc = self._call(*args, self._lib.stream_of(self.device))
+        else:
+            with torch.cuda.device(self.device):
+                rc = self._call(*args, self._lib.stream_of(self.device))
+        if rc != 0:
+            self._lib.check(rc)
         self.pending = True
 
     def result(self, join: bool = True) -> Tuple[torch.Tensor, torch.Tensor]:
@@ -222,8 +230,7 @@ class PeerLossReducer:
         self.pending = False
         if join:
             torch.cuda.current_stream(self.device).wait_stream(self.stream)
-        out = self.out[self.seq & 1]
-        return out[0], out[1]
+        return self._out[self.seq & 1]
 
     def status(self) -> int:
         """Waits for the exchange stream; bit 0 = a bounded wait for a peer gave up (the

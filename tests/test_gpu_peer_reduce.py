@@ -46,7 +46,7 @@ def test_bounded_wait_for_absent_peer():
         out = torch.zeros(2, dtype=torch.float64, device=dev)
         stream = torch.cuda.current_stream(dev).cuda_stream
         _lib.check(_lib.lib.k2b200_loss_sum_all_reduce(
-            vals.data_ptr(), 4, 0, 1.0, 10.0, bufs, 0, 2, 1, 1000, out.data_ptr(), stream))
+            vals.data_ptr(), 4, 0, 1.0, 10.0, bufs, 0, 2, 1, 1000, out.data_ptr(), stream, None))
         st = ctypes.c_int32()
         _lib.check(_lib.lib.k2b200_peer_reduce_status(a.value, stream, ctypes.byref(st)))
         assert st.value & 1
