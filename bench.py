@@ -380,6 +380,12 @@ def run_ours(args):
     if world > 1 and os.environ.get("K2B_NO_NUMA_BIND") is None:
         from k2_b200.parallel import bind_to_gpu_numa_node
         numa = bind_to_gpu_numa_node(dev)  # before the pinned host buffers are allocated
+    if world > 1:
+        every = [None] * world
+        dist.all_gather_object(every, numa)
+        numa = {"by_rank": [[n.get("node"), n.get("cpus_on_node"), n.get("cpus_allowed"),
+                             int(n.get("bound", False))] for n in every],
+                "columns": ["node", "cpus_on_node", "cpus_allowed", "bound"]}
     # every rank owns a whole batch (weak scaling); seeds differ per rank
     w = make_workload(args, rank, syn)
     frames = w.num_frames
@@ -459,6 +465,7 @@ def run_ours(args):
         if profile:
             phases = _lib.profile_read()
             _lib.profile_enable(False)
+        timed.own_ms = ms
         return max_over_ranks(ms), wall, launches, phases
 
     def timed_from_host(nsteps, pipelined):
@@ -493,17 +500,20 @@ def run_ours(args):
     for _ in range(warm):
         step(dev_lp)
     ms, wall, launches, _ = timed(args.steps, lambda: step(dev_lp))
+    own_ms = timed.own_ms / args.steps
     # the same steps again with per-phase events, for the roofline of the top kernel
     _, _, _, phases = timed(args.steps, lambda: step(dev_lp), profile=True)
     kernels = _lib.profile_kernels()
     # time inside this library's kernels per step on every rank
     busy = sum(v[0] for k, v in phases.items()) / args.steps
-    busy_by_rank = [busy]
+    busy_by_rank, ms_by_rank = [busy], [own_ms]
     if dist is not None:
-        t = torch.zeros(world, dtype=torch.float64, device=dev)
-        t[rank] = busy
+        t = torch.zeros(2, world, dtype=torch.float64, device=dev)
+        t[0, rank] = busy
+        t[1, rank] = own_ms
         dist.all_reduce(t)
-        busy_by_rank = [float(x) for x in t.tolist()]
+        busy_by_rank = [float(x) for x in t[0].tolist()]
+        ms_by_rank = [float(x) for x in t[1].tolist()]
     timed_from_host(2, False)
     serial_ms = timed_from_host(args.steps, False)
     timed_from_host(2, True)
@@ -633,6 +643,7 @@ def run_ours(args):
         "phases_ms_per_step": {k: v[0] / args.steps for k, v in phases.items()},
         "phase_kernels": {k: kernels[k] for k, v in phases.items() if v[0] > 0},
         "kernel_ms_per_step_by_rank": busy_by_rank,
+        "ms_per_step_by_rank": ms_by_rank,
         "numa": numa,
         "lattice": {"arcs": A_out, "states": S_out, "graph_arcs": A, "arc_frames": arc_frames,
                     "grid_states": grid_states},

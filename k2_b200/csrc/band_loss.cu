@@ -115,7 +115,8 @@ struct __align__(16) BandFactor {
 static_assert(sizeof(BandFactor) == 32, "BandFactor must be 32 bytes");
 constexpr int kDstByte = 28;
 constexpr uint32_t kNoDst = 255;
-constexpr int kMaxListed = 95;  // entries of a level that the register recursion handles
+constexpr int kMaxRegs = 4;     // values of a level that a lane of the register recursion holds
+constexpr int kMaxListed = 32 * kMaxRegs - 1;  // entries of a level that it handles (one lane is padding)
 // words of BandPrep's per-state scratch: bit 15 = the state survives, bits 0-8 = its
 // position in the level's list, bits 9-11 = entering-arc bits
 constexpr uint32_t kMetaKept = 0x8000u, kMetaPos = 0x1ffu;
@@ -733,7 +734,7 @@ BandPrep(const BandInfo *__restrict__ infos, const BandState *__restrict__ tab,
 
 // ---------------------------------------------------------------------------
 // alpha (dir 0) and beta (dir 1) over the lists, in registers.  grid = (2, pairs), one warp
-// per CTA.  Lane j holds the value of entry j (and j + 32, j + 64) of the current level's
+// per CTA.  Lane j holds the value of entry j (and j + 32, j + 64, j + 96) of the current level's
 // list; an entry says at which POSITIONS of the previous list its neighbours are, so the
 // values it needs come by shuffles from the lanes that hold them:
 //   alpha_l[j] = sum_d pw_l[j][d] * alpha_{l-1}[src_l[j][d]]
@@ -752,7 +753,7 @@ BandPrep(const BandInfo *__restrict__ infos, const BandState *__restrict__ tab,
 // ---------------------------------------------------------------------------
 constexpr int kRescale = 8;                     // levels between changes of the shared scale
 constexpr int kChainSlots = 3;                  // chunks in flight
-constexpr int kFacSlot = kPrepLevels * 96;      // BandFactor entries of a chunk: 16 levels of 3 x 32
+constexpr int kFacSlot = kPrepLevels * 32 * kMaxRegs;  // BandFactor entries of a chunk's levels
 constexpr int kChainMaxChunks = 4096;           // of a graph: 65534 frames
 constexpr int kSlotItems = kPrepLevels * 128;   // BandItem entries likewise (BandChainExact)
 
@@ -798,8 +799,9 @@ struct ChunkRing {
 // pw[d] * value of the level before (backward); both are replaced by this level's.
 template <int DIR, int RC, int RP, bool kScaled>
 __device__ __forceinline__ void ChainLevel(const BandFactor *rec, double *__restrict__ out,
-                                           double scale, double (&v)[3], double (&pc)[3][3],
-                                           int32_t &hi_max, uint32_t &min_hi) {
+                                           double scale, double (&v)[kMaxRegs],
+                                           double (&pc)[3][kMaxRegs], int32_t &hi_max,
+                                           uint32_t &min_hi) {
   constexpr unsigned kAll = 0xffffffffu;
   double nv[RC], pw[RC][3];
 #pragma unroll
@@ -823,6 +825,10 @@ __device__ __forceinline__ void ChainLevel(const BandFactor *rec, double *__rest
       if (RP > 2) {
         const double x2 = __shfl_sync(kAll, DIR == 0 ? v[2] : pc[d][2], (int)pos);
         x[d] = pos >= 64u ? x2 : x[d];
+      }
+      if (RP > 3) {
+        const double x3 = __shfl_sync(kAll, DIR == 0 ? v[3] : pc[d][3], (int)pos);
+        x[d] = pos >= 96u ? x3 : x[d];
       }
     }
     double acc;
@@ -849,19 +855,19 @@ __device__ __forceinline__ void ChainLevel(const BandFactor *rec, double *__rest
 template <int DIR>
 __device__ __forceinline__ void ChainLevelAny(int32_t rc, int32_t rp, const BandFactor *rec,
                                               double *__restrict__ out, double scale,
-                                              double (&v)[3], double (&pc)[3][3],
-                                              int32_t &hi_max, uint32_t &min_hi) {
-  switch (rc * 4 + rp) {
-    case 5: ChainLevel<DIR, 1, 1, true>(rec, out, scale, v, pc, hi_max, min_hi); break;
-    case 6: ChainLevel<DIR, 1, 2, true>(rec, out, scale, v, pc, hi_max, min_hi); break;
-    case 7: ChainLevel<DIR, 1, 3, true>(rec, out, scale, v, pc, hi_max, min_hi); break;
-    case 9: ChainLevel<DIR, 2, 1, true>(rec, out, scale, v, pc, hi_max, min_hi); break;
-    case 10: ChainLevel<DIR, 2, 2, true>(rec, out, scale, v, pc, hi_max, min_hi); break;
-    case 11: ChainLevel<DIR, 2, 3, true>(rec, out, scale, v, pc, hi_max, min_hi); break;
-    case 13: ChainLevel<DIR, 3, 1, true>(rec, out, scale, v, pc, hi_max, min_hi); break;
-    case 14: ChainLevel<DIR, 3, 2, true>(rec, out, scale, v, pc, hi_max, min_hi); break;
-    default: ChainLevel<DIR, 3, 3, true>(rec, out, scale, v, pc, hi_max, min_hi); break;
+                                              double (&v)[kMaxRegs],
+                                              double (&pc)[3][kMaxRegs], int32_t &hi_max,
+                                              uint32_t &min_hi) {
+#define K2B_LEVEL(RC, RP) \
+  case RC * 8 + RP: ChainLevel<DIR, RC, RP, true>(rec, out, scale, v, pc, hi_max, min_hi); break;
+  switch (rc * 8 + rp) {
+    K2B_LEVEL(1, 1) K2B_LEVEL(1, 2) K2B_LEVEL(1, 3) K2B_LEVEL(1, 4)
+    K2B_LEVEL(2, 1) K2B_LEVEL(2, 2) K2B_LEVEL(2, 3) K2B_LEVEL(2, 4)
+    K2B_LEVEL(3, 1) K2B_LEVEL(3, 2) K2B_LEVEL(3, 3) K2B_LEVEL(3, 4)
+    K2B_LEVEL(4, 1) K2B_LEVEL(4, 2) K2B_LEVEL(4, 3)
+    default: ChainLevel<DIR, 4, 4, true>(rec, out, scale, v, pc, hi_max, min_hi); break;
   }
+#undef K2B_LEVEL
 }
 
 // The new scale after kRescale levels: the exponent of the largest value since the last one.
@@ -881,8 +887,8 @@ constexpr int kChainUnroll = 1;  // (fully unrolled: 178 us for ctc_large; 1: 14
 
 template <int DIR, int RC>
 __device__ __forceinline__ void ChainRest(const BandFactor *base, double *__restrict__ ob,
-                                          int32_t *__restrict__ osc, int lane, double (&v)[3],
-                                          double (&pc)[3][3], int32_t &hi_max, uint32_t &min_hi,
+                                          int32_t *__restrict__ osc, int lane, double (&v)[kMaxRegs],
+                                          double (&pc)[3][kMaxRegs], int32_t &hi_max, uint32_t &min_hi,
                                           int32_t &Ksh) {
   static_assert(kPrepLevels == 2 * kRescale, "a chunk is two groups of kRescale levels");
   constexpr int kStep = DIR == 0 ? 1 : -1;
@@ -949,9 +955,9 @@ __device__ __forceinline__ void ChainWalk(const BandInfo &f, int32_t i, BandFact
   };
   if (lane == 0)
     for (int32_t k = 0; k < kChainSlots; ++k) issue();
-  double v[3] = {0.0, 0.0, 0.0}, pc[3][3];
+  double v[kMaxRegs], pc[3][kMaxRegs];
 #pragma unroll
-  for (int d = 0; d < 3; ++d) pc[d][0] = pc[d][1] = pc[d][2] = 0.0;
+  for (int r = 0; r < kMaxRegs; ++r) v[r] = pc[0][r] = pc[1][r] = pc[2][r] = 0.0;
   int32_t Ksh = 0;
   int32_t hi_max = 0;              // largest high word since the last change of scale
   uint32_t min_hi = 0xffffffffu;   // smallest (high word - 1), zeros apart
@@ -978,9 +984,10 @@ __device__ __forceinline__ void ChainWalk(const BandInfo &f, int32_t i, BandFact
         // the first level holds one state, with the value 1: the start state walking
         // forward, the final state walking backward
         v[0] = lane == 0 ? 1.0 : 0.0;
-        v[1] = v[2] = 0.0;
 #pragma unroll
-        for (int r = 0; r < 3; ++r) {
+        for (int r = 1; r < kMaxRegs; ++r) v[r] = 0.0;
+#pragma unroll
+        for (int r = 0; r < kMaxRegs; ++r) {
           if (r >= rc) break;  // uniform
           out[32 * r] = v[r];
           if (DIR == 1) {
@@ -1001,7 +1008,8 @@ __device__ __forceinline__ void ChainWalk(const BandInfo &f, int32_t i, BandFact
     if (nl == kPrepLevels) {
       if (rc == 1) ChainRest<DIR, 1>(base, ob, osc, lane, v, pc, hi_max, min_hi, Ksh);
       else if (rc == 2) ChainRest<DIR, 2>(base, ob, osc, lane, v, pc, hi_max, min_hi, Ksh);
-      else ChainRest<DIR, 3>(base, ob, osc, lane, v, pc, hi_max, min_hi, Ksh);
+      else if (rc == 3) ChainRest<DIR, 3>(base, ob, osc, lane, v, pc, hi_max, min_hi, Ksh);
+      else ChainRest<DIR, 4>(base, ob, osc, lane, v, pc, hi_max, min_hi, Ksh);
     }
     rp = rc;
     __syncwarp();  // every lane has read the slot

@@ -299,23 +299,34 @@ class HostPrefetcher:
         return self.bufs[slot]
 
 
-def bind_to_gpu_numa_node(device) -> dict:
+def bind_to_gpu_numa_node(device, cpus_per_gpu: int = 4) -> dict:
     """Restricts this process to the CPUs of the NUMA node its GPU hangs off, so that
     pinned host buffers allocated afterwards (first touch) and the threads that feed
     the GPU sit next to its PCIe root: with one process per GPU on a multi-socket host,
     copies that cross the socket interconnect share its bandwidth with every other
     rank.  Reads the node from sysfs; does nothing when the topology cannot be read or
-    the node's CPUs are not among those the process may use.  Returns what it did."""
+    the node's CPUs are not among those the process may use, and does not bind either
+    when that would leave fewer than `cpus_per_gpu` CPUs for each visible GPU of the
+    node (a container whose CPU set lies mostly on the other socket: ranks that crowd
+    onto two or three CPUs run several times slower than ranks that cross the
+    interconnect).  Returns what it did."""
     import os
     info = {"bound": False}
-    try:
-        props = torch.cuda.get_device_properties(torch.device(device))
+
+    def node_of(index):
+        props = torch.cuda.get_device_properties(index)
         bus = f"{props.pci_domain_id:04x}:{props.pci_bus_id:02x}:{props.pci_device_id:02x}.0"
         with open(f"/sys/bus/pci/devices/{bus}/numa_node") as f:
-            node = int(f.read().strip())
+            return bus, int(f.read().strip())
+
+    try:
+        device = torch.device(device)
+        index = device.index if device.index is not None else torch.cuda.current_device()
+        bus, node = node_of(index)
         info.update(pci=bus, node=node)
         if node < 0:
             return info
+        gpus_on_node = sum(1 for k in range(torch.cuda.device_count()) if node_of(k)[1] == node)
         with open(f"/sys/devices/system/node/node{node}/cpulist") as f:
             cpus = set()
             for part in f.read().strip().split(","):
@@ -323,8 +334,8 @@ def bind_to_gpu_numa_node(device) -> dict:
                 cpus.update(range(int(lo), int(hi or lo) + 1))
         allowed = os.sched_getaffinity(0)
         mine = cpus & allowed
-        info["cpus_on_node"] = len(mine)
-        if mine and mine != allowed:
+        info.update(cpus_on_node=len(mine), cpus_allowed=len(allowed), gpus_on_node=gpus_on_node)
+        if mine and mine != allowed and len(mine) >= cpus_per_gpu * gpus_on_node:
             os.sched_setaffinity(0, mine)
             info["bound"] = True
     except (OSError, ValueError, AttributeError, RuntimeError, AssertionError) as e:

@@ -206,6 +206,43 @@ def test_long_transcripts_sixteen_states_per_lane():
     compare(fsa_to_host(graphs), torch.from_numpy(x), seg, 10.0, tag="long")
 
 
+def _most_states_kept(a, lp, seg, beam):
+    """Per sequence, the largest number of distinct graph states on one frame of the
+    oracle's pruned lattice."""
+    scores, brs = host_scores(lp, seg)
+    lat = oracle.intersect_dense(a, scores, brs, beam)
+    row = lat.arc_map_b // scores.shape[1]
+    src = a.arcs[lat.arc_map_a, 0]
+    out = []
+    for i in range(len(brs) - 1):
+        m = (row >= brs[i]) & (row < brs[i + 1])
+        key = np.unique((row[m] - brs[i]).astype(np.int64) * 100000 + src[m])
+        out.append(int(np.bincount((key // 100000).astype(np.int64)).max()))
+    return out
+
+
+def test_levels_with_about_a_hundred_surviving_states():
+    # flat log-probs and wide beams: levels with 96..127 surviving states take four
+    # registers per lane of the list recursion, levels with more send the graph to the
+    # (mantissa, exponent) recursion; both next to graphs that need neither
+    rng = np.random.default_rng(11)
+    from k2_b200.fsa_algo import ctc_graph
+    from gpu_util import fsa_to_host
+    C, T, n = 40, 200, 3
+    symbols = [rng.integers(1, C, size=int(L)).tolist() for L in (95, 90, 60)]
+    a = fsa_to_host(ctc_graph(symbols, device=DEV))
+    x = (rng.normal(size=(n, T, C)) * 0.5).astype(np.float32)
+    x = x - np.log(np.exp(x.astype(np.float64)).sum(-1, keepdims=True)).astype(np.float32)
+    lp = torch.from_numpy(x)
+    seg = torch.tensor([[0, 0, 200], [1, 0, 196], [2, 0, 190]], dtype=torch.int32)
+    widest = {beam: _most_states_kept(a, lp, seg, beam) for beam in (14.0, 20.0, 40.0)}
+    assert 96 <= widest[14.0][0] <= 127 and widest[14.0][2] <= 95, widest
+    assert all(96 <= w <= 127 for w in widest[20.0]), widest
+    assert widest[40.0][0] > 127 and 96 <= widest[40.0][2] <= 127, widest
+    for beam in widest:
+        compare(a, lp, seg, beam, tot_grad=rng.normal(size=n), tag=f"beam {beam}")
+
+
 def test_same_numbers_as_the_general_kernels_and_the_lattice():
     import k2_b200 as k2
     from gpu_util import host_to_fsa
