@@ -633,11 +633,17 @@ def _band_loss_args_uncached(a_fsas: Fsa, b_fsas: DenseFsaVec,
             return None  # the general path reports the error
     elif a.num_fsas != b_fsas.dim0():
         return None
-    h_rs1 = np.ascontiguousarray(a.h_row_splits1, dtype=np.int32)
-    if int(np.diff(h_rs1).max(initial=0)) > 512:
-        return None
     states, arcs, ok = a.band_tables()
     if not ok:
+        return None
+    # host arrays of the graphs, kept with the tables (which follow the arc tensor's version)
+    host = getattr(a, "_band_host", None)
+    if host is None or host[0] is not states:
+        h_rs1 = np.ascontiguousarray(a.h_row_splits1, dtype=np.int32)
+        host = a._band_host = (states, h_rs1, np.ascontiguousarray(a.h_arc_splits, dtype=np.int32),
+                               int(np.diff(h_rs1).max(initial=0)))
+    _, h_rs1, h_as, most_states = host
+    if most_states > 512:
         return None
     frames = np.diff(b_fsas.h_row_splits) - 1
     first = src[1]
@@ -645,7 +651,6 @@ def _band_loss_args_uncached(a_fsas: Fsa, b_fsas: DenseFsaVec,
         frames, first = frames[h_map], first[h_map]
     frames = np.ascontiguousarray(frames, dtype=np.int32)
     first = np.ascontiguousarray(first, dtype=np.int32)
-    h_as = np.ascontiguousarray(a.h_arc_splits, dtype=np.int32)
     args = _lib.BandLossArgs(
         num_fsas=a.num_fsas, num_states=a.num_states, a_row_splits2=_lib.ptr(a._row_splits2),
         h_a_row_splits1=h_rs1.ctypes.data, h_a_arc_splits=h_as.ctypes.data,
@@ -729,6 +734,42 @@ class _BandTotScoresFunction(torch.autograd.Function):
                 stride, _lib.ptr(grad_a), _lib.ptr(grad_b), _lib.ptr(ctx.grad_rows),
                 ctx.grad_pitch, ctx.grad_col_off, _lib.stream_of(dev)))
         return None, None, None, None, grad_a, grad_b
+
+
+class _BandNegSumFunction(torch.autograd.Function):
+    """`-tot_scores.sum(dtype=torch.float32)` over `_BandTotScoresFunction` as ONE node of
+    the autograd graph (the `reduction="sum"` of k2/python/k2/ctc_loss.py:72-84 on the band
+    path): the same kernels, two nodes less to build in the forward and to run in the
+    backward, on the thread that feeds the GPU."""
+
+    @staticmethod
+    def forward(ctx, a_fsas: Fsa, b_fsas: DenseFsaVec, band, use_double_scores: bool,
+                unused_scores_a: torch.Tensor, unused_scores_b: torch.Tensor) -> torch.Tensor:
+        tot = _BandTotScoresFunction.forward(ctx, a_fsas, b_fsas, band, use_double_scores,
+                                             unused_scores_a, unused_scores_b)
+        ctx.tot_shape = tot.shape
+        # (-1 * tot_scores).to(float32).sum() of the reference: the reduction casts every
+        # element before adding, and negation commutes with rounding, so the bits are the same
+        return -tot.sum(dtype=torch.float32)
+
+    @staticmethod
+    def backward(ctx, loss_grad: torch.Tensor):
+        tot_grad = (-loss_grad).to(torch.float64).expand(ctx.tot_shape)  # stride 0
+        return _BandTotScoresFunction.backward(ctx, tot_grad)
+
+
+def band_ctc_loss_sum(a_fsas: Fsa, b_fsas: DenseFsaVec, output_beam: float,
+                      use_double_scores: bool = True) -> Optional[torch.Tensor]:
+    """`-intersect_dense_tot_scores(...).sum(dtype=torch.float32)` on the band kernels, or
+    None when they do not take these inputs."""
+    args = _band_loss_args(a_fsas, b_fsas, None, output_beam, 15000000, 1073741824)
+    if args is None or BAND_VERIFY:
+        return None
+    src = b_fsas._source
+    from_log_probs = src[0].requires_grad and src[0].dtype == torch.float32
+    scores_b = src[0] if (from_log_probs or b_fsas._scores is None) else b_fsas.scores
+    return _BandNegSumFunction.apply(a_fsas, b_fsas, args, use_double_scores, a_fsas.scores,
+                                     scores_b)
 
 
 def band_loss_supported(a_fsas: Fsa, b_fsas: DenseFsaVec,

@@ -4,7 +4,7 @@ from typing import Optional
 import torch
 import torch.nn as nn
 
-from .autograd import (band_loss_supported, dense_loss_supported, intersect_dense,
+from .autograd import (band_ctc_loss_sum, band_loss_supported, dense_loss_supported, intersect_dense,
                        intersect_dense_tot_scores)
 from .dense_fsa_vec import DenseFsaVec
 from .fsa import Fsa
@@ -35,6 +35,11 @@ class CtcLoss(nn.Module):
     def forward(self, decoding_graph: Fsa, dense_fsa_vec: DenseFsaVec,
                 delay_penalty: float = 0.0,
                 target_lengths: Optional[torch.Tensor] = None) -> torch.Tensor:
+        if FUSED_LOSS and delay_penalty <= 0.0 and self.reduction == "sum":
+            loss = band_ctc_loss_sum(decoding_graph, dense_fsa_vec, self.output_beam,
+                                     self.use_double_scores)
+            if loss is not None:
+                return loss
         if FUSED_LOSS and delay_penalty <= 0.0 and (
                 band_loss_supported(decoding_graph, dense_fsa_vec)
                 or (dense_fsa_vec.num_cols <= FUSED_MAX_CLASSES

@@ -95,16 +95,22 @@ class DenseFsaVec(object):
         assert allow_truncate >= 0
 
         N, T, C = log_probs.shape
-        seg = supervision_segments.numpy().astype(np.int64)
+        seg = supervision_segments.numpy()  # int32 [num_segs, 3]: sequence, start, duration
         num_segs = seg.shape[0]
-        seq, start, end = seg[:, 0], seg[:, 1], seg[:, 1] + seg[:, 2]
+        seq, start = seg[:, 0], seg[:, 1]
+        dur = seg[:, 2]
+        truncated = False
         if num_segs:
-            assert seq.min() >= 0 and seq.max() < N
-            assert start.min() >= 0 and start.max() < T
-            assert seg[:, 2].min() >= 0
-            assert end.max() <= T + allow_truncate
-        # durations after truncation; every segment gets one extra (final) row
-        dur = np.minimum(end, T) - start
+            # (few numpy calls: this runs on the thread that feeds the GPU, every step)
+            top = seg.max(axis=0)
+            assert seg.min() >= 0 and top[0] < N and top[1] < T
+            if int(top[1]) + int(top[2]) > T:  # only then can a segment pass the end
+                end = start.astype(np.int64) + dur
+                assert end.max() <= T + allow_truncate
+                # durations after truncation
+                dur = (np.minimum(end, T) - start).astype(np.int32)
+                truncated = True
+        # every segment gets one extra (final) row
         row_splits = np.zeros(num_segs + 1, dtype=np.int32)
         np.cumsum(dur + 1, out=row_splits[1:])
         rows = int(row_splits[-1])
@@ -113,13 +119,15 @@ class DenseFsaVec(object):
         if log_probs.is_cuda:
             # one kernel writes the whole matrix; two segments that touch the same
             # frame make the backward use atomic adds
-            first = seq * T + start
+            first = seq * np.int32(T) + start if N * T < 2**31 else seq.astype(np.int64) * T + start
             if num_segs == 0 or np.bincount(seq, minlength=N).max() <= 1:
                 overlapping = False  # at most one segment per sequence
             else:
                 order = np.argsort(first, kind="stable")
                 overlapping = bool(np.any((first + dur)[order][:-1] > first[order][1:]))
-            eff = np.stack([seq, start, dur], axis=1).astype(np.int32)
+            # (a copy: the caller's tensor may change before the scores are made)
+            eff = seg.copy() if not truncated else \
+                np.stack([seq, start, dur], axis=1).astype(np.int32)
             fn = _LogSoftmaxDenseFunction if _logits else _DenseFsaVecFunction
             # The score matrix, and the device copy of the row splits, are made on first
             # use: a loss that reads the log-probs directly (k2b200_band_loss_*) needs
@@ -133,7 +141,7 @@ class DenseFsaVec(object):
                 # gradient straight to it (k2b200_band_loss_*,
                 # k2b200_dense_loss_backward_log_probs): the tensor and, per
                 # sequence, the row of its first frame
-                self._source = (log_probs, first.astype(np.int32))
+                self._source = (log_probs, first.astype(np.int32, copy=False))
             return
         else:
             if _logits:
@@ -144,8 +152,8 @@ class DenseFsaVec(object):
             index = np.zeros(rows, dtype=np.int64)
             for k in range(seg.shape[0]):
                 r0 = int(row_splits[k])
-                index[r0:r0 + int(dur[k])] = np.arange(seg[k, 1], seg[k, 1] + dur[k]) + \
-                    seg[k, 0] * T
+                index[r0:r0 + int(dur[k])] = np.arange(int(seg[k, 1]), int(seg[k, 1]) + int(dur[k])) + \
+                    int(seg[k, 0]) * T
             scores = torch.empty(rows, C + 1, dtype=log_probs.dtype, device=device)
             scores[:, 1:] = log_probs.reshape(-1, C).index_select(0, torch.from_numpy(index))
             scores[:, 0] = float('-inf')
