@@ -1370,7 +1370,7 @@ BandGrad(const BandInfo *__restrict__ infos, const BandArc *__restrict__ tabf,
 // ---------------------------------------------------------------------------
 struct BandLayout {
   std::vector<BandInfo> infos;
-  int64_t grid_elems = 0, grid_states = 0, levels = 0;
+  int64_t grid_elems = 0, reachable_states = 0, levels = 0;
   long long arc_frames = 0;
   int32_t max_states = 0, max_frames = 0;
   int32_t vit_threads = 32, vit_frames = 0, vit_batches = 0, xch_pad = 0;
@@ -1414,7 +1414,15 @@ static int32_t MakeBandLayout(const k2b200_band_loss_args *a, BandLayout *L) {
     f.level_off = (int32_t)levels;
     f.grid_off = grid;
     grid += (int64_t)(f.frames + 2) * f.pitch;
-    L->grid_states += (int64_t)(f.frames + 2) * f.num_states;
+    {
+      // States that can survive: level l (0 .. R = T + 1) holds state s only if the start
+      // state reaches it (arcs advance by at most two states: s <= 2 l) and it reaches
+      // the last state m = S - 1 at level R (m - s <= 2 (R - l)).  Summed over the
+      // levels, with k = m / 2: the grid without two triangles of k (k + 1) states.
+      const int64_t S = f.num_states, m = S - 1, R = (int64_t)f.frames + 1, k = m / 2;
+      L->reachable_states += (S > 0 && 2 * R >= m) ? 2 * k * (k + 1) + (R - 2 * k - 1) * m + R + 1
+                                              : (R + 1) * S;
+    }
     levels += f.frames + 2;
     L->max_states = std::max(L->max_states, f.num_states);
     L->max_frames = std::max(L->max_frames, f.frames);
@@ -1634,10 +1642,11 @@ int32_t k2b200_band_loss_forward(const k2b200_band_loss_args *args, void *worksp
     K2B_CUDA_OK(cudaGetLastError());
   }
   // The lattice is never built, but its size still decides the beam
-  // (intersect_dense.cu:300-320).  The grid bounds it: the host reads the counts only
-  // when that bound does not already satisfy the limits, and after it has launched the
-  // recursions, which in the rare case of a reduction run again.
-  const bool need_count = L.grid_states > args->max_states || L.arc_frames > args->max_arcs;
+  // (intersect_dense.cu:300-320).  The grid bounds it (for the states: the part of the grid
+  // that lies both behind the start state and before the last one): the host reads the
+  // counts only when that bound does not already satisfy the limits, and after it has
+  // launched the recursions, which in the rare case of a reduction run again.
+  const bool need_count = L.reachable_states > args->max_states || L.arc_frames > args->max_arcs;
   float beam = args->output_beam;
   bool join_side = false;
   struct JoinOnExit {  // also on error returns: the caller may free the buffer being cleared

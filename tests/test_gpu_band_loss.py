@@ -281,6 +281,69 @@ def test_beam_reduction_under_a_state_limit():
     ref_tot = lat.get_tot_scores(True, True).cpu().numpy()
     tot, _, _ = run(a, lp, seg, 50.0, max_states=limit)
     assert close(tot, ref_tot, rtol=1e-6, atol=1e-6)
+    # limits around the number of survivors, around the part of the grid that the start
+    # state reaches and that reaches the last state (below that the host reads the counts,
+    # from there on it does not) and up to the whole grid
+    S = np.diff(a.row_splits1).astype(np.int64)
+    T = seg[:, 2].numpy().astype(np.int64)
+    grid = int(((T + 2) * S).sum())
+    for limit in sorted({full.num_states - 1, full.num_states, full.num_states + 1,
+                         (full.num_states + grid) // 2, grid - 1, grid}):
+        lat, _, _ = intersect_raw(host_to_fsa(a), dense, 50.0, max_states=limit)
+        want = oracle.intersect_dense(a, scores, brs, 50.0, max_states=limit)
+        assert lat.arcs.num_states == want.num_states, limit
+        ref_tot = lat.get_tot_scores(True, True).cpu().numpy()
+        tot, _, _ = run(a, lp, seg, 50.0, max_states=limit)
+        assert close(tot, ref_tot, rtol=1e-6, atol=1e-6), limit
+
+
+def test_state_limit_at_the_number_of_reachable_grid_states():
+    # complete band graphs, zero scores, a beam that keeps everything: the survivors are
+    # all but a few of the grid states that the start state reaches and that reach the
+    # last state, which is the bound from which on the host does not read the counts.
+    # Limits on both sides of the survivors and of that bound.
+    import k2_b200 as k2
+    from gpu_util import host_to_fsa, intersect_raw
+    rng = np.random.default_rng(8)
+    C = 8
+    rs1, rs2, rows = [0], [0], []
+    for ns in (9, 14, 6, 2):
+        lab = rng.integers(0, C, size=ns)
+        lab[ns - 1] = -1
+        for s in range(ns - 1):
+            for d in (0, 1, 2):
+                if s + d <= ns - 1:
+                    rows.append((s, s + d, int(lab[s + d]), 0.0))
+            rs2.append(len(rows))
+        rs2.append(len(rows))
+        rs1.append(rs1[-1] + ns)
+    r = np.array(rows, dtype=np.float64).reshape(-1, 4)
+    a = HostFsaVec(np.asarray(rs1, np.int32), np.asarray(rs2, np.int32),
+                   make_arcs(r[:, 0].astype(np.int32), r[:, 1].astype(np.int32),
+                             r[:, 2].astype(np.int32), r[:, 3].astype(np.float32)))
+    x = rng.normal(size=(4, 12, C)).astype(np.float32)
+    lp = torch.from_numpy(
+        x - np.log(np.exp(x.astype(np.float64)).sum(-1, keepdims=True)).astype(np.float32))
+    # (every graph can reach its last state within its frames)
+    seg = torch.tensor([[0, 0, 12], [1, 0, 9], [2, 0, 9], [3, 0, 3]], dtype=torch.int32)
+    scores, brs = host_scores(lp, seg)
+    reachable = 0
+    for S, T in zip((9, 14, 6, 2), seg[:, 2].tolist()):
+        m, R = S - 1, T + 1
+        reachable += sum(min(m, 2 * l) - max(0, m - 2 * (R - l)) + 1 for l in range(R + 1))
+    beam = 1.0e4
+    kept = oracle.intersect_dense(a, scores, brs, beam).num_states
+    assert kept <= reachable
+    dense = k2.DenseFsaVec(lp.to(DEV), seg)
+    for limit in sorted({kept - 1, kept, (kept + reachable) // 2, reachable - 1, reachable,
+                         reachable + 1}):
+        want = oracle.intersect_dense(a, scores, brs, beam, max_states=limit)
+        lat, _, _ = intersect_raw(host_to_fsa(a), dense, beam, max_states=limit)
+        assert lat.arcs.num_states == want.num_states, limit
+        ref_tot = lat.get_tot_scores(True, True).cpu().numpy()
+        tot, _, _ = run(a, lp, seg, beam, max_states=limit)
+        assert close(tot, ref_tot, rtol=1e-6, atol=1e-6), limit
+    assert oracle.intersect_dense(a, scores, brs, beam, max_states=kept - 1).num_states < kept
 
 
 def test_graphs_that_are_not_band_graphs_take_the_general_kernels():
