@@ -465,7 +465,12 @@ int32_t k2b200_dense_loss_backward_log_probs(const k2b200_intersect_args *args, 
  *     k2b200_last_error() says which.  Host-side only.
  *   k2b200_band_loss_forward: tot_scores[num_fsas] (device, float64; -inf for a graph
  *     with no surviving path; NaN if a copy into shared memory timed out, see
- *     k2b200_band_loss_status).  The workspace keeps what the backward needs.
+ *     k2b200_band_loss_status).  The workspace keeps what the backward needs.  The call
+ *     waits on the host (for the numbers of surviving states and arcs, behind the kernels it
+ *     has already launched) only when max_states is below the number of grid states that
+ *     the start state can reach and that can reach the last state, or max_arcs below
+ *     (frames + 1) x arcs summed over the graphs; otherwise no reduction of the beam is
+ *     possible and the call is asynchronous.
  *   k2b200_band_loss_backward: with tot_grad[i * tot_grad_stride] = dL/dtot[i] (device,
  *     float64), ADDS dL/d(dense score) to grad_b[(grad_row0[i] + frame) * grad_pitch +
  *     label + grad_col_off] (grad_row0: device, one per graph; NULL = h_first_row as the

@@ -206,6 +206,38 @@ def test_long_transcripts_sixteen_states_per_lane():
     compare(fsa_to_host(graphs), torch.from_numpy(x), seg, 10.0, tag="long")
 
 
+def test_summed_ctc_loss_as_one_node_equals_the_composition():
+    # ctc_loss(reduction="sum") on the band path is one autograd node; the same numbers
+    # and gradients as -tot_scores.sum() composed from its parts, for a loss that is scaled
+    # before the backward pass and for float32 total scores
+    import k2_b200 as k2
+    from k2_b200.fsa_algo import ctc_graph
+    rng = np.random.default_rng(21)
+    C, T, n = 12, 30, 4
+    graphs = ctc_graph([rng.integers(1, C, size=int(L)).tolist() for L in (9, 7, 4, 1)],
+                       device=DEV)
+    x = rng.normal(size=(n, T, C)).astype(np.float32)
+    x = x - np.log(np.exp(x.astype(np.float64)).sum(-1, keepdims=True)).astype(np.float32)
+    seg = torch.tensor([[0, 0, 30], [1, 0, 28], [2, 0, 20], [3, 0, 11]], dtype=torch.int32)
+    for use_double in (True, False):
+        grads = []
+        for fused in (True, False):
+            lp = torch.from_numpy(x).to(DEV).requires_grad_(True)
+            dense = k2.DenseFsaVec(lp, seg)
+            if fused:
+                loss = k2.ctc_loss(graphs, dense, output_beam=8.0, reduction="sum",
+                                   use_double_scores=use_double)
+                assert type(loss.grad_fn).__name__.startswith("_BandNegSum"), loss.grad_fn
+            else:
+                tot = k2.intersect_dense_tot_scores(graphs, dense, 8.0,
+                                                    use_double_scores=use_double)
+                loss = (-1 * tot).to(torch.float32).sum()
+            (loss * 3.0).backward()
+            grads.append((float(loss), lp.grad.cpu().numpy()))
+        assert grads[0][0] == grads[1][0]
+        assert np.array_equal(grads[0][1], grads[1][1])
+
+
 def _most_states_kept(a, lp, seg, beam):
     """Per sequence, the largest number of distinct graph states on one frame of the
     oracle's pruned lattice."""
