@@ -106,22 +106,34 @@ def ctc_graph(symbols: List[List[int]], modified: bool = False,
     return _fsa_vec_from_numpy(state_off, rs2, values, device, aux)
 
 
+def _ctc_graph_splits(lens: np.ndarray, sym: np.ndarray, modified: bool):
+    """(first symbol, first state, first arc) of every graph, int64 [n + 1] each.  A
+    transcript of L symbols gives 2L + 2 states; its symbol states have 3 arcs - 2 when
+    the next symbol of the transcript is the same and `modified` is False -, its blank
+    states 2.  (A few numpy calls over the flat symbols: this runs on the thread that
+    feeds the GPU whenever a batch brings new transcripts.)"""
+    n, tot = len(lens), len(sym)
+    sym_off = np.zeros(n + 1, dtype=np.int64)
+    np.cumsum(lens, out=sym_off[1:])
+    per_fsa = 5 * lens + 2
+    if tot > 1 and not modified:
+        same = sym[1:] == sym[:-1]
+        # the last symbol of a transcript always has its third arc (into the final state)
+        ends = sym_off[1:][lens > 0] - 1
+        same[ends[ends < tot - 1]] = False
+        at = np.searchsorted(np.flatnonzero(same), sym_off)  # symbols without one, before each
+        per_fsa -= at[1:] - at[:-1]
+    h_arc_splits = np.zeros(n + 1, dtype=np.int64)
+    np.cumsum(per_fsa, out=h_arc_splits[1:])
+    h_rs1 = 2 * sym_off + 2 * np.arange(n + 1)
+    return sym_off, h_rs1, h_arc_splits
+
+
 def _ctc_graph_cuda(lens: np.ndarray, sym: np.ndarray, modified: bool, device) -> Fsa:
     """The graphs are written by CUDA kernels; the host only counts the arcs (to
     size the outputs) and derives the per-FSA splits it needs later anyway."""
     n, tot = len(lens), int(lens.sum())
-    sym_off = np.zeros(n + 1, dtype=np.int64)
-    np.cumsum(lens, out=sym_off[1:])
-    fsa_of_sym = np.repeat(np.arange(n), lens)
-    is_last = (np.arange(tot) + 1) == sym_off[1:][fsa_of_sym]
-    nxt = np.where(is_last, -1, np.append(sym[1:], -1)) if tot else sym
-    has3 = np.ones(tot, dtype=np.int64) if modified else (sym != nxt).astype(np.int64)
-    per_fsa = np.zeros(n, dtype=np.int64)
-    np.add.at(per_fsa, fsa_of_sym, 4 + has3)
-    per_fsa += 2
-    h_arc_splits = np.zeros(n + 1, dtype=np.int64)
-    np.cumsum(per_fsa, out=h_arc_splits[1:])
-    h_rs1 = 2 * sym_off + 2 * np.arange(n + 1)
+    sym_off, h_rs1, h_arc_splits = _ctc_graph_splits(lens, sym, modified)
     num_arcs, num_states = int(h_arc_splits[-1]), int(h_rs1[-1])
     meta = _lib.upload_i32(np.concatenate([sym_off, sym]), device)
     i32 = dict(dtype=torch.int32, device=device)

@@ -264,3 +264,26 @@ def test_online_decoding_sizing_and_validation_need_no_gpu():
         assert lib.k2b200_online_decode_workspace_bytes(ctypes.byref(a),
                                                         ctypes.byref(nbytes)) != 0
         assert msg in lib.k2b200_last_error(), (bad, lib.k2b200_last_error())
+
+
+def test_splits_of_the_device_ctc_graphs_match_the_host_builder():
+    # the CUDA ctc_graph sizes its outputs from host prefix sums over the flat symbols; the
+    # host builder writes the same graphs arc by arc
+    import itertools
+    from k2_b200 import fsa_algo
+    rng = np.random.default_rng(0)
+    for trial in range(200):
+        n = int(rng.integers(1, 8))
+        symbols = [rng.integers(1, 4, size=int(rng.integers(0, 7))).tolist() for _ in range(n)]
+        if trial % 10 == 0:
+            symbols = [[] for _ in range(n)]
+        lens = np.fromiter(map(len, symbols), dtype=np.int64, count=n)
+        sym = np.fromiter(itertools.chain.from_iterable(symbols), dtype=np.int64,
+                          count=int(lens.sum()))
+        for modified in (False, True):
+            arcs = fsa_algo.ctc_graph(symbols, modified=modified, device="cpu").arcs
+            sym_off, rs1, arc_splits = fsa_algo._ctc_graph_splits(lens, sym, modified)
+            want_rs1 = np.asarray(arcs.h_row_splits1)
+            assert np.array_equal(sym_off[1:], np.cumsum(lens))
+            assert np.array_equal(rs1, want_rs1), symbols
+            assert np.array_equal(arc_splits, arcs._row_splits2.numpy()[want_rs1]), symbols
