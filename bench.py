@@ -18,6 +18,12 @@ only collective is one all-reduce of [loss, frames].
 --impl reference times the reference's own CPU code for the same path
 (oracle/_ref/libk2ref.so when present, else the C restatement in oracle/) on the
 host cores, single-threaded as the reference is by construction.
+
+Diagnostics of the N > 1 arm (environment): K2B_NCCL_REDUCE=1 exchanges [loss, frames]
+with torch.distributed on a helper thread instead of the peer-memory kernel,
+K2B_NO_REDUCE=1 runs the ranks side by side with no exchange at all, K2B_PEER_POLL=n
+bounds the kernel's wait for a peer to n polls, K2B_NO_NUMA_BIND=1 leaves the ranks
+unbound.
 """
 import argparse
 import json
