@@ -233,7 +233,7 @@ def test_summed_ctc_loss_as_one_node_equals_the_composition():
                                                     use_double_scores=use_double)
                 loss = (-1 * tot).to(torch.float32).sum()
             (loss * 3.0).backward()
-            grads.append((float(loss), lp.grad.cpu().numpy()))
+            grads.append((loss.detach().item(), lp.grad.cpu().numpy()))
         assert grads[0][0] == grads[1][0]
         assert np.array_equal(grads[0][1], grads[1][1])
 
