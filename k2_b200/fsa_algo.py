@@ -44,7 +44,8 @@ def ctc_graph(symbols: List[List[int]], modified: bool = False,
     n = len(symbols)
     lens = np.fromiter(map(len, symbols), dtype=np.int64, count=n)
     tot = int(lens.sum())
-    sym = np.fromiter(itertools.chain.from_iterable(symbols), dtype=np.int64, count=tot)
+    # (labels are int32 everywhere below; converting Python ints is what this call costs)
+    sym = np.fromiter(itertools.chain.from_iterable(symbols), dtype=np.int32, count=tot)
     assert not np.any(sym == -1), "symbols must not contain -1"
     if torch.device(device).type == "cuda":
         return _ctc_graph_cuda(lens, sym, modified, torch.device(device))
@@ -135,7 +136,10 @@ def _ctc_graph_cuda(lens: np.ndarray, sym: np.ndarray, modified: bool, device) -
     n, tot = len(lens), int(lens.sum())
     sym_off, h_rs1, h_arc_splits = _ctc_graph_splits(lens, sym, modified)
     num_arcs, num_states = int(h_arc_splits[-1]), int(h_rs1[-1])
-    meta = _lib.upload_i32(np.concatenate([sym_off, sym]), device)
+    h_meta = np.empty(n + 1 + tot, dtype=np.int32)
+    h_meta[:n + 1] = sym_off
+    h_meta[n + 1:] = sym
+    meta = _lib.upload_i32(h_meta, device)
     i32 = dict(dtype=torch.int32, device=device)
     rs1 = torch.empty(n + 1, **i32)
     rs2 = torch.empty(num_states + 1, **i32)
